@@ -1,0 +1,97 @@
+// Peer-memory signalling used by fused compute+collective kernels.
+//
+// Contract (the bounded-wait + status-word contract of the reference's CUDA-IPC
+// all-reduce, src/csrc/cuda_kernel_impl.cu:4788-4829, with its multi-block defects
+// fixed): a producer kernel stores its partial result into every peer's slot buffer,
+// every block fences, the LAST block to finish publishes `flag[peer][my_rank] = seq`
+// with release semantics at system scope. A consumer kernel's blocks each poll their
+// own GPU's flag words with acquire loads until all ranks reached `seq` or a time
+// budget runs out; on expiry the kernel records PK_COMM_TIMEOUT in a status word and
+// carries on with whatever data is there (the host checks the word after the step and
+// falls back to NCCL or raises). Nothing ever spins without a limit.
+#pragma once
+
+#include <stdint.h>
+
+#include "pk_common.cuh"
+
+#define PK_MAX_RANKS 8
+
+// One collective "site": where a producer pushes and how it signals.
+struct PkPush {
+  float* dst[PK_MAX_RANKS];      // peer r's slot buffer base ([world][rows][cols] fp32)
+  uint32_t* flag[PK_MAX_RANKS];  // peer r's flag array base ([world] words for this slot)
+  uint32_t* block_counter;       // local, zero between launches
+  const uint32_t* epoch;         // local device word, bumped once per forward
+  uint32_t sites_per_epoch;
+  uint32_t site;
+  int world;
+  int rank;
+};
+
+// What a consumer waits on before reading its local slot buffer.
+struct PkWait {
+  const uint32_t* flag;   // local flag array base ([world] words for this slot), or null
+  const uint32_t* epoch;  // local device word
+  uint32_t sites_per_epoch;
+  uint32_t site;
+  int world;
+  uint32_t* status;       // local status word, 0 = ok
+  uint32_t timeout_us;
+};
+
+#define PK_COMM_TIMEOUT 1u
+
+namespace pk {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint32_t comm_seq(const uint32_t* epoch, uint32_t sites, uint32_t site) {
+  return (*((const volatile uint32_t*)epoch)) * sites + site + 1u;
+}
+
+// Called by ONE thread of a block. Returns false if the budget ran out.
+__device__ __forceinline__ bool wait_all_ranks(const PkWait& w) {
+  if (w.flag == nullptr || w.world <= 1) return true;
+  const uint32_t target = comm_seq(w.epoch, w.sites_per_epoch, w.site);
+  const uint64_t t0 = global_timer_ns();
+  const uint64_t budget = (uint64_t)w.timeout_us * 1000ull;
+  for (int r = 0; r < w.world; ++r) {
+    // Sequence numbers only grow; a later one also satisfies the wait.
+    while ((int32_t)(ld_acquire_sys(w.flag + r) - target) < 0) {
+      if (global_timer_ns() - t0 > budget) {
+        atomicExch(w.status, PK_COMM_TIMEOUT);
+        return false;
+      }
+      __nanosleep(40);
+    }
+  }
+  return true;
+}
+
+// Called by every thread of every block after its last store of the producer kernel.
+__device__ __forceinline__ void publish_when_grid_done(const PkPush& p) {
+  if (p.world <= 1 && p.flag[0] == nullptr) return;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t nblocks = gridDim.x * gridDim.y * gridDim.z;
+    const uint32_t done = atomicAdd(p.block_counter, 1u) + 1u;
+    if (done == nblocks) {
+      *p.block_counter = 0u;  // ready for the next launch (stream-ordered)
+      __threadfence_system();
+      const uint32_t seq = comm_seq(p.epoch, p.sites_per_epoch, p.site);
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.flag[r] + p.rank, seq);
+    }
+  }
+}
+
+}  // namespace pk

@@ -1,0 +1,147 @@
+// Shared device helpers for every kernel of the library: dtype conversion, warp and
+// block reductions, FP8 E4M3 / FP4 E2M1 / E8M0 decoding, bounded waits.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define PK_API extern "C" __attribute__((visibility("default")))
+
+// Return codes of every launcher in the library.
+enum PkStatus : int {
+  PK_OK = 0,
+  PK_ERR_BAD_ARG = 1,      // shape / alignment contract broken, nothing launched
+  PK_ERR_CUDA = 2,         // a CUDA runtime call failed (see pk_last_cuda_error)
+  PK_ERR_TIMEOUT = 3,      // a bounded device wait gave up
+  PK_ERR_UNSUPPORTED = 4,
+};
+
+#define PK_CHECK_LAUNCH()                                   \
+  do {                                                      \
+    cudaError_t e__ = cudaGetLastError();                   \
+    if (e__ != cudaSuccess) {                               \
+      pk_set_last_cuda_error((int)e__);                     \
+      return PK_ERR_CUDA;                                   \
+    }                                                       \
+  } while (0)
+
+PK_API void pk_set_last_cuda_error(int code);
+PK_API int pk_last_cuda_error();
+
+namespace pk {
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) {
+  return __uint_as_float(((uint32_t)b) << 16);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum. `scratch` holds at least 33 floats. All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// Two FP8 E4M3 codes (low byte first) -> two floats.
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+__device__ __forceinline__ uint8_t float_to_e4m3(float v) {
+  return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+// E8M0 exponent-only scale: 2^(code - 127). Code 255 is NaN in the format; the
+// loaders never emit it.
+__device__ __forceinline__ float e8m0_to_float(uint8_t code) {
+  return __uint_as_float(code == 0 ? 0x00400000u : ((uint32_t)code) << 23);
+}
+
+// FP4 E2M1 value table {0, .5, 1, 1.5, 2, 3, 4, 6} with sign in bit 3.
+__device__ __forceinline__ float e2m1_to_float(uint32_t nib) {
+  const uint32_t mag = nib & 7u;
+  // 0,0.5,1,1.5,2,3,4,6
+  float v = mag < 2 ? 0.5f * (float)mag
+                    : __uint_as_float(((126u + (mag >> 1)) << 23) | ((mag & 1u) << 22));
+  return (nib & 8u) ? -v : v;
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) {
+  return x > 20.f ? x : log1pf(__expf(x));
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// 128-bit streaming load that does not pollute L1 (weights are read once).
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint2 ld_stream_u2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+               : "=r"(v.x), "=r"(v.y)
+               : "l"(p));
+  return v;
+}
+
+}  // namespace pk

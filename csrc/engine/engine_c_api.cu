@@ -1,0 +1,144 @@
+// C ABI of the native engine, used by the Python package (ctypes) and by external
+// callers. Every function returns 0 on success; pk_engine_last_error() gives the
+// message of the last failure on the calling thread.
+#include <cstring>
+#include <string>
+
+#include "json.hpp"
+#include "qwen_engine.hpp"
+
+#define PK_EAPI extern "C" __attribute__((visibility("default")))
+
+namespace {
+thread_local std::string g_err;
+
+template <class F>
+int guarded(F&& f) {
+  try {
+    f();
+    return 0;
+  } catch (const std::exception& e) {
+    g_err = e.what();
+    return 1;
+  } catch (...) {
+    g_err = "unknown error";
+    return 1;
+  }
+}
+}  // namespace
+
+PK_EAPI const char* pk_engine_last_error() { return g_err.c_str(); }
+
+// config_json: a Hugging Face style config (flat or under text_config), or the literal
+// "benchmark_27b" for the 64-layer benchmark shape.
+PK_EAPI void* pk_qwen_create(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
+                             int prefill_chunk, int use_cuda_graph, int decode_splits) {
+  pk::QwenEngine* eng = nullptr;
+  guarded([&] {
+    pk::QwenConfig cfg = std::string(config_json) == "benchmark_27b"
+                             ? pk::QwenConfig::benchmark_27b()
+                             : pk::QwenConfig::from_json(pk::Json::parse(std::string(config_json)));
+    pk::QwenEngineOptions opt;
+    opt.tp_rank = tp_rank;
+    opt.tp_world = tp_world;
+    opt.device = device;
+    if (max_context > 0) opt.max_context = max_context;
+    if (prefill_chunk > 0) opt.prefill_chunk = prefill_chunk;
+    if (decode_splits > 0) opt.decode_splits = decode_splits;
+    opt.use_cuda_graph = use_cuda_graph != 0;
+    eng = new pk::QwenEngine(cfg, opt);
+  });
+  return eng;
+}
+
+PK_EAPI void pk_qwen_destroy(void* h) { delete (pk::QwenEngine*)h; }
+
+PK_EAPI int pk_qwen_load_safetensors(void* h, const char* path) {
+  return guarded([&] { ((pk::QwenEngine*)h)->load_safetensors(path); });
+}
+
+PK_EAPI int pk_qwen_init_random(void* h, uint64_t seed, float sigma) {
+  return guarded([&] { ((pk::QwenEngine*)h)->init_random(seed, sigma); });
+}
+
+PK_EAPI int pk_qwen_reset(void* h) {
+  return guarded([&] { ((pk::QwenEngine*)h)->reset(); });
+}
+
+PK_EAPI int pk_qwen_prefill(void* h, const int* tokens, int n, int* first_token) {
+  return guarded([&] {
+    const int t = ((pk::QwenEngine*)h)->prefill(tokens, n);
+    if (first_token) *first_token = t;
+  });
+}
+
+PK_EAPI int pk_qwen_decode(void* h, int steps, int* out_tokens, int sync_each_step) {
+  return guarded([&] { ((pk::QwenEngine*)h)->decode(steps, out_tokens, sync_each_step != 0); });
+}
+
+PK_EAPI int pk_qwen_forward_rows(void* h, const int* tokens, int M, int* out_tokens) {
+  return guarded([&] { ((pk::QwenEngine*)h)->forward_rows(tokens, M, out_tokens); });
+}
+
+PK_EAPI int pk_qwen_copy_logits(void* h, float* out, int row) {
+  return guarded([&] { ((pk::QwenEngine*)h)->copy_logits(out, row); });
+}
+
+PK_EAPI int pk_qwen_vocab_local(void* h) { return ((pk::QwenEngine*)h)->vocab_local(); }
+PK_EAPI int pk_qwen_position(void* h) { return ((pk::QwenEngine*)h)->position(); }
+PK_EAPI int pk_qwen_last_token(void* h) { return ((pk::QwenEngine*)h)->last_token(); }
+PK_EAPI unsigned pk_qwen_comm_status(void* h) {
+  unsigned s = 0xffffffffu;
+  guarded([&] { s = ((pk::QwenEngine*)h)->comm_status(); });
+  return s;
+}
+PK_EAPI unsigned long long pk_qwen_weight_bytes(void* h) { return ((pk::QwenEngine*)h)->weight_bytes(); }
+
+// out[0] prefill_ms, out[1] decode_ms, out[2] prefill_tokens, out[3] decode_tokens, out[4] launches
+PK_EAPI void pk_qwen_timings(void* h, double* out) {
+  const pk::QwenTimings& t = ((pk::QwenEngine*)h)->timings();
+  out[0] = t.prefill_ms;
+  out[1] = t.decode_ms;
+  out[2] = t.prefill_tokens;
+  out[3] = t.decode_tokens;
+  out[4] = (double)t.kernel_launches;
+}
+
+// ---- peer memory plumbing (handles travel through the host control plane) ----
+PK_EAPI void* pk_qwen_comm_arena(void* h, unsigned long long* bytes) {
+  auto* e = (pk::QwenEngine*)h;
+  if (bytes) *bytes = e->comm_arena_bytes();
+  return e->comm_arena();
+}
+
+PK_EAPI int pk_qwen_set_peer_arenas(void* h, void* const* arenas) {
+  return guarded([&] { ((pk::QwenEngine*)h)->set_peer_arenas(arenas); });
+}
+
+PK_EAPI int pk_ipc_export(void* dev_ptr, void* handle_out_64) {
+  return guarded([&] {
+    cudaIpcMemHandle_t hd;
+    cudaError_t e = cudaIpcGetMemHandle(&hd, dev_ptr);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e));
+    static_assert(sizeof(hd) == 64, "ipc handle size");
+    memcpy(handle_out_64, &hd, 64);
+  });
+}
+
+PK_EAPI void* pk_ipc_open(const void* handle_64) {
+  void* p = nullptr;
+  guarded([&] {
+    cudaIpcMemHandle_t hd;
+    memcpy(&hd, handle_64, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e));
+  });
+  return p;
+}
+
+PK_EAPI int pk_ipc_close(void* p) {
+  return guarded([&] {
+    cudaError_t e = cudaIpcCloseMemHandle(p);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("cudaIpcCloseMemHandle: ") + cudaGetErrorString(e));
+  });
+}

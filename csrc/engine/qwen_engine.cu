@@ -1,0 +1,752 @@
+#include "qwen_engine.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <stdexcept>
+
+#include "pk_kernels.h"
+#include "safetensors.hpp"
+
+namespace pk {
+
+namespace {
+
+constexpr int kHeadDim = 128;
+constexpr int kSmallRows = 8;
+constexpr int kArgmaxBlocks = 64;
+
+void cuda_check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+float bf16_to_f32(uint16_t b) {
+  uint32_t u = ((uint32_t)b) << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+// ---- host-side shard cutting ----
+struct HostMat {
+  std::vector<uint8_t> data;
+  int rows = 0, cols = 0, elem = 1;
+};
+
+HostMat cut(const StTensor& t, int elem, int64_t r0, int64_t nr, int64_t c0, int64_t nc) {
+  if (t.shape.size() < 1) throw std::runtime_error("tensor rank: " + t.name);
+  const int64_t R = t.shape[0];
+  int64_t C = 1;
+  for (size_t i = 1; i < t.shape.size(); ++i) C *= t.shape[i];
+  if (r0 < 0 || r0 + nr > R || c0 < 0 || c0 + nc > C) throw std::runtime_error("shard out of range: " + t.name);
+  if ((size_t)(R * C * elem) != t.nbytes) throw std::runtime_error("dtype size mismatch: " + t.name);
+  HostMat m;
+  m.rows = (int)nr;
+  m.cols = (int)nc;
+  m.elem = elem;
+  m.data.resize((size_t)nr * nc * elem);
+  for (int64_t r = 0; r < nr; ++r)
+    memcpy(m.data.data() + (size_t)r * nc * elem, t.data + ((size_t)(r0 + r) * C + c0) * elem, (size_t)nc * elem);
+  return m;
+}
+
+void append_rows(HostMat& dst, const HostMat& src) {
+  if (dst.data.empty()) {
+    dst = src;
+    return;
+  }
+  if (dst.cols != src.cols || dst.elem != src.elem) throw std::runtime_error("append_rows: shape mismatch");
+  dst.data.insert(dst.data.end(), src.data.begin(), src.data.end());
+  dst.rows += src.rows;
+}
+
+std::vector<float> bf16_vec_to_f32(const HostMat& m) {
+  std::vector<float> out((size_t)m.rows * m.cols);
+  const uint16_t* p = (const uint16_t*)m.data.data();
+  for (size_t i = 0; i < out.size(); ++i) out[i] = bf16_to_f32(p[i]);
+  return out;
+}
+
+}  // namespace
+
+void QwenEngine::check(int status, const char* what) const {
+  if (status != 0) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "%s failed: status %d (cuda error %d)", what, status, pk_last_cuda_error());
+    throw std::runtime_error(buf);
+  }
+  ++launches_;
+}
+
+void* QwenEngine::dalloc(size_t bytes, bool weight) {
+  void* p = nullptr;
+  cuda_check(cudaMalloc(&p, std::max<size_t>(bytes, 16)), "cudaMalloc");
+  allocs_.push_back(p);
+  if (weight) weight_bytes_ += bytes;
+  return p;
+}
+
+void QwenEngine::alloc_fp8(Fp8Linear& l, int N, int K) {
+  l.N = N;
+  l.K = K;
+  l.w = (uint8_t*)dalloc((size_t)N * K, true);
+  l.scale = (float*)dalloc((size_t)((N + 127) / 128) * ((K + 127) / 128) * sizeof(float), true);
+}
+
+QwenEngine::QwenEngine(const QwenConfig& cfg, const QwenEngineOptions& opt) : cfg_(cfg), opt_(opt) {
+  cfg_.validate(opt.tp_world);
+  if (opt.tp_world > PK_MAX_RANKS) throw std::runtime_error("tp_world > 8");
+  cuda_check(cudaSetDevice(opt.device), "cudaSetDevice");
+  cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "stream");
+  cudaDeviceProp prop;
+  cuda_check(cudaGetDeviceProperties(&prop, opt.device), "props");
+  sm_count_ = prop.multiProcessorCount;
+  cuda_check(cudaEventCreate(&ev0_), "event");
+  cuda_check(cudaEventCreate(&ev1_), "event");
+
+  const int W = opt.tp_world;
+  hidden_ = (int)cfg_.hidden_size;
+  inter_l_ = (int)cfg_.intermediate_size / W;
+  vocab_l_ = (int)cfg_.vocab_size / W;
+  vocab_start_ = vocab_l_ * opt.tp_rank;
+  hq_l_ = cfg_.num_heads / W;
+  hkv_l_ = cfg_.num_kv_heads / W;
+  kh_l_ = cfg_.linear_key_heads / W;
+  vh_l_ = cfg_.linear_value_heads / W;
+  kd_l_ = kh_l_ * kHeadDim;
+  vd_l_ = vh_l_ * kHeadDim;
+  conv_c_l_ = 2 * kd_l_ + vd_l_;
+  ld_lin_ = (int)align_up(2 * kd_l_ + 2 * vd_l_ + 2 * vh_l_, 8);
+  ld_full_ = hq_l_ * 2 * kHeadDim + 2 * hkv_l_ * kHeadDim;
+  ld_proj_ = std::max(ld_lin_, ld_full_);
+  rows_cap_ = std::max(opt.prefill_chunk, kSmallRows);
+  sites_per_epoch_ = 2 * cfg_.num_layers + 1;
+
+  // ---- weights ----
+  layers_.resize(cfg_.num_layers);
+  for (int i = 0; i < cfg_.num_layers; ++i) {
+    QwenLayer& L = layers_[i];
+    L.full = cfg_.layer_is_full[i] != 0;
+    L.input_norm = (float*)dalloc(hidden_ * sizeof(float), true);
+    L.post_norm = (float*)dalloc(hidden_ * sizeof(float), true);
+    if (L.full) {
+      alloc_fp8(L.qkv, ld_full_, hidden_);
+      alloc_fp8(L.o_proj, hidden_, hq_l_ * kHeadDim);
+      L.q_norm = (float*)dalloc(kHeadDim * sizeof(float), true);
+      L.k_norm = (float*)dalloc(kHeadDim * sizeof(float), true);
+      const size_t kv = (size_t)hkv_l_ * opt.max_context * kHeadDim * 2;
+      L.kcache = dalloc(kv);
+      L.vcache = dalloc(kv);
+    } else {
+      alloc_fp8(L.in_proj, 2 * kd_l_ + 2 * vd_l_, hidden_);
+      L.in_proj_ab = dalloc((size_t)2 * vh_l_ * hidden_ * 2, true);
+      L.conv_w = (float*)dalloc((size_t)conv_c_l_ * 4 * sizeof(float), true);
+      L.A_log = (float*)dalloc(vh_l_ * sizeof(float), true);
+      L.dt_bias = (float*)dalloc(vh_l_ * sizeof(float), true);
+      L.lin_norm = (float*)dalloc(kHeadDim * sizeof(float), true);
+      alloc_fp8(L.out_proj, hidden_, vd_l_);
+      L.lin_state = (float*)dalloc((size_t)vh_l_ * kHeadDim * kHeadDim * sizeof(float));
+      L.conv_state = (float*)dalloc((size_t)conv_c_l_ * 3 * sizeof(float));
+    }
+    alloc_fp8(L.gate_up, 2 * inter_l_, hidden_);
+    alloc_fp8(L.down, hidden_, inter_l_);
+  }
+  embed_ = dalloc((size_t)cfg_.vocab_size * hidden_ * 2, true);
+  final_norm_ = (float*)dalloc(hidden_ * sizeof(float), true);
+  lm_head_ = dalloc((size_t)vocab_l_ * hidden_ * 2, true);
+  alloc_buffers();
+  reset();
+}
+
+void QwenEngine::alloc_buffers() {
+  const size_t R = rows_cap_;
+  for (int i = 0; i < 2; ++i) hidden_buf_[i] = dalloc(R * hidden_ * 2);
+  xn_ = dalloc(R * hidden_ * 2);
+  proj_ = dalloc(R * ld_proj_ * 2);
+  const int attn_w = std::max(vd_l_, hq_l_ * kHeadDim);
+  attn_out_ = dalloc(R * attn_w * 2);
+  q_buf_ = dalloc(R * hq_l_ * kHeadDim * 2);
+  mlp_h_ = dalloc(R * inter_l_ * 2);
+  const size_t ws_small = (size_t)kSmallRows * hq_l_ * opt_.decode_splits * (kHeadDim + 2);
+  const size_t ws_big = R * hq_l_ * 1 * (kHeadDim + 2);
+  attn_ws_ = (float*)dalloc(std::max(ws_small, ws_big) * sizeof(float));
+  logits_ = (float*)dalloc((size_t)kSmallRows * vocab_l_ * sizeof(float));
+  cand_val_ = (float*)dalloc(kSmallRows * kArgmaxBlocks * sizeof(float));
+  cand_idx_ = (int*)dalloc(kSmallRows * kArgmaxBlocks * sizeof(int));
+  best_val_ = (float*)dalloc(kSmallRows * sizeof(float));
+  best_idx_ = (int*)dalloc(kSmallRows * sizeof(int));
+  tokens_dev_ = (int*)dalloc(R * sizeof(int));
+  pos_dev_ = (int*)dalloc(R * sizeof(int));
+  next_tok_dev_ = (int*)dalloc(kSmallRows * sizeof(int));
+  out_cap_ = 1 << 16;
+  out_tokens_dev_ = (int*)dalloc(out_cap_ * sizeof(int));
+  out_counter_dev_ = (int*)dalloc(sizeof(int));
+  gemm_status_ = (uint32_t*)dalloc(sizeof(uint32_t));
+  cuda_check(cudaMemset(gemm_status_, 0, sizeof(uint32_t)), "memset");
+  cuda_check(cudaMallocHost((void**)&pinned_tok_, (size_t)std::max<int>(rows_cap_, out_cap_) * sizeof(int)), "pinned");
+
+  // comm arena: [slot0][slot1][flags0][flags1][cand val][cand idx][cand flags][epoch][status][counter]
+  const int W = opt_.tp_world;
+  size_t off = 0;
+  const size_t slot_bytes = (size_t)W * kSmallRows * hidden_ * sizeof(float);
+  for (int s = 0; s < 2; ++s) { off_slot_[s] = off; off = align_up(off + slot_bytes, 256); }
+  for (int s = 0; s < 2; ++s) { off_flag_[s] = off; off = align_up(off + PK_MAX_RANKS * 4, 256); }
+  off_cval_ = off; off = align_up(off + (size_t)W * kSmallRows * 4, 256);
+  off_cidx_ = off; off = align_up(off + (size_t)W * kSmallRows * 4, 256);
+  off_cflag_ = off; off = align_up(off + PK_MAX_RANKS * 4, 256);
+  off_epoch_ = off; off = align_up(off + 4, 256);
+  off_status_ = off; off = align_up(off + 4, 256);
+  off_counter_ = off; off = align_up(off + 4, 256);
+  arena_bytes_ = off;
+  arena_ = dalloc(arena_bytes_);
+  cuda_check(cudaMemset(arena_, 0, arena_bytes_), "memset arena");
+  for (int r = 0; r < PK_MAX_RANKS; ++r) peers_[r] = nullptr;
+  peers_[opt_.tp_rank] = arena_;
+  peer_cval_dev_ = (float**)dalloc(PK_MAX_RANKS * sizeof(void*));
+  peer_cidx_dev_ = (int**)dalloc(PK_MAX_RANKS * sizeof(void*));
+  peers_set_ = W == 1;
+  if (W == 1) {
+    void* a[1] = {arena_};
+    set_peer_arenas(a);
+  }
+}
+
+void QwenEngine::set_peer_arenas(void* const* arenas) {
+  float* cv[PK_MAX_RANKS] = {nullptr};
+  int* ci[PK_MAX_RANKS] = {nullptr};
+  for (int r = 0; r < opt_.tp_world; ++r) {
+    peers_[r] = r == opt_.tp_rank ? arena_ : arenas[r];
+    if (peers_[r] == nullptr) throw std::runtime_error("set_peer_arenas: null arena");
+    cv[r] = (float*)((char*)peers_[r] + off_cval_);
+    ci[r] = (int*)((char*)peers_[r] + off_cidx_);
+  }
+  cuda_check(cudaMemcpy(peer_cval_dev_, cv, sizeof cv, cudaMemcpyHostToDevice), "peer table");
+  cuda_check(cudaMemcpy(peer_cidx_dev_, ci, sizeof ci, cudaMemcpyHostToDevice), "peer table");
+  peers_set_ = true;
+  if (decode_graph_) {
+    cudaGraphExecDestroy(decode_graph_);
+    decode_graph_ = nullptr;
+  }
+}
+
+QwenEngine::~QwenEngine() {
+  cudaSetDevice(opt_.device);
+  cudaStreamSynchronize(stream_);
+  if (decode_graph_) cudaGraphExecDestroy(decode_graph_);
+  for (void* p : allocs_) cudaFree(p);
+  if (pinned_tok_) cudaFreeHost(pinned_tok_);
+  if (ev0_) cudaEventDestroy(ev0_);
+  if (ev1_) cudaEventDestroy(ev1_);
+  if (stream_) cudaStreamDestroy(stream_);
+}
+
+// ---------------------------------------------------------------------------------------
+// weights
+
+void QwenEngine::init_random(uint64_t seed, float sigma) {
+  uint64_t s = seed * 1000003ull + 17;
+  auto fp8 = [&](Fp8Linear& l) { check(pk_fill_fp8_gauss(l.w, l.scale, l.N, l.K, sigma, s++, stream_), "fill fp8"); };
+  auto f32 = [&](float* p, size_t n, float mean, float sd) { check(pk_fill_f32_gauss(p, n, mean, sd, s++, stream_), "fill f32"); };
+  auto b16 = [&](void* p, size_t n, float sd) { check(pk_fill_bf16_gauss(p, n, 0.f, sd, s++, stream_), "fill bf16"); };
+  for (auto& L : layers_) {
+    f32(L.input_norm, hidden_, 0.f, 0.02f);
+    f32(L.post_norm, hidden_, 0.f, 0.02f);
+    if (L.full) {
+      fp8(L.qkv);
+      fp8(L.o_proj);
+      f32(L.q_norm, kHeadDim, 0.f, 0.02f);
+      f32(L.k_norm, kHeadDim, 0.f, 0.02f);
+    } else {
+      fp8(L.in_proj);
+      b16(L.in_proj_ab, (size_t)2 * vh_l_ * hidden_, sigma);
+      f32(L.conv_w, (size_t)conv_c_l_ * 4, 0.f, 0.3f);
+      f32(L.A_log, vh_l_, 0.f, 0.5f);
+      f32(L.dt_bias, vh_l_, 0.f, 0.5f);
+      f32(L.lin_norm, kHeadDim, 1.f, 0.02f);
+      fp8(L.out_proj);
+    }
+    fp8(L.gate_up);
+    fp8(L.down);
+  }
+  // The embedding is replicated, so every rank must draw the same table.
+  check(pk_fill_bf16_gauss(embed_, (size_t)cfg_.vocab_size * hidden_, 0.f, sigma, seed * 7919ull + 1, stream_), "fill embed");
+  check(pk_fill_f32_gauss(final_norm_, hidden_, 0.f, 0.02f, seed * 7919ull + 2, stream_), "fill norm");
+  b16(lm_head_, (size_t)vocab_l_ * hidden_, sigma);
+  cuda_check(cudaStreamSynchronize(stream_), "init_random");
+}
+
+void QwenEngine::load_safetensors(const std::string& path) {
+  SafetensorsModel st(path);
+  const int W = opt_.tp_world, R = opt_.tp_rank;
+  std::string root = "model.language_model.";
+  if (!st.has(root + "embed_tokens.weight")) root = "model.";
+  if (!st.has(root + "embed_tokens.weight")) throw std::runtime_error("checkpoint has no embed_tokens.weight");
+
+  auto upload = [&](void* dst, const void* src, size_t n) {
+    cuda_check(cudaMemcpy(dst, src, n, cudaMemcpyHostToDevice), "upload");
+  };
+  auto norm_vec = [&](const std::string& name, float* dst, int64_t r0, int64_t n) {
+    const StTensor& t = st.get(name);
+    std::vector<float> v;
+    if (t.dtype == StDtype::BF16) v = bf16_vec_to_f32(cut(t, 2, r0, n, 0, t.numel() / t.shape[0]));
+    else if (t.dtype == StDtype::F32) {
+      HostMat m = cut(t, 4, r0, n, 0, t.numel() / t.shape[0]);
+      v.resize(m.data.size() / 4);
+      memcpy(v.data(), m.data.data(), m.data.size());
+    } else throw std::runtime_error("unsupported dtype for " + name);
+    upload(dst, v.data(), v.size() * sizeof(float));
+  };
+  // One FP8 linear shard: weight rows [r0, r0+nr), cols [c0, c0+nc) and the matching scales.
+  struct Piece { HostMat w; std::vector<float> s; int sb_rows, sb_cols; };
+  auto fp8_piece = [&](const std::string& name, int64_t r0, int64_t nr, int64_t c0, int64_t nc) {
+    const StTensor& w = st.get(name + ".weight");
+    if (w.dtype != StDtype::F8_E4M3) throw std::runtime_error(name + ".weight is not F8_E4M3");
+    if (r0 % 128 || c0 % 128 || nr % 128 || nc % 128)
+      throw std::runtime_error("FP8 shard of " + name + " is not aligned to the 128x128 scale blocks");
+    const StTensor& s = st.get(name + ".weight_scale_inv");
+    Piece p;
+    p.w = cut(w, 1, r0, nr, c0, nc);
+    p.sb_rows = (int)(nr / 128);
+    p.sb_cols = (int)(nc / 128);
+    if (s.dtype == StDtype::BF16) p.s = bf16_vec_to_f32(cut(s, 2, r0 / 128, nr / 128, c0 / 128, nc / 128));
+    else if (s.dtype == StDtype::F32) {
+      HostMat m = cut(s, 4, r0 / 128, nr / 128, c0 / 128, nc / 128);
+      p.s.resize(m.data.size() / 4);
+      memcpy(p.s.data(), m.data.data(), m.data.size());
+    } else throw std::runtime_error("unsupported scale dtype for " + name);
+    return p;
+  };
+  auto upload_fp8 = [&](Fp8Linear& dst, std::vector<Piece>& pieces) {
+    size_t roff = 0, soff = 0;
+    for (auto& p : pieces) {
+      if (p.w.cols != dst.K) throw std::runtime_error("fp8 upload: K mismatch");
+      upload(dst.w + roff * dst.K, p.w.data.data(), p.w.data.size());
+      upload(dst.scale + soff, p.s.data(), p.s.size() * sizeof(float));
+      roff += p.w.rows;
+      soff += p.s.size();
+    }
+    if ((int)roff != dst.N) throw std::runtime_error("fp8 upload: N mismatch");
+  };
+
+  {
+    const StTensor& e = st.get(root + "embed_tokens.weight");
+    if (e.dtype != StDtype::BF16) throw std::runtime_error("embed_tokens must be BF16");
+    upload(embed_, e.data, e.nbytes);
+    norm_vec(root + "norm.weight", final_norm_, 0, hidden_);
+    const StTensor& h = st.get("lm_head.weight");
+    HostMat hm = cut(h, 2, (int64_t)vocab_start_, vocab_l_, 0, hidden_);
+    upload(lm_head_, hm.data.data(), hm.data.size());
+  }
+  const int64_t KD = (int64_t)cfg_.linear_key_heads * kHeadDim, VD = (int64_t)cfg_.linear_value_heads * kHeadDim;
+  for (int i = 0; i < cfg_.num_layers; ++i) {
+    QwenLayer& L = layers_[i];
+    const std::string p = root + "layers." + std::to_string(i) + ".";
+    norm_vec(p + "input_layernorm.weight", L.input_norm, 0, hidden_);
+    norm_vec(p + "post_attention_layernorm.weight", L.post_norm, 0, hidden_);
+    if (L.full) {
+      const int64_t qrows = (int64_t)hq_l_ * 2 * kHeadDim, kvrows = (int64_t)hkv_l_ * kHeadDim;
+      std::vector<Piece> pcs;
+      pcs.push_back(fp8_piece(p + "self_attn.q_proj", R * qrows, qrows, 0, hidden_));
+      pcs.push_back(fp8_piece(p + "self_attn.k_proj", R * kvrows, kvrows, 0, hidden_));
+      pcs.push_back(fp8_piece(p + "self_attn.v_proj", R * kvrows, kvrows, 0, hidden_));
+      upload_fp8(L.qkv, pcs);
+      std::vector<Piece> o;
+      o.push_back(fp8_piece(p + "self_attn.o_proj", 0, hidden_, (int64_t)R * hq_l_ * kHeadDim, (int64_t)hq_l_ * kHeadDim));
+      upload_fp8(L.o_proj, o);
+      norm_vec(p + "self_attn.q_norm.weight", L.q_norm, 0, kHeadDim);
+      norm_vec(p + "self_attn.k_norm.weight", L.k_norm, 0, kHeadDim);
+    } else {
+      std::vector<Piece> pcs;
+      pcs.push_back(fp8_piece(p + "linear_attn.in_proj_qkv", (int64_t)R * kd_l_, kd_l_, 0, hidden_));
+      pcs.push_back(fp8_piece(p + "linear_attn.in_proj_qkv", KD + (int64_t)R * kd_l_, kd_l_, 0, hidden_));
+      pcs.push_back(fp8_piece(p + "linear_attn.in_proj_qkv", 2 * KD + (int64_t)R * vd_l_, vd_l_, 0, hidden_));
+      pcs.push_back(fp8_piece(p + "linear_attn.in_proj_z", (int64_t)R * vd_l_, vd_l_, 0, hidden_));
+      upload_fp8(L.in_proj, pcs);
+      std::vector<Piece> o;
+      o.push_back(fp8_piece(p + "linear_attn.out_proj", 0, hidden_, (int64_t)R * vd_l_, vd_l_));
+      upload_fp8(L.out_proj, o);
+      HostMat ab = cut(st.get(p + "linear_attn.in_proj_a.weight"), 2, (int64_t)R * vh_l_, vh_l_, 0, hidden_);
+      append_rows(ab, cut(st.get(p + "linear_attn.in_proj_b.weight"), 2, (int64_t)R * vh_l_, vh_l_, 0, hidden_));
+      upload(L.in_proj_ab, ab.data.data(), ab.data.size());
+      const StTensor& cw = st.get(p + "linear_attn.conv1d.weight");
+      HostMat c = cut(cw, 2, (int64_t)R * kd_l_, kd_l_, 0, 4);
+      append_rows(c, cut(cw, 2, KD + (int64_t)R * kd_l_, kd_l_, 0, 4));
+      append_rows(c, cut(cw, 2, 2 * KD + (int64_t)R * vd_l_, vd_l_, 0, 4));
+      std::vector<float> cf = bf16_vec_to_f32(c);
+      upload(L.conv_w, cf.data(), cf.size() * sizeof(float));
+      norm_vec(p + "linear_attn.A_log", L.A_log, (int64_t)R * vh_l_, vh_l_);
+      norm_vec(p + "linear_attn.dt_bias", L.dt_bias, (int64_t)R * vh_l_, vh_l_);
+      norm_vec(p + "linear_attn.norm.weight", L.lin_norm, 0, kHeadDim);
+    }
+    std::vector<Piece> gu;
+    gu.push_back(fp8_piece(p + "mlp.gate_proj", (int64_t)R * inter_l_, inter_l_, 0, hidden_));
+    gu.push_back(fp8_piece(p + "mlp.up_proj", (int64_t)R * inter_l_, inter_l_, 0, hidden_));
+    upload_fp8(L.gate_up, gu);
+    std::vector<Piece> d;
+    d.push_back(fp8_piece(p + "mlp.down_proj", 0, hidden_, (int64_t)R * inter_l_, inter_l_));
+    upload_fp8(L.down, d);
+  }
+  (void)W;
+  cuda_check(cudaDeviceSynchronize(), "load_safetensors");
+}
+
+// ---------------------------------------------------------------------------------------
+// state
+
+void QwenEngine::reset() {
+  for (auto& L : layers_) {
+    if (!L.full) {
+      cuda_check(cudaMemsetAsync(L.lin_state, 0, (size_t)vh_l_ * kHeadDim * kHeadDim * sizeof(float), stream_), "memset");
+      cuda_check(cudaMemsetAsync(L.conv_state, 0, (size_t)conv_c_l_ * 3 * sizeof(float), stream_), "memset");
+    }
+  }
+  cuda_check(cudaMemsetAsync(out_counter_dev_, 0, sizeof(int), stream_), "memset");
+  cuda_check(cudaStreamSynchronize(stream_), "reset");
+  pos_ = 0;
+  last_token_ = -1;
+  pending_site_ = -1;
+}
+
+std::unique_ptr<QwenEngine::Snapshot> QwenEngine::snapshot() {
+  auto s = std::make_unique<Snapshot>();
+  for (auto& L : layers_) {
+    if (L.full) continue;
+    const size_t sb = (size_t)vh_l_ * kHeadDim * kHeadDim * sizeof(float), cb = (size_t)conv_c_l_ * 3 * sizeof(float);
+    void* a = nullptr;
+    void* b = nullptr;
+    cuda_check(cudaMalloc(&a, sb), "snapshot alloc");
+    cuda_check(cudaMalloc(&b, cb), "snapshot alloc");
+    cuda_check(cudaMemcpyAsync(a, L.lin_state, sb, cudaMemcpyDeviceToDevice, stream_), "snapshot");
+    cuda_check(cudaMemcpyAsync(b, L.conv_state, cb, cudaMemcpyDeviceToDevice, stream_), "snapshot");
+    s->bufs.push_back(a);
+    s->bufs.push_back(b);
+  }
+  s->pos = pos_;
+  s->last_token = last_token_;
+  return s;
+}
+
+void QwenEngine::restore(const Snapshot& s) {
+  size_t i = 0;
+  for (auto& L : layers_) {
+    if (L.full) continue;
+    const size_t sb = (size_t)vh_l_ * kHeadDim * kHeadDim * sizeof(float), cb = (size_t)conv_c_l_ * 3 * sizeof(float);
+    cuda_check(cudaMemcpyAsync(L.lin_state, s.bufs[i++], sb, cudaMemcpyDeviceToDevice, stream_), "restore");
+    cuda_check(cudaMemcpyAsync(L.conv_state, s.bufs[i++], cb, cudaMemcpyDeviceToDevice, stream_), "restore");
+  }
+  pos_ = s.pos;
+  last_token_ = s.last_token;
+}
+
+void QwenEngine::free_snapshot(Snapshot& s) {
+  cudaStreamSynchronize(stream_);
+  for (void* p : s.bufs) cudaFree(p);
+  s.bufs.clear();
+}
+
+uint32_t QwenEngine::comm_status() {
+  uint32_t v[2] = {0, 0};
+  cuda_check(cudaMemcpy(&v[0], (char*)arena_ + off_status_, 4, cudaMemcpyDeviceToHost), "status");
+  cuda_check(cudaMemcpy(&v[1], gemm_status_, 4, cudaMemcpyDeviceToHost), "status");
+  return v[0] | (v[1] << 8);
+}
+
+void QwenEngine::copy_logits(float* out_host, int row) {
+  cuda_check(cudaStreamSynchronize(stream_), "sync");
+  cuda_check(cudaMemcpy(out_host, logits_ + (size_t)row * vocab_l_, (size_t)vocab_l_ * sizeof(float), cudaMemcpyDeviceToHost), "logits");
+}
+
+// ---------------------------------------------------------------------------------------
+// comm helpers
+
+float* QwenEngine::slot_parts(int site) const { return (float*)((char*)arena_ + off_slot_[site & 1]); }
+
+PkWait QwenEngine::make_wait(int site) const {
+  PkWait w{};
+  w.flag = opt_.tp_world > 1 ? (const uint32_t*)((char*)arena_ + off_flag_[site & 1]) : nullptr;
+  w.epoch = (const uint32_t*)((char*)arena_ + off_epoch_);
+  w.sites_per_epoch = sites_per_epoch_;
+  w.site = site;
+  w.world = opt_.tp_world;
+  w.status = (uint32_t*)((char*)arena_ + off_status_);
+  w.timeout_us = opt_.comm_timeout_us;
+  return w;
+}
+
+PkPush QwenEngine::make_push(int site) const {
+  PkPush p{};
+  for (int r = 0; r < opt_.tp_world; ++r) {
+    p.dst[r] = (float*)((char*)peers_[r] + off_slot_[site & 1]);
+    p.flag[r] = opt_.tp_world > 1 ? (uint32_t*)((char*)peers_[r] + off_flag_[site & 1]) : nullptr;
+  }
+  p.block_counter = (uint32_t*)((char*)arena_ + off_counter_);
+  p.epoch = (const uint32_t*)((char*)arena_ + off_epoch_);
+  p.sites_per_epoch = sites_per_epoch_;
+  p.site = site;
+  p.world = opt_.tp_world;
+  p.rank = opt_.tp_rank;
+  return p;
+}
+
+// ---------------------------------------------------------------------------------------
+// forward, weight-streaming path (1..8 rows)
+
+void QwenEngine::run_small(int M, bool all_logits) {
+  if (!peers_set_) throw std::runtime_error("peer arenas not registered");
+  const float eps = (float)cfg_.rms_norm_eps;
+  const int W = opt_.tp_world;
+  check(pk_bump_epoch((uint32_t*)((char*)arena_ + off_epoch_), stream_), "epoch");
+  check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hidden_buf_[cur_], nullptr, stream_), "embedding");
+  int pending = -1;  // site whose partial sums still wait to be added to the residual stream
+
+  auto consume = [&](const Fp8Linear* w, const void* wb, int nb, const float* gamma, int epi, void* y, int ldy,
+                     const PkPush* push) {
+    // x = hidden (+ pending partials) -> norm -> linear. The summed hidden goes to the other buffer.
+    const float* parts = pending >= 0 ? slot_parts(pending) : nullptr;
+    PkWait wt = make_wait(pending >= 0 ? pending : 0);
+    void* hout = pending >= 0 ? hidden_buf_[cur_ ^ 1] : nullptr;
+    check(pk_matvec(w ? w->w : nullptr, w ? w->scale : nullptr, wb, w ? w->N : 0, nb, hidden_, M, hidden_buf_[cur_], parts,
+                    W, hout, gamma, 1, eps, pending >= 0 ? &wt : nullptr, epi, y, ldy, push, sm_count_, stream_),
+          "matvec(consume)");
+    if (pending >= 0) cur_ ^= 1;
+    pending = -1;
+  };
+  auto produce = [&](const Fp8Linear& w, const void* x, int site) {
+    PkPush ps = make_push(site);
+    check(pk_matvec(w.w, w.scale, nullptr, w.N, 0, w.K, M, x, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 3,
+                    nullptr, hidden_, &ps, sm_count_, stream_),
+          "matvec(produce)");
+    pending = site;
+  };
+
+  for (int i = 0; i < cfg_.num_layers; ++i) {
+    QwenLayer& L = layers_[i];
+    if (L.full) {
+      consume(&L.qkv, nullptr, 0, L.input_norm, 0, proj_, ld_proj_, nullptr);
+      check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, pos_dev_, L.q_norm, L.k_norm, eps,
+                                   cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache,
+                                   opt_.max_context, stream_),
+            "qk_norm_rope_append");
+      check(pk_gqa_decode(q_buf_, L.kcache, L.vcache, pos_dev_, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
+                          1.f / sqrtf((float)kHeadDim), opt_.decode_splits, opt_.attention_window, opt_.attention_sink,
+                          attn_ws_, cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
+            "gqa_decode");
+      ++launches_;  // two kernels in that call
+      produce(L.o_proj, attn_out_, 2 * i);
+    } else {
+      consume(&L.in_proj, L.in_proj_ab, 2 * vh_l_, L.input_norm, 0, proj_, ld_proj_, nullptr);
+      check(pk_deltanet_seq(proj_, ld_proj_, M, kh_l_, vh_l_, kHeadDim, kHeadDim, L.conv_w, L.conv_state, L.A_log,
+                            L.dt_bias, L.lin_norm, eps, L.lin_state, attn_out_, stream_),
+            "deltanet_seq");
+      produce(L.out_proj, attn_out_, 2 * i);
+    }
+    consume(&L.gate_up, nullptr, 0, L.post_norm, 1, mlp_h_, inter_l_, nullptr);
+    produce(L.down, mlp_h_, 2 * i + 1);
+  }
+  // final norm + lm_head on every row (speculative verify) or on the last row only
+  if (all_logits || M == 1) {
+    consume(nullptr, lm_head_, vocab_l_, final_norm_, 2, logits_, vocab_l_, nullptr);
+    sample_rows(M, 0);
+  } else {
+    // Fold the pending partials into the hidden state first, then project the last row.
+    const float* parts = slot_parts(pending);
+    PkWait wt = make_wait(pending);
+    check(pk_rmsnorm(hidden_buf_[cur_], parts, W, M, hidden_, hidden_buf_[cur_], final_norm_, 1, eps, nullptr, &wt, stream_),
+          "fold");
+    pending = -1;
+    const char* last = (const char*)hidden_buf_[cur_] + (size_t)(M - 1) * hidden_ * 2;
+    check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, last, nullptr, 0, nullptr, final_norm_, 1, eps,
+                    nullptr, 2, logits_, vocab_l_, nullptr, sm_count_, stream_),
+          "lm_head");
+    sample_rows(1, 0);
+  }
+}
+
+// Greedy token of `M` logits rows -> next_tok_dev_[0..M).
+void QwenEngine::sample_rows(int M, int first_row) {
+  const int W = opt_.tp_world;
+  check(pk_argmax(logits_ + (size_t)first_row * vocab_l_, vocab_l_, M, vocab_l_, vocab_start_, kArgmaxBlocks, cand_val_,
+                  cand_idx_, best_val_, W == 1 ? next_tok_dev_ : best_idx_, stream_),
+        "argmax");
+  ++launches_;
+  if (W > 1) {
+    // Exchange {logit, token} of every rank through peer memory and merge (lowest id on ties).
+    const int site = 2 * cfg_.num_layers;
+    PkPush ps = make_push(site);
+    for (int r = 0; r < W; ++r) ps.flag[r] = (uint32_t*)((char*)peers_[r] + off_cflag_);
+    check(pk_cand_push(best_val_, best_idx_, M, &ps, peer_cval_dev_, peer_cidx_dev_, stream_), "cand_push");
+    PkWait wt = make_wait(site);
+    wt.flag = (const uint32_t*)((char*)arena_ + off_cflag_);
+    check(pk_cand_merge_wait((const float*)((char*)arena_ + off_cval_), (const int*)((char*)arena_ + off_cidx_), M, W,
+                             &wt, next_tok_dev_, stream_),
+          "cand_merge");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// forward, tensor-core path (more than 8 rows, one rank)
+
+void QwenEngine::run_chunk(int M) {
+  const float eps = (float)cfg_.rms_norm_eps;
+  void* hid = hidden_buf_[cur_];
+  check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hid, nullptr, stream_), "embedding");
+  auto gemm = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc) {
+    check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, stream_), "gemm_umma");
+  };
+  for (int i = 0; i < cfg_.num_layers; ++i) {
+    QwenLayer& L = layers_[i];
+    check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, L.input_norm, 1, eps, xn_, nullptr, stream_), "rmsnorm");
+    if (L.full) {
+      gemm(xn_, hidden_, L.qkv, 0, proj_, nullptr, ld_proj_);
+      check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, pos_dev_, L.q_norm, L.k_norm, eps,
+                                   cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache,
+                                   opt_.max_context, stream_),
+            "qk_norm_rope_append");
+      check(pk_gqa_decode(q_buf_, L.kcache, L.vcache, pos_dev_, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
+                          1.f / sqrtf((float)kHeadDim), 1, opt_.attention_window, opt_.attention_sink, attn_ws_,
+                          cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
+            "gqa_prefill");
+      ++launches_;
+      gemm(attn_out_, hq_l_ * kHeadDim, L.o_proj, 2, hid, hid, hidden_);
+    } else {
+      gemm(xn_, hidden_, L.in_proj, 0, proj_, nullptr, ld_proj_);
+      check(pk_gemm_umma(xn_, hidden_, L.in_proj_ab, nullptr, 1, M, 2 * vh_l_, hidden_, 0,
+                         (char*)proj_ + (size_t)L.in_proj.N * 2, nullptr, ld_proj_, gemm_status_, stream_),
+            "gemm_umma(ab)");
+      check(pk_deltanet_seq(proj_, ld_proj_, M, kh_l_, vh_l_, kHeadDim, kHeadDim, L.conv_w, L.conv_state, L.A_log,
+                            L.dt_bias, L.lin_norm, eps, L.lin_state, attn_out_, stream_),
+            "deltanet_seq");
+      gemm(attn_out_, vd_l_, L.out_proj, 2, hid, hid, hidden_);
+    }
+    check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, L.post_norm, 1, eps, xn_, nullptr, stream_), "rmsnorm");
+    gemm(xn_, hidden_, L.gate_up, 1, mlp_h_, nullptr, inter_l_);
+    gemm(mlp_h_, inter_l_, L.down, 2, hid, hid, hidden_);
+  }
+  const char* last = (const char*)hid + (size_t)(M - 1) * hidden_ * 2;
+  check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, last, nullptr, 0, nullptr, final_norm_, 1, eps,
+                  nullptr, 2, logits_, vocab_l_, nullptr, sm_count_, stream_),
+        "lm_head");
+  sample_rows(1, 0);
+}
+
+// ---------------------------------------------------------------------------------------
+// public entry points
+
+int QwenEngine::prefill(const int* tokens_host, int n) {
+  if (n < 1) throw std::runtime_error("prefill: empty prompt");
+  if (pos_ + n + 1 > opt_.max_context) throw std::runtime_error("prefill: prompt exceeds max_context");
+  cuda_check(cudaEventRecord(ev0_, stream_), "event");
+  const long long l0 = launches_;
+  int done = 0;
+  while (done < n) {
+    int M = std::min(n - done, rows_cap_);
+    // More than one rank: the tensor-core path is single-rank for now, use row groups.
+    if (opt_.tp_world > 1) M = std::min(M, kSmallRows);
+    memcpy(pinned_tok_, tokens_host + done, (size_t)M * sizeof(int));
+    cuda_check(cudaMemcpyAsync(tokens_dev_, pinned_tok_, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, stream_), "h2d tokens");
+    check(pk_iota_int(pos_dev_, M, nullptr, pos_, stream_), "iota");
+    if (M <= kSmallRows) run_small(M, false);
+    else run_chunk(M);
+    // The pinned staging buffer is reused by the next chunk.
+    cuda_check(cudaStreamSynchronize(stream_), "prefill chunk");
+    pos_ += M;
+    done += M;
+  }
+  cuda_check(cudaMemcpyAsync(pinned_tok_, next_tok_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h token");
+  cuda_check(cudaEventRecord(ev1_, stream_), "event");
+  cuda_check(cudaStreamSynchronize(stream_), "prefill");
+  float ms = 0;
+  cudaEventElapsedTime(&ms, ev0_, ev1_);
+  timings_.prefill_ms = ms;
+  timings_.prefill_tokens = n;
+  timings_.kernel_launches += launches_ - l0;
+  last_token_ = pinned_tok_[0];
+  return last_token_;
+}
+
+void QwenEngine::capture_decode_graph() {
+  cudaGraph_t g = nullptr;
+  const long long l0 = launches_;
+  cuda_check(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal), "begin capture");
+  try {
+    check(pk_copy_int(next_tok_dev_, tokens_dev_, 1, stream_), "copy token");
+    run_small(1, true);
+    check(pk_add_int(pos_dev_, 1, 1, stream_), "advance pos");
+    check(pk_store_token(next_tok_dev_, out_tokens_dev_, out_counter_dev_, out_cap_, stream_), "store token");
+  } catch (...) {
+    cudaStreamEndCapture(stream_, &g);
+    if (g) cudaGraphDestroy(g);
+    throw;
+  }
+  cuda_check(cudaStreamEndCapture(stream_, &g), "end capture");
+  graph_nodes_ = launches_ - l0;
+  launches_ = l0;
+  cuda_check(cudaGraphInstantiate(&decode_graph_, g, 0), "graph instantiate");
+  cudaGraphDestroy(g);
+}
+
+void QwenEngine::decode(int steps, int* out_host, bool sync_each_step) {
+  if (last_token_ < 0) throw std::runtime_error("decode before prefill");
+  if (steps < 1) return;
+  if (pos_ + steps + 1 > opt_.max_context) throw std::runtime_error("decode: exceeds max_context");
+  if (steps > out_cap_) throw std::runtime_error("decode: too many steps in one call");
+  // The hidden ping-pong index must be the same at capture and at every replay: a forward
+  // flips it an even number of times only if it starts from a fixed buffer.
+  cur_ = 0;
+  if (opt_.use_cuda_graph && decode_graph_ == nullptr) capture_decode_graph();
+  cur_ = 0;
+  cuda_check(cudaMemsetAsync(out_counter_dev_, 0, sizeof(int), stream_), "memset");
+  check(pk_iota_int(pos_dev_, 1, nullptr, pos_, stream_), "iota");
+  --launches_;
+  cuda_check(cudaEventRecord(ev0_, stream_), "event");
+  const long long l0 = launches_;
+  for (int s = 0; s < steps; ++s) {
+    if (decode_graph_) {
+      cuda_check(cudaGraphLaunch(decode_graph_, stream_), "graph launch");
+      launches_ += graph_nodes_;
+    } else {
+      cur_ = 0;
+      check(pk_copy_int(next_tok_dev_, tokens_dev_, 1, stream_), "copy token");
+      run_small(1, true);
+      check(pk_add_int(pos_dev_, 1, 1, stream_), "advance pos");
+      check(pk_store_token(next_tok_dev_, out_tokens_dev_, out_counter_dev_, out_cap_, stream_), "store token");
+    }
+    if (sync_each_step) {
+      cuda_check(cudaMemcpyAsync(pinned_tok_ + s, next_tok_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h");
+      cuda_check(cudaStreamSynchronize(stream_), "decode step");
+    }
+  }
+  if (!sync_each_step)
+    cuda_check(cudaMemcpyAsync(pinned_tok_, out_tokens_dev_, (size_t)steps * sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h");
+  cuda_check(cudaEventRecord(ev1_, stream_), "event");
+  cuda_check(cudaStreamSynchronize(stream_), "decode");
+  float ms = 0;
+  cudaEventElapsedTime(&ms, ev0_, ev1_);
+  timings_.decode_ms = ms;
+  timings_.decode_tokens = steps;
+  timings_.kernel_launches += launches_ - l0;
+  pos_ += steps;
+  last_token_ = pinned_tok_[steps - 1];
+  if (out_host) memcpy(out_host, pinned_tok_, (size_t)steps * sizeof(int));
+}
+
+void QwenEngine::forward_rows(const int* tokens_host, int M, int* out_tokens_host) {
+  if (M < 1 || M > kSmallRows) throw std::runtime_error("forward_rows: 1..8 rows");
+  if (pos_ + M + 1 > opt_.max_context) throw std::runtime_error("forward_rows: exceeds max_context");
+  memcpy(pinned_tok_, tokens_host, (size_t)M * sizeof(int));
+  cuda_check(cudaMemcpyAsync(tokens_dev_, pinned_tok_, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, stream_), "h2d");
+  check(pk_iota_int(pos_dev_, M, nullptr, pos_, stream_), "iota");
+  run_small(M, true);
+  cuda_check(cudaMemcpyAsync(pinned_tok_, next_tok_dev_, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h");
+  // decode() continues from slot 0 of the token buffer
+  if (M > 1) check(pk_copy_int(next_tok_dev_ + (M - 1), next_tok_dev_, 1, stream_), "copy token");
+  cuda_check(cudaStreamSynchronize(stream_), "forward_rows");
+  pos_ += M;
+  last_token_ = pinned_tok_[M - 1];
+  if (out_tokens_host) memcpy(out_tokens_host, pinned_tok_, (size_t)M * sizeof(int));
+}
+
+}  // namespace pk

@@ -1,0 +1,200 @@
+// Native inference engine for the hybrid Gated-DeltaNet / GQA decoder: weights (FP8
+// block-scaled Safetensors or random init), KV + recurrent state, chunked prefill, CUDA
+// graph decode, tensor parallelism over peer memory. Counterpart of the reference's
+// QwenEngine (cpp_engine/src/qwen_engine.cpp:295-557, 910-1303, 1733-2270) with a
+// different execution model: one fused launch per projection, collectives folded into the
+// producing and consuming kernels, and a captured graph per decode step.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../common/pk_comm.cuh"
+#include "qwen_config.hpp"
+
+namespace pk {
+
+struct QwenEngineOptions {
+  int tp_rank = 0;
+  int tp_world = 1;
+  int device = 0;
+  int max_context = 4096;
+  int prefill_chunk = 512;
+  int decode_splits = 8;       // context splits of the decode attention kernel
+  bool use_cuda_graph = true;
+  int attention_window = 0;    // 0 = full attention
+  int attention_sink = 0;
+  uint32_t comm_timeout_us = 2000000;
+};
+
+struct Fp8Linear {
+  uint8_t* w = nullptr;   // [N, K] e4m3
+  float* scale = nullptr; // [ceil(N/128), ceil(K/128)]
+  int N = 0, K = 0;
+};
+
+struct QwenLayer {
+  bool full = false;
+  float* input_norm = nullptr;
+  float* post_norm = nullptr;
+  // linear attention
+  Fp8Linear in_proj;           // q|k|v|z rows of this rank
+  void* in_proj_ab = nullptr;  // bf16 [2*Hv_l, hidden]
+  float* conv_w = nullptr;     // [C_l, 4]
+  float* A_log = nullptr;
+  float* dt_bias = nullptr;
+  float* lin_norm = nullptr;
+  Fp8Linear out_proj;
+  float* lin_state = nullptr;  // [Hv_l, 128, 128]
+  float* conv_state = nullptr; // [C_l, 3]
+  // full attention
+  Fp8Linear qkv;
+  float* q_norm = nullptr;
+  float* k_norm = nullptr;
+  Fp8Linear o_proj;
+  void* kcache = nullptr;      // bf16 [Hkv_l, ctx, 128]
+  void* vcache = nullptr;
+  // mlp
+  Fp8Linear gate_up;
+  Fp8Linear down;
+};
+
+struct QwenTimings {
+  double prefill_ms = 0;      // device time of the last prefill
+  double decode_ms = 0;       // device time of the last decode run
+  int prefill_tokens = 0;
+  int decode_tokens = 0;
+  long long kernel_launches = 0;  // launches issued (graph nodes count once per replay)
+};
+
+class QwenEngine {
+ public:
+  QwenEngine(const QwenConfig& cfg, const QwenEngineOptions& opt);
+  ~QwenEngine();
+  QwenEngine(const QwenEngine&) = delete;
+  QwenEngine& operator=(const QwenEngine&) = delete;
+
+  // Weights: from a checkpoint directory / file (this rank's shard is cut on the host), or
+  // N(0, sigma) values quantised on the device.
+  void load_safetensors(const std::string& path);
+  void init_random(uint64_t seed, float sigma);
+
+  // Peer memory. The arena holds the all-reduce slots, flags and sampler candidates; its
+  // address is exported to the other ranks, and theirs are registered here.
+  void* comm_arena() const { return arena_; }
+  size_t comm_arena_bytes() const { return arena_bytes_; }
+  void set_peer_arenas(void* const* arenas);  // [tp_world], entry tp_rank may be own
+
+  void reset();
+  // Runs the prompt in chunks; returns the first generated token (greedy).
+  int prefill(const int* tokens_host, int n);
+  // Greedy decode of `steps` tokens following the last generated one. Tokens are
+  // written to out_host (may be null). `sync_each_step` reads every token back as soon as
+  // its step ends (streaming); otherwise one read at the end.
+  void decode(int steps, int* out_host, bool sync_each_step);
+  // Verify-style forward over M (<= 8) given tokens at consecutive positions; returns
+  // the greedy token after each row. State advances by M tokens.
+  void forward_rows(const int* tokens_host, int M, int* out_tokens_host);
+
+  int position() const { return pos_; }
+  int last_token() const { return last_token_; }
+  const QwenTimings& timings() const { return timings_; }
+  uint32_t comm_status();
+  // fp32 logits of the last forward's final row: this rank's vocab shard.
+  void copy_logits(float* out_host, int row);
+  int vocab_local() const { return vocab_l_; }
+  const QwenConfig& config() const { return cfg_; }
+  const QwenEngineOptions& options() const { return opt_; }
+  size_t weight_bytes() const { return weight_bytes_; }
+  cudaStream_t stream() const { return stream_; }
+
+  // Recurrent-state snapshot (DeltaNet state + conv tails of every linear layer); KV is
+  // position indexed and needs no copy. Used by speculative decoding and the prefix cache.
+  struct Snapshot {
+    std::vector<void*> bufs;
+    int pos = 0;
+    int last_token = 0;
+  };
+  std::unique_ptr<Snapshot> snapshot();
+  void restore(const Snapshot& s);
+  void free_snapshot(Snapshot& s);
+
+ private:
+  void alloc_buffers();
+  void alloc_fp8(Fp8Linear& l, int N, int K);
+  void* dalloc(size_t bytes, bool weight = false);
+  void run_small(int M, bool all_logits);    // M <= 8 rows: weight-streaming path
+  void run_chunk(int M);                     // M > 8 rows: tensor-core path
+  void sample_rows(int M, int first_row);
+  void capture_decode_graph();
+  PkWait make_wait(int site) const;
+  PkPush make_push(int site) const;
+  float* slot_parts(int site) const;
+  void check(int status, const char* what) const;
+
+  QwenConfig cfg_;
+  QwenEngineOptions opt_;
+  cudaStream_t stream_ = nullptr;
+  int sm_count_ = 148;
+
+  // local (per rank) dims
+  int hidden_, inter_l_, vocab_l_, vocab_start_;
+  int hq_l_, hkv_l_, kh_l_, vh_l_, kd_l_, vd_l_, conv_c_l_;
+  int ld_lin_, ld_full_, ld_proj_;
+  int rows_cap_;  // rows of the activation buffers (prefill chunk)
+
+  std::vector<QwenLayer> layers_;
+  void* embed_ = nullptr;     // bf16 [vocab, hidden] (replicated)
+  float* final_norm_ = nullptr;
+  void* lm_head_ = nullptr;   // bf16 [vocab_l, hidden]
+  size_t weight_bytes_ = 0;
+  std::vector<void*> allocs_;
+
+  // activations
+  void* hidden_buf_[2] = {nullptr, nullptr};
+  int cur_ = 0;
+  void* xn_ = nullptr;
+  void* proj_ = nullptr;
+  void* attn_out_ = nullptr;
+  void* q_buf_ = nullptr;
+  void* mlp_h_ = nullptr;
+  float* attn_ws_ = nullptr;
+  float* logits_ = nullptr;   // [8, vocab_l]
+  float* cand_val_ = nullptr;
+  int* cand_idx_ = nullptr;
+  float* best_val_ = nullptr;
+  int* best_idx_ = nullptr;
+  int* tokens_dev_ = nullptr; // [rows_cap]
+  int* pos_dev_ = nullptr;    // [rows_cap]
+  int* next_tok_dev_ = nullptr;  // [8]
+  int* out_tokens_dev_ = nullptr;
+  int* out_counter_dev_ = nullptr;
+  int out_cap_ = 0;
+  uint32_t* gemm_status_ = nullptr;
+  int* pinned_tok_ = nullptr;   // pinned host staging for token ids / results
+
+  // comm arena layout (all inside arena_): slots, flags, sampler candidates, epoch, status
+  void* arena_ = nullptr;
+  size_t arena_bytes_ = 0;
+  size_t off_slot_[2], off_flag_[2], off_cval_, off_cidx_, off_cflag_, off_epoch_, off_status_, off_counter_;
+  void* peers_[PK_MAX_RANKS] = {nullptr};
+  float** peer_cval_dev_ = nullptr;
+  int** peer_cidx_dev_ = nullptr;
+  bool peers_set_ = false;
+  int sites_per_epoch_ = 0;
+  int pending_site_ = -1;   // site whose partials still have to be added to the hidden state
+
+  int pos_ = 0;
+  int last_token_ = -1;
+  cudaGraphExec_t decode_graph_ = nullptr;
+  long long graph_nodes_ = 0;
+  mutable long long launches_ = 0;
+  QwenTimings timings_;
+  cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+};
+
+}  // namespace pk

@@ -1,0 +1,267 @@
+// GQA attention for decode and speculative verify: fused per-head RMSNorm + partial RoPE
+// + KV append, split-context flash decode, and the merge that also applies the output
+// gate. Behavioural counterpart in the reference: cpp_engine/cuda/qwen_half_ops.cu:932-1158
+// (partial_rope, append_kv, gqa_scores / softmax / gqa_values as separate passes) and
+// cpp_engine/cuda/qwen_gqa_optimized.cu:253-376 (split + merge for long contexts only).
+//
+// Positions are read from device memory so that one captured CUDA graph serves every
+// decode step; the split count is a launch constant and empty splits return at once.
+#include "../common/pk_common.cuh"
+
+namespace {
+
+using namespace pk;
+
+constexpr int kD = 128;  // head dim
+
+struct QkParams {
+  const bf16* proj;   // [M, ld]: per q head [q(D) | gate(D)], then k heads, then v heads
+  int ld;
+  int M, Hq, Hkv;
+  const int* pos;     // [M]
+  const float* q_gamma;  // [D]
+  const float* k_gamma;  // [D]
+  float eps;
+  int rotary_dim;
+  float theta;
+  bf16* q_out;        // [M, Hq, D]
+  bf16* kcache;       // [Hkv, ctx_cap, D]
+  bf16* vcache;
+  int ctx_cap;
+};
+
+__global__ void __launch_bounds__(kD) qk_norm_rope_append_kernel(const QkParams p) {
+  const int m = blockIdx.x, hh = blockIdx.y, d = threadIdx.x;
+  __shared__ float red[40];
+  __shared__ float sy[kD];
+  const bool is_q = hh < p.Hq;
+  const int hk = hh - p.Hq;
+  const bf16* row = p.proj + (size_t)m * p.ld;
+  const int off = is_q ? hh * 2 * kD : p.Hq * 2 * kD + hk * kD;
+  const float x = __bfloat162float(row[off + d]);
+  const float ss = block_sum(x * x, red);
+  const float g = is_q ? p.q_gamma[d] : p.k_gamma[d];
+  float y = x * rsqrtf(ss / (float)kD + p.eps) * (1.f + g);
+  y = __bfloat162float(__float2bfloat16(y));
+  sy[d] = y;
+  __syncthreads();
+  const int pos = p.pos[m];
+  const int hr = p.rotary_dim >> 1;
+  if (d < p.rotary_dim) {
+    const int i = d < hr ? d : d - hr;
+    const double inv_freq = pow((double)p.theta, -2.0 * (double)i / (double)p.rotary_dim);
+    double sn, cs;
+    sincos((double)pos * inv_freq, &sn, &cs);
+    const float other = d < hr ? sy[d + hr] : sy[d - hr];
+    y = d < hr ? y * (float)cs - other * (float)sn : y * (float)cs + other * (float)sn;
+  }
+  if (is_q) {
+    p.q_out[((size_t)m * p.Hq + hh) * kD + d] = __float2bfloat16(y);
+  } else if (pos >= 0 && pos < p.ctx_cap) {
+    const size_t ci = ((size_t)hk * p.ctx_cap + pos) * kD + d;
+    p.kcache[ci] = __float2bfloat16(y);
+    p.vcache[ci] = row[p.Hq * 2 * kD + p.Hkv * kD + hk * kD + d];
+  }
+}
+
+struct DecodeParams {
+  const bf16* q;       // [M, Hq, D]
+  const bf16* kcache;  // [Hkv, ctx_cap, D]
+  const bf16* vcache;
+  const int* pos;      // [M]: row m attends keys 0..pos[m]
+  int M, Hq, Hkv, ctx_cap;
+  float scale;
+  int nsplit;
+  int window;          // 0 = full; else keys in (pos-window, pos] plus the first `sink` keys
+  int sink;
+  float* ws;           // [M, Hq, nsplit, D + 2]
+};
+
+template <int G>
+__global__ void __launch_bounds__(128) gqa_decode_split_kernel(const DecodeParams p) {
+  const int hk = blockIdx.x, split = blockIdx.y, m = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int l16 = lane & 15, khalf = lane >> 4;
+  const int len = min(p.pos[m] + 1, p.ctx_cap);
+  int per = (len + p.nsplit - 1) / p.nsplit;
+  per = (per + 7) & ~7;
+  const int start = split * per, end = min(len, start + per);
+  const int win_lo = p.window > 0 ? max(0, len - p.window) : 0;
+
+  float qv[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p.q + ((size_t)m * p.Hq + hk * G + g) * kD + l16 * 8);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      qv[g][2 * j] = __uint_as_float(w[j] << 16) * p.scale;
+      qv[g][2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u) * p.scale;
+    }
+  }
+  float mx[G], sum[G], acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    mx[g] = -INFINITY;
+    sum[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
+  }
+
+  const bf16* kbase = p.kcache + (size_t)hk * p.ctx_cap * kD;
+  const bf16* vbase = p.vcache + (size_t)hk * p.ctx_cap * kD;
+  for (int t0 = start + warp * 2; t0 < end; t0 += 8) {
+    const int t = t0 + khalf;
+    const bool valid = t < end && (p.window == 0 || t >= win_lo || t < p.sink);
+    uint4 kr = make_uint4(0, 0, 0, 0), vr = kr;
+    if (valid) {
+      kr = *reinterpret_cast<const uint4*>(kbase + (size_t)t * kD + l16 * 8);
+      vr = *reinterpret_cast<const uint4*>(vbase + (size_t)t * kD + l16 * 8);
+    }
+    float kf[8], vf[8];
+    {
+      const uint32_t w[4] = {kr.x, kr.y, kr.z, kr.w};
+      const uint32_t u[4] = {vr.x, vr.y, vr.z, vr.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kf[2 * j] = __uint_as_float(w[j] << 16);
+        kf[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        vf[2 * j] = __uint_as_float(u[j] << 16);
+        vf[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s = fmaf(qv[g][j], kf[j], s);
+      s += __shfl_xor_sync(0xffffffffu, s, 8);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      if (valid) {
+        const float nm = fmaxf(mx[g], s);
+        const float c = __expf(mx[g] - nm), e = __expf(s - nm);
+        sum[g] = sum[g] * c + e;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(e, vf[j], acc[g][j] * c);
+        mx[g] = nm;
+      }
+    }
+  }
+
+  // merge the two key halves of each warp, then the four warps
+  __shared__ float s_m[4][G], s_l[4][G], s_acc[4][G][kD];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float om = __shfl_xor_sync(0xffffffffu, mx[g], 16);
+    const float ol = __shfl_xor_sync(0xffffffffu, sum[g], 16);
+    const float nm = fmaxf(mx[g], om);
+    const float c0 = mx[g] == -INFINITY ? 0.f : __expf(mx[g] - nm);
+    const float c1 = om == -INFINITY ? 0.f : __expf(om - nm);
+    sum[g] = sum[g] * c0 + ol * c1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float oa = __shfl_xor_sync(0xffffffffu, acc[g][j], 16);
+      acc[g][j] = acc[g][j] * c0 + oa * c1;
+    }
+    mx[g] = nm;
+    if (khalf == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s_acc[warp][g][l16 * 8 + j] = acc[g][j];
+      if (l16 == 0) {
+        s_m[warp][g] = mx[g];
+        s_l[warp][g] = sum[g];
+      }
+    }
+  }
+  __syncthreads();
+  const int d = threadIdx.x;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float nm = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
+    float l = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float c = s_m[w][g] == -INFINITY ? 0.f : __expf(s_m[w][g] - nm);
+      l += s_l[w][g] * c;
+      a += s_acc[w][g][d] * c;
+    }
+    float* o = p.ws + (((size_t)m * p.Hq + hk * G + g) * p.nsplit + split) * (kD + 2);
+    o[d] = a;
+    if (d == 0) {
+      o[kD] = nm;
+      o[kD + 1] = l;
+    }
+  }
+}
+
+struct MergeParams {
+  const float* ws;   // [M, Hq, nsplit, D + 2]
+  int nsplit, Hq;
+  const bf16* proj;  // gate source ([M, ld], gate of head h at h*2D + D), may be null
+  int ld;
+  bf16* out;         // [M, Hq*D]
+};
+
+__global__ void __launch_bounds__(kD) gqa_merge_kernel(const MergeParams p) {
+  const int m = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const float* w = p.ws + ((size_t)m * p.Hq + h) * p.nsplit * (kD + 2);
+  float nm = -INFINITY;
+  for (int s = 0; s < p.nsplit; ++s) nm = fmaxf(nm, w[s * (kD + 2) + kD]);
+  float l = 0.f, a = 0.f;
+  for (int s = 0; s < p.nsplit; ++s) {
+    const float ms = w[s * (kD + 2) + kD];
+    const float c = ms == -INFINITY ? 0.f : __expf(ms - nm);
+    l += w[s * (kD + 2) + kD + 1] * c;
+    a += w[s * (kD + 2) + d] * c;
+  }
+  float o = l > 0.f ? a / l : 0.f;
+  if (p.proj != nullptr) {
+    const float gate = __bfloat162float(p.proj[(size_t)m * p.ld + h * 2 * kD + kD + d]);
+    o *= sigmoidf_(gate);
+  }
+  p.out[((size_t)m * p.Hq + h) * kD + d] = __float2bfloat16(o);
+}
+
+}  // namespace
+
+PK_API int pk_qk_norm_rope_append(const void* proj, int ld, int M, int Hq, int Hkv, int head_dim,
+                                  const int* pos, const float* q_gamma, const float* k_gamma, float eps,
+                                  int rotary_dim, float theta, void* q_out, void* kcache, void* vcache,
+                                  int ctx_cap, cudaStream_t stream) {
+  if (head_dim != kD) return PK_ERR_UNSUPPORTED;
+  if (M < 1 || rotary_dim < 0 || rotary_dim > kD || (rotary_dim & 1)) return PK_ERR_BAD_ARG;
+  QkParams p{(const pk::bf16*)proj, ld, M, Hq, Hkv, pos, q_gamma, k_gamma, eps, rotary_dim, theta,
+             (pk::bf16*)q_out, (pk::bf16*)kcache, (pk::bf16*)vcache, ctx_cap};
+  qk_norm_rope_append_kernel<<<dim3(M, Hq + Hkv), kD, 0, stream>>>(p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+// ws must hold M * Hq * nsplit * (head_dim + 2) floats.
+PK_API int pk_gqa_decode(const void* q, const void* kcache, const void* vcache, const int* pos, int M,
+                         int Hq, int Hkv, int head_dim, int ctx_cap, float scale, int nsplit, int window,
+                         int sink, float* ws, const void* gate_proj, int ld, void* out,
+                         cudaStream_t stream) {
+  if (head_dim != kD) return PK_ERR_UNSUPPORTED;
+  if (M < 1 || nsplit < 1 || Hq % Hkv != 0) return PK_ERR_BAD_ARG;
+  DecodeParams p{(const pk::bf16*)q, (const pk::bf16*)kcache, (const pk::bf16*)vcache, pos, M, Hq, Hkv,
+                 ctx_cap, scale, nsplit, window, sink, ws};
+  const dim3 grid(Hkv, nsplit, M);
+  switch (Hq / Hkv) {
+    case 1: gqa_decode_split_kernel<1><<<grid, 128, 0, stream>>>(p); break;
+    case 2: gqa_decode_split_kernel<2><<<grid, 128, 0, stream>>>(p); break;
+    case 3: gqa_decode_split_kernel<3><<<grid, 128, 0, stream>>>(p); break;
+    case 4: gqa_decode_split_kernel<4><<<grid, 128, 0, stream>>>(p); break;
+    case 5: gqa_decode_split_kernel<5><<<grid, 128, 0, stream>>>(p); break;
+    case 6: gqa_decode_split_kernel<6><<<grid, 128, 0, stream>>>(p); break;
+    case 8: gqa_decode_split_kernel<8><<<grid, 128, 0, stream>>>(p); break;
+    default: return PK_ERR_UNSUPPORTED;
+  }
+  PK_CHECK_LAUNCH();
+  MergeParams mp{ws, nsplit, Hq, (const pk::bf16*)gate_proj, ld, (pk::bf16*)out};
+  gqa_merge_kernel<<<dim3(M, Hq), kD, 0, stream>>>(mp);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}

@@ -1,0 +1,376 @@
+// Small memory-bound ops: embedding gather, RMSNorm with fused residual/reduce-in,
+// SwiGLU, argmax / top-k candidates over fp32 logits, epoch bump for the comm protocol.
+// Reference counterparts: cpp_engine/cuda/qwen_half_ops.cu:693-709 (rmsnorm, (1+gamma)),
+// 1529 (embedding), cpp_engine/cuda/cuda_ops.cu:40-128 (argmax_fp32, argmax_fp32_rows).
+#include "../common/pk_comm.cuh"
+#include "../common/pk_common.cuh"
+
+namespace {
+
+using namespace pk;
+
+// Vocabulary-sharded gather: rows outside [vocab_start, vocab_start + rows) give zeros,
+// so that the sum over ranks is the embedding.
+__global__ void embedding_kernel(const int* tokens, const bf16* table, int dim, int vocab_start,
+                                 int vocab_rows, bf16* out_bf16, float* out_f32) {
+  const int m = blockIdx.x;
+  const int tok = tokens[m] - vocab_start;
+  const bool mine = tok >= 0 && tok < vocab_rows;
+  for (int k = threadIdx.x; k < dim; k += blockDim.x) {
+    const bf16 v = mine ? table[(size_t)tok * dim + k] : __float2bfloat16(0.f);
+    if (out_bf16) out_bf16[(size_t)m * dim + k] = v;
+    if (out_f32) out_f32[(size_t)m * dim + k] = __bfloat162float(v);
+  }
+}
+
+struct NormParams {
+  const bf16* x;       // [M, K] or null
+  const float* parts;  // [nparts, M, K] or null
+  int nparts;
+  int M, K;
+  bf16* hidden_out;    // x + sum(parts), bf16 (may be null)
+  const float* gamma;
+  int mode;            // 1: (1+gamma), 2: gamma
+  float eps;
+  bf16* y;             // [M, K]
+  PkWait wait;
+};
+
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const NormParams p) {
+  extern __shared__ float row[];
+  __shared__ float red[40];
+  const int m = blockIdx.x;
+  if (p.parts != nullptr && p.wait.flag != nullptr) {
+    if (threadIdx.x == 0) wait_all_ranks(p.wait);
+    __syncthreads();
+  }
+  float ss = 0.f;
+  for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
+    const size_t gi = (size_t)m * p.K + k;
+    float v = p.x ? __bfloat162float(p.x[gi]) : 0.f;
+    for (int r = 0; r < p.nparts; ++r) v += p.parts[((size_t)r * p.M + m) * p.K + k];
+    const bf16 hv = __float2bfloat16(v);
+    if (p.hidden_out) p.hidden_out[gi] = hv;
+    v = __bfloat162float(hv);
+    row[k] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / (float)p.K + p.eps);
+  if (p.y == nullptr) return;
+  for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
+    const float g = p.gamma[k];
+    p.y[(size_t)m * p.K + k] = __float2bfloat16(row[k] * r * (p.mode == 1 ? 1.f + g : g));
+  }
+}
+
+__global__ void silu_mul_kernel(const bf16* gu, int inter, bf16* out, float limit) {
+  // gu: [M, 2*inter] = gate | up
+  const int m = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= inter) return;
+  float g = __bfloat162float(gu[(size_t)m * 2 * inter + j]);
+  float u = __bfloat162float(gu[(size_t)m * 2 * inter + inter + j]);
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  out[(size_t)m * inter + j] = __float2bfloat16(silu(g) * u);
+}
+
+// Stage 1 of a row argmax: each block scans a slice and keeps (value, index) with the
+// lowest index on ties. Stage 2 merges the slices. Output candidate = {logit, token id}.
+__global__ void __launch_bounds__(256) argmax_stage1(const float* logits, int ld, int n, int id_offset,
+                                                     float* cand_val, int* cand_idx) {
+  const int m = blockIdx.y, nb = gridDim.x;
+  const int per = (n + nb - 1) / nb;
+  const int lo = blockIdx.x * per, hi = min(n, lo + per);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = logits[(size_t)m * ld + i];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  sv[threadIdx.x] = best;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float ov = sv[threadIdx.x + s];
+      const int oi = si[threadIdx.x + s];
+      if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
+        sv[threadIdx.x] = ov;
+        si[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    cand_val[m * nb + blockIdx.x] = sv[0];
+    cand_idx[m * nb + blockIdx.x] = si[0] == 0x7fffffff ? 0x7fffffff : si[0] + id_offset;
+  }
+}
+
+__global__ void argmax_stage2(const float* cand_val, const int* cand_idx, int ncand, float* out_val,
+                              int* out_idx) {
+  const int m = blockIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < ncand; i += 32) {
+    const float v = cand_val[m * ncand + i];
+    const int id = cand_idx[m * ncand + i];
+    if (v > best || (v == best && id < bi)) {
+      best = v;
+      bi = id;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (out_val) out_val[m] = best;
+    out_idx[m] = bi;
+  }
+}
+
+__global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch += 1u; }
+
+__global__ void add_int_kernel(int* p, int n, int delta) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] += delta;
+}
+
+__global__ void copy_int_kernel(const int* src, int* dst, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[i];
+}
+
+}  // namespace
+
+PK_API int pk_embedding(const int* tokens, int M, const void* table, int dim, int vocab_start,
+                        int vocab_rows, void* out_bf16, float* out_f32, cudaStream_t stream) {
+  if (M < 1) return PK_ERR_BAD_ARG;
+  embedding_kernel<<<M, 256, 0, stream>>>(tokens, (const pk::bf16*)table, dim, vocab_start, vocab_rows,
+                                          (pk::bf16*)out_bf16, out_f32);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+PK_API int pk_rmsnorm(const void* x, const float* parts, int nparts, int M, int K, void* hidden_out,
+                      const float* gamma, int mode, float eps, void* y, const PkWait* wait,
+                      cudaStream_t stream) {
+  if (M < 1 || K < 1 || (x == nullptr && parts == nullptr)) return PK_ERR_BAD_ARG;
+  if (hidden_out != nullptr && hidden_out == x && parts != nullptr) {
+    // in place is fine here: every element is read and written by the same thread
+  }
+  NormParams p{};
+  p.x = (const pk::bf16*)x;
+  p.parts = parts;
+  p.nparts = parts ? nparts : 0;
+  p.M = M;
+  p.K = K;
+  p.hidden_out = (pk::bf16*)hidden_out;
+  p.gamma = gamma;
+  p.mode = mode;
+  p.eps = eps;
+  p.y = (pk::bf16*)y;
+  if (wait) p.wait = *wait;
+  const size_t smem = (size_t)K * sizeof(float);
+  if (smem > 200 * 1024) return PK_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    static size_t configured = 0;
+    if (smem > configured) {
+      if (cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        pk_set_last_cuda_error((int)cudaGetLastError());
+        return PK_ERR_CUDA;
+      }
+      configured = smem;
+    }
+  }
+  rmsnorm_kernel<<<M, 256, smem, stream>>>(p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+PK_API int pk_silu_mul(const void* gate_up, int M, int inter, void* out, float limit, cudaStream_t stream) {
+  silu_mul_kernel<<<dim3((inter + 255) / 256, M), 256, 0, stream>>>((const pk::bf16*)gate_up, inter,
+                                                                   (pk::bf16*)out, limit);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+// cand_* hold M * nblocks entries. Token ids are shifted by id_offset (vocab shard start).
+PK_API int pk_argmax(const float* logits, int ld, int M, int n, int id_offset, int nblocks, float* cand_val,
+                     int* cand_idx, float* out_val, int* out_idx, cudaStream_t stream) {
+  if (M < 1 || n < 1 || nblocks < 1) return PK_ERR_BAD_ARG;
+  argmax_stage1<<<dim3(nblocks, M), 256, 0, stream>>>(logits, ld, n, id_offset, cand_val, cand_idx);
+  PK_CHECK_LAUNCH();
+  if (out_idx != nullptr) {
+    argmax_stage2<<<M, 32, 0, stream>>>(cand_val, cand_idx, nblocks, out_val, out_idx);
+    PK_CHECK_LAUNCH();
+  }
+  return PK_OK;
+}
+
+PK_API int pk_argmax_merge(const float* cand_val, const int* cand_idx, int M, int ncand, float* out_val,
+                           int* out_idx, cudaStream_t stream) {
+  argmax_stage2<<<M, 32, 0, stream>>>(cand_val, cand_idx, ncand, out_val, out_idx);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+PK_API int pk_bump_epoch(uint32_t* epoch, cudaStream_t stream) {
+  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+PK_API int pk_add_int(int* p, int n, int delta, cudaStream_t stream) {
+  add_int_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p, n, delta);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+PK_API int pk_copy_int(const int* src, int* dst, int n, cudaStream_t stream) {
+  copy_int_kernel<<<(n + 127) / 128, 128, 0, stream>>>(src, dst, n);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Random initialisation on the device (benchmarks use random-init weights of the real
+// shapes; no checkpoint file is involved) and small helpers of the decode loop.
+namespace {
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+__device__ __forceinline__ float gauss_from(uint64_t seed, uint64_t i) {
+  const uint64_t h = splitmix64(seed ^ (i * 0xD6E8FEB86659FD93ull));
+  const float u1 = ((float)(uint32_t)(h >> 40) + 1.f) * (1.f / 16777217.f);
+  const float u2 = (float)(uint32_t)((h >> 8) & 0xffffffu) * (1.f / 16777216.f);
+  return sqrtf(-2.f * __logf(u1)) * __cosf(6.2831853f * u2);
+}
+
+// FP8 E4M3 codes of N(0, sigma) values with one scale per 128x128 block chosen so that
+// 4.5 sigma maps to the largest finite code (448); blocks get slightly different scales.
+__global__ void fill_fp8_gauss_kernel(uint8_t* w, float* scale, int N, int K, float sigma, uint64_t seed) {
+  const size_t total = (size_t)N * K;
+  const int kb = (K + 127) >> 7;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int n = (int)(i / K), k = (int)(i % K);
+    const int b = (n >> 7) * kb + (k >> 7);
+    const float jitter = 1.f + 0.25f * (float)(splitmix64(seed + 77u + b) & 0xff) * (1.f / 255.f);
+    const float s = sigma * 4.5f / 448.f * jitter;
+    if ((n & 127) == 0 && (k & 127) == 0) scale[b] = s;
+    w[i] = float_to_e4m3(gauss_from(seed, i) * sigma / s);
+  }
+}
+
+__global__ void fill_bf16_gauss_kernel(bf16* w, size_t n, float mean, float sigma, uint64_t seed) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    w[i] = __float2bfloat16(mean + sigma * gauss_from(seed, i));
+}
+
+__global__ void fill_f32_gauss_kernel(float* w, size_t n, float mean, float sigma, uint64_t seed) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    w[i] = mean + sigma * gauss_from(seed, i);
+}
+
+__global__ void iota_int_kernel(int* p, int n, const int* base_dev, int base_host) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = (base_dev ? *base_dev : base_host) + i;
+}
+
+__global__ void store_token_kernel(const int* token, int* out, int* counter, int cap) {
+  const int c = *counter;
+  if (c < cap) out[c] = *token;
+  *counter = c + 1;
+}
+
+__global__ void cand_push_kernel(const float* val, const int* idx, int M, const PkPush push,
+                                 float* const* peer_val, int* const* peer_idx) {
+  const int m = threadIdx.x;
+  if (m < M) {
+    for (int r = 0; r < push.world; ++r) {
+      peer_val[r][push.rank * M + m] = val[m];
+      peer_idx[r][push.rank * M + m] = idx[m];
+    }
+  }
+  publish_when_grid_done(push);
+}
+
+__global__ void cand_merge_wait_kernel(const float* cand_val, const int* cand_idx, int M, int world,
+                                       const PkWait wait, int* out_idx) {
+  if (threadIdx.x == 0) wait_all_ranks(wait);
+  __syncthreads();
+  const int m = threadIdx.x;
+  if (m >= M) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int r = 0; r < world; ++r) {
+    const float v = cand_val[r * M + m];
+    const int id = cand_idx[r * M + m];
+    if (v > best || (v == best && id < bi)) {
+      best = v;
+      bi = id;
+    }
+  }
+  out_idx[m] = bi;
+}
+
+}  // namespace
+
+PK_API int pk_fill_fp8_gauss(void* w, float* scale, int N, int K, float sigma, uint64_t seed, cudaStream_t stream) {
+  fill_fp8_gauss_kernel<<<2048, 256, 0, stream>>>((uint8_t*)w, scale, N, K, sigma, seed);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+PK_API int pk_fill_bf16_gauss(void* w, size_t n, float mean, float sigma, uint64_t seed, cudaStream_t stream) {
+  fill_bf16_gauss_kernel<<<1024, 256, 0, stream>>>((pk::bf16*)w, n, mean, sigma, seed);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+PK_API int pk_fill_f32_gauss(float* w, size_t n, float mean, float sigma, uint64_t seed, cudaStream_t stream) {
+  fill_f32_gauss_kernel<<<256, 256, 0, stream>>>(w, n, mean, sigma, seed);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+PK_API int pk_iota_int(int* p, int n, const int* base_dev, int base_host, cudaStream_t stream) {
+  iota_int_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p, n, base_dev, base_host);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+PK_API int pk_store_token(const int* token, int* out, int* counter, int cap, cudaStream_t stream) {
+  store_token_kernel<<<1, 1, 0, stream>>>(token, out, counter, cap);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+PK_API int pk_cand_push(const float* val, const int* idx, int M, const PkPush* push, float* const* peer_val,
+                        int* const* peer_idx, cudaStream_t stream) {
+  if (M > 32 || push == nullptr) return PK_ERR_BAD_ARG;
+  cand_push_kernel<<<1, 32, 0, stream>>>(val, idx, M, *push, peer_val, peer_idx);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+PK_API int pk_cand_merge_wait(const float* cand_val, const int* cand_idx, int M, int world, const PkWait* wait,
+                              int* out_idx, cudaStream_t stream) {
+  if (M > 32 || wait == nullptr) return PK_ERR_BAD_ARG;
+  cand_merge_wait_kernel<<<1, 32, 0, stream>>>(cand_val, cand_idx, M, world, *wait, out_idx);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}

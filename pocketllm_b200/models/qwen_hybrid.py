@@ -1,0 +1,413 @@
+"""Hybrid Gated-DeltaNet / GQA decoder (Qwen3.x-FP8 family).
+
+* `QwenHybridConfig`      -- Hugging Face style config (same keys as the reference parses,
+                             cpp_engine/src/qwen_config.cpp:105-151).
+* `random_checkpoint`     -- random-init tensors in the on-disk FP8 layout with the reference's
+                             tensor names (cpp_engine/src/qwen_weights.cpp:314-468).
+* `ReferenceModel`        -- plain PyTorch fp32 restatement of the numerical contract
+                             (cpp_engine/src/qwen_engine.cpp:960-1303, cuda/qwen_half_ops.cu:693-1158);
+                             the oracle for kernel and engine tests.
+* `QwenEngine`            -- the native engine (csrc/engine) behind a Python API: prefill,
+                             CUDA-graph decode, speculative verify rows, snapshots.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import math
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Sequence
+
+import torch
+
+from ..formats import fp8 as fp8fmt
+from ..formats import safetensors_io as st_io
+from ..ops import lib as _lib
+
+
+@dataclass
+class QwenHybridConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 5120
+    intermediate_size: int = 17408
+    num_hidden_layers: int = 64
+    num_attention_heads: int = 40
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    attn_output_gate: bool = True
+    rope_theta: float = 1.0e6
+    partial_rotary_factor: float = 0.25
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_conv_kernel_dim: int = 4
+    rms_norm_eps: float = 1e-6
+    max_position_embeddings: int = 262144
+    full_attention_interval: int = 4
+    mtp_num_hidden_layers: int = 0
+    layer_types: list[str] = field(default_factory=list)
+    model_type: str = "qwen3_5_text"
+
+    def __post_init__(self) -> None:
+        if not self.layer_types:
+            self.layer_types = ["full_attention" if (i + 1) % self.full_attention_interval == 0 else "linear_attention"
+                                for i in range(self.num_hidden_layers)]
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor) & ~1
+
+    def to_json(self) -> str:
+        return json.dumps(asdict(self))
+
+    @classmethod
+    def from_json(cls, text: str) -> "QwenHybridConfig":
+        d = json.loads(text)
+        d = d.get("text_config", d)
+        rp = d.get("rope_parameters") or {}
+        names = {f for f in cls.__dataclass_fields__}
+        kw = {k: v for k, v in d.items() if k in names}
+        kw.update({k: v for k, v in rp.items() if k in names})
+        return cls(**kw)
+
+    @classmethod
+    def benchmark_27b(cls) -> "QwenHybridConfig":
+        """64 layers, hidden 5120, SwiGLU 17408, vocab 151936, 40/8 GQA heads, 16/32 DeltaNet heads."""
+        return cls()
+
+    @classmethod
+    def tiny(cls, layers: int = 4, hidden: int = 256, inter: int = 512, vocab: int = 1024) -> "QwenHybridConfig":
+        return cls(vocab_size=vocab, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=layers,
+                   num_attention_heads=4, num_key_value_heads=2, linear_num_key_heads=2, linear_num_value_heads=4,
+                   max_position_embeddings=4096)
+
+
+# --------------------------------------------------------------------------------------
+# random checkpoints in the reference's tensor naming
+
+def random_checkpoint(cfg: QwenHybridConfig, seed: int = 0, sigma: float = 0.02,
+                      prefix: str = "model.language_model.") -> dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    out: dict[str, torch.Tensor] = {}
+    H, D = cfg.hidden_size, cfg.head_dim
+
+    def fp8(name: str, n: int, k: int) -> None:
+        w = torch.randn(n, k, generator=g) * sigma
+        q, s = fp8fmt.quantize_block128(w)
+        out[name + ".weight"] = q
+        out[name + ".weight_scale_inv"] = s
+
+    def bf16(name: str, *shape: int, mean: float = 0.0, std: float = sigma) -> None:
+        out[name] = (mean + std * torch.randn(*shape, generator=g)).to(torch.bfloat16)
+
+    bf16(prefix + "embed_tokens.weight", cfg.vocab_size, H)
+    bf16(prefix + "norm.weight", H, std=0.05)
+    bf16("lm_head.weight", cfg.vocab_size, H)
+    KD = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+    VD = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+    for i, kind in enumerate(cfg.layer_types):
+        p = f"{prefix}layers.{i}."
+        bf16(p + "input_layernorm.weight", H, std=0.05)
+        bf16(p + "post_attention_layernorm.weight", H, std=0.05)
+        if kind == "linear_attention":
+            fp8(p + "linear_attn.in_proj_qkv", 2 * KD + VD, H)
+            fp8(p + "linear_attn.in_proj_z", VD, H)
+            fp8(p + "linear_attn.out_proj", H, VD)
+            bf16(p + "linear_attn.in_proj_a.weight", cfg.linear_num_value_heads, H)
+            bf16(p + "linear_attn.in_proj_b.weight", cfg.linear_num_value_heads, H)
+            bf16(p + "linear_attn.conv1d.weight", 2 * KD + VD, 1, cfg.linear_conv_kernel_dim, std=0.3)
+            bf16(p + "linear_attn.A_log", cfg.linear_num_value_heads, std=0.5)
+            bf16(p + "linear_attn.dt_bias", cfg.linear_num_value_heads, std=0.5)
+            bf16(p + "linear_attn.norm.weight", cfg.linear_value_head_dim, mean=1.0, std=0.05)
+        else:
+            qd = cfg.num_attention_heads * D * (2 if cfg.attn_output_gate else 1)
+            kvd = cfg.num_key_value_heads * D
+            fp8(p + "self_attn.q_proj", qd, H)
+            fp8(p + "self_attn.k_proj", kvd, H)
+            fp8(p + "self_attn.v_proj", kvd, H)
+            fp8(p + "self_attn.o_proj", H, cfg.num_attention_heads * D)
+            bf16(p + "self_attn.q_norm.weight", D, std=0.05)
+            bf16(p + "self_attn.k_norm.weight", D, std=0.05)
+        fp8(p + "mlp.gate_proj", cfg.intermediate_size, H)
+        fp8(p + "mlp.up_proj", cfg.intermediate_size, H)
+        fp8(p + "mlp.down_proj", H, cfg.intermediate_size)
+    return out
+
+
+def save_checkpoint(directory: str | Path, cfg: QwenHybridConfig, tensors: dict[str, torch.Tensor],
+                    max_shard_bytes: int = 4 << 30) -> None:
+    d = Path(directory)
+    d.mkdir(parents=True, exist_ok=True)
+    (d / "config.json").write_text(cfg.to_json())
+    st_io.write_sharded(d, tensors, max_shard_bytes=max_shard_bytes)
+
+
+# --------------------------------------------------------------------------------------
+# fp32 oracle
+
+def _r16(x: torch.Tensor) -> torch.Tensor:
+    """Round to bf16 and back: where the engine stores an activation in 16 bit."""
+    return x.to(torch.bfloat16).float()
+
+
+class ReferenceModel:
+    """Token-by-token fp32 model with explicit state; small shapes only."""
+
+    def __init__(self, cfg: QwenHybridConfig, tensors: dict[str, torch.Tensor], prefix: str = "model.language_model.",
+                 emulate_bf16: bool = True, device: str = "cpu"):
+        self.cfg, self.device = cfg, device
+        self.r = _r16 if emulate_bf16 else (lambda x: x)
+        self.p = prefix
+
+        def lin(name: str) -> torch.Tensor:
+            return fp8fmt.dequantize_block128(tensors[name + ".weight"], tensors[name + ".weight_scale_inv"]).to(device)
+
+        def f(name: str) -> torch.Tensor:
+            return tensors[name].float().to(device)
+
+        self.embed, self.norm, self.lm_head = f(prefix + "embed_tokens.weight"), f(prefix + "norm.weight"), f("lm_head.weight")
+        self.layers = []
+        for i, kind in enumerate(cfg.layer_types):
+            p = f"{prefix}layers.{i}."
+            L = {"kind": kind, "in_norm": f(p + "input_layernorm.weight"), "post_norm": f(p + "post_attention_layernorm.weight"),
+                 "gate": lin(p + "mlp.gate_proj"), "up": lin(p + "mlp.up_proj"), "down": lin(p + "mlp.down_proj")}
+            if kind == "linear_attention":
+                L.update(qkv=lin(p + "linear_attn.in_proj_qkv"), z=lin(p + "linear_attn.in_proj_z"), out=lin(p + "linear_attn.out_proj"),
+                         a=f(p + "linear_attn.in_proj_a.weight"), b=f(p + "linear_attn.in_proj_b.weight"),
+                         conv=f(p + "linear_attn.conv1d.weight").squeeze(1), A_log=f(p + "linear_attn.A_log"),
+                         dt_bias=f(p + "linear_attn.dt_bias"), lnorm=f(p + "linear_attn.norm.weight"))
+            else:
+                L.update(q=lin(p + "self_attn.q_proj"), k=lin(p + "self_attn.k_proj"), v=lin(p + "self_attn.v_proj"),
+                         o=lin(p + "self_attn.o_proj"), qn=f(p + "self_attn.q_norm.weight"), kn=f(p + "self_attn.k_norm.weight"))
+            self.layers.append(L)
+        self.reset()
+
+    def reset(self) -> None:
+        c = self.cfg
+        KD = c.linear_num_key_heads * c.linear_key_head_dim
+        VD = c.linear_num_value_heads * c.linear_value_head_dim
+        self.pos = 0
+        self.state = []
+        for L in self.layers:
+            if L["kind"] == "linear_attention":
+                self.state.append({"S": torch.zeros(c.linear_num_value_heads, c.linear_key_head_dim, c.linear_value_head_dim, device=self.device),
+                                   "tail": torch.zeros(2 * KD + VD, c.linear_conv_kernel_dim - 1, device=self.device)})
+            else:
+                self.state.append({"k": [], "v": []})
+
+    def _rms(self, x: torch.Tensor, g: torch.Tensor, plus_one: bool = True) -> torch.Tensor:
+        r = torch.rsqrt((x * x).mean(-1, keepdim=True) + self.cfg.rms_norm_eps)
+        return x * r * ((1.0 + g) if plus_one else g)
+
+    def _linear_attn(self, L: dict, st: dict, x: torch.Tensor) -> torch.Tensor:
+        c, r = self.cfg, self.r
+        Hk, Hv, Dk, Dv = c.linear_num_key_heads, c.linear_num_value_heads, c.linear_key_head_dim, c.linear_value_head_dim
+        KD, VD = Hk * Dk, Hv * Dv
+        packed, z = r(L["qkv"] @ x), r(L["z"] @ x)
+        a, b = r(L["a"] @ x), r(L["b"] @ x)
+        window = torch.cat([st["tail"], packed[:, None]], dim=1)          # [C, 4]
+        y = r(torch.nn.functional.silu((window * L["conv"]).sum(-1)))
+        st["tail"] = window[:, 1:].clone()
+        q, k, v = y[:KD].view(Hk, Dk), y[KD:2 * KD].view(Hk, Dk), y[2 * KD:].view(Hv, Dv)
+        q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6)
+        k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        rep = Hv // Hk
+        q, k = q.repeat_interleave(rep, 0), k.repeat_interleave(rep, 0)   # per value head
+        g = -torch.exp(L["A_log"]) * torch.nn.functional.softplus(a + L["dt_bias"])
+        beta = torch.sigmoid(b)
+        S = st["S"] * torch.exp(g)[:, None, None]
+        kv = torch.einsum("hkv,hk->hv", S, k)
+        delta = (v - kv) * beta[:, None]
+        S = S + torch.einsum("hk,hv->hkv", k, delta)
+        st["S"] = S
+        o = torch.einsum("hkv,hk->hv", S, q) * (Dk ** -0.5)
+        o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + c.rms_norm_eps) * L["lnorm"] * torch.nn.functional.silu(z.view(Hv, Dv))
+        return L["out"] @ r(o.reshape(VD))
+
+    def _rope(self, x: torch.Tensor, pos: int) -> torch.Tensor:
+        rd = self.cfg.rotary_dim
+        if rd == 0:
+            return x
+        half = rd // 2
+        inv = torch.pow(torch.tensor(self.cfg.rope_theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rd)
+        ang = pos * inv
+        cs, sn = torch.cos(ang).float().to(x.device), torch.sin(ang).float().to(x.device)
+        x1, x2 = x[..., :half], x[..., half:rd]
+        return torch.cat([x1 * cs - x2 * sn, x2 * cs + x1 * sn, x[..., rd:]], dim=-1)
+
+    def _full_attn(self, L: dict, st: dict, x: torch.Tensor, pos: int) -> torch.Tensor:
+        c, r = self.cfg, self.r
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        qg = r(L["q"] @ x).view(Hq, 2 * D) if c.attn_output_gate else None
+        q = qg[:, :D] if qg is not None else r(L["q"] @ x).view(Hq, D)
+        gate = qg[:, D:] if qg is not None else None
+        k, v = r(L["k"] @ x).view(Hkv, D), r(L["v"] @ x).view(Hkv, D)
+        q = r(self._rope(r(self._rms(q, L["qn"])), pos))
+        k = r(self._rope(r(self._rms(k, L["kn"])), pos))
+        st["k"].append(k)
+        st["v"].append(v)
+        K, V = torch.stack(st["k"], 1), torch.stack(st["v"], 1)          # [Hkv, T, D]
+        rep = Hq // Hkv
+        K, V = K.repeat_interleave(rep, 0), V.repeat_interleave(rep, 0)
+        s = torch.einsum("hd,htd->ht", q, K) * (D ** -0.5)
+        o = torch.einsum("ht,htd->hd", torch.softmax(s, -1), V)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
+        return L["o"] @ r(o.reshape(Hq * D))
+
+    def step(self, token: int) -> torch.Tensor:
+        """Feed one token; returns fp32 logits [vocab]."""
+        r = self.r
+        h = self.embed[token].clone()
+        for L, st in zip(self.layers, self.state):
+            x = r(self._rms(h, L["in_norm"]))
+            att = self._linear_attn(L, st, x) if L["kind"] == "linear_attention" else self._full_attn(L, st, x, self.pos)
+            h = r(h + att)
+            x = r(self._rms(h, L["post_norm"]))
+            mid = r(torch.nn.functional.silu(L["gate"] @ x) * (L["up"] @ x))
+            h = r(h + L["down"] @ mid)
+        self.pos += 1
+        return self.lm_head @ r(self._rms(h, self.norm))
+
+    def generate(self, prompt: Sequence[int], max_new_tokens: int) -> tuple[list[int], list[torch.Tensor]]:
+        logits = None
+        for t in prompt:
+            logits = self.step(int(t))
+        out, all_logits = [], []
+        for _ in range(max_new_tokens):
+            all_logits.append(logits)
+            nxt = int(torch.argmax(logits))
+            out.append(nxt)
+            logits = self.step(nxt)
+        return out, all_logits
+
+
+# --------------------------------------------------------------------------------------
+# native engine
+
+class EngineError(RuntimeError):
+    pass
+
+
+class QwenEngine:
+    """Native engine for one tensor-parallel rank.
+
+    `QwenEngine(cfg).load(path)` or `.init_random(seed)`, then `prefill(tokens)` followed
+    by `decode(n)`. With `tp_world > 1` call `connect(...)` (see `parallel.tp`) once every
+    rank has created its engine.
+    """
+
+    def __init__(self, cfg: QwenHybridConfig | str, *, tp_rank: int = 0, tp_world: int = 1, device: int = 0,
+                 max_context: int = 4096, prefill_chunk: int = 512, use_cuda_graph: bool = True, decode_splits: int = 8):
+        self._L = _lib.engine()
+        L = self._L
+        L.pk_qwen_create.restype = ctypes.c_void_p
+        L.pk_engine_last_error.restype = ctypes.c_char_p
+        L.pk_qwen_comm_arena.restype = ctypes.c_void_p
+        L.pk_qwen_weight_bytes.restype = ctypes.c_ulonglong
+        L.pk_ipc_open.restype = ctypes.c_void_p
+        self.cfg = cfg
+        text = cfg if isinstance(cfg, str) else cfg.to_json()
+        self.tp_rank, self.tp_world, self.device = tp_rank, tp_world, device
+        self._h = L.pk_qwen_create(text.encode(), tp_rank, tp_world, device, max_context, prefill_chunk,
+                                   int(use_cuda_graph), decode_splits)
+        if not self._h:
+            raise EngineError(L.pk_engine_last_error().decode())
+        self._h = ctypes.c_void_p(self._h)
+
+    def _ck(self, status: int) -> None:
+        if status != 0:
+            raise EngineError(self._L.pk_engine_last_error().decode())
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._L.pk_qwen_destroy(self._h)
+            self._h = None
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load(self, path: str | Path) -> "QwenEngine":
+        self._ck(self._L.pk_qwen_load_safetensors(self._h, str(path).encode()))
+        return self
+
+    def init_random(self, seed: int = 0, sigma: float = 0.02) -> "QwenEngine":
+        self._ck(self._L.pk_qwen_init_random(self._h, ctypes.c_uint64(seed), ctypes.c_float(sigma)))
+        return self
+
+    def reset(self) -> None:
+        self._ck(self._L.pk_qwen_reset(self._h))
+
+    def prefill(self, tokens: Sequence[int]) -> int:
+        arr = (ctypes.c_int * len(tokens))(*[int(t) for t in tokens])
+        first = ctypes.c_int(0)
+        self._ck(self._L.pk_qwen_prefill(self._h, arr, len(tokens), ctypes.byref(first)))
+        return first.value
+
+    def decode(self, steps: int, sync_each_step: bool = False) -> list[int]:
+        out = (ctypes.c_int * steps)()
+        self._ck(self._L.pk_qwen_decode(self._h, steps, out, int(sync_each_step)))
+        return list(out)
+
+    def forward_rows(self, tokens: Sequence[int]) -> list[int]:
+        n = len(tokens)
+        arr = (ctypes.c_int * n)(*[int(t) for t in tokens])
+        out = (ctypes.c_int * n)()
+        self._ck(self._L.pk_qwen_forward_rows(self._h, arr, n, out))
+        return list(out)
+
+    def generate(self, prompt: Sequence[int], max_new_tokens: int) -> list[int]:
+        first = self.prefill(prompt)
+        if max_new_tokens <= 1:
+            return [first][:max_new_tokens]
+        return [first] + self.decode(max_new_tokens - 1)
+
+    def logits(self, row: int = 0) -> torch.Tensor:
+        n = self._L.pk_qwen_vocab_local(self._h)
+        buf = (ctypes.c_float * n)()
+        self._ck(self._L.pk_qwen_copy_logits(self._h, buf, row))
+        return torch.tensor(list(buf), dtype=torch.float32)
+
+    @property
+    def position(self) -> int:
+        return self._L.pk_qwen_position(self._h)
+
+    @property
+    def weight_bytes(self) -> int:
+        return int(self._L.pk_qwen_weight_bytes(self._h))
+
+    def comm_status(self) -> int:
+        return int(self._L.pk_qwen_comm_status(self._h)) & 0xFFFFFFFF
+
+    def timings(self) -> dict[str, float]:
+        buf = (ctypes.c_double * 5)()
+        self._L.pk_qwen_timings(self._h, buf)
+        return {"prefill_ms": buf[0], "decode_ms": buf[1], "prefill_tokens": buf[2], "decode_tokens": buf[3],
+                "kernel_launches": buf[4]}
+
+    # ---- peer memory ----
+    def export_arena(self) -> bytes:
+        n = ctypes.c_ulonglong(0)
+        ptr = self._L.pk_qwen_comm_arena(self._h, ctypes.byref(n))
+        handle = (ctypes.c_ubyte * 64)()
+        self._ck(self._L.pk_ipc_export(ctypes.c_void_p(ptr), handle))
+        return bytes(handle)
+
+    def connect(self, handles: Sequence[bytes]) -> None:
+        """Register the comm arenas of all ranks (`handles[r]` from rank r's `export_arena`)."""
+        ptrs = (ctypes.c_void_p * self.tp_world)()
+        for r, hb in enumerate(handles):
+            if r == self.tp_rank:
+                ptrs[r] = None
+                continue
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(hb)
+            p = self._L.pk_ipc_open(buf)
+            if not p:
+                raise EngineError(self._L.pk_engine_last_error().decode())
+            ptrs[r] = p
+        self._ck(self._L.pk_qwen_set_peer_arenas(self._h, ptrs))

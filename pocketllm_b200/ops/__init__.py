@@ -1,0 +1,164 @@
+"""Python bindings of the hand-written sm_100a kernels (ctypes over `libpocket_kernels.so`).
+
+Every function takes CUDA tensors, launches on the current torch stream and returns the
+output tensor. There is one implementation per op and no fallback: a missing library or
+a non-zero status raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_size_t, c_uint64, c_void_p
+
+import torch
+
+from . import lib as _lib
+
+__all__ = [
+    "matvec", "gemm_umma", "deltanet_seq", "qk_norm_rope_append", "gqa_decode", "rmsnorm",
+    "embedding", "argmax", "silu_mul", "KernelError",
+]
+
+WFMT_FP8_BLOCK128 = 0
+WFMT_BF16 = 1
+EPI_BF16, EPI_SWIGLU, EPI_RESID, EPI_F32 = 0, 1, 2, 3
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        err = _lib.kernels().pk_last_cuda_error()
+        raise KernelError(f"{what}: status {status} (cuda error {err})")
+
+
+def _sm_count() -> int:
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+
+
+def matvec(x: torch.Tensor, w_fp8: torch.Tensor | None, scale: torch.Tensor | None, w_bf16: torch.Tensor | None = None,
+           *, gamma: torch.Tensor | None = None, norm_mode: int = 1, eps: float = 1e-6, parts: torch.Tensor | None = None,
+           hidden_out: torch.Tensor | None = None, epi: int = 0) -> torch.Tensor:
+    """Small-batch linear (1..8 rows): y = norm(x + sum(parts)) @ [w_fp8 * scale ; w_bf16]^T.
+
+    epi 0 -> bf16, 1 -> SiLU(gate) * up (rows of w_fp8: gate then up), 2 -> fp32.
+    """
+    M, K = x.shape
+    N = 0 if w_fp8 is None else w_fp8.shape[0]
+    Nb = 0 if w_bf16 is None else w_bf16.shape[0]
+    ncols = N // 2 if epi == 1 else N + Nb
+    y = torch.empty(M, ncols, device=x.device, dtype=torch.float32 if epi == 2 else torch.bfloat16)
+    nparts = 0 if parts is None else parts.shape[0]
+    st = _lib.kernels().pk_matvec(
+        _ptr(w_fp8), _ptr(scale), _ptr(w_bf16), c_int(N), c_int(Nb), c_int(K), c_int(M), _ptr(x), _ptr(parts),
+        c_int(nparts), _ptr(hidden_out), _ptr(gamma), c_int(norm_mode), c_float(eps), c_void_p(0), c_int(epi),
+        _ptr(y), c_int(ncols), c_void_p(0), c_int(_sm_count()), _stream())
+    _check(st, "pk_matvec")
+    return y
+
+
+def gemm_umma(a: torch.Tensor, w: torch.Tensor, scale: torch.Tensor | None = None, *, epi: int = EPI_BF16,
+              resid: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """tcgen05 GEMM: C = A @ dequant(W)^T with a fused epilogue. A bf16 [M, K]; W fp8 [N, K] with
+    fp32 scales [N/128, K/128], or bf16 [N, K]."""
+    M, K = a.shape
+    N = w.shape[0]
+    wfmt = WFMT_BF16 if w.dtype == torch.bfloat16 else WFMT_FP8_BLOCK128
+    ncols = N // 2 if epi == EPI_SWIGLU else N
+    c = torch.empty(M, ncols, device=a.device, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16)
+    if status is None:
+        status = torch.zeros(1, device=a.device, dtype=torch.int32)
+    st = _lib.kernels().pk_gemm_umma(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), _ptr(scale), c_int(wfmt), c_int(M), c_int(N), c_int(K), c_int(epi),
+        _ptr(c), _ptr(resid), c_int(ncols), _ptr(status), _stream())
+    _check(st, "pk_gemm_umma")
+    return c
+
+
+def deltanet_seq(proj: torch.Tensor, key_heads: int, value_heads: int, conv_w: torch.Tensor, conv_state: torch.Tensor,
+                 A_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, eps: float, state: torch.Tensor) -> torch.Tensor:
+    """Gated DeltaNet over T tokens in order; updates `state` and `conv_state` in place."""
+    T, ld = proj.shape
+    out = torch.empty(T, value_heads * 128, device=proj.device, dtype=torch.bfloat16)
+    st = _lib.kernels().pk_deltanet_seq(
+        _ptr(proj), c_int(ld), c_int(T), c_int(key_heads), c_int(value_heads), c_int(128), c_int(128), _ptr(conv_w),
+        _ptr(conv_state), _ptr(A_log), _ptr(dt_bias), _ptr(norm_w), c_float(eps), _ptr(state), _ptr(out), _stream())
+    _check(st, "pk_deltanet_seq")
+    return out
+
+
+def qk_norm_rope_append(proj: torch.Tensor, Hq: int, Hkv: int, pos: torch.Tensor, q_gamma: torch.Tensor,
+                        k_gamma: torch.Tensor, eps: float, rotary_dim: int, theta: float, kcache: torch.Tensor,
+                        vcache: torch.Tensor) -> torch.Tensor:
+    M, ld = proj.shape
+    q = torch.empty(M, Hq, 128, device=proj.device, dtype=torch.bfloat16)
+    st = _lib.kernels().pk_qk_norm_rope_append(
+        _ptr(proj), c_int(ld), c_int(M), c_int(Hq), c_int(Hkv), c_int(128), _ptr(pos), _ptr(q_gamma), _ptr(k_gamma),
+        c_float(eps), c_int(rotary_dim), c_float(theta), _ptr(q), _ptr(kcache), _ptr(vcache), c_int(kcache.shape[1]),
+        _stream())
+    _check(st, "pk_qk_norm_rope_append")
+    return q
+
+
+def gqa_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor, *, nsplit: int = 4,
+               gate_proj: torch.Tensor | None = None, window: int = 0, sink: int = 0) -> torch.Tensor:
+    M, Hq, D = q.shape
+    Hkv, cap, _ = kcache.shape
+    ws = torch.empty(M * Hq * nsplit * (D + 2), device=q.device, dtype=torch.float32)
+    out = torch.empty(M, Hq * D, device=q.device, dtype=torch.bfloat16)
+    ld = 0 if gate_proj is None else gate_proj.stride(0)
+    st = _lib.kernels().pk_gqa_decode(
+        _ptr(q), _ptr(kcache), _ptr(vcache), _ptr(pos), c_int(M), c_int(Hq), c_int(Hkv), c_int(D), c_int(cap),
+        c_float(D ** -0.5), c_int(nsplit), c_int(window), c_int(sink), _ptr(ws), _ptr(gate_proj), c_int(ld), _ptr(out),
+        _stream())
+    _check(st, "pk_gqa_decode")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, *, mode: int = 1, eps: float = 1e-6) -> torch.Tensor:
+    M, K = x.shape
+    y = torch.empty_like(x)
+    st = _lib.kernels().pk_rmsnorm(_ptr(x), c_void_p(0), c_int(0), c_int(M), c_int(K), c_void_p(0), _ptr(gamma),
+                                   c_int(mode), c_float(eps), _ptr(y), c_void_p(0), _stream())
+    _check(st, "pk_rmsnorm")
+    return y
+
+
+def embedding(tokens: torch.Tensor, table: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
+    M = tokens.numel()
+    out = torch.empty(M, table.shape[1], device=table.device, dtype=torch.bfloat16)
+    st = _lib.kernels().pk_embedding(_ptr(tokens), c_int(M), _ptr(table), c_int(table.shape[1]), c_int(vocab_start),
+                                     c_int(table.shape[0]), _ptr(out), c_void_p(0), _stream())
+    _check(st, "pk_embedding")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, limit: float = 0.0) -> torch.Tensor:
+    M, two_inter = gate_up.shape
+    out = torch.empty(M, two_inter // 2, device=gate_up.device, dtype=torch.bfloat16)
+    st = _lib.kernels().pk_silu_mul(_ptr(gate_up), c_int(M), c_int(two_inter // 2), _ptr(out), c_float(limit), _stream())
+    _check(st, "pk_silu_mul")
+    return out
+
+
+def argmax(logits: torch.Tensor, id_offset: int = 0) -> torch.Tensor:
+    """Row argmax of fp32 logits with the lowest index winning ties."""
+    M, n = logits.shape
+    nb = 64
+    cv = torch.empty(M * nb, device=logits.device, dtype=torch.float32)
+    ci = torch.empty(M * nb, device=logits.device, dtype=torch.int32)
+    ov = torch.empty(M, device=logits.device, dtype=torch.float32)
+    oi = torch.empty(M, device=logits.device, dtype=torch.int32)
+    st = _lib.kernels().pk_argmax(_ptr(logits), c_int(logits.stride(0)), c_int(M), c_int(n), c_int(id_offset), c_int(nb),
+                                  _ptr(cv), _ptr(ci), _ptr(ov), _ptr(oi), _stream())
+    _check(st, "pk_argmax")
+    return oi

@@ -1,0 +1,230 @@
+"""Numerics of the hand-written kernels against plain PyTorch fp32 references (B200 only)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _fp8_weight(n, k, seed=0, sigma=0.02):
+    from pocketllm_b200.formats import fp8
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(n, k, generator=g) * sigma
+    q, s = fp8.quantize_block128(w)
+    return q.cuda(), s.float().cuda(), fp8.dequantize_block128(q, s).cuda()
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+def test_native_library_is_loaded():
+    from pocketllm_b200.ops import lib
+    lib.kernels()
+    assert any("libpocket_kernels.so" in p for p in lib.loaded_library_paths())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(256, 512), (1024, 5120), (384, 2176)])
+def test_matvec_fp8(M, N, K):
+    from pocketllm_b200 import ops
+    q, s, wd = _fp8_weight(N, K, seed=N + K)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    y = ops.matvec(x, q, s, epi=2)
+    ref = x.float() @ wd.t()
+    assert _rel_err(y, ref) < 2e-3
+
+
+def test_matvec_chunked_k_and_bf16_rows():
+    from pocketllm_b200 import ops
+    N, Nb, K, M = 256, 64, 17408, 8
+    q, s, wd = _fp8_weight(N, K, seed=5)
+    wb = (torch.randn(Nb, K, device="cuda") * 0.02).to(torch.bfloat16)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    y = ops.matvec(x, q, s, wb, epi=2)
+    ref = torch.cat([x.float() @ wd.t(), x.float() @ wb.float().t()], dim=1)
+    assert _rel_err(y, ref) < 2e-3
+
+
+def test_matvec_fused_norm_parts_swiglu():
+    from pocketllm_b200 import ops
+    inter, K, M, R = 512, 1024, 2, 3
+    q, s, wd = _fp8_weight(2 * inter, K, seed=9)
+    x = (torch.randn(M, K, device="cuda")).to(torch.bfloat16)
+    parts = torch.randn(R, M, K, device="cuda") * 0.3
+    gamma = torch.randn(K, device="cuda") * 0.1
+    hidden_out = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+    y = ops.matvec(x, q, s, gamma=gamma, parts=parts, hidden_out=hidden_out, epi=1)
+    h = (x.float() + parts.sum(0)).to(torch.bfloat16)
+    assert torch.equal(h, hidden_out)
+    hf = h.float()
+    xn = (hf * torch.rsqrt((hf * hf).mean(-1, keepdim=True) + 1e-6) * (1 + gamma)).to(torch.bfloat16).float()
+    gu = xn @ wd.t()
+    ref = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
+    assert _rel_err(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (512, 1024, 5120), (200, 384, 256), (64, 256, 2176), (1000, 640, 512)])
+def test_gemm_umma_fp8(M, N, K):
+    from pocketllm_b200 import ops
+    q, s, wd = _fp8_weight(N, K, seed=M + N)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    c = ops.gemm_umma(a, q, s, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = a.float() @ wd.t()
+    assert _rel_err(c, ref) < 6e-3
+
+
+def test_gemm_umma_bf16_and_epilogues():
+    from pocketllm_b200 import ops
+    M, N, K = 300, 512, 1024
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    wb = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+    c = ops.gemm_umma(a, wb, epi=ops.EPI_F32)
+    ref = a.float() @ wb.float().t()
+    assert _rel_err(c, ref) < 2e-3
+    # residual add
+    q, s, wd = _fp8_weight(N, K, seed=3)
+    resid = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    c2 = ops.gemm_umma(a, q, s, epi=ops.EPI_RESID, resid=resid)
+    assert _rel_err(c2, resid.float() + a.float() @ wd.t()) < 6e-3
+    # SwiGLU: rows = gate then up
+    c3 = ops.gemm_umma(a, q, s, epi=ops.EPI_SWIGLU)
+    gu = a.float() @ wd.t()
+    ref3 = torch.nn.functional.silu(gu[:, : N // 2]) * gu[:, N // 2:]
+    assert c3.shape == (M, N // 2)
+    assert _rel_err(c3, ref3) < 1.5e-2
+
+
+def test_gemm_umma_narrow_n():
+    from pocketllm_b200 import ops
+    M, N, K = 130, 64, 256
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    wb = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+    c = ops.gemm_umma(a, wb)
+    assert _rel_err(c, a.float() @ wb.float().t()) < 6e-3
+
+
+def test_rmsnorm_embedding_argmax():
+    from pocketllm_b200 import ops
+    x = torch.randn(5, 640, device="cuda").to(torch.bfloat16)
+    g = torch.randn(640, device="cuda") * 0.1
+    y = ops.rmsnorm(x, g, mode=1)
+    xf = x.float()
+    ref = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * (1 + g)
+    assert _rel_err(y, ref) < 5e-3
+    table = torch.randn(100, 64, device="cuda").to(torch.bfloat16)
+    tok = torch.tensor([3, 99, 0], device="cuda", dtype=torch.int32)
+    assert torch.equal(ops.embedding(tok, table), table[tok.long()])
+    logits = torch.randn(4, 5000, device="cuda")
+    logits[1, 77] = logits[1, 4000] = 50.0   # tie: lowest index wins
+    am = ops.argmax(logits, id_offset=10)
+    exp = logits.argmax(-1)
+    exp[1] = 77
+    assert am.tolist() == (exp + 10).tolist()
+
+
+def _deltanet_ref(proj, Hk, Hv, conv_w, conv_state, A_log, dt_bias, norm_w, eps, S):
+    """Serial recurrence in fp32 (cpp_engine/cuda/qwen_half_ops.cu:746-930 semantics)."""
+    T = proj.shape[0]
+    KD, VD = Hk * 128, Hv * 128
+    outs = []
+    tail = conv_state.clone()
+    S = S.clone()
+    rep = Hv // Hk
+    for t in range(T):
+        row = proj[t].float()
+        packed, z = row[: 2 * KD + VD], row[2 * KD + VD: 2 * KD + 2 * VD]
+        a, b = row[2 * KD + 2 * VD: 2 * KD + 2 * VD + Hv], row[2 * KD + 2 * VD + Hv: 2 * KD + 2 * VD + 2 * Hv]
+        win = torch.cat([tail, packed[:, None]], 1)
+        y = torch.nn.functional.silu((win * conv_w).sum(-1)).to(torch.bfloat16).float()
+        tail = win[:, 1:]
+        q, k, v = y[:KD].view(Hk, 128), y[KD:2 * KD].view(Hk, 128), y[2 * KD:].view(Hv, 128)
+        q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6)
+        k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        q, k = q.repeat_interleave(rep, 0), k.repeat_interleave(rep, 0)
+        g = -torch.exp(A_log) * torch.nn.functional.softplus(a + dt_bias)
+        beta = torch.sigmoid(b)
+        S = S * torch.exp(g)[:, None, None]
+        kv = torch.einsum("hkv,hk->hv", S, k)
+        delta = (v - kv) * beta[:, None]
+        S = S + torch.einsum("hk,hv->hkv", k, delta)
+        o = torch.einsum("hkv,hk->hv", S, q) * (128 ** -0.5)
+        o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * norm_w * torch.nn.functional.silu(z.view(Hv, 128))
+        outs.append(o.reshape(VD))
+    return torch.stack(outs), S, tail
+
+
+@pytest.mark.parametrize("Hk,Hv,T", [(2, 4, 1), (2, 4, 9), (1, 1, 5), (2, 2, 40)])
+def test_deltanet_seq(Hk, Hv, T):
+    from pocketllm_b200 import ops
+    torch.manual_seed(Hk * 10 + T)
+    KD, VD = Hk * 128, Hv * 128
+    ld = 2 * KD + 2 * VD + 2 * Hv
+    ld = (ld + 7) // 8 * 8
+    proj = (torch.randn(T, ld, device="cuda")).to(torch.bfloat16)
+    conv_w = torch.randn(2 * KD + VD, 4, device="cuda") * 0.3
+    conv_state = torch.randn(2 * KD + VD, 3, device="cuda")
+    A_log, dt_bias = torch.randn(Hv, device="cuda") * 0.5, torch.randn(Hv, device="cuda") * 0.5
+    norm_w = 1 + torch.randn(128, device="cuda") * 0.05
+    S = torch.randn(Hv, 128, 128, device="cuda") * 0.1
+    ref_o, ref_S, ref_tail = _deltanet_ref(proj, Hk, Hv, conv_w, conv_state, A_log, dt_bias, norm_w, 1e-6, S)
+    S2, cs2 = S.clone(), conv_state.clone()
+    out = ops.deltanet_seq(proj, Hk, Hv, conv_w, cs2, A_log, dt_bias, norm_w, 1e-6, S2)
+    assert _rel_err(out, ref_o) < 1e-2
+    assert _rel_err(S2, ref_S) < 1e-3
+    assert torch.allclose(cs2, ref_tail, atol=1e-6)
+
+
+@pytest.mark.parametrize("M,ctx,Hq,Hkv,nsplit", [(1, 1, 4, 2, 4), (1, 700, 10, 2, 8), (5, 300, 5, 1, 3), (8, 64, 8, 8, 2)])
+def test_gqa_append_and_decode(M, ctx, Hq, Hkv, nsplit):
+    from pocketllm_b200 import ops
+    torch.manual_seed(ctx)
+    D, cap, rd, theta = 128, 1024, 32, 1e6
+    ld = Hq * 2 * D + 2 * Hkv * D
+    kc = torch.zeros(Hkv, cap, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    base = ctx - 1                          # rows occupy positions base .. base+M-1
+    kc[:, :base] = torch.randn(Hkv, base, D, device="cuda").to(torch.bfloat16)
+    vc[:, :base] = torch.randn(Hkv, base, D, device="cuda").to(torch.bfloat16)
+    proj = torch.randn(M, ld, device="cuda").to(torch.bfloat16)
+    pos = torch.arange(base, base + M, device="cuda", dtype=torch.int32)
+    qg, kg = torch.randn(D, device="cuda") * 0.1, torch.randn(D, device="cuda") * 0.1
+    q = ops.qk_norm_rope_append(proj, Hq, Hkv, pos, qg, kg, 1e-6, rd, theta, kc, vc)
+    out = ops.gqa_decode(q, kc, vc, pos, nsplit=nsplit, gate_proj=proj)
+
+    def rope(x, p):
+        half = rd // 2
+        inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rd)
+        ang = (p * inv)
+        cs, sn = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+        x1, x2 = x[..., :half], x[..., half:rd]
+        return torch.cat([x1 * cs - x2 * sn, x2 * cs + x1 * sn, x[..., rd:]], -1)
+
+    def rms(x, g):
+        return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * (1 + g)
+
+    pf = proj.float()
+    for m in range(M):
+        p = base + m
+        qm = pf[m, : Hq * 2 * D].view(Hq, 2 * D)
+        qh, gate = qm[:, :D], qm[:, D:]
+        kh = pf[m, Hq * 2 * D: Hq * 2 * D + Hkv * D].view(Hkv, D)
+        vh = pf[m, Hq * 2 * D + Hkv * D:].view(Hkv, D)
+        qr = rope(rms(qh, qg).to(torch.bfloat16).float(), p).to(torch.bfloat16).float()
+        kr = rope(rms(kh, kg).to(torch.bfloat16).float(), p).to(torch.bfloat16)
+        assert _rel_err(q[m], qr) < 1e-2
+        assert _rel_err(kc[:, p], kr) < 1e-2
+        assert torch.equal(vc[:, p], vh.to(torch.bfloat16))
+        K = kc[:, : p + 1].float().repeat_interleave(Hq // Hkv, 0)
+        V = vc[:, : p + 1].float().repeat_interleave(Hq // Hkv, 0)
+        sc = torch.einsum("hd,htd->ht", q[m].float(), K) * D ** -0.5
+        o = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), V) * torch.sigmoid(gate)
+        assert _rel_err(out[m].view(Hq, D), o) < 1e-2

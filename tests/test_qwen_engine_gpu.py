@@ -1,0 +1,98 @@
+"""Tiny end-to-end model: native engine vs the fp32 PyTorch oracle (same idea as the
+reference's cpp_engine/tests/test_qwen_engine.cpp:1-110, with random instead of zero weights)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=4, hidden=256, inter=512, vocab=1024)
+    tensors = qh.random_checkpoint(cfg, seed=1, sigma=0.05)
+    d = tmp_path_factory.mktemp("tiny_qwen")
+    qh.save_checkpoint(d, cfg, tensors)
+    return cfg, tensors, d
+
+
+def _close(a, b, tol):
+    return ((a - b).norm() / b.norm()).item() < tol
+
+
+def test_engine_matches_oracle_decode_path(tiny):
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    ref = qh.ReferenceModel(cfg, tensors)
+    prompt = [5, 17, 300, 44, 9, 1000, 2]
+    ref_tokens, ref_logits = ref.generate(prompt, 6)
+    eng = qh.QwenEngine(cfg, max_context=256, prefill_chunk=64, use_cuda_graph=False).load(d)
+    first = eng.prefill(prompt)                      # 7 rows -> weight-streaming path
+    assert _close(eng.logits(0), ref_logits[0], 3e-2)
+    assert first == ref_tokens[0]
+    rest = eng.decode(5)
+    assert [first] + rest == ref_tokens
+    assert eng.comm_status() == 0
+    eng.close()
+
+
+def test_cuda_graph_decode_equals_eager(tiny):
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    prompt = list(range(3, 40))
+    outs = []
+    for graph in (False, True):
+        eng = qh.QwenEngine(cfg, max_context=256, prefill_chunk=64, use_cuda_graph=graph).load(d)
+        outs.append(eng.generate(prompt, 12))
+        t = eng.timings()
+        assert t["kernel_launches"] > 0
+        eng.close()
+    assert outs[0] == outs[1]
+
+
+def test_tensor_core_prefill_matches_streaming_prefill(tiny):
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    torch.manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab_size, (100,)).tolist()
+    big = qh.QwenEngine(cfg, max_context=512, prefill_chunk=64).load(d)      # 64 + 36 rows: tcgen05 GEMMs
+    small = qh.QwenEngine(cfg, max_context=512, prefill_chunk=8).load(d)     # 8-row groups: matvec path
+    tb, ts = big.prefill(prompt), small.prefill(prompt)
+    lb, ls = big.logits(0), small.logits(0)
+    assert _close(lb, ls, 3e-2)
+    assert big.comm_status() == 0
+    if (ls.topk(2).values[0] - ls.topk(2).values[1]) > 0.05 * ls.abs().max():
+        assert tb == ts
+    # continuing from either state gives the same greedy continuation
+    assert big.position == small.position == 100
+    big.close()
+    small.close()
+
+
+def test_forward_rows_equals_step_by_step(tiny):
+    """Speculative verify: M rows at once == M single steps (tokens and state)."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    prompt = [11, 12, 13, 14, 15]
+    a = qh.QwenEngine(cfg, max_context=256, prefill_chunk=8).load(d)
+    b = qh.QwenEngine(cfg, max_context=256, prefill_chunk=8).load(d)
+    fa, fb = a.prefill(prompt), b.prefill(prompt)
+    assert fa == fb
+    seq = [fa] + a.decode(4)                       # plain greedy: 5 tokens
+    rows = b.forward_rows(seq[:4])                 # feed the first 4 as a perfect draft
+    assert rows == seq[1:5]                        # each row predicts its successor
+    assert a.decode(3) == b.decode(3)              # same state afterwards
+    a.close()
+    b.close()
+
+
+def test_random_init_runs_and_is_deterministic():
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=4, hidden=256, inter=512, vocab=1024)
+    outs = []
+    for _ in range(2):
+        eng = qh.QwenEngine(cfg, max_context=128, prefill_chunk=32).init_random(seed=3, sigma=0.05)
+        outs.append(eng.generate([1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12], 8))
+        eng.close()
+    assert outs[0] == outs[1]
+    assert all(0 <= t < cfg.vocab_size for t in outs[0])
