@@ -1,0 +1,198 @@
+#!/usr/bin/env python
+"""Headline benchmark: single-request prefill and decode tok/s of the Qwen3.8-27B-FP8-shaped
+hybrid decoder (64 layers, hidden 5120, SwiGLU 17408, vocab 151936; every 4th layer GQA
+40/8 heads, the rest Gated DeltaNet 16/32 heads; FP8 E4M3 weights with 128x128 scales),
+random-init weights, uniform-random prompt, greedy decode, tensor parallel over N GPUs.
+
+One "step" is one request: prefill of `--prompt-len` tokens (the first generated token
+belongs to prefill) followed by `--decode-len` greedy decode steps. `value` is decode
+tokens per second of the whole job, device-timed (CUDA events inside the engine), max over
+ranks; `prefill_tok_s` is reported beside it. `e2e` repeats the measurement through the
+public Python API with the prompt copied from pinned host memory and every generated
+token read back to the host as soon as its step ends.
+
+    python bench.py [--gpus N --steps K --warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+PUBLISHED_DECODE_TOK_S = 35.87   # reference README.md:37, 4x RTX 2080 Ti TP4, 512-token prompt
+PUBLISHED_PREFILL_TOK_S = 416.48
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[tuple[float, float, dict[str, str]]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
+                if out:
+                    f = [x.strip() for x in out[0].split(",")]
+                    self.samples.append((float(f[0]), float(f[1]), {"hw_slowdown": f[2], "hw_thermal_slowdown": f[3],
+                                                                   "sw_thermal_slowdown": f[4], "sw_power_cap": f[5]}))
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self) -> "ClockSampler":
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a) -> None:
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        reasons = sorted({k for _, _, r in self.samples for k, v in r.items() if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_max_mhz": max(s[1] for s in self.samples),
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from pocketllm_b200.models import qwen_hybrid as qh
+    from pocketllm_b200.parallel import tp as tp_mod
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = qh.QwenHybridConfig.benchmark_27b() if args.model == "qwen27b" else qh.QwenHybridConfig.tiny()
+    ctx = args.prompt_len + args.decode_len + 16
+    eng = qh.QwenEngine(cfg, tp_rank=rank, tp_world=world, device=local, max_context=ctx,
+                        prefill_chunk=min(args.prefill_chunk, max(args.prompt_len, 8)))
+    eng.init_random(seed=0, sigma=0.02)
+    if world > 1:
+        tp_mod.connect_engine(eng)
+    g = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
+               for _ in range(args.warmup + args.steps)]
+
+    def barrier() -> None:
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_request(prompt, sync_each_step: bool):
+        eng.reset()
+        first = eng.prefill(prompt)
+        rest = eng.decode(args.decode_len, sync_each_step=sync_each_step)
+        return [first] + rest
+
+    for i in range(args.warmup):
+        one_request(prompts[i], False)
+
+    # ---- device-timed run: exactly K requests ----
+    pre_ms = dec_ms = 0.0
+    launches0 = eng.timings()["kernel_launches"]
+    barrier()
+    t0 = time.perf_counter()
+    with ClockSampler(local) as clocks:
+        for i in range(args.steps):
+            toks = one_request(prompts[args.warmup + i], False)
+            t = eng.timings()
+            pre_ms += t["prefill_ms"]
+            dec_ms += t["decode_ms"]
+        barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    launches = eng.timings()["kernel_launches"] - launches0
+
+    # ---- end to end through the public API: every token read back per step ----
+    barrier()
+    e0 = time.perf_counter()
+    e_dec = 0.0
+    for i in range(args.steps):
+        eng.reset()
+        torch.cuda.synchronize()
+        eng.prefill(prompts[args.warmup + i])
+        d0 = time.perf_counter()
+        eng.decode(args.decode_len, sync_each_step=True)
+        e_dec += time.perf_counter() - d0
+    barrier()
+    e2e_wall = time.perf_counter() - e0
+
+    vals = torch.tensor([pre_ms, dec_ms, wall_ms, e_dec * 1e3, e2e_wall * 1e3], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    pre_ms, dec_ms, wall_ms, e_dec_ms, e2e_wall_ms = vals.tolist()
+    status = eng.comm_status()
+    decode_tok_s = args.steps * args.decode_len / (dec_ms / 1e3)
+    prefill_tok_s = args.steps * args.prompt_len / (pre_ms / 1e3)
+    res = {
+        "metric": "single-request decode tok/s (Qwen3.8-27B-FP8 shape, 512-token prompt, 256 greedy steps)",
+        "value": round(decode_tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round((pre_ms + dec_ms) / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": round(decode_tok_s / PUBLISHED_DECODE_TOK_S, 3), "dtype": "bf16 activations, fp8 e4m3 weights (128x128 scales)",
+        "data": "synthetic: uniform-random token prompts, random-init N(0,0.02) weights quantised to FP8",
+        "prefill_tok_s": round(prefill_tok_s, 1), "prefill_vs_baseline": round(prefill_tok_s / PUBLISHED_PREFILL_TOK_S, 2),
+        "prefill_ms": round(pre_ms / args.steps, 3), "decode_ms_per_token": round(dec_ms / args.steps / args.decode_len, 4),
+        "config": {"model": "Qwen3.8-27B-FP8-shaped hybrid (64L, hidden 5120, inter 17408, vocab 151936)" if args.model == "qwen27b" else "tiny",
+                   "global_batch": 1, "seq_len": args.prompt_len, "decode_len": args.decode_len,
+                   "parallelism": f"tp{world}", "l2": "inputs larger than L2 (27 GB of weights streamed per token)",
+                   "prefill_chunk": args.prefill_chunk},
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(args.steps * args.decode_len / (e_dec_ms / 1e3), 2), "unit": "tok/s",
+                "h2d_bytes_per_step": args.prompt_len * 4, "d2h_bytes_per_step": (args.decode_len + 1) * 4,
+                "wall_ms_per_step": round(e2e_wall_ms / args.steps, 3)},
+        "gpu_launches": int(launches), "wall_ms": round(wall_ms, 1), "comm_status": status,
+        "weight_bytes_per_rank": eng.weight_bytes, "last_tokens": toks[-4:],
+    }
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return res if rank == 0 else {}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--decode-len", type=int, default=256)
+    ap.add_argument("--prefill-chunk", type=int, default=512)
+    ap.add_argument("--model", default="qwen27b", choices=["qwen27b", "tiny"])
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        from baseline import reference_arm
+        res = reference_arm.run(args)
+    else:
+        res = run_ours(args)
+    if res:
+        print(json.dumps(res), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
