@@ -25,6 +25,12 @@ int pk_deltanet_seq(const void* proj, int ld, int T, int key_heads, int value_he
                     const float* dt_bias, const float* norm_w, float eps, float* state, void* out,
                     cudaStream_t stream);
 
+size_t pk_deltanet_chunk_workspace(int T, int key_heads, int value_heads);
+int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, int value_heads, int key_dim,
+                        int value_dim, const float* conv_w, float* conv_state, const float* A_log,
+                        const float* dt_bias, const float* norm_w, float eps, float* state, void* out, float* ws,
+                        cudaStream_t stream);
+
 int pk_qk_norm_rope_append(const void* proj, int ld, int M, int Hq, int Hkv, int head_dim, const int* pos,
                            const float* q_gamma, const float* k_gamma, float eps, int rotary_dim, float theta,
                            void* q_out, void* kcache, void* vcache, int ctx_cap, cudaStream_t stream);

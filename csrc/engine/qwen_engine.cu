@@ -173,6 +173,7 @@ void QwenEngine::alloc_buffers() {
   const size_t ws_small = (size_t)kSmallRows * hq_l_ * opt_.decode_splits * (kHeadDim + 2);
   const size_t ws_big = R * hq_l_ * 1 * (kHeadDim + 2);
   attn_ws_ = (float*)dalloc(std::max(ws_small, ws_big) * sizeof(float));
+  lin_ws_ = (float*)dalloc(pk_deltanet_chunk_workspace(rows_cap_, kh_l_, vh_l_) * sizeof(float));
   logits_ = (float*)dalloc((size_t)kSmallRows * vocab_l_ * sizeof(float));
   cand_val_ = (float*)dalloc(kSmallRows * kArgmaxBlocks * sizeof(float));
   cand_idx_ = (int*)dalloc(kSmallRows * kArgmaxBlocks * sizeof(int));
@@ -616,9 +617,16 @@ void QwenEngine::run_chunk(int M) {
       check(pk_gemm_umma(xn_, hidden_, L.in_proj_ab, nullptr, 1, M, 2 * vh_l_, hidden_, 0,
                          (char*)proj_ + (size_t)L.in_proj.N * 2, nullptr, ld_proj_, gemm_status_, stream_),
             "gemm_umma(ab)");
-      check(pk_deltanet_seq(proj_, ld_proj_, M, kh_l_, vh_l_, kHeadDim, kHeadDim, L.conv_w, L.conv_state, L.A_log,
-                            L.dt_bias, L.lin_norm, eps, L.lin_state, attn_out_, stream_),
-            "deltanet_seq");
+      if (M >= 32) {
+        check(pk_deltanet_chunked(proj_, ld_proj_, M, kh_l_, vh_l_, kHeadDim, kHeadDim, L.conv_w, L.conv_state, L.A_log,
+                                  L.dt_bias, L.lin_norm, eps, L.lin_state, attn_out_, lin_ws_, stream_),
+              "deltanet_chunked");
+        launches_ += 4;  // five kernels in that call
+      } else {
+        check(pk_deltanet_seq(proj_, ld_proj_, M, kh_l_, vh_l_, kHeadDim, kHeadDim, L.conv_w, L.conv_state, L.A_log,
+                              L.dt_bias, L.lin_norm, eps, L.lin_state, attn_out_, stream_),
+              "deltanet_seq");
+      }
       gemm(attn_out_, vd_l_, L.out_proj, 2, hid, hid, hidden_);
     }
     check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, L.post_norm, 1, eps, xn_, nullptr, stream_), "rmsnorm");

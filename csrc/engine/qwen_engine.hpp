@@ -163,6 +163,7 @@ class QwenEngine {
   void* q_buf_ = nullptr;
   void* mlp_h_ = nullptr;
   float* attn_ws_ = nullptr;
+  float* lin_ws_ = nullptr;   // chunked DeltaNet scan workspace
   float* logits_ = nullptr;   // [8, vocab_l]
   float* cand_val_ = nullptr;
   int* cand_idx_ = nullptr;

@@ -1,0 +1,395 @@
+// Chunked Gated DeltaNet scan for prefill (chunk = 64 tokens).
+//
+// The recurrence  S_t = e^{g_t} S_{t-1} + k_t (x) delta_t,  delta_t = beta_t (v_t - (e^{g_t} S_{t-1})^T k_t)
+// is serial in t; inside a chunk it is rewritten (WY / UT transform) so that only one
+// state update per chunk stays serial. With G_i the running sum of g inside the chunk,
+//   A_ij = beta_i e^{G_i - G_j} (k_i . k_j)  (j < i),       (I + A) Delta = beta (V - e^{G} K S_0)
+//   U = (I + A)^{-1} (beta V),  W = (I + A)^{-1} (beta e^{G} K),   Delta = U - W S_0
+//   O = e^{G} Q S_0 + P Delta,  P_ij = e^{G_i - G_j} (q_i . k_j)  (j <= i)
+//   S_C = e^{G_C} S_0 + (e^{G_C - G} K)^T Delta
+// Everything that does not touch S (conv + SiLU, norms, gates, A, U, W, P) runs in
+// parallel over (head, chunk); the state pass runs over (head, quarter of the value dim).
+// The reference engine has only the token-serial form for prefill
+// (cpp_engine/cuda/qwen_half_ops.cu:858-930, one 128-float state column per thread).
+//
+// All matrix products here are fp32 SIMT; they are the next candidates for tcgen05 tiles.
+#include "../common/pk_common.cuh"
+
+namespace {
+
+using namespace pk;
+
+constexpr int CH = 64;   // chunk length
+constexpr int D = 128;   // key and value head dim
+constexpr int KS = 129;  // padded row stride of K / Q tiles in shared memory
+
+// ---------------------------------------------------------------------------------------
+// prep: conv + SiLU, L2 norms, gates, for every token in parallel
+
+struct PrepParams {
+  const bf16* proj;  // [T, ld]: q(KD) | k(KD) | v(VD) | z(VD) | a(Hv) | b(Hv)
+  int ld, T, Tpad, Hk, Hv;
+  const float* conv_w;      // [C, 4]
+  const float* conv_state;  // [C, 3] inputs at times -3, -2, -1
+  const float* A_log;
+  const float* dt_bias;
+  float* qn;    // [Tpad, Hk, 128] l2-normalised, times 1/sqrt(128)
+  float* kn;    // [Tpad, Hk, 128]
+  float* v;     // [Tpad, Hv, 128]
+  float* g;     // [Tpad, Hv] log decay
+  float* beta;  // [Tpad, Hv]
+};
+
+__device__ __forceinline__ float conv_input(const PrepParams& p, int t, int ch) {
+  return t >= 0 ? __bfloat162float(p.proj[(size_t)t * p.ld + ch]) : p.conv_state[(size_t)ch * 3 + (3 + t)];
+}
+
+__global__ void __launch_bounds__(512) deltanet_prep_kernel(const PrepParams p) {
+  const int t = blockIdx.x, hk = blockIdx.y;
+  const int rep = p.Hv / p.Hk;
+  const int seg = threadIdx.x >> 7, d = threadIdx.x & 127;  // seg 0: q, 1: k, 2+: value heads
+  const int KD = p.Hk * D, VD = p.Hv * D;
+  __shared__ float s_sum[4][4];
+  const int h = hk * rep + (seg - 2);
+  float y = 0.f;
+  if (t < p.T) {
+    const int ch = seg == 0 ? hk * D + d : seg == 1 ? KD + hk * D + d : 2 * KD + h * D + d;
+    const float4 w = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch * 4);
+    y = w.x * conv_input(p, t - 3, ch) + w.y * conv_input(p, t - 2, ch) + w.z * conv_input(p, t - 1, ch) +
+        w.w * conv_input(p, t, ch);
+    y = __bfloat162float(__float2bfloat16(silu(y)));
+  }
+  const float ss = warp_sum(y * y);
+  if ((threadIdx.x & 31) == 0) s_sum[seg][(threadIdx.x >> 5) & 3] = ss;
+  __syncthreads();
+  if (seg < 2) {
+    const float tot = s_sum[seg][0] + s_sum[seg][1] + s_sum[seg][2] + s_sum[seg][3];
+    const float n = rsqrtf(tot + 1e-6f) * (seg == 0 ? rsqrtf((float)D) : 1.f);
+    float* dst = (seg == 0 ? p.qn : p.kn) + ((size_t)t * p.Hk + hk) * D + d;
+    *dst = y * n;
+  } else {
+    p.v[((size_t)t * p.Hv + h) * D + d] = y;
+    if (d == 0) {
+      float gg = 0.f, bb = 0.f;
+      if (t < p.T) {
+        const bf16* row = p.proj + (size_t)t * p.ld;
+        const float a = __bfloat162float(row[2 * KD + 2 * VD + h]);
+        const float b = __bfloat162float(row[2 * KD + 2 * VD + p.Hv + h]);
+        gg = -__expf(p.A_log[h]) * softplusf_(a + p.dt_bias[h]);
+        bb = sigmoidf_(b);
+      }
+      p.g[(size_t)t * p.Hv + h] = gg;
+      p.beta[(size_t)t * p.Hv + h] = bb;
+    }
+  }
+}
+
+// New conv tail = inputs of the last three tokens. Runs after prep (which reads the old tail).
+__global__ void deltanet_tail_kernel(const bf16* proj, int ld, int T, int channels, float* conv_state) {
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= channels) return;
+  float nv[3];
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int t = T - 3 + j;
+    nv[j] = t >= 0 ? __bfloat162float(proj[(size_t)t * ld + ch]) : conv_state[(size_t)ch * 3 + (3 + t)];
+  }
+#pragma unroll
+  for (int j = 0; j < 3; ++j) conv_state[(size_t)ch * 3 + j] = nv[j];
+}
+
+// ---------------------------------------------------------------------------------------
+// per (chunk, value head): G, A, U, W, P
+
+struct ChunkParams {
+  const float* qn; const float* kn; const float* v; const float* g; const float* beta;
+  int Hk, Hv, Tpad;
+  float* U;   // [Hv, Tpad, 128]
+  float* W;   // [Hv, Tpad, 128]
+  float* P;   // [Hv, Tpad/64, 64, 64]
+  float* G;   // [Hv, Tpad] running log decay inside the chunk
+};
+
+__global__ void __launch_bounds__(256) deltanet_chunk_kernel(const ChunkParams p) {
+  extern __shared__ float smem[];
+  float* Ks = smem;                  // [64][129]
+  float* Qs = Ks + CH * KS;          // [64][129]
+  float* As = Qs + CH * KS;          // [64][64]
+  float* Gs = As + CH * CH;          // [64]
+  float* Bs = Gs + CH;               // [64]
+  const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int hk = h / (p.Hv / p.Hk);
+  const int t0 = c * CH;
+
+  for (int i = tid; i < CH * D; i += 256) {
+    const int r = i >> 7, d = i & 127;
+    Ks[r * KS + d] = p.kn[((size_t)(t0 + r) * p.Hk + hk) * D + d];
+    Qs[r * KS + d] = p.qn[((size_t)(t0 + r) * p.Hk + hk) * D + d];
+  }
+  if (tid < 32) {
+    // inclusive scan of g over the 64 tokens (two per lane)
+    const float g0 = p.g[(size_t)(t0 + 2 * tid) * p.Hv + h], g1 = p.g[(size_t)(t0 + 2 * tid + 1) * p.Hv + h];
+    float s = g0 + g1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float n = __shfl_up_sync(0xffffffffu, s, o);
+      if (tid >= o) s += n;
+    }
+    Gs[2 * tid + 1] = s;
+    Gs[2 * tid] = s - g1;
+    Bs[2 * tid] = p.beta[(size_t)(t0 + 2 * tid) * p.Hv + h];
+    Bs[2 * tid + 1] = p.beta[(size_t)(t0 + 2 * tid + 1) * p.Hv + h];
+  }
+  __syncthreads();
+  if (tid < CH) p.G[(size_t)h * p.Tpad + t0 + tid] = Gs[tid];
+
+  // A and P: thread owns column j and rows i = ig + 4n
+  {
+    const int j = tid & 63, ig = tid >> 6;
+    float accA[16], accP[16];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) { accA[n] = 0.f; accP[n] = 0.f; }
+    for (int k = 0; k < D; ++k) {
+      const float kj = Ks[j * KS + k];
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        const int i = ig + 4 * n;
+        accA[n] = fmaf(Ks[i * KS + k], kj, accA[n]);
+        accP[n] = fmaf(Qs[i * KS + k], kj, accP[n]);
+      }
+    }
+    float* Pout = p.P + (((size_t)h * (p.Tpad / CH) + c) * CH) * CH;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      const int i = ig + 4 * n;
+      const float e = __expf(Gs[i] - Gs[j]);
+      As[i * CH + j] = j < i ? Bs[i] * e * accA[n] : 0.f;
+      Pout[i * CH + j] = j <= i ? e * accP[n] : 0.f;
+    }
+  }
+  __syncthreads();
+
+  // Forward substitution, one right-hand-side column per thread: columns 0..127 are
+  // beta*V (-> U), columns 128..255 are beta*e^G*K (-> W).
+  {
+    const int col = tid & 127;
+    const bool isW = tid >= 128;
+    float X[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      float b;
+      if (isW) b = Bs[i] * __expf(Gs[i]) * Ks[i * KS + col];
+      else b = Bs[i] * p.v[((size_t)(t0 + i) * p.Hv + h) * D + col];
+      float acc = b;
+#pragma unroll
+      for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+        const float4 a = *reinterpret_cast<const float4*>(As + i * CH + j4 * 4);
+        // entries at or right of the diagonal are stored as zero
+        if (j4 * 4 + 0 < i) acc = fmaf(-a.x, X[j4 * 4 + 0], acc);
+        if (j4 * 4 + 1 < i) acc = fmaf(-a.y, X[j4 * 4 + 1], acc);
+        if (j4 * 4 + 2 < i) acc = fmaf(-a.z, X[j4 * 4 + 2], acc);
+        if (j4 * 4 + 3 < i) acc = fmaf(-a.w, X[j4 * 4 + 3], acc);
+      }
+      X[i] = acc;
+      float* dst = (isW ? p.W : p.U) + ((size_t)h * p.Tpad + t0 + i) * D + col;
+      *dst = acc;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// state pass: serial over chunks, parallel over (value head, 32-column slice of the state)
+
+struct StateParams {
+  const float* qn; const float* kn; const float* U; const float* W; const float* P; const float* G;
+  int Hk, Hv, Tpad, nchunks;
+  float* state;  // [Hv, 128, 128]
+  float* O;      // [Tpad, Hv, 128]
+};
+
+constexpr int SL = 32;  // state columns per block
+
+__global__ void __launch_bounds__(256) deltanet_state_kernel(const StateParams p) {
+  extern __shared__ float smem[];
+  float* Ws = smem;               // [64][128]
+  float* Qe = Ws + CH * D;        // [64][128]  e^{G_i} q_i
+  float* Kd = Qe + CH * D;        // [64][128]  e^{G_C - G_i} k_i
+  float* Ps = Kd + CH * D;        // [64][64]
+  float* Us = Ps + CH * CH;       // [64][32]
+  float* Ds = Us + CH * SL;       // [64][32]   Delta
+  float* Ss = Ds + CH * SL;       // [128][32]  state slice
+  float* Gs = Ss + D * SL;        // [64]
+  const int h = blockIdx.x, sl = blockIdx.y, tid = threadIdx.x;
+  const int hk = h / (p.Hv / p.Hk);
+  const int tx = tid & 31, ty = tid >> 5;
+  float* sp = p.state + (size_t)h * D * D + sl * SL;
+  for (int i = tid; i < D * SL; i += 256) Ss[i] = sp[(size_t)(i >> 5) * D + (i & 31)];
+
+  for (int c = 0; c < p.nchunks; ++c) {
+    const int t0 = c * CH;
+    __syncthreads();
+    if (tid < CH) Gs[tid] = p.G[(size_t)h * p.Tpad + t0 + tid];
+    __syncthreads();
+    const float gC = Gs[CH - 1];
+    for (int i = tid; i < CH * D / 4; i += 256) {
+      const int r = i >> 5, d4 = (i & 31) * 4;
+      *reinterpret_cast<float4*>(Ws + r * D + d4) =
+          *reinterpret_cast<const float4*>(p.W + ((size_t)h * p.Tpad + t0 + r) * D + d4);
+      float4 q = *reinterpret_cast<const float4*>(p.qn + ((size_t)(t0 + r) * p.Hk + hk) * D + d4);
+      float4 k = *reinterpret_cast<const float4*>(p.kn + ((size_t)(t0 + r) * p.Hk + hk) * D + d4);
+      const float eq = __expf(Gs[r]), ek = __expf(gC - Gs[r]);
+      q.x *= eq; q.y *= eq; q.z *= eq; q.w *= eq;
+      k.x *= ek; k.y *= ek; k.z *= ek; k.w *= ek;
+      *reinterpret_cast<float4*>(Qe + r * D + d4) = q;
+      *reinterpret_cast<float4*>(Kd + r * D + d4) = k;
+    }
+    for (int i = tid; i < CH * CH / 4; i += 256)
+      *reinterpret_cast<float4*>(Ps + i * 4) =
+          *reinterpret_cast<const float4*>(p.P + (((size_t)h * p.nchunks + c) * CH) * CH + i * 4);
+    for (int i = tid; i < CH * SL; i += 256)
+      Us[i] = p.U[((size_t)h * p.Tpad + t0 + (i >> 5)) * D + sl * SL + (i & 31)];
+    __syncthreads();
+
+    // Delta = U - W S, rows ty*8 .. ty*8+7
+    float acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc[r] = Us[(ty * 8 + r) * SL + tx];
+    for (int k = 0; k < D; k += 4) {
+      const float s0 = Ss[(k + 0) * SL + tx], s1 = Ss[(k + 1) * SL + tx], s2 = Ss[(k + 2) * SL + tx],
+                  s3 = Ss[(k + 3) * SL + tx];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 w = *reinterpret_cast<const float4*>(Ws + (ty * 8 + r) * D + k);
+        acc[r] -= w.x * s0 + w.y * s1 + w.z * s2 + w.w * s3;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) Ds[(ty * 8 + r) * SL + tx] = acc[r];
+    __syncthreads();
+
+    // O = Qe S + P Delta
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+    for (int k = 0; k < D; k += 4) {
+      const float s0 = Ss[(k + 0) * SL + tx], s1 = Ss[(k + 1) * SL + tx], s2 = Ss[(k + 2) * SL + tx],
+                  s3 = Ss[(k + 3) * SL + tx];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 w = *reinterpret_cast<const float4*>(Qe + (ty * 8 + r) * D + k);
+        acc[r] += w.x * s0 + w.y * s1 + w.z * s2 + w.w * s3;
+      }
+    }
+    for (int j = 0; j < CH; j += 4) {
+      const float d0 = Ds[(j + 0) * SL + tx], d1 = Ds[(j + 1) * SL + tx], d2 = Ds[(j + 2) * SL + tx],
+                  d3 = Ds[(j + 3) * SL + tx];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 w = *reinterpret_cast<const float4*>(Ps + (ty * 8 + r) * CH + j);
+        acc[r] += w.x * d0 + w.y * d1 + w.z * d2 + w.w * d3;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      p.O[((size_t)(t0 + ty * 8 + r) * p.Hv + h) * D + sl * SL + tx] = acc[r];
+
+    // S <- e^{G_C} S + Kd^T Delta, rows ty*16 .. ty*16+15
+    float sn[16];
+    const float eC = __expf(gC);
+#pragma unroll
+    for (int r = 0; r < 16; ++r) sn[r] = eC * Ss[(ty * 16 + r) * SL + tx];
+    for (int j = 0; j < CH; ++j) {
+      const float dj = Ds[j * SL + tx];
+#pragma unroll
+      for (int r4 = 0; r4 < 4; ++r4) {
+        const float4 k = *reinterpret_cast<const float4*>(Kd + j * D + ty * 16 + r4 * 4);
+        sn[r4 * 4 + 0] = fmaf(k.x, dj, sn[r4 * 4 + 0]);
+        sn[r4 * 4 + 1] = fmaf(k.y, dj, sn[r4 * 4 + 1]);
+        sn[r4 * 4 + 2] = fmaf(k.z, dj, sn[r4 * 4 + 2]);
+        sn[r4 * 4 + 3] = fmaf(k.w, dj, sn[r4 * 4 + 3]);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 16; ++r) Ss[(ty * 16 + r) * SL + tx] = sn[r];
+  }
+  __syncthreads();
+  for (int i = tid; i < D * SL; i += 256) sp[(size_t)(i >> 5) * D + (i & 31)] = Ss[i];
+}
+
+// ---------------------------------------------------------------------------------------
+// gated RMSNorm of the scan output
+
+__global__ void __launch_bounds__(128) deltanet_out_kernel(const float* O, const bf16* proj, int ld, int Hk, int Hv,
+                                                           const float* norm_w, float eps, bf16* out) {
+  const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  __shared__ float red[40];
+  const float o = O[((size_t)t * Hv + h) * D + d];
+  const float ss = block_sum(o * o, red);
+  const int KD = Hk * D, VD = Hv * D;
+  const float z = __bfloat162float(proj[(size_t)t * ld + 2 * KD + VD + h * D + d]);
+  out[(size_t)t * VD + h * D + d] = __float2bfloat16(o * rsqrtf(ss / (float)D + eps) * norm_w[d] * silu(z));
+}
+
+}  // namespace
+
+// Workspace floats needed for T tokens (Tpad = T rounded up to 64).
+PK_API size_t pk_deltanet_chunk_workspace(int T, int key_heads, int value_heads) {
+  const size_t Tpad = (size_t)((T + CH - 1) / CH) * CH;
+  return Tpad * key_heads * D * 2      // qn, kn
+         + Tpad * value_heads * D * 4  // v, U, W, O
+         + Tpad * value_heads * 3      // g, beta, G
+         + (size_t)value_heads * Tpad * CH;  // P
+}
+
+// Same contract as pk_deltanet_seq (state and conv_state advance by T tokens), but the
+// work is chunk-parallel. `ws` holds pk_deltanet_chunk_workspace(T, ...) floats.
+PK_API int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, int value_heads, int key_dim,
+                               int value_dim, const float* conv_w, float* conv_state, const float* A_log,
+                               const float* dt_bias, const float* norm_w, float eps, float* state, void* out,
+                               float* ws, cudaStream_t stream) {
+  if (key_dim != D || value_dim != D) return PK_ERR_UNSUPPORTED;
+  if (T < 1 || key_heads < 1 || value_heads % key_heads != 0) return PK_ERR_BAD_ARG;
+  const int rep = value_heads / key_heads;
+  if (rep > 2) return PK_ERR_UNSUPPORTED;
+  const int nchunks = (T + CH - 1) / CH, Tpad = nchunks * CH;
+  float* qn = ws;
+  float* kn = qn + (size_t)Tpad * key_heads * D;
+  float* v = kn + (size_t)Tpad * key_heads * D;
+  float* U = v + (size_t)Tpad * value_heads * D;
+  float* W = U + (size_t)Tpad * value_heads * D;
+  float* O = W + (size_t)Tpad * value_heads * D;
+  float* g = O + (size_t)Tpad * value_heads * D;
+  float* beta = g + (size_t)Tpad * value_heads;
+  float* G = beta + (size_t)Tpad * value_heads;
+  float* P = G + (size_t)Tpad * value_heads;
+
+  PrepParams pp{(const pk::bf16*)proj, ld, T, Tpad, key_heads, value_heads, conv_w, conv_state, A_log, dt_bias,
+                qn, kn, v, g, beta};
+  deltanet_prep_kernel<<<dim3(Tpad, key_heads), 128 * (2 + rep), 0, stream>>>(pp);
+  PK_CHECK_LAUNCH();
+  const int channels = (2 * key_heads + value_heads) * D;
+  deltanet_tail_kernel<<<(channels + 255) / 256, 256, 0, stream>>>((const pk::bf16*)proj, ld, T, channels, conv_state);
+  PK_CHECK_LAUNCH();
+
+  static bool configured = false;
+  const size_t smem_chunk = (size_t)(2 * CH * KS + CH * CH + 2 * CH) * sizeof(float);
+  const size_t smem_state = (size_t)(3 * CH * D + CH * CH + 2 * CH * SL + D * SL + CH) * sizeof(float);
+  if (!configured) {
+    if (cudaFuncSetAttribute(deltanet_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_chunk) != cudaSuccess ||
+        cudaFuncSetAttribute(deltanet_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state) != cudaSuccess) {
+      pk_set_last_cuda_error((int)cudaGetLastError());
+      return PK_ERR_CUDA;
+    }
+    configured = true;
+  }
+  ChunkParams cp{qn, kn, v, g, beta, key_heads, value_heads, Tpad, U, W, P, G};
+  deltanet_chunk_kernel<<<dim3(nchunks, value_heads), 256, smem_chunk, stream>>>(cp);
+  PK_CHECK_LAUNCH();
+  StateParams sp{qn, kn, U, W, P, G, key_heads, value_heads, Tpad, nchunks, state, O};
+  deltanet_state_kernel<<<dim3(value_heads, D / SL), 256, smem_state, stream>>>(sp);
+  PK_CHECK_LAUNCH();
+  deltanet_out_kernel<<<dim3(T, value_heads), 128, 0, stream>>>(O, (const pk::bf16*)proj, ld, key_heads, value_heads,
+                                                              norm_w, eps, (pk::bf16*)out);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}

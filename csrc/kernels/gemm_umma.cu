@@ -1,15 +1,16 @@
 // Prefill GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * dequant(W[N,K])^T.
 //
-//   A   bf16 activations, moved by TMA (2-D tiled, 128-byte swizzle, no multicast) into a
-//       4-stage shared-memory ring.
-//   W   quantised weights that are NEVER expanded in HBM: four producer warps read the
-//       raw tile (FP8 E4M3 with one fp32 scale per 128x128 block, or plain bf16), decode
-//       it in registers and write the bf16 K-major tile into shared memory in the same
-//       128-byte swizzle the tensor core expects.
-//   MMA one elected thread issues tcgen05.mma (kind::f16, 128x128x16) with the fp32
-//       accumulator in TMEM; tcgen05.commit releases ring slots and signals the epilogue.
-//   EPI the producer warps read TMEM with tcgen05.ld and fuse: bf16 store, residual add,
-//       SiLU(gate)*up (gate and up rows share a tile), or an fp32 partial store.
+//   A    bf16 activations, moved by TMA (2-D tiled, 128-byte swizzle, no multicast) into a
+//        5-stage shared-memory ring.
+//   W    quantised weights that are NEVER expanded in HBM. The raw FP8 E4M3 tile (128 rows x
+//        64 bytes) rides the same TMA ring; eight decode warps turn it into the bf16 K-major
+//        tile in the 128-byte swizzle the tensor core expects, applying the fp32 scale of
+//        its 128x128 block on the way. bf16 weights skip the decode: TMA writes the
+//        swizzled tile directly.
+//   MMA  one elected thread issues tcgen05.mma (kind::f16, 128x128x16) with the fp32
+//        accumulator in TMEM; tcgen05.commit releases ring slots and signals the epilogue.
+//   EPI  the decode warps read TMEM with tcgen05.ld and fuse: bf16 store, residual add,
+//        SiLU(gate)*up (gate and up rows share a tile), or an fp32 partial store.
 //
 // Replaces the reference's prefill paths: cpp_engine/cuda/qwen_half_ops.cu:379-583 (SIMT
 // tiles with an LUT decode) and cpp_engine/cuda/fp8_ops.cu:142-300 (whole-weight dequant
@@ -22,16 +23,17 @@ using namespace pk;
 using namespace pk::sm100;
 
 constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int kStages = 4;
-constexpr int kTileBytes = BM * BK * 2;  // 16 KB per operand tile (bf16)
-constexpr int kThreads = 192;            // warp0 TMA, warp1 MMA, warps 2-5 dequant + epilogue
+constexpr int kStages = 5;
+constexpr int kTileBytes = BM * BK * 2;   // 16 KB per bf16 operand tile
+constexpr int kRawBytes = BN * BK;        // 8 KB of raw FP8 per stage
+constexpr int kDecodeWarps = 8;
+constexpr int kThreads = 64 + kDecodeWarps * 32;  // warp0 TMA, warp1 MMA, warps 2-9 decode + epilogue
 constexpr uint32_t kTmemCols = 128;
 
 enum { WFMT_FP8_BLOCK128 = 0, WFMT_BF16 = 1 };
 enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_RESID = 2, EPI_F32 = 3 };
 
 struct GemmParams {
-  const void* W;        // [N, K] raw weights
   const float* scale;   // fp8: [ceil(N/128), ceil(K/128)]
   int wfmt;
   int M, N, K;
@@ -46,25 +48,25 @@ struct GemmParams {
 struct __align__(1024) SmemLayout {
   uint8_t a[kStages][kTileBytes];
   uint8_t b[kStages][kTileBytes];
-  uint64_t full_a[kStages];
-  uint64_t full_b[kStages];
-  uint64_t empty[kStages];
+  uint8_t raw[kStages][kRawBytes];
+  uint64_t full_in[kStages];   // TMA landed (A tile + raw or bf16 weight tile)
+  uint64_t full_b[kStages];    // decode warps finished the bf16 weight tile
+  uint64_t empty[kStages];     // MMAs that read the stage completed
   uint64_t accum_full;
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
 
-// Tile row -> weight row. For SwiGLU the first 64 tile rows are gate rows and the last
-// 64 the matching up rows, so that one thread of the epilogue owns both values.
-__device__ __forceinline__ int weight_row(const GemmParams& p, int n0, int r) {
+// First weight row of each 64-row half of the tile. For SwiGLU the first half holds gate
+// rows and the second the matching up rows, so one epilogue thread owns both values.
+__device__ __forceinline__ void tile_rows(const GemmParams& p, int n0, int& r0, int& r1) {
   if (p.epi == EPI_SWIGLU) {
-    const int half_n = p.N >> 1;
-    const int j = (n0 >> 1) + (r & 63);
-    if (j >= half_n) return -1;
-    return r < 64 ? j : half_n + j;
+    r0 = n0 >> 1;
+    r1 = (p.N >> 1) + (n0 >> 1);
+  } else {
+    r0 = n0;
+    r1 = n0 + 64;
   }
-  const int n = n0 + r;
-  return n < p.N ? n : -1;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -73,18 +75,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
+gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                 const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int num_kb = p.K / BK;
+  const bool fp8 = p.wfmt == WFMT_FP8_BLOCK128;
+  int wr0, wr1;
+  tile_rows(p, n0, wr0, wr1);
+  // Rows of the second half that do not exist (N edge) must read as zero: TMA fills
+  // out-of-range rows with zeros, but a SwiGLU "up" half always starts inside the matrix,
+  // so its tail rows are masked in the epilogue instead.
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&sm.full_a[s], 1);
-      mbar_init(&sm.full_b[s], 128);
+      mbar_init(&sm.full_in[s], 1);
+      mbar_init(&sm.full_b[s], kDecodeWarps * 32);
       mbar_init(&sm.empty[s], 1);
     }
     mbar_init(&sm.accum_full, 1);
@@ -101,15 +110,24 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p)
   const uint32_t tmem_acc = sm.tmem_base;
 
   if (warp == 0) {
-    // ---------------- TMA producer for A ----------------
+    // ---------------- TMA producer ----------------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_w);
+      const uint32_t tx = kTileBytes + (fp8 ? kRawBytes : kTileBytes);
       int issued = 0;
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % kStages;
         if (!mbar_wait(&sm.empty[s], ((kb / kStages) & 1) ^ 1, &sm.abort_flag, p.status, 11)) break;
-        mbar_arrive_expect_tx(&sm.full_a[s], kTileBytes);
-        tma_load_2d(sm.a[s], &tmap_a, &sm.full_a[s], kb * BK, m0);
+        mbar_arrive_expect_tx(&sm.full_in[s], tx);
+        tma_load_2d(sm.a[s], &tmap_a, &sm.full_in[s], kb * BK, m0);
+        if (fp8) {
+          tma_load_2d(sm.raw[s], &tmap_w, &sm.full_in[s], kb * BK, wr0);
+          tma_load_2d(sm.raw[s] + kRawBytes / 2, &tmap_w, &sm.full_in[s], kb * BK, wr1);
+        } else {
+          tma_load_2d(sm.b[s], &tmap_w, &sm.full_in[s], kb * BK, wr0);
+          tma_load_2d(sm.b[s] + kTileBytes / 2, &tmap_w, &sm.full_in[s], kb * BK, wr1);
+        }
         issued = kb + 1;
       }
       if (sm.abort_flag) {
@@ -117,7 +135,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p)
         for (int kb = max(0, issued - kStages); kb < issued; ++kb) {
           const int s = kb % kStages;
           for (uint32_t i = 0; i < (1u << 20); ++i)
-            if (mbar_try_wait(&sm.full_a[s], (kb / kStages) & 1)) break;
+            if (mbar_try_wait(&sm.full_in[s], (kb / kStages) & 1)) break;
         }
       }
     }
@@ -128,8 +146,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p)
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % kStages;
         const uint32_t ph = (kb / kStages) & 1;
-        mbar_wait(&sm.full_a[s], ph, &sm.abort_flag, p.status, 12);
-        mbar_wait(&sm.full_b[s], ph, &sm.abort_flag, p.status, 13);
+        mbar_wait(&sm.full_in[s], ph, &sm.abort_flag, p.status, 12);
+        if (fp8) mbar_wait(&sm.full_b[s], ph, &sm.abort_flag, p.status, 13);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
 #pragma unroll
@@ -143,106 +161,80 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p)
       umma_commit(&sm.accum_full);
     }
   } else {
-    // ---------------- weight decode producers, then epilogue ----------------
-    const int t = threadIdx.x - 64;        // 0..127
-    const int chunk = t & 3;               // which 16 K-elements of the 64-wide tile row
-    const int rbase = t >> 2;              // row within a group of 32
-    const int kb_scale = (p.K + 127) >> 7;
-    int wrow[4];
+    // ---------------- weight decode, then epilogue ----------------
+    const int t = threadIdx.x - 64;        // 0..255
+    if (fp8) {
+      const int r = t >> 1;                // tile row 0..127
+      const int hf = t & 1;                // which 32 of the row's 64 K-elements
+      const int grow = (r < 64 ? wr0 + r : wr1 + (r - 64));
+      const bool row_valid = p.epi == EPI_SWIGLU ? ((n0 >> 1) + (r & 63)) < (p.N >> 1) : grow < p.N;
+      const int kb_scale = (p.K + 127) >> 7;
+      const float* srow = p.scale + (size_t)((row_valid ? grow : 0) >> 7) * kb_scale;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages;
+        const float sc = row_valid ? __ldg(srow + ((kb * BK) >> 7)) : 0.f;
+        mbar_wait(&sm.full_in[s], (kb / kStages) & 1, &sm.abort_flag, p.status, 14);
+        const uint4 q0 = *reinterpret_cast<const uint4*>(sm.raw[s] + r * BK + hf * 32);
+        const uint4 q1 = *reinterpret_cast<const uint4*>(sm.raw[s] + r * BK + hf * 32 + 16);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        uint32_t o[16];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) wrow[i] = weight_row(p, n0, rbase + 32 * i);
-
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % kStages;
-      const int k0 = kb * BK + chunk * 16;
-      // Issue the global loads before waiting for the slot.
-      uint4 raw[4][2];
-      float sc[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        raw[i][0] = make_uint4(0, 0, 0, 0);
-        raw[i][1] = raw[i][0];
-        sc[i] = 0.f;
-        if (wrow[i] >= 0) {
-          if (p.wfmt == WFMT_FP8_BLOCK128) {
-            raw[i][0] = ld_stream_u4((const uint8_t*)p.W + (size_t)wrow[i] * p.K + k0);
-            sc[i] = __ldg(p.scale + (size_t)(wrow[i] >> 7) * kb_scale + (k0 >> 7));
-          } else {
-            const bf16* src = (const bf16*)p.W + (size_t)wrow[i] * p.K + k0;
-            raw[i][0] = ld_stream_u4(src);
-            raw[i][1] = ld_stream_u4(src + 8);
-          }
-        }
-      }
-      mbar_wait(&sm.empty[s], ((kb / kStages) & 1) ^ 1, &sm.abort_flag, p.status, 14);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = rbase + 32 * i;
-        uint4 lo, hi;
-        if (p.wfmt == WFMT_FP8_BLOCK128) {
-          const uint32_t w[4] = {raw[i][0].x, raw[i][0].y, raw[i][0].z, raw[i][0].w};
-          uint32_t o[8];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 a = e4m3x2_to_float2((uint16_t)(w[j] & 0xffffu));
-            const float2 b = e4m3x2_to_float2((uint16_t)(w[j] >> 16));
-            o[2 * j] = pack_bf16(a.x * sc[i], a.y * sc[i]);
-            o[2 * j + 1] = pack_bf16(b.x * sc[i], b.y * sc[i]);
-          }
-          lo = make_uint4(o[0], o[1], o[2], o[3]);
-          hi = make_uint4(o[4], o[5], o[6], o[7]);
-        } else {
-          lo = raw[i][0];
-          hi = raw[i][1];
+        for (int j = 0; j < 8; ++j) {
+          const float2 a = e4m3x2_to_float2((uint16_t)(w[j] & 0xffffu));
+          const float2 b = e4m3x2_to_float2((uint16_t)(w[j] >> 16));
+          o[2 * j] = pack_bf16(a.x * sc, a.y * sc);
+          o[2 * j + 1] = pack_bf16(b.x * sc, b.y * sc);
         }
         uint8_t* rowp = sm.b[s] + (r >> 3) * 1024 + (r & 7) * 128;
-        *reinterpret_cast<uint4*>(rowp + (((2 * chunk) ^ (r & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(rowp + (((2 * chunk + 1) ^ (r & 7)) << 4)) = hi;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int chunk = hf * 4 + c;    // 16-byte chunk of the 128-byte row
+          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&sm.full_b[s]);
       }
-      fence_proxy_async_smem();
-      mbar_arrive(&sm.full_b[s]);
     }
 
     // ---------------- epilogue ----------------
     mbar_wait(&sm.accum_full, 0, &sm.abort_flag, p.status, 15);
     tc_fence_after();
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int ch = (warp - 2) >> 2;         // which half of the columns
     const int m = m0 + q * 32 + lane;
     const uint32_t lane_addr = tmem_acc + ((uint32_t)(q * 32) << 16);
     const bool row_ok = m < p.M && !sm.abort_flag;
     if (p.epi == EPI_SWIGLU) {
       const int half_n = p.N >> 1;
-      const int j0 = n0 >> 1;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t g[32], u[32];
-        tmem_ld_32x32(lane_addr + c * 32, g);
-        tmem_ld_32x32(lane_addr + 64 + c * 32, u);
-        tmem_ld_wait();
-        if (row_ok) {
-          bf16* dst = p.C + (size_t)m * p.ldc + j0 + c * 32;
-          if (j0 + c * 32 + 32 <= half_n) {
+      const int j0 = (n0 >> 1) + ch * 32;
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(lane_addr + ch * 32, g);
+      tmem_ld_32x32(lane_addr + 64 + ch * 32, u);
+      tmem_ld_wait();
+      if (row_ok) {
+        bf16* dst = p.C + (size_t)m * p.ldc + j0;
+        if (j0 + 32 <= half_n) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t o[4];
+          for (int v = 0; v < 4; ++v) {
+            uint32_t o[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int i = v * 8 + e * 2;
-                o[e] = pack_bf16(silu(__uint_as_float(g[i])) * __uint_as_float(u[i]),
-                                 silu(__uint_as_float(g[i + 1])) * __uint_as_float(u[i + 1]));
-              }
-              *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int e = 0; e < 4; ++e) {
+              const int i = v * 8 + e * 2;
+              o[e] = pack_bf16(silu(__uint_as_float(g[i])) * __uint_as_float(u[i]),
+                               silu(__uint_as_float(g[i + 1])) * __uint_as_float(u[i + 1]));
             }
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (j0 + c * 32 + i < half_n)
-                dst[i] = __float2bfloat16(silu(__uint_as_float(g[i])) * __uint_as_float(u[i]));
+            *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
           }
+        } else {
+          for (int i = 0; i < 32; ++i)
+            if (j0 + i < half_n) dst[i] = __float2bfloat16(silu(__uint_as_float(g[i])) * __uint_as_float(u[i]));
         }
       }
     } else {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = ch * 2 + cc;
         uint32_t r[32];
         tmem_ld_32x32(lane_addr + c * 32, r);
         tmem_ld_wait();
@@ -308,36 +300,47 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+bool encode_2d(EncodeTiledFn encode, CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* base,
+               uint64_t inner, uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+               CUtensorMapSwizzle swz) {
+  const cuuint64_t gdim[2] = {inner, outer};
+  const cuuint64_t gstride[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  (void)elem;
+  return encode(map, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 // A: [M, K] bf16 row-major with row stride lda elements (lda*2 bytes a multiple of 16, base
-// 16-byte aligned). K must be a multiple of 64. For epi == 1 (SwiGLU) W holds N/2 gate rows
-// followed by N/2 up rows and C has N/2 columns.
+// 16-byte aligned). W: [N, K] row-major, 16-byte aligned base. K must be a multiple of 64.
+// For epi == 1 (SwiGLU) W holds N/2 gate rows followed by N/2 up rows and C has N/2 columns.
 PK_API int pk_gemm_umma(const void* A, int lda, const void* W, const float* scale, int wfmt, int M, int N,
                         int K, int epi, void* C, const void* resid, int ldc, uint32_t* status,
                         cudaStream_t stream) {
   if (M < 1 || N < 1 || K < BK || (K % BK) != 0) return PK_ERR_BAD_ARG;
-  if (((uintptr_t)A & 15) != 0 || ((size_t)lda * 2) % 16 != 0) return PK_ERR_BAD_ARG;
+  if (((uintptr_t)A & 15) != 0 || ((size_t)lda * 2) % 16 != 0 || ((uintptr_t)W & 15) != 0) return PK_ERR_BAD_ARG;
   if (wfmt != WFMT_FP8_BLOCK128 && wfmt != WFMT_BF16) return PK_ERR_UNSUPPORTED;
-  if (wfmt == WFMT_FP8_BLOCK128 && (scale == nullptr || ((uintptr_t)W & 15) != 0)) return PK_ERR_BAD_ARG;
+  if (wfmt == WFMT_FP8_BLOCK128 && scale == nullptr) return PK_ERR_BAD_ARG;
   if (epi == EPI_SWIGLU && ((N & 1) != 0)) return PK_ERR_BAD_ARG;
   if ((ldc & 7) != 0 && epi != EPI_F32) return PK_ERR_BAD_ARG;
   EncodeTiledFn encode = get_encode_fn();
   if (encode == nullptr) return PK_ERR_UNSUPPORTED;
 
-  CUtensorMap tmap;
-  const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
-  const cuuint64_t gstride[1] = {(cuuint64_t)lda * 2};
-  const cuuint32_t box[2] = {BK, BM};
-  const cuuint32_t estr[2] = {1, 1};
-  if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(A), gdim, gstride, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+  CUtensorMap tmap_a, tmap_w;
+  if (!encode_2d(encode, &tmap_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2,
+                 BK, BM, CU_TENSOR_MAP_SWIZZLE_128B))
     return PK_ERR_CUDA;
-  }
+  const bool ok_w = wfmt == WFMT_FP8_BLOCK128
+                        ? encode_2d(encode, &tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, (uint64_t)K, (uint64_t)N,
+                                    (uint64_t)K, BK, 64, CU_TENSOR_MAP_SWIZZLE_NONE)
+                        : encode_2d(encode, &tmap_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, (uint64_t)K, (uint64_t)N,
+                                    (uint64_t)K * 2, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok_w) return PK_ERR_CUDA;
 
   GemmParams p{};
-  p.W = W;
   p.scale = scale;
   p.wfmt = wfmt;
   p.M = M;
@@ -360,7 +363,7 @@ PK_API int pk_gemm_umma(const void* A, int lda, const void* W, const float* scal
     configured = true;
   }
   const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_umma_kernel<<<grid, kThreads, smem, stream>>>(tmap, p);
+  gemm_umma_kernel<<<grid, kThreads, smem, stream>>>(tmap_a, tmap_w, p);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }

@@ -96,8 +96,47 @@ __device__ __forceinline__ void fma16_bf16(const uint4& w0, const uint4& w1, con
   }
 }
 
+// A batch of four k-iterations for a row pair: eight 16-byte loads in flight per lane.
+struct Fp8Batch {
+  uint4 a[4], b[4];
+  float sa[4], sb[4];
+};
+
+__device__ __forceinline__ void load_fp8_batch(Fp8Batch& bt, const uint8_t* w0p, const uint8_t* w1p,
+                                               const float* s0p, const float* s1p, int it0, int klen, int lane) {
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int ka = ((it0 + u) << 9) + (lane << 4);
+    const bool ok = ka < klen;
+    bt.a[u] = ok ? ld_stream_u4(w0p + ka) : make_uint4(0, 0, 0, 0);
+    bt.b[u] = ok ? ld_stream_u4(w1p + ka) : make_uint4(0, 0, 0, 0);
+    bt.sa[u] = ok ? __ldg(s0p + (ka >> 7)) : 0.f;
+    bt.sb[u] = ok ? __ldg(s1p + (ka >> 7)) : 0.f;
+  }
+}
+
 template <int M>
-__global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) {
+__device__ __forceinline__ void consume_fp8_batch(const Fp8Batch& bt, const float* xs, int kc, int it0, int iters,
+                                                  int lane, float (&acc0)[M], float (&acc1)[M]) {
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    // The staged chunk ends at iteration `iters`; nothing beyond it may be read.
+    if (it0 + u >= iters) break;
+    float pa[M], pb[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) { pa[m] = 0.f; pb[m] = 0.f; }
+    fma16_fp8<M>(bt.a[u], xs, ((it0 + u) << 9) + (lane << 2), kc, pa);
+    fma16_fp8<M>(bt.b[u], xs, ((it0 + u) << 9) + (lane << 2), kc, pb);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      acc0[m] = fmaf(pa[m], bt.sa[u], acc0[m]);
+      acc1[m] = fmaf(pb[m], bt.sb[u], acc1[m]);
+    }
+  }
+}
+
+template <int M>
+__global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams p) {
   extern __shared__ __align__(16) float xs[];  // [M][kc] staged activations (permuted)
   __shared__ float red[40];
   __shared__ float rstd[8];
@@ -114,12 +153,29 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) 
   const int warps_total = gridDim.x * kWarps;
   const int gwarp = blockIdx.x * kWarps + warp;
 
+  const int kb_count = (K + 127) >> 7;
+  // Weights do not depend on the activations: issue the first batch of this warp's first
+  // row pair before the prologue so that the HBM latency overlaps the norm.
+  Fp8Batch bt;
+  bool have_pre = false;
+  {
+    const int g0 = gwarp;
+    const int r0 = swiglu ? g0 : 2 * g0;
+    if (g0 < n_groups && r0 < p.N) {
+      const int r1c = swiglu ? g0 + half_n : (2 * g0 + 1 < p.N ? 2 * g0 + 1 : r0);
+      load_fp8_batch(bt, p.W + (size_t)r0 * K, p.W + (size_t)r1c * K, p.scale + (size_t)(r0 >> 7) * kb_count,
+                     p.scale + (size_t)(r1c >> 7) * kb_count, 0, min(kc, K), lane);
+      have_pre = true;
+    }
+  }
+
   // ---- wait for the producers of `parts`, then the per-row statistics ----
   if (p.parts != nullptr && p.wait.flag != nullptr) {
     if (tid == 0) wait_all_ranks(p.wait);
     __syncthreads();
   }
-  if (p.gamma != nullptr) {
+  const bool single_chunk = K <= kc;
+  if (p.gamma != nullptr && !single_chunk) {
     for (int m = 0; m < M; ++m) {
       float ss = 0.f;
       for (int k = tid; k < K; k += kThreads) {
@@ -141,31 +197,117 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) 
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
 
-  const int kb_count = (K + 127) >> 7;
-
   for (int k0 = 0; k0 < K; k0 += kc) {
     const int klen = min(kc, K - k0);
     // ---- stage the chunk ----
     if (k0 > 0) __syncthreads();
-    for (int m = 0; m < M; ++m) {
-      for (int k = tid; k < kc; k += kThreads) {
-        float v = 0.f;
-        if (k < klen) {
-          const size_t gi = (size_t)m * K + k0 + k;
-          v = p.x_in ? __bfloat162float(p.x_in[gi]) : 0.f;
-          for (int r = 0; r < p.nparts; ++r) v += p.parts[((size_t)r * M + m) * K + k0 + k];
-          const bf16 hv = __float2bfloat16(v);
-          if (p.hidden_out != nullptr && blockIdx.x == 0) p.hidden_out[gi] = hv;
-          if (p.parts != nullptr) v = __bfloat162float(hv);
-          if (p.gamma != nullptr) {
-            const float g = p.gamma[k0 + k];
-            v = v * rstd[m] * (p.norm_mode == 1 ? 1.f + g : g);
-            // Activations are bf16 everywhere else; round here too so that the fused
-            // and unfused paths see the same operand.
-            v = __bfloat162float(__float2bfloat16(v));
+    if (single_chunk) {
+      // One pass over global memory: stage the raw rows and their sums of squares, then
+      // normalise in shared memory.
+      for (int m = 0; m < M; ++m) {
+        float ss = 0.f;
+        // Zero the padding of the last 512-element run (read by lanes past K, times zero weights).
+        for (int k = K + tid; k < kc; k += kThreads) xs[m * kc + staged_index(k)] = 0.f;
+        // Eight elements per thread and step, four steps in flight, so that the loads of
+        // the whole row overlap instead of forming one latency chain per element.
+        const int nchunks = K >> 3;
+        for (int c0 = tid; c0 < nchunks; c0 += kThreads * 4) {
+          float v[4][8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u * kThreads;
+            uint4 xv = make_uint4(0, 0, 0, 0);
+            if (c < nchunks && p.x_in) xv = __ldg(reinterpret_cast<const uint4*>(p.x_in + (size_t)m * K + c * 8));
+            const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              v[u][2 * j] = __uint_as_float(w[j] << 16);
+              v[u][2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            }
+          }
+          for (int r = 0; r < p.nparts; ++r) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int c = c0 + u * kThreads;
+              if (c < nchunks) {
+                const float4* pp = reinterpret_cast<const float4*>(p.parts + ((size_t)r * M + m) * K + c * 8);
+                const float4 a = pp[0], b = pp[1];
+                v[u][0] += a.x; v[u][1] += a.y; v[u][2] += a.z; v[u][3] += a.w;
+                v[u][4] += b.x; v[u][5] += b.y; v[u][6] += b.z; v[u][7] += b.w;
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u * kThreads;
+            if (c >= nchunks) continue;
+            uint32_t packed[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[u][2 * j], v[u][2 * j + 1]);
+              packed[j] = *reinterpret_cast<const uint32_t*>(&h2);
+              if (p.parts != nullptr) {
+                v[u][2 * j] = __uint_as_float(packed[j] << 16);
+                v[u][2 * j + 1] = __uint_as_float(packed[j] & 0xffff0000u);
+              }
+            }
+            if (p.hidden_out != nullptr && blockIdx.x == 0)
+              *reinterpret_cast<uint4*>(p.hidden_out + (size_t)m * K + c * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            // elements 8c..8c+7 live in two float4 of the permuted layout
+            const int si = m * kc + staged_index(c * 8);
+            *reinterpret_cast<float4*>(xs + si) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+            *reinterpret_cast<float4*>(xs + si + 128) = make_float4(v[u][4], v[u][5], v[u][6], v[u][7]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += v[u][j] * v[u][j];
           }
         }
-        xs[m * kc + staged_index(k)] = v;
+        if (p.gamma != nullptr) {
+          ss = block_sum(ss, red);
+          const float rs = rsqrtf(ss / (float)K + p.eps);
+          const float one = p.norm_mode == 1 ? 1.f : 0.f;
+          const int nq = K >> 2;
+          for (int c0 = tid; c0 < nq; c0 += kThreads * 4) {
+            float4 gv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int c = c0 + u * kThreads;
+              gv[u] = c < nq ? __ldg(reinterpret_cast<const float4*>(p.gamma) + c) : make_float4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int c = c0 + u * kThreads;
+              if (c >= nq) continue;
+              float4* xp = reinterpret_cast<float4*>(xs + m * kc + staged_index(c * 4));
+              float4 xv = *xp;
+              // Activations are bf16 everywhere else; round here too so that the fused and
+              // unfused paths see the same operand.
+              xv.x = __bfloat162float(__float2bfloat16(xv.x * rs * (one + gv[u].x)));
+              xv.y = __bfloat162float(__float2bfloat16(xv.y * rs * (one + gv[u].y)));
+              xv.z = __bfloat162float(__float2bfloat16(xv.z * rs * (one + gv[u].z)));
+              xv.w = __bfloat162float(__float2bfloat16(xv.w * rs * (one + gv[u].w)));
+              *xp = xv;
+            }
+          }
+        }
+      }
+    } else {
+      for (int m = 0; m < M; ++m) {
+        for (int k = tid; k < kc; k += kThreads) {
+          float v = 0.f;
+          if (k < klen) {
+            const size_t gi = (size_t)m * K + k0 + k;
+            v = p.x_in ? __bfloat162float(p.x_in[gi]) : 0.f;
+            for (int r = 0; r < p.nparts; ++r) v += p.parts[((size_t)r * M + m) * K + k0 + k];
+            const bf16 hv = __float2bfloat16(v);
+            if (p.hidden_out != nullptr && blockIdx.x == 0) p.hidden_out[gi] = hv;
+            if (p.parts != nullptr) v = __bfloat162float(hv);
+            if (p.gamma != nullptr) {
+              const float g = p.gamma[k0 + k];
+              v = __bfloat162float(__float2bfloat16(v * rstd[m] * (p.norm_mode == 1 ? 1.f + g : g)));
+            }
+          }
+          xs[m * kc + staged_index(k)] = v;
+        }
       }
     }
     __syncthreads();
@@ -182,32 +324,18 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) 
       }
       const int iters = (klen + 511) >> 9;
       if (row[0] < p.N) {
-        // Both rows are FP8 (N is even). One 16-byte load per row and iteration, two
-        // iterations unrolled: four loads in flight per lane.
+        // Both rows are FP8 (N is even).
         const bool has1 = row[1] < p.N;
         const uint8_t* w0p = p.W + (size_t)row[0] * K + k0;
         const uint8_t* w1p = p.W + (size_t)(has1 ? row[1] : row[0]) * K + k0;
         const float* s0p = p.scale + (size_t)(row[0] >> 7) * kb_count + (k0 >> 7);
         const float* s1p = p.scale + (size_t)((has1 ? row[1] : row[0]) >> 7) * kb_count + (k0 >> 7);
-#pragma unroll 2
-        for (int it = 0; it < iters; ++it) {
-          const int ka = (it << 9) + (lane << 4);
-          if (ka < klen) {
-            const uint4 wa = ld_stream_u4(w0p + ka);
-            const uint4 wb = ld_stream_u4(w1p + ka);
-            const float sa = __ldg(s0p + (ka >> 7));
-            const float sb = __ldg(s1p + (ka >> 7));
-            float pa[M], pb[M];
-#pragma unroll
-            for (int m = 0; m < M; ++m) { pa[m] = 0.f; pb[m] = 0.f; }
-            fma16_fp8<M>(wa, xs, (it << 9) + (lane << 2), kc, pa);
-            fma16_fp8<M>(wb, xs, (it << 9) + (lane << 2), kc, pb);
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-              acc[0][m] = fmaf(pa[m], sa, acc[0][m]);
-              acc[1][m] = fmaf(pb[m], sb, acc[1][m]);
-            }
-          }
+        bool loaded = have_pre && k0 == 0 && g == gwarp;
+#pragma unroll 1
+        for (int it0 = 0; it0 < iters; it0 += 4) {
+          if (!loaded) load_fp8_batch(bt, w0p, w1p, s0p, s1p, it0, klen, lane);
+          loaded = false;
+          consume_fp8_batch<M>(bt, xs, kc, it0, iters, lane, acc[0], acc[1]);
         }
       } else {
         const bool has1 = row[1] < total_rows;
@@ -331,7 +459,7 @@ PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, i
   if (chunked) {
     blocks = (groups + kWarps - 1) / kWarps;  // exactly one group per warp
   } else {
-    const int per_sm = 3;
+    const int per_sm = 2;
     blocks = (groups + kWarps - 1) / kWarps;
     const int cap = (sm_count > 0 ? sm_count : 148) * per_sm;
     if (blocks > cap) blocks = cap;

@@ -14,7 +14,7 @@ import torch
 from . import lib as _lib
 
 __all__ = [
-    "matvec", "gemm_umma", "deltanet_seq", "qk_norm_rope_append", "gqa_decode", "rmsnorm",
+    "matvec", "gemm_umma", "deltanet_seq", "deltanet_chunked", "qk_norm_rope_append", "gqa_decode", "rmsnorm",
     "embedding", "argmax", "silu_mul", "KernelError",
 ]
 
@@ -93,6 +93,22 @@ def deltanet_seq(proj: torch.Tensor, key_heads: int, value_heads: int, conv_w: t
         _ptr(proj), c_int(ld), c_int(T), c_int(key_heads), c_int(value_heads), c_int(128), c_int(128), _ptr(conv_w),
         _ptr(conv_state), _ptr(A_log), _ptr(dt_bias), _ptr(norm_w), c_float(eps), _ptr(state), _ptr(out), _stream())
     _check(st, "pk_deltanet_seq")
+    return out
+
+
+def deltanet_chunked(proj: torch.Tensor, key_heads: int, value_heads: int, conv_w: torch.Tensor, conv_state: torch.Tensor,
+                     A_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, eps: float, state: torch.Tensor) -> torch.Tensor:
+    """Chunk-parallel (chunk 64) form of `deltanet_seq`: same inputs, outputs and state updates."""
+    T, ld = proj.shape
+    K = _lib.kernels()
+    K.pk_deltanet_chunk_workspace.restype = c_size_t
+    nws = K.pk_deltanet_chunk_workspace(c_int(T), c_int(key_heads), c_int(value_heads))
+    ws = torch.empty(nws, device=proj.device, dtype=torch.float32)
+    out = torch.empty(T, value_heads * 128, device=proj.device, dtype=torch.bfloat16)
+    st = K.pk_deltanet_chunked(
+        _ptr(proj), c_int(ld), c_int(T), c_int(key_heads), c_int(value_heads), c_int(128), c_int(128), _ptr(conv_w),
+        _ptr(conv_state), _ptr(A_log), _ptr(dt_bias), _ptr(norm_w), c_float(eps), _ptr(state), _ptr(out), _ptr(ws), _stream())
+    _check(st, "pk_deltanet_chunked")
     return out
 
 

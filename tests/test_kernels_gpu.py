@@ -183,6 +183,30 @@ def test_deltanet_seq(Hk, Hv, T):
     assert torch.allclose(cs2, ref_tail, atol=1e-6)
 
 
+@pytest.mark.parametrize("Hk,Hv,T", [(2, 4, 64), (1, 2, 100), (2, 2, 33), (1, 1, 200)])
+def test_deltanet_chunked_matches_serial_recurrence(Hk, Hv, T):
+    from pocketllm_b200 import ops
+    torch.manual_seed(Hv * 100 + T)
+    KD, VD = Hk * 128, Hv * 128
+    ld = (2 * KD + 2 * VD + 2 * Hv + 7) // 8 * 8
+    proj = (torch.randn(T, ld, device="cuda")).to(torch.bfloat16)
+    conv_w = torch.randn(2 * KD + VD, 4, device="cuda") * 0.3
+    conv_state = torch.randn(2 * KD + VD, 3, device="cuda")
+    A_log, dt_bias = torch.randn(Hv, device="cuda") * 0.5, torch.randn(Hv, device="cuda") * 0.5
+    norm_w = 1 + torch.randn(128, device="cuda") * 0.05
+    S = torch.randn(Hv, 128, 128, device="cuda") * 0.1
+    ref_o, ref_S, ref_tail = _deltanet_ref(proj, Hk, Hv, conv_w, conv_state, A_log, dt_bias, norm_w, 1e-6, S)
+    S2, cs2 = S.clone(), conv_state.clone()
+    out = ops.deltanet_chunked(proj, Hk, Hv, conv_w, cs2, A_log, dt_bias, norm_w, 1e-6, S2)
+    assert _rel_err(out, ref_o) < 1e-2
+    assert _rel_err(S2, ref_S) < 2e-3
+    assert torch.allclose(cs2, ref_tail, atol=1e-6)
+    # and against the serial kernel, continuing from the produced state
+    S3, cs3 = S.clone(), conv_state.clone()
+    out3 = ops.deltanet_seq(proj, Hk, Hv, conv_w, cs3, A_log, dt_bias, norm_w, 1e-6, S3)
+    assert _rel_err(out, out3) < 1e-2 and _rel_err(S2, S3) < 2e-3
+
+
 @pytest.mark.parametrize("M,ctx,Hq,Hkv,nsplit", [(1, 1, 4, 2, 4), (1, 700, 10, 2, 8), (5, 300, 5, 1, 3), (8, 64, 8, 8, 2)])
 def test_gqa_append_and_decode(M, ctx, Hq, Hkv, nsplit):
     from pocketllm_b200 import ops
