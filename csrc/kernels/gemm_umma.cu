@@ -3,7 +3,8 @@
 //   A    bf16 activations, moved by TMA (2-D tiled, 128-byte swizzle, no multicast) into a
 //        5-stage shared-memory ring.
 //   W    quantised weights that are NEVER expanded in HBM. The raw FP8 E4M3 tile (128 rows x
-//        64 bytes) rides the same TMA ring; eight decode warps turn it into the bf16 K-major
+//        64 bytes) rides the same TMA ring; two groups of eight decode warps (alternating
+//        stages) turn it into the bf16 K-major
 //        tile in the 128-byte swizzle the tensor core expects, applying the fp32 scale of
 //        its 128x128 block on the way. bf16 weights skip the decode: TMA writes the
 //        swizzled tile directly.
@@ -27,7 +28,9 @@ constexpr int kStages = 5;
 constexpr int kTileBytes = BM * BK * 2;   // 16 KB per bf16 operand tile
 constexpr int kRawBytes = BN * BK;        // 8 KB of raw FP8 per stage
 constexpr int kDecodeWarps = 8;
-constexpr int kThreads = 64 + kDecodeWarps * 32;  // warp0 TMA, warp1 MMA, warps 2-9 decode + epilogue
+constexpr int kDecodeGroups = 2;          // groups alternate ring stages so that decode latency overlaps
+constexpr int kThreads = 64 + kDecodeGroups * kDecodeWarps * 32;  // warp0 TMA, warp1 MMA, then decode (+ epilogue) warps
+constexpr int kMaxScaleKb = 512;          // K <= 65536 for the shared-memory scale table
 constexpr uint32_t kTmemCols = 128;
 
 enum { WFMT_FP8_BLOCK128 = 0, WFMT_BF16 = 1 };
@@ -55,6 +58,7 @@ struct __align__(1024) SmemLayout {
   uint64_t accum_full;
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
+  float scale_tab[2][kMaxScaleKb];  // block scales of the tile's two 64-row halves along K
 };
 
 // First weight row of each 64-row half of the tile. For SwiGLU the first half holds gate
@@ -81,7 +85,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  // m-tiles vary fastest so that the CTAs sharing a weight tile run together and the
+  // weights cross HBM once.
+  const int n0 = blockIdx.y * BN, m0 = blockIdx.x * BM;
   const int num_kb = p.K / BK;
   const bool fp8 = p.wfmt == WFMT_FP8_BLOCK128;
   int wr0, wr1;
@@ -99,6 +105,15 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     mbar_init(&sm.accum_full, 1);
     sm.abort_flag = 0;
     mbar_fence_init();
+  }
+  if (fp8) {
+    // Block scales of this tile along K, one row of the table per 64-row half.
+    const int kb_scale = (p.K + 127) >> 7;
+    for (int i = threadIdx.x; i < 2 * kb_scale; i += kThreads) {
+      const int hfi = i / kb_scale, kk = i % kb_scale;
+      const int row = min(hfi == 0 ? wr0 : wr1, p.N - 1);
+      sm.scale_tab[hfi][kk] = __ldg(p.scale + (size_t)(row >> 7) * kb_scale + kk);
+    }
   }
   if (warp == 1) {
     tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -162,17 +177,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // ---------------- weight decode, then epilogue ----------------
-    const int t = threadIdx.x - 64;        // 0..255
+    const int grp = (warp - 2) / kDecodeWarps;             // decode group of this warp
+    const int t = (threadIdx.x - 64) % (kDecodeWarps * 32);  // 0..255 within the group
     if (fp8) {
       const int r = t >> 1;                // tile row 0..127
       const int hf = t & 1;                // which 32 of the row's 64 K-elements
       const int grow = (r < 64 ? wr0 + r : wr1 + (r - 64));
       const bool row_valid = p.epi == EPI_SWIGLU ? ((n0 >> 1) + (r & 63)) < (p.N >> 1) : grow < p.N;
-      const int kb_scale = (p.K + 127) >> 7;
-      const float* srow = p.scale + (size_t)((row_valid ? grow : 0) >> 7) * kb_scale;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      const float* stab = sm.scale_tab[r >> 6];
+      for (int kb = grp; kb < num_kb; kb += kDecodeGroups) {
         const int s = kb % kStages;
-        const float sc = row_valid ? __ldg(srow + ((kb * BK) >> 7)) : 0.f;
+        const float sc = row_valid ? stab[(kb * BK) >> 7] : 0.f;
         mbar_wait(&sm.full_in[s], (kb / kStages) & 1, &sm.abort_flag, p.status, 14);
         const uint4 q0 = *reinterpret_cast<const uint4*>(sm.raw[s] + r * BK + hf * 32);
         const uint4 q1 = *reinterpret_cast<const uint4*>(sm.raw[s] + r * BK + hf * 32 + 16);
@@ -196,6 +211,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         mbar_arrive(&sm.full_b[s]);
       }
     }
+    if (grp != 0) goto done;  // the first group also runs the epilogue
 
     // ---------------- epilogue ----------------
     mbar_wait(&sm.accum_full, 0, &sm.abort_flag, p.status, 15);
@@ -276,6 +292,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_before();
   }
 
+done:
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -362,7 +379,8 @@ PK_API int pk_gemm_umma(const void* A, int lda, const void* W, const float* scal
     }
     configured = true;
   }
-  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  const dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
+  if (grid.y > 65535 || (K + 127) / 128 > kMaxScaleKb) return PK_ERR_UNSUPPORTED;
   gemm_umma_kernel<<<grid, kThreads, smem, stream>>>(tmap_a, tmap_w, p);
   PK_CHECK_LAUNCH();
   return PK_OK;

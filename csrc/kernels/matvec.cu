@@ -12,6 +12,12 @@
 //   epilogue  store bf16 / fp32, SiLU(gate) * up, or push the fp32 partial rows into every
 //             peer's slot buffer and publish a flag (the scatter side of the all-reduce).
 //
+// Arithmetic: the activations are staged in shared memory as fp16 scaled by a power of two
+// so that |x| <= 1; FP8 codes unpack to fp16 pairs with one instruction, products are
+// accumulated four at a time with packed fp16 FMAs (|sum| <= 4 * 448) and then folded into
+// fp32 with the block scale. This keeps the instruction count per weight byte low enough
+// for the loads, not the ALUs, to set the pace.
+//
 // Behavioural counterpart in the reference: cpp_engine/cuda/qwen_half_ops.cu:89-374
 // (fp8_matvec_f16*, fp8_matmul_f16_small_batch, fp8_swiglu_*), which are separate SIMT
 // kernels with an LUT decode and NCCL all-reduces between them.
@@ -24,7 +30,7 @@ using namespace pk;
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kSmemFloats = 18 * 1024;  // 72 KB of staged activations per block
+constexpr int kSmemBytes = 108 * 1024;  // staged fp16 activations + one fp32 scratch row
 
 struct MatvecParams {
   const uint8_t* W;      // [N, K] e4m3
@@ -47,53 +53,50 @@ struct MatvecParams {
   float* y_f32;
   int ldy;               // row stride of y (elements)
   PkPush push;
+  int kc;                // staged chunk length (multiple of 512)
+  int single_chunk;
 };
 
-// Position of element k of a row inside the staged chunk. Within each run of 512
-// elements the four float4 of a lane's 16 values are spread 128 floats apart so that a
-// warp's LDS.128 touches 32 consecutive float4 (no bank conflicts).
+// Position (in halves) of element k inside a staged row. Within each run of 512 elements the
+// two 16-byte pieces of a lane's 16 values sit 256 halves apart, so a warp's LDS.128 touches
+// 32 consecutive 16-byte words (no bank conflicts).
 __device__ __forceinline__ int staged_index(int k) {
   const int blk = k >> 9, r = k & 511;
-  return (blk << 9) + (((r >> 2) & 3) << 7) + ((r >> 4) << 2) + (r & 3);
+  return (blk << 9) + (((r >> 3) & 1) << 8) + ((r >> 4) << 3) + (r & 7);
 }
 
-template <int M>
-__device__ __forceinline__ void fma16_fp8(const uint4& w, const float* xs, int base, int kc_stride,
-                                          float (&part)[M]) {
-  // 16 fp8 codes -> 16 floats, times x rows.
+__device__ __forceinline__ __half2 e4m3x2_to_half2(uint32_t v16) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v16, __NV_E4M3);
+  return *reinterpret_cast<__half2*>(&h);
+}
+
+// 16 fp8 codes times 16 staged activations -> fp32 partial (unscaled).
+__device__ __forceinline__ float dot16_fp8(const uint4& w, const uint4& x0, const uint4& x1) {
   const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+  const uint32_t xx[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+  __half2 a0 = __float2half2_rn(0.f), a1 = a0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float2 a = e4m3x2_to_float2((uint16_t)(ww[j] & 0xffffu));
-    const float2 b = e4m3x2_to_float2((uint16_t)(ww[j] >> 16));
-#pragma unroll
-    for (int m = 0; m < M; ++m) {
-      const float4 xv = *reinterpret_cast<const float4*>(xs + m * kc_stride + base + (j << 7));
-      part[m] = fmaf(a.x, xv.x, part[m]);
-      part[m] = fmaf(a.y, xv.y, part[m]);
-      part[m] = fmaf(b.x, xv.z, part[m]);
-      part[m] = fmaf(b.y, xv.w, part[m]);
-    }
+    const __half2 lo = e4m3x2_to_half2(ww[j] & 0xffffu);
+    const __half2 hi = e4m3x2_to_half2(ww[j] >> 16);
+    a0 = __hfma2(lo, *reinterpret_cast<const __half2*>(&xx[2 * j]), a0);
+    a1 = __hfma2(hi, *reinterpret_cast<const __half2*>(&xx[2 * j + 1]), a1);
   }
+  const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
+  return (f0.x + f0.y) + (f1.x + f1.y);
 }
 
-template <int M>
-__device__ __forceinline__ void fma16_bf16(const uint4& w0, const uint4& w1, const float* xs, int base,
-                                           int kc_stride, float (&part)[M]) {
+__device__ __forceinline__ float dot16_bf16(const uint4& w0, const uint4& w1, const uint4& x0, const uint4& x1) {
   const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+  const uint32_t xx[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+  float acc = 0.f;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float a0 = __uint_as_float(ww[2 * j] << 16), a1 = __uint_as_float(ww[2 * j] & 0xffff0000u);
-    const float a2 = __uint_as_float(ww[2 * j + 1] << 16), a3 = __uint_as_float(ww[2 * j + 1] & 0xffff0000u);
-#pragma unroll
-    for (int m = 0; m < M; ++m) {
-      const float4 xv = *reinterpret_cast<const float4*>(xs + m * kc_stride + base + (j << 7));
-      part[m] = fmaf(a0, xv.x, part[m]);
-      part[m] = fmaf(a1, xv.y, part[m]);
-      part[m] = fmaf(a2, xv.z, part[m]);
-      part[m] = fmaf(a3, xv.w, part[m]);
-    }
+  for (int j = 0; j < 8; ++j) {
+    const float2 xv = __half22float2(*reinterpret_cast<const __half2*>(&xx[j]));
+    acc = fmaf(__uint_as_float(ww[j] << 16), xv.x, acc);
+    acc = fmaf(__uint_as_float(ww[j] & 0xffff0000u), xv.y, acc);
   }
+  return acc;
 }
 
 // A batch of four k-iterations for a row pair: eight 16-byte loads in flight per lane.
@@ -116,34 +119,120 @@ __device__ __forceinline__ void load_fp8_batch(Fp8Batch& bt, const uint8_t* w0p,
 }
 
 template <int M>
-__device__ __forceinline__ void consume_fp8_batch(const Fp8Batch& bt, const float* xs, int kc, int it0, int iters,
+__device__ __forceinline__ void consume_fp8_batch(const Fp8Batch& bt, const __half* xs, int kc, int it0, int iters,
                                                   int lane, float (&acc0)[M], float (&acc1)[M]) {
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     // The staged chunk ends at iteration `iters`; nothing beyond it may be read.
     if (it0 + u >= iters) break;
-    float pa[M], pb[M];
-#pragma unroll
-    for (int m = 0; m < M; ++m) { pa[m] = 0.f; pb[m] = 0.f; }
-    fma16_fp8<M>(bt.a[u], xs, ((it0 + u) << 9) + (lane << 2), kc, pa);
-    fma16_fp8<M>(bt.b[u], xs, ((it0 + u) << 9) + (lane << 2), kc, pb);
+    const int base = ((it0 + u) << 9) + (lane << 3);
 #pragma unroll
     for (int m = 0; m < M; ++m) {
-      acc0[m] = fmaf(pa[m], bt.sa[u], acc0[m]);
-      acc1[m] = fmaf(pb[m], bt.sb[u], acc1[m]);
+      const uint4 x0 = *reinterpret_cast<const uint4*>(xs + m * kc + base);
+      const uint4 x1 = *reinterpret_cast<const uint4*>(xs + m * kc + base + 256);
+      acc0[m] = fmaf(dot16_fp8(bt.a[u], x0, x1), bt.sa[u], acc0[m]);
+      acc1[m] = fmaf(dot16_fp8(bt.b[u], x0, x1), bt.sb[u], acc1[m]);
     }
   }
 }
 
+// Raw (pre-norm) value of eight consecutive elements of row m: x_in + sum of parts.
+__device__ __forceinline__ void load8(const MatvecParams& p, int M, int m, int k, float (&v)[8]) {
+  uint4 xv = make_uint4(0, 0, 0, 0);
+  if (p.x_in) xv = __ldg(reinterpret_cast<const uint4*>(p.x_in + (size_t)m * p.K + k));
+  const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(w[j] << 16);
+    v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+  }
+  for (int r = 0; r < p.nparts; ++r) {
+    const float4* pp = reinterpret_cast<const float4*>(p.parts + ((size_t)r * M + m) * p.K + k);
+    const float4 a = pp[0], b = pp[1];
+    v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+    v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+  }
+}
+
+// Round to the bf16 residual stream; optionally store it; returns the rounded values.
+__device__ __forceinline__ void round_store8(const MatvecParams& p, int m, int k, float (&v)[8], bool store) {
+  uint32_t packed[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    packed[j] = *reinterpret_cast<const uint32_t*>(&h2);
+    v[2 * j] = __uint_as_float(packed[j] << 16);
+    v[2 * j + 1] = __uint_as_float(packed[j] & 0xffff0000u);
+  }
+  if (store)
+    *reinterpret_cast<uint4*>(p.hidden_out + (size_t)m * p.K + k) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+__device__ __forceinline__ void gamma8(const MatvecParams& p, int k, float (&v)[8]) {
+  if (p.gamma == nullptr) return;
+  const float one = p.norm_mode == 1 ? 1.f : 0.f;
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p.gamma + k));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p.gamma + k + 4));
+  v[0] *= one + a.x; v[1] *= one + a.y; v[2] *= one + a.z; v[3] *= one + a.w;
+  v[4] *= one + b.x; v[5] *= one + b.y; v[6] *= one + b.z; v[7] *= one + b.w;
+}
+
+// Two block-wide reductions at once: sum of a, max of b.
+__device__ __forceinline__ void block_sum_max(float& a, float& b, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  a = warp_sum(a);
+  b = warp_max(b);
+  __syncthreads();
+  if (lane == 0) {
+    red[warp] = a;
+    red[16 + warp] = b;
+  }
+  __syncthreads();
+  float ta = 0.f, tb = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    ta += red[w];
+    tb = fmaxf(tb, red[16 + w]);
+  }
+  a = ta;
+  b = tb;
+}
+
+// Final staged value: normalise, round to bf16 (what an unfused pipeline would have stored),
+// scale into [-1, 1] and write fp16 at the permuted position.
+__device__ __forceinline__ void stage8(__half* xs_row, int k_in_chunk, const float (&t)[8], float rs, float cinv,
+                                       bool round_bf16) {
+  uint32_t out[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float a = t[2 * j] * rs, b = t[2 * j + 1] * rs;
+    if (round_bf16) {
+      a = __bfloat162float(__float2bfloat16(a));
+      b = __bfloat162float(__float2bfloat16(b));
+    }
+    const __half2 h = __floats2half2_rn(a * cinv, b * cinv);
+    out[j] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(xs_row + staged_index(k_in_chunk)) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+__device__ __forceinline__ float pow2_at_least(float a) {
+  // smallest power of two >= a (a > 0), as a float
+  int e;
+  const float m = frexpf(a, &e);  // a = m * 2^e, m in [0.5, 1)
+  return ldexpf(1.f, m == 0.5f ? e - 1 : e);
+}
+
 template <int M>
 __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams p) {
-  extern __shared__ __align__(16) float xs[];  // [M][kc] staged activations (permuted)
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);                         // [M][kc]
+  float* scratch = reinterpret_cast<float*>(smem_raw + (size_t)M * p.kc * 2);  // [K] (single chunk only)
   __shared__ float red[40];
-  __shared__ float rstd[8];
+  __shared__ float s_rs[8], s_c[8];  // per row: rstd (or 1) and the power-of-two range scale
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int K = p.K;
-  const int kc = min(((kSmemFloats / M) >> 9) << 9, (K + 511) & ~511);  // chunk length, multiple of 512
+  const int K = p.K, kc = p.kc;
   const bool swiglu = p.epi == 1;
   const int half_n = p.N >> 1;
   // Row pairs: a warp owns two output rows at a time (gate_j and up_j for SwiGLU, else
@@ -152,8 +241,9 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
   const int n_groups = swiglu ? half_n : (total_rows + 1) >> 1;
   const int warps_total = gridDim.x * kWarps;
   const int gwarp = blockIdx.x * kWarps + warp;
-
   const int kb_count = (K + 127) >> 7;
+  const bool round_x = p.gamma != nullptr;
+
   // Weights do not depend on the activations: issue the first batch of this warp's first
   // row pair before the prologue so that the HBM latency overlaps the norm.
   Fp8Batch bt;
@@ -169,24 +259,80 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
     }
   }
 
-  // ---- wait for the producers of `parts`, then the per-row statistics ----
   if (p.parts != nullptr && p.wait.flag != nullptr) {
     if (tid == 0) wait_all_ranks(p.wait);
     __syncthreads();
   }
-  const bool single_chunk = K <= kc;
-  if (p.gamma != nullptr && !single_chunk) {
+
+  const int nchunks8 = K >> 3;
+  const bool write_hidden = p.hidden_out != nullptr && blockIdx.x == 0;
+  if (p.single_chunk) {
+    // One pass over global memory: t = bf16(x + parts) * (1 + gamma) into the fp32 scratch
+    // row with the sum of squares and the largest magnitude, then a shared-memory pass that
+    // normalises, scales and converts.
     for (int m = 0; m < M; ++m) {
-      float ss = 0.f;
-      for (int k = tid; k < K; k += kThreads) {
-        float v = p.x_in ? __bfloat162float(p.x_in[(size_t)m * K + k]) : 0.f;
-        for (int r = 0; r < p.nparts; ++r) v += p.parts[((size_t)r * M + m) * K + k];
-        // The residual stream is kept in bf16; normalise what a later reader will see.
-        v = __bfloat162float(__float2bfloat16(v));
-        ss += v * v;
+      float ss = 0.f, amax = 0.f;
+      for (int c0 = tid; c0 < nchunks8; c0 += kThreads * 4) {
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * kThreads;
+          if (c < nchunks8) load8(p, M, m, c * 8, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * kThreads;
+          if (c >= nchunks8) continue;
+          if (p.parts != nullptr || write_hidden) round_store8(p, m, c * 8, v[u], write_hidden);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += v[u][j] * v[u][j];
+          gamma8(p, c * 8, v[u]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[u][j]));
+          *reinterpret_cast<float4*>(scratch + c * 8) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+          *reinterpret_cast<float4*>(scratch + c * 8 + 4) = make_float4(v[u][4], v[u][5], v[u][6], v[u][7]);
+        }
       }
-      ss = block_sum(ss, red);
-      if (tid == 0) rstd[m] = rsqrtf(ss / (float)K + p.eps);
+      block_sum_max(ss, amax, red);
+      const float rs = p.gamma != nullptr ? rsqrtf(ss / (float)K + p.eps) : 1.f;
+      const float c = pow2_at_least(fmaxf(amax * rs, 1e-30f));
+      if (tid == 0) s_c[m] = c;
+      const float cinv = 1.f / c;
+      __half* row = xs + m * kc;
+      for (int c8 = tid; c8 < (kc >> 3); c8 += kThreads) {
+        float t[8];
+        if (c8 < nchunks8) {
+          const float4 a = *reinterpret_cast<const float4*>(scratch + c8 * 8);
+          const float4 b = *reinterpret_cast<const float4*>(scratch + c8 * 8 + 4);
+          t[0] = a.x; t[1] = a.y; t[2] = a.z; t[3] = a.w; t[4] = b.x; t[5] = b.y; t[6] = b.z; t[7] = b.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t[j] = 0.f;
+        }
+        stage8(row, c8 * 8, t, rs, cinv, round_x);
+      }
+      __syncthreads();  // the scratch row is reused by the next m
+    }
+  } else {
+    // The row does not fit: statistics first (one extra pass over L2-resident data).
+    for (int m = 0; m < M; ++m) {
+      float ss = 0.f, amax = 0.f;
+      for (int c = tid; c < nchunks8; c += kThreads) {
+        float v[8];
+        load8(p, M, m, c * 8, v);
+        if (p.parts != nullptr) round_store8(p, m, c * 8, v, false);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+        gamma8(p, c * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      }
+      block_sum_max(ss, amax, red);
+      const float rs = p.gamma != nullptr ? rsqrtf(ss / (float)K + p.eps) : 1.f;
+      if (tid == 0) {
+        s_rs[m] = rs;
+        s_c[m] = pow2_at_least(fmaxf(amax * rs, 1e-30f));
+      }
     }
     __syncthreads();
   }
@@ -199,118 +345,25 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
 
   for (int k0 = 0; k0 < K; k0 += kc) {
     const int klen = min(kc, K - k0);
-    // ---- stage the chunk ----
-    if (k0 > 0) __syncthreads();
-    if (single_chunk) {
-      // One pass over global memory: stage the raw rows and their sums of squares, then
-      // normalise in shared memory.
+    if (!p.single_chunk) {
+      if (k0 > 0) __syncthreads();
       for (int m = 0; m < M; ++m) {
-        float ss = 0.f;
-        // Zero the padding of the last 512-element run (read by lanes past K, times zero weights).
-        for (int k = K + tid; k < kc; k += kThreads) xs[m * kc + staged_index(k)] = 0.f;
-        // Eight elements per thread and step, four steps in flight, so that the loads of
-        // the whole row overlap instead of forming one latency chain per element.
-        const int nchunks = K >> 3;
-        for (int c0 = tid; c0 < nchunks; c0 += kThreads * 4) {
-          float v[4][8];
+        const float rs = s_rs[m], cinv = 1.f / s_c[m];
+        for (int c8 = tid; c8 < (kc >> 3); c8 += kThreads) {
+          float t[8];
+          if (c8 * 8 < klen) {
+            load8(p, M, m, k0 + c8 * 8, t);
+            if (p.parts != nullptr || write_hidden) round_store8(p, m, k0 + c8 * 8, t, write_hidden);
+            gamma8(p, k0 + c8 * 8, t);
+          } else {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = c0 + u * kThreads;
-            uint4 xv = make_uint4(0, 0, 0, 0);
-            if (c < nchunks && p.x_in) xv = __ldg(reinterpret_cast<const uint4*>(p.x_in + (size_t)m * K + c * 8));
-            const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              v[u][2 * j] = __uint_as_float(w[j] << 16);
-              v[u][2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-            }
+            for (int j = 0; j < 8; ++j) t[j] = 0.f;
           }
-          for (int r = 0; r < p.nparts; ++r) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int c = c0 + u * kThreads;
-              if (c < nchunks) {
-                const float4* pp = reinterpret_cast<const float4*>(p.parts + ((size_t)r * M + m) * K + c * 8);
-                const float4 a = pp[0], b = pp[1];
-                v[u][0] += a.x; v[u][1] += a.y; v[u][2] += a.z; v[u][3] += a.w;
-                v[u][4] += b.x; v[u][5] += b.y; v[u][6] += b.z; v[u][7] += b.w;
-              }
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = c0 + u * kThreads;
-            if (c >= nchunks) continue;
-            uint32_t packed[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[u][2 * j], v[u][2 * j + 1]);
-              packed[j] = *reinterpret_cast<const uint32_t*>(&h2);
-              if (p.parts != nullptr) {
-                v[u][2 * j] = __uint_as_float(packed[j] << 16);
-                v[u][2 * j + 1] = __uint_as_float(packed[j] & 0xffff0000u);
-              }
-            }
-            if (p.hidden_out != nullptr && blockIdx.x == 0)
-              *reinterpret_cast<uint4*>(p.hidden_out + (size_t)m * K + c * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            // elements 8c..8c+7 live in two float4 of the permuted layout
-            const int si = m * kc + staged_index(c * 8);
-            *reinterpret_cast<float4*>(xs + si) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
-            *reinterpret_cast<float4*>(xs + si + 128) = make_float4(v[u][4], v[u][5], v[u][6], v[u][7]);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) ss += v[u][j] * v[u][j];
-          }
-        }
-        if (p.gamma != nullptr) {
-          ss = block_sum(ss, red);
-          const float rs = rsqrtf(ss / (float)K + p.eps);
-          const float one = p.norm_mode == 1 ? 1.f : 0.f;
-          const int nq = K >> 2;
-          for (int c0 = tid; c0 < nq; c0 += kThreads * 4) {
-            float4 gv[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int c = c0 + u * kThreads;
-              gv[u] = c < nq ? __ldg(reinterpret_cast<const float4*>(p.gamma) + c) : make_float4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int c = c0 + u * kThreads;
-              if (c >= nq) continue;
-              float4* xp = reinterpret_cast<float4*>(xs + m * kc + staged_index(c * 4));
-              float4 xv = *xp;
-              // Activations are bf16 everywhere else; round here too so that the fused and
-              // unfused paths see the same operand.
-              xv.x = __bfloat162float(__float2bfloat16(xv.x * rs * (one + gv[u].x)));
-              xv.y = __bfloat162float(__float2bfloat16(xv.y * rs * (one + gv[u].y)));
-              xv.z = __bfloat162float(__float2bfloat16(xv.z * rs * (one + gv[u].z)));
-              xv.w = __bfloat162float(__float2bfloat16(xv.w * rs * (one + gv[u].w)));
-              *xp = xv;
-            }
-          }
+          stage8(xs + m * kc, c8 * 8, t, rs, cinv, round_x);
         }
       }
-    } else {
-      for (int m = 0; m < M; ++m) {
-        for (int k = tid; k < kc; k += kThreads) {
-          float v = 0.f;
-          if (k < klen) {
-            const size_t gi = (size_t)m * K + k0 + k;
-            v = p.x_in ? __bfloat162float(p.x_in[gi]) : 0.f;
-            for (int r = 0; r < p.nparts; ++r) v += p.parts[((size_t)r * M + m) * K + k0 + k];
-            const bf16 hv = __float2bfloat16(v);
-            if (p.hidden_out != nullptr && blockIdx.x == 0) p.hidden_out[gi] = hv;
-            if (p.parts != nullptr) v = __bfloat162float(hv);
-            if (p.gamma != nullptr) {
-              const float g = p.gamma[k0 + k];
-              v = __bfloat162float(__float2bfloat16(v * rstd[m] * (p.norm_mode == 1 ? 1.f + g : g)));
-            }
-          }
-          xs[m * kc + staged_index(k)] = v;
-        }
-      }
+      __syncthreads();
     }
-    __syncthreads();
 
     // ---- stream the weight rows ----
     for (int g = gwarp; g < n_groups; g += warps_total) {
@@ -349,8 +402,14 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
             const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(w0p + ka + 8));
             const uint4 b0 = __ldg(reinterpret_cast<const uint4*>(w1p + ka));
             const uint4 b1 = __ldg(reinterpret_cast<const uint4*>(w1p + ka + 8));
-            fma16_bf16<M>(a0, a1, xs, (it << 9) + (lane << 2), kc, acc[0]);
-            fma16_bf16<M>(b0, b1, xs, (it << 9) + (lane << 2), kc, acc[1]);
+            const int base = (it << 9) + (lane << 3);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              const uint4 x0 = *reinterpret_cast<const uint4*>(xs + m * kc + base);
+              const uint4 x1 = *reinterpret_cast<const uint4*>(xs + m * kc + base + 256);
+              acc[0][m] += dot16_bf16(a0, a1, x0, x1);
+              acc[1][m] += dot16_bf16(b0, b1, x0, x1);
+            }
           }
         }
       }
@@ -360,7 +419,7 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
 #pragma unroll
         for (int r = 0; r < 2; ++r)
 #pragma unroll
-          for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+          for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]) * s_c[m];
         if (lane == 0) {
           if (swiglu) {
 #pragma unroll
@@ -399,13 +458,28 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
 }
 
 template <int M>
-int launch_m(const MatvecParams& p, int blocks, cudaStream_t stream) {
-  const int kc = min(((kSmemFloats / M) >> 9) << 9, (p.K + 511) & ~511);
-  const size_t smem = (size_t)M * kc * sizeof(float);
+int launch_m(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
+  // Single chunk when M fp16 rows plus one fp32 scratch row fit; else chunks of fp16 only.
+  const int kround = (p.K + 511) & ~511;
+  size_t smem;
+  if ((size_t)M * kround * 2 + (size_t)p.K * 4 <= (size_t)kSmemBytes) {
+    p.kc = kround;
+    p.single_chunk = 1;
+    smem = (size_t)M * kround * 2 + (size_t)p.K * 4;
+  } else {
+    p.kc = ((kSmemBytes / (2 * M)) >> 9) << 9;
+    p.single_chunk = 0;
+    smem = (size_t)M * p.kc * 2;
+  }
+  int blocks = (groups + kWarps - 1) / kWarps;
+  if (p.single_chunk) {
+    const int cap = (sm_count > 0 ? sm_count : 148) * 2;
+    if (blocks > cap) blocks = cap;
+  }  // chunked: exactly one group per warp (one accumulator set per warp)
+  if (blocks < 1) blocks = 1;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(matvec_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemFloats * (int)sizeof(float)) != cudaSuccess) {
+    if (cudaFuncSetAttribute(matvec_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
@@ -418,8 +492,6 @@ int launch_m(const MatvecParams& p, int blocks, cudaStream_t stream) {
 
 }  // namespace
 
-// A chunked K loop keeps one accumulator set per warp, so a warp may own only one row
-// group when K does not fit one chunk. The launcher sizes the grid accordingly.
 PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, int Nb, int K, int M,
                      const void* x_in, const float* parts, int nparts, void* hidden_out,
                      const float* gamma, int norm_mode, float eps, const PkWait* wait, int epi,
@@ -430,6 +502,7 @@ PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, i
   if (hidden_out != nullptr && hidden_out == x_in) return PK_ERR_BAD_ARG;  // other blocks still read x_in
   if (x_in == nullptr && (parts == nullptr || nparts <= 0)) return PK_ERR_BAD_ARG;
   if (epi == 3 && push == nullptr) return PK_ERR_BAD_ARG;
+  if (((uintptr_t)x_in & 15) != 0 || ((uintptr_t)parts & 15) != 0 || ((uintptr_t)gamma & 15) != 0) return PK_ERR_BAD_ARG;
   MatvecParams p{};
   p.W = (const uint8_t*)W;
   p.scale = scale;
@@ -453,26 +526,14 @@ PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, i
   if (push) p.push = *push;
 
   const int groups = epi == 1 ? N / 2 : (N + Nb + 1) / 2;
-  const int kc = (((kSmemFloats / M) >> 9) << 9);
-  const bool chunked = K > kc;
-  int blocks;
-  if (chunked) {
-    blocks = (groups + kWarps - 1) / kWarps;  // exactly one group per warp
-  } else {
-    const int per_sm = 2;
-    blocks = (groups + kWarps - 1) / kWarps;
-    const int cap = (sm_count > 0 ? sm_count : 148) * per_sm;
-    if (blocks > cap) blocks = cap;
-  }
-  if (blocks < 1) blocks = 1;
   switch (M) {
-    case 1: return launch_m<1>(p, blocks, stream);
-    case 2: return launch_m<2>(p, blocks, stream);
-    case 3: return launch_m<3>(p, blocks, stream);
-    case 4: return launch_m<4>(p, blocks, stream);
-    case 5: return launch_m<5>(p, blocks, stream);
-    case 6: return launch_m<6>(p, blocks, stream);
-    case 7: return launch_m<7>(p, blocks, stream);
-    default: return launch_m<8>(p, blocks, stream);
+    case 1: return launch_m<1>(p, groups, sm_count, stream);
+    case 2: return launch_m<2>(p, groups, sm_count, stream);
+    case 3: return launch_m<3>(p, groups, sm_count, stream);
+    case 4: return launch_m<4>(p, groups, sm_count, stream);
+    case 5: return launch_m<5>(p, groups, sm_count, stream);
+    case 6: return launch_m<6>(p, groups, sm_count, stream);
+    case 7: return launch_m<7>(p, groups, sm_count, stream);
+    default: return launch_m<8>(p, groups, sm_count, stream);
   }
 }

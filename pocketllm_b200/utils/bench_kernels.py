@@ -1,0 +1,108 @@
+"""Micro-benchmarks of the hot kernels at the benchmark model's shapes, timed with CUDA
+events (warm-up, synchronise on both sides, weight copies larger than L2 cycled through) and reported
+as a fraction of the measured peaks (`MEASURED_PEAKS.json` at the repository root, else
+6.65 TB/s / 1.59 PFLOP/s as the stated fallback).
+
+    python -m pocketllm_b200.utils.bench_kernels --op gemm --M 512 --N 34816 --K 5120 --epi 1
+    python -m pocketllm_b200.utils.bench_kernels --op matvec --N 34816 --K 5120 --epi 1
+    python -m pocketllm_b200.utils.bench_kernels --suite
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from .. import ops
+
+
+def peaks() -> tuple[float, float, str]:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _time(fns, reps: int = 20, warmup: int = 3) -> float:
+    """Mean time of one launch in microseconds. `fns` is a list of equivalent launches over
+    different weight copies (together larger than L2) that are cycled through, so that every
+    launch streams its weights from HBM; `reps` launches are queued back to back between one
+    pair of events so that host launch overhead stays off the device timeline."""
+    for i in range(warmup):
+        fns[i % len(fns)]()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fns[i % len(fns)]()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3
+
+
+def _copies(nbytes: int) -> int:
+    return max(2, -(-(300 << 20) // nbytes))
+
+
+def _fp8(n: int, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    w = torch.randint(0, 119, (n, k), device="cuda", dtype=torch.uint8)   # finite positive codes
+    w |= torch.randint(0, 2, (n, k), device="cuda", dtype=torch.uint8) << 7
+    s = torch.full(((n + 127) // 128, (k + 127) // 128), 1e-4, device="cuda", dtype=torch.float32)
+    return w.view(torch.float8_e4m3fn), s
+
+
+def bench_gemm(M: int, N: int, K: int, epi: int, iters: int) -> dict:
+    hbm, tf, src = peaks()
+    ws = [_fp8(N, K) for _ in range(_copies(N * K))]
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    resid = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16) if epi == ops.EPI_RESID else None
+    fns = [(lambda w=w, s=s: ops.gemm_umma(a, w, s, epi=epi, resid=resid)) for w, s in ws]
+    us = _time(fns, iters)
+    flops = 2.0 * M * N * K
+    return {"op": "gemm_umma", "M": M, "N": N, "K": K, "epi": epi, "us": round(us, 2),
+            "tflops": round(flops / us / 1e6, 1), "frac_of_peak": round(flops / us / 1e6 / tf, 3), "peak": f"{tf} TFLOP/s bf16 ({src})",
+            "weight_gbs": round(N * K / us / 1e3, 1)}
+
+
+def bench_matvec(M: int, N: int, K: int, epi: int, iters: int) -> dict:
+    hbm, tf, src = peaks()
+    ws = [_fp8(N, K) for _ in range(_copies(N * K))]
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    gamma = torch.zeros(K, device="cuda")
+    fns = [(lambda w=w, s=s: ops.matvec(x, w, s, gamma=gamma, epi=epi)) for w, s in ws]
+    us = _time(fns, iters)
+    nbytes = N * K + ws[0][1].numel() * 4
+    return {"op": "matvec", "M": M, "N": N, "K": K, "epi": epi, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+            "frac_of_peak": round(nbytes / us / 1e3 / hbm, 3), "peak": f"{hbm} GB/s copy ({src})"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="gemm", choices=["gemm", "matvec"])
+    ap.add_argument("--M", type=int, default=512)
+    ap.add_argument("--N", type=int, default=34816)
+    ap.add_argument("--K", type=int, default=5120)
+    ap.add_argument("--epi", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=40)
+    ap.add_argument("--suite", action="store_true", help="all projections of the 27B-shaped model")
+    args = ap.parse_args()
+    if args.suite:
+        for name, n, k, epi in [("in_proj", 12288, 5120, 0), ("out_proj", 5120, 4096, 0), ("qkv", 12288, 5120, 0),
+                                ("o_proj", 5120, 5120, 0), ("gate_up", 34816, 5120, 1), ("down", 5120, 17408, 0)]:
+            r = bench_gemm(512, n, k, epi, args.iters)
+            r["name"] = name
+            print(json.dumps(r))
+            r = bench_matvec(1, n, k, epi, args.iters)
+            r["name"] = name
+            print(json.dumps(r))
+        return 0
+    r = bench_gemm(args.M, args.N, args.K, args.epi, args.iters) if args.op == "gemm" else bench_matvec(args.M if args.op != "matvec" or args.M <= 8 else 1, args.N, args.K, args.epi, args.iters)
+    print(json.dumps(r))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
