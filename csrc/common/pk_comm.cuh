@@ -61,6 +61,9 @@ __device__ __forceinline__ uint32_t comm_seq(const uint32_t* epoch, uint32_t sit
 // Called by ONE thread of a block. Returns false if the budget ran out.
 __device__ __forceinline__ bool wait_all_ranks(const PkWait& w) {
   if (w.flag == nullptr || w.world <= 1) return true;
+  // Once a wait of this step has given up, later waits return at once: the step is lost
+  // anyway and the kernels only have to drain.
+  if (*((volatile uint32_t*)w.status) != 0u) return false;
   const uint32_t target = comm_seq(w.epoch, w.sites_per_epoch, w.site);
   const uint64_t t0 = global_timer_ns();
   const uint64_t budget = (uint64_t)w.timeout_us * 1000ull;
