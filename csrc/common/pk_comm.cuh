@@ -97,4 +97,18 @@ __device__ __forceinline__ void publish_when_grid_done(const PkPush& p) {
   }
 }
 
+// Variant for kernels whose threads already ran __threadfence_system() after their last
+// store and met at a block barrier: called by ONE thread of each block.
+__device__ __forceinline__ void publish_after_block_sync(const PkPush& p) {
+  if (p.world <= 1 && p.flag[0] == nullptr) return;
+  const uint32_t nblocks = gridDim.x * gridDim.y * gridDim.z;
+  const uint32_t done = atomicAdd(p.block_counter, 1u) + 1u;
+  if (done == nblocks) {
+    *p.block_counter = 0u;
+    __threadfence_system();
+    const uint32_t seq = comm_seq(p.epoch, p.sites_per_epoch, p.site);
+    for (int r = 0; r < p.world; ++r) st_release_sys(p.flag[r] + p.rank, seq);
+  }
+}
+
 }  // namespace pk

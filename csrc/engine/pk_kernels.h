@@ -18,7 +18,8 @@ int pk_matvec(const void* W, const float* scale, const void* Wb, int N, int Nb, 
               cudaStream_t stream);
 
 int pk_gemm_umma(const void* A, int lda, const void* W, const float* scale, int wfmt, int M, int N, int K,
-                 int epi, void* C, const void* resid, int ldc, uint32_t* status, cudaStream_t stream);
+                 int epi, void* C, const void* resid, int ldc, uint32_t* status, const PkPush* push,
+                 cudaStream_t stream);
 
 int pk_deltanet_seq(const void* proj, int ld, int T, int key_heads, int value_heads, int key_dim,
                     int value_dim, const float* conv_w, float* conv_state, const float* A_log,

@@ -195,6 +195,8 @@ void QwenEngine::alloc_buffers() {
   const size_t slot_bytes = (size_t)W * kSmallRows * hidden_ * sizeof(float);
   for (int s = 0; s < 2; ++s) { off_slot_[s] = off; off = align_up(off + slot_bytes, 256); }
   for (int s = 0; s < 2; ++s) { off_flag_[s] = off; off = align_up(off + PK_MAX_RANKS * 4, 256); }
+  const size_t bslot_bytes = W > 1 ? (size_t)W * rows_cap_ * hidden_ * sizeof(float) : 0;
+  for (int s = 0; s < 2; ++s) { off_bslot_[s] = off; off = align_up(off + bslot_bytes, 256); }
   off_cval_ = off; off = align_up(off + (size_t)W * kSmallRows * 4, 256);
   off_cidx_ = off; off = align_up(off + (size_t)W * kSmallRows * 4, 256);
   off_cflag_ = off; off = align_up(off + PK_MAX_RANKS * 4, 256);
@@ -203,7 +205,8 @@ void QwenEngine::alloc_buffers() {
   off_counter_ = off; off = align_up(off + 4, 256);
   arena_bytes_ = off;
   arena_ = dalloc(arena_bytes_);
-  cuda_check(cudaMemset(arena_, 0, arena_bytes_), "memset arena");
+  cuda_check(cudaMemset(arena_, 0, std::min<size_t>(arena_bytes_, off_bslot_[0] + 4096)), "memset arena head");
+  cuda_check(cudaMemset((char*)arena_ + off_cval_, 0, arena_bytes_ - off_cval_), "memset arena tail");
   for (int r = 0; r < PK_MAX_RANKS; ++r) peers_[r] = nullptr;
   peers_[opt_.tp_rank] = arena_;
   peer_cval_dev_ = (float**)dalloc(PK_MAX_RANKS * sizeof(void*));
@@ -463,7 +466,9 @@ void QwenEngine::copy_logits(float* out_host, int row) {
 // ---------------------------------------------------------------------------------------
 // comm helpers
 
-float* QwenEngine::slot_parts(int site) const { return (float*)((char*)arena_ + off_slot_[site & 1]); }
+float* QwenEngine::slot_parts(int site, bool big) const {
+  return (float*)((char*)arena_ + (big ? off_bslot_[site & 1] : off_slot_[site & 1]));
+}
 
 PkWait QwenEngine::make_wait(int site) const {
   PkWait w{};
@@ -477,10 +482,10 @@ PkWait QwenEngine::make_wait(int site) const {
   return w;
 }
 
-PkPush QwenEngine::make_push(int site) const {
+PkPush QwenEngine::make_push(int site, bool big) const {
   PkPush p{};
   for (int r = 0; r < opt_.tp_world; ++r) {
-    p.dst[r] = (float*)((char*)peers_[r] + off_slot_[site & 1]);
+    p.dst[r] = (float*)((char*)peers_[r] + (big ? off_bslot_[site & 1] : off_slot_[site & 1]));
     p.flag[r] = opt_.tp_world > 1 ? (uint32_t*)((char*)peers_[r] + off_flag_[site & 1]) : nullptr;
   }
   p.block_counter = (uint32_t*)((char*)arena_ + off_counter_);
@@ -591,15 +596,41 @@ void QwenEngine::sample_rows(int M, int first_row) {
 // forward, tensor-core path (more than 8 rows, one rank)
 
 void QwenEngine::run_chunk(int M) {
+  if (!peers_set_) throw std::runtime_error("peer arenas not registered");
   const float eps = (float)cfg_.rms_norm_eps;
+  const int W = opt_.tp_world;
   void* hid = hidden_buf_[cur_];
+  if (W > 1) check(pk_bump_epoch((uint32_t*)((char*)arena_ + off_epoch_), stream_), "epoch");
   check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hid, nullptr, stream_), "embedding");
+  int pending = -1;  // site whose partial sums still wait to be added to the residual stream
   auto gemm = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc) {
-    check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, stream_), "gemm_umma");
+    check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, stream_), "gemm_umma");
+  };
+  // Row-parallel projection back into the residual stream. One rank: residual add in the
+  // epilogue. Several ranks: the epilogue pushes the fp32 partial tiles into every rank's
+  // slot and the next norm kernel sums them (all-reduce fused on both sides).
+  auto gemm_out = [&](const void* A, int lda, const Fp8Linear& w, int site) {
+    if (W == 1) {
+      gemm(A, lda, w, 2, hid, hid, hidden_);
+    } else {
+      PkPush ps = make_push(site, true);
+      check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, 4, nullptr, nullptr, hidden_, gemm_status_, &ps, stream_),
+            "gemm_umma(push)");
+      pending = site;
+    }
+  };
+  auto norm = [&](const float* gamma, void* y) {
+    if (pending >= 0) {
+      PkWait wt = make_wait(pending);
+      check(pk_rmsnorm(hid, slot_parts(pending, true), W, M, hidden_, hid, gamma, 1, eps, y, &wt, stream_), "rmsnorm(reduce)");
+      pending = -1;
+    } else {
+      check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, gamma, 1, eps, y, nullptr, stream_), "rmsnorm");
+    }
   };
   for (int i = 0; i < cfg_.num_layers; ++i) {
     QwenLayer& L = layers_[i];
-    check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, L.input_norm, 1, eps, xn_, nullptr, stream_), "rmsnorm");
+    norm(L.input_norm, xn_);
     if (L.full) {
       gemm(xn_, hidden_, L.qkv, 0, proj_, nullptr, ld_proj_);
       check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, pos_dev_, L.q_norm, L.k_norm, eps,
@@ -611,11 +642,11 @@ void QwenEngine::run_chunk(int M) {
                           cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
             "gqa_prefill");
       ++launches_;
-      gemm(attn_out_, hq_l_ * kHeadDim, L.o_proj, 2, hid, hid, hidden_);
+      gemm_out(attn_out_, hq_l_ * kHeadDim, L.o_proj, 2 * i);
     } else {
       gemm(xn_, hidden_, L.in_proj, 0, proj_, nullptr, ld_proj_);
       check(pk_gemm_umma(xn_, hidden_, L.in_proj_ab, nullptr, 1, M, 2 * vh_l_, hidden_, 0,
-                         (char*)proj_ + (size_t)L.in_proj.N * 2, nullptr, ld_proj_, gemm_status_, stream_),
+                         (char*)proj_ + (size_t)L.in_proj.N * 2, nullptr, ld_proj_, gemm_status_, nullptr, stream_),
             "gemm_umma(ab)");
       if (M >= 32) {
         check(pk_deltanet_chunked(proj_, ld_proj_, M, kh_l_, vh_l_, kHeadDim, kHeadDim, L.conv_w, L.conv_state, L.A_log,
@@ -627,12 +658,13 @@ void QwenEngine::run_chunk(int M) {
                               L.dt_bias, L.lin_norm, eps, L.lin_state, attn_out_, stream_),
               "deltanet_seq");
       }
-      gemm(attn_out_, vd_l_, L.out_proj, 2, hid, hid, hidden_);
+      gemm_out(attn_out_, vd_l_, L.out_proj, 2 * i);
     }
-    check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, L.post_norm, 1, eps, xn_, nullptr, stream_), "rmsnorm");
+    norm(L.post_norm, xn_);
     gemm(xn_, hidden_, L.gate_up, 1, mlp_h_, nullptr, inter_l_);
-    gemm(mlp_h_, inter_l_, L.down, 2, hid, hid, hidden_);
+    gemm_out(mlp_h_, inter_l_, L.down, 2 * i + 1);
   }
+  if (pending >= 0) norm(final_norm_, nullptr);  // fold the last partials into the residual stream
   const char* last = (const char*)hid + (size_t)(M - 1) * hidden_ * 2;
   check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, last, nullptr, 0, nullptr, final_norm_, 1, eps,
                   nullptr, 2, logits_, vocab_l_, nullptr, sm_count_, stream_),
@@ -651,8 +683,6 @@ int QwenEngine::prefill(const int* tokens_host, int n) {
   int done = 0;
   while (done < n) {
     int M = std::min(n - done, rows_cap_);
-    // More than one rank: the tensor-core path is single-rank for now, use row groups.
-    if (opt_.tp_world > 1) M = std::min(M, kSmallRows);
     memcpy(pinned_tok_, tokens_host + done, (size_t)M * sizeof(int));
     cuda_check(cudaMemcpyAsync(tokens_dev_, pinned_tok_, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, stream_), "h2d tokens");
     check(pk_iota_int(pos_dev_, M, nullptr, pos_, stream_), "iota");

@@ -132,8 +132,8 @@ class QwenEngine {
   void sample_rows(int M, int first_row);
   void capture_decode_graph();
   PkWait make_wait(int site) const;
-  PkPush make_push(int site) const;
-  float* slot_parts(int site) const;
+  PkPush make_push(int site, bool big = false) const;
+  float* slot_parts(int site, bool big = false) const;
   void check(int status, const char* what) const;
 
   QwenConfig cfg_;
@@ -181,6 +181,7 @@ class QwenEngine {
   // comm arena layout (all inside arena_): slots, flags, sampler candidates, epoch, status
   void* arena_ = nullptr;
   size_t arena_bytes_ = 0;
+  size_t off_bslot_[2];   // prefill-size slots [world][rows_cap][hidden] fp32
   size_t off_slot_[2], off_flag_[2], off_cval_, off_cidx_, off_cflag_, off_epoch_, off_status_, off_counter_;
   void* peers_[PK_MAX_RANKS] = {nullptr};
   float** peer_cval_dev_ = nullptr;

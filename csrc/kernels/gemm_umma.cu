@@ -16,6 +16,7 @@
 // Replaces the reference's prefill paths: cpp_engine/cuda/qwen_half_ops.cu:379-583 (SIMT
 // tiles with an LUT decode) and cpp_engine/cuda/fp8_ops.cu:142-300 (whole-weight dequant
 // to fp16 in HBM followed by cublasGemmEx).
+#include "../common/pk_comm.cuh"
 #include "../common/pk_sm100.cuh"
 
 namespace {
@@ -34,7 +35,7 @@ constexpr int kMaxScaleKb = 512;          // K <= 65536 for the shared-memory sc
 constexpr uint32_t kTmemCols = 128;
 
 enum { WFMT_FP8_BLOCK128 = 0, WFMT_BF16 = 1 };
-enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_RESID = 2, EPI_F32 = 3 };
+enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_RESID = 2, EPI_F32 = 3, EPI_PUSH = 4 };
 
 struct GemmParams {
   const float* scale;   // fp8: [ceil(N/128), ceil(K/128)]
@@ -46,6 +47,7 @@ struct GemmParams {
   const bf16* resid;    // EPI_RESID: [M, ldc]
   int ldc;
   uint32_t* status;     // device status word, 0 = ok
+  PkPush push;          // EPI_PUSH: fp32 partial tile into every rank's slot [world][M][ldc], then a flag
 };
 
 struct __align__(1024) SmemLayout {
@@ -260,6 +262,21 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           float* dst = p.Cf + (size_t)m * p.ldc + n;
           for (int i = 0; i < 32; ++i)
             if (n + i < p.N) dst[i] = __uint_as_float(r[i]);
+        } else if (p.epi == EPI_PUSH) {
+          // The scatter side of the all-reduce, issued tile by tile from the epilogue: this
+          // rank's fp32 partial goes straight into every peer's slot over NVLink.
+          const size_t off = ((size_t)p.push.rank * p.M + m) * p.ldc + n;
+          for (int pr = 0; pr < p.push.world; ++pr) {
+            float* dst = p.push.dst[pr] + off;
+            if (n + 32 <= p.N) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                *reinterpret_cast<uint4*>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (n + i < p.N) dst[i] = __uint_as_float(r[i]);
+            }
+          }
         } else {
           bf16* dst = p.C + (size_t)m * p.ldc + n;
           const bf16* rs = p.epi == EPI_RESID ? p.resid + (size_t)m * p.ldc + n : nullptr;
@@ -289,11 +306,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
+    if (p.epi == EPI_PUSH) __threadfence_system();
     tc_fence_before();
   }
 
 done:
   __syncthreads();
+  if (p.epi == EPI_PUSH && threadIdx.x == 0) publish_after_block_sync(p.push);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_acc, kTmemCols);
@@ -336,13 +355,14 @@ bool encode_2d(EncodeTiledFn encode, CUtensorMap* map, CUtensorMapDataType dt, i
 // For epi == 1 (SwiGLU) W holds N/2 gate rows followed by N/2 up rows and C has N/2 columns.
 PK_API int pk_gemm_umma(const void* A, int lda, const void* W, const float* scale, int wfmt, int M, int N,
                         int K, int epi, void* C, const void* resid, int ldc, uint32_t* status,
-                        cudaStream_t stream) {
+                        const PkPush* push, cudaStream_t stream) {
   if (M < 1 || N < 1 || K < BK || (K % BK) != 0) return PK_ERR_BAD_ARG;
   if (((uintptr_t)A & 15) != 0 || ((size_t)lda * 2) % 16 != 0 || ((uintptr_t)W & 15) != 0) return PK_ERR_BAD_ARG;
   if (wfmt != WFMT_FP8_BLOCK128 && wfmt != WFMT_BF16) return PK_ERR_UNSUPPORTED;
   if (wfmt == WFMT_FP8_BLOCK128 && scale == nullptr) return PK_ERR_BAD_ARG;
   if (epi == EPI_SWIGLU && ((N & 1) != 0)) return PK_ERR_BAD_ARG;
   if ((ldc & 7) != 0 && epi != EPI_F32) return PK_ERR_BAD_ARG;
+  if (epi == EPI_PUSH && (push == nullptr || (ldc & 3) != 0)) return PK_ERR_BAD_ARG;
   EncodeTiledFn encode = get_encode_fn();
   if (encode == nullptr) return PK_ERR_UNSUPPORTED;
 
@@ -369,6 +389,7 @@ PK_API int pk_gemm_umma(const void* A, int lda, const void* W, const float* scal
   p.resid = (const pk::bf16*)resid;
   p.ldc = ldc;
   p.status = status;
+  if (push) p.push = *push;
 
   const size_t smem = sizeof(SmemLayout) + 1024;
   static bool configured = false;

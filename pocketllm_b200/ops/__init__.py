@@ -79,7 +79,7 @@ def gemm_umma(a: torch.Tensor, w: torch.Tensor, scale: torch.Tensor | None = Non
         status = torch.zeros(1, device=a.device, dtype=torch.int32)
     st = _lib.kernels().pk_gemm_umma(
         _ptr(a), c_int(a.stride(0)), _ptr(w), _ptr(scale), c_int(wfmt), c_int(M), c_int(N), c_int(K), c_int(epi),
-        _ptr(c), _ptr(resid), c_int(ncols), _ptr(status), _stream())
+        _ptr(c), _ptr(resid), c_int(ncols), _ptr(status), c_void_p(0), _stream())
     _check(st, "pk_gemm_umma")
     return c
 

@@ -12,11 +12,15 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _run(world: int, ckpt: Path, port: int) -> dict:
+PROMPT_SHORT = "5,17,300,44,9,1000,2,77,12"
+PROMPT_LONG = ",".join(str((i * 37 + 11) % 1024) for i in range(100))   # 64 + 36 rows: tensor-core prefill
+
+
+def _run(world: int, ckpt: Path, port: int, prompt: str = PROMPT_SHORT) -> dict:
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), "-m", "pocketllm_b200.parallel.tp_check", "--ckpt", str(ckpt), "--prompt",
-           "5,17,300,44,9,1000,2,77,12", "--new", "10"]
+           prompt, "--new", "10"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
     assert r.returncode == 0, r.stderr[-3000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
@@ -32,3 +36,17 @@ def test_tp2_matches_tp1(tmp_path):
     two = _run(2, tmp_path, 29532)
     assert two["ranks_agree"] and two["comm_status"] == [0, 0]
     assert one["tokens"] == two["tokens"]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_tensor_core_prefill_matches_tp1(tmp_path):
+    """The GEMM epilogue pushes partial tiles to the peer; the next norm sums them."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=4, hidden=256, inter=512, vocab=1024)
+    qh.save_checkpoint(tmp_path, cfg, qh.random_checkpoint(cfg, seed=4, sigma=0.05))
+    one = _run(1, tmp_path, 29533, PROMPT_LONG)
+    two = _run(2, tmp_path, 29534, PROMPT_LONG)
+    assert two["ranks_agree"] and two["comm_status"] == [0, 0]
+    # partial sums are added in a different order: allow a late divergence, not an early one
+    same = sum(1 for a, b in zip(one["tokens"], two["tokens"]) if a == b)
+    assert one["tokens"][:3] == two["tokens"][:3] and same >= 6, (one["tokens"], two["tokens"])
