@@ -15,32 +15,7 @@
 
 #include "pk_common.cuh"
 
-#define PK_MAX_RANKS 8
-
-// One collective "site": where a producer pushes and how it signals.
-struct PkPush {
-  float* dst[PK_MAX_RANKS];      // peer r's slot buffer base ([world][rows][cols] fp32)
-  uint32_t* flag[PK_MAX_RANKS];  // peer r's flag array base ([world] words for this slot)
-  uint32_t* block_counter;       // local, zero between launches
-  const uint32_t* epoch;         // local device word, bumped once per forward
-  uint32_t sites_per_epoch;
-  uint32_t site;
-  int world;
-  int rank;
-};
-
-// What a consumer waits on before reading its local slot buffer.
-struct PkWait {
-  const uint32_t* flag;   // local flag array base ([world] words for this slot), or null
-  const uint32_t* epoch;  // local device word
-  uint32_t sites_per_epoch;
-  uint32_t site;
-  int world;
-  uint32_t* status;       // local status word, 0 = ok
-  uint32_t timeout_us;
-};
-
-#define PK_COMM_TIMEOUT 1u
+#include "pk_comm_types.h"
 
 namespace pk {
 

@@ -1,0 +1,265 @@
+// pocket_engine: command-line front end of the native engine, one process per rank.
+//
+// Flag surface and `key=value` result lines follow the reference's dsv4_cpp_engine for its
+// Qwen path (cpp_engine/src/main.cpp:28-68, 407-746): --ckpt, --token-ids(-file),
+// --max-new-tokens, --tp-world/--tp-rank, --device, --nccl-id-path (here: the rendezvous
+// path for the peer-memory handles), --max-context, --prefill-chunk-tokens,
+// --qwen-persistent-stdin, --qwen-attention-window/-sink-tokens, --dump-config, --inspect.
+// Additions: --random-init SEED and --benchmark-27b run without a checkpoint.
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <iostream>
+#include <memory>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "control_plane.hpp"
+#include "json.hpp"
+#include "qwen_config.hpp"
+#include "qwen_engine.hpp"
+#include "safetensors.hpp"
+
+namespace {
+
+struct Args {
+  std::string ckpt, token_ids, token_ids_file, id_path = "/tmp/pocket_engine.rdv";
+  int max_new_tokens = 16, tp_world = 1, tp_rank = 0, device = -1, max_context = 4096, prefill_chunk = 512;
+  int window = 0, sink = 0;
+  long random_seed = -1;
+  bool benchmark_27b = false, dump_config = false, inspect = false, persistent_stdin = false, no_graph = false;
+};
+
+void usage() {
+  std::fprintf(stderr,
+               "usage: pocket_engine --ckpt DIR | --benchmark-27b [--random-init SEED]\n"
+               "  --token-ids 1,2,3 | --token-ids-file F   --max-new-tokens N\n"
+               "  --tp-world N --tp-rank R --device D --nccl-id-path PATH\n"
+               "  --max-context N --prefill-chunk-tokens N --no-cuda-graph\n"
+               "  --qwen-attention-window N --qwen-attention-sink-tokens N\n"
+               "  --qwen-persistent-stdin | --dump-config | --inspect\n");
+}
+
+Args parse(int argc, char** argv) {
+  Args a;
+  auto need = [&](int& i) -> std::string {
+    if (i + 1 >= argc) throw std::runtime_error(std::string("missing value for ") + argv[i]);
+    return argv[++i];
+  };
+  for (int i = 1; i < argc; ++i) {
+    const std::string f = argv[i];
+    if (f == "--ckpt") a.ckpt = need(i);
+    else if (f == "--model") need(i);  // accepted for compatibility; the checkpoint decides
+    else if (f == "--token-ids") a.token_ids = need(i);
+    else if (f == "--token-ids-file") a.token_ids_file = need(i);
+    else if (f == "--max-new-tokens") a.max_new_tokens = std::stoi(need(i));
+    else if (f == "--tp-world") a.tp_world = std::stoi(need(i));
+    else if (f == "--tp-rank") a.tp_rank = std::stoi(need(i));
+    else if (f == "--device") a.device = std::stoi(need(i));
+    else if (f == "--nccl-id-path" || f == "--rendezvous-path") a.id_path = need(i);
+    else if (f == "--max-context") a.max_context = std::stoi(need(i));
+    else if (f == "--prefill-chunk-tokens") a.prefill_chunk = std::stoi(need(i));
+    else if (f == "--qwen-attention-window") a.window = std::stoi(need(i));
+    else if (f == "--qwen-attention-sink-tokens") a.sink = std::stoi(need(i));
+    else if (f == "--random-init") a.random_seed = std::stol(need(i));
+    else if (f == "--benchmark-27b") a.benchmark_27b = true;
+    else if (f == "--dump-config") a.dump_config = true;
+    else if (f == "--inspect") a.inspect = true;
+    else if (f == "--qwen-persistent-stdin") a.persistent_stdin = true;
+    else if (f == "--no-cuda-graph") a.no_graph = true;
+    else if (f == "--help" || f == "-h") { usage(); std::exit(0); }
+    else throw std::runtime_error("unknown flag " + f);
+  }
+  if (a.device < 0) a.device = a.tp_rank;
+  return a;
+}
+
+std::vector<int> parse_ids(const std::string& text) {
+  std::vector<int> out;
+  std::string cur;
+  for (char c : text + ",") {
+    if (c == ',' || c == ' ' || c == '\n' || c == '\t') {
+      if (!cur.empty()) out.push_back(std::stoi(cur));
+      cur.clear();
+    } else {
+      cur.push_back(c);
+    }
+  }
+  return out;
+}
+
+enum Op : int32_t { OP_GENERATE = 1, OP_RESET = 2, OP_SHUTDOWN = 3 };
+
+struct RunResult {
+  std::vector<int> tokens;
+  double prefill_s = 0, decode_s = 0;
+};
+
+RunResult generate(pk::QwenEngine& eng, const std::vector<int>& prompt, int max_new) {
+  RunResult r;
+  eng.reset();
+  const int first = eng.prefill(prompt.data(), (int)prompt.size());
+  r.tokens.push_back(first);
+  r.prefill_s = eng.timings().prefill_ms / 1e3;
+  if (max_new > 1) {
+    std::vector<int> rest(max_new - 1);
+    eng.decode(max_new - 1, rest.data(), false);
+    r.tokens.insert(r.tokens.end(), rest.begin(), rest.end());
+    r.decode_s = eng.timings().decode_ms / 1e3;
+  }
+  return r;
+}
+
+void print_result(const char* tag, const Args& a, const pk::QwenEngine& eng, size_t prompt_len, const RunResult& r) {
+  std::printf("%s=1 tp_world=%d tp_rank=%d prompt_tokens=%zu generated_tokens=%zu prefill_seconds=%.6f "
+              "prefill_tokens_per_s=%.3f decode_seconds=%.6f decode_tokens_per_s=%.3f weight_bytes=%zu generated_token_ids=",
+              tag, a.tp_world, a.tp_rank, prompt_len, r.tokens.size(), r.prefill_s,
+              r.prefill_s > 0 ? prompt_len / r.prefill_s : 0.0, r.decode_s,
+              r.decode_s > 0 ? (r.tokens.size() - 1) / r.decode_s : 0.0, eng.weight_bytes());
+  for (size_t i = 0; i < r.tokens.size(); ++i) std::printf(i ? ",%d" : "%d", r.tokens[i]);
+  std::printf("\n");
+  std::fflush(stdout);
+}
+
+int run(const Args& a) {
+  if (a.inspect) {
+    pk::SafetensorsModel st(a.ckpt);
+    for (const auto& n : st.names()) {
+      const pk::StTensor& t = st.get(n);
+      std::printf("%s dtype=%s shape=[", n.c_str(), pk::st_dtype_name(t.dtype));
+      for (size_t i = 0; i < t.shape.size(); ++i) std::printf(i ? ",%lld" : "%lld", (long long)t.shape[i]);
+      std::printf("] bytes=%zu\n", t.nbytes);
+    }
+    return 0;
+  }
+  pk::QwenConfig cfg = a.benchmark_27b ? pk::QwenConfig::benchmark_27b() : pk::QwenConfig::from_file(a.ckpt + "/config.json");
+  if (a.dump_config) {
+    std::printf("%s\n", cfg.to_json().c_str());
+    return 0;
+  }
+  pk::QwenEngineOptions opt;
+  opt.tp_rank = a.tp_rank;
+  opt.tp_world = a.tp_world;
+  opt.device = a.device;
+  opt.max_context = a.max_context;
+  opt.prefill_chunk = a.prefill_chunk;
+  opt.use_cuda_graph = !a.no_graph;
+  opt.attention_window = a.window;
+  opt.attention_sink = a.sink;
+  pk::QwenEngine eng(cfg, opt);
+  if (a.random_seed >= 0 || a.benchmark_27b) eng.init_random((uint64_t)std::max(0L, a.random_seed), 0.02f);
+  else eng.load_safetensors(a.ckpt);
+
+  std::vector<void*> opened;
+  if (a.tp_world > 1) {
+    // Exchange the arenas' IPC handles through files, then map the peers.
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, eng.comm_arena()) != cudaSuccess) throw std::runtime_error("cudaIpcGetMemHandle failed");
+    std::vector<uint8_t> blob(sizeof h);
+    std::memcpy(blob.data(), &h, sizeof h);
+    auto all = pk::file_rendezvous(a.id_path, a.tp_rank, a.tp_world, blob);
+    std::vector<void*> arenas(a.tp_world, nullptr);
+    for (int r = 0; r < a.tp_world; ++r) {
+      if (r == a.tp_rank) continue;
+      cudaIpcMemHandle_t ph;
+      std::memcpy(&ph, all[r].data(), sizeof ph);
+      if (cudaIpcOpenMemHandle(&arenas[r], ph, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+        throw std::runtime_error("cudaIpcOpenMemHandle failed for rank " + std::to_string(r));
+      opened.push_back(arenas[r]);
+    }
+    eng.set_peer_arenas(arenas.data());
+  }
+  pk::CmdChannel chan(a.id_path + ".cmdsock", a.tp_rank, a.tp_world);
+  if (a.tp_world > 1) pk::file_rendezvous_cleanup(a.id_path, a.tp_rank);
+
+  int rc = 0;
+  if (a.persistent_stdin) {
+    // Rank 0 reads "<max_new_tokens> tok0 tok1 ..." lines ("reset" / "quit" also accepted) and
+    // replays them to the workers; every rank runs the same generate.
+    if (a.tp_rank == 0) {
+      std::string line;
+      while (std::getline(std::cin, line)) {
+        if (line == "quit" || line == "shutdown") break;
+        pk::CmdChannel::Message m;
+        if (line == "reset") {
+          m.op = OP_RESET;
+          chan.broadcast(m);
+          eng.reset();
+          std::printf("qwen_persistent_reset=1\n");
+          std::fflush(stdout);
+          continue;
+        }
+        std::vector<int> nums = parse_ids(line);
+        if (nums.size() < 2) {
+          std::printf("qwen_persistent_error=1 message=expected_max_new_tokens_then_token_ids\n");
+          std::fflush(stdout);
+          continue;
+        }
+        m.op = OP_GENERATE;
+        m.payload.assign(nums.begin(), nums.end());
+        chan.broadcast(m);
+        std::vector<int> prompt(nums.begin() + 1, nums.end());
+        try {
+          RunResult r = generate(eng, prompt, nums[0]);
+          print_result("qwen_persistent_result", a, eng, prompt.size(), r);
+        } catch (const std::exception& e) {
+          std::printf("qwen_persistent_error=1 message=%s\n", e.what());
+          std::fflush(stdout);
+        }
+      }
+      pk::CmdChannel::Message bye;
+      bye.op = OP_SHUTDOWN;
+      chan.broadcast(bye);
+    } else {
+      pk::CmdChannel::Message m;
+      while (chan.receive(m)) {  // blocks in recv(): an idle worker uses no GPU and no CPU
+        if (m.op == OP_SHUTDOWN) break;
+        if (m.op == OP_RESET) { eng.reset(); continue; }
+        if (m.op == OP_GENERATE && m.payload.size() >= 2) {
+          std::vector<int> prompt(m.payload.begin() + 1, m.payload.end());
+          try {
+            generate(eng, prompt, m.payload[0]);
+          } catch (const std::exception& e) {
+            std::fprintf(stderr, "worker %d: %s\n", a.tp_rank, e.what());
+          }
+        }
+      }
+    }
+  } else {
+    std::vector<int> prompt;
+    if (!a.token_ids_file.empty()) {
+      std::ifstream in(a.token_ids_file);
+      std::stringstream ss;
+      ss << in.rdbuf();
+      prompt = parse_ids(ss.str());
+    } else {
+      prompt = parse_ids(a.token_ids);
+    }
+    if (prompt.empty()) throw std::runtime_error("no prompt: give --token-ids or --token-ids-file");
+    RunResult r = generate(eng, prompt, a.max_new_tokens);
+    if (eng.comm_status() != 0) {
+      std::printf("qwen_comm_status=%u\n", eng.comm_status());
+      rc = 3;
+    }
+    print_result("qwen_runtime", a, eng, prompt.size(), r);
+  }
+  for (void* p : opened) cudaIpcCloseMemHandle(p);
+  return rc;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  try {
+    return run(parse(argc, argv));
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "pocket_engine: %s\n", e.what());
+    return 1;
+  }
+}

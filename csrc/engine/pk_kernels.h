@@ -5,7 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include "../common/pk_comm.cuh"
+#include "../common/pk_comm_types.h"
 
 extern "C" {
 

@@ -13,7 +13,7 @@
 #include <string>
 #include <vector>
 
-#include "../common/pk_comm.cuh"
+#include "../common/pk_comm_types.h"
 #include "qwen_config.hpp"
 
 namespace pk {

@@ -106,11 +106,15 @@ def build(verbose: bool = False, jobs: int | None = None) -> dict[str, Path]:
         arts["cpu"] = cpu_so
     if main_src.exists():
         exe = OUT / "pocket_engine"
-        _link([objs[main_src]], exe, False, ["-L" + str(OUT), "-lpocket_engine", "-lpocket_kernels", "-lcudart", "-lpthread", *rpath], verbose)
+        # The engine's C++ classes are not exported from the shared library (only its C ABI
+        # is), so the CLI links the engine objects themselves.
+        _link([objs[main_src]] + [objs[s] for s in engine_srcs], exe, False,
+              ["-L" + str(OUT), "-lpocket_kernels", "-lcudart", "-lpthread", "-ldl", *rpath], verbose)
         arts["cli"] = exe
     for s in tool_srcs:
         exe = OUT / s.stem
-        _link([objs[s]], exe, False, ["-L" + str(OUT), "-lpocket_engine", "-lpocket_kernels", "-lcudart", *rpath], verbose)
+        _link([objs[s]] + [objs[e] for e in engine_srcs], exe, False,
+              ["-L" + str(OUT), "-lpocket_kernels", "-lcudart", "-lpthread", "-ldl", *rpath], verbose)
         arts[s.stem] = exe
     return arts
 
