@@ -1,0 +1,557 @@
+// Linear layers and routed experts on RAW GGUF blocks: the quantised weights stay in their
+// file layout in HBM and are decoded in registers, eight weights per lane, on their way
+// into the FMA. One warp walks one output row (or a gate/up row pair) 256 weights per step.
+//
+//   pk_gguf_linear   y[m, n] = sum_k x[m, k] W[n, k]        (1..8 rows; bf16 / fp32 / SwiGLU out)
+//   pk_gguf_moe_w13  h[route, j] = silu(W1_e x_t) * (W3_e x_t) * route weight
+//   pk_gguf_moe_w2   y[t] += W2_e h[route]                   (fp32 atomics, or per-route partials)
+//
+// Device type ids follow the reference's table (src/loader/gguf/quant_types.py): iq2_xxs 0,
+// q2_k 1, iq1_m 2, q4_k 3, q5_k 4, iq2_xs 5, iq3_xxs 6, iq4_xs 7, q6_k 8, plus q8_0 9 and
+// bf16 10 here. Replaces its DP4A / float kernels (src/csrc/cuda_kernel_impl.cu:6545-6632,
+// 7039-8275: gguf_quant_gemm*, gguf_moe_w13*, gguf_moe_w2*, gguf_moe_single_*).
+#include "../common/pk_common.cuh"
+
+namespace {
+
+using namespace pk;
+
+#include "gguf_codebooks.inc"
+
+enum : int { T_IQ2_XXS = 0, T_Q2_K = 1, T_IQ1_M = 2, T_Q4_K = 3, T_Q5_K = 4, T_IQ2_XS = 5, T_IQ3_XXS = 6,
+             T_IQ4_XS = 7, T_Q6_K = 8, T_Q8_0 = 9, T_BF16 = 10 };
+
+__host__ __device__ constexpr int block_bytes(int t) {
+  return t == T_IQ2_XXS ? 66 : t == T_Q2_K ? 84 : t == T_IQ1_M ? 56 : t == T_Q4_K ? 144 : t == T_Q5_K ? 176
+       : t == T_IQ2_XS ? 74 : t == T_IQ3_XXS ? 98 : t == T_IQ4_XS ? 136 : t == T_Q6_K ? 210 : t == T_Q8_0 ? 272 : 512;
+}
+
+__device__ __forceinline__ float ld_f16(const uint8_t* p) {
+  const uint16_t v = (uint16_t)p[0] | ((uint16_t)p[1] << 8);
+  return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ uint32_t ld_u32(const uint8_t* p) {
+  return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+}
+__device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8); }
+
+__device__ __forceinline__ void k4_scale_min(const uint8_t* s, int j, float& sc, float& mn) {
+  if (j < 4) {
+    sc = (float)(s[j] & 63);
+    mn = (float)(s[j + 4] & 63);
+  } else {
+    sc = (float)((s[j + 4] & 15) | ((s[j - 4] >> 6) << 4));
+    mn = (float)((s[j + 4] >> 4) | ((s[j] >> 6) << 4));
+  }
+}
+
+__device__ const float kIq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+// Weights [8p, 8p + 8) of one 256-weight super block (for q8_0: eight 34-byte blocks).
+template <int TYPE>
+__device__ __forceinline__ void decode8(const uint8_t* b, int p, float (&w)[8]) {
+  if constexpr (TYPE == T_Q8_0) {
+    const uint8_t* blk = b + (p >> 2) * 34;
+    const float d = ld_f16(blk);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = d * (float)(int8_t)blk[2 + (p & 3) * 8 + i];
+  } else if constexpr (TYPE == T_BF16) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __uint_as_float(ld_u16(b + (p * 8 + i) * 2) << 16);
+  } else if constexpr (TYPE == T_Q2_K) {
+    const int g = p >> 1, half = g >> 3, gi = g & 7, shift = (gi >> 1) * 2;
+    const uint8_t* q = b + 16 + half * 32 + (gi & 1) * 16 + (p & 1) * 8;
+    const uint8_t s = b[g];
+    const float d = ld_f16(b + 80) * (float)(s & 15), m = ld_f16(b + 82) * (float)(s >> 4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = d * (float)((q[i] >> shift) & 3) - m;
+  } else if constexpr (TYPE == T_Q4_K || TYPE == T_Q5_K) {
+    const int pr = p >> 3, h = (p >> 2) & 1, l0 = (p & 3) * 8, j = 2 * pr + h;
+    float sc, mn;
+    k4_scale_min(b + 4, j, sc, mn);
+    const float d = ld_f16(b) * sc, m = ld_f16(b + 2) * mn;
+    const uint8_t* q = b + (TYPE == T_Q4_K ? 16 : 48) + pr * 32 + l0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int v = h ? (q[i] >> 4) : (q[i] & 15);
+      if constexpr (TYPE == T_Q5_K) v += ((b[16 + l0 + i] >> j) & 1) << 4;
+      w[i] = d * (float)v - m;
+    }
+  } else if constexpr (TYPE == T_Q6_K) {
+    const int n = p >> 4, idx = (p & 15) * 8, k = idx >> 5, l0 = idx & 31;
+    const uint8_t* ql = b + 64 * n + (k & 1) * 32 + l0;
+    const uint8_t* qh = b + 128 + 32 * n + l0;
+    const float d = ld_f16(b + 208) * (float)(int8_t)b[192 + 8 * n + 2 * k + (l0 >> 4)];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int lo = k < 2 ? (ql[i] & 15) : (ql[i] >> 4);
+      w[i] = d * (float)((lo | (((qh[i] >> (2 * k)) & 3) << 4)) - 32);
+    }
+  } else if constexpr (TYPE == T_IQ2_XXS) {
+    const int sub = p >> 2, part = p & 3;
+    const uint8_t* q = b + 2 + sub * 8;
+    const uint32_t aux = ld_u32(q + 4);
+    const float d = ld_f16(b) * 0.125f * (float)(2 * (aux >> 28) + 1);
+    const uint64_t g = kIq2xxsGrid[q[part]];
+    const uint8_t sg = kKsigns[(aux >> (7 * part)) & 127];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float v = d * (float)((g >> (8 * i)) & 0xff);
+      w[i] = (sg >> i) & 1 ? -v : v;
+    }
+  } else if constexpr (TYPE == T_IQ2_XS) {
+    const int sub = p >> 2, part = p & 3;
+    const uint32_t q = ld_u16(b + 2 + (sub * 4 + part) * 2);
+    const uint32_t nib = (b[66 + sub] >> (4 * (part >> 1))) & 15;
+    const float d = ld_f16(b) * 0.25f * ((float)nib + 0.5f);
+    const uint64_t g = kIq2xsGrid[q & 511];
+    const uint8_t sg = kKsigns[q >> 9];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float v = d * (float)((g >> (8 * i)) & 0xff);
+      w[i] = (sg >> i) & 1 ? -v : v;
+    }
+  } else if constexpr (TYPE == T_IQ3_XXS) {
+    const int sub = p >> 2, pr = p & 3;
+    const uint32_t aux = ld_u32(b + 66 + sub * 4);
+    const float d = ld_f16(b) * 0.5f * ((float)(aux >> 28) + 0.5f);
+    const uint32_t g0 = kIq3xxsGrid[b[2 + sub * 8 + pr * 2]], g1 = kIq3xxsGrid[b[2 + sub * 8 + pr * 2 + 1]];
+    const uint8_t sg = kKsigns[(aux >> (7 * pr)) & 127];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float v0 = d * (float)((g0 >> (8 * i)) & 0xff), v1 = d * (float)((g1 >> (8 * i)) & 0xff);
+      w[i] = (sg >> i) & 1 ? -v0 : v0;
+      w[4 + i] = (sg >> (4 + i)) & 1 ? -v1 : v1;
+    }
+  } else if constexpr (TYPE == T_IQ4_XS) {
+    const int ib = p >> 2, q = p & 3;
+    const uint32_t sh = ld_u16(b + 2);
+    const int ls = ((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 15) | (((sh >> (2 * ib)) & 3) << 4);
+    const float d = ld_f16(b) * (float)(ls - 32);
+    const uint8_t* qs = b + 8 + 16 * ib + 8 * (q & 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = d * kIq4nl[q < 2 ? (qs[i] & 15) : (qs[i] >> 4)];
+  } else if constexpr (TYPE == T_IQ1_M) {
+    const int ib = p >> 2, g = p & 3;
+    const uint32_t s0 = ld_u16(b + 48), s1 = ld_u16(b + 50), s2 = ld_u16(b + 52), s3 = ld_u16(b + 54);
+    const uint16_t dbits = (uint16_t)((s0 >> 12) | ((s1 >> 8) & 0xf0) | ((s2 >> 4) & 0xf00) | (s3 & 0xf000));
+    const uint32_t sw = ld_u16(b + 48 + (ib >> 1) * 2) >> (6 * (ib & 1));
+    const float dl = __half2float(__ushort_as_half(dbits)) * (float)(2 * ((sw >> (3 * (g >> 1))) & 7) + 1);
+    const uint32_t h = b[32 + 2 * ib + (g >> 1)];
+    const uint32_t idx = b[4 * ib + g] | (((g & 1) ? (h << 4) : (h << 8)) & 0x700);
+    const float delta = (h & ((g & 1) ? 0x80 : 0x08)) ? -0.125f : 0.125f;
+    const uint64_t gr = kIq1Grid[idx];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = dl * ((float)(int8_t)((gr >> (8 * i)) & 0xff) + delta);
+  }
+}
+
+constexpr int kThreads = 256;
+constexpr int kWarps = 8;
+
+// One warp: dot products of one raw row with M staged activation rows (fp32, [M][K]).
+template <int TYPE, int M>
+__device__ __forceinline__ void row_dot(const uint8_t* wrow, const float* xs, int K, int lane, float (&acc)[M]) {
+  constexpr int BB = block_bytes(TYPE);
+  const int nblk = K >> 8;
+  for (int blk = 0; blk < nblk; ++blk) {
+    float w[8];
+    decode8<TYPE>(wrow + (size_t)blk * BB, lane, w);
+    const int k = (blk << 8) + (lane << 3);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const float4 a = *reinterpret_cast<const float4*>(xs + m * K + k);
+      const float4 c = *reinterpret_cast<const float4*>(xs + m * K + k + 4);
+      acc[m] += w[0] * a.x + w[1] * a.y + w[2] * a.z + w[3] * a.w + w[4] * c.x + w[5] * c.y + w[6] * c.z + w[7] * c.w;
+    }
+  }
+}
+
+struct LinearParams {
+  const uint8_t* W;   // [N, K/256 blocks]
+  int type, N, K, M;
+  const bf16* x;      // [M, K]
+  const float* gamma; // optional fused RMSNorm (plain gamma)
+  float eps;
+  int epi;            // 0 bf16, 1 swiglu (rows j and j + N/2), 2 fp32
+  void* y;
+  int ldy;
+};
+
+template <int M>
+__device__ __forceinline__ void dispatch_row(int type, const uint8_t* wrow, const float* xs, int K, int lane, float (&acc)[M]) {
+  switch (type) {
+    case T_IQ2_XXS: row_dot<T_IQ2_XXS, M>(wrow, xs, K, lane, acc); break;
+    case T_Q2_K: row_dot<T_Q2_K, M>(wrow, xs, K, lane, acc); break;
+    case T_IQ1_M: row_dot<T_IQ1_M, M>(wrow, xs, K, lane, acc); break;
+    case T_Q4_K: row_dot<T_Q4_K, M>(wrow, xs, K, lane, acc); break;
+    case T_Q5_K: row_dot<T_Q5_K, M>(wrow, xs, K, lane, acc); break;
+    case T_IQ2_XS: row_dot<T_IQ2_XS, M>(wrow, xs, K, lane, acc); break;
+    case T_IQ3_XXS: row_dot<T_IQ3_XXS, M>(wrow, xs, K, lane, acc); break;
+    case T_IQ4_XS: row_dot<T_IQ4_XS, M>(wrow, xs, K, lane, acc); break;
+    case T_Q6_K: row_dot<T_Q6_K, M>(wrow, xs, K, lane, acc); break;
+    case T_Q8_0: row_dot<T_Q8_0, M>(wrow, xs, K, lane, acc); break;
+    default: row_dot<T_BF16, M>(wrow, xs, K, lane, acc); break;
+  }
+}
+
+__host__ __device__ inline size_t row_bytes(int type, int K) { return (size_t)(K >> 8) * block_bytes(type); }
+
+template <int M>
+__global__ void __launch_bounds__(kThreads) gguf_linear_kernel(const LinearParams p) {
+  extern __shared__ __align__(16) float xs[];  // [M][K]
+  __shared__ float red[40];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int m = 0; m < M; ++m) {
+    float ss = 0.f;
+    for (int k = tid; k < p.K; k += kThreads) {
+      const float v = __bfloat162float(p.x[(size_t)m * p.K + k]);
+      xs[m * p.K + k] = v;
+      ss += v * v;
+    }
+    if (p.gamma != nullptr) {
+      ss = block_sum(ss, red);
+      const float rs = rsqrtf(ss / (float)p.K + p.eps);
+      for (int k = tid; k < p.K; k += kThreads)
+        xs[m * p.K + k] = __bfloat162float(__float2bfloat16(xs[m * p.K + k] * rs * p.gamma[k]));
+    }
+  }
+  __syncthreads();
+  const size_t rb = row_bytes(p.type, p.K);
+  const int half_n = p.N >> 1;
+  const int groups = p.epi == 1 ? half_n : p.N;
+  for (int g = blockIdx.x * kWarps + warp; g < groups; g += gridDim.x * kWarps) {
+    float a0[M], a1[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) { a0[m] = 0.f; a1[m] = 0.f; }
+    dispatch_row<M>(p.type, p.W + (size_t)g * rb, xs, p.K, lane, a0);
+    if (p.epi == 1) dispatch_row<M>(p.type, p.W + (size_t)(g + half_n) * rb, xs, p.K, lane, a1);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      a0[m] = warp_sum(a0[m]);
+      if (p.epi == 1) a1[m] = warp_sum(a1[m]);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        if (p.epi == 1) ((bf16*)p.y)[(size_t)m * p.ldy + g] = __float2bfloat16(silu(a0[m]) * a1[m]);
+        else if (p.epi == 0) ((bf16*)p.y)[(size_t)m * p.ldy + g] = __float2bfloat16(a0[m]);
+        else ((float*)p.y)[(size_t)m * p.ldy + g] = a0[m];
+      }
+    }
+  }
+}
+
+// ---- routed experts ----
+// Routes are sorted by expert: seg_start[e] .. seg_start[e+1] index into route_token / route_weight.
+struct MoeParams {
+  const uint8_t* W13;  // [E, 2I, H] raw rows (gate rows then up rows per expert)
+  const uint8_t* W2;   // [E, H, I]
+  int type13, type2;
+  int E, H, I;
+  const bf16* x;        // [T, H]
+  const int* seg_start; // [E + 1]
+  const int* route_token;   // [R]
+  const float* route_weight; // [R]
+  float* hbuf;          // [R, I] fp32 hidden of every route (already times the route weight)
+  float* y;             // [T, H] fp32, accumulated with atomics
+  float limit;          // SwiGLU clamp, 0 = off
+  int expert_offset;    // first expert id stored in W13 / W2 (expert parallel shard)
+  int local_experts;
+};
+
+// grid: (row tiles, local experts). Each block stages up to 8 routed tokens of its expert at a
+// time and lets its warps walk gate/up row pairs.
+__global__ void __launch_bounds__(kThreads) gguf_moe_w13_kernel(const MoeParams p) {
+  extern __shared__ __align__(16) float xs[];  // [8][H]
+  const int le = blockIdx.y, e = le + p.expert_offset;
+  const int r0 = p.seg_start[e], r1 = p.seg_start[e + 1];
+  if (r0 >= r1) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t rb = row_bytes(p.type13, p.H);
+  const uint8_t* base = p.W13 + (size_t)le * 2 * p.I * rb;
+  for (int rs = r0; rs < r1; rs += 8) {
+    const int cnt = min(8, r1 - rs);
+    __syncthreads();
+    for (int m = 0; m < 8; ++m)
+      for (int k = tid; k < p.H; k += kThreads)
+        xs[m * p.H + k] = m < cnt ? __bfloat162float(p.x[(size_t)p.route_token[rs + m] * p.H + k]) : 0.f;
+    __syncthreads();
+    for (int j = blockIdx.x * kWarps + warp; j < p.I; j += gridDim.x * kWarps) {
+      float g[8], u[8];
+#pragma unroll
+      for (int m = 0; m < 8; ++m) { g[m] = 0.f; u[m] = 0.f; }
+      dispatch_row<8>(p.type13, base + (size_t)j * rb, xs, p.H, lane, g);
+      dispatch_row<8>(p.type13, base + (size_t)(p.I + j) * rb, xs, p.H, lane, u);
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        float gv = warp_sum(g[m]), uv = warp_sum(u[m]);
+        if (p.limit > 0.f) {
+          gv = fminf(gv, p.limit);
+          uv = fminf(fmaxf(uv, -p.limit), p.limit);
+        }
+        if (lane == 0 && m < cnt) p.hbuf[(size_t)(rs + m) * p.I + j] = silu(gv) * uv * p.route_weight[rs + m];
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) gguf_moe_w2_kernel(const MoeParams p) {
+  extern __shared__ __align__(16) float hs[];  // [8][I]
+  const int le = blockIdx.y, e = le + p.expert_offset;
+  const int r0 = p.seg_start[e], r1 = p.seg_start[e + 1];
+  if (r0 >= r1) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t rb = row_bytes(p.type2, p.I);
+  const uint8_t* base = p.W2 + (size_t)le * p.H * rb;
+  for (int rs = r0; rs < r1; rs += 8) {
+    const int cnt = min(8, r1 - rs);
+    __syncthreads();
+    for (int m = 0; m < 8; ++m)
+      for (int k = tid; k < p.I; k += kThreads) hs[m * p.I + k] = m < cnt ? p.hbuf[(size_t)(rs + m) * p.I + k] : 0.f;
+    __syncthreads();
+    for (int n = blockIdx.x * kWarps + warp; n < p.H; n += gridDim.x * kWarps) {
+      float a[8];
+#pragma unroll
+      for (int m = 0; m < 8; ++m) a[m] = 0.f;
+      dispatch_row<8>(p.type2, base + (size_t)n * rb, hs, p.I, lane, a);
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        const float v = warp_sum(a[m]);
+        if (lane == 0 && m < cnt) atomicAdd(p.y + (size_t)p.route_token[rs + m] * p.H + n, v);
+      }
+    }
+  }
+}
+
+// ---- routing ----
+// One block per token: scores over E experts, top-k with lowest-id tie break.
+// score_func 0 softmax, 1 sigmoid, 2 sqrt(softplus); selection on score + bias.
+__global__ void __launch_bounds__(256) router_topk_kernel(const bf16* x, const float* rw, const float* bias, int H, int E,
+                                                          int topk, int score_func, int norm_topk, float route_scale,
+                                                          int* ids, float* weights) {
+  extern __shared__ float sm[];  // [H] activations, [E] scores, [E] selection keys
+  float* xs = sm;
+  float* sc = sm + H;
+  float* key = sc + E;
+  __shared__ float red[40];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int k = tid; k < H; k += 256) xs[k] = __bfloat162float(x[(size_t)t * H + k]);
+  __syncthreads();
+  for (int e = warp; e < E; e += 8) {
+    float a = 0.f;
+    for (int k = lane; k < H; k += 32) a = fmaf(rw[(size_t)e * H + k], xs[k], a);
+    a = warp_sum(a);
+    if (lane == 0) sc[e] = a;
+  }
+  __syncthreads();
+  if (score_func == 0) {
+    float mx = -INFINITY;
+    for (int e = tid; e < E; e += 256) mx = fmaxf(mx, sc[e]);
+    mx = block_max(mx, red);
+    float s = 0.f;
+    for (int e = tid; e < E; e += 256) {
+      sc[e] = __expf(sc[e] - mx);
+      s += sc[e];
+    }
+    s = block_sum(s, red);
+    for (int e = tid; e < E; e += 256) sc[e] /= s;
+  } else {
+    for (int e = tid; e < E; e += 256) sc[e] = score_func == 1 ? sigmoidf_(sc[e]) : sqrtf(softplusf_(sc[e]));
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += 256) key[e] = sc[e] + (bias ? bias[e] : 0.f);
+  __syncthreads();
+  if (warp == 0) {
+    float wsum = 0.f;
+    for (int j = 0; j < topk; ++j) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int e = lane; e < E; e += 32)
+        if (key[e] > bv) { bv = key[e]; bi = e; }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (lane == 0) {
+        ids[(size_t)t * topk + j] = bi;
+        weights[(size_t)t * topk + j] = sc[bi];
+        key[bi] = -INFINITY;
+      }
+      wsum += sc[bi];
+      __syncwarp();
+    }
+    if (lane < topk) {
+      float w = weights[(size_t)t * topk + lane];
+      if (norm_topk) w /= (wsum > 0.f ? wsum : 1.f);
+      weights[(size_t)t * topk + lane] = w * route_scale;
+    }
+  }
+}
+
+// Group routes by expert (single block; T * topk routes): counts, exclusive scan, fill in
+// token order so that the layout is deterministic.
+__global__ void __launch_bounds__(256) group_routes_kernel(const int* ids, const float* weights, int T, int topk, int E,
+                                                           int* seg_start, int* route_token, float* route_weight,
+                                                           int* route_src) {
+  extern __shared__ int cnt[];  // [E + 1]
+  const int tid = threadIdx.x, R = T * topk;
+  for (int e = tid; e <= E; e += 256) cnt[e] = 0;
+  __syncthreads();
+  for (int r = tid; r < R; r += 256) atomicAdd(&cnt[ids[r]], 1);
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = cnt[e];
+      cnt[e] = run;
+      seg_start[e] = run;
+      run += c;
+    }
+    cnt[E] = run;
+    seg_start[E] = run;
+  }
+  __syncthreads();
+  // deterministic fill: expert e's routes in increasing route index
+  for (int e = tid; e < E; e += 256) {
+    int pos = cnt[e];
+    for (int r = 0; r < R; ++r)
+      if (ids[r] == e) {
+        route_token[pos] = r / topk;
+        route_weight[pos] = weights[r];
+        if (route_src) route_src[pos] = r;
+        ++pos;
+      }
+  }
+}
+
+// Quantised embedding: decode selected rows to bf16 (one warp per 256 weights).
+__global__ void __launch_bounds__(256) gguf_dequant_rows_kernel(const uint8_t* W, int type, const int* rows, int nrows,
+                                                                int K, int row_offset, int table_rows, bf16* out) {
+  const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int src = (rows ? rows[r] : r) - row_offset;
+  const bool mine = src >= 0 && src < table_rows;
+  const size_t rb = row_bytes(type, K);
+  for (int blk = warp; blk < (K >> 8); blk += 8) {
+    float w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = 0.f;
+    if (mine) {
+      const uint8_t* b = W + (size_t)src * rb + (size_t)blk * block_bytes(type);
+      switch (type) {
+        case T_IQ2_XXS: decode8<T_IQ2_XXS>(b, lane, w); break;
+        case T_Q2_K: decode8<T_Q2_K>(b, lane, w); break;
+        case T_IQ1_M: decode8<T_IQ1_M>(b, lane, w); break;
+        case T_Q4_K: decode8<T_Q4_K>(b, lane, w); break;
+        case T_Q5_K: decode8<T_Q5_K>(b, lane, w); break;
+        case T_IQ2_XS: decode8<T_IQ2_XS>(b, lane, w); break;
+        case T_IQ3_XXS: decode8<T_IQ3_XXS>(b, lane, w); break;
+        case T_IQ4_XS: decode8<T_IQ4_XS>(b, lane, w); break;
+        case T_Q6_K: decode8<T_Q6_K>(b, lane, w); break;
+        case T_Q8_0: decode8<T_Q8_0>(b, lane, w); break;
+        default: decode8<T_BF16>(b, lane, w); break;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[(size_t)r * K + (blk << 8) + (lane << 3) + i] = __float2bfloat16(w[i]);
+  }
+}
+
+template <int M>
+int launch_linear(const LinearParams& p, int sm_count, cudaStream_t stream) {
+  const size_t smem = (size_t)M * p.K * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    if (cudaFuncSetAttribute(gguf_linear_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+      pk_set_last_cuda_error((int)cudaGetLastError());
+      return PK_ERR_CUDA;
+    }
+    configured = 200 * 1024;
+  }
+  const int groups = p.epi == 1 ? p.N / 2 : p.N;
+  int blocks = (groups + kWarps - 1) / kWarps;
+  blocks = min(blocks, (sm_count > 0 ? sm_count : 148) * 4);
+  gguf_linear_kernel<M><<<blocks, kThreads, smem, stream>>>(p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+}  // namespace
+
+PK_API int pk_gguf_block_bytes(int type) { return (type >= 0 && type <= T_BF16) ? block_bytes(type) : 0; }
+
+// x bf16 [M, K] (M <= 8, M * K * 4 bytes <= 200 KB), W raw rows, K a multiple of 256.
+PK_API int pk_gguf_linear(const void* W, int type, int N, int K, int M, const void* x, const float* gamma, float eps,
+                          int epi, void* y, int ldy, int sm_count, cudaStream_t stream) {
+  if (type < 0 || type > T_BF16 || M < 1 || M > 8 || (K & 255) != 0 || N < 1) return PK_ERR_BAD_ARG;
+  if ((size_t)M * K * 4 > 200 * 1024) return PK_ERR_UNSUPPORTED;
+  if (epi == 1 && (N & 1)) return PK_ERR_BAD_ARG;
+  LinearParams p{(const uint8_t*)W, type, N, K, M, (const pk::bf16*)x, gamma, eps, epi, y, ldy};
+  switch (M) {
+    case 1: return launch_linear<1>(p, sm_count, stream);
+    case 2: return launch_linear<2>(p, sm_count, stream);
+    case 3: case 4: p.M = M; return launch_linear<4>(p, sm_count, stream);
+    default: return launch_linear<8>(p, sm_count, stream);
+  }
+}
+
+PK_API int pk_router_topk(const void* x, const float* router_w, const float* bias, int T, int H, int E, int topk,
+                          int score_func, int norm_topk, float route_scale, int* ids, float* weights,
+                          cudaStream_t stream) {
+  if (T < 1 || topk < 1 || topk > 32 || topk > E) return PK_ERR_BAD_ARG;
+  const size_t smem = (size_t)(H + 2 * E) * sizeof(float);
+  if (smem > 48 * 1024) return PK_ERR_UNSUPPORTED;
+  router_topk_kernel<<<T, 256, smem, stream>>>((const pk::bf16*)x, router_w, bias, H, E, topk, score_func, norm_topk,
+                                               route_scale, ids, weights);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+PK_API int pk_group_routes(const int* ids, const float* weights, int T, int topk, int E, int* seg_start, int* route_token,
+                           float* route_weight, int* route_src, cudaStream_t stream) {
+  if (E + 1 > 12000) return PK_ERR_UNSUPPORTED;
+  group_routes_kernel<<<1, 256, (size_t)(E + 1) * sizeof(int), stream>>>(ids, weights, T, topk, E, seg_start, route_token,
+                                                                         route_weight, route_src);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+// Routed experts of one rank: experts [expert_offset, expert_offset + local_experts) live in
+// W13 / W2. y (fp32 [T, H]) must be zeroed by the caller; hbuf holds R * I floats.
+PK_API int pk_gguf_moe_forward(const void* W13, const void* W2, int type13, int type2, int E, int H, int I,
+                               const void* x, const int* seg_start, const int* route_token, const float* route_weight,
+                               float* hbuf, float* y, float limit, int expert_offset, int local_experts, int sm_count,
+                               cudaStream_t stream) {
+  if ((H & 255) || (I & 255) || local_experts < 1) return PK_ERR_BAD_ARG;
+  if ((size_t)8 * H * 4 > 200 * 1024 || (size_t)8 * I * 4 > 200 * 1024) return PK_ERR_UNSUPPORTED;
+  MoeParams p{(const uint8_t*)W13, (const uint8_t*)W2, type13, type2, E, H, I, (const pk::bf16*)x, seg_start, route_token,
+              route_weight, hbuf, y, limit, expert_offset, local_experts};
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gguf_moe_w13_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gguf_moe_w2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+      pk_set_last_cuda_error((int)cudaGetLastError());
+      return PK_ERR_CUDA;
+    }
+    configured = true;
+  }
+  const int tiles13 = min((I + kWarps - 1) / kWarps, 32), tiles2 = min((H + kWarps - 1) / kWarps, 32);
+  (void)sm_count;
+  gguf_moe_w13_kernel<<<dim3(tiles13, local_experts), kThreads, (size_t)8 * H * 4, stream>>>(p);
+  PK_CHECK_LAUNCH();
+  gguf_moe_w2_kernel<<<dim3(tiles2, local_experts), kThreads, (size_t)8 * I * 4, stream>>>(p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+// out[r, :] = dequant(W[rows[r] - row_offset, :]) as bf16; rows outside the local table give zeros
+// (vocabulary-sharded embedding). rows == null means rows 0..nrows-1.
+PK_API int pk_gguf_dequant_rows(const void* W, int type, const int* rows, int nrows, int K, int row_offset,
+                                int table_rows, void* out, cudaStream_t stream) {
+  if (type < 0 || type > T_BF16 || (K & 255) != 0 || nrows < 1) return PK_ERR_BAD_ARG;
+  gguf_dequant_rows_kernel<<<nrows, 256, 0, stream>>>((const uint8_t*)W, type, rows, nrows, K, row_offset, table_rows,
+                                                     (pk::bf16*)out);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}

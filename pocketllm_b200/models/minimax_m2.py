@@ -1,0 +1,276 @@
+"""MiniMax-M2 on raw GGUF blocks: GQA attention + sigmoid top-k routed MoE, no shared expert.
+
+Numerical contract (reference: src/models/minimax_m2/architecture.py:57-472): plain-gamma
+RMSNorm; q/k norms over the whole projected vector; half-split RoPE on the first
+`rope_dim` dims; softmax scale 1/sqrt(head_dim); router p = sigmoid(x W^T), top-k of p + bias,
+weights p normalised to sum 1; experts are SwiGLU. Attention weights are Q5_K, embedding and
+output Q4_K, experts IQ2_XXS (other mixes: Q2_K, IQ1_M).
+
+Execution here: every projection and expert runs on the raw blocks (`ops.gguf_ops`), the
+attention core on the split-context GQA kernel, experts are partitioned over ranks
+(contiguous ranges) and the per-token outputs are summed across ranks.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..formats import gguf, gguf_quants as gq
+
+ARCH = "minimax-m2"
+
+
+@dataclass
+class MiniMaxM2Config:
+    vocab_size: int = 200064
+    dim: int = 3072
+    n_layers: int = 62
+    n_heads: int = 48
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    rope_dim: int = 64
+    rope_theta: float = 5.0e6
+    n_experts: int = 256
+    n_experts_used: int = 8
+    expert_inter: int = 1536
+    norm_eps: float = 1e-6
+    attn_type: str = "q5_k"
+    embed_type: str = "q4_k"
+    expert_type: str = "iq2_xxs"
+    expert_down_type: str = "iq2_xxs"
+
+    @classmethod
+    def from_gguf(cls, md: dict) -> "MiniMaxM2Config":
+        p = ARCH + "."
+        return cls(vocab_size=int(md.get(p + "vocab_size", len(md.get("tokenizer.ggml.tokens", [])) or 200064)),
+                   dim=int(md[p + "embedding_length"]), n_layers=int(md[p + "block_count"]),
+                   n_heads=int(md[p + "attention.head_count"]), n_kv_heads=int(md[p + "attention.head_count_kv"]),
+                   head_dim=int(md.get(p + "attention.key_length", 128)), rope_dim=int(md.get(p + "rope.dimension_count", 64)),
+                   rope_theta=float(md.get(p + "rope.freq_base", 5e6)), n_experts=int(md[p + "expert_count"]),
+                   n_experts_used=int(md[p + "expert_used_count"]), expert_inter=int(md[p + "expert_feed_forward_length"]),
+                   norm_eps=float(md.get(p + "attention.layer_norm_rms_epsilon", 1e-6)))
+
+    @classmethod
+    def tiny(cls) -> "MiniMaxM2Config":
+        return cls(vocab_size=512, dim=256, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=128, rope_dim=64, n_experts=8,
+                   n_experts_used=2, expert_inter=256)
+
+    def metadata(self) -> dict:
+        p = ARCH + "."
+        return {"general.architecture": ARCH, p + "vocab_size": self.vocab_size, p + "embedding_length": self.dim,
+                p + "block_count": self.n_layers, p + "attention.head_count": self.n_heads,
+                p + "attention.head_count_kv": self.n_kv_heads, p + "attention.key_length": self.head_dim,
+                p + "rope.dimension_count": self.rope_dim, p + "rope.freq_base": float(self.rope_theta),
+                p + "expert_count": self.n_experts, p + "expert_used_count": self.n_experts_used,
+                p + "expert_feed_forward_length": self.expert_inter, p + "attention.layer_norm_rms_epsilon": float(self.norm_eps)}
+
+
+def tensor_plan(cfg: MiniMaxM2Config) -> list[tuple[str, tuple[int, ...], str]]:
+    """(name, logical shape, ggml type) of every tensor of the checkpoint."""
+    H, D = cfg.dim, cfg.head_dim
+    out = [("token_embd.weight", (cfg.vocab_size, H), cfg.embed_type), ("output_norm.weight", (H,), "f32"),
+           ("output.weight", (cfg.vocab_size, H), cfg.embed_type)]
+    for i in range(cfg.n_layers):
+        b = f"blk.{i}."
+        out += [(b + "attn_norm.weight", (H,), "f32"), (b + "ffn_norm.weight", (H,), "f32"),
+                (b + "attn_q.weight", (cfg.n_heads * D, H), cfg.attn_type), (b + "attn_k.weight", (cfg.n_kv_heads * D, H), cfg.attn_type),
+                (b + "attn_v.weight", (cfg.n_kv_heads * D, H), cfg.attn_type), (b + "attn_output.weight", (H, cfg.n_heads * D), cfg.attn_type),
+                (b + "attn_q_norm.weight", (cfg.n_heads * D,), "f32"), (b + "attn_k_norm.weight", (cfg.n_kv_heads * D,), "f32"),
+                (b + "ffn_gate_inp.weight", (cfg.n_experts, H), "f32"), (b + "exp_probs_b.bias", (cfg.n_experts,), "f32"),
+                (b + "ffn_gate_exps.weight", (cfg.n_experts, cfg.expert_inter, H), cfg.expert_type),
+                (b + "ffn_up_exps.weight", (cfg.n_experts, cfg.expert_inter, H), cfg.expert_type),
+                (b + "ffn_down_exps.weight", (cfg.n_experts, H, cfg.expert_inter), cfg.expert_down_type)]
+    return out
+
+
+def write_random_gguf(path: str | Path, cfg: MiniMaxM2Config, seed: int = 0, sigma: float = 0.02) -> None:
+    """Random-init checkpoint with real block payloads (N(0, sigma) through the quantisers)."""
+    rng = np.random.default_rng(seed)
+    w = gguf.GGUFWriter()
+    for k, v in cfg.metadata().items():
+        w.add_meta(k, v)
+    for name, shape, typ in tensor_plan(cfg):
+        if typ == "f32":
+            if name.endswith("norm.weight"):
+                data = (1.0 + 0.05 * rng.standard_normal(shape)).astype(np.float32)
+            else:
+                data = (sigma * rng.standard_normal(shape)).astype(np.float32)
+            w.add_tensor(name, data, "f32", shape)
+        else:
+            x = (sigma * rng.standard_normal(shape)).astype(np.float32)
+            w.add_tensor(name, gq.quantize(x, typ), typ, shape)
+    w.write(path)
+
+
+def _rope(x: torch.Tensor, pos: torch.Tensor, rope_dim: int, theta: float) -> torch.Tensor:
+    """Half-split rotation of the first rope_dim dims. x [T, heads, D], pos [T]."""
+    half = rope_dim // 2
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rope_dim)
+    ang = pos.double()[:, None] * inv[None, :]
+    cs, sn = torch.cos(ang).float().to(x.device)[:, None, :], torch.sin(ang).float().to(x.device)[:, None, :]
+    x1, x2 = x[..., :half], x[..., half:rope_dim]
+    return torch.cat([x1 * cs - x2 * sn, x2 * cs + x1 * sn, x[..., rope_dim:]], dim=-1)
+
+
+def _rms(x: torch.Tensor, g: torch.Tensor, eps: float) -> torch.Tensor:
+    return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * g
+
+
+class ReferenceModel:
+    """fp32 PyTorch oracle on dequantised weights (CPU, tiny shapes)."""
+
+    def __init__(self, path: str | Path):
+        self.bundle = gguf.GGUFBundle(path)
+        self.cfg = MiniMaxM2Config.from_gguf(self.bundle.metadata)
+        self.w = {n: torch.from_numpy(gq.dequantize(self.bundle.blocks(n) if t.type_name not in ("f32",) else self.bundle.raw(n),
+                                                    t.type_name).reshape(t.shape).copy())
+                  for n, t in self.bundle.tensors.items()}
+        self.k: list[list[torch.Tensor]] = [[] for _ in range(self.cfg.n_layers)]
+        self.v: list[list[torch.Tensor]] = [[] for _ in range(self.cfg.n_layers)]
+        self.pos = 0
+
+    def forward(self, tokens: Sequence[int]) -> torch.Tensor:
+        c, w = self.cfg, self.w
+        T = len(tokens)
+        r16 = lambda t: t.to(torch.bfloat16).float()
+        pos = torch.arange(self.pos, self.pos + T)
+        h = r16(w["token_embd.weight"][list(tokens)])
+        for i in range(c.n_layers):
+            b = f"blk.{i}."
+            x = r16(_rms(h, w[b + "attn_norm.weight"], c.norm_eps))
+            q, k, v = r16(x @ w[b + "attn_q.weight"].t()), r16(x @ w[b + "attn_k.weight"].t()), r16(x @ w[b + "attn_v.weight"].t())
+            q = _rms(q, w[b + "attn_q_norm.weight"], c.norm_eps).view(T, c.n_heads, c.head_dim)
+            k = _rms(k, w[b + "attn_k_norm.weight"], c.norm_eps).view(T, c.n_kv_heads, c.head_dim)
+            q, k = r16(_rope(q, pos, c.rope_dim, c.rope_theta)), r16(_rope(k, pos, c.rope_dim, c.rope_theta))
+            self.k[i].append(k)
+            self.v[i].append(v.view(T, c.n_kv_heads, c.head_dim))
+            K, V = torch.cat(self.k[i]), torch.cat(self.v[i])
+            rep = c.n_heads // c.n_kv_heads
+            K, V = K.repeat_interleave(rep, 1), V.repeat_interleave(rep, 1)
+            s = torch.einsum("thd,shd->hts", q, K) * c.head_dim ** -0.5
+            mask = torch.arange(K.shape[0])[None, :] > pos[:, None]
+            s = s.masked_fill(mask[None], float("-inf"))
+            o = r16(torch.einsum("hts,shd->thd", torch.softmax(s, -1), V).reshape(T, -1))
+            h = r16(h + o @ w[b + "attn_output.weight"].t())
+            x = r16(_rms(h, w[b + "ffn_norm.weight"], c.norm_eps))
+            p = torch.sigmoid(x @ w[b + "ffn_gate_inp.weight"].t())
+            ids = torch.topk(p + w[b + "exp_probs_b.bias"], c.n_experts_used, dim=-1).indices
+            wt = torch.gather(p, 1, ids)
+            wt = wt / wt.sum(-1, keepdim=True)
+            y = torch.zeros_like(h)
+            for t in range(T):
+                for j in range(c.n_experts_used):
+                    e = int(ids[t, j])
+                    g, u = w[b + "ffn_gate_exps.weight"][e] @ x[t], w[b + "ffn_up_exps.weight"][e] @ x[t]
+                    y[t] += wt[t, j] * (w[b + "ffn_down_exps.weight"][e] @ (torch.nn.functional.silu(g) * u))
+            h = r16(h + y)
+        self.pos += T
+        x = r16(_rms(h, w["output_norm.weight"], c.norm_eps))
+        return x @ w["output.weight"].t()
+
+
+class MiniMaxM2Model:
+    """GPU runtime on raw blocks. `expert range` of rank r: [r * E/W, (r+1) * E/W)."""
+
+    def __init__(self, path: str | Path, *, device: str = "cuda", rank: int = 0, world: int = 1, max_context: int = 4096,
+                 layers: int | None = None, group=None):
+        from ..ops import gguf_ops as go
+        self.go = go
+        self.bundle = gguf.GGUFBundle(path)
+        if self.bundle.architecture() != ARCH:
+            raise ValueError(f"not a {ARCH} checkpoint: {self.bundle.architecture()!r}")
+        self.cfg = c = MiniMaxM2Config.from_gguf(self.bundle.metadata)
+        if layers:
+            c.n_layers = min(c.n_layers, layers)
+        if c.n_experts % world:
+            raise ValueError("expert count must divide by the world size")
+        self.device, self.rank, self.world, self.group = torch.device(device), rank, world, group
+        self.e_local = c.n_experts // world
+        self.e_start = rank * self.e_local
+        self.types = {n: t.type_name for n, t in self.bundle.tensors.items()}
+
+        def raw(name: str, lo: int | None = None, hi: int | None = None) -> torch.Tensor:
+            b = self.bundle.blocks(name)
+            if lo is not None:
+                b = b[lo:hi]
+            return torch.from_numpy(np.ascontiguousarray(b).reshape(-1)).to(self.device)
+
+        def f32(name: str) -> torch.Tensor:
+            return torch.from_numpy(self.bundle.raw(name).view(np.float32).copy()).to(self.device)
+
+        self.embed, self.head = raw("token_embd.weight"), raw("output.weight")
+        self.final_norm = f32("output_norm.weight")
+        self.layers = []
+        for i in range(c.n_layers):
+            b = f"blk.{i}."
+            L = {"attn_norm": f32(b + "attn_norm.weight"), "ffn_norm": f32(b + "ffn_norm.weight"),
+                 "q": raw(b + "attn_q.weight"), "k": raw(b + "attn_k.weight"), "v": raw(b + "attn_v.weight"),
+                 "o": raw(b + "attn_output.weight"), "q_norm": f32(b + "attn_q_norm.weight"), "k_norm": f32(b + "attn_k_norm.weight"),
+                 "router": f32(b + "ffn_gate_inp.weight").view(c.n_experts, c.dim), "bias": f32(b + "exp_probs_b.bias"),
+                 # gate rows then up rows per expert, this rank's experts only
+                 "w13": torch.cat([raw(b + "ffn_gate_exps.weight", self.e_start, self.e_start + self.e_local).view(self.e_local, -1),
+                                   raw(b + "ffn_up_exps.weight", self.e_start, self.e_start + self.e_local).view(self.e_local, -1)], dim=1).contiguous(),
+                 "w2": raw(b + "ffn_down_exps.weight", self.e_start, self.e_start + self.e_local),
+                 "kc": torch.zeros(c.n_kv_heads, max_context, c.head_dim, device=self.device, dtype=torch.bfloat16),
+                 "vc": torch.zeros(c.n_kv_heads, max_context, c.head_dim, device=self.device, dtype=torch.bfloat16)}
+            self.layers.append(L)
+        self.max_context = max_context
+        self.pos = 0
+
+    def reset(self) -> None:
+        self.pos = 0
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() + self.head.numel()
+        for L in self.layers:
+            n += sum(L[k].numel() * L[k].element_size() for k in ("q", "k", "v", "o", "w13", "w2", "router"))
+        return n
+
+    @torch.no_grad()
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens int32 [T] on the device; returns fp32 logits of the last row [vocab]."""
+        from .. import ops
+        c, go = self.cfg, self.go
+        T = tokens.numel()
+        if self.pos + T > self.max_context:
+            raise ValueError("context exceeds max_context")
+        pos = torch.arange(self.pos, self.pos + T, device=self.device, dtype=torch.int32)
+        h = go.gguf_dequant_rows(self.embed, self.types["token_embd.weight"], c.dim, tokens)
+        for i, L in enumerate(self.layers):
+            b = f"blk.{i}."
+            ta = self.types[b + "attn_q.weight"]
+            q = go.gguf_linear(h, L["q"], ta, c.n_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
+            k = go.gguf_linear(h, L["k"], self.types[b + "attn_k.weight"], c.n_kv_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
+            v = go.gguf_linear(h, L["v"], self.types[b + "attn_v.weight"], c.n_kv_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
+            q = _rms(q.float(), L["q_norm"], c.norm_eps).view(T, c.n_heads, c.head_dim)
+            k = _rms(k.float(), L["k_norm"], c.norm_eps).view(T, c.n_kv_heads, c.head_dim)
+            q = _rope(q, pos, c.rope_dim, c.rope_theta).to(torch.bfloat16).contiguous()
+            k = _rope(k, pos, c.rope_dim, c.rope_theta).to(torch.bfloat16)
+            L["kc"][:, self.pos:self.pos + T] = k.transpose(0, 1)
+            L["vc"][:, self.pos:self.pos + T] = v.view(T, c.n_kv_heads, c.head_dim).transpose(0, 1)
+            o = ops.gqa_decode(q, L["kc"], L["vc"], pos, nsplit=1 if T > 8 else 8)
+            att = go.gguf_linear(o, L["o"], self.types[b + "attn_output.weight"], c.dim, epi=2)
+            h = (h.float() + att).to(torch.bfloat16)
+            xn = _rms(h.float(), L["ffn_norm"], c.norm_eps).to(torch.bfloat16)
+            ids, wt = go.router_topk(xn, L["router"], c.n_experts_used, bias=L["bias"], score_func="sigmoid", norm_topk=True)
+            seg, tok, rw = go.group_routes(ids, wt, c.n_experts)
+            y = go.gguf_moe_forward(xn, L["w13"], L["w2"], self.types[b + "ffn_gate_exps.weight"], self.types[b + "ffn_down_exps.weight"],
+                                    c.n_experts, c.expert_inter, seg, tok, rw, expert_offset=self.e_start, local_experts=self.e_local)
+            if self.world > 1:
+                torch.distributed.all_reduce(y, group=self.group)
+            h = (h.float() + y).to(torch.bfloat16)
+        self.pos += T
+        return go.gguf_linear(h[-1:], self.head, self.types["output.weight"], c.vocab_size, gamma=self.final_norm, eps=c.norm_eps, epi=2)[0]
+
+    # protocol of the generic generation runtime
+    def prefill(self, tokens: Sequence[int]) -> int:
+        t = torch.tensor(list(tokens), dtype=torch.int32, device=self.device)
+        return int(torch.argmax(self.forward(t)))
+
+    def decode_one(self, token: int) -> int:
+        return int(torch.argmax(self.forward(torch.tensor([token], dtype=torch.int32, device=self.device))))

@@ -1,0 +1,93 @@
+"""Bindings of the raw-GGUF-block kernels: linear layers, router top-k, route grouping and
+the routed-expert pass. Weights are uint8 tensors holding the file's blocks unchanged."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import _check, _ptr, _sm_count, _stream
+from . import lib as _lib
+
+# device type ids (reference: src/loader/gguf/quant_types.py, plus q8_0 and bf16)
+DEVICE_TYPE = {"iq2_xxs": 0, "q2_k": 1, "iq1_m": 2, "q4_k": 3, "q5_k": 4, "iq2_xs": 5, "iq3_xxs": 6, "iq4_xs": 7,
+               "q6_k": 8, "q8_0": 9, "bf16": 10}
+SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
+
+
+def row_bytes(type_name: str, K: int) -> int:
+    return K // 256 * _lib.kernels().pk_gguf_block_bytes(DEVICE_TYPE[type_name])
+
+
+def gguf_linear(x: torch.Tensor, w_raw: torch.Tensor, type_name: str, N: int, *, gamma: torch.Tensor | None = None,
+                eps: float = 1e-6, epi: int = 0) -> torch.Tensor:
+    """y = rmsnorm?(x) @ dequant(W)^T for any number of rows (groups of up to 8 per launch)."""
+    M, K = x.shape
+    ncols = N // 2 if epi == 1 else N
+    y = torch.empty(M, ncols, device=x.device, dtype=torch.float32 if epi == 2 else torch.bfloat16)
+    step = max(1, min(8, (200 * 1024) // (K * 4)))
+    step = 8 if step >= 8 else 4 if step >= 4 else 2 if step >= 2 else 1
+    for m0 in range(0, M, step):
+        m = min(step, M - m0)
+        st = _lib.kernels().pk_gguf_linear(_ptr(w_raw), c_int(DEVICE_TYPE[type_name]), c_int(N), c_int(K), c_int(m),
+                                           _ptr(x[m0:]), _ptr(gamma), c_float(eps), c_int(epi), _ptr(y[m0:]), c_int(ncols),
+                                           c_int(_sm_count()), _stream())
+        _check(st, "pk_gguf_linear")
+    return y
+
+
+def router_topk(x: torch.Tensor, router_w: torch.Tensor, topk: int, *, bias: torch.Tensor | None = None,
+                score_func: str = "sigmoid", norm_topk: bool = True, route_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    T, H = x.shape
+    E = router_w.shape[0]
+    ids = torch.empty(T, topk, device=x.device, dtype=torch.int32)
+    w = torch.empty(T, topk, device=x.device, dtype=torch.float32)
+    st = _lib.kernels().pk_router_topk(_ptr(x), _ptr(router_w), _ptr(bias), c_int(T), c_int(H), c_int(E), c_int(topk),
+                                       c_int(SCORE_FUNCS[score_func]), c_int(int(norm_topk)), c_float(route_scale), _ptr(ids),
+                                       _ptr(w), _stream())
+    _check(st, "pk_router_topk")
+    return ids, w
+
+
+def group_routes(ids: torch.Tensor, weights: torch.Tensor, E: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Sort routes by expert: (seg_start [E+1], route_token [R], route_weight [R])."""
+    T, topk = ids.shape
+    seg = torch.empty(E + 1, device=ids.device, dtype=torch.int32)
+    tok = torch.empty(T * topk, device=ids.device, dtype=torch.int32)
+    rw = torch.empty(T * topk, device=ids.device, dtype=torch.float32)
+    st = _lib.kernels().pk_group_routes(_ptr(ids), _ptr(weights), c_int(T), c_int(topk), c_int(E), _ptr(seg), _ptr(tok),
+                                        _ptr(rw), c_void_p(0), _stream())
+    _check(st, "pk_group_routes")
+    return seg, tok, rw
+
+
+def gguf_moe_forward(x: torch.Tensor, w13_raw: torch.Tensor, w2_raw: torch.Tensor, type13: str, type2: str, E: int, inter: int,
+                     seg: torch.Tensor, tok: torch.Tensor, rw: torch.Tensor, *, limit: float = 0.0, expert_offset: int = 0,
+                     local_experts: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Routed experts of this rank accumulated into fp32 `out` [T, H] (zeroed when not given)."""
+    T, H = x.shape
+    R = tok.numel()
+    local = E if local_experts is None else local_experts
+    if out is None:
+        out = torch.zeros(T, H, device=x.device, dtype=torch.float32)
+    hbuf = torch.empty(R, inter, device=x.device, dtype=torch.float32)
+    st = _lib.kernels().pk_gguf_moe_forward(
+        _ptr(w13_raw), _ptr(w2_raw), c_int(DEVICE_TYPE[type13]), c_int(DEVICE_TYPE[type2]), c_int(E), c_int(H), c_int(inter),
+        _ptr(x), _ptr(seg), _ptr(tok), _ptr(rw), _ptr(hbuf), _ptr(out), c_float(limit), c_int(expert_offset), c_int(local),
+        c_int(_sm_count()), _stream())
+    _check(st, "pk_gguf_moe_forward")
+    return out
+
+
+def gguf_dequant_rows(w_raw: torch.Tensor, type_name: str, K: int, rows: torch.Tensor | None = None, *, nrows: int | None = None,
+                      row_offset: int = 0) -> torch.Tensor:
+    """Decode rows of a quantised table to bf16 (quantised embedding gather, or a whole
+    weight when `rows` is None)."""
+    rb = row_bytes(type_name, K)
+    table_rows = w_raw.numel() // rb
+    n = rows.numel() if rows is not None else (nrows if nrows is not None else table_rows)
+    out = torch.empty(n, K, device=w_raw.device, dtype=torch.bfloat16)
+    st = _lib.kernels().pk_gguf_dequant_rows(_ptr(w_raw), c_int(DEVICE_TYPE[type_name]), _ptr(rows), c_int(n), c_int(K),
+                                             c_int(row_offset), c_int(table_rows), _ptr(out), _stream())
+    _check(st, "pk_gguf_dequant_rows")
+    return out

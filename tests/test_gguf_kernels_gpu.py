@@ -1,0 +1,97 @@
+"""Raw-GGUF-block kernels against the numpy dequantisers (B200 only)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TYPES = ["iq2_xxs", "q2_k", "iq1_m", "q4_k", "q5_k", "iq2_xs", "iq3_xxs", "q8_0"]
+
+
+def _quant(w, name):
+    from pocketllm_b200.formats import gguf_quants as gq
+    blocks = gq.quantize(w, name)
+    deq = gq.dequantize(blocks, name)
+    return torch.from_numpy(blocks.reshape(w.shape[0], -1).copy()).cuda(), torch.from_numpy(deq).cuda()
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+
+@pytest.mark.parametrize("name", TYPES)
+@pytest.mark.parametrize("M", [1, 5])
+def test_gguf_linear(name, M):
+    from pocketllm_b200.ops import gguf_ops as go
+    rng = np.random.default_rng(3)
+    N, K = 96, 768
+    raw, wd = _quant((rng.standard_normal((N, K)) * 0.02).astype(np.float32), name)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    y = go.gguf_linear(x, raw, name, N, epi=2)
+    assert _rel(y, x.float() @ wd.t()) < 2e-3
+
+
+def test_gguf_linear_norm_swiglu_and_many_rows():
+    from pocketllm_b200.ops import gguf_ops as go
+    rng = np.random.default_rng(4)
+    N, K, M = 128, 512, 19
+    raw, wd = _quant((rng.standard_normal((N, K)) * 0.02).astype(np.float32), "q4_k")
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    gamma = 1 + torch.randn(K, device="cuda") * 0.1
+    y = go.gguf_linear(x, raw, "q4_k", N, gamma=gamma, epi=1)
+    xf = x.float()
+    xn = (xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * gamma).to(torch.bfloat16).float()
+    gu = xn @ wd.t()
+    assert _rel(y, torch.nn.functional.silu(gu[:, :64]) * gu[:, 64:]) < 1e-2
+
+
+@pytest.mark.parametrize("score,norm", [("sigmoid", True), ("softmax", False), ("sqrtsoftplus", True)])
+def test_router_topk(score, norm):
+    from pocketllm_b200.ops import gguf_ops as go
+    T, H, E, k = 7, 512, 64, 8
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    rw = torch.randn(E, H, device="cuda") * 0.05
+    bias = torch.randn(E, device="cuda") * 0.01
+    ids, w = go.router_topk(x, rw, k, bias=bias, score_func=score, norm_topk=norm, route_scale=1.5)
+    logits = x.float() @ rw.t()
+    sc = {"sigmoid": torch.sigmoid, "softmax": lambda z: torch.softmax(z, -1),
+          "sqrtsoftplus": lambda z: torch.sqrt(torch.nn.functional.softplus(z))}[score](logits)
+    ref_ids = torch.topk(sc + bias, k, dim=-1).indices
+    assert torch.equal(ids.long().sort(-1).values, ref_ids.sort(-1).values)
+    ref_w = torch.gather(sc, 1, ids.long())
+    if norm:
+        ref_w = ref_w / ref_w.sum(-1, keepdim=True)
+    assert torch.allclose(w, ref_w * 1.5, rtol=2e-3, atol=1e-5)
+
+
+@pytest.mark.parametrize("t13,t2,T", [("iq2_xxs", "q2_k", 1), ("iq2_xxs", "iq2_xxs", 40), ("iq1_m", "iq1_m", 9)])
+def test_moe_forward_matches_dequantised_reference(t13, t2, T):
+    from pocketllm_b200.ops import gguf_ops as go
+    rng = np.random.default_rng(5)
+    E, H, I, k = 8, 512, 256, 2
+    w13 = (rng.standard_normal((E * 2 * I, H)) * 0.02).astype(np.float32)
+    w2 = (rng.standard_normal((E * H, I)) * 0.02).astype(np.float32)
+    raw13, d13 = _quant(w13, t13)
+    raw2, d2 = _quant(w2, t2)
+    d13, d2 = d13.view(E, 2 * I, H), d2.view(E, H, I)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    rw = torch.randn(E, H, device="cuda") * 0.05
+    ids, w = go.router_topk(x, rw, k, score_func="sigmoid")
+    seg, tok, rwt = go.group_routes(ids, w, E)
+    assert int(seg[-1]) == T * k
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=E)
+    assert torch.equal((seg[1:] - seg[:-1]).long(), counts)
+    y = go.gguf_moe_forward(x, raw13, raw2, t13, t2, E, I, seg, tok, rwt)
+    ref = torch.zeros(T, H, device="cuda")
+    xf = x.float()
+    for t in range(T):
+        for j in range(k):
+            e = int(ids[t, j])
+            gu = d13[e] @ xf[t]
+            ref[t] += w[t, j] * (d2[e] @ (torch.nn.functional.silu(gu[:I]) * gu[I:]))
+    assert _rel(y, ref) < 3e-3
+    # expert-parallel halves add up to the whole
+    lo = go.gguf_moe_forward(x, raw13[: E // 2 * 2 * I], raw2[: E // 2 * H], t13, t2, E, I, seg, tok, rwt, local_experts=E // 2)
+    hi = go.gguf_moe_forward(x, raw13[E // 2 * 2 * I:], raw2[E // 2 * H:], t13, t2, E, I, seg, tok, rwt,
+                             expert_offset=E // 2, local_experts=E // 2)
+    assert _rel(lo + hi, ref) < 3e-3

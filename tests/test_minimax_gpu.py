@@ -1,0 +1,37 @@
+"""MiniMax-M2 on a tiny synthetic GGUF: raw-block GPU runtime vs the fp32 oracle."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny_gguf(tmp_path_factory):
+    from pocketllm_b200.models import minimax_m2 as mm
+    p = tmp_path_factory.mktemp("mm") / "tiny.gguf"
+    mm.write_random_gguf(p, mm.MiniMaxM2Config.tiny(), seed=0, sigma=0.05)
+    return p
+
+
+def test_forward_matches_oracle(tiny_gguf):
+    from pocketllm_b200.models import minimax_m2 as mm
+    ref = mm.ReferenceModel(tiny_gguf)
+    model = mm.MiniMaxM2Model(tiny_gguf, max_context=128)
+    prompt = [3, 77, 140, 9, 255, 31, 8, 500, 64, 2, 19]
+    lr = ref.forward(prompt)[-1]
+    lg = model.forward(torch.tensor(prompt, dtype=torch.int32, device="cuda")).cpu()
+    assert ((lg - lr).norm() / lr.norm()) < 3e-2
+    # one decode step after the prefill
+    nxt = int(lr.argmax())
+    lr2 = ref.forward([nxt])[-1]
+    lg2 = model.forward(torch.tensor([nxt], dtype=torch.int32, device="cuda")).cpu()
+    assert ((lg2 - lr2).norm() / lr2.norm()) < 3e-2
+
+
+def test_generate_cli_runtime(tiny_gguf):
+    from pocketllm_b200.models import registry
+    from pocketllm_b200.runtime import generation as gen
+    rt = registry.build_runtime(tiny_gguf, max_context=64)
+    res = gen.greedy_generate(rt, [1, 2, 3, 4], 6)
+    assert len(res.tokens) == 6 and res.prefill_seconds > 0 and res.decode_tps > 0
+    assert res.result_line().startswith("RESULT prefill_seconds=")
