@@ -79,6 +79,7 @@ def read_seed_tokens(path: str | Path) -> list[int]:
 
 def greedy_generate(rt: TokenRuntime, prompt: Sequence[int], max_new_tokens: int, eos: int | None = None) -> GenerationResult:
     res = GenerationResult(prompt_tokens=len(prompt))
+    rt.reset()
     _sync()
     t0 = time.perf_counter()
     tok = rt.prefill(prompt)
