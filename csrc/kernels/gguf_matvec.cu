@@ -205,7 +205,8 @@ __global__ void __launch_bounds__(kThreads) gguf_linear_kernel(const LinearParam
   for (int m = 0; m < M; ++m) {
     float ss = 0.f;
     for (int k = tid; k < p.K; k += kThreads) {
-      const float v = __bfloat162float(p.x[(size_t)m * p.K + k]);
+      // the template may be wider than the number of rows given: pad with zeros
+      const float v = m < p.M ? __bfloat162float(p.x[(size_t)m * p.K + k]) : 0.f;
       xs[m * p.K + k] = v;
       ss += v * v;
     }
@@ -234,6 +235,7 @@ __global__ void __launch_bounds__(kThreads) gguf_linear_kernel(const LinearParam
     if (lane == 0) {
 #pragma unroll
       for (int m = 0; m < M; ++m) {
+        if (m >= p.M) break;
         if (p.epi == 1) ((bf16*)p.y)[(size_t)m * p.ldy + g] = __float2bfloat16(silu(a0[m]) * a1[m]);
         else if (p.epi == 0) ((bf16*)p.y)[(size_t)m * p.ldy + g] = __float2bfloat16(a0[m]);
         else ((float*)p.y)[(size_t)m * p.ldy + g] = a0[m];

@@ -111,7 +111,7 @@ def _rope(x: torch.Tensor, pos: torch.Tensor, rope_dim: int, theta: float) -> to
     """Half-split rotation of the first rope_dim dims. x [T, heads, D], pos [T]."""
     half = rope_dim // 2
     inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rope_dim)
-    ang = pos.double()[:, None] * inv[None, :]
+    ang = pos.double().cpu()[:, None] * inv[None, :]
     cs, sn = torch.cos(ang).float().to(x.device)[:, None, :], torch.sin(ang).float().to(x.device)[:, None, :]
     x1, x2 = x[..., :half], x[..., half:rope_dim]
     return torch.cat([x1 * cs - x2 * sn, x2 * cs + x1 * sn, x[..., rope_dim:]], dim=-1)
@@ -198,7 +198,7 @@ class MiniMaxM2Model:
             b = self.bundle.blocks(name)
             if lo is not None:
                 b = b[lo:hi]
-            return torch.from_numpy(np.ascontiguousarray(b).reshape(-1)).to(self.device)
+            return torch.from_numpy(np.array(b, copy=True).reshape(-1)).to(self.device)
 
         def f32(name: str) -> torch.Tensor:
             return torch.from_numpy(self.bundle.raw(name).view(np.float32).copy()).to(self.device)
