@@ -1,0 +1,116 @@
+"""Model backends of the OpenAI server: the native Qwen engine and the GGUF runtimes, each
+paired with a chat tokenizer."""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Iterator, Sequence
+
+import torch
+
+from ..encoding import chat, dsv4, gguf_tokenizer
+from .engine import SamplingParams, apply_penalties, sample_token
+
+
+class QwenBackend:
+    """Greedy requests run on the engine's CUDA-graph decode in bursts; sampled requests read
+    the logits back after every step."""
+
+    def __init__(self, engine, burst: int = 8):
+        self.eng, self.burst = engine, burst
+
+    def generate(self, prompt_ids: Sequence[int], p: SamplingParams) -> Iterator[int]:
+        eng = self.eng
+        eng.reset()
+        tok = eng.prefill(list(prompt_ids))
+        produced = [tok]
+        yield tok
+        greedy = p.temperature <= 0 and p.repetition_penalty == 1.0 and p.frequency_penalty == 0 and p.presence_penalty == 0
+        gen = torch.Generator().manual_seed(p.seed) if p.seed is not None else None
+        while len(produced) < p.max_tokens and produced[-1] not in p.stop_token_ids:
+            if greedy:
+                n = min(self.burst, p.max_tokens - len(produced))
+                for t in eng.decode(n, sync_each_step=False):
+                    produced.append(t)
+                    yield t
+                    if t in p.stop_token_ids:
+                        return
+            else:
+                # re-run the last position's logits through the host sampler
+                logits = apply_penalties(eng.logits(0), produced, p)
+                t = sample_token(logits, p, gen)
+                produced[-1] = t
+                eng_next = eng.forward_rows([t])[0]
+                produced.append(eng_next)
+                yield eng_next
+
+
+class GGUFBackend:
+    def __init__(self, runtime):
+        self.rt = runtime
+
+    def generate(self, prompt_ids: Sequence[int], p: SamplingParams) -> Iterator[int]:
+        self.rt.reset()
+        tok = self.rt.prefill(list(prompt_ids))
+        n = 1
+        yield tok
+        while n < p.max_tokens and tok not in p.stop_token_ids:
+            tok = self.rt.decode_one(tok)
+            n += 1
+            yield tok
+
+
+class HFChatTokenizer:
+    """`tokenizers.Tokenizer` + a chat renderer + a completion parser."""
+
+    def __init__(self, tok, render, eos_ids: Sequence[int], parse=None):
+        self.tok, self.render, self._eos, self._parse = tok, render, tuple(eos_ids), parse
+
+    def encode_chat(self, messages, *, tools=None, thinking=False, reasoning_effort=None, response_format=None):
+        text = self.render(messages, tools=tools, thinking=thinking, reasoning_effort=reasoning_effort, response_format=response_format)
+        return self.tok.encode(text, add_special_tokens=False).ids
+
+    def decode(self, ids):
+        return self.tok.decode(list(ids), skip_special_tokens=False)
+
+    def parse(self, text: str, thinking: bool) -> dict:
+        if self._parse:
+            return self._parse(text, thinking)
+        r, v = chat.split_thinking(text)
+        msg = {"role": "assistant", "content": v}
+        if r:
+            msg["reasoning_content"] = r
+        return msg
+
+    @property
+    def eos_ids(self):
+        return self._eos
+
+
+def build(kind: str, ckpt: str, max_context: int):
+    """(backend, tokenizer) for `--model qwen|gguf`."""
+    if kind == "qwen":
+        from tokenizers import Tokenizer
+        from ..models import qwen_hybrid as qh
+        cfg = qh.QwenHybridConfig.from_json((Path(ckpt) / "config.json").read_text())
+        eng = qh.QwenEngine(cfg, max_context=max_context).load(ckpt)
+        tok = Tokenizer.from_file(str(Path(ckpt) / "tokenizer.json"))
+        eos = [i for i in (tok.token_to_id("<|im_end|>"), tok.token_to_id("<|endoftext|>")) if i is not None]
+
+        def render(messages, *, tools=None, thinking=False, **_):
+            out = ""
+            for m in messages:
+                out += f"<|im_start|>{m['role']}\n{dsv4._text(m.get('content'))}<|im_end|>\n"
+            return out + "<|im_start|>assistant\n" + ("<think>\n" if thinking else "")
+        return QwenBackend(eng), HFChatTokenizer(tok, render, eos)
+    from ..models import registry
+    md = gguf_tokenizer.read_metadata(ckpt)
+    tok = gguf_tokenizer.build_tokenizer(md)
+    arch = md.get("general.architecture")
+    rt = registry.build_runtime(ckpt, max_context=max_context)
+    sp = gguf_tokenizer.special_ids(md)
+    eos = [i for i in (sp["eos"], sp["eot"]) if i is not None]
+    if arch == "glm-dsa":
+        render = lambda messages, *, thinking=False, **_: chat.render_glm(messages, thinking=thinking)
+    else:
+        render = lambda messages, *, thinking=False, **_: chat.render_minimax(messages, thinking=thinking)
+    return GGUFBackend(rt), HFChatTokenizer(tok, render, eos)

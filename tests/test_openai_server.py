@@ -1,0 +1,144 @@
+"""OpenAI server behaviours over real HTTP with a fake engine and tokenizer (CPU): JSON and SSE
+responses, stop strings, thinking content, tool calls, validation errors, context limit."""
+import json
+import threading
+import urllib.error
+import urllib.request
+
+import pytest
+
+from pocketllm_b200.encoding import dsv4
+from pocketllm_b200.server import openai as oa
+from pocketllm_b200.server.engine import SamplingParams, ServingEngine, sample_token
+
+
+class CharTokenizer:
+    """One token per character (ids = code points); id 0 is EOS."""
+    eos_ids = (0,)
+
+    def __init__(self):
+        self.last_prompt = None
+
+    def encode_chat(self, messages, *, tools=None, thinking=False, reasoning_effort=None, response_format=None):
+        self.last_prompt = dsv4.encode_messages(messages, tools=tools, thinking_mode="thinking" if thinking else "chat",
+                                                reasoning_effort=reasoning_effort, response_format=response_format)
+        return [ord(c) for c in self.last_prompt]
+
+    def decode(self, ids):
+        return "".join(chr(i) for i in ids)
+
+    def parse(self, text, thinking):
+        return dsv4.parse_completion(("" if thinking else "</think>") + text if not thinking else "<think>" + text, "thinking" if thinking else "chat")
+
+
+class ScriptedBackend:
+    def __init__(self, script: str):
+        self.script = script
+        self.calls = []
+
+    def generate(self, prompt_ids, params: SamplingParams):
+        self.calls.append((len(prompt_ids), params))
+        for ch in self.script:
+            yield ord(ch)
+        yield 0
+
+
+@pytest.fixture
+def server():
+    made = []
+
+    def make(script, max_context=4096):
+        backend = ScriptedBackend(script)
+        app = oa.OpenAIApp(ServingEngine(backend), CharTokenizer(), model_name="fake", max_context=max_context)
+        httpd = oa.serve(app, "127.0.0.1", 0)
+        threading.Thread(target=httpd.serve_forever, daemon=True).start()
+        made.append((httpd, app))
+        return f"http://127.0.0.1:{httpd.server_address[1]}", backend, app
+    yield make
+    for httpd, app in made:
+        httpd.shutdown()
+        app.engine.close()
+
+
+def _post(url, body):
+    req = urllib.request.Request(url + "/v1/chat/completions", data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=20) as r:
+            return r.status, r.read().decode()
+    except urllib.error.HTTPError as e:
+        return e.code, e.read().decode()
+
+
+def test_health_models_and_completion(server):
+    url, backend, app = server("Hello there")
+    assert json.loads(urllib.request.urlopen(url + "/health").read())["status"] == "ok"
+    assert json.loads(urllib.request.urlopen(url + "/v1/models").read())["data"][0]["id"] == "fake"
+    code, text = _post(url, {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 64})
+    d = json.loads(text)
+    assert code == 200 and d["choices"][0]["message"]["content"] == "Hello there"
+    assert d["choices"][0]["finish_reason"] == "stop"
+    assert d["usage"]["completion_tokens"] == len("Hello there") + 1 and d["usage"]["prompt_tokens"] == backend.calls[0][0]
+    assert d["timings"]["prefill_seconds"] is not None
+
+
+def test_stop_string_and_max_tokens(server):
+    url, _, _ = server("abcSTOPdef")
+    _, text = _post(url, {"messages": [{"role": "user", "content": "x"}], "stop": ["STOP"]})
+    d = json.loads(text)
+    assert d["choices"][0]["message"]["content"] == "abc" and d["choices"][0]["finish_reason"] == "stop"
+    _, text = _post(url, {"messages": [{"role": "user", "content": "x"}], "max_tokens": 4})
+    d = json.loads(text)
+    assert d["choices"][0]["message"]["content"] == "abcS" and d["choices"][0]["finish_reason"] == "length"
+
+
+def test_streaming_sse_with_thinking_and_tools(server):
+    call = [{"type": "function", "function": {"name": "f", "arguments": json.dumps({"a": 1})}}]
+    script = "think hard</think>Answer.\n\n" + dsv4.render_tool_calls(call)
+    url, _, _ = server(script)
+    code, text = _post(url, {"messages": [{"role": "user", "content": "x"}], "stream": True, "reasoning_effort": "high",
+                             "stream_options": {"include_usage": True},
+                             "tools": [{"type": "function", "function": {"name": "f", "parameters": {}}}]})
+    assert code == 200
+    events = [json.loads(l[6:]) for l in text.split("\n\n") if l.startswith("data: {")]
+    assert text.strip().endswith("data: [DONE]")
+    reasoning = "".join(e["choices"][0]["delta"].get("reasoning_content", "") for e in events)
+    content = "".join(e["choices"][0]["delta"].get("content", "") for e in events)
+    assert reasoning == "think hard" and content.startswith("Answer.")
+    tool_events = [e for e in events if "tool_calls" in e["choices"][0]["delta"]]
+    assert tool_events and tool_events[0]["choices"][0]["delta"]["tool_calls"][0]["function"]["name"] == "f"
+    assert events[-1]["choices"][0]["finish_reason"] == "tool_calls" and events[-1]["usage"]["completion_tokens"] > 0
+
+
+def test_validation_errors_and_context_limit(server):
+    url, _, _ = server("x", max_context=64)
+    for body in ({"messages": []}, {"messages": [{"role": "user", "content": "x"}], "stream": True, "n": 2},
+                 {"messages": [{"role": "user", "content": "x"}], "max_tokens": 0},
+                 {"messages": [{"role": "user", "content": "x"}], "stream": True, "logprobs": True},
+                 {"messages": [{"role": "user", "content": "y" * 200}]}):
+        code, text = _post(url, body)
+        assert code == 400 and "error" in json.loads(text)
+    req = urllib.request.Request(url + "/v1/chat/completions", data=b"{not json", headers={"Content-Type": "application/json"})
+    with pytest.raises(urllib.error.HTTPError) as ei:
+        urllib.request.urlopen(req)
+    assert ei.value.code == 400
+
+
+def test_streaming_decoder_holds_back_partial_stop():
+    tok = CharTokenizer()
+    dec = oa.StreamingDecoder(tok, ["END"])
+    out = [dec.push(ord(c)) for c in "abEN"]
+    assert "".join(out) == "ab"          # "EN" could still become "END"
+    assert dec.push(ord("x")) == "ENx"
+    out = "".join(dec.push(ord(c)) for c in "yENDz")
+    assert out == "y" and dec.stopped and dec.text == "abENxy"
+
+
+def test_sampler_greedy_and_topk():
+    import torch
+    logits = torch.tensor([0.1, 3.0, 3.0, -1.0])
+    assert sample_token(logits, SamplingParams(temperature=0.0)) == 1
+    g = torch.Generator().manual_seed(0)
+    picks = {sample_token(logits, SamplingParams(temperature=1.0, top_k=2), g) for _ in range(50)}
+    assert picks <= {1, 2}
+    picks = {sample_token(logits, SamplingParams(temperature=1.0, top_p=0.3), g) for _ in range(20)}
+    assert len(picks) == 1
