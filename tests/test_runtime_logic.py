@@ -1,0 +1,65 @@
+"""Pure-CPU runtime logic: prefix snapshot cache, PD scheduler, DSpark gate."""
+from pocketllm_b200.runtime.dspark_gate import DSparkGate, GateCosts
+from pocketllm_b200.runtime.pd_scheduler import PDScheduler, PhaseResources
+from pocketllm_b200.runtime.prefix_snapshot import PrefixSnapshotCache, chain_hashes
+
+
+def test_chain_hashes_are_prefix_stable():
+    a = list(range(600))
+    b = a[:512] + [7] * 88
+    ha, hb = chain_hashes(a), chain_hashes(b)
+    assert len(ha) == 2 and ha == hb                       # same first 512 tokens
+    assert chain_hashes(a[:255]) == [] and chain_hashes([1] + a[1:600])[0] != ha[0]
+
+
+def test_prefix_cache_restore_capture_lru():
+    evicted = []
+    c = PrefixSnapshotCache(capacity=2, on_evict=lambda s: evicted.append(s.length))
+    p = list(range(1000))
+    assert c.restore(p) is None
+    assert c.capture(p[:256], "s256") and c.capture(p[:512], "s512")
+    assert c.lookup_hint(p) == 512
+    assert c.restore(p).state == "s512"
+    assert c.restore(p[:512]).state == "s256"              # must leave one token to compute
+    assert c.restore(p[:256]) is None
+    q = [5] * 300
+    c.capture(q, "q256")                                    # evicts the least recently used
+    assert len(c) == 2 and evicted == [512]
+    assert c.restore([1] + p[1:]) is None and c.stats["hits"] == 2
+    assert not c.capture([1, 2, 3], "short")
+
+
+def test_pd_scheduler_prefers_decode():
+    s = PDScheduler(prefill=PhaseResources(env={"POCKET_PHASE": "prefill"}), decode=PhaseResources(env={"POCKET_PHASE": "decode"}),
+                    max_pending=3)
+    assert s.submit("a") and s.submit("b")
+    req, phase = s.next()
+    assert (req, phase) == ("a", "prefill")
+    s.prefill_done("a")
+    assert s.next() == ("a", "decode")                      # decode before the second prefill
+    s.requeue_decode("a")
+    assert s.next() == ("a", "decode")
+    assert s.next() == ("b", "prefill")
+    assert s.next(timeout=0.01) is None
+    assert s.submit("c") and s.submit("d") and s.submit("e") and not s.submit("f")
+    assert s.stats["rejected"] == 1 and s.stats["phase_switches"] >= 3
+    import os
+    assert os.environ["POCKET_PHASE"] == "prefill"
+
+
+def test_dspark_gate_decisions_and_calibration():
+    g = DSparkGate(GateCosts(plain_ms=300, draft_ms=200, verify_base_ms=300, verify_per_token_ms=100), max_draft=5)
+    # with the 0.6 prior a round (>= 600 ms) cannot beat 300 ms per token
+    assert g.choose_draft_len([0.9] * 5) == 0 and not g.should_draft()
+    for _ in range(200):
+        g.observe([0.95] * 5, accepted=5, proposed=5)
+    assert g.match_probability(0, 0.95) > 0.95
+    n = g.choose_draft_len([0.95] * 5)
+    assert n == 5 and g.expected_tokens([0.95] * 5, 5) > 5.0
+    # low-confidence buckets stay at the prior and are rejected
+    assert g.choose_draft_len([0.1] * 5) == 0
+    assert abs(g.acceptance_rate() - 1.0) < 1e-9
+    g2 = DSparkGate(GateCosts(300, 20, 30, 10), margin_threshold=0.5)
+    assert not g2.should_draft(target_margin=0.1) and g2.should_draft(target_margin=2.0)
+    g2.observe([0.5, 0.5, 0.5], accepted=1, proposed=3)
+    assert g2.stats["accepted_tokens"] == 1 and g2.stats["proposed_tokens"] == 3
