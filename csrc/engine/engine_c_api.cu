@@ -80,6 +80,28 @@ PK_EAPI int pk_qwen_forward_rows(void* h, const int* tokens, int M, int* out_tok
   return guarded([&] { ((pk::QwenEngine*)h)->forward_rows(tokens, M, out_tokens); });
 }
 
+// Recurrent-state snapshots (KV is position indexed and is not copied). A snapshot handle
+// belongs to the engine that made it.
+PK_EAPI void* pk_qwen_snapshot(void* h) {
+  void* out = nullptr;
+  guarded([&] { out = ((pk::QwenEngine*)h)->snapshot().release(); });
+  return out;
+}
+PK_EAPI int pk_qwen_snapshot_update(void* h, void* snap) {
+  return guarded([&] { ((pk::QwenEngine*)h)->update_snapshot(*(pk::QwenEngine::Snapshot*)snap); });
+}
+PK_EAPI int pk_qwen_restore(void* h, void* snap) {
+  return guarded([&] { ((pk::QwenEngine*)h)->restore(*(pk::QwenEngine::Snapshot*)snap); });
+}
+PK_EAPI int pk_qwen_snapshot_position(void* snap) { return ((pk::QwenEngine::Snapshot*)snap)->pos; }
+PK_EAPI int pk_qwen_free_snapshot(void* h, void* snap) {
+  return guarded([&] {
+    auto* s = (pk::QwenEngine::Snapshot*)snap;
+    ((pk::QwenEngine*)h)->free_snapshot(*s);
+    delete s;
+  });
+}
+
 PK_EAPI int pk_qwen_copy_logits(void* h, float* out, int row) {
   return guarded([&] { ((pk::QwenEngine*)h)->copy_logits(out, row); });
 }

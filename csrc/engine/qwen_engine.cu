@@ -433,6 +433,18 @@ std::unique_ptr<QwenEngine::Snapshot> QwenEngine::snapshot() {
   return s;
 }
 
+void QwenEngine::update_snapshot(Snapshot& s) {
+  size_t i = 0;
+  for (auto& L : layers_) {
+    if (L.full) continue;
+    const size_t sb = (size_t)vh_l_ * kHeadDim * kHeadDim * sizeof(float), cb = (size_t)conv_c_l_ * 3 * sizeof(float);
+    cuda_check(cudaMemcpyAsync(s.bufs[i++], L.lin_state, sb, cudaMemcpyDeviceToDevice, stream_), "snapshot");
+    cuda_check(cudaMemcpyAsync(s.bufs[i++], L.conv_state, cb, cudaMemcpyDeviceToDevice, stream_), "snapshot");
+  }
+  s.pos = pos_;
+  s.last_token = last_token_;
+}
+
 void QwenEngine::restore(const Snapshot& s) {
   size_t i = 0;
   for (auto& L : layers_) {
@@ -441,6 +453,9 @@ void QwenEngine::restore(const Snapshot& s) {
     cuda_check(cudaMemcpyAsync(L.lin_state, s.bufs[i++], sb, cudaMemcpyDeviceToDevice, stream_), "restore");
     cuda_check(cudaMemcpyAsync(L.conv_state, s.bufs[i++], cb, cudaMemcpyDeviceToDevice, stream_), "restore");
   }
+  // decode() reads its input token from slot 0 of the device token buffer
+  cuda_check(cudaMemcpyAsync(next_tok_dev_, &s.last_token, sizeof(int), cudaMemcpyHostToDevice, stream_), "restore token");
+  cuda_check(cudaStreamSynchronize(stream_), "restore");
   pos_ = s.pos;
   last_token_ = s.last_token;
 }

@@ -120,6 +120,7 @@ class QwenEngine {
     int last_token = 0;
   };
   std::unique_ptr<Snapshot> snapshot();
+  void update_snapshot(Snapshot& s);   // re-capture into existing buffers (no allocation)
   void restore(const Snapshot& s);
   void free_snapshot(Snapshot& s);
 

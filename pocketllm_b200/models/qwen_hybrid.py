@@ -291,6 +291,30 @@ class EngineError(RuntimeError):
     pass
 
 
+class EngineSnapshot:
+    """Device copy of the DeltaNet states and conv tails at one position. `update()` re-captures
+    into the same buffers; `restore()` rewinds the engine (the KV cache is position indexed,
+    so entries beyond the restored position are simply overwritten later)."""
+
+    def __init__(self, engine: "QwenEngine", handle):
+        self._e, self._s = engine, handle
+
+    @property
+    def position(self) -> int:
+        return self._e._L.pk_qwen_snapshot_position(self._s)
+
+    def update(self) -> None:
+        self._e._ck(self._e._L.pk_qwen_snapshot_update(self._e._h, self._s))
+
+    def restore(self) -> None:
+        self._e._ck(self._e._L.pk_qwen_restore(self._e._h, self._s))
+
+    def free(self) -> None:
+        if self._s is not None and self._e._h:
+            self._e._L.pk_qwen_free_snapshot(self._e._h, self._s)
+        self._s = None
+
+
 class QwenEngine:
     """Native engine for one tensor-parallel rank.
 
@@ -308,6 +332,7 @@ class QwenEngine:
         L.pk_qwen_comm_arena.restype = ctypes.c_void_p
         L.pk_qwen_weight_bytes.restype = ctypes.c_ulonglong
         L.pk_ipc_open.restype = ctypes.c_void_p
+        L.pk_qwen_snapshot.restype = ctypes.c_void_p
         self.cfg = cfg
         text = cfg if isinstance(cfg, str) else cfg.to_json()
         self.tp_rank, self.tp_world, self.device = tp_rank, tp_world, device
@@ -360,6 +385,21 @@ class QwenEngine:
         out = (ctypes.c_int * n)()
         self._ck(self._L.pk_qwen_forward_rows(self._h, arr, n, out))
         return list(out)
+
+    # -- recurrent-state snapshots (speculative decoding, prefix cache) -----------------
+    def snapshot(self) -> "EngineSnapshot":
+        h = self._L.pk_qwen_snapshot(self._h)
+        if not h:
+            raise EngineError(self._L.pk_engine_last_error().decode())
+        return EngineSnapshot(self, ctypes.c_void_p(h))
+
+    @property
+    def position(self) -> int:
+        return self._L.pk_qwen_position(self._h)
+
+    @property
+    def last_token(self) -> int:
+        return self._L.pk_qwen_last_token(self._h)
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int) -> list[int]:
         first = self.prefill(prompt)

@@ -44,8 +44,10 @@ def _random_blocks(name, n, seed=0):
 
 @pytest.mark.parametrize("name", sorted(ORACLE))
 def test_dequantize_matches_gguf_package(name):
-    b = _random_blocks(name, 64, seed=hash(name) % 1000)
+    b = _random_blocks(name, 64, seed=sum(map(ord, name)))
     mine = gq.dequantize(b[None], name)[0]
+    if hasattr(ORACLE[name], "init_grid"):
+        ORACLE[name].init_grid()               # the package fills its codebooks lazily
     ref = ORACLE[name].dequantize_blocks(b)
     assert mine.shape == ref.reshape(-1).shape or mine.reshape(ref.shape).shape == ref.shape
     np.testing.assert_allclose(mine.reshape(ref.shape), ref, rtol=1e-5, atol=1e-7)

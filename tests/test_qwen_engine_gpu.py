@@ -96,3 +96,47 @@ def test_random_init_runs_and_is_deterministic():
         eng.close()
     assert outs[0] == outs[1]
     assert all(0 <= t < cfg.vocab_size for t in outs[0])
+
+
+def test_snapshot_restore_rewinds_recurrent_state(tiny):
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    e = qh.QwenEngine(cfg, max_context=256, prefill_chunk=8).load(d)
+    e.prefill([5, 6, 7, 8, 9, 10])
+    snap = e.snapshot()
+    first = e.decode(6)
+    assert e.position == snap.position + 6
+    snap.restore()
+    assert e.position == snap.position and e.decode(6) == first
+    snap.restore()
+    e.forward_rows([1, 2, 3])                      # a rejected draft pollutes the state ...
+    snap.restore()
+    assert e.decode(6) == first                    # ... and the rewind removes it
+    snap.free()
+    e.close()
+
+
+def test_speculative_decoding_equals_greedy(tiny):
+    """Perfect, wrong and n-gram drafts all reproduce plain greedy decoding token for token."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    from pocketllm_b200.runtime.speculative import NGramDrafter, ReplayDrafter, speculative_generate
+    cfg, tensors, d = tiny
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5]
+    e = qh.QwenEngine(cfg, max_context=256, prefill_chunk=8).load(d)
+    ref = e.generate(prompt, 33)
+    n = len(prompt) + 1
+    e.reset()
+    out, st = speculative_generate(e, prompt, 33, ReplayDrafter(ref[1:], n), k=4)
+    assert out == ref and st.acceptance == 1.0 and st.tokens_per_pass > 4.0
+    e.reset()
+    wrong = [(t + 1) % cfg.vocab_size for t in ref[1:]]
+    out, st = speculative_generate(e, prompt, 33, ReplayDrafter(wrong, n), k=3)
+    assert out == ref and st.accepted == 0
+    e.reset()
+    half = [t if i % 3 else (t + 7) % cfg.vocab_size for i, t in enumerate(ref[1:])]
+    out, st = speculative_generate(e, prompt, 33, ReplayDrafter(half, n), k=7)
+    assert out == ref and 0 < st.acceptance < 1
+    e.reset()
+    out, _ = speculative_generate(e, prompt, 33, NGramDrafter(), k=4)
+    assert out == ref
+    e.close()

@@ -63,3 +63,88 @@ def test_dspark_gate_decisions_and_calibration():
     assert not g2.should_draft(target_margin=0.1) and g2.should_draft(target_margin=2.0)
     g2.observe([0.5, 0.5, 0.5], accepted=1, proposed=3)
     assert g2.stats["accepted_tokens"] == 1 and g2.stats["proposed_tokens"] == 3
+
+
+# ---------------------------------------------------------------------------------------
+# speculative loop against a fake engine (deterministic next-token function + recurrent state)
+class _FakeSnap:
+    def __init__(self, e):
+        self.e, self.state = e, None
+        self.update()
+
+    def update(self):
+        self.state = (self.e.h, self.e.pos)
+
+    def restore(self):
+        self.e.h, self.e.pos = self.state
+
+    def free(self):
+        pass
+
+
+class _FakeEngine:
+    """next token = f(running hash of all tokens fed so far): any wrong rewind changes the output."""
+
+    def __init__(self):
+        self.h, self.pos, self.passes = 0, 0, 0
+
+    def _feed(self, t):
+        self.h = (self.h * 1000003 + t + 1) % 2147483647
+        self.pos += 1
+        return (self.h >> 3) % 11      # small vocabulary so that n-grams repeat
+
+    def prefill(self, prompt):
+        self.h, self.pos = 0, 0
+        for t in prompt:
+            nxt = self._feed(t)
+        return nxt
+
+    def forward_rows(self, rows):
+        assert 1 <= len(rows) <= 8
+        self.passes += 1
+        return [self._feed(t) for t in rows]
+
+    def snapshot(self):
+        return _FakeSnap(self)
+
+
+def _plain(prompt, n):
+    e = _FakeEngine()
+    out = [e.prefill(prompt)]
+    while len(out) < n:
+        out.append(e.forward_rows([out[-1]])[0])
+    return out
+
+
+def test_speculative_matches_plain_greedy_for_any_drafter():
+    from pocketllm_b200.runtime.speculative import NGramDrafter, ReplayDrafter, speculative_generate
+    prompt = [1, 2, 3, 4, 5, 1, 2, 3]
+    ref = _plain(prompt, 40)
+    # perfect draft: every round accepts k and emits k+1
+    e = _FakeEngine()
+    out, st = speculative_generate(e, prompt, 40, ReplayDrafter(ref[1:] , len(prompt) + 1), k=4)
+    assert out == ref and st.acceptance == 1.0 and st.replays == 0 and st.tokens_per_pass > 4.0
+    # adversarial draft: always wrong -> one replay per round, still identical output
+    bad = [(t + 1) % 11 for t in ref[1:]]
+    out, st = speculative_generate(_FakeEngine(), prompt, 40, ReplayDrafter(bad, len(prompt) + 1), k=3)
+    assert out == ref and st.accepted == 0 and st.replays == st.rounds
+    # half-right draft: rewinds in the middle of a round
+    half = [t if i % 3 else (t + 5) % 11 for i, t in enumerate(ref[1:])]
+    out, st = speculative_generate(_FakeEngine(), prompt, 40, ReplayDrafter(half, len(prompt) + 1), k=5)
+    assert out == ref and 0 < st.acceptance < 1
+    out, st = speculative_generate(_FakeEngine(), prompt, 40, NGramDrafter(), k=4)
+    assert out == ref
+
+
+def test_speculative_respects_eos_and_gate():
+    from pocketllm_b200.runtime.dspark_gate import DSparkGate
+    from pocketllm_b200.runtime.speculative import ReplayDrafter, speculative_generate
+    prompt = [4, 4, 2]
+    ref = _plain(prompt, 30)
+    eos = ref[7]
+    cut = ref[:ref.index(eos) + 1]
+    out, _ = speculative_generate(_FakeEngine(), prompt, 30, ReplayDrafter(ref[1:], len(prompt) + 1), k=4, eos=eos)
+    assert out == cut
+    gate = DSparkGate()
+    out, st = speculative_generate(_FakeEngine(), prompt, 30, ReplayDrafter(ref[1:], len(prompt) + 1), k=4, gate=gate)
+    assert out == ref and gate.stats["rounds"] == st.rounds
