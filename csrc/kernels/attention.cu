@@ -265,3 +265,68 @@ PK_API int pk_gqa_decode(const void* q, const void* kcache, const void* vcache, 
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant: the split partials live in a fixed array inside the library
+// image instead of a caller-provided workspace. Contract in pk_gqa_decode_static.h.
+#include <cstdio>
+#include <mutex>
+
+#include "pk_gqa_decode_static.h"
+
+namespace {
+static __device__ __align__(256) float g_gqa_static_ws[PK_GQA_STATIC_WS_FLOATS];
+
+constexpr int kMaxStaticDevices = 64;
+float* g_gqa_static_ptr[kMaxStaticDevices] = {};   // device address of the array, per device
+std::mutex g_gqa_static_mu;
+thread_local char g_gqa_static_msg[192] = "";
+}  // namespace
+
+PK_API const char* pk_gqa_decode_static_error(void) { return g_gqa_static_msg; }
+
+PK_API int pk_gqa_decode_static(const void* q, const void* kcache, const void* vcache, const int* pos, int M,
+                                int Hq, int Hkv, int head_dim, int ctx_cap, float scale, int nsplit,
+                                int window, int sink, const void* gate_proj, int ld, void* out,
+                                cudaStream_t stream) {
+  g_gqa_static_msg[0] = 0;
+  if (M < 1 || Hq < 1 || nsplit < 1 || head_dim < 1) {
+    snprintf(g_gqa_static_msg, sizeof g_gqa_static_msg, "pk_gqa_decode_static: M, Hq, nsplit and head_dim must be positive");
+    return PK_ERR_BAD_ARG;
+  }
+  const unsigned long long need = (unsigned long long)M * Hq * nsplit * (head_dim + 2);
+  if (need > (unsigned long long)PK_GQA_STATIC_WS_FLOATS) {
+    snprintf(g_gqa_static_msg, sizeof g_gqa_static_msg,
+             "pk_gqa_decode_static: M*Hq*nsplit*(head_dim+2) = %llu floats exceeds the fixed scratch of %d floats; "
+             "use pk_gqa_decode with your own workspace",
+             need, (int)PK_GQA_STATIC_WS_FLOATS);
+    return PK_ERR_BAD_ARG;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    pk_set_last_cuda_error((int)e);
+    return PK_ERR_CUDA;
+  }
+  if (dev < 0 || dev >= kMaxStaticDevices) {
+    snprintf(g_gqa_static_msg, sizeof g_gqa_static_msg, "pk_gqa_decode_static: device ordinal %d is not supported", dev);
+    return PK_ERR_UNSUPPORTED;
+  }
+  float* ws = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_gqa_static_mu);
+    ws = g_gqa_static_ptr[dev];
+    if (ws == nullptr) {   // first call on this device: resolve the array's device address
+      e = cudaGetSymbolAddress((void**)&ws, g_gqa_static_ws);
+      if (e != cudaSuccess || ws == nullptr) {
+        pk_set_last_cuda_error((int)e);
+        snprintf(g_gqa_static_msg, sizeof g_gqa_static_msg, "pk_gqa_decode_static: cudaGetSymbolAddress failed (%s)",
+                 cudaGetErrorString(e));
+        return PK_ERR_CUDA;
+      }
+      g_gqa_static_ptr[dev] = ws;
+    }
+  }
+  return pk_gqa_decode(q, kcache, vcache, pos, M, Hq, Hkv, head_dim, ctx_cap, scale, nsplit, window, sink, ws,
+                       gate_proj, ld, out, stream);
+}
