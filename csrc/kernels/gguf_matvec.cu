@@ -19,11 +19,12 @@ using namespace pk;
 #include "gguf_codebooks.inc"
 
 enum : int { T_IQ2_XXS = 0, T_Q2_K = 1, T_IQ1_M = 2, T_Q4_K = 3, T_Q5_K = 4, T_IQ2_XS = 5, T_IQ3_XXS = 6,
-             T_IQ4_XS = 7, T_Q6_K = 8, T_Q8_0 = 9, T_BF16 = 10 };
+             T_IQ4_XS = 7, T_Q6_K = 8, T_Q8_0 = 9, T_BF16 = 10, T_MXFP4 = 11 };
+constexpr int T_LAST = T_MXFP4;
 
 __host__ __device__ constexpr int block_bytes(int t) {
   return t == T_IQ2_XXS ? 66 : t == T_Q2_K ? 84 : t == T_IQ1_M ? 56 : t == T_Q4_K ? 144 : t == T_Q5_K ? 176
-       : t == T_IQ2_XS ? 74 : t == T_IQ3_XXS ? 98 : t == T_IQ4_XS ? 136 : t == T_Q6_K ? 210 : t == T_Q8_0 ? 272 : 512;
+       : t == T_IQ2_XS ? 74 : t == T_IQ3_XXS ? 98 : t == T_IQ4_XS ? 136 : t == T_Q6_K ? 210 : t == T_Q8_0 ? 272 : t == T_MXFP4 ? 136 : 512;
 }
 
 __device__ __forceinline__ float ld_f16(const uint8_t* p) {
@@ -58,6 +59,16 @@ __device__ __forceinline__ void decode8(const uint8_t* b, int p, float (&w)[8]) 
   } else if constexpr (TYPE == T_BF16) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) w[i] = __uint_as_float(ld_u16(b + (p * 8 + i) * 2) << 16);
+  } else if constexpr (TYPE == T_MXFP4) {
+    // eight 17-byte groups: one E8M0 scale, then 32 E2M1 nibbles (element 2j low, 2j+1 high)
+    const uint8_t* blk = b + (p >> 2) * 17;
+    const float d = e8m0_to_float(blk[0]);
+    const uint8_t* q = blk + 1 + (p & 3) * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w[2 * i] = d * e2m1_to_float(q[i] & 15);
+      w[2 * i + 1] = d * e2m1_to_float(q[i] >> 4);
+    }
   } else if constexpr (TYPE == T_Q2_K) {
     const int g = p >> 1, half = g >> 3, gi = g & 7, shift = (gi >> 1) * 2;
     const uint8_t* q = b + 16 + half * 32 + (gi & 1) * 16 + (p & 1) * 8;
@@ -191,6 +202,7 @@ __device__ __forceinline__ void dispatch_row(int type, const uint8_t* wrow, cons
     case T_IQ4_XS: row_dot<T_IQ4_XS, M>(wrow, xs, K, lane, acc); break;
     case T_Q6_K: row_dot<T_Q6_K, M>(wrow, xs, K, lane, acc); break;
     case T_Q8_0: row_dot<T_Q8_0, M>(wrow, xs, K, lane, acc); break;
+    case T_MXFP4: row_dot<T_MXFP4, M>(wrow, xs, K, lane, acc); break;
     default: row_dot<T_BF16, M>(wrow, xs, K, lane, acc); break;
   }
 }
@@ -452,6 +464,7 @@ __global__ void __launch_bounds__(256) gguf_dequant_rows_kernel(const uint8_t* W
         case T_IQ4_XS: decode8<T_IQ4_XS>(b, lane, w); break;
         case T_Q6_K: decode8<T_Q6_K>(b, lane, w); break;
         case T_Q8_0: decode8<T_Q8_0>(b, lane, w); break;
+        case T_MXFP4: decode8<T_MXFP4>(b, lane, w); break;
         default: decode8<T_BF16>(b, lane, w); break;
       }
     }
@@ -481,12 +494,12 @@ int launch_linear(const LinearParams& p, int sm_count, cudaStream_t stream) {
 
 }  // namespace
 
-PK_API int pk_gguf_block_bytes(int type) { return (type >= 0 && type <= T_BF16) ? block_bytes(type) : 0; }
+PK_API int pk_gguf_block_bytes(int type) { return (type >= 0 && type <= T_LAST) ? block_bytes(type) : 0; }
 
 // x bf16 [M, K] (M <= 8, M * K * 4 bytes <= 200 KB), W raw rows, K a multiple of 256.
 PK_API int pk_gguf_linear(const void* W, int type, int N, int K, int M, const void* x, const float* gamma, float eps,
                           int epi, void* y, int ldy, int sm_count, cudaStream_t stream) {
-  if (type < 0 || type > T_BF16 || M < 1 || M > 8 || (K & 255) != 0 || N < 1) return PK_ERR_BAD_ARG;
+  if (type < 0 || type > T_LAST || M < 1 || M > 8 || (K & 255) != 0 || N < 1) return PK_ERR_BAD_ARG;
   if ((size_t)M * K * 4 > 200 * 1024) return PK_ERR_UNSUPPORTED;
   if (epi == 1 && (N & 1)) return PK_ERR_BAD_ARG;
   LinearParams p{(const uint8_t*)W, type, N, K, M, (const pk::bf16*)x, gamma, eps, epi, y, ldy};
@@ -551,7 +564,7 @@ PK_API int pk_gguf_moe_forward(const void* W13, const void* W2, int type13, int 
 // (vocabulary-sharded embedding). rows == null means rows 0..nrows-1.
 PK_API int pk_gguf_dequant_rows(const void* W, int type, const int* rows, int nrows, int K, int row_offset,
                                 int table_rows, void* out, cudaStream_t stream) {
-  if (type < 0 || type > T_BF16 || (K & 255) != 0 || nrows < 1) return PK_ERR_BAD_ARG;
+  if (type < 0 || type > T_LAST || (K & 255) != 0 || nrows < 1) return PK_ERR_BAD_ARG;
   gguf_dequant_rows_kernel<<<nrows, 256, 0, stream>>>((const uint8_t*)W, type, rows, nrows, K, row_offset, table_rows,
                                                      (pk::bf16*)out);
   PK_CHECK_LAUNCH();

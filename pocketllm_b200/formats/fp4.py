@@ -31,6 +31,6 @@ def dequantize_e2m1(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     K = half * 2
     lo, hi = packed & 15, packed >> 4
     code = torch.stack([lo, hi], dim=-1).reshape(*lead, K).long()
-    val = E2M1_VALUES[code & 7] * torch.where((code & 8) != 0, -1.0, 1.0)
+    val = E2M1_VALUES.to(code.device)[code & 7] * torch.where((code & 8) != 0, -1.0, 1.0)
     s = torch.pow(2.0, scales.float() - 127.0).repeat_interleave(GROUP, dim=-1)
     return val * s

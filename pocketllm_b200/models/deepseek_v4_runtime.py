@@ -1,0 +1,313 @@
+"""DeepSeek-V4 on the GPU: incremental runtime over the kernels in `ops.dsv4_ops`.
+
+Every piece of per-request state is indexed by token position (window ring, compressed entries,
+compressor rings, indexer keys), so rewinding after a rejected speculative draft is just
+`rollback(position)`: nothing has to be copied or restored. Rings are sized so that the rows of
+one call (at most `max_rows`) never overwrite a row that this call, or a call issued after a
+rewind, still needs.
+
+Per block (reference flow: src/models/deepseek_v4/runtime.py:4423-4476 Block.forward, 1459-1659
+Attention.forward, 3643 MoE.forward):
+
+    hc_pre(+RMSNorm) -> one stacked projection [wq_a | wkv | compressor kv,score | indexer kv,score |
+    indexer head weights] -> q path (norm, wq_b, per-head RMS + RoPE) / kv_prep into the ring /
+    compressor pooling / indexer scores + top-k -> sink-softmax sparse attention (inverse RoPE fused)
+    -> grouped wo_a -> wo_b -> hc_post -> hc_pre(+RMSNorm) -> router (scored or hash) -> FP4 routed
+    experts + shared expert -> hc_post
+
+Dense weights run through the weight-streaming kernel for <= 8 rows and through the tcgen05 GEMM
+for more; routed experts stay FP4 (E2M1 + E8M0 per 32) in HBM and are decoded in registers.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from .. import ops
+from ..ops import dsv4_ops as dk
+from ..ops import gguf_ops as gk
+from . import deepseek_v4 as d4
+
+
+def _cuda_bf16(t: torch.Tensor) -> torch.Tensor:
+    return t.to(device="cuda", dtype=torch.bfloat16).contiguous()
+
+
+class _Lin:
+    """y = x @ W^T for bf16 x [M, K]; W bf16 [N, K] (or FP8 block-128 codes + fp32 scales)."""
+
+    def __init__(self, w: torch.Tensor, scale: torch.Tensor | None = None):
+        if w.dtype == torch.float8_e4m3fn:
+            self.w8, self.scale, self.wb = w.cuda().contiguous(), scale.float().cuda().contiguous(), None
+        else:
+            self.w8, self.scale, self.wb = None, None, _cuda_bf16(w)
+        self.N = w.shape[0]
+
+    def __call__(self, x: torch.Tensor, f32: bool = False) -> torch.Tensor:
+        M = x.shape[0]
+        if M <= 8:
+            return ops.matvec(x, self.w8, self.scale, self.wb, epi=2 if f32 else 0)
+        w = self.wb if self.wb is not None else self.w8
+        if f32 or self.N % 8:
+            y = ops.gemm_umma(x, w, self.scale, epi=ops.EPI_F32)
+            return y if f32 else y.to(torch.bfloat16)
+        return ops.gemm_umma(x, w, self.scale)
+
+
+def pack_mxfp4(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """[N, K/2] nibble pairs + [N, K/32] E8M0 -> [N, K/32 * 17] bytes: scale byte, then 16 nibble bytes, per 32 weights."""
+    N, half = weight.shape
+    w = weight.view(torch.uint8).reshape(N, half // 16, 16)
+    s = scale.view(torch.uint8).reshape(N, half // 16, 1)
+    return torch.cat([s, w], -1).reshape(N, -1).contiguous()
+
+
+class _BlockWeights:
+    def __init__(self, cfg: d4.DSV4Config, W: dict, p: str, layer: int):
+        f32 = lambda n: W[n].float().cuda().contiguous()
+        self.name = p
+        self.ratio = cfg.ratio(layer)
+        self.hash = layer < cfg.n_hash_layers
+        for kind in ("attn", "ffn"):
+            setattr(self, f"hc_{kind}", (f32(f"{p}.hc_{kind}_fn"), f32(f"{p}.hc_{kind}_scale"), f32(f"{p}.hc_{kind}_base")))
+        self.attn_norm, self.ffn_norm = f32(f"{p}.attn_norm.weight"), f32(f"{p}.ffn_norm.weight")
+        a = f"{p}.attn"
+        stack = [W[f"{a}.wq_a.weight"], W[f"{a}.wkv.weight"]]
+        if self.ratio:
+            stack += [W[f"{a}.compressor.wkv.weight"], W[f"{a}.compressor.wgate.weight"]]
+            self.c_ape, self.c_norm = f32(f"{a}.compressor.ape"), f32(f"{a}.compressor.norm.weight")
+        if self.ratio == 4:
+            stack += [W[f"{a}.indexer.compressor.wkv.weight"], W[f"{a}.indexer.compressor.wgate.weight"], W[f"{a}.indexer.weights_proj.weight"]]
+            self.i_ape, self.i_norm = f32(f"{a}.indexer.compressor.ape"), f32(f"{a}.indexer.compressor.norm.weight")
+            self.i_wq_b = _Lin(W[f"{a}.indexer.wq_b.weight"])
+        self.proj = _Lin(torch.cat([t.float() for t in stack], 0))
+        self.q_norm, self.kv_norm = f32(f"{a}.q_norm.weight"), f32(f"{a}.kv_norm.weight")
+        self.wq_b = _Lin(W[f"{a}.wq_b.weight"])
+        self.sink = f32(f"{a}.attn_sink")
+        G = cfg.o_groups
+        self.wo_a = [_Lin(w) for w in W[f"{a}.wo_a.weight"].view(G, cfg.o_lora_rank, -1)]
+        self.wo_b = _Lin(W[f"{a}.wo_b.weight"])
+        f = f"{p}.ffn"
+        self.gate_w = f32(f"{f}.gate.weight")
+        self.gate_bias = f32(f"{f}.gate.bias") if f"{f}.gate.bias" in W else None
+        self.tid2eid = W[f"{f}.gate.tid2eid"].to(torch.int32).cuda().contiguous() if self.hash else None
+        E = cfg.n_routed_experts
+        w13, w2 = [], []
+        for e in range(E):
+            w13.append(torch.cat([pack_mxfp4(W[f"{f}.experts.{e}.w1.weight"], W[f"{f}.experts.{e}.w1.scale"]),
+                                  pack_mxfp4(W[f"{f}.experts.{e}.w3.weight"], W[f"{f}.experts.{e}.w3.scale"])], 0))
+            w2.append(pack_mxfp4(W[f"{f}.experts.{e}.w2.weight"], W[f"{f}.experts.{e}.w2.scale"]))
+        self.w13, self.w2 = torch.stack(w13).cuda().contiguous(), torch.stack(w2).cuda().contiguous()
+        s = f"{f}.shared_experts"
+        self.s_w13 = _Lin(torch.cat([W[f"{s}.w1.weight"].float(), W[f"{s}.w3.weight"].float()], 0))
+        self.s_w2 = _Lin(W[f"{s}.w2.weight"])
+
+
+class _BlockState:
+    def __init__(self, cfg: d4.DSV4Config, ratio: int, max_context: int, max_rows: int):
+        hd = cfg.head_dim
+        self.ring = cfg.window_size + max_rows
+        n_ent = max_context // ratio + 1 if ratio else 0
+        self.kv = torch.zeros(self.ring + n_ent, hd, device="cuda", dtype=torch.bfloat16)
+        if ratio:
+            coff = 2 if ratio == 4 else 1
+            self.c_ring = torch.zeros(2, coff * ratio + max_rows, coff * hd, device="cuda", dtype=torch.float32)
+        if ratio == 4:
+            self.ik = torch.zeros(n_ent, cfg.index_head_dim, device="cuda", dtype=torch.bfloat16)
+            self.i_ring = torch.zeros(2, 2 * ratio + max_rows, 2 * cfg.index_head_dim, device="cuda", dtype=torch.float32)
+
+
+class DSV4Runtime:
+    """`prefill(tokens)` / `forward_rows(tokens)` / `decode(n)`; greedy sampling.
+
+    `forward_rows(tokens)` feeds `len(tokens)` (<= max_rows) tokens at consecutive positions and returns the
+    greedy token after each row; `rollback(position)` rewinds to an earlier position."""
+
+    def __init__(self, cfg: d4.DSV4Config, weights: dict[str, torch.Tensor], *, max_context: int | None = None, max_rows: int = 64):
+        self.cfg = cfg
+        self.max_context = max_context or cfg.max_seq_len
+        self.max_rows = max_rows
+        # when a dict: records every discrete choice (expert ids, selected entries) per block, call by call
+        self.capture: dict | None = None
+        W = weights
+        f32 = lambda n: W[n].float().cuda().contiguous()
+        self.embed = W["embed.weight"].float().cuda()
+        self.blocks = [_BlockWeights(cfg, W, f"layers.{i}", i) for i in range(cfg.n_layers)]
+        self.hc_head = (f32("hc_head_fn"), f32("hc_head_scale"), f32("hc_head_base"))
+        self.norm = f32("norm.weight")
+        self.head = _Lin(W["head.weight"])
+        self.mtp = []
+        for m in range(cfg.n_mtp_layers):
+            p = f"mtp.{m}"
+            if f"{p}.e_proj.weight" not in W:
+                break
+            blk = _BlockWeights(cfg, W, p, cfg.n_layers + m)
+            blk.e_proj, blk.h_proj = _Lin(W[f"{p}.e_proj.weight"]), _Lin(W[f"{p}.h_proj.weight"])
+            blk.enorm, blk.hnorm, blk.norm = f32(f"{p}.enorm.weight"), f32(f"{p}.hnorm.weight"), f32(f"{p}.norm.weight")
+            blk.hc_head = (f32(f"{p}.hc_head_fn"), f32(f"{p}.hc_head_scale"), f32(f"{p}.hc_head_base"))
+            self.mtp.append(blk)
+        pos = torch.arange(self.max_context + max_rows)
+        self.rope = {}
+        for comp in (False, True):
+            ang = d4.rope_angles(cfg, comp, pos)
+            self.rope[comp] = (torch.cos(ang).float().cuda().contiguous(), torch.sin(ang).float().cuda().contiguous())
+        self.reset()
+
+    # -- state ---------------------------------------------------------------------------
+    def reset(self) -> None:
+        cfg = self.cfg
+        self.state = [_BlockState(cfg, b.ratio, self.max_context, self.max_rows) for b in self.blocks]
+        self.mtp_state = [_BlockState(cfg, b.ratio, self.max_context, self.max_rows) for b in self.mtp]
+        self.pos = 0
+        self.mtp_pos = 0
+        self.last_token = -1
+        self.last_hidden: torch.Tensor | None = None
+
+    def rollback(self, position: int) -> None:
+        if not 0 <= position <= self.pos:
+            raise ValueError("rollback target must not lie ahead of the current position")
+        self.pos = position
+        self.mtp_pos = min(self.mtp_pos, position)
+
+    # -- one block -----------------------------------------------------------------------
+    def _attention(self, b: _BlockWeights, st: _BlockState, x: torch.Tensor, pos_t: torch.Tensor, pos0: int) -> torch.Tensor:
+        cfg = self.cfg
+        M, H, hd, rd, ql = x.shape[0], cfg.n_heads, cfg.head_dim, cfg.rope_head_dim, cfg.q_lora_rank
+        cos_t, sin_t = self.rope[b.ratio != 0]
+        A = b.proj(x, f32=True)
+        qr = ops.rmsnorm(A[:, :ql].to(torch.bfloat16).contiguous(), b.q_norm, mode=2, eps=cfg.norm_eps)
+        q = b.wq_b(qr).view(M, H, hd)
+        dk.head_prep(q, pos_t, cos_t, sin_t, rd, dk.PREP_NORM | dk.PREP_ROPE, cfg.norm_eps)
+        dk.kv_prep(A[:, ql:ql + hd].contiguous(), b.kv_norm, pos_t, cos_t, sin_t, rd, st.ring, st.kv, cfg.norm_eps)
+        off = ql + hd
+        sel, all_entries = None, False
+        if b.ratio:
+            C = (2 if b.ratio == 4 else 1) * hd
+            dk.compress(A[:, off:off + 2 * C].contiguous(), b.c_ape, st.c_ring, b.c_norm, cos_t, sin_t, pos0, b.ratio, hd, rd, False,
+                        st.kv[st.ring:], cfg.norm_eps)
+            off += 2 * C
+            all_entries = True
+        if b.ratio == 4:
+            ih, idim = cfg.index_n_heads, cfg.index_head_dim
+            dk.compress(A[:, off:off + 4 * idim].contiguous(), b.i_ape, st.i_ring, b.i_norm, cos_t, sin_t, pos0, 4, idim, rd, True, st.ik,
+                        cfg.norm_eps)
+            off += 4 * idim
+            nmax = (pos0 + M) // 4
+            if nmax > cfg.index_topk:
+                iq = b.i_wq_b(qr).view(M, ih, idim)
+                dk.head_prep(iq, pos_t, cos_t, sin_t, rd, dk.PREP_ROPE | dk.PREP_HADAMARD_FP4)
+                score = dk.index_score(iq, st.ik, A[:, off:], pos_t, 4, nmax, idim ** -0.5 * ih ** -0.5)
+                top, sel = score.topk(cfg.index_topk, dim=-1)
+                sel = torch.where(torch.isinf(top), torch.full_like(sel, -1), sel).to(torch.int32).contiguous()
+                nvalid = ((pos_t + 1) // 4).unsqueeze(1)
+                # rows that see at most index_topk entries take all of them
+                few = nvalid <= cfg.index_topk
+                ar = torch.arange(cfg.index_topk, device="cuda", dtype=torch.int32).unsqueeze(0)
+                sel = torch.where(few, torch.where(ar < nvalid, ar, torch.full_like(ar, -1)), sel).contiguous()
+                all_entries = False
+        if self.capture is not None and b.ratio == 4:
+            rows = [None] * M if sel is None else [[c for c in r if c >= 0] for r in sel.tolist()]
+            self.capture.setdefault(f"{b.name}.attn.index_sel", []).extend(rows)
+        o = dk.sparse_attn(q, st.kv, pos_t, b.sink, cos_t, sin_t, win=cfg.window_size, ring=st.ring, ratio=b.ratio, rd=rd, sel=sel,
+                           all_entries=all_entries)
+        G = cfg.o_groups
+        og = o.view(M, G, H // G * hd).transpose(0, 1).contiguous()
+        oo = torch.cat([b.wo_a[g](og[g]) for g in range(G)], -1)
+        return b.wo_b(oo, f32=True)
+
+    def _ffn(self, b: _BlockWeights, x: torch.Tensor, tok_t: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        cfg = self.cfg
+        if b.hash:
+            ids, w = dk.hash_route(x, b.gate_w, b.tid2eid, tok_t, cfg.score_func, cfg.route_scale)
+        else:
+            ids, w = gk.router_topk(x, b.gate_w, cfg.n_activated_experts, bias=b.gate_bias, score_func=cfg.score_func,
+                                    norm_topk=cfg.score_func != "softmax", route_scale=cfg.route_scale)
+        if self.capture is not None:
+            self.capture.setdefault(f"{b.name}.ffn.route_idx", []).append(ids.clone())
+        seg, tok, rw = gk.group_routes(ids, w, cfg.n_routed_experts)
+        y = gk.gguf_moe_forward(x, self.w_flat(b.w13), self.w_flat(b.w2), "mxfp4", "mxfp4", cfg.n_routed_experts, cfg.moe_inter_dim,
+                                seg, tok, rw, limit=cfg.swiglu_limit)
+        hs = ops.silu_mul(b.s_w13(x), cfg.swiglu_limit)
+        return y, b.s_w2(hs, f32=True)
+
+    @staticmethod
+    def w_flat(t: torch.Tensor) -> torch.Tensor:
+        return t.view(-1)
+
+    def _block(self, b: _BlockWeights, st: _BlockState, h: torch.Tensor, pos_t: torch.Tensor, tok_t: torch.Tensor, pos0: int) -> torch.Tensor:
+        cfg = self.cfg
+        kw = dict(iters=cfg.hc_sinkhorn_iters, hc_eps=cfg.hc_eps, norm_eps=cfg.norm_eps)
+        x, post, comb = dk.hc_pre(h, *b.hc_attn, b.attn_norm, **kw)
+        y = self._attention(b, st, x, pos_t, pos0)
+        h = dk.hc_post(y, h, post, comb)
+        x, post, comb = dk.hc_pre(h, *b.hc_ffn, b.ffn_norm, **kw)
+        y, y2 = self._ffn(b, x, tok_t)
+        return dk.hc_post(y, h, post, comb, y2=y2)
+
+    def _logits(self, h: torch.Tensor, hc_head, norm: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        x = dk.hc_pre(h, *hc_head, norm, iters=0, hc_eps=cfg.hc_eps, norm_eps=cfg.norm_eps, head=True)
+        return self.head(x, f32=True)
+
+    # -- public --------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward_logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        """Feed tokens at positions pos..pos+len-1 (any length; split into calls of max_rows); fp32 logits per row."""
+        out = []
+        toks = list(tokens)
+        hidden = []
+        for i in range(0, len(toks), self.max_rows):
+            part = toks[i:i + self.max_rows]
+            M, pos0 = len(part), self.pos
+            if pos0 + M > self.max_context:
+                raise ValueError("exceeds max_context")
+            tok_t = torch.tensor(part, device="cuda", dtype=torch.int32)
+            pos_t = torch.arange(pos0, pos0 + M, device="cuda", dtype=torch.int32)
+            h = self.embed[tok_t.long()].unsqueeze(1).repeat(1, self.cfg.hc_mult, 1).contiguous()
+            for b, st in zip(self.blocks, self.state):
+                h = self._block(b, st, h, pos_t, tok_t, pos0)
+            hidden.append(h)
+            out.append(self._logits(h, self.hc_head, self.norm))
+            self.pos += M
+        self.last_hidden = torch.cat(hidden, 0)
+        return torch.cat(out, 0)
+
+    def forward_rows(self, tokens: Sequence[int]) -> list[int]:
+        nxt = self.forward_logits(tokens).argmax(-1).tolist()
+        self.last_token = nxt[-1]
+        return nxt
+
+    def prefill(self, tokens: Sequence[int]) -> int:
+        self.reset()
+        return self.forward_rows(tokens)[-1]
+
+    def decode(self, n: int) -> list[int]:
+        out = []
+        for _ in range(n):
+            out.append(self.forward_rows([self.last_token])[0])
+        return out
+
+    def generate(self, prompt: Sequence[int], n: int) -> list[int]:
+        first = self.prefill(prompt)
+        return [first] + self.decode(n - 1)
+
+    # -- MTP draft -----------------------------------------------------------------------
+    @torch.no_grad()
+    def mtp_forward(self, hidden: torch.Tensor, next_tokens: Sequence[int], m: int = 0) -> torch.Tensor:
+        """MTP block over rows at positions mtp_pos..: row t takes the backbone hidden of position t and the
+        token of position t+1; returns fp32 logits for position t+2."""
+        cfg, b, st = self.cfg, self.mtp[m], self.mtp_state[m]
+        M, pos0 = hidden.shape[0], self.mtp_pos
+        if M > self.max_rows:
+            raise ValueError("mtp_forward: at most max_rows rows per call")
+        tok_t = torch.tensor(list(next_tokens), device="cuda", dtype=torch.int32)
+        pos_t = torch.arange(pos0, pos0 + M, device="cuda", dtype=torch.int32)
+        e = ops.rmsnorm(self.embed[tok_t.long()].to(torch.bfloat16).contiguous(), b.enorm, mode=2, eps=cfg.norm_eps)
+        hn = ops.rmsnorm(hidden.reshape(M * cfg.hc_mult, cfg.dim).to(torch.bfloat16).contiguous(), b.hnorm, mode=2, eps=cfg.norm_eps)
+        hp = b.h_proj(hn, f32=True)
+        h = (b.e_proj(e, f32=True).unsqueeze(1) + hp.view(M, cfg.hc_mult, cfg.dim)).contiguous()
+        h = self._block(b, st, h, pos_t, tok_t, pos0)
+        self.mtp_pos += M
+        x = dk.hc_pre(h, *b.hc_head, b.norm, iters=0, hc_eps=cfg.hc_eps, norm_eps=cfg.norm_eps, head=True)
+        return self.head(x, f32=True)

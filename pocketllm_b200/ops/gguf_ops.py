@@ -10,7 +10,7 @@ from . import _check, _ptr, _sm_count, _stream
 from . import lib as _lib
 
 # device type ids (reference: src/loader/gguf/quant_types.py, plus q8_0 and bf16)
-DEVICE_TYPE = {"iq2_xxs": 0, "q2_k": 1, "iq1_m": 2, "q4_k": 3, "q5_k": 4, "iq2_xs": 5, "iq3_xxs": 6, "iq4_xs": 7,
+DEVICE_TYPE = {"iq2_xxs": 0, "q2_k": 1, "iq1_m": 2, "q4_k": 3, "q5_k": 4, "iq2_xs": 5, "iq3_xxs": 6, "iq4_xs": 7, "mxfp4": 11,
                "q6_k": 8, "q8_0": 9, "bf16": 10}
 SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
 
