@@ -311,3 +311,38 @@ class DSV4Runtime:
         self.mtp_pos += M
         x = dk.hc_pre(h, *b.hc_head, b.norm, iters=0, hc_eps=cfg.hc_eps, norm_eps=cfg.norm_eps, head=True)
         return self.head(x, f32=True)
+
+    # -- speculative decoding with the MTP block ---------------------------------------------
+    @torch.no_grad()
+    def generate_mtp(self, prompt: Sequence[int], n: int) -> tuple[list[int], dict]:
+        """Greedy generation where the MTP block drafts one token per round and the backbone verifies
+        [last token, draft] in one two-row pass (reference loop: src/runtime/generation.py MTP speculative
+        path; Transformer.draft_with_mtp, runtime.py:4882-4901). A rejected draft costs nothing but the
+        rewind: all state is position indexed. Returns (tokens, {"rounds", "accepted"})."""
+        if not self.mtp:
+            raise RuntimeError("checkpoint has no MTP block")
+        prompt = list(prompt)
+        out = [self.prefill(prompt)]
+        nxt = prompt[1:] + out[:1]
+        lg = None
+        for i in range(0, len(prompt), self.max_rows):
+            lg = self.mtp_forward(self.last_hidden[i:i + self.max_rows], nxt[i:i + self.max_rows])
+        draft = int(lg[-1].argmax())
+        stats = {"rounds": 0, "accepted": 0}
+        while len(out) < n:
+            p = self.pos
+            pred = self.forward_rows([out[-1], draft])
+            hidden = self.last_hidden
+            stats["rounds"] += 1
+            if pred[0] == draft:
+                stats["accepted"] += 1
+                new = [draft, pred[1]]
+                lg = self.mtp_forward(hidden, new)
+            else:
+                new = [pred[0]]
+                self.rollback(p + 1)
+                self.last_token = pred[0]
+                lg = self.mtp_forward(hidden[:1], new)
+            out += new
+            draft = int(lg[-1].argmax())
+        return out[:n], stats

@@ -256,3 +256,25 @@ def test_mtp_block_matches_oracle(tiny):
     rt.forward_logits(toks)
     got = torch.cat([rt.mtp_forward(rt.last_hidden[i:min(i + 16, 29)], toks[1 + i:1 + min(i + 16, 29)]) for i in range(0, 29, 16)], 0)
     assert _rel(got, want) < 5e-2
+
+
+@pytest.mark.gpu
+def test_mtp_speculative_generation_equals_plain_greedy(tiny):
+    from pocketllm_b200.models.deepseek_v4_runtime import DSV4Runtime
+    cfg, W = tiny
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, cfg.vocab_size, (37,), generator=g).tolist()
+    rt = DSV4Runtime(cfg, W, max_context=128, max_rows=16)
+    plain = rt.generate(prompt, 24)
+    spec, stats = rt.generate_mtp(prompt, 24)
+    assert spec == plain
+    assert stats["rounds"] >= 12 and 0 <= stats["accepted"] <= stats["rounds"]
+    # a drafter that is always right halves the number of backbone passes: feed the known continuation
+    rt.prefill(prompt)
+    pos, passes, out = rt.pos, 0, plain[:1]
+    while len(out) < 23:
+        pred = rt.forward_rows([out[-1], plain[len(out)]])
+        passes += 1
+        assert pred[0] == plain[len(out)]
+        out += [plain[len(out)], pred[1]]
+    assert out == plain[:len(out)] and passes <= 12
