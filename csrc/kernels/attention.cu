@@ -31,6 +31,8 @@ struct QkParams {
 };
 
 __global__ void __launch_bounds__(kD) qk_norm_rope_append_kernel(const QkParams p) {
+  pk::pdl_wait();
+  pk::pdl_trigger();
   const int m = blockIdx.x, hh = blockIdx.y, d = threadIdx.x;
   __shared__ float red[40];
   __shared__ float sy[kD];
@@ -79,6 +81,8 @@ struct DecodeParams {
 
 template <int G>
 __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const DecodeParams p) {
+  pk::pdl_wait();
+  pk::pdl_trigger();
   const int hk = blockIdx.x, split = blockIdx.y, m = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int l16 = lane & 15, khalf = lane >> 4;
@@ -205,6 +209,8 @@ struct MergeParams {
 };
 
 __global__ void __launch_bounds__(kD) gqa_merge_kernel(const MergeParams p) {
+  pk::pdl_wait();
+  pk::pdl_trigger();
   const int m = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const float* w = p.ws + ((size_t)m * p.Hq + h) * p.nsplit * (kD + 2);
   float nm = -INFINITY;
@@ -234,8 +240,7 @@ PK_API int pk_qk_norm_rope_append(const void* proj, int ld, int M, int Hq, int H
   if (M < 1 || rotary_dim < 0 || rotary_dim > kD || (rotary_dim & 1)) return PK_ERR_BAD_ARG;
   QkParams p{(const pk::bf16*)proj, ld, M, Hq, Hkv, pos, q_gamma, k_gamma, eps, rotary_dim, theta,
              (pk::bf16*)q_out, (pk::bf16*)kcache, (pk::bf16*)vcache, ctx_cap};
-  qk_norm_rope_append_kernel<<<dim3(M, Hq + Hkv), kD, 0, stream>>>(p);
-  PK_CHECK_LAUNCH();
+  PK_LAUNCH_PDL(qk_norm_rope_append_kernel, dim3(M, Hq + Hkv), dim3(kD), 0, stream, p);
   return PK_OK;
 }
 
@@ -250,19 +255,18 @@ PK_API int pk_gqa_decode(const void* q, const void* kcache, const void* vcache, 
                  ctx_cap, scale, nsplit, window, sink, ws};
   const dim3 grid(Hkv, nsplit, M);
   switch (Hq / Hkv) {
-    case 1: gqa_decode_split_kernel<1><<<grid, 128, 0, stream>>>(p); break;
-    case 2: gqa_decode_split_kernel<2><<<grid, 128, 0, stream>>>(p); break;
-    case 3: gqa_decode_split_kernel<3><<<grid, 128, 0, stream>>>(p); break;
-    case 4: gqa_decode_split_kernel<4><<<grid, 128, 0, stream>>>(p); break;
-    case 5: gqa_decode_split_kernel<5><<<grid, 128, 0, stream>>>(p); break;
-    case 6: gqa_decode_split_kernel<6><<<grid, 128, 0, stream>>>(p); break;
-    case 8: gqa_decode_split_kernel<8><<<grid, 128, 0, stream>>>(p); break;
+    case 1: PK_LAUNCH_PDL(gqa_decode_split_kernel<1>, grid, dim3(128), 0, stream, p); break;
+    case 2: PK_LAUNCH_PDL(gqa_decode_split_kernel<2>, grid, dim3(128), 0, stream, p); break;
+    case 3: PK_LAUNCH_PDL(gqa_decode_split_kernel<3>, grid, dim3(128), 0, stream, p); break;
+    case 4: PK_LAUNCH_PDL(gqa_decode_split_kernel<4>, grid, dim3(128), 0, stream, p); break;
+    case 5: PK_LAUNCH_PDL(gqa_decode_split_kernel<5>, grid, dim3(128), 0, stream, p); break;
+    case 6: PK_LAUNCH_PDL(gqa_decode_split_kernel<6>, grid, dim3(128), 0, stream, p); break;
+    case 8: PK_LAUNCH_PDL(gqa_decode_split_kernel<8>, grid, dim3(128), 0, stream, p); break;
     default: return PK_ERR_UNSUPPORTED;
   }
   PK_CHECK_LAUNCH();
   MergeParams mp{ws, nsplit, Hq, (const pk::bf16*)gate_proj, ld, (pk::bf16*)out};
-  gqa_merge_kernel<<<dim3(M, Hq), kD, 0, stream>>>(mp);
-  PK_CHECK_LAUNCH();
+  PK_LAUNCH_PDL(gqa_merge_kernel, dim3(M, Hq), dim3(kD), 0, stream, mp);
   return PK_OK;
 }
 

@@ -42,6 +42,8 @@ struct DeltaParams {
 // (256 threads each), so q/k are convolved and normalised once and no two blocks touch
 // the same conv-tail rows.
 __global__ void __launch_bounds__(512) deltanet_seq_kernel(const DeltaParams p) {
+  pk::pdl_wait();
+  pk::pdl_trigger();
   const int hk = blockIdx.x;
   const int rep = p.value_heads / p.key_heads;
   const int KD = p.key_heads * kDk, VD = p.value_heads * kDv;
@@ -195,7 +197,6 @@ PK_API int pk_deltanet_seq(const void* proj, int ld, int T, int key_heads, int v
   p.eps = eps;
   p.state = state;
   p.out = (pk::bf16*)out;
-  deltanet_seq_kernel<<<key_heads, kThreads * rep, 0, stream>>>(p);
-  PK_CHECK_LAUNCH();
+  PK_LAUNCH_PDL(deltanet_seq_kernel, dim3(key_heads), dim3(kThreads * rep), 0, stream, p);
   return PK_OK;
 }

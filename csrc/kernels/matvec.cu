@@ -45,6 +45,8 @@ struct MatvecParams {
   bf16* hidden_out;      // [M, K]: x before the norm, written by block 0 (may be null)
   const float* gamma;    // [K] or null
   int norm_mode;         // 1: *(1+gamma), 2: *gamma
+  int flat_path;         // 1: blocks own whole row pairs and their warps split the block's k-iterations evenly
+  unsigned long long* dbg;  // optional phase timestamps (see pk_matvec_set_debug); null in normal use
   float eps;
   PkWait wait;
   // epilogue
@@ -234,6 +236,7 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.K, kc = p.kc;
   const bool swiglu = p.epi == 1;
+  if (p.dbg != nullptr && tid == 0) atomicMin(p.dbg + 0, global_timer_ns());
   const int half_n = p.N >> 1;
   // Row pairs: a warp owns two output rows at a time (gate_j and up_j for SwiGLU, else
   // rows 2g and 2g+1), so that every staged activation is read once per two weight rows.
@@ -248,7 +251,28 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
   // row pair before the prologue so that the HBM latency overlaps the norm.
   Fp8Batch bt;
   bool have_pre = false;
-  {
+  // Flat path: the block owns row pairs [g_lo, g_hi); their k-iterations, laid end to end, are cut
+  // into one contiguous range per warp, so every warp streams the same number of bytes whatever the
+  // row count. A warp adds the partial sums of each row pair it touches into shared memory.
+  const int iters_all = (K + 511) >> 9;
+  const int g_lo = (int)(((long long)blockIdx.x * n_groups) / gridDim.x);
+  const int g_hi = (int)(((long long)(blockIdx.x + 1) * n_groups) / gridDim.x);
+  const int flat_total = (g_hi - g_lo) * iters_all;
+  const int flat_begin = (int)(((long long)warp * flat_total) / kWarps);
+  const int flat_end = (int)(((long long)(warp + 1) * flat_total) / kWarps);
+  if (p.flat_path) {
+    if (flat_begin < flat_end) {
+      const int gl = flat_begin / iters_all, it = flat_begin - gl * iters_all, g0 = g_lo + gl;
+      const int it_stop = min(iters_all, it + (flat_end - flat_begin));
+      const int r0 = swiglu ? g0 : 2 * g0;
+      if (r0 < p.N) {
+        const int r1c = swiglu ? g0 + half_n : (2 * g0 + 1 < p.N ? 2 * g0 + 1 : r0);
+        load_fp8_batch(bt, p.W + (size_t)r0 * K, p.W + (size_t)r1c * K, p.scale + (size_t)(r0 >> 7) * kb_count,
+                       p.scale + (size_t)(r1c >> 7) * kb_count, it, min(K, it_stop << 9), lane);
+        have_pre = true;
+      }
+    }
+  } else {
     const int g0 = gwarp;
     const int r0 = swiglu ? g0 : 2 * g0;
     if (g0 < n_groups && r0 < p.N) {
@@ -259,6 +283,11 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
     }
   }
 
+  // Programmatic dependent launch (when enabled): this grid may have been scheduled while the
+  // previous kernel of the stream was still draining. Everything above touched weights only;
+  // activations, partial sums and every output are behind this point.
+  pdl_wait();
+  pdl_trigger();
   if (p.parts != nullptr && p.wait.flag != nullptr) {
     if (tid == 0) wait_all_ranks(p.wait);
     __syncthreads();
@@ -337,6 +366,126 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
     __syncthreads();
   }
 
+  if (p.dbg != nullptr && tid == 0) {
+    atomicMin(p.dbg + 1, global_timer_ns());
+    atomicMax(p.dbg + 2, global_timer_ns());
+  }
+  if (p.flat_path) {
+    float* s_acc = scratch;                         // [row pairs of the block][2][M]; the scratch row is free now
+    const int ngb = g_hi - g_lo;
+    __shared__ int s_edge_g[kWarps][2];
+    __shared__ float s_edge_v[kWarps][2][2 * M];
+    for (int i = tid; i < ngb * 2 * M; i += kThreads) s_acc[i] = 0.f;
+    if (tid < kWarps * 2) s_edge_g[tid >> 1][tid & 1] = -1;
+    __syncthreads();
+    int pos = flat_begin;
+    while (pos < flat_end) {
+      const int gl = pos / iters_all, it = pos - gl * iters_all, g = g_lo + gl;
+      const int it_stop = min(iters_all, it + (flat_end - pos));
+      const int klim = min(K, it_stop << 9);
+      const int r0 = swiglu ? g : 2 * g;
+      const int r1 = swiglu ? g + half_n : 2 * g + 1;
+      float a0[M], a1[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) a0[m] = a1[m] = 0.f;
+      if (r0 < p.N) {
+        const int r1c = r1 < p.N ? r1 : r0;
+        const uint8_t* w0p = p.W + (size_t)r0 * K;
+        const uint8_t* w1p = p.W + (size_t)r1c * K;
+        const float* s0p = p.scale + (size_t)(r0 >> 7) * kb_count;
+        const float* s1p = p.scale + (size_t)(r1c >> 7) * kb_count;
+        bool loaded = have_pre && pos == flat_begin;
+#pragma unroll 1
+        for (int it0 = it; it0 < it_stop; it0 += 4) {
+          if (!loaded) load_fp8_batch(bt, w0p, w1p, s0p, s1p, it0, klim, lane);
+          loaded = false;
+          consume_fp8_batch<M>(bt, xs, kc, it0, it_stop, lane, a0, a1);
+        }
+      } else {
+        const int r1c = r1 < total_rows ? r1 : r0;
+        const bf16* w0p = p.Wb + (size_t)(r0 - p.N) * K;
+        const bf16* w1p = p.Wb + (size_t)(r1c - p.N) * K;
+#pragma unroll 2
+        for (int i2 = it; i2 < it_stop; ++i2) {
+          const int ka = (i2 << 9) + (lane << 4);
+          if (ka < K) {
+            const uint4 w00 = __ldg(reinterpret_cast<const uint4*>(w0p + ka));
+            const uint4 w01 = __ldg(reinterpret_cast<const uint4*>(w0p + ka + 8));
+            const uint4 w10 = __ldg(reinterpret_cast<const uint4*>(w1p + ka));
+            const uint4 w11 = __ldg(reinterpret_cast<const uint4*>(w1p + ka + 8));
+            const int base = (i2 << 9) + (lane << 3);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              const uint4 x0 = *reinterpret_cast<const uint4*>(xs + m * kc + base);
+              const uint4 x1 = *reinterpret_cast<const uint4*>(xs + m * kc + base + 256);
+              a0[m] += dot16_bf16(w00, w01, x0, x1);
+              a1[m] += dot16_bf16(w10, w11, x0, x1);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        a0[m] = warp_sum(a0[m]);
+        a1[m] = warp_sum(a1[m]);
+      }
+      if (lane == 0) {
+        // A row pair wholly inside this warp's range has one writer. Only the first and the last
+        // segment of a range can be partial; they go to this warp's two edge slots and are added in
+        // warp order below, so the result does not depend on timing.
+        const bool whole = it == 0 && it_stop == iters_all;
+        const int e = pos == flat_begin ? 0 : 1;
+        float* dst0 = whole ? s_acc + (gl * 2) * M : &s_edge_v[warp][e][0];
+        float* dst1 = whole ? s_acc + (gl * 2 + 1) * M : &s_edge_v[warp][e][M];
+        if (!whole) s_edge_g[warp][e] = gl;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          dst0[m] = a0[m];
+          dst1[m] = a1[m];
+        }
+      }
+      pos += it_stop - it;
+    }
+    if (p.dbg != nullptr && lane == 0) {
+      atomicMin(p.dbg + 3, global_timer_ns());
+      atomicMax(p.dbg + 4, global_timer_ns());
+    }
+    __syncthreads();
+    for (int idx = tid; idx < ngb * M; idx += kThreads) {
+      const int gl = idx / M, m = idx - gl * M, g = g_lo + gl;
+      float v0 = s_acc[(gl * 2) * M + m], v1 = s_acc[(gl * 2 + 1) * M + m];
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w)
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          if (s_edge_g[w][e] == gl) {
+            v0 += s_edge_v[w][e][m];
+            v1 += s_edge_v[w][e][M + m];
+          }
+      v0 *= s_c[m];
+      v1 *= s_c[m];
+      if (swiglu) {
+        p.y_bf16[(size_t)m * p.ldy + g] = __float2bfloat16(silu(v0) * v1);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int n = 2 * g + r;
+          if (n >= total_rows) continue;
+          const float v = r == 0 ? v0 : v1;
+          if (p.epi == 0) {
+            p.y_bf16[(size_t)m * p.ldy + n] = __float2bfloat16(v);
+          } else if (p.epi == 2) {
+            p.y_f32[(size_t)m * p.ldy + n] = v;
+          } else {
+            const size_t off = ((size_t)p.push.rank * M + m) * p.ldy + n;
+            for (int pr = 0; pr < p.push.world; ++pr) p.push.dst[pr][off] = v;
+          }
+        }
+      }
+    }
+    if (p.epi == 3) publish_when_grid_done(p.push);
+    return;
+  }
   float acc[2][M];
 #pragma unroll
   for (int r = 0; r < 2; ++r)
@@ -454,6 +603,10 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
     }
   }
 
+  if (p.dbg != nullptr && lane == 0) {
+    atomicMin(p.dbg + 3, global_timer_ns());
+    atomicMax(p.dbg + 4, global_timer_ns());
+  }
   if (p.epi == 3) publish_when_grid_done(p.push);
 }
 
@@ -472,9 +625,17 @@ int launch_m(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
     smem = (size_t)M * p.kc * 2;
   }
   int blocks = (groups + kWarps - 1) / kWarps;
+  p.flat_path = 0;
   if (p.single_chunk) {
     const int cap = (sm_count > 0 ? sm_count : 148) * 2;
-    if (blocks > cap) blocks = cap;
+    const int fb = groups < cap ? groups : cap;
+    const int per_block = (groups + fb - 1) / fb;
+    if ((size_t)per_block * 2 * M <= (size_t)p.K) {   // the block's accumulators reuse the scratch row
+      p.flat_path = 1;
+      blocks = fb;
+    } else if (blocks > cap) {
+      blocks = cap;
+    }
   }  // chunked: exactly one group per warp (one accumulator set per warp)
   if (blocks < 1) blocks = 1;
   static bool configured = false;
@@ -485,12 +646,17 @@ int launch_m(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
     }
     configured = true;
   }
-  matvec_kernel<M><<<blocks, kThreads, smem, stream>>>(p);
-  PK_CHECK_LAUNCH();
+  PK_LAUNCH_PDL(matvec_kernel<M>, dim3(blocks), dim3(kThreads), smem, stream, p);
   return PK_OK;
 }
 
+unsigned long long* g_matvec_dbg = nullptr;
 }  // namespace
+
+// Phase timestamps for tuning: `buf` (device, 5 x u64, caller presets [0],[1],[3] to ~0 and [2],[4] to 0)
+// receives %globaltimer values: earliest block entry, earliest / latest end of the activation staging,
+// earliest / latest warp finish. Pass null to switch the stamps off (the default).
+PK_API void pk_matvec_set_debug(void* buf) { g_matvec_dbg = (unsigned long long*)buf; }
 
 PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, int Nb, int K, int M,
                      const void* x_in, const float* parts, int nparts, void* hidden_out,
@@ -517,6 +683,7 @@ PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, i
   p.hidden_out = (pk::bf16*)hidden_out;
   p.gamma = gamma;
   p.norm_mode = norm_mode;
+  p.dbg = g_matvec_dbg;
   p.eps = eps;
   if (wait) p.wait = *wait;
   p.epi = epi;

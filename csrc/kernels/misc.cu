@@ -160,7 +160,7 @@ __global__ void copy_int_kernel(const int* src, int* dst, int n) {
 PK_API int pk_embedding(const int* tokens, int M, const void* table, int dim, int vocab_start,
                         int vocab_rows, void* out_bf16, float* out_f32, cudaStream_t stream) {
   if (M < 1) return PK_ERR_BAD_ARG;
-  embedding_kernel<<<M, 256, 0, stream>>>(tokens, (const pk::bf16*)table, dim, vocab_start, vocab_rows,
+  PK_LAUNCH(embedding_kernel, dim3(M), dim3(256), 0, stream, tokens, (const pk::bf16*)table, dim, vocab_start, vocab_rows,
                                           (pk::bf16*)out_bf16, out_f32);
   PK_CHECK_LAUNCH();
   return PK_OK;
@@ -197,7 +197,7 @@ PK_API int pk_rmsnorm(const void* x, const float* parts, int nparts, int M, int 
       configured = smem;
     }
   }
-  rmsnorm_kernel<<<M, 256, smem, stream>>>(p);
+  PK_LAUNCH(rmsnorm_kernel, dim3(M), dim3(256), smem, stream, p);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
@@ -213,10 +213,10 @@ PK_API int pk_silu_mul(const void* gate_up, int M, int inter, void* out, float l
 PK_API int pk_argmax(const float* logits, int ld, int M, int n, int id_offset, int nblocks, float* cand_val,
                      int* cand_idx, float* out_val, int* out_idx, cudaStream_t stream) {
   if (M < 1 || n < 1 || nblocks < 1) return PK_ERR_BAD_ARG;
-  argmax_stage1<<<dim3(nblocks, M), 256, 0, stream>>>(logits, ld, n, id_offset, cand_val, cand_idx);
+  PK_LAUNCH(argmax_stage1, dim3(nblocks, M), dim3(256), 0, stream, logits, ld, n, id_offset, cand_val, cand_idx);
   PK_CHECK_LAUNCH();
   if (out_idx != nullptr) {
-    argmax_stage2<<<M, 32, 0, stream>>>(cand_val, cand_idx, nblocks, out_val, out_idx);
+    PK_LAUNCH(argmax_stage2, dim3(M), dim3(32), 0, stream, cand_val, cand_idx, nblocks, out_val, out_idx);
     PK_CHECK_LAUNCH();
   }
   return PK_OK;
@@ -224,25 +224,25 @@ PK_API int pk_argmax(const float* logits, int ld, int M, int n, int id_offset, i
 
 PK_API int pk_argmax_merge(const float* cand_val, const int* cand_idx, int M, int ncand, float* out_val,
                            int* out_idx, cudaStream_t stream) {
-  argmax_stage2<<<M, 32, 0, stream>>>(cand_val, cand_idx, ncand, out_val, out_idx);
+  PK_LAUNCH(argmax_stage2, dim3(M), dim3(32), 0, stream, cand_val, cand_idx, ncand, out_val, out_idx);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
 
 PK_API int pk_bump_epoch(uint32_t* epoch, cudaStream_t stream) {
-  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch);
+  PK_LAUNCH(bump_epoch_kernel, dim3(1), dim3(1), 0, stream, epoch);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
 
 PK_API int pk_add_int(int* p, int n, int delta, cudaStream_t stream) {
-  add_int_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p, n, delta);
+  PK_LAUNCH(add_int_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, p, n, delta);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
 
 PK_API int pk_copy_int(const int* src, int* dst, int n, cudaStream_t stream) {
-  copy_int_kernel<<<(n + 127) / 128, 128, 0, stream>>>(src, dst, n);
+  PK_LAUNCH(copy_int_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, src, dst, n);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
@@ -356,7 +356,7 @@ PK_API int pk_iota_int(int* p, int n, const int* base_dev, int base_host, cudaSt
   return PK_OK;
 }
 PK_API int pk_store_token(const int* token, int* out, int* counter, int cap, cudaStream_t stream) {
-  store_token_kernel<<<1, 1, 0, stream>>>(token, out, counter, cap);
+  PK_LAUNCH(store_token_kernel, dim3(1), dim3(1), 0, stream, token, out, counter, cap);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
