@@ -5,7 +5,9 @@
 #include <string>
 
 #include "json.hpp"
+#include "gguf_reader.hpp"
 #include "qwen_engine.hpp"
+#include "sampler.hpp"
 
 #define PK_EAPI extern "C" __attribute__((visibility("default")))
 
@@ -163,4 +165,46 @@ PK_EAPI int pk_ipc_close(void* p) {
     cudaError_t e = cudaIpcCloseMemHandle(p);
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaIpcCloseMemHandle: ") + cudaGetErrorString(e));
   });
+}
+
+// Host sampler (greedy when temperature <= 0). `rng_state` is advanced in place and must be non-zero.
+PK_EAPI int pk_sample_token(const float* logits, int n, float temperature, float top_p, int top_k, uint64_t* rng_state) {
+  pk::SamplerConfig c;
+  c.temperature = temperature;
+  c.top_p = top_p;
+  c.top_k = top_k;
+  return pk::sample_token(logits, n, c, *rng_state);
+}
+
+// Native GGUF reader: returns the metadata plus the tensor table as a JSON string owned by the
+// calling thread (valid until its next call), or null on error.
+PK_EAPI const char* pk_gguf_describe(const char* path) {
+  thread_local std::string out;
+  const int rc = guarded([&] {
+    pk::GgufFile f(path);
+    pk::Json j = pk::Json::object();
+    j["version"] = pk::Json((int64_t)f.version());
+    j["alignment"] = pk::Json((int64_t)f.alignment());
+    j["metadata"] = f.metadata();
+    pk::Json ts = pk::Json::array();
+    for (const auto& t : f.tensors()) {
+      pk::Json e = pk::Json::object();
+      e["name"] = pk::Json(t.name);
+      e["type"] = pk::Json(pk::ggml_type_name(t.type));
+      pk::Json dims = pk::Json::array();
+      for (uint64_t d : t.dims) dims.push_back(pk::Json((int64_t)d));
+      e["dims"] = dims;
+      e["offset"] = pk::Json((int64_t)t.offset);
+      e["nbytes"] = pk::Json((int64_t)t.nbytes);
+      // first bytes of the data, so that callers can check the mapping
+      const uint8_t* p = f.data(t);
+      int64_t sum = 0;
+      for (uint64_t i = 0; i < (t.nbytes < 64 ? t.nbytes : 64); ++i) sum += p[i];
+      e["head_sum"] = pk::Json(sum);
+      ts.push_back(e);
+    }
+    j["tensors"] = ts;
+    out = j.dump();
+  });
+  return rc == 0 ? out.c_str() : nullptr;
 }

@@ -14,6 +14,7 @@
 #include <cstring>
 #include <fstream>
 #include <iostream>
+#include <map>
 #include <memory>
 #include <sstream>
 #include <stdexcept>
@@ -21,7 +22,9 @@
 #include <vector>
 
 #include "control_plane.hpp"
+#include "gguf_reader.hpp"
 #include "json.hpp"
+#include "openai_server.hpp"
 #include "qwen_config.hpp"
 #include "qwen_engine.hpp"
 #include "safetensors.hpp"
@@ -34,6 +37,12 @@ struct Args {
   int window = 0, sink = 0;
   long random_seed = -1;
   bool benchmark_27b = false, dump_config = false, inspect = false, persistent_stdin = false, no_graph = false;
+  // serving
+  bool serve = false, allow_shutdown = false, list_tensors = false;
+  std::string host = "127.0.0.1", sidecar_python = "python", tokenizer = "chars", chat_format = "qwen", model_name = "pocketllm-b200";
+  std::string fake_script, inspect_gguf;
+  bool fake_engine = false;
+  int port = 8000;
 };
 
 void usage() {
@@ -43,7 +52,9 @@ void usage() {
                "  --tp-world N --tp-rank R --device D --nccl-id-path PATH\n"
                "  --max-context N --prefill-chunk-tokens N --no-cuda-graph\n"
                "  --qwen-attention-window N --qwen-attention-sink-tokens N\n"
-               "  --qwen-persistent-stdin | --dump-config | --inspect\n");
+               "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
+               "  --serve [--host H --port P --model-name N --tokenizer chars|hf:DIR|gguf:FILE --chat-format qwen|glm|minimax|dsv4\n"
+               "           --sidecar-python EXE --fake-engine-script TEXT --allow-shutdown]\n");
 }
 
 Args parse(int argc, char** argv) {
@@ -73,6 +84,17 @@ Args parse(int argc, char** argv) {
     else if (f == "--inspect") a.inspect = true;
     else if (f == "--qwen-persistent-stdin") a.persistent_stdin = true;
     else if (f == "--no-cuda-graph") a.no_graph = true;
+    else if (f == "--serve") a.serve = true;
+    else if (f == "--host") a.host = need(i);
+    else if (f == "--port") a.port = std::stoi(need(i));
+    else if (f == "--model-name") a.model_name = need(i);
+    else if (f == "--tokenizer") a.tokenizer = need(i);
+    else if (f == "--chat-format") a.chat_format = need(i);
+    else if (f == "--sidecar-python") a.sidecar_python = need(i);
+    else if (f == "--fake-engine-script") { a.fake_script = need(i); a.fake_engine = true; }
+    else if (f == "--allow-shutdown") a.allow_shutdown = true;
+    else if (f == "--inspect-gguf") a.inspect_gguf = need(i);
+    else if (f == "--tensors") a.list_tensors = true;
     else if (f == "--help" || f == "-h") { usage(); std::exit(0); }
     else throw std::runtime_error("unknown flag " + f);
   }
@@ -94,7 +116,104 @@ std::vector<int> parse_ids(const std::string& text) {
   return out;
 }
 
-enum Op : int32_t { OP_GENERATE = 1, OP_RESET = 2, OP_SHUTDOWN = 3 };
+enum Op : int32_t { OP_GENERATE = 1, OP_RESET = 2, OP_SHUTDOWN = 3, OP_PREFILL = 4, OP_NEXT = 5 };
+
+// The Qwen engine behind the server. Greedy requests run the device sampler; with a temperature the
+// logits of each step come back to the host sampler (single rank only: logits are vocabulary shards).
+// With tensor parallelism rank 0 replays every step to the workers over the command channel.
+class QwenTokenEngine : public pk::TokenEngine {
+ public:
+  QwenTokenEngine(pk::QwenEngine& e, pk::CmdChannel& chan, int world) : e_(e), chan_(chan), world_(world) {}
+  int max_context() const override { return e_.options().max_context; }
+  int prefill(const std::vector<int>& prompt, const pk::SamplerConfig& sc, uint64_t seed) override {
+    sc_ = sc;
+    rng_ = seed | 1;
+    host_sampling_ = sc.temperature > 0.f && world_ == 1;
+    if (world_ > 1) {
+      pk::CmdChannel::Message m;
+      m.op = OP_PREFILL;
+      m.payload.assign(prompt.begin(), prompt.end());
+      chan_.broadcast(m);
+    }
+    e_.reset();
+    const int first = e_.prefill(prompt.data(), (int)prompt.size());
+    return host_sampling_ ? resample(first) : first;
+  }
+  int next() override {
+    if (world_ > 1) {
+      pk::CmdChannel::Message m;
+      m.op = OP_NEXT;
+      chan_.broadcast(m);
+    }
+    if (host_sampling_) {
+      int out = 0;
+      e_.forward_rows(&last_, 1, &out);
+      return resample(out);
+    }
+    int out = 0;
+    e_.decode(1, &out, true);
+    return out;
+  }
+
+ private:
+  int resample(int greedy) {
+    logits_.resize((size_t)e_.vocab_local());
+    e_.copy_logits(logits_.data(), 0);
+    last_ = pk::sample_token(logits_.data(), (int)logits_.size(), sc_, rng_);
+    (void)greedy;
+    return last_;
+  }
+  pk::QwenEngine& e_;
+  pk::CmdChannel& chan_;
+  int world_;
+  pk::SamplerConfig sc_;
+  uint64_t rng_ = 1;
+  bool host_sampling_ = false;
+  int last_ = 0;
+  std::vector<float> logits_;
+};
+
+std::vector<std::string> sidecar_command(const Args& a) {
+  return {a.sidecar_python, "-m", "pocketllm_b200.server.cpp_sidecar", "--tokenizer", a.tokenizer, "--chat-format", a.chat_format};
+}
+
+int inspect_gguf(const Args& a) {
+  pk::GgufFile f(a.inspect_gguf);
+  std::map<std::string, std::pair<size_t, uint64_t>> by_type;
+  uint64_t total = 0;
+  for (const auto& t : f.tensors()) {
+    auto& e = by_type[pk::ggml_type_name(t.type)];
+    e.first += 1;
+    e.second += t.nbytes;
+    total += t.nbytes;
+  }
+  std::printf("gguf_version=%u architecture=%s alignment=%llu tensors=%zu metadata_keys=%zu tensor_bytes=%llu file_bytes=%llu\n", f.version(),
+              f.architecture().c_str(), (unsigned long long)f.alignment(), f.tensors().size(), f.metadata().size(),
+              (unsigned long long)total, (unsigned long long)f.file_size());
+  for (const auto& kv : by_type)
+    std::printf("type=%s tensors=%zu bytes=%llu\n", kv.first.c_str(), kv.second.first, (unsigned long long)kv.second.second);
+  if (a.list_tensors) {
+    for (const auto& t : f.tensors()) {
+      std::printf("%s type=%s shape=[", t.name.c_str(), pk::ggml_type_name(t.type));
+      for (size_t i = 0; i < t.dims.size(); ++i) std::printf(i ? ",%llu" : "%llu", (unsigned long long)t.dims[i]);
+      std::printf("] offset=%llu bytes=%llu\n", (unsigned long long)t.offset, (unsigned long long)t.nbytes);
+    }
+  }
+  return 0;
+}
+
+int serve_scripted(const Args& a) {
+  auto eng = pk::make_scripted_engine(a.fake_script, a.max_context);
+  pk::Sidecar sidecar(sidecar_command(a));
+  pk::HttpServer http(a.host, a.port);
+  std::printf("openai_server_listening host=%s port=%d engine=scripted\n", a.host.c_str(), http.port());
+  std::fflush(stdout);
+  pk::OpenAIServerOptions so;
+  so.model_name = a.model_name;
+  so.allow_shutdown = a.allow_shutdown;
+  pk::run_openai_server(http, *eng, sidecar, so);
+  return 0;
+}
 
 struct RunResult {
   std::vector<int> tokens;
@@ -128,6 +247,8 @@ void print_result(const char* tag, const Args& a, const pk::QwenEngine& eng, siz
 }
 
 int run(const Args& a) {
+  if (!a.inspect_gguf.empty()) return inspect_gguf(a);
+  if (a.serve && a.fake_engine) return serve_scripted(a);
   if (a.inspect) {
     pk::SafetensorsModel st(a.ckpt);
     for (const auto& n : st.names()) {
@@ -179,7 +300,39 @@ int run(const Args& a) {
   if (a.tp_world > 1) pk::file_rendezvous_cleanup(a.id_path, a.tp_rank);
 
   int rc = 0;
-  if (a.persistent_stdin) {
+  if (a.serve) {
+    if (a.tp_rank == 0) {
+      QwenTokenEngine te(eng, chan, a.tp_world);
+      pk::Sidecar sidecar(sidecar_command(a));
+      pk::HttpServer http(a.host, a.port);
+      std::printf("openai_server_listening host=%s port=%d engine=qwen tp_world=%d\n", a.host.c_str(), http.port(), a.tp_world);
+      std::fflush(stdout);
+      pk::OpenAIServerOptions so;
+      so.model_name = a.model_name;
+      so.allow_shutdown = a.allow_shutdown;
+      pk::run_openai_server(http, te, sidecar, so);
+      pk::CmdChannel::Message bye;
+      bye.op = OP_SHUTDOWN;
+      chan.broadcast(bye);
+    } else {
+      pk::CmdChannel::Message m;
+      while (chan.receive(m)) {
+        if (m.op == OP_SHUTDOWN) break;
+        try {
+          if (m.op == OP_PREFILL) {
+            std::vector<int> prompt(m.payload.begin(), m.payload.end());
+            eng.reset();
+            eng.prefill(prompt.data(), (int)prompt.size());
+          } else if (m.op == OP_NEXT) {
+            int out = 0;
+            eng.decode(1, &out, true);
+          }
+        } catch (const std::exception& e) {
+          std::fprintf(stderr, "worker %d: %s\n", a.tp_rank, e.what());
+        }
+      }
+    }
+  } else if (a.persistent_stdin) {
     // Rank 0 reads "<max_new_tokens> tok0 tok1 ..." lines ("reset" / "quit" also accepted) and
     // replays them to the workers; every rank runs the same generate.
     if (a.tp_rank == 0) {

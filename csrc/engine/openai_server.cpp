@@ -1,0 +1,311 @@
+#include "openai_server.hpp"
+
+#include <signal.h>
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <stdexcept>
+
+namespace pk {
+
+// ---------------------------------------------------------------------------------------
+// sidecar
+
+Sidecar::Sidecar(const std::vector<std::string>& argv) {
+  if (argv.empty()) throw std::runtime_error("sidecar: empty command");
+  int in_pipe[2], out_pipe[2];
+  if (pipe(in_pipe) != 0 || pipe(out_pipe) != 0) throw std::runtime_error("sidecar: pipe() failed");
+  const pid_t pid = fork();
+  if (pid < 0) throw std::runtime_error("sidecar: fork() failed");
+  if (pid == 0) {
+    dup2(in_pipe[0], 0);
+    dup2(out_pipe[1], 1);
+    close(in_pipe[0]);
+    close(in_pipe[1]);
+    close(out_pipe[0]);
+    close(out_pipe[1]);
+    std::vector<char*> args;
+    for (const auto& a : argv) args.push_back(const_cast<char*>(a.c_str()));
+    args.push_back(nullptr);
+    execvp(args[0], args.data());
+    std::perror("sidecar: exec");
+    _exit(127);
+  }
+  close(in_pipe[0]);
+  close(out_pipe[1]);
+  to_child_ = in_pipe[1];
+  from_child_ = out_pipe[0];
+  pid_ = (int)pid;
+  signal(SIGPIPE, SIG_IGN);
+  const Json hello = call(Json::parse("{\"op\":\"hello\"}"));
+  if (!hello.get_bool("ok", false)) throw std::runtime_error("sidecar: handshake failed");
+}
+
+Sidecar::~Sidecar() {
+  if (to_child_ >= 0) {
+    const char bye[] = "{\"op\":\"quit\"}\n";
+    (void)!write(to_child_, bye, sizeof bye - 1);
+    close(to_child_);
+  }
+  if (from_child_ >= 0) close(from_child_);
+  if (pid_ > 0) {
+    int st = 0;
+    for (int i = 0; i < 50; ++i) {          // up to ~5 s for a clean exit, then end exactly this child
+      if (waitpid(pid_, &st, WNOHANG) == pid_) return;
+      usleep(100 * 1000);
+    }
+    kill(pid_, SIGKILL);
+    waitpid(pid_, &st, 0);
+  }
+}
+
+Json Sidecar::call(const Json& request) {
+  std::string line = request.dump();
+  line.push_back('\n');
+  size_t off = 0;
+  while (off < line.size()) {
+    const ssize_t w = write(to_child_, line.data() + off, line.size() - off);
+    if (w <= 0) throw std::runtime_error("sidecar: write failed (process gone?)");
+    off += (size_t)w;
+  }
+  for (;;) {
+    const size_t nl = pending_.find('\n');
+    if (nl != std::string::npos) {
+      const std::string reply = pending_.substr(0, nl);
+      pending_.erase(0, nl + 1);
+      return Json::parse(reply);
+    }
+    char buf[65536];
+    const ssize_t n = read(from_child_, buf, sizeof buf);
+    if (n <= 0) throw std::runtime_error("sidecar: closed its output");
+    pending_.append(buf, (size_t)n);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// scripted engine
+
+namespace {
+class ScriptedEngine : public TokenEngine {
+ public:
+  ScriptedEngine(const std::string& script, int max_context) : max_context_(max_context) {
+    // UTF-8 -> code points
+    for (size_t i = 0; i < script.size();) {
+      const unsigned char c = (unsigned char)script[i];
+      int len = c < 0x80 ? 1 : (c >> 5) == 6 ? 2 : (c >> 4) == 14 ? 3 : 4;
+      int cp = len == 1 ? c : c & (0xff >> (len + 1));
+      for (int k = 1; k < len && i + k < script.size(); ++k) cp = (cp << 6) | ((unsigned char)script[i + k] & 0x3f);
+      cps_.push_back(cp);
+      i += (size_t)len;
+    }
+  }
+  int max_context() const override { return max_context_; }
+  int prefill(const std::vector<int>&, const SamplerConfig&, uint64_t) override {
+    pos_ = 0;
+    return next();
+  }
+  int next() override { return pos_ < cps_.size() ? cps_[pos_++] : 0; }
+
+ private:
+  std::vector<int> cps_;
+  size_t pos_ = 0;
+  int max_context_;
+};
+
+std::string error_json(const std::string& msg, const std::string& type) {
+  Json e = Json::object();
+  e["message"] = Json(msg);
+  e["type"] = Json(type);
+  Json o = Json::object();
+  o["error"] = e;
+  return o.dump();
+}
+
+int64_t now_s() { return (int64_t)std::chrono::duration_cast<std::chrono::seconds>(std::chrono::system_clock::now().time_since_epoch()).count(); }
+
+}  // namespace
+
+std::unique_ptr<TokenEngine> make_scripted_engine(const std::string& script, int max_context) {
+  return std::make_unique<ScriptedEngine>(script, max_context);
+}
+
+// ---------------------------------------------------------------------------------------
+// routes
+
+void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, const OpenAIServerOptions& opt) {
+  std::atomic<bool> stop{false};
+  uint64_t counter = 0;
+  auto handler = [&](const HttpRequest& req, HttpResponse& res) {
+    if (req.method == "GET" && (req.path == "/health" || req.path == "/healthz")) {
+      res.send(200, "application/json", "{\"status\":\"ok\"}");
+      return;
+    }
+    if (req.method == "GET" && req.path == "/v1/models") {
+      Json m = Json::object();
+      m["id"] = Json(opt.model_name);
+      m["object"] = Json("model");
+      m["created"] = Json(now_s());
+      m["owned_by"] = Json("pocketllm-b200");
+      Json list = Json::object();
+      list["object"] = Json("list");
+      list["data"] = Json::array();
+      list["data"].push_back(m);
+      res.send(200, "application/json", list.dump());
+      return;
+    }
+    if (req.method == "POST" && req.path == "/shutdown" && opt.allow_shutdown) {
+      stop.store(true);
+      res.send(200, "application/json", "{\"status\":\"stopping\"}");
+      return;
+    }
+    if (req.path != "/v1/chat/completions") {
+      res.send(404, "application/json", error_json("unknown route " + req.path, "invalid_request_error"));
+      return;
+    }
+    if (req.method != "POST") {
+      res.send(405, "application/json", error_json("use POST", "invalid_request_error"));
+      return;
+    }
+    Json body;
+    try {
+      body = Json::parse(req.body);
+      if (!body.is_object()) throw std::runtime_error("body must be a JSON object");
+    } catch (const std::exception& e) {
+      res.send(400, "application/json", error_json(std::string("invalid JSON: ") + e.what(), "invalid_request_error"));
+      return;
+    }
+    Json begin = Json::object();
+    begin["op"] = Json("begin");
+    begin["body"] = body;
+    const Json plan = sidecar.call(begin);
+    if (!plan.get_bool("ok", false)) {
+      res.send((int)plan.get_int("status", 400), "application/json",
+               error_json(plan.get_string("error", "bad request"), "invalid_request_error"));
+      return;
+    }
+    std::vector<int> prompt;
+    for (const Json& t : plan.at("tokens").items()) prompt.push_back((int)t.as_int());
+    const int max_tokens = (int)plan.get_int("max_tokens", 512);
+    if ((int)prompt.size() + max_tokens > engine.max_context()) {
+      res.send(400, "application/json",
+               error_json("prompt (" + std::to_string(prompt.size()) + " tokens) plus max_tokens (" + std::to_string(max_tokens) +
+                              ") exceeds the context of " + std::to_string(engine.max_context()) + " tokens",
+                          "context_length_exceeded"));
+      return;
+    }
+    std::vector<int> eos;
+    for (const Json& t : plan.at("stop_token_ids").items()) eos.push_back((int)t.as_int());
+    const bool stream = plan.get_bool("stream", false), include_usage = plan.get_bool("include_usage", false);
+    SamplerConfig sc;
+    sc.temperature = (float)plan.get_double("temperature", 0.0);
+    sc.top_p = (float)plan.get_double("top_p", 1.0);
+    sc.top_k = (int)plan.get_int("top_k", 0);
+    const uint64_t seed = (uint64_t)plan.get_int("seed", 0) * 0x9E3779B97F4A7C15ULL + 0x1234567ULL;
+    const std::string id = "chatcmpl-" + std::to_string(now_s()) + "-" + std::to_string(++counter);
+    const int64_t created = now_s();
+
+    auto chunk = [&](const Json& delta, const Json& finish) {
+      Json c = Json::object();
+      c["id"] = Json(id);
+      c["object"] = Json("chat.completion.chunk");
+      c["created"] = Json(created);
+      c["model"] = Json(opt.model_name);
+      Json choice = Json::object();
+      choice["index"] = Json(0);
+      choice["delta"] = delta;
+      choice["finish_reason"] = finish;
+      c["choices"] = Json::array();
+      c["choices"].push_back(choice);
+      return c.dump();
+    };
+    if (stream) {
+      res.begin_sse();
+      Json role = Json::object();
+      role["role"] = Json("assistant");
+      res.event(chunk(role, Json()));
+    }
+    int generated = 0;
+    std::string finish = "length";
+    int tok = engine.prefill(prompt, sc, seed);
+    while (true) {
+      ++generated;
+      bool is_eos = false;
+      for (int e : eos) is_eos |= tok == e;
+      if (is_eos) {
+        finish = "stop";
+        break;
+      }
+      Json feed = Json::object();
+      feed["op"] = Json("token");
+      feed["token"] = Json(tok);
+      const Json out = sidecar.call(feed);
+      const std::string text = out.get_string("delta", "");
+      if (stream && !text.empty()) {
+        Json d = Json::object();
+        d[out.get_string("channel", "content")] = Json(text);
+        if (!res.event(chunk(d, Json()))) break;          // client went away
+      }
+      if (out.get_bool("stop", false)) {
+        finish = "stop";
+        break;
+      }
+      if (generated >= max_tokens) break;
+      tok = engine.next();
+    }
+    Json endq = Json::object();
+    endq["op"] = Json("end");
+    endq["finish_reason"] = Json(finish);
+    const Json fin = sidecar.call(endq);
+    finish = fin.get_string("finish_reason", finish);
+    Json usage = Json::object();
+    usage["prompt_tokens"] = Json((int64_t)prompt.size());
+    usage["completion_tokens"] = Json(generated);
+    usage["total_tokens"] = Json((int64_t)prompt.size() + generated);
+    if (stream) {
+      const std::string tail = fin.get_string("tail", "");
+      if (!tail.empty()) {
+        Json d = Json::object();
+        d[fin.get_string("channel", "content")] = Json(tail);
+        res.event(chunk(d, Json()));
+      }
+      if (const Json* tc = fin.at("message").find("tool_calls")) {
+        Json d = Json::object();
+        d["tool_calls"] = *tc;
+        res.event(chunk(d, Json()));
+      }
+      res.event(chunk(Json::object(), Json(finish)));
+      if (include_usage) {
+        Json u = Json::object();
+        u["id"] = Json(id);
+        u["object"] = Json("chat.completion.chunk");
+        u["created"] = Json(created);
+        u["model"] = Json(opt.model_name);
+        u["choices"] = Json::array();
+        u["usage"] = usage;
+        res.event(u.dump());
+      }
+      res.event("[DONE]");
+      res.end_sse();
+      return;
+    }
+    Json out = Json::object();
+    out["id"] = Json(id);
+    out["object"] = Json("chat.completion");
+    out["created"] = Json(created);
+    out["model"] = Json(opt.model_name);
+    Json choice = Json::object();
+    choice["index"] = Json(0);
+    choice["message"] = fin.at("message");
+    choice["finish_reason"] = Json(finish);
+    out["choices"] = Json::array();
+    out["choices"].push_back(choice);
+    out["usage"] = usage;
+    res.send(200, "application/json", out.dump());
+  };
+  http.serve(handler, stop);
+}
+
+}  // namespace pk

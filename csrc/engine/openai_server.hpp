@@ -1,0 +1,55 @@
+// OpenAI-compatible endpoint of the native engine: /health, /v1/models, /v1/chat/completions
+// (JSON or server-sent events). Chat templating, tokenisation, incremental detokenisation with
+// stop strings and tool-call / reasoning parsing run in a Python sidecar process that speaks JSON
+// lines over pipes; token generation stays in this process.
+// Roles in the reference: cpp_engine/src/openai_server.cpp (routes 444-446, streaming 338,
+// context check 265) and cpp_engine/src/python_sidecar.cpp + cpp_sidecar.py.
+#pragma once
+
+#include <atomic>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "http_server.hpp"
+#include "json.hpp"
+#include "sampler.hpp"
+
+namespace pk {
+
+// What the server needs from a model.
+class TokenEngine {
+ public:
+  virtual ~TokenEngine() = default;
+  virtual int max_context() const = 0;
+  // Starts a new request; returns the first generated token.
+  virtual int prefill(const std::vector<int>& prompt, const SamplerConfig& sampler, uint64_t seed) = 0;
+  // The token after the last one returned.
+  virtual int next() = 0;
+};
+
+// Child process speaking one JSON object per line on stdin/stdout.
+class Sidecar {
+ public:
+  explicit Sidecar(const std::vector<std::string>& argv);
+  ~Sidecar();
+  Json call(const Json& request);
+
+ private:
+  int to_child_ = -1, from_child_ = -1;
+  int pid_ = -1;
+  std::string pending_;
+};
+
+struct OpenAIServerOptions {
+  std::string model_name = "pocketllm-b200";
+  bool allow_shutdown = false;   // POST /shutdown ends serve() (used by tests)
+};
+
+// Blocks until stopped.
+void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, const OpenAIServerOptions& opt);
+
+// Deterministic stand-in for a model: replays `script` code points, then token 0 (EOS), for every request.
+std::unique_ptr<TokenEngine> make_scripted_engine(const std::string& script, int max_context);
+
+}  // namespace pk

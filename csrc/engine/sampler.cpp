@@ -1,0 +1,64 @@
+#include "sampler.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <numeric>
+#include <vector>
+
+namespace pk {
+
+double next_uniform(uint64_t& s) {
+  s ^= s >> 12;
+  s ^= s << 25;
+  s ^= s >> 27;
+  return (double)((s * 0x2545F4914F6CDD1DULL) >> 11) / (double)(1ULL << 53);
+}
+
+int sample_token(const float* logits, int n, const SamplerConfig& cfg, uint64_t& rng) {
+  if (n <= 0) return -1;
+  int best = 0;
+  for (int i = 1; i < n; ++i)
+    if (logits[i] > logits[best]) best = i;
+  if (cfg.temperature <= 0.f) return best;
+  // Candidates sorted by logit; top-k / top-p cut the tail before the draw.
+  std::vector<int> order(n);
+  std::iota(order.begin(), order.end(), 0);
+  int keep = n;
+  if (cfg.top_k > 0 && cfg.top_k < n) keep = cfg.top_k;
+  if (keep < n || cfg.top_p < 1.f) {
+    const int limit = (cfg.top_p < 1.f && keep == n) ? std::min(n, 4096) : keep;   // nucleus rarely needs more
+    std::partial_sort(order.begin(), order.begin() + limit, order.end(),
+                      [&](int a, int b) { return logits[a] > logits[b] || (logits[a] == logits[b] && a < b); });
+    keep = limit;
+  }
+  const double inv_t = 1.0 / cfg.temperature, mx = logits[best];
+  std::vector<double> p(keep);
+  double total = 0.0;
+  for (int i = 0; i < keep; ++i) {
+    p[i] = std::exp((logits[order[i]] - mx) * inv_t);
+    total += p[i];
+  }
+  if (cfg.top_p < 1.f) {
+    // `total` covers only the kept candidates; the tail beyond 4096 sorted entries is negligible.
+    double run = 0.0;
+    int cut = keep;
+    for (int i = 0; i < keep; ++i) {
+      run += p[i];
+      if (run >= cfg.top_p * total) {
+        cut = i + 1;
+        break;
+      }
+    }
+    keep = cut;
+    total = 0.0;
+    for (int i = 0; i < keep; ++i) total += p[i];
+  }
+  double r = next_uniform(rng) * total;
+  for (int i = 0; i < keep; ++i) {
+    r -= p[i];
+    if (r <= 0.0) return order[i];
+  }
+  return order[keep - 1];
+}
+
+}  // namespace pk

@@ -114,3 +114,34 @@ def build(kind: str, ckpt: str, max_context: int):
     else:
         render = lambda messages, *, thinking=False, **_: chat.render_minimax(messages, thinking=thinking)
     return GGUFBackend(rt), HFChatTokenizer(tok, render, eos)
+
+
+def build_tokenizer(kind: str, path: str, chat_format: str = "qwen"):
+    """Chat tokenizer alone (no model): `hf` = a directory with tokenizer.json, `gguf` = a GGUF file's metadata.
+    chat_format: qwen | glm | minimax | dsv4."""
+    if kind == "hf":
+        from tokenizers import Tokenizer
+        tok = Tokenizer.from_file(str(Path(path) / "tokenizer.json"))
+        names = {"qwen": ("<|im_end|>", "<|endoftext|>"), "dsv4": (dsv4.EOS,)}.get(chat_format, ("</s>",))
+        eos = [i for i in (tok.token_to_id(n) for n in names) if i is not None]
+    else:
+        md = gguf_tokenizer.read_metadata(path)
+        tok = gguf_tokenizer.build_tokenizer(md)
+        sp = gguf_tokenizer.special_ids(md)
+        eos = [i for i in (sp["eos"], sp["eot"]) if i is not None]
+
+    def render(messages, *, tools=None, thinking=False, reasoning_effort=None, response_format=None, **_):
+        if chat_format == "glm":
+            return chat.render_glm(messages, thinking=thinking)
+        if chat_format == "minimax":
+            return chat.render_minimax(messages, thinking=thinking)
+        if chat_format == "dsv4":
+            return dsv4.encode_messages(messages, tools=tools, thinking_mode="thinking" if thinking else "chat",
+                                        reasoning_effort=reasoning_effort, response_format=response_format)
+        out = ""
+        for m in messages:
+            out += f"<|im_start|>{m['role']}\n{dsv4._text(m.get('content'))}<|im_end|>\n"
+        return out + "<|im_start|>assistant\n" + ("<think>\n" if thinking else "")
+    parse = (lambda text, thinking: dsv4.parse_completion(("<think>" if thinking else "") + text, "thinking" if thinking else "chat")) \
+        if chat_format == "dsv4" else None
+    return HFChatTokenizer(tok, render, eos, parse)

@@ -1,0 +1,191 @@
+"""The native CLI's OpenAI server (HTTP + SSE + Python sidecar) with its scripted engine, the native GGUF
+reader and the host sampler: everything here runs without a GPU."""
+import ctypes
+import http.client
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+BINARY = ROOT / "pocketllm_b200" / "_C" / "pocket_engine"
+
+pytestmark = pytest.mark.skipif(not BINARY.exists(), reason="pocket_engine is not built")
+
+
+class Server:
+    def __init__(self, script: str, max_context: int = 4096):
+        env = dict(os.environ, PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        self.proc = subprocess.Popen(
+            [str(BINARY), "--serve", "--port", "0", "--fake-engine-script", script, "--tokenizer", "chars", "--chat-format", "dsv4",
+             "--sidecar-python", sys.executable, "--allow-shutdown", "--max-context", str(max_context), "--model-name", "scripted"],
+            stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+        line = self.proc.stdout.readline()
+        assert line.startswith("openai_server_listening"), (line, self.proc.stderr.read() if self.proc.poll() is not None else "")
+        self.port = int(dict(kv.split("=") for kv in line.split()[1:])["port"])
+
+    def request(self, method, path, body=None):
+        c = http.client.HTTPConnection("127.0.0.1", self.port, timeout=60)
+        c.request(method, path, None if body is None else json.dumps(body), {"Content-Type": "application/json"})
+        r = c.getresponse()
+        data = r.read().decode()
+        c.close()
+        return r.status, r.getheader("Content-Type"), data
+
+    def close(self):
+        try:
+            self.request("POST", "/shutdown", {})
+            self.proc.wait(timeout=20)
+        except Exception:
+            self.proc.kill()
+            self.proc.wait(timeout=20)
+
+
+@pytest.fixture
+def server(request):
+    s = Server(getattr(request, "param", "Hello, world!"))
+    yield s
+    s.close()
+
+
+def _chat(content="hi", **kw):
+    return dict({"model": "scripted", "messages": [{"role": "user", "content": content}]}, **kw)
+
+
+def test_health_models_and_errors(server):
+    assert server.request("GET", "/health")[0] == 200
+    st, ct, data = server.request("GET", "/v1/models")
+    assert st == 200 and "json" in ct and json.loads(data)["data"][0]["id"] == "scripted"
+    assert server.request("GET", "/nope")[0] == 404
+    assert server.request("GET", "/v1/chat/completions")[0] == 405
+    st, _, data = server.request("POST", "/v1/chat/completions", {"messages": []})
+    assert st == 400 and "messages" in json.loads(data)["error"]["message"]
+    st, _, data = server.request("POST", "/v1/chat/completions", _chat(max_tokens=100000))
+    assert st == 400 and json.loads(data)["error"]["type"] == "context_length_exceeded"
+
+
+def test_completion_stop_string_and_length(server):
+    st, _, data = server.request("POST", "/v1/chat/completions", _chat())
+    out = json.loads(data)
+    assert st == 200 and out["object"] == "chat.completion"
+    assert out["choices"][0]["message"] == {"role": "assistant", "content": "Hello, world!"}
+    assert out["choices"][0]["finish_reason"] == "stop"
+    u = out["usage"]
+    assert u["completion_tokens"] == len("Hello, world!") + 1 and u["total_tokens"] == u["prompt_tokens"] + u["completion_tokens"]
+    out = json.loads(server.request("POST", "/v1/chat/completions", _chat(stop=["wor"]))[2])
+    assert out["choices"][0]["message"]["content"] == "Hello, " and out["choices"][0]["finish_reason"] == "stop"
+    out = json.loads(server.request("POST", "/v1/chat/completions", _chat(max_tokens=3))[2])
+    assert out["choices"][0]["message"]["content"] == "Hel" and out["choices"][0]["finish_reason"] == "length"
+
+
+def test_streaming_chunks(server):
+    st, ct, data = server.request("POST", "/v1/chat/completions", _chat(stream=True, stream_options={"include_usage": True}))
+    assert st == 200 and ct.startswith("text/event-stream")
+    events = [e[len("data: "):] for e in data.split("\n\n") if e.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in events[:-1]]
+    assert chunks[0]["choices"][0]["delta"] == {"role": "assistant"}
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"])
+    assert text == "Hello, world!"
+    assert [c["choices"][0]["finish_reason"] for c in chunks if c["choices"]][-1] == "stop"
+    assert chunks[-1]["choices"] == [] and chunks[-1]["usage"]["completion_tokens"] == len(text) + 1
+    assert all(c["id"] == chunks[0]["id"] and c["object"] == "chat.completion.chunk" for c in chunks)
+
+
+TOOL_SCRIPT = ('Let me check.\n\n<｜DSML｜tool_calls>\n<｜DSML｜invoke name="get_weather">\n'
+               '<｜DSML｜parameter name="city" string="true">Paris</｜DSML｜parameter>\n'
+               '<｜DSML｜parameter name="days" string="false">3</｜DSML｜parameter>\n</｜DSML｜invoke>\n</｜DSML｜tool_calls>')
+
+
+@pytest.mark.parametrize("server", [TOOL_SCRIPT], indirect=True)
+def test_tool_calls_are_parsed_by_the_sidecar(server):
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object"}}}]
+    out = json.loads(server.request("POST", "/v1/chat/completions", _chat("weather?", tools=tools))[2])
+    ch = out["choices"][0]
+    assert ch["finish_reason"] == "tool_calls" and ch["message"]["content"] == "Let me check."
+    call = ch["message"]["tool_calls"][0]["function"]
+    assert call["name"] == "get_weather" and json.loads(call["arguments"]) == {"city": "Paris", "days": 3}
+
+
+@pytest.mark.parametrize("server", ["because</think>42"], indirect=True)
+def test_reasoning_goes_to_its_own_channel(server):
+    out = json.loads(server.request("POST", "/v1/chat/completions", _chat("why?", reasoning_effort="high"))[2])
+    msg = out["choices"][0]["message"]
+    assert msg["content"] == "42" and msg["reasoning_content"] == "because"
+    data = server.request("POST", "/v1/chat/completions", _chat("why?", reasoning_effort="high", stream=True))[2]
+    chunks = [json.loads(e[6:]) for e in data.split("\n\n") if e.startswith("data: {")]
+    assert "".join(c["choices"][0]["delta"].get("reasoning_content", "") for c in chunks if c["choices"]) == "because"
+
+
+def test_native_gguf_inspect(tmp_path):
+    from pocketllm_b200.models import minimax_m2
+    p = tmp_path / "mm.gguf"
+    minimax_m2.write_random_gguf(p, minimax_m2.MiniMaxM2Config.tiny())
+    out = subprocess.run([str(BINARY), "--inspect-gguf", str(p), "--tensors"], capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stderr
+    head = dict(kv.split("=") for kv in out.stdout.splitlines()[0].split())
+    from pocketllm_b200.formats import gguf
+    ref = gguf.GGUFFile(p)
+    assert head["architecture"] == "minimax-m2" and int(head["tensors"]) == len(ref.tensors) and int(head["file_bytes"]) == p.stat().st_size
+    types = {l.split()[0].split("=")[1]: int(l.split()[2].split("=")[1]) for l in out.stdout.splitlines() if l.startswith("type=")}
+    want = {}
+    for t in ref.tensors.values():
+        want[t.type_name] = want.get(t.type_name, 0) + t.nbytes
+    assert types == want
+    line = next(l for l in out.stdout.splitlines() if l.startswith("token_embd.weight "))
+    t = ref.tensors["token_embd.weight"]
+    assert f"bytes={t.nbytes}" in line
+    bad = tmp_path / "bad.gguf"
+    bad.write_bytes(p.read_bytes()[:200])
+    assert subprocess.run([str(BINARY), "--inspect-gguf", str(bad)], capture_output=True, text=True).returncode == 1
+
+
+def _engine_lib():
+    from pocketllm_b200.ops import lib
+    return lib.engine()
+
+
+def test_host_sampler_greedy_temperature_top_p():
+    L = _engine_lib()
+    logits = np.array([0.1, 2.0, 2.0, -1.0, 1.5, 0.0], dtype=np.float32)
+    ptr = logits.ctypes.data_as(ctypes.c_void_p)
+    rng = ctypes.c_uint64(12345)
+    call = lambda t, p, k: L.pk_sample_token(ptr, ctypes.c_int(len(logits)), ctypes.c_float(t), ctypes.c_float(p), ctypes.c_int(k), ctypes.byref(rng))
+    assert call(0.0, 1.0, 0) == 1                                   # greedy, lowest index on ties
+    draws = np.bincount([call(1.0, 1.0, 0) for _ in range(20000)], minlength=6) / 20000
+    want = np.exp(logits) / np.exp(logits).sum()
+    assert np.abs(draws - want).max() < 0.02
+    draws = np.bincount([call(1.0, 0.6, 0) for _ in range(5000)], minlength=6)
+    assert draws[[0, 3, 5]].sum() == 0 and draws[1] > 0 and draws[2] > 0          # nucleus keeps the head only
+    draws = np.bincount([call(0.7, 1.0, 2) for _ in range(2000)], minlength=6)
+    assert draws[[0, 3, 4, 5]].sum() == 0
+
+
+def test_native_gguf_reader_matches_python_reader(tmp_path):
+    from pocketllm_b200.formats import gguf
+    from pocketllm_b200.models import glm_dsa
+    p = tmp_path / "glm.gguf"
+    glm_dsa.write_random_gguf(p, glm_dsa.GLMDSAConfig.tiny())
+    L = _engine_lib()
+    L.pk_gguf_describe.restype = ctypes.c_char_p
+    d = json.loads(L.pk_gguf_describe(str(p).encode()))
+    ref = gguf.GGUFFile(p)
+    assert d["version"] == 3 and d["metadata"]["general.architecture"] == "glm-dsa"
+    for k, v in ref.metadata.items():
+        got = d["metadata"][k]
+        if isinstance(v, float):
+            assert abs(got - v) < 1e-6 * max(1.0, abs(v)), k
+        elif isinstance(v, (int, str, bool)):
+            assert got == v, k
+        else:
+            assert list(got) == list(v), k
+    assert [t["name"] for t in d["tensors"]] == list(ref.tensors)
+    for t in d["tensors"]:
+        r = ref.tensors[t["name"]]
+        assert t["type"] == r.type_name and t["nbytes"] == r.nbytes and tuple(reversed(t["dims"])) == tuple(r.shape)
+        assert t["head_sum"] == int(np.frombuffer(ref.raw(t["name"]).tobytes()[:64], dtype=np.uint8).sum())
+    assert L.pk_gguf_describe(str(tmp_path / "missing.gguf").encode()) is None
