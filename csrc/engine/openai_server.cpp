@@ -229,7 +229,24 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
     }
     int generated = 0;
     std::string finish = "length";
-    int tok = engine.prefill(prompt, sc, seed);
+    int tok = 0;
+    try {
+      tok = engine.prefill(prompt, sc, seed);
+    } catch (const std::exception& e) {
+      // nothing has been sent yet when the request is not streamed; a stream gets an error event
+      Json endq = Json::object();
+      endq["op"] = Json("end");
+      endq["finish_reason"] = Json("stop");
+      sidecar.call(endq);
+      if (!stream) {
+        res.send(400, "application/json", error_json(e.what(), "invalid_request_error"));
+      } else {
+        res.event(error_json(e.what(), "invalid_request_error"));
+        res.event("[DONE]");
+        res.end_sse();
+      }
+      return;
+    }
     while (true) {
       ++generated;
       bool is_eos = false;

@@ -691,6 +691,9 @@ void QwenEngine::run_chunk(int M) {
 // public entry points
 
 int QwenEngine::prefill(const int* tokens_host, int n) {
+  for (int t = 0; t < n; ++t)
+    if (tokens_host[t] < 0 || tokens_host[t] >= cfg_.vocab_size)
+      throw std::runtime_error("token id " + std::to_string(tokens_host[t]) + " is outside the vocabulary of " + std::to_string(cfg_.vocab_size));
   if (n < 1) throw std::runtime_error("prefill: empty prompt");
   if (pos_ + n + 1 > opt_.max_context) throw std::runtime_error("prefill: prompt exceeds max_context");
   cuda_check(cudaEventRecord(ev0_, stream_), "event");
@@ -787,6 +790,8 @@ void QwenEngine::decode(int steps, int* out_host, bool sync_each_step) {
 }
 
 void QwenEngine::forward_rows(const int* tokens_host, int M, int* out_tokens_host) {
+  for (int t = 0; t < M; ++t)
+    if (tokens_host[t] < 0 || tokens_host[t] >= cfg_.vocab_size) throw std::runtime_error("forward_rows: token id outside the vocabulary");
   if (M < 1 || M > kSmallRows) throw std::runtime_error("forward_rows: 1..8 rows");
   if (pos_ + M + 1 > opt_.max_context) throw std::runtime_error("forward_rows: exceeds max_context");
   memcpy(pinned_tok_, tokens_host, (size_t)M * sizeof(int));

@@ -25,7 +25,12 @@ class CharTokenizer:
     """One token per character (id = code point, 0 = EOS) with the DSV4 chat framing; for tests."""
     eos_ids = (0,)
 
+    def __init__(self, chat_format: str = "dsv4"):
+        self.chat_format = chat_format
+
     def encode_chat(self, messages, *, tools=None, thinking=False, reasoning_effort=None, response_format=None):
+        if self.chat_format == "plain":                    # ASCII only: for models with a tiny vocabulary
+            return [ord(c) for c in "".join(f"{m['role']}: {dsv4._text(m.get('content'))}\n" for m in messages) + "assistant: "]
         text = dsv4.encode_messages(messages, tools=tools, thinking_mode="thinking" if thinking else "chat",
                                     reasoning_effort=reasoning_effort, response_format=response_format)
         return [ord(c) for c in text]
@@ -39,7 +44,7 @@ class CharTokenizer:
 
 def build_tokenizer(spec: str, chat_format: str):
     if spec == "chars":
-        return CharTokenizer()
+        return CharTokenizer(chat_format)
     from . import backends
     kind, _, path = spec.partition(":")
     if kind in ("hf", "gguf"):

@@ -140,3 +140,61 @@ def test_speculative_decoding_equals_greedy(tiny):
     out, _ = speculative_generate(e, prompt, 33, NGramDrafter(), k=4)
     assert out == ref
     e.close()
+
+
+def test_native_server_serves_the_engine(tiny):
+    """pocket_engine --serve: the tokens behind the HTTP answer are the engine's greedy tokens."""
+    import http.client
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    from pocketllm_b200.models import qwen_hybrid as qh
+    from pocketllm_b200.server.cpp_sidecar import CharTokenizer
+    cfg, tensors, d = tiny
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    proc = subprocess.Popen([str(root / "pocketllm_b200" / "_C" / "pocket_engine"), "--ckpt", str(d), "--serve", "--port", "0", "--tokenizer", "chars",
+                             "--chat-format", "plain", "--sidecar-python", sys.executable, "--allow-shutdown", "--max-context", "512"],
+                            stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+    try:
+        line = proc.stdout.readline()
+        assert line.startswith("openai_server_listening"), proc.stderr.read()
+        port = int(dict(kv.split("=") for kv in line.split()[1:])["port"])
+        body = {"messages": [{"role": "user", "content": "abc"}], "max_tokens": 12}
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+        c.request("POST", "/v1/chat/completions", json.dumps(body), {"Content-Type": "application/json"})
+        out = json.loads(c.getresponse().read())
+        c.close()
+        prompt = CharTokenizer("plain").encode_chat(body["messages"])
+        assert all(t < cfg.vocab_size for t in prompt)
+        eng = qh.QwenEngine(cfg, max_context=512).load(d)
+        want = eng.generate(prompt, 12)
+        eng.close()
+        if 0 in want:
+            want = want[:want.index(0)]
+        assert out["usage"]["prompt_tokens"] == len(prompt)
+        assert out["choices"][0]["message"]["content"] == "".join(chr(t) for t in want)
+        # a token outside the vocabulary is refused, and the server keeps serving
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+        c.request("POST", "/v1/chat/completions", json.dumps({"messages": [{"role": "user", "content": "\uff5c"}], "max_tokens": 4}), {"Content-Type": "application/json"})
+        r = c.getresponse()
+        assert r.status == 400 and "vocabulary" in json.loads(r.read())["error"]["message"]
+        c.close()
+        # sampled request: different seeds give different continuations, the same seed repeats
+        texts = []
+        for seed in (1, 1, 2):
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+            c.request("POST", "/v1/chat/completions", json.dumps(dict(body, temperature=1.5, seed=seed)), {"Content-Type": "application/json"})
+            texts.append(json.loads(c.getresponse().read())["choices"][0]["message"]["content"])
+            c.close()
+        assert texts[0] == texts[1] and texts[0] != texts[2]
+    finally:
+        try:
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=20)
+            c.request("POST", "/shutdown", "{}")
+            c.getresponse().read()
+            proc.wait(timeout=30)
+        except Exception:
+            proc.kill()
