@@ -26,6 +26,7 @@ import torch
 
 from .. import ops
 from ..ops import dsv4_ops as dk
+from ..formats import fp8 as fp8fmt
 from ..ops import gguf_ops as gk
 from . import deepseek_v4 as d4
 
@@ -55,6 +56,22 @@ class _Lin:
         return ops.gemm_umma(x, w, self.scale)
 
 
+def _lin(W: dict, name: str) -> _Lin:
+    """Linear `name` (without `.weight`): FP8 codes with E8M0 block scales stay FP8, anything else becomes bf16."""
+    w = W[name + ".weight"]
+    if w.dtype == torch.float8_e4m3fn:
+        return _Lin(w, fp8fmt.e8m0_to_float(W[name + ".scale"].view(torch.uint8)))
+    return _Lin(w)
+
+
+def _dense(W: dict, name: str) -> torch.Tensor:
+    """fp32 matrix of linear `name`, dequantised if needed (exact: E4M3 times a power of two)."""
+    w = W[name + ".weight"]
+    if w.dtype == torch.float8_e4m3fn:
+        return fp8fmt.dequantize_block128(w, fp8fmt.e8m0_to_float(W[name + ".scale"].view(torch.uint8)))
+    return w.float()
+
+
 def pack_mxfp4(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """[N, K/2] nibble pairs + [N, K/32] E8M0 -> [N, K/32 * 17] bytes: scale byte, then 16 nibble bytes, per 32 weights."""
     N, half = weight.shape
@@ -73,21 +90,21 @@ class _BlockWeights:
             setattr(self, f"hc_{kind}", (f32(f"{p}.hc_{kind}_fn"), f32(f"{p}.hc_{kind}_scale"), f32(f"{p}.hc_{kind}_base")))
         self.attn_norm, self.ffn_norm = f32(f"{p}.attn_norm.weight"), f32(f"{p}.ffn_norm.weight")
         a = f"{p}.attn"
-        stack = [W[f"{a}.wq_a.weight"], W[f"{a}.wkv.weight"]]
+        stack = [_dense(W, f"{a}.wq_a"), _dense(W, f"{a}.wkv")]
         if self.ratio:
             stack += [W[f"{a}.compressor.wkv.weight"], W[f"{a}.compressor.wgate.weight"]]
             self.c_ape, self.c_norm = f32(f"{a}.compressor.ape"), f32(f"{a}.compressor.norm.weight")
         if self.ratio == 4:
             stack += [W[f"{a}.indexer.compressor.wkv.weight"], W[f"{a}.indexer.compressor.wgate.weight"], W[f"{a}.indexer.weights_proj.weight"]]
             self.i_ape, self.i_norm = f32(f"{a}.indexer.compressor.ape"), f32(f"{a}.indexer.compressor.norm.weight")
-            self.i_wq_b = _Lin(W[f"{a}.indexer.wq_b.weight"])
+            self.i_wq_b = _lin(W, f"{a}.indexer.wq_b")
         self.proj = _Lin(torch.cat([t.float() for t in stack], 0))
         self.q_norm, self.kv_norm = f32(f"{a}.q_norm.weight"), f32(f"{a}.kv_norm.weight")
-        self.wq_b = _Lin(W[f"{a}.wq_b.weight"])
+        self.wq_b = _lin(W, f"{a}.wq_b")
         self.sink = f32(f"{a}.attn_sink")
         G = cfg.o_groups
         self.wo_a = [_Lin(w) for w in W[f"{a}.wo_a.weight"].view(G, cfg.o_lora_rank, -1)]
-        self.wo_b = _Lin(W[f"{a}.wo_b.weight"])
+        self.wo_b = _lin(W, f"{a}.wo_b")
         f = f"{p}.ffn"
         self.gate_w = f32(f"{f}.gate.weight")
         self.gate_bias = f32(f"{f}.gate.bias") if f"{f}.gate.bias" in W else None
@@ -100,8 +117,13 @@ class _BlockWeights:
             w2.append(pack_mxfp4(W[f"{f}.experts.{e}.w2.weight"], W[f"{f}.experts.{e}.w2.scale"]))
         self.w13, self.w2 = torch.stack(w13).cuda().contiguous(), torch.stack(w2).cuda().contiguous()
         s = f"{f}.shared_experts"
-        self.s_w13 = _Lin(torch.cat([W[f"{s}.w1.weight"].float(), W[f"{s}.w3.weight"].float()], 0))
-        self.s_w2 = _Lin(W[f"{s}.w2.weight"])
+        if W[f"{s}.w1.weight"].dtype == torch.float8_e4m3fn and W[f"{s}.w1.weight"].shape[0] % 128 == 0:
+            # stacked gate|up keeps FP8: the row blocks of both halves stay aligned to 128
+            cat = lambda k: torch.cat([W[f"{s}.w1.{k}"].view(torch.uint8), W[f"{s}.w3.{k}"].view(torch.uint8)], 0)
+            self.s_w13 = _Lin(cat("weight").view(torch.float8_e4m3fn), fp8fmt.e8m0_to_float(cat("scale")))
+        else:
+            self.s_w13 = _Lin(torch.cat([_dense(W, f"{s}.w1"), _dense(W, f"{s}.w3")], 0))
+        self.s_w2 = _lin(W, f"{s}.w2")
 
 
 class _BlockState:
@@ -143,7 +165,7 @@ class DSV4Runtime:
             if f"{p}.e_proj.weight" not in W:
                 break
             blk = _BlockWeights(cfg, W, p, cfg.n_layers + m)
-            blk.e_proj, blk.h_proj = _Lin(W[f"{p}.e_proj.weight"]), _Lin(W[f"{p}.h_proj.weight"])
+            blk.e_proj, blk.h_proj = _lin(W, f"{p}.e_proj"), _lin(W, f"{p}.h_proj")
             blk.enorm, blk.hnorm, blk.norm = f32(f"{p}.enorm.weight"), f32(f"{p}.hnorm.weight"), f32(f"{p}.norm.weight")
             blk.hc_head = (f32(f"{p}.hc_head_fn"), f32(f"{p}.hc_head_scale"), f32(f"{p}.hc_head_base"))
             self.mtp.append(blk)

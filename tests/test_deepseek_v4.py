@@ -45,6 +45,23 @@ def test_config_json_roundtrip_and_flash_shape():
     assert d4.DSV4Config.from_json(cfg.to_json()) == cfg
 
 
+def test_checkpoint_roundtrip_keeps_quantised_tensors(tiny, tmp_path):
+    from pocketllm_b200.models import deepseek_v4_loader as ld
+    cfg, W = tiny
+    ld.save_checkpoint(tmp_path / "ck", cfg, W)
+    cfg2, W2 = ld.load_checkpoint(tmp_path / "ck")
+    assert cfg2 == cfg and set(k for k in W if not k.endswith(".scale")) <= set(W2)
+    assert W2["layers.1.attn.wq_b.weight"].dtype == torch.float8_e4m3fn and W2["layers.1.attn.wq_b.scale"].dtype == torch.uint8
+    assert W2["layers.1.attn.wo_a.weight"].dtype == torch.bfloat16 and W2["layers.1.hc_attn_fn"].dtype == torch.float32
+    assert torch.equal(W2["layers.2.ffn.experts.3.w1.weight"], W["layers.2.ffn.experts.3.w1.weight"])
+    dense = ld.dense_view(W2)
+    w, ref = dense["layers.1.attn.wq_b.weight"], W["layers.1.attn.wq_b.weight"]
+    assert w.dtype == torch.float32 and (w - ref).abs().max() <= ref.abs().max() * 0.07
+    assert "layers.1.attn.wq_b.scale" not in dense and "layers.2.ffn.experts.3.w1.scale" in dense
+    lg, _ = d4.DSV4Oracle(cfg2, dense).forward([5, 6, 7, 8, 9])
+    assert torch.isfinite(lg).all()
+
+
 # ---------------------------------------------------------------------------------------
 def _rel(a, b):
     return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-9)).item()
@@ -278,3 +295,25 @@ def test_mtp_speculative_generation_equals_plain_greedy(tiny):
         assert pred[0] == plain[len(out)]
         out += [plain[len(out)], pred[1]]
     assert out == plain[:len(out)] and passes <= 12
+
+
+@pytest.mark.gpu
+def test_runtime_on_fp8_checkpoint_matches_oracle(tiny, tmp_path):
+    """FP8 (E8M0 block scales) dense linears stay FP8 in the runtime and go through the FP8 kernels."""
+    from pocketllm_b200.models import deepseek_v4_loader as ld
+    from pocketllm_b200.models.deepseek_v4_runtime import DSV4Runtime
+    cfg, W = tiny
+    ld.save_checkpoint(tmp_path / "ck", cfg, W)
+    cfg2, W2 = ld.load_checkpoint(tmp_path / "ck")
+    g = torch.Generator().manual_seed(13)
+    prompt = torch.randint(0, cfg.vocab_size, (41,), generator=g).tolist()
+    rt = DSV4Runtime(cfg2, W2, max_context=128, max_rows=16)
+    assert rt.blocks[0].wq_b.w8 is not None and rt.blocks[0].s_w13.w8 is not None
+    rt.capture = {}
+    got = rt.forward_logits(prompt)
+    oracle = d4.DSV4Oracle(cfg2, ld.dense_view(W2), device="cuda")
+    want, _ = _pinned(oracle, rt.capture).forward(prompt)
+    assert _rel(got, want) < 3e-2
+    rt.capture = None
+    rt.last_token = int(got[-1].argmax())
+    assert len(rt.decode(3)) == 3                       # single-row path through the FP8 weight-streaming kernel
