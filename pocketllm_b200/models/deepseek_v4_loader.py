@@ -50,7 +50,7 @@ def save_checkpoint(directory: str | Path, cfg: d4.DSV4Config, W: dict[str, torc
         elif fp8_dense and _FP8_LINEAR.search(name) and t.dim() == 2:
             q, code = quantize_fp8_e8m0(t)
             out[name], out[name[:-len("weight")] + "scale"] = q, code
-        elif _BF16.search(name) or (t.dim() == 1 and "hc_" not in name):
+        elif t.dtype == torch.bfloat16 or _BF16.search(name) or (t.dim() == 1 and "hc_" not in name):
             out[name] = t.to(torch.bfloat16)
         else:
             out[name] = t.float()

@@ -317,3 +317,18 @@ def test_runtime_on_fp8_checkpoint_matches_oracle(tiny, tmp_path):
     rt.capture = None
     rt.last_token = int(got[-1].argmax())
     assert len(rt.decode(3)) == 3                       # single-row path through the FP8 weight-streaming kernel
+
+
+@pytest.mark.gpu
+def test_generate_cli_on_a_saved_checkpoint(tiny, tmp_path, capsys):
+    from pocketllm_b200.cli import generate
+    from pocketllm_b200.models import deepseek_v4_loader as ld
+    cfg, W = tiny
+    ld.save_checkpoint(tmp_path / "ck", cfg, W)
+    base = ["--ckpt-path", str(tmp_path / "ck"), "--tokenizer-path", "chars", "--prompt", "hello there", "--max-new-tokens", "9", "--max-context", "128"]
+    assert generate.main(base) == 0
+    plain = capsys.readouterr().out
+    assert generate.main(base + ["--mtp"]) == 0
+    spec = capsys.readouterr().out
+    assert len(plain.rstrip("\n")) > 0 and spec == plain
+    assert generate.main(base + ["--temperature", "1.0", "--seed", "3"]) == 0
