@@ -1,0 +1,48 @@
+"""Peer-memory all-reduce: bounded wait on one GPU, agreement with NCCL on two."""
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_wait_runs_out_and_context_stays_usable():
+    """A context whose 'peers' never publish: the wait gives up after its budget, the status word says so,
+    and the same context works again for a world of one."""
+    from pocketllm_b200.parallel.peer_allreduce import PeerAllReduce
+    par = PeerAllReduce(1024, timeout_us=200_000, _solo_world=2)      # rank 0 of 2; nobody plays rank 1
+    x = torch.ones(1024, device="cuda")
+    t0 = time.perf_counter()
+    par.all_reduce(x.clone())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert 0.15 < dt < 5.0
+    assert par.status() == 1
+    with pytest.raises(TimeoutError):
+        par.check()
+    assert par.status() == 0
+    par.close()
+    solo = PeerAllReduce(1024, _solo_world=1)
+    y = solo.all_reduce(torch.arange(1000, device="cuda", dtype=torch.float32))
+    assert torch.equal(y, torch.arange(1000, device="cuda", dtype=torch.float32)) and solo.status() == 0
+    z = solo.all_reduce(torch.full((7,), 2.5, device="cuda"))          # odd length: scalar tail
+    assert torch.equal(z, torch.full((7,), 2.5, device="cuda"))
+    solo.close()
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_matches_nccl_on_two_gpus():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29551",
+           "-m", "pocketllm_b200.parallel.par_check", "--sizes", "1001,4096,262144", "--iters", "20"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert r.returncode == 0, r.stderr[-3000:]
+    out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["status"] == 0 and max(out["max_abs_err"]) < 1e-5
