@@ -81,7 +81,7 @@ def pack_mxfp4(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
 
 
 class _BlockWeights:
-    def __init__(self, cfg: d4.DSV4Config, W: dict, p: str, layer: int):
+    def __init__(self, cfg: d4.DSV4Config, W: dict, p: str, layer: int, e_lo: int = 0, e_hi: int | None = None):
         f32 = lambda n: W[n].float().cuda().contiguous()
         self.name = p
         self.ratio = cfg.ratio(layer)
@@ -109,9 +109,9 @@ class _BlockWeights:
         self.gate_w = f32(f"{f}.gate.weight")
         self.gate_bias = f32(f"{f}.gate.bias") if f"{f}.gate.bias" in W else None
         self.tid2eid = W[f"{f}.gate.tid2eid"].to(torch.int32).cuda().contiguous() if self.hash else None
-        E = cfg.n_routed_experts
+        self.e_lo, self.e_hi = e_lo, cfg.n_routed_experts if e_hi is None else e_hi
         w13, w2 = [], []
-        for e in range(E):
+        for e in range(self.e_lo, self.e_hi):               # this rank's experts only
             w13.append(torch.cat([pack_mxfp4(W[f"{f}.experts.{e}.w1.weight"], W[f"{f}.experts.{e}.w1.scale"]),
                                   pack_mxfp4(W[f"{f}.experts.{e}.w3.weight"], W[f"{f}.experts.{e}.w3.scale"])], 0))
             w2.append(pack_mxfp4(W[f"{f}.experts.{e}.w2.weight"], W[f"{f}.experts.{e}.w2.scale"]))
@@ -146,8 +146,18 @@ class DSV4Runtime:
     `forward_rows(tokens)` feeds `len(tokens)` (<= max_rows) tokens at consecutive positions and returns the
     greedy token after each row; `rollback(position)` rewinds to an earlier position."""
 
-    def __init__(self, cfg: d4.DSV4Config, weights: dict[str, torch.Tensor], *, max_context: int | None = None, max_rows: int = 64):
+    def __init__(self, cfg: d4.DSV4Config, weights: dict[str, torch.Tensor], *, max_context: int | None = None, max_rows: int = 64,
+                 rank: int = 0, world: int = 1, group=None, use_peer_allreduce: bool = True):
+        """With `world > 1` the routed experts are split over the ranks in contiguous ranges (everything else is
+        replicated) and their outputs are summed across ranks; every rank feeds the same tokens."""
         self.cfg = cfg
+        if cfg.n_routed_experts % world:
+            raise ValueError("the expert count must divide by the world size")
+        self.rank, self.world = rank, world
+        from ..parallel.combine import ExpertCombine
+        self.combine = ExpertCombine(world, group, capacity=max_rows * cfg.dim, use_peer=use_peer_allreduce)
+        per = cfg.n_routed_experts // world
+        e_lo, e_hi = rank * per, (rank + 1) * per
         self.max_context = max_context or cfg.max_seq_len
         self.max_rows = max_rows
         # when a dict: records every discrete choice (expert ids, selected entries) per block, call by call
@@ -155,7 +165,7 @@ class DSV4Runtime:
         W = weights
         f32 = lambda n: W[n].float().cuda().contiguous()
         self.embed = W["embed.weight"].float().cuda()
-        self.blocks = [_BlockWeights(cfg, W, f"layers.{i}", i) for i in range(cfg.n_layers)]
+        self.blocks = [_BlockWeights(cfg, W, f"layers.{i}", i, e_lo, e_hi) for i in range(cfg.n_layers)]
         self.hc_head = (f32("hc_head_fn"), f32("hc_head_scale"), f32("hc_head_base"))
         self.norm = f32("norm.weight")
         self.head = _Lin(W["head.weight"])
@@ -164,7 +174,7 @@ class DSV4Runtime:
             p = f"mtp.{m}"
             if f"{p}.e_proj.weight" not in W:
                 break
-            blk = _BlockWeights(cfg, W, p, cfg.n_layers + m)
+            blk = _BlockWeights(cfg, W, p, cfg.n_layers + m, e_lo, e_hi)
             blk.e_proj, blk.h_proj = _lin(W, f"{p}.e_proj"), _lin(W, f"{p}.h_proj")
             blk.enorm, blk.hnorm, blk.norm = f32(f"{p}.enorm.weight"), f32(f"{p}.hnorm.weight"), f32(f"{p}.norm.weight")
             blk.hc_head = (f32(f"{p}.hc_head_fn"), f32(f"{p}.hc_head_scale"), f32(f"{p}.hc_head_base"))
@@ -249,7 +259,8 @@ class DSV4Runtime:
             self.capture.setdefault(f"{b.name}.ffn.route_idx", []).append(ids.clone())
         seg, tok, rw = gk.group_routes(ids, w, cfg.n_routed_experts)
         y = gk.gguf_moe_forward(x, self.w_flat(b.w13), self.w_flat(b.w2), "mxfp4", "mxfp4", cfg.n_routed_experts, cfg.moe_inter_dim,
-                                seg, tok, rw, limit=cfg.swiglu_limit)
+                                seg, tok, rw, limit=cfg.swiglu_limit, expert_offset=b.e_lo, local_experts=b.e_hi - b.e_lo)
+        y = self.combine(y)
         hs = ops.silu_mul(b.s_w13(x), cfg.swiglu_limit)
         return y, b.s_w2(hs, f32=True)
 

@@ -309,6 +309,7 @@ class GLMDSAModel:
             raise ValueError("expert count must divide by the world size")
         self.device, self.rank, self.world, self.group = torch.device(device), rank, world, group
         self.e_local, self.e_start = c.n_experts // world, rank * (c.n_experts // world)
+        self._combiner = None
         self.types = {n: t.type_name for n, t in self.bundle.tensors.items()}
         self.shapes = {n: t.shape for n, t in self.bundle.tensors.items()}
         W = _Weights(self.bundle)
@@ -330,6 +331,13 @@ class GLMDSAModel:
             self.raw[b + "w13"] = torch.cat([self.raw.pop(b + "ffn_gate_exps.weight"), self.raw.pop(b + "ffn_up_exps.weight")], dim=1).contiguous()
         self.cache = [{"latent": [], "krope": [], "ki": []} for _ in range(c.n_layers)]
         self.max_context, self.pos = max_context, 0
+
+    def _combine(self, y: torch.Tensor) -> torch.Tensor:
+        """Sum the ranks' expert outputs (peer-memory all-reduce for small payloads, NCCL for large ones)."""
+        if self._combiner is None:
+            from ..parallel.combine import ExpertCombine
+            self._combiner = ExpertCombine(self.world, self.group)
+        return self._combiner(y)
 
     def reset(self) -> None:
         self.pos = 0
@@ -359,7 +367,7 @@ class GLMDSAModel:
                                 self.types[b + "ffn_down_exps.weight"], c.n_experts, c.expert_inter, seg, tok, rw,
                                 expert_offset=self.e_start, local_experts=self.e_local)
         if self.world > 1:
-            torch.distributed.all_reduce(y, group=self.group)
+            self._combine(y)
         return y
 
     @torch.no_grad()

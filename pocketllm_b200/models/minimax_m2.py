@@ -191,6 +191,7 @@ class MiniMaxM2Model:
             raise ValueError("expert count must divide by the world size")
         self.device, self.rank, self.world, self.group = torch.device(device), rank, world, group
         self.e_local = c.n_experts // world
+        self._combiner = None
         self.e_start = rank * self.e_local
         self.types = {n: t.type_name for n, t in self.bundle.tensors.items()}
 
@@ -221,6 +222,13 @@ class MiniMaxM2Model:
             self.layers.append(L)
         self.max_context = max_context
         self.pos = 0
+
+    def _combine(self, y: torch.Tensor) -> torch.Tensor:
+        """Sum the ranks' expert outputs (peer-memory all-reduce for small payloads, NCCL for large ones)."""
+        if self._combiner is None:
+            from ..parallel.combine import ExpertCombine
+            self._combiner = ExpertCombine(self.world, self.group)
+        return self._combiner(y)
 
     def reset(self) -> None:
         self.pos = 0
@@ -262,7 +270,7 @@ class MiniMaxM2Model:
             y = go.gguf_moe_forward(xn, L["w13"], L["w2"], self.types[b + "ffn_gate_exps.weight"], self.types[b + "ffn_down_exps.weight"],
                                     c.n_experts, c.expert_inter, seg, tok, rw, expert_offset=self.e_start, local_experts=self.e_local)
             if self.world > 1:
-                torch.distributed.all_reduce(y, group=self.group)
+                self._combine(y)
             h = (h.float() + y).to(torch.bfloat16)
         self.pos += T
         return go.gguf_linear(h[-1:], self.head, self.types["output.weight"], c.vocab_size, gamma=self.final_norm, eps=c.norm_eps, epi=2)[0]

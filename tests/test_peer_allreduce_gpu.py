@@ -46,3 +46,27 @@ def test_matches_nccl_on_two_gpus():
     assert r.returncode == 0, r.stderr[-3000:]
     out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert out["status"] == 0 and max(out["max_abs_err"]) < 1e-5
+
+
+def _ep(world: int, ckpt, port: int, extra=()):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(port),
+           "-m", "pocketllm_b200.parallel.dsv4_ep_check", "--ckpt", str(ckpt), "--prompt", ",".join(str((i * 29 + 3) % 500) for i in range(37)), "--new", "8", *extra]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert r.returncode == 0, r.stderr[-3000:]
+    return json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_dsv4_expert_parallel_matches_single_gpu(tmp_path):
+    from pocketllm_b200.models import deepseek_v4 as d4
+    from pocketllm_b200.models import deepseek_v4_loader as ld
+    cfg = d4.DSV4Config.tiny()
+    ld.save_checkpoint(tmp_path, cfg, d4.random_checkpoint(cfg, seed=0))
+    one = _ep(1, tmp_path, 29581)
+    two = _ep(2, tmp_path, 29582)
+    nccl = _ep(2, tmp_path, 29583, ["--nccl"])
+    assert two["ranks_agree"] and two["status"] == 0 and two["combine_calls"]["peer"] > 0 and two["combine_calls"]["nccl"] == 0
+    assert nccl["combine_calls"]["peer"] == 0
+    assert one["tokens"] == two["tokens"] == nccl["tokens"]
+    assert abs(one["logit_checksum"] - two["logit_checksum"]) < 1e-3
