@@ -272,6 +272,7 @@ struct MoeParams {
   float limit;          // SwiGLU clamp, 0 = off
   int expert_offset;    // first expert id stored in W13 / W2 (expert parallel shard)
   int local_experts;
+  float* ybuf;          // [R, H] per-route outputs for the fixed-order reduce; null = atomics into y
 };
 
 // grid: (row tiles, local experts). Each block stages up to 8 routed tokens of its expert at a
@@ -332,10 +333,33 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w2_kernel(const MoeParams p
 #pragma unroll
       for (int m = 0; m < 8; ++m) {
         const float v = warp_sum(a[m]);
-        if (lane == 0 && m < cnt) atomicAdd(p.y + (size_t)p.route_token[rs + m] * p.H + n, v);
+        if (lane == 0 && m < cnt) {
+          if (p.ybuf != nullptr) p.ybuf[(size_t)(rs + m) * p.H + n] = v;
+          else atomicAdd(p.y + (size_t)p.route_token[rs + m] * p.H + n, v);
+        }
       }
     }
   }
+}
+
+// Fixed-order reduce: y[t] += sum over k = 0..topk-1 of the output of route (t, k), skipping routes whose
+// expert lives on another rank. route_pos[t * topk + k] is the route's position in the expert-sorted order.
+__global__ void moe_reduce_routes_kernel(const float* __restrict__ ybuf, const int* __restrict__ route_pos, const int* __restrict__ seg_start,
+                                         int topk, int H, int expert_offset, int local_experts, float* y) {
+  const int t = blockIdx.y, n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= H) return;
+  const int lo = seg_start[expert_offset], hi = seg_start[expert_offset + local_experts];
+  float acc = y[(size_t)t * H + n];
+  for (int k = 0; k < topk; ++k) {
+    const int pos = route_pos[t * topk + k];
+    if (pos >= lo && pos < hi) acc += ybuf[(size_t)pos * H + n];
+  }
+  y[(size_t)t * H + n] = acc;
+}
+
+__global__ void invert_routes_kernel(const int* __restrict__ route_src, int R, int* route_pos) {
+  const int pos = blockIdx.x * blockDim.x + threadIdx.x;
+  if (pos < R) route_pos[route_src[pos]] = pos;
 }
 
 // ---- routing ----
@@ -534,14 +558,45 @@ PK_API int pk_group_routes(const int* ids, const float* weights, int T, int topk
 
 // Routed experts of one rank: experts [expert_offset, expert_offset + local_experts) live in
 // W13 / W2. y (fp32 [T, H]) must be zeroed by the caller; hbuf holds R * I floats.
+static int moe_forward_impl(const void* W13, const void* W2, int type13, int type2, int E, int H, int I, const void* x,
+                            const int* seg_start, const int* route_token, const float* route_weight, float* hbuf, float* y,
+                            float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream);
+
 PK_API int pk_gguf_moe_forward(const void* W13, const void* W2, int type13, int type2, int E, int H, int I,
                                const void* x, const int* seg_start, const int* route_token, const float* route_weight,
                                float* hbuf, float* y, float limit, int expert_offset, int local_experts, int sm_count,
                                cudaStream_t stream) {
+  return moe_forward_impl(W13, W2, type13, type2, E, H, I, x, seg_start, route_token, route_weight, hbuf, y, limit, expert_offset,
+                          local_experts, sm_count, nullptr, stream);
+}
+
+// Same result up to rounding, but bitwise reproducible: every route writes its own output row (ybuf, R * H
+// floats) and a second kernel adds the rows of each token in route order. route_src comes from pk_group_routes;
+// route_pos is R ints of scratch; T tokens with topk routes each.
+PK_API int pk_gguf_moe_forward_det(const void* W13, const void* W2, int type13, int type2, int E, int H, int I, const void* x,
+                                   const int* seg_start, const int* route_token, const float* route_weight, const int* route_src,
+                                   float* hbuf, float* ybuf, int* route_pos, float* y, int T, int topk, float limit,
+                                   int expert_offset, int local_experts, int sm_count, cudaStream_t stream) {
+  if (route_src == nullptr || ybuf == nullptr || route_pos == nullptr || T < 1 || topk < 1) return PK_ERR_BAD_ARG;
+  const int rc = moe_forward_impl(W13, W2, type13, type2, E, H, I, x, seg_start, route_token, route_weight, hbuf, y, limit,
+                                  expert_offset, local_experts, sm_count, ybuf, stream);
+  if (rc != PK_OK) return rc;
+  const int R = T * topk;
+  invert_routes_kernel<<<(R + 255) / 256, 256, 0, stream>>>(route_src, R, route_pos);
+  PK_CHECK_LAUNCH();
+  moe_reduce_routes_kernel<<<dim3((H + 255) / 256, T), 256, 0, stream>>>(ybuf, route_pos, seg_start, topk, H, expert_offset,
+                                                                         local_experts, y);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+static int moe_forward_impl(const void* W13, const void* W2, int type13, int type2, int E, int H, int I, const void* x,
+                            const int* seg_start, const int* route_token, const float* route_weight, float* hbuf, float* y,
+                            float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream) {
   if ((H & 255) || (I & 255) || local_experts < 1) return PK_ERR_BAD_ARG;
   if ((size_t)8 * H * 4 > 200 * 1024 || (size_t)8 * I * 4 > 200 * 1024) return PK_ERR_UNSUPPORTED;
   MoeParams p{(const uint8_t*)W13, (const uint8_t*)W2, type13, type2, E, H, I, (const pk::bf16*)x, seg_start, route_token,
-              route_weight, hbuf, y, limit, expert_offset, local_experts};
+              route_weight, hbuf, y, limit, expert_offset, local_experts, ybuf};
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gguf_moe_w13_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||

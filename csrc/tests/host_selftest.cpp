@@ -1,0 +1,203 @@
+// Self-test of the engine's host code (JSON, GGUF and Safetensors readers, sampler, file rendezvous, command
+// channel, host model of the peer all-reduce protocol). Built with -fsanitize=address,undefined (or thread)
+// by the test-suite and run on a machine without a GPU.
+//   host_selftest <file.gguf> <safetensors dir> <scratch dir>
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../common/pk_comm_host.hpp"
+#include "../engine/control_plane.hpp"
+#include "../engine/gguf_reader.hpp"
+#include "../engine/json.hpp"
+#include "../engine/safetensors.hpp"
+#include "../engine/sampler.hpp"
+
+#define CHECK(cond)                                                             \
+  do {                                                                          \
+    if (!(cond)) {                                                              \
+      std::fprintf(stderr, "FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond);    \
+      return 1;                                                                 \
+    }                                                                           \
+  } while (0)
+
+static int test_json() {
+  const std::string text = R"({"a":[1,2.5,-3e2,true,null,"xé\n\"q\""],"b":{"c":9007199254740993,"d":{}},"e":[]})";
+  pk::Json j = pk::Json::parse(text);
+  CHECK(j.at("a").items().size() == 6 && j.at("a").items()[1].as_double() == 2.5 && j.at("a").items()[2].as_double() == -300.0);
+  CHECK(j.at("b").at("c").as_int() == 9007199254740993LL);
+  CHECK(j.at("a").items()[5].as_string() == std::string("x\xc3\xa9\n\"q\""));
+  pk::Json again = pk::Json::parse(j.dump());
+  CHECK(again.dump() == j.dump());
+  for (const char* bad : {"{", "[1,]", "{\"a\":}", "\"unterminated", "tru", "{\"a\":1}x", ""}) {
+    bool threw = false;
+    try {
+      pk::Json::parse(bad);
+    } catch (const std::exception&) {
+      threw = true;
+    }
+    CHECK(threw);
+  }
+  return 0;
+}
+
+static int test_readers(const std::string& gguf_path, const std::string& st_dir) {
+  pk::GgufFile g(gguf_path);
+  CHECK(!g.architecture().empty() && !g.tensors().empty());
+  uint64_t sum = 0;
+  for (const auto& t : g.tensors()) {
+    const uint8_t* p = g.data(t);
+    sum += p[0] + p[t.nbytes - 1];                 // touches the first and the last byte of every tensor
+  }
+  CHECK(g.find("no.such.tensor") == nullptr);
+  pk::SafetensorsModel st(st_dir);
+  CHECK(!st.names().empty());
+  for (const auto& n : st.names()) {
+    const pk::StTensor& t = st.get(n);
+    if (t.nbytes) sum += ((const uint8_t*)t.data)[0] + ((const uint8_t*)t.data)[t.nbytes - 1];
+  }
+  std::printf("readers_checksum=%llu\n", (unsigned long long)sum);
+  return 0;
+}
+
+static int test_sampler() {
+  const float logits[5] = {0.f, 3.f, 3.f, -2.f, 1.f};
+  uint64_t rng = 99;
+  pk::SamplerConfig greedy;
+  CHECK(pk::sample_token(logits, 5, greedy, rng) == 1);
+  pk::SamplerConfig hot;
+  hot.temperature = 1.f;
+  hot.top_p = 0.5f;
+  int seen[5] = {0};
+  for (int i = 0; i < 2000; ++i) seen[pk::sample_token(logits, 5, hot, rng)]++;
+  CHECK(seen[0] == 0 && seen[3] == 0 && seen[4] == 0 && seen[1] > 0);
+  return 0;
+}
+
+static int test_control_plane(const std::string& scratch) {
+  const int world = 3;
+  std::vector<std::vector<std::vector<uint8_t>>> got(world);
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r)
+    th.emplace_back([&, r] { got[r] = pk::file_rendezvous(scratch + "/rdv", r, world, std::vector<uint8_t>(64, (uint8_t)(r + 1)), 20000, 5); });
+  for (auto& t : th) t.join();
+  for (int r = 0; r < world; ++r)
+    for (int q = 0; q < world; ++q) CHECK(got[r][q].size() == 64 && got[r][q][0] == q + 1);
+  for (int r = 0; r < world; ++r) pk::file_rendezvous_cleanup(scratch + "/rdv", r);
+  // a rank that never arrives: the others give up with an error instead of waiting for ever
+  bool threw = false;
+  try {
+    pk::file_rendezvous(scratch + "/rdv_missing", 0, 2, std::vector<uint8_t>(64, 1), 300, 5);
+  } catch (const std::exception& e) {
+    threw = std::string(e.what()).find("never published") != std::string::npos;
+  }
+  CHECK(threw);
+  pk::file_rendezvous_cleanup(scratch + "/rdv_missing", 0);
+  // command channel: rank 0 drives two workers; when rank 0 goes away the workers' receive() ends
+  std::atomic<int> received{0}, eof{0};
+  std::vector<std::thread> workers;
+  for (int r = 1; r < world; ++r)
+    workers.emplace_back([&, r] {
+      pk::CmdChannel ch(scratch + "/cmd.sock", r, world, 400, 10);
+      pk::CmdChannel::Message m;
+      while (ch.receive(m)) {
+        if (m.op == 7 && m.payload.size() == 3 && m.payload[2] == 30) received++;
+      }
+      eof++;
+    });
+  {
+    pk::CmdChannel ch0(scratch + "/cmd.sock", 0, world, 400, 10);
+    pk::CmdChannel::Message m;
+    m.op = 7;
+    m.payload = {10, 20, 30};
+    for (int i = 0; i < 5; ++i) ch0.broadcast(m);
+  }   // rank 0 closes its sockets here
+  for (auto& t : workers) t.join();
+  CHECK(received == 10 && eof == 2);
+  // a worker that hangs up makes the next broadcast fail loudly
+  threw = false;
+  {
+    std::thread w([&] { pk::CmdChannel ch(scratch + "/cmd2.sock", 1, 2, 400, 10); });
+    pk::CmdChannel ch0(scratch + "/cmd2.sock", 0, 2, 400, 10);
+    w.join();
+    pk::CmdChannel::Message m;
+    m.op = 1;
+    m.payload.assign(1 << 16, 5);
+    try {
+      for (int i = 0; i < 50; ++i) ch0.broadcast(m);
+    } catch (const std::exception&) {
+      threw = true;
+    }
+  }
+  CHECK(threw);
+  return 0;
+}
+
+static int test_protocol() {
+  const int world = 4, iters = 300;
+  const size_t n = 257;
+  std::vector<std::unique_ptr<pk::HostArena>> own;
+  std::vector<pk::HostArena*> arenas;
+  for (int r = 0; r < world; ++r) {
+    own.push_back(std::make_unique<pk::HostArena>(world, n));
+    arenas.push_back(own.back().get());
+  }
+  std::atomic<int> bad{0};
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r)
+    th.emplace_back([&, r] {
+      std::vector<float> in(n), out(n);
+      for (int it = 0; it < iters; ++it) {
+        for (size_t i = 0; i < n; ++i) in[i] = (float)(r + 1) * (float)(it % 7 + 1) + (float)(i % 3);
+        if ((it + r) % 5 == 0) std::this_thread::sleep_for(std::chrono::microseconds(200));   // ranks drift apart
+        if (!pk::host_allreduce(arenas, r, in.data(), out.data(), n, 20000)) bad++;
+        for (size_t i = 0; i < n; ++i) {
+          const float want = 10.f * (float)(it % 7 + 1) + 4.f * (float)(i % 3);
+          if (std::fabs(out[i] - want) > 1e-3f) bad++;
+        }
+      }
+    });
+  for (auto& t : th) t.join();
+  CHECK(bad == 0);
+  // rank 3 stays away: the others notice within their budget and say so through the status word
+  std::vector<std::unique_ptr<pk::HostArena>> own2;
+  std::vector<pk::HostArena*> arenas2;
+  for (int r = 0; r < world; ++r) {
+    own2.push_back(std::make_unique<pk::HostArena>(world, n));
+    arenas2.push_back(own2.back().get());
+  }
+  std::atomic<int> timed_out{0};
+  th.clear();
+  for (int r = 0; r < world - 1; ++r)
+    th.emplace_back([&, r] {
+      std::vector<float> in(n, 1.f), out(n);
+      if (!pk::host_allreduce(arenas2, r, in.data(), out.data(), n, 100)) timed_out++;
+    });
+  for (auto& t : th) t.join();
+  CHECK(timed_out == world - 1 && arenas2[0]->status.load() == 1);
+  return 0;
+}
+
+int main(int argc, char** argv) {
+  if (argc < 4) {
+    std::fprintf(stderr, "usage: host_selftest file.gguf safetensors_dir scratch_dir\n");
+    return 2;
+  }
+  try {
+    if (test_json()) return 1;
+    if (test_readers(argv[1], argv[2])) return 1;
+    if (test_sampler()) return 1;
+    if (test_control_plane(argv[3])) return 1;
+    if (test_protocol()) return 1;
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "host_selftest: unexpected exception: %s\n", e.what());
+    return 1;
+  }
+  std::printf("host_selftest=ok\n");
+  return 0;
+}

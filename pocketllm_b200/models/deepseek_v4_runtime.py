@@ -257,9 +257,10 @@ class DSV4Runtime:
                                     norm_topk=cfg.score_func != "softmax", route_scale=cfg.route_scale)
         if self.capture is not None:
             self.capture.setdefault(f"{b.name}.ffn.route_idx", []).append(ids.clone())
-        seg, tok, rw = gk.group_routes(ids, w, cfg.n_routed_experts)
+        routes = gk.group_routes(ids, w, cfg.n_routed_experts)
+        seg, tok, rw = routes
         y = gk.gguf_moe_forward(x, self.w_flat(b.w13), self.w_flat(b.w2), "mxfp4", "mxfp4", cfg.n_routed_experts, cfg.moe_inter_dim,
-                                seg, tok, rw, limit=cfg.swiglu_limit, expert_offset=b.e_lo, local_experts=b.e_hi - b.e_lo)
+                                seg, tok, rw, limit=cfg.swiglu_limit, expert_offset=b.e_lo, local_experts=b.e_hi - b.e_lo, routes=routes)
         y = self.combine(y)
         hs = ops.silu_mul(b.s_w13(x), cfg.swiglu_limit)
         return y, b.s_w2(hs, f32=True)

@@ -266,9 +266,10 @@ class MiniMaxM2Model:
             h = (h.float() + att).to(torch.bfloat16)
             xn = _rms(h.float(), L["ffn_norm"], c.norm_eps).to(torch.bfloat16)
             ids, wt = go.router_topk(xn, L["router"], c.n_experts_used, bias=L["bias"], score_func="sigmoid", norm_topk=True)
-            seg, tok, rw = go.group_routes(ids, wt, c.n_experts)
+            routes = go.group_routes(ids, wt, c.n_experts)
+            seg, tok, rw = routes
             y = go.gguf_moe_forward(xn, L["w13"], L["w2"], self.types[b + "ffn_gate_exps.weight"], self.types[b + "ffn_down_exps.weight"],
-                                    c.n_experts, c.expert_inter, seg, tok, rw, expert_offset=self.e_start, local_experts=self.e_local)
+                                    c.n_experts, c.expert_inter, seg, tok, rw, expert_offset=self.e_start, local_experts=self.e_local, routes=routes)
             if self.world > 1:
                 self._combine(y)
             h = (h.float() + y).to(torch.bfloat16)

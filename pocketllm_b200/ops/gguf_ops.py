@@ -49,28 +49,49 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, topk: int, *, bias: tor
     return ids, w
 
 
-def group_routes(ids: torch.Tensor, weights: torch.Tensor, E: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Sort routes by expert: (seg_start [E+1], route_token [R], route_weight [R])."""
+class Routes(tuple):
+    """(seg_start [E+1], route_token [R], route_weight [R]) plus `.src` [R]: original route index t * topk + k of each
+    sorted route, and `.topk`."""
+    src: torch.Tensor
+    topk: int
+
+
+def group_routes(ids: torch.Tensor, weights: torch.Tensor, E: int) -> Routes:
+    """Sort routes by expert (stable in route index)."""
     T, topk = ids.shape
     seg = torch.empty(E + 1, device=ids.device, dtype=torch.int32)
     tok = torch.empty(T * topk, device=ids.device, dtype=torch.int32)
     rw = torch.empty(T * topk, device=ids.device, dtype=torch.float32)
+    src = torch.empty(T * topk, device=ids.device, dtype=torch.int32)
     st = _lib.kernels().pk_group_routes(_ptr(ids), _ptr(weights), c_int(T), c_int(topk), c_int(E), _ptr(seg), _ptr(tok),
-                                        _ptr(rw), c_void_p(0), _stream())
+                                        _ptr(rw), _ptr(src), _stream())
     _check(st, "pk_group_routes")
-    return seg, tok, rw
+    r = Routes((seg, tok, rw))
+    r.src, r.topk = src, topk
+    return r
 
 
 def gguf_moe_forward(x: torch.Tensor, w13_raw: torch.Tensor, w2_raw: torch.Tensor, type13: str, type2: str, E: int, inter: int,
                      seg: torch.Tensor, tok: torch.Tensor, rw: torch.Tensor, *, limit: float = 0.0, expert_offset: int = 0,
-                     local_experts: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Routed experts of this rank accumulated into fp32 `out` [T, H] (zeroed when not given)."""
+                     local_experts: int | None = None, out: torch.Tensor | None = None, routes: "Routes | None" = None) -> torch.Tensor:
+    """Routed experts of this rank accumulated into fp32 `out` [T, H] (zeroed when not given). With `routes` (the object
+    `group_routes` returned) the per-token sum runs in a fixed order and the result is bitwise reproducible; without it
+    the routes are added with atomics."""
     T, H = x.shape
     R = tok.numel()
     local = E if local_experts is None else local_experts
     if out is None:
         out = torch.zeros(T, H, device=x.device, dtype=torch.float32)
     hbuf = torch.empty(R, inter, device=x.device, dtype=torch.float32)
+    if routes is not None:
+        ybuf = torch.empty(R, H, device=x.device, dtype=torch.float32)
+        pos = torch.empty(R, device=x.device, dtype=torch.int32)
+        st = _lib.kernels().pk_gguf_moe_forward_det(
+            _ptr(w13_raw), _ptr(w2_raw), c_int(DEVICE_TYPE[type13]), c_int(DEVICE_TYPE[type2]), c_int(E), c_int(H), c_int(inter),
+            _ptr(x), _ptr(seg), _ptr(tok), _ptr(rw), _ptr(routes.src), _ptr(hbuf), _ptr(ybuf), _ptr(pos), _ptr(out), c_int(T),
+            c_int(routes.topk), c_float(limit), c_int(expert_offset), c_int(local), c_int(_sm_count()), _stream())
+        _check(st, "pk_gguf_moe_forward_det")
+        return out
     st = _lib.kernels().pk_gguf_moe_forward(
         _ptr(w13_raw), _ptr(w2_raw), c_int(DEVICE_TYPE[type13]), c_int(DEVICE_TYPE[type2]), c_int(E), c_int(H), c_int(inter),
         _ptr(x), _ptr(seg), _ptr(tok), _ptr(rw), _ptr(hbuf), _ptr(out), c_float(limit), c_int(expert_offset), c_int(local),

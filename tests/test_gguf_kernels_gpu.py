@@ -95,3 +95,28 @@ def test_moe_forward_matches_dequantised_reference(t13, t2, T):
     hi = go.gguf_moe_forward(x, raw13[E // 2 * 2 * I:], raw2[E // 2 * H:], t13, t2, E, I, seg, tok, rwt,
                              expert_offset=E // 2, local_experts=E // 2)
     assert _rel(lo + hi, ref) < 3e-3
+
+
+def test_moe_forward_fixed_order_reduce_is_bitwise_reproducible():
+    """Per-route outputs summed in route order: two runs agree bit for bit and match the atomic path closely."""
+    import numpy as np
+    from pocketllm_b200.formats import gguf_quants as gq
+    from pocketllm_b200.ops import gguf_ops as go
+    torch.manual_seed(0)
+    E, H, I, T, topk = 8, 512, 256, 37, 3
+    rng = np.random.default_rng(0)
+    w13 = torch.from_numpy(gq.quantize((rng.standard_normal((E * 2 * I, H)) * 0.05).astype(np.float32), "q4_k")).cuda().view(-1)
+    w2 = torch.from_numpy(gq.quantize((rng.standard_normal((E * H, I)) * 0.05).astype(np.float32), "q4_k")).cuda().view(-1)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E)[:topk] for _ in range(T)]).int().cuda()
+    wts = torch.rand(T, topk, device="cuda")
+    routes = go.group_routes(ids, wts, E)
+    seg, tok, rw = routes
+    runs = [go.gguf_moe_forward(x, w13, w2, "q4_k", "q4_k", E, I, seg, tok, rw, routes=routes) for _ in range(3)]
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
+    atomic = go.gguf_moe_forward(x, w13, w2, "q4_k", "q4_k", E, I, seg, tok, rw)
+    assert ((runs[0] - atomic).norm() / atomic.norm()).item() < 1e-5
+    # expert-parallel halves add up to the whole
+    lo = go.gguf_moe_forward(x, w13[: w13.numel() // 2], w2[: w2.numel() // 2], "q4_k", "q4_k", E, I, seg, tok, rw, expert_offset=0, local_experts=4, routes=routes)
+    hi = go.gguf_moe_forward(x, w13[w13.numel() // 2:], w2[w2.numel() // 2:], "q4_k", "q4_k", E, I, seg, tok, rw, expert_offset=4, local_experts=4, routes=routes)
+    assert ((lo + hi - runs[0]).norm() / runs[0].norm()).item() < 1e-6
