@@ -8,6 +8,7 @@
 #include "gguf_reader.hpp"
 #include "qwen_engine.hpp"
 #include "sampler.hpp"
+#include "tokenizer.hpp"
 
 #define PK_EAPI extern "C" __attribute__((visibility("default")))
 
@@ -87,6 +88,12 @@ PK_EAPI int pk_qwen_forward_rows(void* h, const int* tokens, int M, int* out_tok
 PK_EAPI void* pk_qwen_snapshot(void* h) {
   void* out = nullptr;
   guarded([&] { out = ((pk::QwenEngine*)h)->snapshot().release(); });
+  return out;
+}
+// Snapshot that also holds the KV rows of positions [0, position): survives other requests (prefix cache).
+PK_EAPI void* pk_qwen_snapshot_with_kv(void* h) {
+  void* out = nullptr;
+  guarded([&] { out = ((pk::QwenEngine*)h)->snapshot(true).release(); });
   return out;
 }
 PK_EAPI int pk_qwen_snapshot_update(void* h, void* snap) {
@@ -207,4 +214,31 @@ PK_EAPI const char* pk_gguf_describe(const char* path) {
     out = j.dump();
   });
   return rc == 0 ? out.c_str() : nullptr;
+}
+
+// Native byte-level BPE tokenizer from a GGUF file's metadata.
+PK_EAPI void* pk_tokenizer_from_gguf(const char* path) {
+  void* out = nullptr;
+  guarded([&] {
+    pk::GgufFile f(path);
+    out = new pk::BpeTokenizer(pk::BpeTokenizer::from_gguf(f));
+  });
+  return out;
+}
+PK_EAPI void pk_tokenizer_destroy(void* t) { delete (pk::BpeTokenizer*)t; }
+// Writes up to `cap` ids; returns the number of ids of the full encoding (call again with a larger buffer if > cap), -1 on error.
+PK_EAPI int pk_tokenizer_encode(void* t, const char* text, int parse_special, int* out, int cap) {
+  int n = -1;
+  guarded([&] {
+    const std::vector<int> ids = ((pk::BpeTokenizer*)t)->encode(text, parse_special != 0);
+    for (int i = 0; i < (int)ids.size() && i < cap; ++i) out[i] = ids[i];
+    n = (int)ids.size();
+  });
+  return n;
+}
+// UTF-8 text owned by the calling thread (valid until its next call); null on error.
+PK_EAPI const char* pk_tokenizer_decode(void* t, const int* ids, int n, int skip_special) {
+  thread_local std::string text;
+  const int rc = guarded([&] { text = ((pk::BpeTokenizer*)t)->decode(std::vector<int>(ids, ids + n), skip_special != 0); });
+  return rc == 0 ? text.c_str() : nullptr;
 }

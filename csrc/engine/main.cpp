@@ -28,6 +28,7 @@
 #include "qwen_config.hpp"
 #include "qwen_engine.hpp"
 #include "safetensors.hpp"
+#include "tokenizer.hpp"
 
 namespace {
 
@@ -40,7 +41,8 @@ struct Args {
   // serving
   bool serve = false, allow_shutdown = false, list_tensors = false;
   std::string host = "127.0.0.1", sidecar_python = "python", tokenizer = "chars", chat_format = "qwen", model_name = "pocketllm-b200";
-  std::string fake_script, inspect_gguf;
+  std::string fake_script, inspect_gguf, tokenizer_gguf, tokenize_text, detokenize_ids;
+  bool have_tokenize = false;
   bool fake_engine = false;
   int port = 8000;
 };
@@ -53,6 +55,7 @@ void usage() {
                "  --max-context N --prefill-chunk-tokens N --no-cuda-graph\n"
                "  --qwen-attention-window N --qwen-attention-sink-tokens N\n"
                "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
+               "  --tokenizer-gguf FILE --tokenize TEXT | --detokenize 1,2,3\n"
                "  --serve [--host H --port P --model-name N --tokenizer chars|hf:DIR|gguf:FILE --chat-format qwen|glm|minimax|dsv4\n"
                "           --sidecar-python EXE --fake-engine-script TEXT --allow-shutdown]\n");
 }
@@ -95,6 +98,9 @@ Args parse(int argc, char** argv) {
     else if (f == "--allow-shutdown") a.allow_shutdown = true;
     else if (f == "--inspect-gguf") a.inspect_gguf = need(i);
     else if (f == "--tensors") a.list_tensors = true;
+    else if (f == "--tokenizer-gguf") a.tokenizer_gguf = need(i);
+    else if (f == "--tokenize") { a.tokenize_text = need(i); a.have_tokenize = true; }
+    else if (f == "--detokenize") a.detokenize_ids = need(i);
     else if (f == "--help" || f == "-h") { usage(); std::exit(0); }
     else throw std::runtime_error("unknown flag " + f);
   }
@@ -246,7 +252,21 @@ void print_result(const char* tag, const Args& a, const pk::QwenEngine& eng, siz
   std::fflush(stdout);
 }
 
+int tokenizer_tool(const Args& a) {
+  pk::GgufFile f(a.tokenizer_gguf);
+  const pk::BpeTokenizer tok = pk::BpeTokenizer::from_gguf(f);
+  if (a.have_tokenize) {
+    const std::vector<int> ids = tok.encode(a.tokenize_text);
+    std::printf("token_ids=");
+    for (size_t i = 0; i < ids.size(); ++i) std::printf(i ? ",%d" : "%d", ids[i]);
+    std::printf("\n");
+  }
+  if (!a.detokenize_ids.empty()) std::printf("text=%s\n", tok.decode(parse_ids(a.detokenize_ids)).c_str());
+  return 0;
+}
+
 int run(const Args& a) {
+  if (!a.tokenizer_gguf.empty() && (a.have_tokenize || !a.detokenize_ids.empty())) return tokenizer_tool(a);
   if (!a.inspect_gguf.empty()) return inspect_gguf(a);
   if (a.serve && a.fake_engine) return serve_scripted(a);
   if (a.inspect) {

@@ -414,8 +414,20 @@ void QwenEngine::reset() {
   pending_site_ = -1;
 }
 
-std::unique_ptr<QwenEngine::Snapshot> QwenEngine::snapshot() {
+std::unique_ptr<QwenEngine::Snapshot> QwenEngine::snapshot(bool with_kv) {
   auto s = std::make_unique<Snapshot>();
+  if (with_kv && pos_ > 0) {
+    const size_t row = (size_t)pos_ * kHeadDim * sizeof(uint16_t), pitch = (size_t)opt_.max_context * kHeadDim * sizeof(uint16_t);
+    for (auto& L : layers_) {
+      if (!L.full) continue;
+      for (void* cache : {L.kcache, L.vcache}) {
+        void* b = nullptr;
+        cuda_check(cudaMalloc(&b, row * hkv_l_), "snapshot kv alloc");
+        cuda_check(cudaMemcpy2DAsync(b, row, cache, pitch, row, (size_t)hkv_l_, cudaMemcpyDeviceToDevice, stream_), "snapshot kv");
+        s->kv.push_back(b);
+      }
+    }
+  }
   for (auto& L : layers_) {
     if (L.full) continue;
     const size_t sb = (size_t)vh_l_ * kHeadDim * kHeadDim * sizeof(float), cb = (size_t)conv_c_l_ * 3 * sizeof(float);
@@ -453,6 +465,15 @@ void QwenEngine::restore(const Snapshot& s) {
     cuda_check(cudaMemcpyAsync(L.lin_state, s.bufs[i++], sb, cudaMemcpyDeviceToDevice, stream_), "restore");
     cuda_check(cudaMemcpyAsync(L.conv_state, s.bufs[i++], cb, cudaMemcpyDeviceToDevice, stream_), "restore");
   }
+  if (!s.kv.empty()) {
+    const size_t row = (size_t)s.pos * kHeadDim * sizeof(uint16_t), pitch = (size_t)opt_.max_context * kHeadDim * sizeof(uint16_t);
+    size_t k = 0;
+    for (auto& L : layers_) {
+      if (!L.full) continue;
+      for (void* cache : {L.kcache, L.vcache})
+        cuda_check(cudaMemcpy2DAsync(cache, pitch, s.kv[k++], row, row, (size_t)hkv_l_, cudaMemcpyDeviceToDevice, stream_), "restore kv");
+    }
+  }
   // decode() reads its input token from slot 0 of the device token buffer
   cuda_check(cudaMemcpyAsync(next_tok_dev_, &s.last_token, sizeof(int), cudaMemcpyHostToDevice, stream_), "restore token");
   cuda_check(cudaStreamSynchronize(stream_), "restore");
@@ -463,7 +484,9 @@ void QwenEngine::restore(const Snapshot& s) {
 void QwenEngine::free_snapshot(Snapshot& s) {
   cudaStreamSynchronize(stream_);
   for (void* p : s.bufs) cudaFree(p);
+  for (void* p : s.kv) cudaFree(p);
   s.bufs.clear();
+  s.kv.clear();
 }
 
 uint32_t QwenEngine::comm_status() {

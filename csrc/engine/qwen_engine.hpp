@@ -116,10 +116,13 @@ class QwenEngine {
   // position indexed and needs no copy. Used by speculative decoding and the prefix cache.
   struct Snapshot {
     std::vector<void*> bufs;
+    std::vector<void*> kv;      // with_kv: K then V rows [0, pos) of every full-attention layer, [Hkv][pos][128] bf16
     int pos = 0;
     int last_token = 0;
   };
-  std::unique_ptr<Snapshot> snapshot();
+  // with_kv also copies the KV rows of positions [0, pos): needed when other requests run in between
+  // (prefix cache); a speculative rewind inside one request does not need it.
+  std::unique_ptr<Snapshot> snapshot(bool with_kv = false);
   void update_snapshot(Snapshot& s);   // re-capture into existing buffers (no allocation)
   void restore(const Snapshot& s);
   void free_snapshot(Snapshot& s);

@@ -333,6 +333,7 @@ class QwenEngine:
         L.pk_qwen_weight_bytes.restype = ctypes.c_ulonglong
         L.pk_ipc_open.restype = ctypes.c_void_p
         L.pk_qwen_snapshot.restype = ctypes.c_void_p
+        L.pk_qwen_snapshot_with_kv.restype = ctypes.c_void_p
         self.cfg = cfg
         text = cfg if isinstance(cfg, str) else cfg.to_json()
         self.tp_rank, self.tp_world, self.device = tp_rank, tp_world, device
@@ -387,8 +388,10 @@ class QwenEngine:
         return list(out)
 
     # -- recurrent-state snapshots (speculative decoding, prefix cache) -----------------
-    def snapshot(self) -> "EngineSnapshot":
-        h = self._L.pk_qwen_snapshot(self._h)
+    def snapshot(self, with_kv: bool = False) -> "EngineSnapshot":
+        """`with_kv` also keeps the KV rows before the current position, so that the snapshot stays valid after
+        other requests have used the engine (prefix cache)."""
+        h = (self._L.pk_qwen_snapshot_with_kv if with_kv else self._L.pk_qwen_snapshot)(self._h)
         if not h:
             raise EngineError(self._L.pk_engine_last_error().decode())
         return EngineSnapshot(self, ctypes.c_void_p(h))
@@ -400,6 +403,29 @@ class QwenEngine:
     @property
     def last_token(self) -> int:
         return self._L.pk_qwen_last_token(self._h)
+
+    def generate_cached(self, prompt: Sequence[int], max_new_tokens: int, cache) -> tuple[list[int], int]:
+        """`generate` through a `runtime.prefix_snapshot.PrefixSnapshotCache`: the longest cached prefix (whole blocks,
+        at least one token left to run) is restored instead of recomputed, and the state at the last block boundary of
+        this prompt is captured for later requests. Returns (tokens, number of prompt tokens that were reused)."""
+        prompt = list(prompt)
+        self.reset()
+        hit = cache.restore(prompt)
+        reused = 0
+        if hit is not None:
+            hit.state.restore()
+            reused = hit.length
+        boundary = (len(prompt) - 1) // cache.block * cache.block
+        first = None
+        if boundary > reused:
+            self.prefill(prompt[reused:boundary])
+            cache.capture(prompt[:boundary], self.snapshot(with_kv=True))
+            reused_now = boundary
+        else:
+            reused_now = reused
+        first = self.prefill(prompt[reused_now:])
+        out = [first] if max_new_tokens <= 1 else [first] + self.decode(max_new_tokens - 1)
+        return out[:max_new_tokens], reused
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int) -> list[int]:
         first = self.prefill(prompt)

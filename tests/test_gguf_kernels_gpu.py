@@ -120,3 +120,29 @@ def test_moe_forward_fixed_order_reduce_is_bitwise_reproducible():
     lo = go.gguf_moe_forward(x, w13[: w13.numel() // 2], w2[: w2.numel() // 2], "q4_k", "q4_k", E, I, seg, tok, rw, expert_offset=0, local_experts=4, routes=routes)
     hi = go.gguf_moe_forward(x, w13[w13.numel() // 2:], w2[w2.numel() // 2:], "q4_k", "q4_k", E, I, seg, tok, rw, expert_offset=4, local_experts=4, routes=routes)
     assert ((lo + hi - runs[0]).norm() / runs[0].norm()).item() < 1e-6
+
+
+def test_staged_experts_match_resident_experts():
+    """Experts staged from pinned host memory through a 3-slot device cache give the resident result."""
+    import numpy as np
+    from pocketllm_b200.formats import gguf_quants as gq
+    from pocketllm_b200.moe.expert_cache import ExpertStagingCache, staged_moe_forward
+    from pocketllm_b200.ops import gguf_ops as go
+    torch.manual_seed(1)
+    E, H, I, T, topk = 8, 256, 256, 21, 2
+    rng = np.random.default_rng(1)
+    w13 = torch.from_numpy(gq.quantize((rng.standard_normal((E * 2 * I, H)) * 0.05).astype(np.float32), "q4_k")).reshape(E, -1)
+    w2 = torch.from_numpy(gq.quantize((rng.standard_normal((E * H, I)) * 0.05).astype(np.float32), "q4_k")).reshape(E, -1)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E)[:topk] for _ in range(T)]).int().cuda()
+    wts = torch.rand(T, topk, device="cuda")
+    routes = go.group_routes(ids, wts, E)
+    want = go.gguf_moe_forward(x, w13.cuda().view(-1), w2.cuda().view(-1), "q4_k", "q4_k", E, I, *routes, routes=routes)
+    cache = ExpertStagingCache({"w13": w13, "w2": w2}, slots=3)
+    got = staged_moe_forward(cache, x, ids, wts, "q4_k", "q4_k", I)
+    assert ((got - want).norm() / want.norm()).item() < 1e-6
+    assert cache.lru.stats["misses"] >= E - 1 and cache.bytes_staged > 0
+    again = staged_moe_forward(cache, x[:1], ids[:1], wts[:1], "q4_k", "q4_k", I)            # decode-like step
+    assert ((again - want[:1]).norm() / want[:1].norm()).item() < 1e-6
+    cache.prefetch([0, 1, 2])
+    assert all(int(cache.table[e]) >= 0 for e in (0, 1, 2))

@@ -198,3 +198,29 @@ def test_native_server_serves_the_engine(tiny):
             proc.wait(timeout=30)
         except Exception:
             proc.kill()
+
+
+def test_prefix_cache_reuses_state_across_requests(tiny):
+    """A snapshot with KV rows taken at a block boundary survives an unrelated request in between."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    from pocketllm_b200.runtime.prefix_snapshot import PrefixSnapshotCache
+    cfg, tensors, d = tiny
+    e = qh.QwenEngine(cfg, max_context=256, prefill_chunk=8).load(d)
+    cache = PrefixSnapshotCache(capacity=2, block=8, on_evict=lambda s: s.state.free())
+    shared = [(7 * i + 3) % 1000 for i in range(19)]
+    a, b = shared + [5, 6, 7], shared + [9, 8, 7, 6]
+    other = [(11 * i + 1) % 1000 for i in range(40)]
+    want_a, want_b = e.generate(a, 6), None
+    e.reset()
+    want_b = e.generate(b, 6)
+    e.reset()
+    got_a, reused_a = e.generate_cached(a, 6, cache)
+    assert got_a == want_a and reused_a == 0 and cache.stats["captures"] == 1
+    e.reset()
+    e.generate(other, 4)                                   # overwrites KV rows and recurrent state
+    got_b, reused_b = e.generate_cached(b, 6, cache)
+    assert reused_b == 16 and got_b == want_b
+    got_a2, reused_a2 = e.generate_cached(a, 6, cache)
+    assert reused_a2 == 16 and got_a2 == want_a
+    cache.clear()
+    e.close()

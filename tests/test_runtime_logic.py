@@ -148,3 +148,23 @@ def test_speculative_respects_eos_and_gate():
     gate = DSparkGate()
     out, st = speculative_generate(_FakeEngine(), prompt, 30, ReplayDrafter(ref[1:], len(prompt) + 1), k=4, gate=gate)
     assert out == ref and gate.stats["rounds"] == st.rounds
+
+
+def test_lru_slots_and_waves():
+    import torch
+    from pocketllm_b200.moe.expert_cache import LRUSlots, waves
+    lru = LRUSlots(3)
+    m, copies = lru.assign([5, 1, 5])
+    assert set(m) == {5, 1} and len(copies) == 2 and lru.stats == {"hits": 0, "misses": 2, "evictions": 0}
+    m, copies = lru.assign([7])
+    assert len(copies) == 1 and lru.stats["evictions"] == 0
+    m, copies = lru.assign([1, 9])                          # 5 is the least recently used and goes
+    assert copies == [(9, m[9])] and 5 not in lru.where and lru.stats["evictions"] == 1 and lru.stats["hits"] == 1
+    m, copies = lru.assign([5, 7, 9])                       # 1 must go although it was used more recently than 7's slot holder
+    assert 1 not in lru.where and len({m[5], m[7], m[9]}) == 3
+    import pytest
+    with pytest.raises(ValueError):
+        lru.assign([0, 1, 2, 3])
+    ids = torch.tensor([[0, 1], [1, 2], [3, 4], [4, 0], [5, 6]])
+    assert waves(ids, 3) == [(0, 2), (2, 4), (4, 5)]
+    assert waves(ids, 8) == [(0, 5)]
