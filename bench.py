@@ -163,7 +163,7 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": args.prompt_len * 4, "d2h_bytes_per_step": (args.decode_len + 1) * 4,
                 "wall_ms_per_step": round(e2e_wall_ms / args.steps, 3)},
         "gpu_launches": int(launches), "wall_ms": round(wall_ms, 1), "comm_status": status,
-        "weight_bytes_per_rank": eng.weight_bytes, "last_tokens": toks[-4:],
+        "weight_bytes_per_rank": eng.weight_bytes, "prefill_bf16_shadow_bytes_per_rank": eng.prefill_shadow_bytes, "last_tokens": toks[-4:],
     }
     eng.close()
     if world > 1:

@@ -124,6 +124,8 @@ PK_EAPI unsigned pk_qwen_comm_status(void* h) {
   return s;
 }
 PK_EAPI unsigned long long pk_qwen_weight_bytes(void* h) { return ((pk::QwenEngine*)h)->weight_bytes(); }
+// bytes of the bf16 copies kept for the prefill GEMM (0 when they are off)
+PK_EAPI unsigned long long pk_qwen_shadow_bytes(void* h) { return ((pk::QwenEngine*)h)->shadow_bytes(); }
 
 // out[0] prefill_ms, out[1] decode_ms, out[2] prefill_tokens, out[3] decode_tokens, out[4] launches
 PK_EAPI void pk_qwen_timings(void* h, double* out) {

@@ -66,4 +66,5 @@ int pk_cand_push(const float* val, const int* idx, int M, const PkPush* push, fl
                  int* const* peer_idx, cudaStream_t stream);
 int pk_cand_merge_wait(const float* cand_val, const int* cand_idx, int M, int world, const PkWait* wait,
                        int* out_idx, cudaStream_t stream);
+int pk_fp8_to_bf16(const void* w, const float* scale, int N, int K, void* out, cudaStream_t stream);
 }

@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <stdexcept>
 
@@ -250,6 +251,35 @@ QwenEngine::~QwenEngine() {
 // ---------------------------------------------------------------------------------------
 // weights
 
+void QwenEngine::build_prefill_shadow() {
+  int mode = opt_.prefill_bf16_shadow;
+  if (const char* v = getenv("POCKET_PREFILL_SHADOW")) mode = atoi(v);
+  if (mode == 0 || shadow_bytes_ > 0) return;
+  size_t need = 0;
+  auto count = [&](const Fp8Linear& l) { need += (size_t)l.N * l.K * 2; };
+  for (auto& L : layers_) {
+    if (L.full) { count(L.qkv); count(L.o_proj); } else { count(L.in_proj); count(L.out_proj); }
+    count(L.gate_up);
+    count(L.down);
+  }
+  if (mode < 0) {
+    size_t free_b = 0, total_b = 0;
+    if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess || free_b < need + (size_t(16) << 30)) return;   // keep 16 GiB for activations / KV
+  }
+  auto make = [&](Fp8Linear& l) {
+    if (l.N == 0 || (l.K & 15)) return;
+    l.wb = dalloc((size_t)l.N * l.K * 2);
+    check(pk_fp8_to_bf16(l.w, l.scale, l.N, l.K, l.wb, stream_), "fp8_to_bf16");
+  };
+  for (auto& L : layers_) {
+    if (L.full) { make(L.qkv); make(L.o_proj); } else { make(L.in_proj); make(L.out_proj); }
+    make(L.gate_up);
+    make(L.down);
+  }
+  cuda_check(cudaStreamSynchronize(stream_), "prefill shadow");
+  shadow_bytes_ = need;
+}
+
 void QwenEngine::init_random(uint64_t seed, float sigma) {
   uint64_t s = seed * 1000003ull + 17;
   auto fp8 = [&](Fp8Linear& l) { check(pk_fill_fp8_gauss(l.w, l.scale, l.N, l.K, sigma, s++, stream_), "fill fp8"); };
@@ -280,6 +310,7 @@ void QwenEngine::init_random(uint64_t seed, float sigma) {
   check(pk_fill_f32_gauss(final_norm_, hidden_, 0.f, 0.02f, seed * 7919ull + 2, stream_), "fill norm");
   b16(lm_head_, (size_t)vocab_l_ * hidden_, sigma);
   cuda_check(cudaStreamSynchronize(stream_), "init_random");
+  build_prefill_shadow();
 }
 
 void QwenEngine::load_safetensors(const std::string& path) {
@@ -395,6 +426,7 @@ void QwenEngine::load_safetensors(const std::string& path) {
   }
   (void)W;
   cuda_check(cudaDeviceSynchronize(), "load_safetensors");
+  build_prefill_shadow();
 }
 
 // ---------------------------------------------------------------------------------------
@@ -642,7 +674,10 @@ void QwenEngine::run_chunk(int M) {
   check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hid, nullptr, stream_), "embedding");
   int pending = -1;  // site whose partial sums still wait to be added to the residual stream
   auto gemm = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc) {
-    check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, stream_), "gemm_umma");
+    if (w.wb != nullptr)
+      check(pk_gemm_umma(A, lda, w.wb, nullptr, 1, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, stream_), "gemm_umma(bf16)");
+    else
+      check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, stream_), "gemm_umma");
   };
   // Row-parallel projection back into the residual stream. One rank: residual add in the
   // epilogue. Several ranks: the epilogue pushes the fp32 partial tiles into every rank's
@@ -652,7 +687,8 @@ void QwenEngine::run_chunk(int M) {
       gemm(A, lda, w, 2, hid, hid, hidden_);
     } else {
       PkPush ps = make_push(site, true);
-      check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, 4, nullptr, nullptr, hidden_, gemm_status_, &ps, stream_),
+      check(pk_gemm_umma(A, lda, w.wb ? w.wb : (const void*)w.w, w.wb ? nullptr : w.scale, w.wb ? 1 : 0, M, w.N, w.K, 4, nullptr, nullptr,
+                         hidden_, gemm_status_, &ps, stream_),
             "gemm_umma(push)");
       pending = site;
     }

@@ -29,11 +29,16 @@ struct QwenEngineOptions {
   int attention_window = 0;    // 0 = full attention
   int attention_sink = 0;
   uint32_t comm_timeout_us = 2000000;
+  // bf16 copies of the FP8 linears for the tensor-core prefill path (the decode path keeps streaming FP8):
+  // -1 = when HBM has room for them (twice the FP8 bytes plus a reserve), 0 = never, 1 = always.
+  // POCKET_PREFILL_SHADOW in the environment overrides.
+  int prefill_bf16_shadow = -1;
 };
 
 struct Fp8Linear {
   uint8_t* w = nullptr;   // [N, K] e4m3
   float* scale = nullptr; // [ceil(N/128), ceil(K/128)]
+  void* wb = nullptr;     // optional bf16 [N, K] copy used by the prefill GEMM
   int N = 0, K = 0;
 };
 
@@ -110,6 +115,7 @@ class QwenEngine {
   const QwenConfig& config() const { return cfg_; }
   const QwenEngineOptions& options() const { return opt_; }
   size_t weight_bytes() const { return weight_bytes_; }
+  size_t shadow_bytes() const { return shadow_bytes_; }
   cudaStream_t stream() const { return stream_; }
 
   // Recurrent-state snapshot (DeltaNet state + conv tails of every linear layer); KV is
@@ -129,6 +135,7 @@ class QwenEngine {
 
  private:
   void alloc_buffers();
+  void build_prefill_shadow();   // after the weights are in place
   void alloc_fp8(Fp8Linear& l, int N, int K);
   void* dalloc(size_t bytes, bool weight = false);
   void run_small(int M, bool all_logits);    // M <= 8 rows: weight-streaming path
@@ -156,6 +163,7 @@ class QwenEngine {
   float* final_norm_ = nullptr;
   void* lm_head_ = nullptr;   // bf16 [vocab_l, hidden]
   size_t weight_bytes_ = 0;
+  size_t shadow_bytes_ = 0;
   std::vector<void*> allocs_;
 
   // activations

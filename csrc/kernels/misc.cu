@@ -374,3 +374,38 @@ PK_API int pk_cand_merge_wait(const float* cand_val, const int* cand_idx, int M,
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
+
+// FP8 E4M3 block-128 weights -> bf16 (w = e4m3(code) * scale[n / 128][k / 128]); 16 weights per thread.
+namespace {
+__global__ void __launch_bounds__(256) fp8_to_bf16_kernel(const uint8_t* __restrict__ w, const float* __restrict__ scale, int N, int K,
+                                                          pk::bf16* __restrict__ out) {
+  const size_t total16 = (size_t)N * K / 16;
+  const int kb = (K + 127) >> 7;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total16; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t e = i * 16;
+    const int n = (int)(e / K), k = (int)(e % K);
+    const float s = scale[(size_t)(n >> 7) * kb + (k >> 7)];
+    const uint4 raw = *reinterpret_cast<const uint4*>(w + e);
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t packed[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = pk::e4m3x2_to_float2((uint16_t)(words[j] & 0xffffu)), b = pk::e4m3x2_to_float2((uint16_t)(words[j] >> 16));
+      const __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x * s, a.y * s), p1 = __floats2bfloat162_rn(b.x * s, b.y * s);
+      packed[2 * j] = *reinterpret_cast<const uint32_t*>(&p0);
+      packed[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&p1);
+    }
+    uint4* o = reinterpret_cast<uint4*>(out + e);
+    o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+  }
+}
+}  // namespace
+
+// K must be a multiple of 16; w and out 16-byte aligned.
+PK_API int pk_fp8_to_bf16(const void* w, const float* scale, int N, int K, void* out, cudaStream_t stream) {
+  if (N < 1 || K < 16 || (K & 15) != 0) return PK_ERR_BAD_ARG;
+  fp8_to_bf16_kernel<<<1184, 256, 0, stream>>>((const uint8_t*)w, scale, N, K, (pk::bf16*)out);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}

@@ -331,6 +331,7 @@ class QwenEngine:
         L.pk_engine_last_error.restype = ctypes.c_char_p
         L.pk_qwen_comm_arena.restype = ctypes.c_void_p
         L.pk_qwen_weight_bytes.restype = ctypes.c_ulonglong
+        L.pk_qwen_shadow_bytes.restype = ctypes.c_ulonglong
         L.pk_ipc_open.restype = ctypes.c_void_p
         L.pk_qwen_snapshot.restype = ctypes.c_void_p
         L.pk_qwen_snapshot_with_kv.restype = ctypes.c_void_p
@@ -446,6 +447,11 @@ class QwenEngine:
     @property
     def weight_bytes(self) -> int:
         return int(self._L.pk_qwen_weight_bytes(self._h))
+
+    @property
+    def prefill_shadow_bytes(self) -> int:
+        """Bytes of the bf16 weight copies used by the tensor-core prefill path (0 when off)."""
+        return int(self._L.pk_qwen_shadow_bytes(self._h))
 
     def comm_status(self) -> int:
         return int(self._L.pk_qwen_comm_status(self._h)) & 0xFFFFFFFF
