@@ -1,6 +1,7 @@
 // C ABI of the native engine, used by the Python package (ctypes) and by external
 // callers. Every function returns 0 on success; pk_engine_last_error() gives the
 // message of the last failure on the calling thread.
+#include <algorithm>
 #include <cstring>
 #include <string>
 
@@ -47,7 +48,9 @@ PK_EAPI void* pk_qwen_create(const char* config_json, int tp_rank, int tp_world,
     opt.device = device;
     if (max_context > 0) opt.max_context = max_context;
     if (prefill_chunk > 0) opt.prefill_chunk = prefill_chunk;
+    // 0 = choose from the context length: one split per 2048 positions, between 8 and 64
     if (decode_splits > 0) opt.decode_splits = decode_splits;
+    else opt.decode_splits = std::min(64, std::max(8, max_context / 2048));
     opt.use_cuda_graph = use_cuda_graph != 0;
     eng = new pk::QwenEngine(cfg, opt);
   });

@@ -316,8 +316,11 @@ def random_checkpoint(cfg: DSV4Config, seed: int = 0, sigma: float = 0.05) -> di
 
 
 def expert_weight(W: dict, name: str) -> torch.Tensor:
-    """Dequantised fp32 matrix of an FP4 expert tensor (`name` without the `.weight` suffix)."""
-    return fp4fmt.dequantize_e2m1(W[name + ".weight"], W[name + ".scale"])
+    """fp32 matrix of a routed expert (`name` without the `.weight` suffix): FP4 nibbles + E8M0 scales, or already dense."""
+    w = W[name + ".weight"]
+    if w.is_floating_point():
+        return w.float()
+    return fp4fmt.dequantize_e2m1(w, W[name + ".scale"])
 
 
 # ---------------------------------------------------------------------------------------

@@ -81,7 +81,7 @@ def pack_mxfp4(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
 
 
 class _BlockWeights:
-    def __init__(self, cfg: d4.DSV4Config, W: dict, p: str, layer: int, e_lo: int = 0, e_hi: int | None = None):
+    def __init__(self, cfg: d4.DSV4Config, W: dict, p: str, layer: int, e_lo: int = 0, e_hi: int | None = None, raw_experts: dict | None = None):
         f32 = lambda n: W[n].float().cuda().contiguous()
         self.name = p
         self.ratio = cfg.ratio(layer)
@@ -110,12 +110,18 @@ class _BlockWeights:
         self.gate_bias = f32(f"{f}.gate.bias") if f"{f}.gate.bias" in W else None
         self.tid2eid = W[f"{f}.gate.tid2eid"].to(torch.int32).cuda().contiguous() if self.hash else None
         self.e_lo, self.e_hi = e_lo, cfg.n_routed_experts if e_hi is None else e_hi
-        w13, w2 = [], []
-        for e in range(self.e_lo, self.e_hi):               # this rank's experts only
-            w13.append(torch.cat([pack_mxfp4(W[f"{f}.experts.{e}.w1.weight"], W[f"{f}.experts.{e}.w1.scale"]),
-                                  pack_mxfp4(W[f"{f}.experts.{e}.w3.weight"], W[f"{f}.experts.{e}.w3.scale"])], 0))
-            w2.append(pack_mxfp4(W[f"{f}.experts.{e}.w2.weight"], W[f"{f}.experts.{e}.w2.scale"]))
-        self.w13, self.w2 = torch.stack(w13).cuda().contiguous(), torch.stack(w2).cuda().contiguous()
+        if raw_experts is not None and f"{f}.w13" in raw_experts:
+            # GGUF checkpoint: blocks exactly as stored, this rank's experts only
+            (b13, self.type13), (b2, self.type2) = raw_experts[f"{f}.w13"], raw_experts[f"{f}.w2"]
+            self.w13, self.w2 = b13[self.e_lo:self.e_hi].cuda().contiguous(), b2[self.e_lo:self.e_hi].cuda().contiguous()
+        else:
+            self.type13 = self.type2 = "mxfp4"
+            w13, w2 = [], []
+            for e in range(self.e_lo, self.e_hi):               # this rank's experts only
+                w13.append(torch.cat([pack_mxfp4(W[f"{f}.experts.{e}.w1.weight"], W[f"{f}.experts.{e}.w1.scale"]),
+                                      pack_mxfp4(W[f"{f}.experts.{e}.w3.weight"], W[f"{f}.experts.{e}.w3.scale"])], 0))
+                w2.append(pack_mxfp4(W[f"{f}.experts.{e}.w2.weight"], W[f"{f}.experts.{e}.w2.scale"]))
+            self.w13, self.w2 = torch.stack(w13).cuda().contiguous(), torch.stack(w2).cuda().contiguous()
         s = f"{f}.shared_experts"
         if W[f"{s}.w1.weight"].dtype == torch.float8_e4m3fn and W[f"{s}.w1.weight"].shape[0] % 128 == 0:
             # stacked gate|up keeps FP8: the row blocks of both halves stay aligned to 128
@@ -147,8 +153,9 @@ class DSV4Runtime:
     greedy token after each row; `rollback(position)` rewinds to an earlier position."""
 
     def __init__(self, cfg: d4.DSV4Config, weights: dict[str, torch.Tensor], *, max_context: int | None = None, max_rows: int = 64,
-                 rank: int = 0, world: int = 1, group=None, use_peer_allreduce: bool = True):
-        """With `world > 1` the routed experts are split over the ranks in contiguous ranges (everything else is
+                 rank: int = 0, world: int = 1, group=None, use_peer_allreduce: bool = True, raw_experts: dict | None = None):
+        """`raw_experts` (from `deepseek_v4_gguf.load_gguf`) supplies routed experts as GGUF blocks instead of FP4 tensors in `weights`.
+        With `world > 1` the routed experts are split over the ranks in contiguous ranges (everything else is
         replicated) and their outputs are summed across ranks; every rank feeds the same tokens."""
         self.cfg = cfg
         if cfg.n_routed_experts % world:
@@ -165,7 +172,7 @@ class DSV4Runtime:
         W = weights
         f32 = lambda n: W[n].float().cuda().contiguous()
         self.embed = W["embed.weight"].float().cuda()
-        self.blocks = [_BlockWeights(cfg, W, f"layers.{i}", i, e_lo, e_hi) for i in range(cfg.n_layers)]
+        self.blocks = [_BlockWeights(cfg, W, f"layers.{i}", i, e_lo, e_hi, raw_experts) for i in range(cfg.n_layers)]
         self.hc_head = (f32("hc_head_fn"), f32("hc_head_scale"), f32("hc_head_base"))
         self.norm = f32("norm.weight")
         self.head = _Lin(W["head.weight"])
@@ -259,7 +266,7 @@ class DSV4Runtime:
             self.capture.setdefault(f"{b.name}.ffn.route_idx", []).append(ids.clone())
         routes = gk.group_routes(ids, w, cfg.n_routed_experts)
         seg, tok, rw = routes
-        y = gk.gguf_moe_forward(x, self.w_flat(b.w13), self.w_flat(b.w2), "mxfp4", "mxfp4", cfg.n_routed_experts, cfg.moe_inter_dim,
+        y = gk.gguf_moe_forward(x, self.w_flat(b.w13), self.w_flat(b.w2), b.type13, b.type2, cfg.n_routed_experts, cfg.moe_inter_dim,
                                 seg, tok, rw, limit=cfg.swiglu_limit, expert_offset=b.e_lo, local_experts=b.e_hi - b.e_lo, routes=routes)
         y = self.combine(y)
         hs = ops.silu_mul(b.s_w13(x), cfg.swiglu_limit)

@@ -324,7 +324,7 @@ class QwenEngine:
     """
 
     def __init__(self, cfg: QwenHybridConfig | str, *, tp_rank: int = 0, tp_world: int = 1, device: int = 0,
-                 max_context: int = 4096, prefill_chunk: int = 512, use_cuda_graph: bool = True, decode_splits: int = 8):
+                 max_context: int = 4096, prefill_chunk: int = 512, use_cuda_graph: bool = True, decode_splits: int = 0):
         self._L = _lib.engine()
         L = self._L
         L.pk_qwen_create.restype = ctypes.c_void_p

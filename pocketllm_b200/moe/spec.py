@@ -13,7 +13,7 @@ from typing import Any
 from ..formats import gguf
 
 # block types every kernel path can decode in place
-SUPPORTED_QUANTS = ("f32", "f16", "bf16", "q8_0", "q2_k", "q4_k", "q5_k", "q6_k", "iq1_m", "iq2_xxs", "iq2_xs", "iq3_xxs", "iq4_xs")
+SUPPORTED_QUANTS = ("f32", "f16", "bf16", "i32", "q8_0", "q2_k", "q4_k", "q5_k", "q6_k", "iq1_m", "iq2_xxs", "iq2_xs", "iq3_xxs", "iq4_xs")
 
 
 @dataclass
@@ -91,6 +91,10 @@ def _plan_for(arch: str, md: dict):
         from ..models import glm_dsa as m
         cfg = m.GLMDSAConfig.from_gguf(md)
         return cfg, m.tensor_plan(cfg)
+    if arch == "deepseek4":
+        from ..models import deepseek_v4_gguf as m
+        cfg = m.config_from_metadata(md)
+        return cfg, m.tensor_plan(cfg)
     raise KeyError(f"no spec for architecture {arch!r}")
 
 
@@ -101,6 +105,10 @@ def parse_params(bundle: gguf.GGUFBundle) -> MoEArchitectureParams:
         return MoEArchitectureParams(arch, cfg.n_layers, cfg.dim, cfg.vocab_size, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
                                      cfg.n_experts, cfg.n_experts_used, cfg.expert_inter, 0, 0,
                                      int(bundle.metadata.get(arch + ".context_length", 0)), cfg.rope_dim, cfg.rope_theta, cfg.norm_eps)
+    if arch == "deepseek4":
+        return MoEArchitectureParams(arch, cfg.n_layers, cfg.dim, cfg.vocab_size, cfg.n_heads, 1, cfg.head_dim, cfg.n_routed_experts,
+                                     cfg.n_activated_experts, cfg.moe_inter_dim, cfg.n_shared_experts, 0, cfg.max_seq_len, cfg.rope_head_dim,
+                                     cfg.rope_theta, cfg.norm_eps)
     return MoEArchitectureParams(arch, cfg.n_layers, cfg.dim, cfg.vocab_size, cfg.n_heads, 1, cfg.key_mla_dim, cfg.n_experts, cfg.top_k,
                                  cfg.expert_inter, cfg.n_shared, cfg.leading_dense_layers,
                                  int(bundle.metadata.get(arch + ".context_length", 0)), cfg.rope_dim, cfg.rope_theta, cfg.norm_eps)
@@ -118,7 +126,7 @@ def validate(bundle: gguf.GGUFBundle) -> SpecValidation:
         t = have[name]
         if tuple(t.shape) != tuple(shape):
             v.wrong_shape.append(f"{name}: {tuple(t.shape)} != {tuple(shape)}")
-        if t.type_name not in SUPPORTED_QUANTS or (typ == "f32" and t.type_name != "f32"):
+        if t.type_name not in SUPPORTED_QUANTS or (typ in ("f32", "i32") and t.type_name != typ):
             v.unexpected_types.append(f"{name}: {t.type_name}")
     v.ok = not (v.missing or v.wrong_shape or v.unexpected_types)
     return v

@@ -332,3 +332,45 @@ def test_generate_cli_on_a_saved_checkpoint(tiny, tmp_path, capsys):
     spec = capsys.readouterr().out
     assert len(plain.rstrip("\n")) > 0 and spec == plain
     assert generate.main(base + ["--temperature", "1.0", "--seed", "3"]) == 0
+
+
+def test_gguf_roundtrip_oracle_and_spec(tiny, tmp_path):
+    from pocketllm_b200.formats import gguf
+    from pocketllm_b200.models import deepseek_v4_gguf as dg
+    from pocketllm_b200.moe import spec
+    cfg, W = tiny
+    p = tmp_path / "v4.gguf"
+    dg.write_gguf(p, cfg, W, dense_type="q8_0", expert_type="q4_k")
+    b = gguf.GGUFBundle(p)
+    assert b.architecture() == "deepseek4" and spec.validate(b).ok
+    params = spec.parse_params(b)
+    assert params.n_routed_experts == cfg.n_routed_experts and params.top_k == cfg.n_activated_experts
+    assert spec.placement(b).mode == "resident"
+    cfg2, D, raw = dg.load_gguf(p)
+    assert cfg2 == cfg and raw["layers.1.ffn.w13"][1] == "q4_k" and raw["layers.1.ffn.w13"][0].shape[0] == cfg.n_routed_experts
+    assert torch.equal(D["layers.0.ffn.gate.tid2eid"], W["layers.0.ffn.gate.tid2eid"])
+    assert (D["layers.1.attn.wq_b.weight"] - W["layers.1.attn.wq_b.weight"]).abs().max() < 2e-3          # q8_0 error
+    full = dg.dense_experts(p, D)
+    toks = [(i * 13 + 5) % cfg.vocab_size for i in range(21)]
+    lg, _ = d4.DSV4Oracle(cfg2, full).forward(toks)
+    ref, _ = d4.DSV4Oracle(cfg, W).forward(toks)
+    assert torch.isfinite(lg).all() and ((lg - ref).norm() / ref.norm()).item() < 0.35        # 4-bit experts vs FP4 experts
+
+
+@pytest.mark.gpu
+def test_runtime_from_gguf_matches_oracle(tiny, tmp_path):
+    from pocketllm_b200.models import deepseek_v4_gguf as dg
+    from pocketllm_b200.models.deepseek_v4_runtime import DSV4Runtime
+    cfg, W = tiny
+    p = tmp_path / "v4.gguf"
+    dg.write_gguf(p, cfg, W, dense_type="q8_0", expert_type="q4_k")
+    cfg2, D, raw = dg.load_gguf(p)
+    g = torch.Generator().manual_seed(17)
+    prompt = torch.randint(0, cfg.vocab_size, (43,), generator=g).tolist()
+    rt = DSV4Runtime(cfg2, D, max_context=128, max_rows=16, raw_experts=raw)
+    assert rt.blocks[0].type13 == "q4_k" and not rt.mtp
+    rt.capture = {}
+    got = rt.forward_logits(prompt)
+    oracle = d4.DSV4Oracle(cfg2, dg.dense_experts(p, D), device="cuda")
+    want, _ = _pinned(oracle, rt.capture).forward(prompt)
+    assert _rel(got, want) < 3e-2
