@@ -674,9 +674,12 @@ void QwenEngine::run_chunk(int M) {
   check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hid, nullptr, stream_), "embedding");
   int pending = -1;  // site whose partial sums still wait to be added to the residual stream
   auto gemm = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc) {
-    if (w.wb != nullptr)
-      check(pk_gemm_umma(A, lda, w.wb, nullptr, 1, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, stream_), "gemm_umma(bf16)");
-    else
+    if (w.wb != nullptr) {
+      // persistent 128x256 kernel; shapes it does not take (SwiGLU halves not a multiple of 128) go to the 128x128 one
+      int rc = pk_gemm_bf16(A, lda, w.wb, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, sm_count_, stream_);
+      if (rc == 4) rc = pk_gemm_umma(A, lda, w.wb, nullptr, 1, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, stream_);
+      check(rc, "gemm_bf16");
+    } else
       check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, stream_), "gemm_umma");
   };
   // Row-parallel projection back into the residual stream. One rank: residual add in the
@@ -687,9 +690,10 @@ void QwenEngine::run_chunk(int M) {
       gemm(A, lda, w, 2, hid, hid, hidden_);
     } else {
       PkPush ps = make_push(site, true);
-      check(pk_gemm_umma(A, lda, w.wb ? w.wb : (const void*)w.w, w.wb ? nullptr : w.scale, w.wb ? 1 : 0, M, w.N, w.K, 4, nullptr, nullptr,
-                         hidden_, gemm_status_, &ps, stream_),
-            "gemm_umma(push)");
+      if (w.wb != nullptr)
+        check(pk_gemm_bf16(A, lda, w.wb, M, w.N, w.K, 4, nullptr, nullptr, hidden_, gemm_status_, &ps, sm_count_, stream_), "gemm_bf16(push)");
+      else
+        check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, 4, nullptr, nullptr, hidden_, gemm_status_, &ps, stream_), "gemm_umma(push)");
       pending = site;
     }
   };

@@ -14,7 +14,7 @@ import torch
 from . import lib as _lib
 
 __all__ = [
-    "matvec", "gemm_umma", "deltanet_seq", "deltanet_chunked", "qk_norm_rope_append", "gqa_decode", "rmsnorm",
+    "matvec", "gemm_umma", "gemm_bf16", "deltanet_seq", "deltanet_chunked", "qk_norm_rope_append", "gqa_decode", "rmsnorm",
     "embedding", "argmax", "silu_mul", "KernelError",
 ]
 
@@ -81,6 +81,22 @@ def gemm_umma(a: torch.Tensor, w: torch.Tensor, scale: torch.Tensor | None = Non
         _ptr(a), c_int(a.stride(0)), _ptr(w), _ptr(scale), c_int(wfmt), c_int(M), c_int(N), c_int(K), c_int(epi),
         _ptr(c), _ptr(resid), c_int(ncols), _ptr(status), c_void_p(0), _stream())
     _check(st, "pk_gemm_umma")
+    return c
+
+
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, epi: int = EPI_BF16, resid: torch.Tensor | None = None,
+              status: torch.Tensor | None = None) -> torch.Tensor:
+    """Persistent tcgen05 GEMM with 128x256 tiles and a double-buffered TMEM accumulator: C = A @ W^T, bf16 A [M, K] and W [N, K].
+    Same epilogues as `gemm_umma`."""
+    M, K = a.shape
+    N = w.shape[0]
+    ncols = N // 2 if epi == EPI_SWIGLU else N
+    c = torch.empty(M, ncols, device=a.device, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16)
+    if status is None:
+        status = torch.zeros(1, device=a.device, dtype=torch.int32)
+    st = _lib.kernels().pk_gemm_bf16(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(epi), _ptr(c), _ptr(resid),
+                                     c_int(ncols), _ptr(status), c_void_p(0), c_int(_sm_count()), _stream())
+    _check(st, "pk_gemm_bf16")
     return c
 
 

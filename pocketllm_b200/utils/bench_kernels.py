@@ -56,7 +56,7 @@ def _fp8(n: int, k: int) -> tuple[torch.Tensor, torch.Tensor]:
 
 def bench_gemm(M: int, N: int, K: int, epi: int, iters: int, wfmt: str = "fp8") -> dict:
     hbm, tf, src = peaks()
-    if wfmt == "bf16":
+    if wfmt in ("bf16", "bf16p"):
         ws = [((torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16), None) for _ in range(_copies(N * K * 2))]
     elif wfmt == "cublas":
         ws = [((torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16), None) for _ in range(_copies(N * K * 2))]
@@ -66,11 +66,13 @@ def bench_gemm(M: int, N: int, K: int, epi: int, iters: int, wfmt: str = "fp8") 
     resid = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16) if epi == ops.EPI_RESID else None
     if wfmt == "cublas":
         fns = [(lambda w=w: torch.matmul(a, w.t())) for w, _ in ws]
+    elif wfmt == "bf16p":
+        fns = [(lambda w=w: ops.gemm_bf16(a, w, epi=epi, resid=resid)) for w, _ in ws]
     else:
         fns = [(lambda w=w, s=s: ops.gemm_umma(a, w, s, epi=epi, resid=resid)) for w, s in ws]
     us = _time(fns, iters)
     flops = 2.0 * M * N * K
-    return {"op": "gemm_umma" if wfmt != "cublas" else "torch.matmul", "wfmt": wfmt, "M": M, "N": N, "K": K, "epi": epi, "us": round(us, 2),
+    return {"op": "torch.matmul" if wfmt == "cublas" else "gemm_bf16" if wfmt == "bf16p" else "gemm_umma", "wfmt": wfmt, "M": M, "N": N, "K": K, "epi": epi, "us": round(us, 2),
             "tflops": round(flops / us / 1e6, 1), "frac_of_peak": round(flops / us / 1e6 / tf, 3), "peak": f"{tf} TFLOP/s bf16 ({src})",
             "weight_gbs": round(N * K / us / 1e3, 1)}
 
@@ -95,7 +97,7 @@ def main() -> int:
     ap.add_argument("--K", type=int, default=5120)
     ap.add_argument("--epi", type=int, default=0)
     ap.add_argument("--iters", type=int, default=40)
-    ap.add_argument("--wfmt", default="fp8", choices=["fp8", "bf16", "cublas"], help="gemm: weight format (cublas = torch.matmul on bf16, the library baseline)")
+    ap.add_argument("--wfmt", default="fp8", choices=["fp8", "bf16", "bf16p", "cublas"], help="gemm: weight format (cublas = torch.matmul on bf16, the library baseline)")
     ap.add_argument("--suite", action="store_true", help="all projections of the 27B-shaped model")
     args = ap.parse_args()
     if args.suite:

@@ -112,6 +112,39 @@ def test_gemm_umma_narrow_n():
     assert _rel_err(c, a.float() @ wb.float().t()) < 6e-3
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 512), (300, 768, 1024), (130, 64, 256), (1, 256, 64), (700, 2304, 320)])
+def test_gemm_bf16_persistent_tiles(M, N, K):
+    """128x256 tiles, several tiles per CTA (double-buffered accumulator), ragged M and N edges."""
+    from pocketllm_b200 import ops
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    ref = a.float() @ w.float().t()
+    c = ops.gemm_bf16(a, w, epi=ops.EPI_F32, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and _rel_err(c, ref) < 2e-3
+    assert _rel_err(ops.gemm_bf16(a, w), ref) < 6e-3
+    resid = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    assert _rel_err(ops.gemm_bf16(a, w, epi=ops.EPI_RESID, resid=resid), resid.float() + ref) < 6e-3
+    if (N // 2) % 128 == 0:
+        got = ops.gemm_bf16(a, w, epi=ops.EPI_SWIGLU)
+        want = torch.nn.functional.silu(ref[:, : N // 2]) * ref[:, N // 2:]
+        assert got.shape == (M, N // 2) and _rel_err(got, want) < 1.5e-2
+
+
+def test_gemm_bf16_many_tiles_per_cta():
+    """More tiles than SMs: every CTA walks several tiles and both accumulators are reused."""
+    from pocketllm_b200 import ops
+    torch.manual_seed(5)
+    M, N, K = 1024, 12288, 256                # 8 x 48 = 384 tiles
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    c = ops.gemm_bf16(a, w)
+    assert _rel_err(c, a.float() @ w.float().t()) < 6e-3
+    assert torch.equal(c, ops.gemm_bf16(a, w))
+
+
 def test_rmsnorm_embedding_argmax():
     from pocketllm_b200 import ops
     x = torch.randn(5, 640, device="cuda").to(torch.bfloat16)
