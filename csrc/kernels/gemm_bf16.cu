@@ -13,6 +13,9 @@
 //   warps 2-9   epilogue (tcgen05.ld, then bf16 store / residual add / SiLU(gate)*up / fp32 / push to peers)
 //
 // Every mbarrier wait is bounded (status word + CTA-wide abort flag), as in gemm_umma.cu.
+#include <cstdlib>
+#include <mutex>
+
 #include "../common/pk_comm.cuh"
 #include "../common/pk_sm100.cuh"
 
@@ -40,6 +43,49 @@ struct Params {
   int tiles_m, tiles_n;
   uint32_t* status;
   PkPush push;
+  // stream-K: the k-steps of all tiles, laid end to end, are cut into one contiguous range per CTA
+  int streamk;
+  float* ws;            // [gridDim.x][BM][BN] fp32 partial accumulators (each CTA writes at most one)
+  uint32_t* flags;      // [gridDim.x] sequence number of the launch whose partial is in ws
+  uint32_t seq;
+  uint32_t timeout_us;
+};
+
+// One stretch of k-steps of one tile. A CTA's first segment may start in the middle of a tile (the CTA before it
+// owns that tile and adds this partial); its last one may end early (then this CTA owns the tile and adds the
+// partials of the CTAs after it, which computed them at the very start of their run).
+struct Seg {
+  int tile, kb0, kb1;
+};
+
+struct WorkIter {
+  int num_kb, num_tiles, streamk;
+  long long pos, end;     // stream-K: flattened k-steps
+  int t, stride;          // tile mode
+  __device__ WorkIter(const Params& p, int nkb) : num_kb(nkb), num_tiles(p.tiles_m * p.tiles_n), streamk(p.streamk) {
+    const long long total = (long long)num_tiles * num_kb;
+    pos = total * blockIdx.x / gridDim.x;
+    end = total * (blockIdx.x + 1) / gridDim.x;
+    t = blockIdx.x;
+    stride = gridDim.x;
+  }
+  __device__ bool next(Seg& s) {
+    if (!streamk) {
+      if (t >= num_tiles) return false;
+      s.tile = t;
+      s.kb0 = 0;
+      s.kb1 = num_kb;
+      t += stride;
+      return true;
+    }
+    if (pos >= end) return false;
+    s.tile = (int)(pos / num_kb);
+    s.kb0 = (int)(pos - (long long)s.tile * num_kb);
+    const long long left = end - pos;
+    s.kb1 = (int)(left < (long long)(num_kb - s.kb0) ? s.kb0 + left : num_kb);
+    pos += s.kb1 - s.kb0;
+    return true;
+  }
 };
 
 struct __align__(1024) Smem {
@@ -51,6 +97,7 @@ struct __align__(1024) Smem {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
+  uint32_t part_done;     // epilogue warps that have stored their share of this CTA's partial
 };
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -87,6 +134,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(&sm.acc_empty[b], kEpiWarps);
     }
     sm.abort_flag = 0;
+    sm.part_done = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -104,11 +152,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_w);
       uint32_t it = 0, issued = 0;
-      for (int t = blockIdx.x; t < num_tiles && !sm.abort_flag; t += gridDim.x) {
-        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      WorkIter work(p, num_kb);
+      Seg sg;
+      while (!sm.abort_flag && work.next(sg)) {
+        const int tm = sg.tile % p.tiles_m, tn = sg.tile / p.tiles_m;
         int r0, r1;
         weight_rows(p, tn, r0, r1);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const int s = it % kStages;
           if (!mbar_wait(&sm.empty[s], ((it / kStages) & 1) ^ 1, &sm.abort_flag, p.status, 21)) break;
           mbar_arrive_expect_tx(&sm.full[s], kABytes + kBBytes);
@@ -133,21 +183,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       constexpr uint32_t idesc = umma_idesc(1, 1, BM, BN);
       uint32_t it = 0;
       int local = 0;
-      for (int t = blockIdx.x; t < num_tiles && !sm.abort_flag; t += gridDim.x, ++local) {
+      WorkIter work(p, num_kb);
+      Seg sg;
+      for (; !sm.abort_flag && work.next(sg); ++local) {
         const int buf = local & 1;
         const uint32_t use = (uint32_t)local >> 1;
         // the epilogue must have drained this accumulator (passes at once for its first use)
         if (!mbar_wait(&sm.acc_empty[buf], (use & 1) ^ 1, &sm.abort_flag, p.status, 22)) break;
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + (uint32_t)buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const int s = it % kStages;
           if (!mbar_wait(&sm.full[s], (it / kStages) & 1, &sm.abort_flag, p.status, 23)) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            umma_f16(tmem_acc, smem_desc_k_sw128(a_addr + k * 32), smem_desc_k_sw128(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16(tmem_acc, smem_desc_k_sw128(a_addr + k * 32), smem_desc_k_sw128(b_addr + k * 32), idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
           umma_commit(&sm.empty[s]);
         }
         umma_commit(&sm.acc_full[buf]);
@@ -158,15 +210,80 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int ch = (warp - 2) >> 2;         // which half of the tile's columns
     int local = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+    WorkIter work(p, num_kb);
+    Seg sg;
+    for (; work.next(sg); ++local) {
       const int buf = local & 1;
       const uint32_t use = (uint32_t)local >> 1;
-      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      const int tm = sg.tile % p.tiles_m, tn = sg.tile / p.tiles_m;
       if (!mbar_wait(&sm.acc_full[buf], use & 1, &sm.abort_flag, p.status, 24)) break;
       tc_fence_after();
       const int m = tm * BM + q * 32 + lane;
       const bool row_ok = m < p.M;
       const uint32_t lane_addr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(q * 32) << 16);
+      const int row_in_tile = q * 32 + lane;
+      if (sg.kb0 > 0) {
+        // Not the owner of this tile: park the fp32 partial in this CTA's workspace slot and publish it.
+        float* dst = p.ws + ((size_t)blockIdx.x * BM + row_in_tile) * BN + ch * 128;
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t r[32];
+          tmem_ld_32x32(lane_addr + ch * 128 + cc * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 8; ++v) *reinterpret_cast<uint4*>(dst + cc * 32 + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+        }
+        __threadfence();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&sm.acc_empty[buf]);
+          if (atomicAdd(&sm.part_done, 1u) == (uint32_t)kEpiWarps - 1u) {
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.flags + blockIdx.x), "r"(p.seq) : "memory");
+          }
+        }
+        continue;
+      }
+      // Owner of a tile that other CTAs finish: their partials were computed first thing in their run.
+      int n_parts = 0;
+      if (sg.kb1 < num_kb) {
+        const long long total = (long long)num_tiles * num_kb, tile_end = (long long)(sg.tile + 1) * num_kb;
+        for (int j = blockIdx.x + 1; j < (int)gridDim.x && total * j / gridDim.x < tile_end; ++j) ++n_parts;
+        bool ok = true;
+        if (lane == 0) {
+          const uint64_t t0 = global_timer_ns(), budget = (uint64_t)p.timeout_us * 1000ull;
+          for (int j = 1; j <= n_parts && ok; ++j) {
+            uint32_t v;
+            do {
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.flags + blockIdx.x + j) : "memory");
+              if (v != p.seq && global_timer_ns() - t0 > budget) {
+                ok = false;
+                sm.abort_flag = 1u;
+                if (p.status) atomicCAS(p.status, 0u, 25u);
+                break;
+              }
+            } while (v != p.seq);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) n_parts = 0;
+      }
+      const float* part0 = p.ws + ((size_t)(blockIdx.x + 1) * BM + row_in_tile) * BN;
+      // adds the parked partials of the following CTAs to one 32-column chunk
+      auto add_parts = [&](int c0, uint32_t (&r)[32]) {
+        for (int j = 0; j < n_parts; ++j) {
+          const float* src = part0 + (size_t)j * BM * BN + c0;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const float4 x = __ldcg(reinterpret_cast<const float4*>(src + v * 4));
+            r[v * 4] = __float_as_uint(__uint_as_float(r[v * 4]) + x.x);
+            r[v * 4 + 1] = __float_as_uint(__uint_as_float(r[v * 4 + 1]) + x.y);
+            r[v * 4 + 2] = __float_as_uint(__uint_as_float(r[v * 4 + 2]) + x.z);
+            r[v * 4 + 3] = __float_as_uint(__uint_as_float(r[v * 4 + 3]) + x.w);
+          }
+        }
+      };
       if (p.epi == EPI_SWIGLU) {
         const int half_n = p.N >> 1;
 #pragma unroll 1
@@ -176,6 +293,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           tmem_ld_32x32(lane_addr + c0, g);
           tmem_ld_32x32(lane_addr + 128 + c0, u);
           tmem_ld_wait();
+          if (n_parts) {
+            add_parts(c0, g);
+            add_parts(128 + c0, u);
+          }
           if (!row_ok) continue;
           const int j0 = tn * 128 + c0;
           bf16* dst = p.C + (size_t)m * p.ldc + j0;
@@ -202,6 +323,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint32_t r[32];
           tmem_ld_32x32(lane_addr + c0, r);
           tmem_ld_wait();
+          if (n_parts) add_parts(c0, r);
           if (!row_ok) continue;
           const int n = tn * BN + c0;
           if (n >= p.N) continue;
@@ -285,6 +407,36 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Per-device stream-K scratch: one fp32 tile and one flag per CTA. Allocated on first use.
+struct StreamKBuffers {
+  float* ws = nullptr;
+  uint32_t* flags = nullptr;
+  uint32_t seq = 0;
+  int ctas = 0;
+};
+
+StreamKBuffers* streamk_buffers(int ctas) {
+  static StreamKBuffers per_device[64];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  StreamKBuffers& b = per_device[dev];
+  if (b.ws == nullptr || b.ctas < ctas) {
+    if (b.ws) cudaFree(b.ws);
+    if (b.flags) cudaFree(b.flags);
+    b = StreamKBuffers();
+    if (cudaMalloc(&b.ws, (size_t)ctas * BM * BN * sizeof(float)) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&b.flags, (size_t)ctas * sizeof(uint32_t)) != cudaSuccess || cudaMemset(b.flags, 0, (size_t)ctas * sizeof(uint32_t)) != cudaSuccess) {
+      cudaFree(b.ws);
+      b = StreamKBuffers();
+      return nullptr;
+    }
+    b.ctas = ctas;
+  }
+  return &b;
+}
+
 bool encode_bf16_2d(EncodeTiledFn encode, CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                     uint32_t box_inner, uint32_t box_outer) {
   const cuuint64_t gdim[2] = {inner, outer};
@@ -337,7 +489,23 @@ PK_API int pk_gemm_bf16(const void* A, int lda, const void* W, int M, int N, int
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int sms = sm_count > 0 ? sm_count : 148;
-  const int grid = tiles < sms ? tiles : sms;
+  int grid = tiles < sms ? tiles : sms;
+  // Stream-K when whole tiles would leave many SMs idle in the last round (or the whole time).
+  const int num_kb = K / BK;
+  const double rounds = (double)tiles / sms;
+  const double eff = rounds / (double)((tiles + sms - 1) / sms);
+  p.streamk = 0;
+  if (eff < 0.88 && num_kb >= 8 && (long long)tiles * num_kb >= (long long)sms * 8 && getenv("POCKET_GEMM_NO_STREAMK") == nullptr) {
+    StreamKBuffers* b = streamk_buffers(sms);
+    if (b != nullptr) {
+      p.streamk = 1;
+      p.ws = b->ws;
+      p.flags = b->flags;
+      p.seq = ++b->seq;
+      p.timeout_us = 2000000;
+      grid = sms;
+    }
+  }
   gemm_bf16_kernel<<<grid, kThreads, smem, stream>>>(tmap_a, tmap_w, p);
   PK_CHECK_LAUNCH();
   return PK_OK;

@@ -46,6 +46,8 @@ struct MatvecParams {
   const float* gamma;    // [K] or null
   int norm_mode;         // 1: *(1+gamma), 2: *gamma
   int flat_path;         // 1: blocks own whole row pairs and their warps split the block's k-iterations evenly
+  const uint8_t* pf_ptr[2];   // weights of the NEXT kernel to pull into L2 as this one drains (may be null)
+  unsigned int pf_bytes[2];
   unsigned long long* dbg;  // optional phase timestamps (see pk_matvec_set_debug); null in normal use
   float eps;
   PkWait wait;
@@ -223,6 +225,21 @@ __device__ __forceinline__ float pow2_at_least(float a) {
   int e;
   const float m = frexpf(a, &e);  // a = m * 2^e, m in [0.5, 1)
   return ldexpf(1.f, m == 0.5f ? e - 1 : e);
+}
+
+// A warp that has finished its rows pulls a slice of the next kernel's weights into L2: HBM keeps streaming through
+// this kernel's tail, the launch gap and the next kernel's activation staging.
+__device__ __forceinline__ void prefetch_next_weights(const MatvecParams& p, int gwarp, int warps_total, int lane) {
+  constexpr unsigned kChunk = 16384;
+  if (lane != 0) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (p.pf_ptr[r] == nullptr) continue;
+    for (unsigned off = (unsigned)gwarp * kChunk; off < p.pf_bytes[r]; off += (unsigned)warps_total * kChunk) {
+      const unsigned n = min(kChunk, p.pf_bytes[r] - off) & ~15u;
+      if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr[r] + off), "r"(n) : "memory");
+    }
+  }
 }
 
 template <int M>
@@ -446,6 +463,7 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
       }
       pos += it_stop - it;
     }
+    prefetch_next_weights(p, gwarp, warps_total, lane);
     if (p.dbg != nullptr && lane == 0) {
       atomicMin(p.dbg + 3, global_timer_ns());
       atomicMax(p.dbg + 4, global_timer_ns());
@@ -651,7 +669,19 @@ int launch_m(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
 }
 
 unsigned long long* g_matvec_dbg = nullptr;
+thread_local const void* g_pf_ptr[2] = {nullptr, nullptr};
+thread_local size_t g_pf_bytes[2] = {0, 0};
 }  // namespace
+
+// Hint for the NEXT pk_matvec call of this thread only: up to two ranges of weights that the kernel launched after it
+// will read first. The matvec kernel asks L2 to fetch them while it drains. Ranges must be 16-byte aligned device
+// memory; bytes are clamped to 64 MiB each.
+PK_API void pk_matvec_prefetch_next(const void* p0, size_t bytes0, const void* p1, size_t bytes1) {
+  g_pf_ptr[0] = p0;
+  g_pf_bytes[0] = bytes0;
+  g_pf_ptr[1] = p1;
+  g_pf_bytes[1] = bytes1;
+}
 
 // Phase timestamps for tuning: `buf` (device, 5 x u64, caller presets [0],[1],[3] to ~0 and [2],[4] to 0)
 // receives %globaltimer values: earliest block entry, earliest / latest end of the activation staging,
@@ -684,6 +714,13 @@ PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, i
   p.gamma = gamma;
   p.norm_mode = norm_mode;
   p.dbg = g_matvec_dbg;
+  for (int r = 0; r < 2; ++r) {
+    const bool ok = g_pf_ptr[r] != nullptr && ((uintptr_t)g_pf_ptr[r] & 15) == 0;
+    p.pf_ptr[r] = ok ? (const uint8_t*)g_pf_ptr[r] : nullptr;
+    p.pf_bytes[r] = ok ? (unsigned)(g_pf_bytes[r] < ((size_t)64 << 20) ? g_pf_bytes[r] : ((size_t)64 << 20)) : 0u;
+    g_pf_ptr[r] = nullptr;
+    g_pf_bytes[r] = 0;
+  }
   p.eps = eps;
   if (wait) p.wait = *wait;
   p.epi = epi;

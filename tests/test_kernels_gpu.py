@@ -133,6 +133,35 @@ def test_gemm_bf16_persistent_tiles(M, N, K):
         assert got.shape == (M, N // 2) and _rel_err(got, want) < 1.5e-2
 
 
+@pytest.mark.parametrize("M,N,K,epi", [(512, 5120, 1024, 0), (512, 5120, 1024, 2), (384, 5120, 2048, 1), (512, 1536, 4096, 3), (200, 2304, 3072, 0)])
+def test_gemm_bf16_stream_k(M, N, K, epi):
+    """Tile counts that would idle most SMs: the k-steps are cut into equal ranges per CTA and partial tiles are
+    combined by the owner; the result must agree with the whole-tile schedule and with fp32 torch."""
+    import os
+    from pocketllm_b200 import ops
+    torch.manual_seed(M + N + K + epi)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    resid = torch.randn(M, N, device="cuda").to(torch.bfloat16) if epi == ops.EPI_RESID else None
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    got = [ops.gemm_bf16(a, w, epi=epi, resid=resid, status=status) for _ in range(3)]
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    os.environ["POCKET_GEMM_NO_STREAMK"] = "1"
+    try:
+        plain = ops.gemm_bf16(a, w, epi=epi, resid=resid)
+    finally:
+        del os.environ["POCKET_GEMM_NO_STREAMK"]
+    ref = a.float() @ w.float().t()
+    if epi == ops.EPI_RESID:
+        ref = ref + resid.float()
+    if epi == ops.EPI_SWIGLU:
+        ref = torch.nn.functional.silu(ref[:, : N // 2]) * ref[:, N // 2:]
+    assert _rel_err(got[0], ref) < (1.5e-2 if epi == 1 else 6e-3)
+    assert _rel_err(got[0], plain) < 4e-3                      # fp32 sums in a different order, then one bf16 rounding
+    assert torch.equal(got[0], got[1]) and torch.equal(got[1], got[2])
+
+
 def test_gemm_bf16_many_tiles_per_cta():
     """More tiles than SMs: every CTA walks several tiles and both accumulators are reused."""
     from pocketllm_b200 import ops
