@@ -69,5 +69,4 @@ int pk_cand_merge_wait(const float* cand_val, const int* cand_idx, int M, int wo
 int pk_fp8_to_bf16(const void* w, const float* scale, int N, int K, void* out, cudaStream_t stream);
 int pk_gemm_bf16(const void* A, int lda, const void* W, int M, int N, int K, int epi, void* C, const void* resid, int ldc,
                  uint32_t* status, const PkPush* push, int sm_count, cudaStream_t stream);
-void pk_matvec_prefetch_next(const void* p0, size_t bytes0, const void* p1, size_t bytes1);
 }

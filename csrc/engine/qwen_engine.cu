@@ -579,44 +579,12 @@ void QwenEngine::run_small(int M, bool all_logits) {
   check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hidden_buf_[cur_], nullptr, stream_), "embedding");
   int pending = -1;  // site whose partial sums still wait to be added to the residual stream
 
-  // Weight-streaming kernels in execution order, so that each one can pull the head of the next one's weights into
-  // L2 while it drains (only worth it when one row is decoded: the kernels are then bound by per-kernel latency).
-  std::vector<const Fp8Linear*> order;
-  const bool prefetch_next = M == 1 && getenv("POCKET_NO_L2_PREFETCH") == nullptr;
-  if (prefetch_next) {
-    for (auto& L : layers_) {
-      order.push_back(L.full ? &L.qkv : &L.in_proj);
-      order.push_back(L.full ? &L.o_proj : &L.out_proj);
-      order.push_back(&L.gate_up);
-      order.push_back(&L.down);
-    }
-  }
-  size_t order_pos = 0;
-  auto hint_next = [&]() {
-    if (!prefetch_next) return;
-    ++order_pos;
-    constexpr size_t kBudget = (size_t)48 << 20;
-    if (order_pos < order.size()) {
-      const Fp8Linear* n = order[order_pos];
-      const size_t bytes = (size_t)n->N * n->K;
-      if (n == &layers_[order_pos / 4].gate_up) {        // SwiGLU pairs row j with row j + N/2: warm both halves
-        const size_t half = bytes / 2, each = std::min(half, kBudget / 2);
-        pk_matvec_prefetch_next(n->w, each, n->w + half, each);
-      } else {
-        pk_matvec_prefetch_next(n->w, std::min(bytes, kBudget), nullptr, 0);
-      }
-    } else {
-      pk_matvec_prefetch_next(lm_head_, std::min((size_t)vocab_l_ * hidden_ * 2, kBudget), nullptr, 0);
-    }
-  };
-
   auto consume = [&](const Fp8Linear* w, const void* wb, int nb, const float* gamma, int epi, void* y, int ldy,
                      const PkPush* push) {
     // x = hidden (+ pending partials) -> norm -> linear. The summed hidden goes to the other buffer.
     const float* parts = pending >= 0 ? slot_parts(pending) : nullptr;
     PkWait wt = make_wait(pending >= 0 ? pending : 0);
     void* hout = pending >= 0 ? hidden_buf_[cur_ ^ 1] : nullptr;
-    if (w != nullptr) hint_next();
     check(pk_matvec(w ? w->w : nullptr, w ? w->scale : nullptr, wb, w ? w->N : 0, nb, hidden_, M, hidden_buf_[cur_], parts,
                     W, hout, gamma, 1, eps, pending >= 0 ? &wt : nullptr, epi, y, ldy, push, sm_count_, stream_),
           "matvec(consume)");
@@ -625,7 +593,6 @@ void QwenEngine::run_small(int M, bool all_logits) {
   };
   auto produce = [&](const Fp8Linear& w, const void* x, int site) {
     PkPush ps = make_push(site);
-    hint_next();
     check(pk_matvec(w.w, w.scale, nullptr, w.N, 0, w.K, M, x, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 3,
                     nullptr, hidden_, &ps, sm_count_, stream_),
           "matvec(produce)");

@@ -274,6 +274,7 @@ struct KvPrepParams {
   int hd, rd, ring;
   float eps;
   bf16* dst;            // [ring + ..., hd]
+  const int* dst_rows;  // optional: row of dst for each input row (null: pos % ring)
 };
 
 __global__ void __launch_bounds__(128) kv_prep_kernel(const KvPrepParams p) {
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(128) kv_prep_kernel(const KvPrepParams p) {
     bscale[tid] = pow2_ceil_scale(fmaxf(amax, 1e-4f) / 448.f);
   }
   __syncthreads();
-  bf16* dst = p.dst + (size_t)(pos % p.ring) * p.hd;
+  bf16* dst = p.dst + (size_t)(p.dst_rows ? p.dst_rows[m] : pos % p.ring) * p.hd;
   for (int d = tid; d < p.hd; d += 128) dst[d] = __float2bfloat16(d < off ? fp8_round_trip(v[d], bscale[d >> 6]) : v[d]);
 }
 
@@ -472,6 +473,7 @@ struct SparseAttnParams {
   const bf16* q;        // [M, H, hd]
   const bf16* kv;       // [ring + entries, hd]
   const int* pos;
+  const int* rope_pos;  // [M] position used for the inverse RoPE of the output (null: pos)
   const int* sel;       // [M, ksel] (mode 2)
   const float* sink;    // [H]
   const float* cos_t;
@@ -538,7 +540,8 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(const SparseAttnParams
       const int d = lane * DPL + i;
       if (d >= off) {
         const int pi = (d - off) >> 1;
-        const float c = p.cos_t[(size_t)pos * half + pi], s = -p.sin_t[(size_t)pos * half + pi];
+        const int rp = p.rope_pos ? p.rope_pos[m] : pos;
+        const float c = p.cos_t[(size_t)rp * half + pi], s = -p.sin_t[(size_t)rp * half + pi];
         const float a = acc[i], b = acc[i + 1];
         acc[i] = a * c - b * s;
         acc[i + 1] = a * s + b * c;
@@ -618,10 +621,19 @@ PK_API int pk_dsv4_head_prep(void* x, const int* pos, const float* cos_t, const 
   return PK_OK;
 }
 
+PK_API int pk_dsv4_kv_prep_rows(const float* kv, const float* gamma, const int* pos, const int* dst_rows, const float* cos_t,
+                                const float* sin_t, int M, int hd, int rd, int ring, float eps, void* dst, cudaStream_t stream);
+
 PK_API int pk_dsv4_kv_prep(const float* kv, const float* gamma, const int* pos, const float* cos_t, const float* sin_t, int M,
                            int hd, int rd, int ring, float eps, void* dst, cudaStream_t stream) {
+  return pk_dsv4_kv_prep_rows(kv, gamma, pos, nullptr, cos_t, sin_t, M, hd, rd, ring, eps, dst, stream);
+}
+
+// dst_rows (may be null) names the destination row of every input row instead of pos % ring.
+PK_API int pk_dsv4_kv_prep_rows(const float* kv, const float* gamma, const int* pos, const int* dst_rows, const float* cos_t,
+                                const float* sin_t, int M, int hd, int rd, int ring, float eps, void* dst, cudaStream_t stream) {
   if (M < 1 || hd < rd || ((hd - rd) & 63) != 0 || (hd - rd) / 64 > 16 || ring < 1) return PK_ERR_BAD_ARG;
-  KvPrepParams p{kv, gamma, pos, cos_t, sin_t, hd, rd, ring, eps, (pk::bf16*)dst};
+  KvPrepParams p{kv, gamma, pos, cos_t, sin_t, hd, rd, ring, eps, (pk::bf16*)dst, dst_rows};
   kv_prep_kernel<<<M, 128, (size_t)hd * 4, stream>>>(p);
   PK_CHECK_LAUNCH();
   return PK_OK;
@@ -666,11 +678,23 @@ PK_API int pk_dsv4_index_score(const void* q, const void* k, const float* w, con
   return PK_OK;
 }
 
+// rope_pos (may be null) gives the positions for the inverse RoPE when they differ from the positions that define the
+// window (draft blocks: every draft query sees the committed window but sits at its own position).
+PK_API int pk_dsv4_sparse_attn_ex(const void* q, const void* kv, const int* pos, const int* rope_pos, const int* sel, const float* sink,
+                                  const float* cos_t, const float* sin_t, int M, int H, int hd, int win, int ring, int ratio,
+                                  int mode, int ksel, int rd, float scale, void* out, cudaStream_t stream);
+
 PK_API int pk_dsv4_sparse_attn(const void* q, const void* kv, const int* pos, const int* sel, const float* sink,
                                const float* cos_t, const float* sin_t, int M, int H, int hd, int win, int ring, int ratio,
                                int mode, int ksel, int rd, float scale, void* out, cudaStream_t stream) {
+  return pk_dsv4_sparse_attn_ex(q, kv, pos, nullptr, sel, sink, cos_t, sin_t, M, H, hd, win, ring, ratio, mode, ksel, rd, scale, out, stream);
+}
+
+PK_API int pk_dsv4_sparse_attn_ex(const void* q, const void* kv, const int* pos, const int* rope_pos, const int* sel, const float* sink,
+                                  const float* cos_t, const float* sin_t, int M, int H, int hd, int win, int ring, int ratio,
+                                  int mode, int ksel, int rd, float scale, void* out, cudaStream_t stream) {
   if (M < 1 || H < 1 || win < 1 || ring < win || (mode == 2 && sel == nullptr) || (mode == 1 && ratio < 1)) return PK_ERR_BAD_ARG;
-  SparseAttnParams p{(const pk::bf16*)q, (const pk::bf16*)kv, pos, sel, sink, cos_t, sin_t, H, win, ring, ratio, mode, ksel, rd,
+  SparseAttnParams p{(const pk::bf16*)q, (const pk::bf16*)kv, pos, rope_pos, sel, sink, cos_t, sin_t, H, win, ring, ratio, mode, ksel, rd,
                      scale, (pk::bf16*)out};
   const int wpb = H >= 8 ? 8 : H;
   const dim3 grid(M, (H + wpb - 1) / wpb);

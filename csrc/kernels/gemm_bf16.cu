@@ -58,14 +58,20 @@ struct Seg {
   int tile, kb0, kb1;
 };
 
+// Stream-K keeps the CTAs that share weight columns in lockstep: CTA c belongs to group c / tiles_m and always works
+// on m-tile c % tiles_m; the k-steps of all column blocks, laid end to end, are cut into one contiguous range per
+// GROUP, so the tiles_m CTAs of a group read the same weight tiles at the same time (one HBM read, L2 hits for the
+// others) exactly as in the whole-tile schedule.
 struct WorkIter {
-  int num_kb, num_tiles, streamk;
-  long long pos, end;     // stream-K: flattened k-steps
+  int num_kb, num_tiles, streamk, tiles_m, tm;
+  long long pos, end;     // stream-K: flattened (column block, k-step) of this CTA's group
   int t, stride;          // tile mode
-  __device__ WorkIter(const Params& p, int nkb) : num_kb(nkb), num_tiles(p.tiles_m * p.tiles_n), streamk(p.streamk) {
-    const long long total = (long long)num_tiles * num_kb;
-    pos = total * blockIdx.x / gridDim.x;
-    end = total * (blockIdx.x + 1) / gridDim.x;
+  __device__ WorkIter(const Params& p, int nkb) : num_kb(nkb), num_tiles(p.tiles_m * p.tiles_n), streamk(p.streamk), tiles_m(p.tiles_m) {
+    const int groups = gridDim.x / p.tiles_m, g = blockIdx.x / p.tiles_m;
+    tm = blockIdx.x % p.tiles_m;
+    const long long total = (long long)p.tiles_n * num_kb;
+    pos = streamk ? total * g / groups : 0;
+    end = streamk ? total * (g + 1) / groups : 0;
     t = blockIdx.x;
     stride = gridDim.x;
   }
@@ -79,8 +85,9 @@ struct WorkIter {
       return true;
     }
     if (pos >= end) return false;
-    s.tile = (int)(pos / num_kb);
-    s.kb0 = (int)(pos - (long long)s.tile * num_kb);
+    const int tn = (int)(pos / num_kb);
+    s.tile = tn * tiles_m + tm;
+    s.kb0 = (int)(pos - (long long)tn * num_kb);
     const long long left = end - pos;
     s.kb1 = (int)(left < (long long)(num_kb - s.kb0) ? s.kb0 + left : num_kb);
     pos += s.kb1 - s.kb0;
@@ -248,15 +255,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // Owner of a tile that other CTAs finish: their partials were computed first thing in their run.
       int n_parts = 0;
       if (sg.kb1 < num_kb) {
-        const long long total = (long long)num_tiles * num_kb, tile_end = (long long)(sg.tile + 1) * num_kb;
-        for (int j = blockIdx.x + 1; j < (int)gridDim.x && total * j / gridDim.x < tile_end; ++j) ++n_parts;
+        const int groups = gridDim.x / p.tiles_m, g = blockIdx.x / p.tiles_m;
+        const long long total = (long long)p.tiles_n * num_kb, block_end = (long long)(sg.tile / p.tiles_m + 1) * num_kb;
+        for (int j = g + 1; j < groups && total * j / groups < block_end; ++j) ++n_parts;
         bool ok = true;
         if (lane == 0) {
           const uint64_t t0 = global_timer_ns(), budget = (uint64_t)p.timeout_us * 1000ull;
           for (int j = 1; j <= n_parts && ok; ++j) {
             uint32_t v;
             do {
-              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.flags + blockIdx.x + j) : "memory");
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.flags + blockIdx.x + j * p.tiles_m) : "memory");
               if (v != p.seq && global_timer_ns() - t0 > budget) {
                 ok = false;
                 sm.abort_flag = 1u;
@@ -269,11 +277,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         if (!ok) n_parts = 0;
       }
-      const float* part0 = p.ws + ((size_t)(blockIdx.x + 1) * BM + row_in_tile) * BN;
+      const float* part0 = p.ws + ((size_t)(blockIdx.x + p.tiles_m) * BM + row_in_tile) * BN;
       // adds the parked partials of the following CTAs to one 32-column chunk
       auto add_parts = [&](int c0, uint32_t (&r)[32]) {
         for (int j = 0; j < n_parts; ++j) {
-          const float* src = part0 + (size_t)j * BM * BN + c0;
+          const float* src = part0 + (size_t)j * p.tiles_m * BM * BN + c0;
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
             const float4 x = __ldcg(reinterpret_cast<const float4*>(src + v * 4));
@@ -415,6 +423,13 @@ struct StreamKBuffers {
   int ctas = 0;
 };
 
+// Stream-K is opt-in (POCKET_GEMM_STREAMK=1); POCKET_GEMM_NO_STREAMK forces whole tiles either way.
+static bool streamk_enabled() {
+  const char* on = getenv("POCKET_GEMM_STREAMK");
+  return on != nullptr && on[0] == '1' && getenv("POCKET_GEMM_NO_STREAMK") == nullptr;
+}
+
+
 StreamKBuffers* streamk_buffers(int ctas) {
   static StreamKBuffers per_device[64];
   static std::mutex mu;
@@ -495,7 +510,8 @@ PK_API int pk_gemm_bf16(const void* A, int lda, const void* W, int M, int N, int
   const double rounds = (double)tiles / sms;
   const double eff = rounds / (double)((tiles + sms - 1) / sms);
   p.streamk = 0;
-  if (eff < 0.88 && num_kb >= 8 && (long long)tiles * num_kb >= (long long)sms * 8 && getenv("POCKET_GEMM_NO_STREAMK") == nullptr) {
+  const int groups = p.tiles_m <= sms ? sms / p.tiles_m : 0;
+  if (eff < 0.88 && groups >= 2 && (long long)p.tiles_n * num_kb >= (long long)groups * 8 && streamk_enabled()) {
     StreamKBuffers* b = streamk_buffers(sms);
     if (b != nullptr) {
       p.streamk = 1;
@@ -503,7 +519,7 @@ PK_API int pk_gemm_bf16(const void* A, int lda, const void* W, int M, int N, int
       p.flags = b->flags;
       p.seq = ++b->seq;
       p.timeout_us = 2000000;
-      grid = sms;
+      grid = groups * p.tiles_m;
     }
   }
   gemm_bf16_kernel<<<grid, kThreads, smem, stream>>>(tmap_a, tmap_w, p);

@@ -21,6 +21,8 @@
 // Behavioural counterpart in the reference: cpp_engine/cuda/qwen_half_ops.cu:89-374
 // (fp8_matvec_f16*, fp8_matmul_f16_small_batch, fp8_swiglu_*), which are separate SIMT
 // kernels with an LUT decode and NCCL all-reduces between them.
+#include <cstdlib>
+
 #include "../common/pk_comm.cuh"
 #include "../common/pk_common.cuh"
 
@@ -46,8 +48,7 @@ struct MatvecParams {
   const float* gamma;    // [K] or null
   int norm_mode;         // 1: *(1+gamma), 2: *gamma
   int flat_path;         // 1: blocks own whole row pairs and their warps split the block's k-iterations evenly
-  const uint8_t* pf_ptr[2];   // weights of the NEXT kernel to pull into L2 as this one drains (may be null)
-  unsigned int pf_bytes[2];
+  int self_prefetch;     // flat path: L2-prefetch the rest of each warp's first stretch before the staging
   unsigned long long* dbg;  // optional phase timestamps (see pk_matvec_set_debug); null in normal use
   float eps;
   PkWait wait;
@@ -227,21 +228,6 @@ __device__ __forceinline__ float pow2_at_least(float a) {
   return ldexpf(1.f, m == 0.5f ? e - 1 : e);
 }
 
-// A warp that has finished its rows pulls a slice of the next kernel's weights into L2: HBM keeps streaming through
-// this kernel's tail, the launch gap and the next kernel's activation staging.
-__device__ __forceinline__ void prefetch_next_weights(const MatvecParams& p, int gwarp, int warps_total, int lane) {
-  constexpr unsigned kChunk = 16384;
-  if (lane != 0) return;
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    if (p.pf_ptr[r] == nullptr) continue;
-    for (unsigned off = (unsigned)gwarp * kChunk; off < p.pf_bytes[r]; off += (unsigned)warps_total * kChunk) {
-      const unsigned n = min(kChunk, p.pf_bytes[r] - off) & ~15u;
-      if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr[r] + off), "r"(n) : "memory");
-    }
-  }
-}
-
 template <int M>
 __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -287,6 +273,18 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
         load_fp8_batch(bt, p.W + (size_t)r0 * K, p.W + (size_t)r1c * K, p.scale + (size_t)(r0 >> 7) * kb_count,
                        p.scale + (size_t)(r1c >> 7) * kb_count, it, min(K, it_stop << 9), lane);
         have_pre = true;
+        // Ask L2 for the rest of this warp's first stretch (up to 16 KB per row) so that HBM keeps streaming while
+        // the block stages the activations.
+        if (p.self_prefetch && lane == 0) {
+          const unsigned k_from = (unsigned)min(K, (it + 4) << 9), k_to = (unsigned)min(K, it_stop << 9);
+          if (k_to > k_from) {
+            const unsigned n = min(k_to - k_from, 16384u) & ~15u;
+            if (n) {
+              asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.W + (size_t)r0 * K + k_from), "r"(n) : "memory");
+              asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.W + (size_t)r1c * K + k_from), "r"(n) : "memory");
+            }
+          }
+        }
       }
     }
   } else {
@@ -463,7 +461,6 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_kernel(const MatvecParams 
       }
       pos += it_stop - it;
     }
-    prefetch_next_weights(p, gwarp, warps_total, lane);
     if (p.dbg != nullptr && lane == 0) {
       atomicMin(p.dbg + 3, global_timer_ns());
       atomicMax(p.dbg + 4, global_timer_ns());
@@ -669,24 +666,14 @@ int launch_m(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
 }
 
 unsigned long long* g_matvec_dbg = nullptr;
-thread_local const void* g_pf_ptr[2] = {nullptr, nullptr};
-thread_local size_t g_pf_bytes[2] = {0, 0};
 }  // namespace
 
-// Hint for the NEXT pk_matvec call of this thread only: up to two ranges of weights that the kernel launched after it
-// will read first. The matvec kernel asks L2 to fetch them while it drains. Ranges must be 16-byte aligned device
-// memory; bytes are clamped to 64 MiB each.
-PK_API void pk_matvec_prefetch_next(const void* p0, size_t bytes0, const void* p1, size_t bytes1) {
-  g_pf_ptr[0] = p0;
-  g_pf_bytes[0] = bytes0;
-  g_pf_ptr[1] = p1;
-  g_pf_bytes[1] = bytes1;
+// Bulk L2 prefetch of a warp's first stretch of weights at kernel start is opt-in (POCKET_L2_PREFETCH=1).
+static bool l2_prefetch_enabled() {
+  const char* on = getenv("POCKET_L2_PREFETCH");
+  return on != nullptr && on[0] == '1';
 }
 
-// Phase timestamps for tuning: `buf` (device, 5 x u64, caller presets [0],[1],[3] to ~0 and [2],[4] to 0)
-// receives %globaltimer values: earliest block entry, earliest / latest end of the activation staging,
-// earliest / latest warp finish. Pass null to switch the stamps off (the default).
-PK_API void pk_matvec_set_debug(void* buf) { g_matvec_dbg = (unsigned long long*)buf; }
 
 PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, int Nb, int K, int M,
                      const void* x_in, const float* parts, int nparts, void* hidden_out,
@@ -714,13 +701,7 @@ PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, i
   p.gamma = gamma;
   p.norm_mode = norm_mode;
   p.dbg = g_matvec_dbg;
-  for (int r = 0; r < 2; ++r) {
-    const bool ok = g_pf_ptr[r] != nullptr && ((uintptr_t)g_pf_ptr[r] & 15) == 0;
-    p.pf_ptr[r] = ok ? (const uint8_t*)g_pf_ptr[r] : nullptr;
-    p.pf_bytes[r] = ok ? (unsigned)(g_pf_bytes[r] < ((size_t)64 << 20) ? g_pf_bytes[r] : ((size_t)64 << 20)) : 0u;
-    g_pf_ptr[r] = nullptr;
-    g_pf_bytes[r] = 0;
-  }
+  p.self_prefetch = l2_prefetch_enabled() && (K & 15) == 0 && (((uintptr_t)W) & 15) == 0;
   p.eps = eps;
   if (wait) p.wait = *wait;
   p.epi = epi;

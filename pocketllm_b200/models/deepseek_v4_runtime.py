@@ -169,6 +169,9 @@ class DSV4Runtime:
         self.max_rows = max_rows
         # when a dict: records every discrete choice (expert ids, selected entries) per block, call by call
         self.capture: dict | None = None
+        # layers whose output (mean over the copies) is kept per row in `last_taps` [rows, len(tap_layers) * dim] (DSpark targets)
+        self.tap_layers: tuple = ()
+        self.last_taps: torch.Tensor | None = None
         W = weights
         f32 = lambda n: W[n].float().cuda().contiguous()
         self.embed = W["embed.weight"].float().cuda()
@@ -298,6 +301,7 @@ class DSV4Runtime:
         out = []
         toks = list(tokens)
         hidden = []
+        taps_all = []
         for i in range(0, len(toks), self.max_rows):
             part = toks[i:i + self.max_rows]
             M, pos0 = len(part), self.pos
@@ -306,12 +310,18 @@ class DSV4Runtime:
             tok_t = torch.tensor(part, device="cuda", dtype=torch.int32)
             pos_t = torch.arange(pos0, pos0 + M, device="cuda", dtype=torch.int32)
             h = self.embed[tok_t.long()].unsqueeze(1).repeat(1, self.cfg.hc_mult, 1).contiguous()
-            for b, st in zip(self.blocks, self.state):
+            taps = []
+            for li, (b, st) in enumerate(zip(self.blocks, self.state)):
                 h = self._block(b, st, h, pos_t, tok_t, pos0)
+                if li in self.tap_layers:
+                    taps.append(h.mean(1))
+            if taps:
+                taps_all.append(torch.cat([taps[self.tap_layers.index(l)] for l in self.tap_layers], -1))
             hidden.append(h)
             out.append(self._logits(h, self.hc_head, self.norm))
             self.pos += M
         self.last_hidden = torch.cat(hidden, 0)
+        self.last_taps = torch.cat(taps_all, 0) if taps_all else None
         return torch.cat(out, 0)
 
     def forward_rows(self, tokens: Sequence[int]) -> list[int]:

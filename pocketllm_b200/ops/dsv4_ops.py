@@ -52,11 +52,12 @@ def head_prep(x: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: to
 
 
 def kv_prep(kv: torch.Tensor, gamma: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, rd: int, ring: int,
-            dst: torch.Tensor, eps: float = 1e-6) -> None:
-    """fp32 [M, hd] projections -> normalised, rotated, FP8-fake-quantised bf16 rows at `dst[pos % ring]`."""
+            dst: torch.Tensor, eps: float = 1e-6, dst_rows: torch.Tensor | None = None) -> None:
+    """fp32 [M, hd] projections -> normalised, rotated (at `pos`), FP8-fake-quantised bf16 rows at `dst[pos % ring]`, or at
+    `dst[dst_rows]` when given."""
     M, hd = kv.shape
-    st = _lib.kernels().pk_dsv4_kv_prep(_ptr(kv), _ptr(gamma), _ptr(pos), _ptr(cos_t), _ptr(sin_t), c_int(M), c_int(hd), c_int(rd),
-                                        c_int(ring), c_float(eps), _ptr(dst), _stream())
+    st = _lib.kernels().pk_dsv4_kv_prep_rows(_ptr(kv), _ptr(gamma), _ptr(pos), _ptr(dst_rows), _ptr(cos_t), _ptr(sin_t), c_int(M), c_int(hd),
+                                             c_int(rd), c_int(ring), c_float(eps), _ptr(dst), _stream())
     _check(st, "pk_dsv4_kv_prep")
 
 
@@ -81,14 +82,15 @@ def index_score(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, pos: torch.Te
 
 
 def sparse_attn(q: torch.Tensor, kv: torch.Tensor, pos: torch.Tensor, sink: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, *,
-                win: int, ring: int, ratio: int, rd: int, sel: torch.Tensor | None = None, all_entries: bool = False) -> torch.Tensor:
+                win: int, ring: int, ratio: int, rd: int, sel: torch.Tensor | None = None, all_entries: bool = False,
+                rope_pos: torch.Tensor | None = None) -> torch.Tensor:
     """Sink-softmax attention of bf16 q [M, H, hd] over window rows and compressed rows of `kv` (K == V);
-    the output has the inverse RoPE applied."""
+    the output has the inverse RoPE applied (at `rope_pos` when given, else at `pos`)."""
     M, H, hd = q.shape
     out = torch.empty_like(q)
     mode = 2 if sel is not None else 1 if all_entries else 0
     ksel = 0 if sel is None else sel.shape[1]
-    st = _lib.kernels().pk_dsv4_sparse_attn(_ptr(q), _ptr(kv), _ptr(pos), _ptr(sel), _ptr(sink), _ptr(cos_t), _ptr(sin_t), c_int(M),
+    st = _lib.kernels().pk_dsv4_sparse_attn_ex(_ptr(q), _ptr(kv), _ptr(pos), _ptr(rope_pos), _ptr(sel), _ptr(sink), _ptr(cos_t), _ptr(sin_t), c_int(M),
                                             c_int(H), c_int(hd), c_int(win), c_int(ring), c_int(max(ratio, 1)), c_int(mode), c_int(ksel),
                                             c_int(rd), c_float(hd ** -0.5), _ptr(out), _stream())
     _check(st, "pk_dsv4_sparse_attn")

@@ -144,14 +144,14 @@ def test_gemm_bf16_stream_k(M, N, K, epi):
     w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
     resid = torch.randn(M, N, device="cuda").to(torch.bfloat16) if epi == ops.EPI_RESID else None
     status = torch.zeros(1, device="cuda", dtype=torch.int32)
-    got = [ops.gemm_bf16(a, w, epi=epi, resid=resid, status=status) for _ in range(3)]
-    torch.cuda.synchronize()
-    assert status.item() == 0
-    os.environ["POCKET_GEMM_NO_STREAMK"] = "1"
+    os.environ["POCKET_GEMM_STREAMK"] = "1"
     try:
-        plain = ops.gemm_bf16(a, w, epi=epi, resid=resid)
+        got = [ops.gemm_bf16(a, w, epi=epi, resid=resid, status=status) for _ in range(3)]
+        torch.cuda.synchronize()
     finally:
-        del os.environ["POCKET_GEMM_NO_STREAMK"]
+        del os.environ["POCKET_GEMM_STREAMK"]
+    assert status.item() == 0
+    plain = ops.gemm_bf16(a, w, epi=epi, resid=resid)
     ref = a.float() @ w.float().t()
     if epi == ops.EPI_RESID:
         ref = ref + resid.float()
