@@ -35,8 +35,17 @@ PK_EAPI const char* pk_engine_last_error() { return g_err.c_str(); }
 
 // config_json: a Hugging Face style config (flat or under text_config), or the literal
 // "benchmark_27b" for the 64-layer benchmark shape.
+PK_EAPI void* pk_qwen_create_ex(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
+                                int prefill_chunk, int use_cuda_graph, int decode_splits, int mtp);
+
 PK_EAPI void* pk_qwen_create(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
                              int prefill_chunk, int use_cuda_graph, int decode_splits) {
+  return pk_qwen_create_ex(config_json, tp_rank, tp_world, device, max_context, prefill_chunk, use_cuda_graph, decode_splits, 0);
+}
+
+// mtp != 0 also builds the multi-token predictor (`mtp.*` tensors) used by pk_qwen_spec_decode.
+PK_EAPI void* pk_qwen_create_ex(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
+                                int prefill_chunk, int use_cuda_graph, int decode_splits, int mtp) {
   pk::QwenEngine* eng = nullptr;
   guarded([&] {
     pk::QwenConfig cfg = std::string(config_json) == "benchmark_27b"
@@ -52,6 +61,7 @@ PK_EAPI void* pk_qwen_create(const char* config_json, int tp_rank, int tp_world,
     if (decode_splits > 0) opt.decode_splits = decode_splits;
     else opt.decode_splits = std::min(64, std::max(8, max_context / 2048));
     opt.use_cuda_graph = use_cuda_graph != 0;
+    opt.mtp = mtp != 0;
     eng = new pk::QwenEngine(cfg, opt);
   });
   return eng;
@@ -84,6 +94,28 @@ PK_EAPI int pk_qwen_decode(void* h, int steps, int* out_tokens, int sync_each_st
 
 PK_EAPI int pk_qwen_forward_rows(void* h, const int* tokens, int M, int* out_tokens) {
   return guarded([&] { ((pk::QwenEngine*)h)->forward_rows(tokens, M, out_tokens); });
+}
+
+// Speculative greedy decode with the multi-token predictor; the tokens equal those of pk_qwen_decode.
+// stats (may be null): [rounds, proposed, accepted, rollbacks, replay_tokens, plain_steps, predictor_rows].
+PK_EAPI int pk_qwen_spec_decode(void* h, int steps, int max_draft, int* out_tokens, long long* stats) {
+  return guarded([&] {
+    pk::QwenSpecStats st;
+    ((pk::QwenEngine*)h)->spec_decode(steps, max_draft, out_tokens, &st);
+    if (stats) {
+      const long long v[7] = {st.rounds, st.proposed, st.accepted, st.rollbacks, st.replay_tokens, st.plain_steps, st.predictor_rows};
+      for (int i = 0; i < 7; ++i) stats[i] = v[i];
+    }
+  });
+}
+PK_EAPI int pk_qwen_mtp_next_token(void* h) { return ((pk::QwenEngine*)h)->mtp_next_token(); }
+PK_EAPI int pk_qwen_copy_mtp_logits(void* h, float* out) {
+  return guarded([&] { ((pk::QwenEngine*)h)->copy_mtp_logits(out); });
+}
+PK_EAPI int pk_qwen_mtp_enabled(void* h) { return ((pk::QwenEngine*)h)->mtp_enabled() ? 1 : 0; }
+// Test hook: drafts are taken from this continuation (the tokens that follow the first generated one); n = 0 clears it.
+PK_EAPI int pk_qwen_set_draft_replay(void* h, const int* tokens, int n) {
+  return guarded([&] { ((pk::QwenEngine*)h)->set_draft_replay(tokens, n); });
 }
 
 // Recurrent-state snapshots (KV is position indexed and is not copied). A snapshot handle

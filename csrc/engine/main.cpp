@@ -36,6 +36,8 @@ struct Args {
   std::string ckpt, token_ids, token_ids_file, id_path = "/tmp/pocket_engine.rdv";
   int max_new_tokens = 16, tp_world = 1, tp_rank = 0, device = -1, max_context = 4096, prefill_chunk = 512;
   int window = 0, sink = 0;
+  bool mtp = false;
+  int mtp_tokens = 4;
   long random_seed = -1;
   bool benchmark_27b = false, dump_config = false, inspect = false, persistent_stdin = false, no_graph = false;
   // serving
@@ -54,6 +56,7 @@ void usage() {
                "  --tp-world N --tp-rank R --device D --nccl-id-path PATH\n"
                "  --max-context N --prefill-chunk-tokens N --no-cuda-graph\n"
                "  --qwen-attention-window N --qwen-attention-sink-tokens N\n"
+               "  --qwen-mtp [--qwen-mtp-tokens K]   speculative decode with the checkpoint's multi-token predictor\n"
                "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
                "  --tokenizer-gguf FILE --tokenize TEXT | --detokenize 1,2,3\n"
                "  --serve [--host H --port P --model-name N --tokenizer chars|hf:DIR|gguf:FILE --chat-format qwen|glm|minimax|dsv4\n"
@@ -81,6 +84,8 @@ Args parse(int argc, char** argv) {
     else if (f == "--prefill-chunk-tokens") a.prefill_chunk = std::stoi(need(i));
     else if (f == "--qwen-attention-window") a.window = std::stoi(need(i));
     else if (f == "--qwen-attention-sink-tokens") a.sink = std::stoi(need(i));
+    else if (f == "--qwen-mtp") a.mtp = true;
+    else if (f == "--qwen-mtp-tokens") { a.mtp_tokens = std::stoi(need(i)); a.mtp = true; }
     else if (f == "--random-init") a.random_seed = std::stol(need(i));
     else if (f == "--benchmark-27b") a.benchmark_27b = true;
     else if (f == "--dump-config") a.dump_config = true;
@@ -224,7 +229,10 @@ int serve_scripted(const Args& a) {
 struct RunResult {
   std::vector<int> tokens;
   double prefill_s = 0, decode_s = 0;
+  pk::QwenSpecStats spec;
 };
+
+int g_mtp_tokens = 4;   // draft length limit of speculative runs (--qwen-mtp-tokens)
 
 RunResult generate(pk::QwenEngine& eng, const std::vector<int>& prompt, int max_new) {
   RunResult r;
@@ -234,7 +242,8 @@ RunResult generate(pk::QwenEngine& eng, const std::vector<int>& prompt, int max_
   r.prefill_s = eng.timings().prefill_ms / 1e3;
   if (max_new > 1) {
     std::vector<int> rest(max_new - 1);
-    eng.decode(max_new - 1, rest.data(), false);
+    if (eng.mtp_enabled()) eng.spec_decode(max_new - 1, g_mtp_tokens, rest.data(), &r.spec);
+    else eng.decode(max_new - 1, rest.data(), false);
     r.tokens.insert(r.tokens.end(), rest.begin(), rest.end());
     r.decode_s = eng.timings().decode_ms / 1e3;
   }
@@ -248,6 +257,9 @@ void print_result(const char* tag, const Args& a, const pk::QwenEngine& eng, siz
               r.prefill_s > 0 ? prompt_len / r.prefill_s : 0.0, r.decode_s,
               r.decode_s > 0 ? (r.tokens.size() - 1) / r.decode_s : 0.0, eng.weight_bytes());
   for (size_t i = 0; i < r.tokens.size(); ++i) std::printf(i ? ",%d" : "%d", r.tokens[i]);
+  if (eng.mtp_enabled())
+    std::printf(" mtp_rounds=%lld mtp_proposed=%lld mtp_accepted=%lld mtp_rollbacks=%lld mtp_replay_tokens=%lld mtp_plain_steps=%lld",
+                r.spec.rounds, r.spec.proposed, r.spec.accepted, r.spec.rollbacks, r.spec.replay_tokens, r.spec.plain_steps);
   std::printf("\n");
   std::fflush(stdout);
 }
@@ -293,6 +305,8 @@ int run(const Args& a) {
   opt.use_cuda_graph = !a.no_graph;
   opt.attention_window = a.window;
   opt.attention_sink = a.sink;
+  opt.mtp = a.mtp;
+  g_mtp_tokens = a.mtp_tokens;
   pk::QwenEngine eng(cfg, opt);
   if (a.random_seed >= 0 || a.benchmark_27b) eng.init_random((uint64_t)std::max(0L, a.random_seed), 0.02f);
   else eng.load_safetensors(a.ckpt);

@@ -46,6 +46,9 @@ int pk_embedding(const int* tokens, int M, const void* table, int dim, int vocab
 int pk_rmsnorm(const void* x, const float* parts, int nparts, int M, int K, void* hidden_out,
                const float* gamma, int mode, float eps, void* y, const PkWait* wait, cudaStream_t stream);
 
+int pk_mtp_concat_norm(const int* tokens, int M, const void* table, const void* hidden, int K, const float* gamma_e,
+                       const float* gamma_h, float eps, void* out, cudaStream_t stream);
+
 int pk_silu_mul(const void* gate_up, int M, int inter, void* out, float limit, cudaStream_t stream);
 
 int pk_argmax(const float* logits, int ld, int M, int n, int id_offset, int nblocks, float* cand_val,

@@ -72,6 +72,44 @@ std::vector<float> bf16_vec_to_f32(const HostMat& m) {
   return out;
 }
 
+// fp32 -> E4M3 (round to nearest even, saturating at 448)
+uint8_t f32_to_e4m3(float f) {
+  const uint8_t sign = std::signbit(f) ? 0x80 : 0;
+  float a = std::fabs(f);
+  if (a != a) return sign | 0x7f;
+  if (a > 448.f) a = 448.f;
+  int e = 0;
+  (void)std::frexp(a, &e);
+  const int E = e - 1;   // a = 1.m * 2^E
+  if (a == 0.f || E < -6) return sign | (uint8_t)std::rint(std::ldexp(a, 9));   // zero and subnormals: multiples of 2^-9
+  int mant = (int)std::rint((std::ldexp(a, -E) - 1.f) * 8.f), ex = E;
+  if (mant == 8) {
+    mant = 0;
+    ++ex;
+  }
+  const int code = ((ex + 7) << 3) | mant;
+  return sign | (uint8_t)std::min(code, 0x7e);
+}
+
+// bf16 [rows, cols] -> E4M3 codes and one fp32 scale per 128 x 128 block (absmax / 448)
+void quantize_block128(const HostMat& m, std::vector<uint8_t>& codes, std::vector<float>& scales) {
+  const uint16_t* src = (const uint16_t*)m.data.data();
+  const int R = m.rows, C = m.cols, rb = (R + 127) / 128, cb = (C + 127) / 128;
+  codes.resize((size_t)R * C);
+  scales.assign((size_t)rb * cb, 1.f);
+  for (int br = 0; br < rb; ++br)
+    for (int bc = 0; bc < cb; ++bc) {
+      float amax = 0.f;
+      const int r1 = std::min(R, br * 128 + 128), c1 = std::min(C, bc * 128 + 128);
+      for (int r = br * 128; r < r1; ++r)
+        for (int c = bc * 128; c < c1; ++c) amax = std::max(amax, std::fabs(bf16_to_f32(src[(size_t)r * C + c])));
+      const float sc = amax > 0.f ? amax / 448.f : 1.f;
+      scales[(size_t)br * cb + bc] = sc;
+      for (int r = br * 128; r < r1; ++r)
+        for (int c = bc * 128; c < c1; ++c) codes[(size_t)r * C + c] = f32_to_e4m3(bf16_to_f32(src[(size_t)r * C + c]) / sc);
+    }
+}
+
 }  // namespace
 
 void QwenEngine::check(int status, const char* what) const {
@@ -129,9 +167,25 @@ QwenEngine::QwenEngine(const QwenConfig& cfg, const QwenEngineOptions& opt) : cf
 
   // ---- weights ----
   layers_.resize(cfg_.num_layers);
-  for (int i = 0; i < cfg_.num_layers; ++i) {
-    QwenLayer& L = layers_[i];
-    L.full = cfg_.layer_is_full[i] != 0;
+  for (int i = 0; i < cfg_.num_layers; ++i) alloc_layer(layers_[i], cfg_.layer_is_full[i] != 0);
+  embed_ = dalloc((size_t)cfg_.vocab_size * hidden_ * 2, true);
+  final_norm_ = (float*)dalloc(hidden_ * sizeof(float), true);
+  lm_head_ = dalloc((size_t)vocab_l_ * hidden_ * 2, true);
+  if (opt_.mtp) {
+    alloc_layer(mtp_layer_, true);
+    mtp_norm_e_ = (float*)dalloc(hidden_ * sizeof(float), true);
+    mtp_norm_h_ = (float*)dalloc(hidden_ * sizeof(float), true);
+    mtp_norm_ = (float*)dalloc(hidden_ * sizeof(float), true);
+    mtp_fc_ = dalloc((size_t)hidden_ * 2 * hidden_ * 2, true);
+  }
+  alloc_buffers();
+  reset();
+}
+
+void QwenEngine::alloc_layer(QwenLayer& L, bool full) {
+  const QwenEngineOptions& opt = opt_;
+  {
+    L.full = full;
     L.input_norm = (float*)dalloc(hidden_ * sizeof(float), true);
     L.post_norm = (float*)dalloc(hidden_ * sizeof(float), true);
     if (L.full) {
@@ -156,11 +210,6 @@ QwenEngine::QwenEngine(const QwenConfig& cfg, const QwenEngineOptions& opt) : cf
     alloc_fp8(L.gate_up, 2 * inter_l_, hidden_);
     alloc_fp8(L.down, hidden_, inter_l_);
   }
-  embed_ = dalloc((size_t)cfg_.vocab_size * hidden_ * 2, true);
-  final_norm_ = (float*)dalloc(hidden_ * sizeof(float), true);
-  lm_head_ = dalloc((size_t)vocab_l_ * hidden_ * 2, true);
-  alloc_buffers();
-  reset();
 }
 
 void QwenEngine::alloc_buffers() {
@@ -189,6 +238,19 @@ void QwenEngine::alloc_buffers() {
   out_counter_dev_ = (int*)dalloc(sizeof(int));
   gemm_status_ = (uint32_t*)dalloc(sizeof(uint32_t));
   cuda_check(cudaMemset(gemm_status_, 0, sizeof(uint32_t)), "memset");
+  if (opt_.mtp) {
+    mtp_cat_ = dalloc(R * 2 * hidden_ * 2);
+    tgt_hid_ = dalloc(R * hidden_ * 2);
+    mtp_out_ = dalloc((size_t)kSmallRows * hidden_ * 2);
+    cuda_check(cudaMemset(tgt_hid_, 0, R * hidden_ * 2), "memset");
+    cuda_check(cudaMemset(mtp_out_, 0, (size_t)kSmallRows * hidden_ * 2), "memset");
+    mtp_tok_dev_ = (int*)dalloc(R * sizeof(int));
+    mtp_pos_dev_ = (int*)dalloc(R * sizeof(int));
+    mtp_logits_ = (float*)dalloc((size_t)vocab_l_ * sizeof(float));
+    mtp_next_dev_ = (int*)dalloc(kSmallRows * sizeof(int));
+    cuda_check(cudaMallocHost((void**)&pinned_mtp_, 16 * sizeof(int)), "pinned");
+    mtp_seed_ = mtp_out_;
+  }
   cuda_check(cudaMallocHost((void**)&pinned_tok_, (size_t)std::max<int>(rows_cap_, out_cap_) * sizeof(int)), "pinned");
 
   // comm arena: [slot0][slot1][flags0][flags1][cand val][cand idx][cand flags][epoch][status][counter]
@@ -244,6 +306,11 @@ QwenEngine::~QwenEngine() {
   if (decode_graph_) cudaGraphExecDestroy(decode_graph_);
   for (void* p : allocs_) cudaFree(p);
   if (pinned_tok_) cudaFreeHost(pinned_tok_);
+  if (pinned_mtp_) cudaFreeHost(pinned_mtp_);
+  if (txn_) {
+    for (void* p : txn_->bufs) cudaFree(p);
+    for (void* p : txn_->kv) cudaFree(p);
+  }
   if (ev0_) cudaEventDestroy(ev0_);
   if (ev1_) cudaEventDestroy(ev1_);
   if (stream_) cudaStreamDestroy(stream_);
@@ -258,7 +325,11 @@ void QwenEngine::build_prefill_shadow() {
   if (mode == 0 || shadow_bytes_ > 0) return;
   size_t need = 0;
   auto count = [&](const Fp8Linear& l) { need += (size_t)l.N * l.K * 2; };
-  for (auto& L : layers_) {
+  std::vector<QwenLayer*> all;
+  for (auto& L : layers_) all.push_back(&L);
+  if (opt_.mtp) all.push_back(&mtp_layer_);
+  for (QwenLayer* lp : all) {
+    QwenLayer& L = *lp;
     if (L.full) { count(L.qkv); count(L.o_proj); } else { count(L.in_proj); count(L.out_proj); }
     count(L.gate_up);
     count(L.down);
@@ -272,7 +343,8 @@ void QwenEngine::build_prefill_shadow() {
     l.wb = dalloc((size_t)l.N * l.K * 2);
     check(pk_fp8_to_bf16(l.w, l.scale, l.N, l.K, l.wb, stream_), "fp8_to_bf16");
   };
-  for (auto& L : layers_) {
+  for (QwenLayer* lp : all) {
+    QwenLayer& L = *lp;
     if (L.full) { make(L.qkv); make(L.o_proj); } else { make(L.in_proj); make(L.out_proj); }
     make(L.gate_up);
     make(L.down);
@@ -286,7 +358,7 @@ void QwenEngine::init_random(uint64_t seed, float sigma) {
   auto fp8 = [&](Fp8Linear& l) { check(pk_fill_fp8_gauss(l.w, l.scale, l.N, l.K, sigma, s++, stream_), "fill fp8"); };
   auto f32 = [&](float* p, size_t n, float mean, float sd) { check(pk_fill_f32_gauss(p, n, mean, sd, s++, stream_), "fill f32"); };
   auto b16 = [&](void* p, size_t n, float sd) { check(pk_fill_bf16_gauss(p, n, 0.f, sd, s++, stream_), "fill bf16"); };
-  for (auto& L : layers_) {
+  auto fill_layer = [&](QwenLayer& L) {
     f32(L.input_norm, hidden_, 0.f, 0.02f);
     f32(L.post_norm, hidden_, 0.f, 0.02f);
     if (L.full) {
@@ -305,11 +377,20 @@ void QwenEngine::init_random(uint64_t seed, float sigma) {
     }
     fp8(L.gate_up);
     fp8(L.down);
-  }
+  };
+  for (auto& L : layers_) fill_layer(L);
   // The embedding is replicated, so every rank must draw the same table.
   check(pk_fill_bf16_gauss(embed_, (size_t)cfg_.vocab_size * hidden_, 0.f, sigma, seed * 7919ull + 1, stream_), "fill embed");
   check(pk_fill_f32_gauss(final_norm_, hidden_, 0.f, 0.02f, seed * 7919ull + 2, stream_), "fill norm");
   b16(lm_head_, (size_t)vocab_l_ * hidden_, sigma);
+  if (opt_.mtp) {
+    fill_layer(mtp_layer_);
+    // replicated tensors: the same draw on every rank
+    check(pk_fill_f32_gauss(mtp_norm_e_, hidden_, 0.f, 0.02f, seed * 7919ull + 3, stream_), "fill norm");
+    check(pk_fill_f32_gauss(mtp_norm_h_, hidden_, 0.f, 0.02f, seed * 7919ull + 4, stream_), "fill norm");
+    check(pk_fill_f32_gauss(mtp_norm_, hidden_, 0.f, 0.02f, seed * 7919ull + 5, stream_), "fill norm");
+    check(pk_fill_bf16_gauss(mtp_fc_, (size_t)hidden_ * 2 * hidden_, 0.f, sigma, seed * 7919ull + 6, stream_), "fill fc");
+  }
   cuda_check(cudaStreamSynchronize(stream_), "init_random");
   build_prefill_shadow();
 }
@@ -339,11 +420,22 @@ void QwenEngine::load_safetensors(const std::string& path) {
   struct Piece { HostMat w; std::vector<float> s; int sb_rows, sb_cols; };
   auto fp8_piece = [&](const std::string& name, int64_t r0, int64_t nr, int64_t c0, int64_t nc) {
     const StTensor& w = st.get(name + ".weight");
-    if (w.dtype != StDtype::F8_E4M3) throw std::runtime_error(name + ".weight is not F8_E4M3");
     if (r0 % 128 || c0 % 128 || nr % 128 || nc % 128)
       throw std::runtime_error("FP8 shard of " + name + " is not aligned to the 128x128 scale blocks");
-    const StTensor& s = st.get(name + ".weight_scale_inv");
     Piece p;
+    if (w.dtype == StDtype::BF16) {
+      // bf16 linears (the predictor's layer in some checkpoints) are quantised here to the engine's FP8 block format
+      HostMat m = cut(w, 2, r0, nr, c0, nc);
+      p.w.rows = m.rows;
+      p.w.cols = m.cols;
+      p.w.elem = 1;
+      quantize_block128(m, p.w.data, p.s);
+      p.sb_rows = (int)(nr / 128);
+      p.sb_cols = (int)(nc / 128);
+      return p;
+    }
+    if (w.dtype != StDtype::F8_E4M3) throw std::runtime_error(name + ".weight is neither F8_E4M3 nor BF16");
+    const StTensor& s = st.get(name + ".weight_scale_inv");
     p.w = cut(w, 1, r0, nr, c0, nc);
     p.sb_rows = (int)(nr / 128);
     p.sb_cols = (int)(nc / 128);
@@ -367,6 +459,29 @@ void QwenEngine::load_safetensors(const std::string& path) {
     if ((int)roff != dst.N) throw std::runtime_error("fp8 upload: N mismatch");
   };
 
+  auto load_full_attention = [&](QwenLayer& L, const std::string& p) {
+    const int64_t qrows = (int64_t)hq_l_ * 2 * kHeadDim, kvrows = (int64_t)hkv_l_ * kHeadDim;
+    std::vector<Piece> pcs;
+    pcs.push_back(fp8_piece(p + "self_attn.q_proj", R * qrows, qrows, 0, hidden_));
+    pcs.push_back(fp8_piece(p + "self_attn.k_proj", R * kvrows, kvrows, 0, hidden_));
+    pcs.push_back(fp8_piece(p + "self_attn.v_proj", R * kvrows, kvrows, 0, hidden_));
+    upload_fp8(L.qkv, pcs);
+    std::vector<Piece> o;
+    o.push_back(fp8_piece(p + "self_attn.o_proj", 0, hidden_, (int64_t)R * hq_l_ * kHeadDim, (int64_t)hq_l_ * kHeadDim));
+    upload_fp8(L.o_proj, o);
+    norm_vec(p + "self_attn.q_norm.weight", L.q_norm, 0, kHeadDim);
+    norm_vec(p + "self_attn.k_norm.weight", L.k_norm, 0, kHeadDim);
+  };
+  auto load_mlp = [&](QwenLayer& L, const std::string& p) {
+    std::vector<Piece> gu;
+    gu.push_back(fp8_piece(p + "mlp.gate_proj", (int64_t)R * inter_l_, inter_l_, 0, hidden_));
+    gu.push_back(fp8_piece(p + "mlp.up_proj", (int64_t)R * inter_l_, inter_l_, 0, hidden_));
+    upload_fp8(L.gate_up, gu);
+    std::vector<Piece> d;
+    d.push_back(fp8_piece(p + "mlp.down_proj", 0, hidden_, (int64_t)R * inter_l_, inter_l_));
+    upload_fp8(L.down, d);
+  };
+
   {
     const StTensor& e = st.get(root + "embed_tokens.weight");
     if (e.dtype != StDtype::BF16) throw std::runtime_error("embed_tokens must be BF16");
@@ -383,17 +498,7 @@ void QwenEngine::load_safetensors(const std::string& path) {
     norm_vec(p + "input_layernorm.weight", L.input_norm, 0, hidden_);
     norm_vec(p + "post_attention_layernorm.weight", L.post_norm, 0, hidden_);
     if (L.full) {
-      const int64_t qrows = (int64_t)hq_l_ * 2 * kHeadDim, kvrows = (int64_t)hkv_l_ * kHeadDim;
-      std::vector<Piece> pcs;
-      pcs.push_back(fp8_piece(p + "self_attn.q_proj", R * qrows, qrows, 0, hidden_));
-      pcs.push_back(fp8_piece(p + "self_attn.k_proj", R * kvrows, kvrows, 0, hidden_));
-      pcs.push_back(fp8_piece(p + "self_attn.v_proj", R * kvrows, kvrows, 0, hidden_));
-      upload_fp8(L.qkv, pcs);
-      std::vector<Piece> o;
-      o.push_back(fp8_piece(p + "self_attn.o_proj", 0, hidden_, (int64_t)R * hq_l_ * kHeadDim, (int64_t)hq_l_ * kHeadDim));
-      upload_fp8(L.o_proj, o);
-      norm_vec(p + "self_attn.q_norm.weight", L.q_norm, 0, kHeadDim);
-      norm_vec(p + "self_attn.k_norm.weight", L.k_norm, 0, kHeadDim);
+      load_full_attention(L, p);
     } else {
       std::vector<Piece> pcs;
       pcs.push_back(fp8_piece(p + "linear_attn.in_proj_qkv", (int64_t)R * kd_l_, kd_l_, 0, hidden_));
@@ -417,13 +522,21 @@ void QwenEngine::load_safetensors(const std::string& path) {
       norm_vec(p + "linear_attn.dt_bias", L.dt_bias, (int64_t)R * vh_l_, vh_l_);
       norm_vec(p + "linear_attn.norm.weight", L.lin_norm, 0, kHeadDim);
     }
-    std::vector<Piece> gu;
-    gu.push_back(fp8_piece(p + "mlp.gate_proj", (int64_t)R * inter_l_, inter_l_, 0, hidden_));
-    gu.push_back(fp8_piece(p + "mlp.up_proj", (int64_t)R * inter_l_, inter_l_, 0, hidden_));
-    upload_fp8(L.gate_up, gu);
-    std::vector<Piece> d;
-    d.push_back(fp8_piece(p + "mlp.down_proj", 0, hidden_, (int64_t)R * inter_l_, inter_l_));
-    upload_fp8(L.down, d);
+    load_mlp(L, p);
+  }
+  if (opt_.mtp) {
+    if (!st.has("mtp.fc.weight")) throw std::runtime_error("the checkpoint has no mtp.* tensors (multi-token predictor requested)");
+    norm_vec("mtp.pre_fc_norm_embedding.weight", mtp_norm_e_, 0, hidden_);
+    norm_vec("mtp.pre_fc_norm_hidden.weight", mtp_norm_h_, 0, hidden_);
+    norm_vec("mtp.norm.weight", mtp_norm_, 0, hidden_);
+    const StTensor& fc = st.get("mtp.fc.weight");
+    if (fc.dtype != StDtype::BF16 || fc.nbytes != (size_t)hidden_ * 2 * hidden_ * 2) throw std::runtime_error("mtp.fc.weight must be BF16 [hidden, 2 * hidden]");
+    upload(mtp_fc_, fc.data, fc.nbytes);
+    const std::string p = "mtp.layers.0.";
+    norm_vec(p + "input_layernorm.weight", mtp_layer_.input_norm, 0, hidden_);
+    norm_vec(p + "post_attention_layernorm.weight", mtp_layer_.post_norm, 0, hidden_);
+    load_full_attention(mtp_layer_, p);
+    load_mlp(mtp_layer_, p);
   }
   (void)W;
   cuda_check(cudaDeviceSynchronize(), "load_safetensors");
@@ -445,6 +558,9 @@ void QwenEngine::reset() {
   pos_ = 0;
   last_token_ = -1;
   pending_site_ = -1;
+  mtp_pos_ = 0;
+  mtp_ready_ = false;
+  tgt_rows_ = 0;
 }
 
 std::unique_ptr<QwenEngine::Snapshot> QwenEngine::snapshot(bool with_kv) {
@@ -512,6 +628,8 @@ void QwenEngine::restore(const Snapshot& s) {
   cuda_check(cudaStreamSynchronize(stream_), "restore");
   pos_ = s.pos;
   last_token_ = s.last_token;
+  mtp_ready_ = false;     // the predictor's boundary row belongs to the abandoned position
+  mtp_pos_ = s.pos;
 }
 
 void QwenEngine::free_snapshot(Snapshot& s) {
@@ -532,6 +650,12 @@ uint32_t QwenEngine::comm_status() {
 void QwenEngine::copy_logits(float* out_host, int row) {
   cuda_check(cudaStreamSynchronize(stream_), "sync");
   cuda_check(cudaMemcpy(out_host, logits_ + (size_t)row * vocab_l_, (size_t)vocab_l_ * sizeof(float), cudaMemcpyDeviceToHost), "logits");
+}
+
+void QwenEngine::copy_mtp_logits(float* out_host) {
+  if (!opt_.mtp) throw std::runtime_error("the engine was built without the multi-token predictor");
+  cuda_check(cudaStreamSynchronize(stream_), "sync");
+  cuda_check(cudaMemcpy(out_host, mtp_logits_, (size_t)vocab_l_ * sizeof(float), cudaMemcpyDeviceToHost), "logits");
 }
 
 // ---------------------------------------------------------------------------------------
@@ -571,12 +695,21 @@ PkPush QwenEngine::make_push(int site, bool big) const {
 // ---------------------------------------------------------------------------------------
 // forward, weight-streaming path (1..8 rows)
 
-void QwenEngine::run_small(int M, bool all_logits) {
+void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
   if (!peers_set_) throw std::runtime_error("peer arenas not registered");
   const float eps = (float)cfg_.rms_norm_eps;
   const int W = opt_.tp_world;
+  const int* posd = mtp ? mtp_pos_dev_ : pos_dev_;
+  const int n_layers = mtp ? 1 : cfg_.num_layers;
   check(pk_bump_epoch((uint32_t*)((char*)arena_ + off_epoch_), stream_), "epoch");
-  check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hidden_buf_[cur_], nullptr, stream_), "embedding");
+  if (mtp) {
+    check(pk_mtp_concat_norm(mtp_tok_dev_, M, embed_, mtp_in_, hidden_, mtp_norm_e_, mtp_norm_h_, eps, mtp_cat_, stream_), "mtp_concat_norm");
+    check(pk_matvec(nullptr, nullptr, mtp_fc_, 0, hidden_, 2 * hidden_, M, mtp_cat_, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 0,
+                    hidden_buf_[cur_], hidden_, nullptr, sm_count_, stream_),
+          "matvec(mtp fc)");
+  } else {
+    check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hidden_buf_[cur_], nullptr, stream_), "embedding");
+  }
   int pending = -1;  // site whose partial sums still wait to be added to the residual stream
 
   auto consume = [&](const Fp8Linear* w, const void* wb, int nb, const float* gamma, int epi, void* y, int ldy,
@@ -599,15 +732,15 @@ void QwenEngine::run_small(int M, bool all_logits) {
     pending = site;
   };
 
-  for (int i = 0; i < cfg_.num_layers; ++i) {
-    QwenLayer& L = layers_[i];
+  for (int i = 0; i < n_layers; ++i) {
+    QwenLayer& L = mtp ? mtp_layer_ : layers_[i];
     if (L.full) {
       consume(&L.qkv, nullptr, 0, L.input_norm, 0, proj_, ld_proj_, nullptr);
-      check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, pos_dev_, L.q_norm, L.k_norm, eps,
+      check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, posd, L.q_norm, L.k_norm, eps,
                                    cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache,
                                    opt_.max_context, stream_),
             "qk_norm_rope_append");
-      check(pk_gqa_decode(q_buf_, L.kcache, L.vcache, pos_dev_, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
+      check(pk_gqa_decode(q_buf_, L.kcache, L.vcache, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
                           1.f / sqrtf((float)kHeadDim), opt_.decode_splits, opt_.attention_window, opt_.attention_sink,
                           attn_ws_, cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
             "gqa_decode");
@@ -623,10 +756,30 @@ void QwenEngine::run_small(int M, bool all_logits) {
     consume(&L.gate_up, nullptr, 0, L.post_norm, 1, mlp_h_, inter_l_, nullptr);
     produce(L.down, mlp_h_, 2 * i + 1);
   }
+  if (opt_.mtp) {
+    // The normalised rows are kept: the target's feed the predictor, the predictor's last one seeds its next row.
+    const float* parts = slot_parts(pending);
+    PkWait wt = make_wait(pending);
+    void* y = mtp ? mtp_out_ : tgt_hid_;
+    check(pk_rmsnorm(hidden_buf_[cur_], parts, W, M, hidden_, hidden_buf_[cur_], mtp ? mtp_norm_ : final_norm_, 1, eps, y, &wt, stream_),
+          "final norm");
+    pending = -1;
+    const bool all = !mtp && (all_logits || M == 1);
+    const int rows = all ? M : 1;
+    const char* x = (const char*)y + (all ? 0 : (size_t)(M - 1) * hidden_ * 2);
+    float* lg = mtp ? mtp_logits_ : logits_;
+    check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, rows, x, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 2, lg,
+                    vocab_l_, nullptr, sm_count_, stream_),
+          "lm_head");
+    sample_rows(rows, lg, mtp ? mtp_next_dev_ : next_tok_dev_);
+    if (mtp) mtp_seed_ = x;
+    else tgt_rows_ = M;
+    return;
+  }
   // final norm + lm_head on every row (speculative verify) or on the last row only
   if (all_logits || M == 1) {
     consume(nullptr, lm_head_, vocab_l_, final_norm_, 2, logits_, vocab_l_, nullptr);
-    sample_rows(M, 0);
+    sample_rows(M, logits_, next_tok_dev_);
   } else {
     // Fold the pending partials into the hidden state first, then project the last row.
     const float* parts = slot_parts(pending);
@@ -638,15 +791,15 @@ void QwenEngine::run_small(int M, bool all_logits) {
     check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, last, nullptr, 0, nullptr, final_norm_, 1, eps,
                     nullptr, 2, logits_, vocab_l_, nullptr, sm_count_, stream_),
           "lm_head");
-    sample_rows(1, 0);
+    sample_rows(1, logits_, next_tok_dev_);
   }
 }
 
-// Greedy token of `M` logits rows -> next_tok_dev_[0..M).
-void QwenEngine::sample_rows(int M, int first_row) {
+// Greedy token of `M` logits rows -> out[0..M).
+void QwenEngine::sample_rows(int M, const float* logits, int* out) {
   const int W = opt_.tp_world;
-  check(pk_argmax(logits_ + (size_t)first_row * vocab_l_, vocab_l_, M, vocab_l_, vocab_start_, kArgmaxBlocks, cand_val_,
-                  cand_idx_, best_val_, W == 1 ? next_tok_dev_ : best_idx_, stream_),
+  check(pk_argmax(logits, vocab_l_, M, vocab_l_, vocab_start_, kArgmaxBlocks, cand_val_,
+                  cand_idx_, best_val_, W == 1 ? out : best_idx_, stream_),
         "argmax");
   ++launches_;
   if (W > 1) {
@@ -658,7 +811,7 @@ void QwenEngine::sample_rows(int M, int first_row) {
     PkWait wt = make_wait(site);
     wt.flag = (const uint32_t*)((char*)arena_ + off_cflag_);
     check(pk_cand_merge_wait((const float*)((char*)arena_ + off_cval_), (const int*)((char*)arena_ + off_cidx_), M, W,
-                             &wt, next_tok_dev_, stream_),
+                             &wt, out, stream_),
           "cand_merge");
   }
 }
@@ -666,13 +819,22 @@ void QwenEngine::sample_rows(int M, int first_row) {
 // ---------------------------------------------------------------------------------------
 // forward, tensor-core path (more than 8 rows, one rank)
 
-void QwenEngine::run_chunk(int M) {
+void QwenEngine::run_chunk(int M, bool mtp) {
   if (!peers_set_) throw std::runtime_error("peer arenas not registered");
   const float eps = (float)cfg_.rms_norm_eps;
   const int W = opt_.tp_world;
+  const int* posd = mtp ? mtp_pos_dev_ : pos_dev_;
+  const int n_layers = mtp ? 1 : cfg_.num_layers;
   void* hid = hidden_buf_[cur_];
   if (W > 1) check(pk_bump_epoch((uint32_t*)((char*)arena_ + off_epoch_), stream_), "epoch");
-  check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hid, nullptr, stream_), "embedding");
+  if (mtp) {
+    check(pk_mtp_concat_norm(mtp_tok_dev_, M, embed_, mtp_in_, hidden_, mtp_norm_e_, mtp_norm_h_, eps, mtp_cat_, stream_), "mtp_concat_norm");
+    int rc = pk_gemm_bf16(mtp_cat_, 2 * hidden_, mtp_fc_, M, hidden_, 2 * hidden_, 0, hid, nullptr, hidden_, gemm_status_, nullptr, sm_count_, stream_);
+    if (rc == 4) rc = pk_gemm_umma(mtp_cat_, 2 * hidden_, mtp_fc_, nullptr, 1, M, hidden_, 2 * hidden_, 0, hid, nullptr, hidden_, gemm_status_, nullptr, stream_);
+    check(rc, "gemm(mtp fc)");
+  } else {
+    check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hid, nullptr, stream_), "embedding");
+  }
   int pending = -1;  // site whose partial sums still wait to be added to the residual stream
   auto gemm = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc) {
     if (w.wb != nullptr) {
@@ -707,16 +869,16 @@ void QwenEngine::run_chunk(int M) {
       check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, gamma, 1, eps, y, nullptr, stream_), "rmsnorm");
     }
   };
-  for (int i = 0; i < cfg_.num_layers; ++i) {
-    QwenLayer& L = layers_[i];
+  for (int i = 0; i < n_layers; ++i) {
+    QwenLayer& L = mtp ? mtp_layer_ : layers_[i];
     norm(L.input_norm, xn_);
     if (L.full) {
       gemm(xn_, hidden_, L.qkv, 0, proj_, nullptr, ld_proj_);
-      check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, pos_dev_, L.q_norm, L.k_norm, eps,
+      check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, posd, L.q_norm, L.k_norm, eps,
                                    cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache,
                                    opt_.max_context, stream_),
             "qk_norm_rope_append");
-      check(pk_gqa_decode(q_buf_, L.kcache, L.vcache, pos_dev_, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
+      check(pk_gqa_decode(q_buf_, L.kcache, L.vcache, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
                           1.f / sqrtf((float)kHeadDim), 1, opt_.attention_window, opt_.attention_sink, attn_ws_,
                           cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
             "gqa_prefill");
@@ -743,12 +905,32 @@ void QwenEngine::run_chunk(int M) {
     gemm(xn_, hidden_, L.gate_up, 1, mlp_h_, nullptr, inter_l_);
     gemm_out(mlp_h_, inter_l_, L.down, 2 * i + 1);
   }
+  if (opt_.mtp && !mtp) {
+    // every normalised row feeds the predictor; the last one also gives the logits
+    norm(final_norm_, tgt_hid_);
+    tgt_rows_ = M;
+    const char* x = (const char*)tgt_hid_ + (size_t)(M - 1) * hidden_ * 2;
+    check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, x, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 2, logits_,
+                    vocab_l_, nullptr, sm_count_, stream_),
+          "lm_head");
+    sample_rows(1, logits_, next_tok_dev_);
+    return;
+  }
   if (pending >= 0) norm(final_norm_, nullptr);  // fold the last partials into the residual stream
   const char* last = (const char*)hid + (size_t)(M - 1) * hidden_ * 2;
+  if (mtp) {
+    check(pk_rmsnorm(last, nullptr, 0, 1, hidden_, nullptr, mtp_norm_, 1, eps, mtp_out_, nullptr, stream_), "mtp norm");
+    check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, mtp_out_, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 2,
+                    mtp_logits_, vocab_l_, nullptr, sm_count_, stream_),
+          "lm_head(mtp)");
+    sample_rows(1, mtp_logits_, mtp_next_dev_);
+    mtp_seed_ = mtp_out_;
+    return;
+  }
   check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, last, nullptr, 0, nullptr, final_norm_, 1, eps,
                   nullptr, 2, logits_, vocab_l_, nullptr, sm_count_, stream_),
         "lm_head");
-  sample_rows(1, 0);
+  sample_rows(1, logits_, next_tok_dev_);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -770,12 +952,21 @@ int QwenEngine::prefill(const int* tokens_host, int n) {
     check(pk_iota_int(pos_dev_, M, nullptr, pos_, stream_), "iota");
     if (M <= kSmallRows) run_small(M, false);
     else run_chunk(M);
+    if (opt_.mtp) {
+      // prime the predictor: row i pairs the target's hidden of position i with the token of position i + 1; the
+      // very last row takes the token the target has just produced
+      if (M > 1) check(pk_copy_int(tokens_dev_ + 1, mtp_tok_dev_, M - 1, stream_), "shift tokens");
+      if (done + M < n) check(pk_iota_int(mtp_tok_dev_ + (M - 1), 1, nullptr, tokens_host[done + M], stream_), "next token");
+      else check(pk_copy_int(next_tok_dev_, mtp_tok_dev_ + (M - 1), 1, stream_), "first output token");
+      mtp_forward(M, tgt_hid_, pos_);
+    }
     // The pinned staging buffer is reused by the next chunk.
     cuda_check(cudaStreamSynchronize(stream_), "prefill chunk");
     pos_ += M;
     done += M;
   }
   cuda_check(cudaMemcpyAsync(pinned_tok_, next_tok_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h token");
+  if (opt_.mtp) cuda_check(cudaMemcpyAsync(pinned_mtp_, mtp_next_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h draft");
   cuda_check(cudaEventRecord(ev1_, stream_), "event");
   cuda_check(cudaStreamSynchronize(stream_), "prefill");
   float ms = 0;
@@ -784,6 +975,11 @@ int QwenEngine::prefill(const int* tokens_host, int n) {
   timings_.prefill_tokens = n;
   timings_.kernel_launches += launches_ - l0;
   last_token_ = pinned_tok_[0];
+  if (opt_.mtp) {
+    mtp_ready_ = true;
+    mtp_seed_token_ = last_token_;
+    mtp_next_token_ = pinned_mtp_[0];
+  }
   return last_token_;
 }
 
@@ -850,6 +1046,9 @@ void QwenEngine::decode(int steps, int* out_host, bool sync_each_step) {
   timings_.kernel_launches += launches_ - l0;
   pos_ += steps;
   last_token_ = pinned_tok_[steps - 1];
+  mtp_ready_ = false;   // the predictor has not seen these positions
+  mtp_pos_ = pos_;
+  tgt_rows_ = 1;
   if (out_host) memcpy(out_host, pinned_tok_, (size_t)steps * sizeof(int));
 }
 
@@ -868,7 +1067,117 @@ void QwenEngine::forward_rows(const int* tokens_host, int M, int* out_tokens_hos
   cuda_check(cudaStreamSynchronize(stream_), "forward_rows");
   pos_ += M;
   last_token_ = pinned_tok_[M - 1];
+  mtp_ready_ = false;
+  mtp_pos_ = pos_;
   if (out_tokens_host) memcpy(out_tokens_host, pinned_tok_, (size_t)M * sizeof(int));
+}
+
+// ---------------------------------------------------------------------------------------
+// multi-token predictor and speculative decode
+
+void QwenEngine::mtp_forward(int M, const void* hidden_rows, int position) {
+  mtp_in_ = hidden_rows;
+  check(pk_iota_int(mtp_pos_dev_, M, nullptr, position, stream_), "iota");
+  if (M <= kSmallRows) run_small(M, false, true);
+  else run_chunk(M, true);
+  mtp_pos_ = position + M;
+}
+
+int QwenEngine::mtp_row(int token, const void* hidden_row, int position) {
+  check(pk_iota_int(mtp_tok_dev_, 1, nullptr, token, stream_), "token");
+  mtp_forward(1, hidden_row, position);
+  cuda_check(cudaMemcpyAsync(pinned_mtp_, mtp_next_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h draft");
+  cuda_check(cudaStreamSynchronize(stream_), "mtp row");
+  mtp_seed_token_ = token;
+  mtp_next_token_ = pinned_mtp_[0];
+  mtp_ready_ = true;
+  return mtp_next_token_;
+}
+
+// Drafts after `input_token` (generated, not yet consumed by the target at position pos_). The first draft is the
+// boundary row's prediction when that row was given this token, else the row is rebuilt from the target's last hidden;
+// further drafts recurse on the predictor's own output.
+void QwenEngine::draft_tokens(int count, int input_token, int produced, std::vector<int>& drafts, QwenSpecStats& st) {
+  drafts.clear();
+  if (!(mtp_ready_ && mtp_seed_token_ == input_token)) {
+    const char* last = (const char*)tgt_hid_ + (size_t)std::max(tgt_rows_ - 1, 0) * hidden_ * 2;
+    mtp_row(input_token, last, pos_ - 1);
+    ++st.predictor_rows;
+  }
+  auto pick = [&](int predicted) {
+    const size_t at = (size_t)produced + drafts.size();
+    return at < replay_.size() ? replay_[at] : predicted;
+  };
+  drafts.push_back(pick(mtp_next_token_));
+  while ((int)drafts.size() < count) {
+    const int next = mtp_row(drafts.back(), mtp_seed_, mtp_pos_);
+    ++st.predictor_rows;
+    drafts.push_back(pick(next));
+  }
+}
+
+void QwenEngine::spec_decode(int steps, int max_draft, int* out_host, QwenSpecStats* stats_out) {
+  if (!opt_.mtp) throw std::runtime_error("spec_decode: the engine was built without the multi-token predictor");
+  if (last_token_ < 0) throw std::runtime_error("spec_decode before prefill");
+  if (steps < 1) return;
+  if (pos_ + steps + kSmallRows + 1 > opt_.max_context) throw std::runtime_error("spec_decode: exceeds max_context");
+  max_draft = std::max(1, std::min(max_draft, kSmallRows - 1));
+  QwenSpecStats st;
+  if (!txn_) txn_ = snapshot(false);
+  std::vector<int> out, drafts, rows(kSmallRows), preds(kSmallRows);
+  out.reserve(steps + kSmallRows);
+  cuda_check(cudaEventRecord(ev0_, stream_), "event");
+  const long long l0 = launches_;
+  int K = 1;
+  while ((int)out.size() < steps) {
+    const int remaining = steps - (int)out.size();
+    if (remaining == 1) {
+      int t = last_token_, next = 0;
+      forward_rows(&t, 1, &next);
+      out.push_back(next);
+      ++st.plain_steps;
+      continue;
+    }
+    const int k = std::min(K, std::min(remaining - 1, max_draft));
+    const int committed = pos_, input = last_token_;
+    draft_tokens(k, input, (int)out.size(), drafts, st);
+    update_snapshot(*txn_);
+    rows[0] = input;
+    for (int i = 0; i < k; ++i) rows[i + 1] = drafts[i];
+    forward_rows(rows.data(), k + 1, preds.data());
+    int correct = 0;
+    while (correct < k && preds[correct] == drafts[correct]) ++correct;
+    const int bonus = preds[correct];
+    ++st.rounds;
+    st.proposed += k;
+    st.accepted += correct;
+    if (correct < k) {
+      // rows after the first mismatch have advanced the recurrent state: rewind and replay the accepted prefix
+      ++st.rollbacks;
+      st.replay_tokens += correct + 1;
+      restore(*txn_);
+      forward_rows(rows.data(), correct + 1, preds.data());
+      if (preds[correct] != bonus) throw std::runtime_error("spec_decode: the replay disagrees with the verify pass");
+    }
+    // pos_ == committed + correct + 1; the target's hidden of the last committed row is row `correct` of tgt_hid_.
+    // Rebind the predictor's boundary row to the bonus token (not yet consumed by the target).
+    mtp_row(bonus, (const char*)tgt_hid_ + (size_t)correct * hidden_ * 2, committed + correct);
+    ++st.predictor_rows;
+    for (int i = 0; i < correct; ++i) out.push_back(drafts[i]);
+    out.push_back(bonus);
+    last_token_ = bonus;
+    K = correct == k ? std::min(2 * K, max_draft) : std::max(1, std::min(K / 2, correct + 1));
+  }
+  // a round may overshoot by nothing: k <= remaining - 1, so at most `remaining` tokens are added
+  cuda_check(cudaEventRecord(ev1_, stream_), "event");
+  cuda_check(cudaStreamSynchronize(stream_), "spec_decode");
+  float ms = 0;
+  cudaEventElapsedTime(&ms, ev0_, ev1_);
+  timings_.decode_ms = ms;
+  timings_.decode_tokens = steps;
+  timings_.kernel_launches += launches_ - l0;
+  if (out_host) memcpy(out_host, out.data(), (size_t)steps * sizeof(int));
+  if (stats_out) *stats_out = st;
 }
 
 }  // namespace pk

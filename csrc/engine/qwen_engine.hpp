@@ -33,6 +33,19 @@ struct QwenEngineOptions {
   // -1 = when HBM has room for them (twice the FP8 bytes plus a reserve), 0 = never, 1 = always.
   // POCKET_PREFILL_SHADOW in the environment overrides.
   int prefill_bf16_shadow = -1;
+  // Multi-token predictor (`mtp.*` tensors: two input norms, fc, one full-attention layer, norm) for speculative decoding.
+  bool mtp = false;
+};
+
+// Counters of spec_decode().
+struct QwenSpecStats {
+  long long rounds = 0;         // draft + verify rounds
+  long long proposed = 0;       // draft tokens sent to the target
+  long long accepted = 0;       // of those, matched by the target
+  long long rollbacks = 0;      // rounds that restored the recurrent state and replayed
+  long long replay_tokens = 0;
+  long long plain_steps = 0;    // tokens produced by single-row decode
+  long long predictor_rows = 0; // rows run through the predictor (priming excluded)
 };
 
 struct Fp8Linear {
@@ -104,6 +117,19 @@ class QwenEngine {
   // Verify-style forward over M (<= 8) given tokens at consecutive positions; returns
   // the greedy token after each row. State advances by M tokens.
   void forward_rows(const int* tokens_host, int M, int* out_tokens_host);
+  // Greedy decode of `steps` tokens with drafts from the multi-token predictor, verified by the target in one
+  // multi-row pass per round. The tokens equal those of decode(). Draft length starts at 1, doubles after a
+  // fully accepted round up to `max_draft` (<= 7), and shrinks to max(1, min(K / 2, accepted + 1)) after a reject;
+  // the last token comes from a plain step.
+  void spec_decode(int steps, int max_draft, int* out_host, QwenSpecStats* stats);
+  bool mtp_enabled() const { return opt_.mtp; }
+  // The predictor's current pick for the token after last_token() (-1 when its boundary row is stale), and the fp32
+  // logits behind it (this rank's vocabulary shard).
+  int mtp_next_token() const { return mtp_ready_ ? mtp_next_token_ : -1; }
+  void copy_mtp_logits(float* out_host);
+  // Test hook: the known continuation (tokens that follow the first generated one). While set, spec_decode drafts
+  // come from it instead of the predictor's picks (the predictor still runs, so its state stays consistent).
+  void set_draft_replay(const int* tokens, int n) { replay_.assign(tokens, tokens + n); }
 
   int position() const { return pos_; }
   int last_token() const { return last_token_; }
@@ -138,9 +164,15 @@ class QwenEngine {
   void build_prefill_shadow();   // after the weights are in place
   void alloc_fp8(Fp8Linear& l, int N, int K);
   void* dalloc(size_t bytes, bool weight = false);
-  void run_small(int M, bool all_logits);    // M <= 8 rows: weight-streaming path
-  void run_chunk(int M);                     // M > 8 rows: tensor-core path
-  void sample_rows(int M, int first_row);
+  // `mtp` runs the predictor stack (input = [norm(embed(mtp_tok_dev_)) | norm(mtp_in_)] through fc, one layer,
+  // mtp.norm, logits of the last row) instead of the target.
+  void run_small(int M, bool all_logits, bool mtp = false);    // M <= 8 rows: weight-streaming path
+  void run_chunk(int M, bool mtp = false);                     // M > 8 rows: tensor-core path
+  void sample_rows(int M, const float* logits, int* out);
+  void mtp_forward(int M, const void* hidden_rows, int position);   // tokens already in mtp_tok_dev_
+  int mtp_row(int token, const void* hidden_row, int position);     // one row; returns the predicted token
+  void draft_tokens(int count, int input_token, int produced, std::vector<int>& drafts, QwenSpecStats& st);
+  void alloc_layer(QwenLayer& L, bool full);
   void capture_decode_graph();
   PkWait make_wait(int site) const;
   PkPush make_push(int site, bool big = false) const;
@@ -201,6 +233,30 @@ class QwenEngine {
   bool peers_set_ = false;
   int sites_per_epoch_ = 0;
   int pending_site_ = -1;   // site whose partials still have to be added to the hidden state
+
+  // multi-token predictor
+  QwenLayer mtp_layer_;
+  float* mtp_norm_e_ = nullptr;
+  float* mtp_norm_h_ = nullptr;
+  float* mtp_norm_ = nullptr;
+  void* mtp_fc_ = nullptr;        // bf16 [hidden, 2 * hidden], replicated
+  void* mtp_cat_ = nullptr;       // [rows_cap, 2 * hidden]
+  void* tgt_hid_ = nullptr;       // [rows_cap, hidden]: the target's last forward after the final norm
+  void* mtp_out_ = nullptr;       // [8, hidden]: the predictor's last forward after mtp.norm
+  const void* mtp_in_ = nullptr;  // hidden rows the next predictor pass reads
+  const void* mtp_seed_ = nullptr;  // row of mtp_out_ that seeds the next recursive draft
+  int* mtp_tok_dev_ = nullptr;
+  int* mtp_pos_dev_ = nullptr;
+  float* mtp_logits_ = nullptr;   // [vocab_l]
+  int* mtp_next_dev_ = nullptr;
+  int* pinned_mtp_ = nullptr;
+  int tgt_rows_ = 0;              // rows of tgt_hid_ written by the last target forward
+  int mtp_pos_ = 0;
+  int mtp_seed_token_ = -1;       // token the predictor's boundary row was given
+  int mtp_next_token_ = -1;       // its prediction
+  bool mtp_ready_ = false;
+  std::unique_ptr<Snapshot> txn_;
+  std::vector<int> replay_;
 
   int pos_ = 0;
   int last_token_ = -1;

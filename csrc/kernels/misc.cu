@@ -155,6 +155,27 @@ __global__ void copy_int_kernel(const int* src, int* dst, int n) {
   if (i < n) dst[i] = src[i];
 }
 
+// Input of the multi-token predictor: out[m] = [ norm_e(embed[tokens[m]]) | norm_h(hidden[m]) ], both (1 + gamma) RMSNorms.
+// blockIdx.y picks the half.
+__global__ void __launch_bounds__(256) mtp_concat_norm_kernel(const int* tokens, const bf16* table, const bf16* hidden, int K,
+                                                              const float* gamma_e, const float* gamma_h, float eps, bf16* out) {
+  extern __shared__ float row[];
+  __shared__ float red[40];
+  const int m = blockIdx.x, half = blockIdx.y;
+  const bf16* src = half == 0 ? table + (size_t)tokens[m] * K : hidden + (size_t)m * K;
+  const float* gamma = half == 0 ? gamma_e : gamma_h;
+  float ss = 0.f;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    const float v = __bfloat162float(src[k]);
+    row[k] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / (float)K + eps);
+  bf16* dst = out + (size_t)m * 2 * K + (size_t)half * K;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = __float2bfloat16(row[k] * r * (1.f + gamma[k]));
+}
+
 }  // namespace
 
 PK_API int pk_embedding(const int* tokens, int M, const void* table, int dim, int vocab_start,
@@ -198,6 +219,16 @@ PK_API int pk_rmsnorm(const void* x, const float* parts, int nparts, int M, int 
     }
   }
   PK_LAUNCH(rmsnorm_kernel, dim3(M), dim3(256), smem, stream, p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+// tokens [M] (ids inside the replicated table), hidden bf16 [M, K] -> out bf16 [M, 2K].
+PK_API int pk_mtp_concat_norm(const int* tokens, int M, const void* table, const void* hidden, int K, const float* gamma_e,
+                              const float* gamma_h, float eps, void* out, cudaStream_t stream) {
+  if (M < 1 || K < 1 || (size_t)K * sizeof(float) > 48 * 1024) return PK_ERR_BAD_ARG;
+  PK_LAUNCH(mtp_concat_norm_kernel, dim3(M, 2), dim3(256), (size_t)K * sizeof(float), stream, tokens, (const pk::bf16*)table,
+            (const pk::bf16*)hidden, K, gamma_e, gamma_h, eps, (pk::bf16*)out);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }

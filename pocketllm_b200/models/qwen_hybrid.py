@@ -88,7 +88,9 @@ class QwenHybridConfig:
 # random checkpoints in the reference's tensor naming
 
 def random_checkpoint(cfg: QwenHybridConfig, seed: int = 0, sigma: float = 0.02,
-                      prefix: str = "model.language_model.") -> dict[str, torch.Tensor]:
+                      prefix: str = "model.language_model.", mtp: bool = False, mtp_bf16_linears: bool = False) -> dict[str, torch.Tensor]:
+    """`mtp` adds the multi-token predictor (`mtp.*`: two input norms, fc, one full-attention layer, norm); its layer
+    linears are FP8 like the backbone's, or plain bf16 with `mtp_bf16_linears`."""
     g = torch.Generator().manual_seed(seed)
     out: dict[str, torch.Tensor] = {}
     H, D = cfg.hidden_size, cfg.head_dim
@@ -133,6 +135,23 @@ def random_checkpoint(cfg: QwenHybridConfig, seed: int = 0, sigma: float = 0.02,
         fp8(p + "mlp.gate_proj", cfg.intermediate_size, H)
         fp8(p + "mlp.up_proj", cfg.intermediate_size, H)
         fp8(p + "mlp.down_proj", H, cfg.intermediate_size)
+    if mtp:
+        lin = (lambda name, n, k: bf16(name + ".weight", n, k)) if mtp_bf16_linears else fp8
+        for name in ("pre_fc_norm_embedding", "pre_fc_norm_hidden", "norm"):
+            bf16(f"mtp.{name}.weight", H, std=0.05)
+        bf16("mtp.fc.weight", H, 2 * H)
+        p = "mtp.layers.0."
+        bf16(p + "input_layernorm.weight", H, std=0.05)
+        bf16(p + "post_attention_layernorm.weight", H, std=0.05)
+        lin(p + "self_attn.q_proj", cfg.num_attention_heads * D * (2 if cfg.attn_output_gate else 1), H)
+        lin(p + "self_attn.k_proj", cfg.num_key_value_heads * D, H)
+        lin(p + "self_attn.v_proj", cfg.num_key_value_heads * D, H)
+        lin(p + "self_attn.o_proj", H, cfg.num_attention_heads * D)
+        bf16(p + "self_attn.q_norm.weight", D, std=0.05)
+        bf16(p + "self_attn.k_norm.weight", D, std=0.05)
+        lin(p + "mlp.gate_proj", cfg.intermediate_size, H)
+        lin(p + "mlp.up_proj", cfg.intermediate_size, H)
+        lin(p + "mlp.down_proj", H, cfg.intermediate_size)
     return out
 
 
@@ -162,6 +181,9 @@ class ReferenceModel:
         self.p = prefix
 
         def lin(name: str) -> torch.Tensor:
+            if name + ".weight_scale_inv" not in tensors:      # bf16 linear: the engine quantises it to FP8 blocks on load
+                q, s = fp8fmt.quantize_block128(tensors[name + ".weight"].float(), scale_dtype=torch.float32)
+                return fp8fmt.dequantize_block128(q, s).to(device)
             return fp8fmt.dequantize_block128(tensors[name + ".weight"], tensors[name + ".weight_scale_inv"]).to(device)
 
         def f(name: str) -> torch.Tensor:
@@ -182,6 +204,15 @@ class ReferenceModel:
                 L.update(q=lin(p + "self_attn.q_proj"), k=lin(p + "self_attn.k_proj"), v=lin(p + "self_attn.v_proj"),
                          o=lin(p + "self_attn.o_proj"), qn=f(p + "self_attn.q_norm.weight"), kn=f(p + "self_attn.k_norm.weight"))
             self.layers.append(L)
+        self.mtp = None
+        if "mtp.fc.weight" in tensors:
+            p = "mtp.layers.0."
+            self.mtp = {"kind": "full_attention", "in_norm": f(p + "input_layernorm.weight"), "post_norm": f(p + "post_attention_layernorm.weight"),
+                        "gate": lin(p + "mlp.gate_proj"), "up": lin(p + "mlp.up_proj"), "down": lin(p + "mlp.down_proj"),
+                        "q": lin(p + "self_attn.q_proj"), "k": lin(p + "self_attn.k_proj"), "v": lin(p + "self_attn.v_proj"),
+                        "o": lin(p + "self_attn.o_proj"), "qn": f(p + "self_attn.q_norm.weight"), "kn": f(p + "self_attn.k_norm.weight"),
+                        "norm_e": f("mtp.pre_fc_norm_embedding.weight"), "norm_h": f("mtp.pre_fc_norm_hidden.weight"),
+                        "norm": f("mtp.norm.weight"), "fc": f("mtp.fc.weight")}
         self.reset()
 
     def reset(self) -> None:
@@ -189,6 +220,8 @@ class ReferenceModel:
         KD = c.linear_num_key_heads * c.linear_key_head_dim
         VD = c.linear_num_value_heads * c.linear_value_head_dim
         self.pos = 0
+        self.last_hidden = None          # the last step's hidden after the final norm (input of the predictor)
+        self.mtp_kv = {}                 # position -> (k, v) of the predictor's layer
         self.state = []
         for L in self.layers:
             if L["kind"] == "linear_attention":
@@ -269,7 +302,26 @@ class ReferenceModel:
             mid = r(torch.nn.functional.silu(L["gate"] @ x) * (L["up"] @ x))
             h = r(h + L["down"] @ mid)
         self.pos += 1
-        return self.lm_head @ r(self._rms(h, self.norm))
+        self.last_hidden = r(self._rms(h, self.norm))
+        return self.lm_head @ self.last_hidden
+
+    def mtp_step(self, token: int, hidden: torch.Tensor, pos: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """One predictor row: the token that FOLLOWS position `pos`, the (normalised) hidden of position `pos`; returns
+        (logits for the token after that, the row's output after mtp.norm). Rows at later positions are forgotten first,
+        as a position-indexed cache does. Reference: cpp_engine/src/qwen_engine.cpp:1423-1489."""
+        r, L = self.r, self.mtp
+        x = torch.cat([r(self._rms(self.embed[token], L["norm_e"])), r(self._rms(hidden, L["norm_h"]))])
+        h = r(L["fc"] @ x)
+        self.mtp_kv = {p: kv for p, kv in self.mtp_kv.items() if p < pos}
+        order = sorted(self.mtp_kv)
+        st = {"k": [self.mtp_kv[p][0] for p in order], "v": [self.mtp_kv[p][1] for p in order]}
+        a = self._full_attn(L, st, r(self._rms(h, L["in_norm"])), pos)
+        self.mtp_kv[pos] = (st["k"][-1], st["v"][-1])
+        h = r(h + a)
+        x = r(self._rms(h, L["post_norm"]))
+        h = r(h + L["down"] @ r(torch.nn.functional.silu(L["gate"] @ x) * (L["up"] @ x)))
+        out = r(self._rms(h, L["norm"]))
+        return self.lm_head @ out, out
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int) -> tuple[list[int], list[torch.Tensor]]:
         logits = None
@@ -324,10 +376,11 @@ class QwenEngine:
     """
 
     def __init__(self, cfg: QwenHybridConfig | str, *, tp_rank: int = 0, tp_world: int = 1, device: int = 0,
-                 max_context: int = 4096, prefill_chunk: int = 512, use_cuda_graph: bool = True, decode_splits: int = 0):
+                 max_context: int = 4096, prefill_chunk: int = 512, use_cuda_graph: bool = True, decode_splits: int = 0,
+                 mtp: bool = False):
         self._L = _lib.engine()
         L = self._L
-        L.pk_qwen_create.restype = ctypes.c_void_p
+        L.pk_qwen_create_ex.restype = ctypes.c_void_p
         L.pk_engine_last_error.restype = ctypes.c_char_p
         L.pk_qwen_comm_arena.restype = ctypes.c_void_p
         L.pk_qwen_weight_bytes.restype = ctypes.c_ulonglong
@@ -338,8 +391,9 @@ class QwenEngine:
         self.cfg = cfg
         text = cfg if isinstance(cfg, str) else cfg.to_json()
         self.tp_rank, self.tp_world, self.device = tp_rank, tp_world, device
-        self._h = L.pk_qwen_create(text.encode(), tp_rank, tp_world, device, max_context, prefill_chunk,
-                                   int(use_cuda_graph), decode_splits)
+        self.mtp = bool(mtp)
+        self._h = L.pk_qwen_create_ex(text.encode(), tp_rank, tp_world, device, max_context, prefill_chunk,
+                                      int(use_cuda_graph), decode_splits, int(self.mtp))
         if not self._h:
             raise EngineError(L.pk_engine_last_error().decode())
         self._h = ctypes.c_void_p(self._h)
@@ -387,6 +441,40 @@ class QwenEngine:
         out = (ctypes.c_int * n)()
         self._ck(self._L.pk_qwen_forward_rows(self._h, arr, n, out))
         return list(out)
+
+    # -- multi-token predictor ------------------------------------------------------------
+    def spec_decode(self, steps: int, max_draft: int = 4) -> tuple[list[int], dict[str, int]]:
+        """`decode(steps)` with drafts from the model's own multi-token predictor (engine built with `mtp=True`),
+        verified by the target in one multi-row pass per round: the same tokens, fewer target passes when drafts match.
+        Returns (tokens, counters). Reference behaviour: cpp_engine/src/qwen_engine.cpp:1527-1553, 1646-1726, 2169-2270."""
+        out = (ctypes.c_int * steps)()
+        st = (ctypes.c_longlong * 7)()
+        self._ck(self._L.pk_qwen_spec_decode(self._h, steps, max_draft, out, st))
+        names = ("rounds", "proposed", "accepted", "rollbacks", "replay_tokens", "plain_steps", "predictor_rows")
+        return list(out), dict(zip(names, (int(v) for v in st)))
+
+    @property
+    def mtp_next_token(self) -> int:
+        """The predictor's pick for the token after `last_token` (-1 when it has to be rebuilt first)."""
+        return self._L.pk_qwen_mtp_next_token(self._h)
+
+    def mtp_logits(self) -> torch.Tensor:
+        n = self._L.pk_qwen_vocab_local(self._h)
+        buf = (ctypes.c_float * n)()
+        self._ck(self._L.pk_qwen_copy_mtp_logits(self._h, buf))
+        return torch.tensor(list(buf), dtype=torch.float32)
+
+    def set_draft_replay(self, tokens: Sequence[int]) -> None:
+        """Test hook: take drafts from a known continuation (the tokens after the first generated one); empty clears."""
+        arr = (ctypes.c_int * max(len(tokens), 1))(*[int(t) for t in tokens])
+        self._ck(self._L.pk_qwen_set_draft_replay(self._h, arr, len(tokens)))
+
+    def generate_mtp(self, prompt: Sequence[int], max_new_tokens: int, max_draft: int = 4) -> tuple[list[int], dict[str, int]]:
+        first = self.prefill(prompt)
+        if max_new_tokens <= 1:
+            return [first][:max_new_tokens], {}
+        toks, stats = self.spec_decode(max_new_tokens - 1, max_draft)
+        return [first] + toks, stats
 
     # -- recurrent-state snapshots (speculative decoding, prefix cache) -----------------
     def snapshot(self, with_kv: bool = False) -> "EngineSnapshot":

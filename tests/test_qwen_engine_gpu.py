@@ -224,3 +224,98 @@ def test_prefix_cache_reuses_state_across_requests(tiny):
     assert reused_a2 == 16 and got_a2 == want_a
     cache.clear()
     e.close()
+
+
+@pytest.fixture(scope="module")
+def tiny_mtp(tmp_path_factory):
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=4, hidden=256, inter=512, vocab=1024)
+    out = {}
+    for name, bf16_lin in (("fp8", False), ("bf16", True)):
+        tensors = qh.random_checkpoint(cfg, seed=2, sigma=0.05, mtp=True, mtp_bf16_linears=bf16_lin)
+        d = tmp_path_factory.mktemp("tiny_qwen_mtp_" + name)
+        qh.save_checkpoint(d, cfg, tensors)
+        out[name] = (tensors, d)
+    return cfg, out
+
+
+@pytest.mark.parametrize("variant,n_prompt", [("fp8", 6), ("fp8", 45), ("bf16", 21)])
+def test_mtp_predictor_matches_oracle(tiny_mtp, variant, n_prompt):
+    """After prefill the predictor has seen (hidden of position i, token i + 1) for the whole prompt plus the first
+    generated token; its pick and logits agree with the fp32 definition, on the streaming and the tensor-core path."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, variants = tiny_mtp
+    tensors, d = variants[variant]
+    g = torch.Generator().manual_seed(n_prompt)
+    prompt = torch.randint(0, cfg.vocab_size, (n_prompt,), generator=g).tolist()
+    ref = qh.ReferenceModel(cfg, tensors)
+    hid = []
+    for t in prompt:
+        logits = ref.step(t)
+        hid.append(ref.last_hidden)
+    first = int(logits.argmax())
+    shifted = prompt[1:] + [first]
+    for i, (t, h) in enumerate(zip(shifted, hid)):
+        mlogits, _ = ref.mtp_step(t, h, i)
+    eng = qh.QwenEngine(cfg, max_context=256, prefill_chunk=32, mtp=True).load(d)
+    assert eng.prefill(prompt) == first
+    got = eng.mtp_logits()
+    assert _close(got, mlogits, 5e-2)
+    top2 = mlogits.topk(2).values
+    if (top2[0] - top2[1]).item() > 0.05 * mlogits.abs().max().item():
+        assert eng.mtp_next_token == int(mlogits.argmax())
+    eng.close()
+
+
+def test_mtp_speculative_decode_equals_plain_decode(tiny_mtp):
+    """Same tokens as plain greedy decode, whatever the drafts are worth: with the predictor's own picks, with perfect
+    drafts (every round accepted, draft length doubling), and with drafts that go wrong now and then (rewind + replay)."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, variants = tiny_mtp
+    tensors, d = variants["fp8"]
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab_size, (53,), generator=g).tolist()
+    n = 48
+    eng = qh.QwenEngine(cfg, max_context=256, prefill_chunk=32, mtp=True).load(d)
+    plain = eng.generate(prompt, n)
+    eng.reset()
+    spec, st = eng.generate_mtp(prompt, n, max_draft=4)
+    assert spec == plain
+    assert st["rounds"] >= 1 and st["proposed"] >= st["rounds"] and 0 <= st["accepted"] <= st["proposed"]
+    assert st["accepted"] + st["rounds"] + st["plain_steps"] == n - 1
+    # perfect drafts
+    eng.reset()
+    eng.set_draft_replay(plain[1:])
+    spec, st = eng.generate_mtp(prompt, n, max_draft=4)
+    assert spec == plain
+    assert st["accepted"] == st["proposed"] and st["rollbacks"] == 0
+    assert st["rounds"] <= 14 and st["proposed"] / st["rounds"] > 2.5          # 1, 2, 4, 4, ... drafts per round
+    # drafts with an error every seventh token
+    bad = [t if (i % 7) != 5 else (t + 1) % cfg.vocab_size for i, t in enumerate(plain[1:])]
+    eng.reset()
+    eng.set_draft_replay(bad)
+    spec, st = eng.generate_mtp(prompt, n, max_draft=7)
+    assert spec == plain
+    assert st["rollbacks"] >= 3 and st["replay_tokens"] >= st["rollbacks"] and st["accepted"] < st["proposed"]
+    # plain decode and speculative decode can alternate on one engine
+    eng.set_draft_replay([])
+    eng.reset()
+    first = eng.prefill(prompt)
+    a = eng.decode(5)
+    b, _ = eng.spec_decode(10, 3)
+    c = eng.decode(4)
+    assert [first] + a + b + c == plain[:20]
+    assert eng.comm_status() == 0
+    eng.close()
+
+
+def test_engine_without_predictor_rejects_spec_decode(tiny):
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    eng = qh.QwenEngine(cfg, max_context=128, prefill_chunk=32).load(d)
+    eng.prefill([1, 2, 3])
+    with pytest.raises(qh.EngineError):
+        eng.spec_decode(4)
+    eng.close()
+    with pytest.raises(qh.EngineError):
+        qh.QwenEngine(cfg, max_context=128, prefill_chunk=32, mtp=True).load(d)      # checkpoint has no mtp.* tensors
