@@ -423,10 +423,14 @@ struct StreamKBuffers {
   int ctas = 0;
 };
 
-// Stream-K is opt-in (POCKET_GEMM_STREAMK=1); POCKET_GEMM_NO_STREAMK forces whole tiles either way.
-static bool streamk_enabled() {
-  const char* on = getenv("POCKET_GEMM_STREAMK");
-  return on != nullptr && on[0] == '1' && getenv("POCKET_GEMM_NO_STREAMK") == nullptr;
+// Stream-K mode: 0 = never (POCKET_GEMM_NO_STREAMK, or POCKET_GEMM_STREAMK=0), 2 = whenever the schedule allows it
+// (POCKET_GEMM_STREAMK=1: tests), 1 = only with long k ranges (default). Measured at M = 512 on B200: K = 12288, N = 5120
+// gains 7 % (104 k-steps per CTA group), K = 5120, N = 4096 loses 25 % (35 k-steps per group: the fix-up dominates).
+static int streamk_mode() {
+  if (getenv("POCKET_GEMM_NO_STREAMK") != nullptr) return 0;
+  const char* v = getenv("POCKET_GEMM_STREAMK");
+  if (v == nullptr) return 1;
+  return v[0] == '1' ? 2 : 0;
 }
 
 
@@ -511,7 +515,8 @@ PK_API int pk_gemm_bf16(const void* A, int lda, const void* W, int M, int N, int
   const double eff = rounds / (double)((tiles + sms - 1) / sms);
   p.streamk = 0;
   const int groups = p.tiles_m <= sms ? sms / p.tiles_m : 0;
-  if (eff < 0.88 && groups >= 2 && (long long)p.tiles_n * num_kb >= (long long)groups * 8 && streamk_enabled()) {
+  if (eff < 0.88 && groups >= 2 && (long long)p.tiles_n * num_kb >= (long long)groups * 8 && streamk_mode() != 0 &&
+      (streamk_mode() == 2 || (long long)p.tiles_n * num_kb >= (long long)groups * 96)) {
     StreamKBuffers* b = streamk_buffers(sms);
     if (b != nullptr) {
       p.streamk = 1;

@@ -27,6 +27,7 @@ def main() -> int:
     ap.add_argument("--new", type=int, default=8)
     ap.add_argument("--prefill-chunk", type=int, default=64)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--mtp", type=int, default=0, help="draft length limit; > 0 also runs the speculative decode of the multi-token predictor")
     args = ap.parse_args()
     rank, world, local = tp.env_rank_world()
     torch.cuda.set_device(local)
@@ -34,13 +35,20 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = qh.QwenHybridConfig.from_json((Path(args.ckpt) / "config.json").read_text())
     eng = qh.QwenEngine(cfg, tp_rank=rank, tp_world=world, device=local, max_context=512,
-                        prefill_chunk=args.prefill_chunk, use_cuda_graph=not args.no_graph).load(args.ckpt)
+                        prefill_chunk=args.prefill_chunk, use_cuda_graph=not args.no_graph, mtp=args.mtp > 0).load(args.ckpt)
     tp.connect_engine(eng)
     prompt = [int(t) for t in args.prompt.split(",")]
     tokens = eng.generate(prompt, args.new)
     logits = eng.logits(0)
     out = {"world": world, "tokens": tokens, "comm_status": eng.comm_status(), "timings": eng.timings(),
            "logit_shard_sum": float(logits.double().sum())}
+    if args.mtp > 0:
+        eng.reset()
+        out["spec_tokens"], out["spec_stats"] = eng.generate_mtp(prompt, args.new, args.mtp)
+        eng.reset()
+        eng.set_draft_replay(tokens[1:])
+        out["replay_tokens"], out["replay_stats"] = eng.generate_mtp(prompt, args.new, args.mtp)
+        out["comm_status"] |= eng.comm_status()
     gathered = [None] * world
     if world > 1:
         dist.all_gather_object(gathered, out)
@@ -48,8 +56,11 @@ def main() -> int:
         gathered = [out]
     if rank == 0:
         same = all(g["tokens"] == gathered[0]["tokens"] for g in gathered)
+        extra = {k: gathered[0][k] for k in ("spec_tokens", "spec_stats", "replay_tokens", "replay_stats") if k in gathered[0]}
+        if extra:
+            same = same and all(g["spec_tokens"] == gathered[0]["spec_tokens"] and g["replay_tokens"] == gathered[0]["replay_tokens"] for g in gathered)
         print(json.dumps({"world": world, "tokens": gathered[0]["tokens"], "ranks_agree": same,
-                          "comm_status": [g["comm_status"] for g in gathered], "timings": gathered[0]["timings"]}), flush=True)
+                          "comm_status": [g["comm_status"] for g in gathered], "timings": gathered[0]["timings"], **extra}), flush=True)
     eng.close()
     if world > 1:
         dist.destroy_process_group()

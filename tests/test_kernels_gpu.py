@@ -151,7 +151,11 @@ def test_gemm_bf16_stream_k(M, N, K, epi):
     finally:
         del os.environ["POCKET_GEMM_STREAMK"]
     assert status.item() == 0
-    plain = ops.gemm_bf16(a, w, epi=epi, resid=resid)
+    os.environ["POCKET_GEMM_NO_STREAMK"] = "1"
+    try:
+        plain = ops.gemm_bf16(a, w, epi=epi, resid=resid)
+    finally:
+        del os.environ["POCKET_GEMM_NO_STREAMK"]
     ref = a.float() @ w.float().t()
     if epi == ops.EPI_RESID:
         ref = ref + resid.float()

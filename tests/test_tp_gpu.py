@@ -16,11 +16,11 @@ PROMPT_SHORT = "5,17,300,44,9,1000,2,77,12"
 PROMPT_LONG = ",".join(str((i * 37 + 11) % 1024) for i in range(100))   # 64 + 36 rows: tensor-core prefill
 
 
-def _run(world: int, ckpt: Path, port: int, prompt: str = PROMPT_SHORT) -> dict:
+def _run(world: int, ckpt: Path, port: int, prompt: str = PROMPT_SHORT, extra: tuple = (), new: int = 10) -> dict:
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), "-m", "pocketllm_b200.parallel.tp_check", "--ckpt", str(ckpt), "--prompt",
-           prompt, "--new", "10"]
+           prompt, "--new", str(new), *extra]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
     assert r.returncode == 0, r.stderr[-3000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
@@ -50,3 +50,16 @@ def test_tp2_tensor_core_prefill_matches_tp1(tmp_path):
     # partial sums are added in a different order: allow a late divergence, not an early one
     same = sum(1 for a, b in zip(one["tokens"], two["tokens"]) if a == b)
     assert one["tokens"][:3] == two["tokens"][:3] and same >= 6, (one["tokens"], two["tokens"])
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_mtp_speculative_decode_equals_plain(tmp_path):
+    """The predictor's layer is sharded like the backbone's; drafts come out of the merged candidates, so every rank takes
+    the same accept / rewind decisions and the speculative tokens equal the plain ones."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=4, hidden=256, inter=512, vocab=1024)
+    qh.save_checkpoint(tmp_path, cfg, qh.random_checkpoint(cfg, seed=6, sigma=0.05, mtp=True))
+    two = _run(2, tmp_path, 29535, PROMPT_LONG, extra=("--mtp", "4"), new=24)
+    assert two["ranks_agree"] and two["comm_status"] == [0, 0]
+    assert two["spec_tokens"] == two["tokens"] and two["replay_tokens"] == two["tokens"]
+    assert two["replay_stats"]["accepted"] == two["replay_stats"]["proposed"] > 0 and two["replay_stats"]["rollbacks"] == 0
