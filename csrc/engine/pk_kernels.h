@@ -17,6 +17,8 @@ int pk_matvec(const void* W, const float* scale, const void* Wb, int N, int Nb, 
               const PkWait* wait, int epi, void* y, int ldy, const PkPush* push, int sm_count,
               cudaStream_t stream);
 
+unsigned pk_matvec_ring_status();
+
 int pk_gemm_umma(const void* A, int lda, const void* W, const float* scale, int wfmt, int M, int N, int K,
                  int epi, void* C, const void* resid, int ldc, uint32_t* status, const PkPush* push,
                  cudaStream_t stream);

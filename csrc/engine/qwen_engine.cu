@@ -644,7 +644,8 @@ uint32_t QwenEngine::comm_status() {
   uint32_t v[2] = {0, 0};
   cuda_check(cudaMemcpy(&v[0], (char*)arena_ + off_status_, 4, cudaMemcpyDeviceToHost), "status");
   cuda_check(cudaMemcpy(&v[1], gemm_status_, 4, cudaMemcpyDeviceToHost), "status");
-  return v[0] | (v[1] << 8);
+  // bits 0-7: peer waits, 8-15: tensor-core GEMM waits, 16-23: matvec ring waits
+  return v[0] | (v[1] << 8) | ((pk_matvec_ring_status() & 0xffu) << 16);
 }
 
 void QwenEngine::copy_logits(float* out_host, int row) {

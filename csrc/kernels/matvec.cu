@@ -25,6 +25,7 @@
 
 #include "../common/pk_comm.cuh"
 #include "../common/pk_common.cuh"
+#include "../common/pk_sm100.cuh"
 
 namespace {
 
@@ -60,6 +61,9 @@ struct MatvecParams {
   PkPush push;
   int kc;                // staged chunk length (multiple of 512)
   int single_chunk;
+  // ring variant: byte offsets inside the dynamic shared memory
+  int use_scratch;       // 0: no norm and no partial sums, the activations are staged straight from x_in
+  int acc_off, ring_off, bar_off, scale_off;
 };
 
 // Position (in halves) of element k inside a staged row. Within each run of 512 elements the
@@ -665,6 +669,344 @@ int launch_m(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
   return PK_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Ring variant of the flat path, for FP8 rows and one or two activation rows (decode). Each warp streams its
+// weight bytes through a private shared-memory ring filled by bulk asynchronous copies (cp.async.bulk completing on
+// an mbarrier), so that no registers are tied up by loads in flight and the amount in flight is set by the ring size:
+// 8 KB per warp, 128 KB per SM. The first ring-full is requested before the wait on the previous kernel and before the
+// activations are staged, which keeps HBM busy across the kernel boundary; afterwards the warp's lane 0 refills a slot
+// as soon as the warp has read it. Weight scales of the block's (at most four) 128-row blocks sit in shared memory.
+// bf16 rows that follow the FP8 rows are loaded directly, as in the other paths.
+
+constexpr int kRingSlots = 4;                         // per warp
+constexpr int kSlotIters = 2;                         // k-iterations (512 weights) per slot and row
+constexpr int kRowSlotBytes = kSlotIters * 512;
+constexpr int kSlotBytes = 2 * kRowSlotBytes;         // a row pair
+constexpr int kRingBytes = kWarps * kRingSlots * kSlotBytes;
+constexpr int kRingSmemLimit = 112 * 1024;
+constexpr int kRingMaxPairsPerBlock = 64;             // keeps a block's rows inside two 128-row scale blocks per side
+
+__device__ uint32_t g_matvec_ring_status = 0;         // first mbarrier wait that ran out (0 = none)
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   sm100::smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(sm100::smem_u32(bar))
+               : "memory");
+}
+
+template <int M>
+__global__ void __launch_bounds__(kThreads, 2) matvec_ring_kernel(const MatvecParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);                            // [M][kc]
+  float* scratch = reinterpret_cast<float*>(smem_raw + (size_t)M * p.kc * 2);  // [K] when use_scratch
+  float* s_acc = reinterpret_cast<float*>(smem_raw + p.acc_off);               // [row pairs of the block][2][M]
+  float* s_scale = reinterpret_cast<float*>(smem_raw + p.scale_off);           // [2 sides][2 row blocks][kb_count]
+  __shared__ float red[40];
+  __shared__ float s_c[8];
+  __shared__ uint32_t s_abort;
+  __shared__ int s_edge_g[kWarps][2];
+  __shared__ float s_edge_v[kWarps][2][2 * M];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint8_t* ring = smem_raw + p.ring_off + (size_t)warp * kRingSlots * kSlotBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + p.bar_off) + warp * kRingSlots;
+  const int K = p.K, kc = p.kc;
+  const bool swiglu = p.epi == 1;
+  const int half_n = p.N >> 1;
+  const int total_rows = p.N + p.Nb;
+  const int n_groups = swiglu ? half_n : (total_rows + 1) >> 1;
+  const int kb_count = (K + 127) >> 7;
+  const bool round_x = p.gamma != nullptr;
+  const int iters_all = (K + 511) >> 9;
+  const int g_lo = (int)(((long long)blockIdx.x * n_groups) / gridDim.x);
+  const int g_hi = (int)(((long long)(blockIdx.x + 1) * n_groups) / gridDim.x);
+  const int flat_total = (g_hi - g_lo) * iters_all;
+  const int flat_begin = (int)(((long long)warp * flat_total) / kWarps);
+  const int flat_end = (int)(((long long)(warp + 1) * flat_total) / kWarps);
+  auto row0_of = [&](int g) { return swiglu ? g : 2 * g; };
+  auto row1_of = [&](int g) { return swiglu ? g + half_n : (2 * g + 1 < p.N ? 2 * g + 1 : 2 * g); };   // FP8 pairs only
+  const int rbA = row0_of(g_lo) >> 7, rbB = row1_of(g_lo) >> 7;
+
+  if (tid == 0) s_abort = 0u;
+  if (lane == 0) {
+#pragma unroll
+    for (int s2 = 0; s2 < kRingSlots; ++s2) sm100::mbar_init(&bars[s2], 1);
+    sm100::mbar_fence_init();
+  }
+  __syncwarp();
+
+  // Producer cursor: the next slot to request, in the same order in which the warp will read.
+  int ppos = flat_begin, pk = 0;
+  auto issue_next = [&]() {
+    while (ppos < flat_end) {
+      const int gl = ppos / iters_all, it = ppos - gl * iters_all;
+      const int seg_stop = min(iters_all, it + (flat_end - ppos));
+      const int n_it = min(kSlotIters, seg_stop - it);
+      const int g = g_lo + gl, r0 = row0_of(g);
+      ppos += n_it;
+      if (r0 >= p.N) continue;   // bf16 rows do not go through the ring
+      if (lane == 0) {
+        const int ka = it << 9;
+        const uint32_t bytes = (uint32_t)min(n_it << 9, K - ka);
+        const int slot = pk % kRingSlots;
+        uint8_t* dst = ring + slot * kSlotBytes;
+        sm100::mbar_arrive_expect_tx(&bars[slot], 2 * bytes);
+        bulk_load(dst, p.W + (size_t)r0 * K + ka, bytes, &bars[slot]);
+        bulk_load(dst + kRowSlotBytes, p.W + (size_t)row1_of(g) * K + ka, bytes, &bars[slot]);
+      }
+      ++pk;
+      return;
+    }
+  };
+#pragma unroll 1
+  for (int s2 = 0; s2 < kRingSlots; ++s2) issue_next();
+
+  // Scales of the block's row blocks (weights only, so still ahead of the dependency wait).
+  if (row0_of(g_lo) < p.N) {
+    const int n_rb = (p.N + 127) >> 7;
+    for (int idx = tid; idx < 4 * kb_count; idx += kThreads) {
+      const int q = idx / kb_count, kb = idx - q * kb_count;
+      const int rb = ((q >> 1) ? rbB : rbA) + (q & 1);
+      s_scale[idx] = rb < n_rb ? __ldg(p.scale + (size_t)rb * kb_count + kb) : 0.f;
+    }
+  }
+
+  pdl_wait();
+  pdl_trigger();
+  if (p.parts != nullptr && p.wait.flag != nullptr) {
+    if (tid == 0) wait_all_ranks(p.wait);
+    __syncthreads();
+  }
+
+  // ---- stage the activations ----
+  const int nchunks8 = K >> 3;
+  const bool write_hidden = p.hidden_out != nullptr && blockIdx.x == 0;
+  for (int m = 0; m < M; ++m) {
+    float ss = 0.f, amax = 0.f;
+    __half* row = xs + m * kc;
+    if (p.use_scratch) {
+      for (int c0 = tid; c0 < nchunks8; c0 += kThreads * 4) {
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * kThreads;
+          if (c < nchunks8) load8(p, M, m, c * 8, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * kThreads;
+          if (c >= nchunks8) continue;
+          if (p.parts != nullptr || write_hidden) round_store8(p, m, c * 8, v[u], write_hidden);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += v[u][j] * v[u][j];
+          gamma8(p, c * 8, v[u]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[u][j]));
+          *reinterpret_cast<float4*>(scratch + c * 8) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+          *reinterpret_cast<float4*>(scratch + c * 8 + 4) = make_float4(v[u][4], v[u][5], v[u][6], v[u][7]);
+        }
+      }
+    } else {
+      // plain bf16 input, no norm: the range scale needs the largest magnitude only
+      for (int c = tid; c < nchunks8; c += kThreads) {
+        float v[8];
+        load8(p, M, m, c * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      }
+    }
+    block_sum_max(ss, amax, red);
+    const float rs = p.gamma != nullptr ? rsqrtf(ss / (float)K + p.eps) : 1.f;
+    const float c = pow2_at_least(fmaxf(amax * rs, 1e-30f));
+    if (tid == 0) s_c[m] = c;
+    const float cinv = 1.f / c;
+    for (int c8 = tid; c8 < (kc >> 3); c8 += kThreads) {
+      float t[8];
+      if (c8 < nchunks8) {
+        if (p.use_scratch) {
+          const float4 a = *reinterpret_cast<const float4*>(scratch + c8 * 8);
+          const float4 b = *reinterpret_cast<const float4*>(scratch + c8 * 8 + 4);
+          t[0] = a.x; t[1] = a.y; t[2] = a.z; t[3] = a.w; t[4] = b.x; t[5] = b.y; t[6] = b.z; t[7] = b.w;
+        } else {
+          load8(p, M, m, c8 * 8, t);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = 0.f;
+      }
+      stage8(row, c8 * 8, t, rs, cinv, round_x);
+    }
+    __syncthreads();  // the scratch row is reused by the next m; the staged rows become visible
+  }
+
+  const int ngb = g_hi - g_lo;
+  for (int i = tid; i < ngb * 2 * M; i += kThreads) s_acc[i] = 0.f;
+  if (tid < kWarps * 2) s_edge_g[tid >> 1][tid & 1] = -1;
+  __syncthreads();
+
+  // ---- stream ----
+  int ck = 0;   // FP8 slots read so far
+  int pos = flat_begin;
+  while (pos < flat_end) {
+    const int gl = pos / iters_all, it = pos - gl * iters_all, g = g_lo + gl;
+    const int it_stop = min(iters_all, it + (flat_end - pos));
+    const int r0 = row0_of(g);
+    float a0[M], a1[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) a0[m] = a1[m] = 0.f;
+    if (r0 < p.N) {
+      const float* sc0 = s_scale + ((r0 >> 7) - rbA) * kb_count;
+      const float* sc1 = s_scale + (2 + (row1_of(g) >> 7) - rbB) * kb_count;
+#pragma unroll 1
+      for (int it0 = it; it0 < it_stop; it0 += kSlotIters) {
+        const int n_it = min(kSlotIters, it_stop - it0);
+        const int slot = ck % kRingSlots;
+        if (!sm100::mbar_wait(&bars[slot], (uint32_t)((ck / kRingSlots) & 1), &s_abort, &g_matvec_ring_status, 31u)) break;
+        const uint8_t* sp = ring + slot * kSlotBytes + (lane << 4);
+#pragma unroll
+        for (int u = 0; u < kSlotIters; ++u) {
+          if (u >= n_it) break;
+          const int ka = ((it0 + u) << 9) + (lane << 4);
+          if (ka < K) {
+            const uint4 wa = *reinterpret_cast<const uint4*>(sp + (u << 9));
+            const uint4 wb = *reinterpret_cast<const uint4*>(sp + kRowSlotBytes + (u << 9));
+            const float sa = sc0[ka >> 7], sb = sc1[ka >> 7];
+            const int base = ((it0 + u) << 9) + (lane << 3);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              const uint4 x0 = *reinterpret_cast<const uint4*>(xs + m * kc + base);
+              const uint4 x1 = *reinterpret_cast<const uint4*>(xs + m * kc + base + 256);
+              a0[m] = fmaf(dot16_fp8(wa, x0, x1), sa, a0[m]);
+              a1[m] = fmaf(dot16_fp8(wb, x0, x1), sb, a1[m]);
+            }
+          }
+        }
+        ++ck;
+        __syncwarp();     // every lane has read the slot: it can be refilled
+        issue_next();
+      }
+    } else {
+      const int r1 = 2 * g + 1;
+      const int r1c = r1 < total_rows ? r1 : r0;
+      const bf16* w0p = p.Wb + (size_t)(r0 - p.N) * K;
+      const bf16* w1p = p.Wb + (size_t)(r1c - p.N) * K;
+#pragma unroll 2
+      for (int i2 = it; i2 < it_stop; ++i2) {
+        const int ka = (i2 << 9) + (lane << 4);
+        if (ka < K) {
+          const uint4 w00 = __ldg(reinterpret_cast<const uint4*>(w0p + ka));
+          const uint4 w01 = __ldg(reinterpret_cast<const uint4*>(w0p + ka + 8));
+          const uint4 w10 = __ldg(reinterpret_cast<const uint4*>(w1p + ka));
+          const uint4 w11 = __ldg(reinterpret_cast<const uint4*>(w1p + ka + 8));
+          const int base = (i2 << 9) + (lane << 3);
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            const uint4 x0 = *reinterpret_cast<const uint4*>(xs + m * kc + base);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(xs + m * kc + base + 256);
+            a0[m] += dot16_bf16(w00, w01, x0, x1);
+            a1[m] += dot16_bf16(w10, w11, x0, x1);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      a0[m] = warp_sum(a0[m]);
+      a1[m] = warp_sum(a1[m]);
+    }
+    if (lane == 0) {
+      // One writer for a row pair that lies wholly inside this warp's range; the partial first and last segments go
+      // to the warp's two edge slots and are added in warp order below (the result does not depend on timing).
+      const bool whole = it == 0 && it_stop == iters_all;
+      const int e = pos == flat_begin ? 0 : 1;
+      float* dst0 = whole ? s_acc + (gl * 2) * M : &s_edge_v[warp][e][0];
+      float* dst1 = whole ? s_acc + (gl * 2 + 1) * M : &s_edge_v[warp][e][M];
+      if (!whole) s_edge_g[warp][e] = gl;
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        dst0[m] = a0[m];
+        dst1[m] = a1[m];
+      }
+    }
+    pos += it_stop - it;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < ngb * M; idx += kThreads) {
+    const int gl = idx / M, m = idx - gl * M, g = g_lo + gl;
+    float v0 = s_acc[(gl * 2) * M + m], v1 = s_acc[(gl * 2 + 1) * M + m];
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w)
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        if (s_edge_g[w][e] == gl) {
+          v0 += s_edge_v[w][e][m];
+          v1 += s_edge_v[w][e][M + m];
+        }
+    v0 *= s_c[m];
+    v1 *= s_c[m];
+    if (swiglu) {
+      p.y_bf16[(size_t)m * p.ldy + g] = __float2bfloat16(silu(v0) * v1);
+    } else {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int n = 2 * g + r;
+        if (n >= total_rows) continue;
+        const float v = r == 0 ? v0 : v1;
+        if (p.epi == 0) {
+          p.y_bf16[(size_t)m * p.ldy + n] = __float2bfloat16(v);
+        } else if (p.epi == 2) {
+          p.y_f32[(size_t)m * p.ldy + n] = v;
+        } else {
+          const size_t off = ((size_t)p.push.rank * M + m) * p.ldy + n;
+          for (int pr = 0; pr < p.push.world; ++pr) p.push.dst[pr][off] = v;
+        }
+      }
+    }
+  }
+  if (p.epi == 3) publish_when_grid_done(p.push);
+}
+
+// Ring variant when it applies: FP8 rows present, one or two activation rows, few enough row pairs per block for the
+// scale staging, and everything fits beside a second resident block. Returns -1 when the caller should use the
+// register-streaming kernel.
+template <int M>
+int launch_ring(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
+  if (p.N <= 0 || (((uintptr_t)p.W) & 15) != 0) return -1;
+  const int cap = (sm_count > 0 ? sm_count : 148) * 2;
+  const int blocks = groups < cap ? groups : cap;
+  const int per_block = (groups + blocks - 1) / blocks;
+  if (per_block > kRingMaxPairsPerBlock) return -1;
+  const int kround = (p.K + 511) & ~511;
+  const int kb_count = (p.K + 127) >> 7;
+  p.kc = kround;
+  p.single_chunk = 1;
+  p.flat_path = 1;
+  p.use_scratch = (p.gamma != nullptr || p.parts != nullptr || p.hidden_out != nullptr) ? 1 : 0;
+  size_t off = (size_t)M * kround * 2 + (p.use_scratch ? (size_t)p.K * 4 : 0);
+  off = (off + 127) & ~(size_t)127;
+  p.acc_off = (int)off;
+  off += (size_t)kRingMaxPairsPerBlock * 2 * M * sizeof(float);
+  off = (off + 127) & ~(size_t)127;
+  p.ring_off = (int)off;
+  off += kRingBytes;
+  p.bar_off = (int)off;
+  off += (size_t)kWarps * kRingSlots * sizeof(uint64_t);
+  p.scale_off = (int)off;
+  off += (size_t)4 * kb_count * sizeof(float);
+  if (off > (size_t)kRingSmemLimit) return -1;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(matvec_ring_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmemLimit) != cudaSuccess) {
+      pk_set_last_cuda_error((int)cudaGetLastError());
+      return PK_ERR_CUDA;
+    }
+    configured = true;
+  }
+  PK_LAUNCH_PDL(matvec_ring_kernel<M>, dim3(blocks), dim3(kThreads), off, stream, p);
+  return PK_OK;
+}
+
 unsigned long long* g_matvec_dbg = nullptr;
 }  // namespace
 
@@ -674,6 +1016,19 @@ static bool l2_prefetch_enabled() {
   return on != nullptr && on[0] == '1';
 }
 
+// The ring variant is on by default; POCKET_MATVEC_RING=0 keeps every shape on the register-streaming kernel.
+static bool ring_enabled() {
+  const char* v = getenv("POCKET_MATVEC_RING");
+  return v == nullptr || v[0] != '0';
+}
+
+// First bounded wait of the ring variant that ran out since the last call (0 = none); clears the word.
+PK_API unsigned pk_matvec_ring_status() {
+  unsigned v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_matvec_ring_status, sizeof v) != cudaSuccess) return 0xffffffffu;
+  if (v != 0) cudaMemcpyToSymbol(g_matvec_ring_status, &zero, sizeof zero);
+  return v;
+}
 
 PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, int Nb, int K, int M,
                      const void* x_in, const float* parts, int nparts, void* hidden_out,
@@ -711,6 +1066,10 @@ PK_API int pk_matvec(const void* W, const float* scale, const void* Wb, int N, i
   if (push) p.push = *push;
 
   const int groups = epi == 1 ? N / 2 : (N + Nb + 1) / 2;
+  if (M <= 2 && ring_enabled()) {
+    const int rc = M == 1 ? launch_ring<1>(p, groups, sm_count, stream) : launch_ring<2>(p, groups, sm_count, stream);
+    if (rc >= 0) return rc;
+  }
   switch (M) {
     case 1: return launch_m<1>(p, groups, sm_count, stream);
     case 2: return launch_m<2>(p, groups, sm_count, stream);

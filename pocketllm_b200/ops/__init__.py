@@ -66,6 +66,14 @@ def matvec(x: torch.Tensor, w_fp8: torch.Tensor | None, scale: torch.Tensor | No
     return y
 
 
+def matvec_ring_status() -> int:
+    """First bounded wait of the ring variant of `matvec` that ran out since the last call (0 = none)."""
+    torch.cuda.synchronize()
+    fn = _lib.kernels().pk_matvec_ring_status
+    fn.restype = ctypes.c_uint
+    return int(fn())
+
+
 def gemm_umma(a: torch.Tensor, w: torch.Tensor, scale: torch.Tensor | None = None, *, epi: int = EPI_BF16,
               resid: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
     """tcgen05 GEMM: C = A @ dequant(W)^T with a fused epilogue. A bf16 [M, K]; W fp8 [N, K] with

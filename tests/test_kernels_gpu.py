@@ -69,6 +69,42 @@ def test_matvec_fused_norm_parts_swiglu():
     assert _rel_err(y, ref) < 1e-2
 
 
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("N,Nb,K,epi,norm", [(4096, 0, 5120, 1, True), (2048, 0, 17408, 0, False), (3072, 64, 5120, 0, True),
+                                             (640, 0, 2176, 2, True), (1024, 0, 6144, 0, False), (130, 0, 512, 2, False)])
+def test_matvec_ring_matches_register_path(M, N, Nb, K, epi, norm):
+    """Decode shapes go through the shared-memory ring (bulk asynchronous copies); the sums are taken in the same order
+    as in the register-streaming kernel, so both agree exactly, and with fp32 torch within the FP8 tolerance."""
+    import os
+    from pocketllm_b200 import ops
+    q, s, wd = _fp8_weight(N, K, seed=N + K + epi)
+    wb = (torch.randn(Nb, K, device="cuda") * 0.02).to(torch.bfloat16) if Nb else None
+    x = (torch.randn(M, K, device="cuda") * 0.7).to(torch.bfloat16)
+    kw = {}
+    if norm:
+        kw = dict(gamma=torch.randn(K, device="cuda") * 0.1, parts=torch.randn(2, M, K, device="cuda") * 0.3,
+                  hidden_out=torch.empty(M, K, device="cuda", dtype=torch.bfloat16))
+    y = ops.matvec(x, q, s, wb, epi=epi, **kw)
+    assert ops.matvec_ring_status() == 0
+    os.environ["POCKET_MATVEC_RING"] = "0"
+    try:
+        y0 = ops.matvec(x, q, s, wb, epi=epi, **kw)
+    finally:
+        del os.environ["POCKET_MATVEC_RING"]
+    assert torch.equal(y, y0)
+    h = x.float()
+    if norm:
+        h = (h + kw["parts"].sum(0)).to(torch.bfloat16)
+        assert torch.equal(h, kw["hidden_out"])
+        hf = h.float()
+        h = (hf * torch.rsqrt((hf * hf).mean(-1, keepdim=True) + 1e-6) * (1 + kw["gamma"])).to(torch.bfloat16).float()
+    w_all = wd if wb is None else torch.cat([wd, wb.float()], 0)
+    ref = h @ w_all.t()
+    if epi == 1:
+        ref = torch.nn.functional.silu(ref[:, : N // 2]) * ref[:, N // 2:]
+    assert _rel_err(y, ref) < (1e-2 if epi == 1 else 3e-3)
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (512, 1024, 5120), (200, 384, 256), (64, 256, 2176), (1000, 640, 512)])
 def test_gemm_umma_fp8(M, N, K):
     from pocketllm_b200 import ops
