@@ -21,9 +21,19 @@ def row_bytes(type_name: str, K: int) -> int:
 
 def gguf_linear(x: torch.Tensor, w_raw: torch.Tensor, type_name: str, N: int, *, gamma: torch.Tensor | None = None,
                 eps: float = 1e-6, epi: int = 0) -> torch.Tensor:
-    """y = rmsnorm?(x) @ dequant(W)^T for any number of rows (groups of up to 8 per launch)."""
+    """y = rmsnorm?(x) @ dequant(W)^T for any number of rows.
+
+    Up to `TENSOR_CORE_MIN_ROWS - 1` rows stream the quantised blocks and decode them in registers (groups of up to 8
+    rows per launch). From there on the weight is decoded once into a bf16 scratch and the product runs on the
+    tcgen05 GEMM: one decode instead of one per 8 rows (the reference switches to its prefill kernels for rows > 1,
+    src/components/gguf/quantized_ops.py:9-76)."""
     M, K = x.shape
     ncols = N // 2 if epi == 1 else N
+    if M >= TENSOR_CORE_MIN_ROWS and K % 64 == 0 and (epi != 1 or (N // 2) % 128 == 0):
+        from . import gemm_bf16, rmsnorm, EPI_BF16, EPI_SWIGLU, EPI_F32
+        w = _dequant_scratch(w_raw, type_name, N, K)
+        xin = x.contiguous() if gamma is None else rmsnorm(x.contiguous(), gamma, mode=2, eps=eps)
+        return gemm_bf16(xin, w, epi={0: EPI_BF16, 1: EPI_SWIGLU, 2: EPI_F32}[epi])
     y = torch.empty(M, ncols, device=x.device, dtype=torch.float32 if epi == 2 else torch.bfloat16)
     step = max(1, min(8, (200 * 1024) // (K * 4)))
     step = 8 if step >= 8 else 4 if step >= 4 else 2 if step >= 2 else 1
@@ -34,6 +44,25 @@ def gguf_linear(x: torch.Tensor, w_raw: torch.Tensor, type_name: str, N: int, *,
                                            c_int(_sm_count()), _stream())
         _check(st, "pk_gguf_linear")
     return y
+
+
+TENSOR_CORE_MIN_ROWS = 32
+_scratch: dict = {}
+
+
+def _dequant_scratch(w_raw: torch.Tensor, type_name: str, N: int, K: int) -> torch.Tensor:
+    """bf16 [N, K] copy of a quantised weight in a per-device buffer that the next call reuses (stream ordered)."""
+    key = (w_raw.device.index, torch.cuda.current_stream().cuda_stream)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < N * K:
+        buf = torch.empty(N * K, device=w_raw.device, dtype=torch.bfloat16)
+        _scratch[key] = buf
+    out = buf[: N * K].view(N, K)
+    rb = row_bytes(type_name, K)
+    st = _lib.kernels().pk_gguf_dequant_rows(_ptr(w_raw), c_int(DEVICE_TYPE[type_name]), c_void_p(0), c_int(N), c_int(K), c_int(0),
+                                             c_int(w_raw.numel() // rb), _ptr(out), _stream())
+    _check(st, "pk_gguf_dequant_rows")
+    return out
 
 
 def router_topk(x: torch.Tensor, router_w: torch.Tensor, topk: int, *, bias: torch.Tensor | None = None,

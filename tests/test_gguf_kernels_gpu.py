@@ -45,6 +45,34 @@ def test_gguf_linear_norm_swiglu_and_many_rows():
     assert _rel(y, torch.nn.functional.silu(gu[:, :64]) * gu[:, 64:]) < 1e-2
 
 
+@pytest.mark.parametrize("name,M,N,K,epi", [("q4_k", 64, 384, 768, 2), ("iq2_xxs", 200, 512, 1024, 1), ("q8_0", 33, 96, 512, 0),
+                                             ("q5_k", 130, 256, 2048, 2)])
+def test_gguf_linear_tensor_core_path_for_many_rows(name, M, N, K, epi):
+    """From 32 rows on the weight is decoded once to bf16 and the product runs on the tcgen05 GEMM; it agrees with the
+    8-rows-at-a-time streaming path and with the dequantised fp32 reference."""
+    from pocketllm_b200.ops import gguf_ops as go
+    rng = np.random.default_rng(M + N)
+    raw, wd = _quant((rng.standard_normal((N, K)) * 0.02).astype(np.float32), name)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    gamma = 1 + torch.randn(K, device="cuda") * 0.1
+    assert M >= go.TENSOR_CORE_MIN_ROWS
+    y = go.gguf_linear(x, raw, name, N, gamma=gamma, epi=epi)
+    keep = go.TENSOR_CORE_MIN_ROWS
+    go.TENSOR_CORE_MIN_ROWS = 1 << 30
+    try:
+        y_stream = go.gguf_linear(x, raw, name, N, gamma=gamma, epi=epi)
+    finally:
+        go.TENSOR_CORE_MIN_ROWS = keep
+    xf = x.float()
+    xn = (xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * gamma).to(torch.bfloat16).float()
+    ref = xn @ wd.t()
+    if epi == 1:
+        ref = torch.nn.functional.silu(ref[:, : N // 2]) * ref[:, N // 2:]
+    tol = 1.5e-2 if epi == 1 else 6e-3
+    assert y.shape == y_stream.shape and y.dtype == y_stream.dtype
+    assert _rel(y, ref) < tol and _rel(y, y_stream) < tol
+
+
 @pytest.mark.parametrize("score,norm", [("sigmoid", True), ("softmax", False), ("sqrtsoftplus", True)])
 def test_router_topk(score, norm):
     from pocketllm_b200.ops import gguf_ops as go
