@@ -29,6 +29,7 @@
 #include "qwen_engine.hpp"
 #include "safetensors.hpp"
 #include "tokenizer.hpp"
+#include "weight_source.hpp"
 
 namespace {
 
@@ -44,6 +45,8 @@ struct Args {
   bool serve = false, allow_shutdown = false, list_tensors = false;
   std::string host = "127.0.0.1", sidecar_python = "python", tokenizer = "chars", chat_format = "qwen", model_name = "pocketllm-b200";
   std::string fake_script, inspect_gguf, tokenizer_gguf, tokenize_text, detokenize_ids;
+  std::string weight_source, lookup, dsv4_config;
+  int lookup_layer = -1, lookup_expert = -1;
   bool have_tokenize = false;
   bool fake_engine = false;
   int port = 8000;
@@ -59,6 +62,8 @@ void usage() {
                "  --qwen-mtp [--qwen-mtp-tokens K]   speculative decode with the checkpoint's multi-token predictor\n"
                "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
                "  --tokenizer-gguf FILE --tokenize TEXT | --detokenize 1,2,3\n"
+               "  --dsv4-config DIR|FILE.gguf [--tp-world N]   parse, validate and print a DeepSeek-V4 config\n"
+               "  --weight-source DIR|FILE.gguf [--lookup NAME | --lookup-expert LAYER,EXPERT,w1|w2|w3]   tensor lookup by model name\n"
                "  --serve [--host H --port P --model-name N --tokenizer chars|hf:DIR|gguf:FILE --chat-format qwen|glm|minimax|dsv4\n"
                "           --sidecar-python EXE --fake-engine-script TEXT --allow-shutdown]\n");
 }
@@ -104,6 +109,17 @@ Args parse(int argc, char** argv) {
     else if (f == "--inspect-gguf") a.inspect_gguf = need(i);
     else if (f == "--tensors") a.list_tensors = true;
     else if (f == "--tokenizer-gguf") a.tokenizer_gguf = need(i);
+    else if (f == "--dsv4-config") a.dsv4_config = need(i);
+    else if (f == "--weight-source") a.weight_source = need(i);
+    else if (f == "--lookup") a.lookup = need(i);
+    else if (f == "--lookup-expert") {
+      const std::string v = need(i);
+      const size_t c1 = v.find(','), c2 = v.find(',', c1 == std::string::npos ? 0 : c1 + 1);
+      if (c1 == std::string::npos || c2 == std::string::npos) throw std::runtime_error("--lookup-expert wants LAYER,EXPERT,PART");
+      a.lookup_layer = std::stoi(v.substr(0, c1));
+      a.lookup_expert = std::stoi(v.substr(c1 + 1, c2 - c1 - 1));
+      a.lookup = v.substr(c2 + 1);
+    }
     else if (f == "--tokenize") { a.tokenize_text = need(i); a.have_tokenize = true; }
     else if (f == "--detokenize") a.detokenize_ids = need(i);
     else if (f == "--help" || f == "-h") { usage(); std::exit(0); }
@@ -264,6 +280,42 @@ void print_result(const char* tag, const Args& a, const pk::QwenEngine& eng, siz
   std::fflush(stdout);
 }
 
+void print_view(const pk::TensorView& v) {
+  if (!v.found) {
+    std::printf("tensor=%s found=0\n", v.name.c_str());
+    return;
+  }
+  unsigned long long sum = 0;
+  for (uint64_t i = 0; i < v.nbytes; ++i) sum += v.data[i];
+  std::printf("tensor=%s found=1 stored=%s dtype=%s shape=[", v.name.c_str(), v.stored_name.c_str(), v.dtype.c_str());
+  for (size_t i = 0; i < v.shape.size(); ++i) std::printf(i ? ",%lld" : "%lld", (long long)v.shape[i]);
+  std::printf("] bytes=%llu byte_sum=%llu\n", (unsigned long long)v.nbytes, sum);
+}
+
+int weight_source_tool(const Args& a) {
+  auto src = pk::open_weight_source(a.weight_source);
+  std::printf("format=%s\n", src->format() == pk::WeightSource::Format::Gguf ? "gguf" : "safetensors");
+  if (a.lookup_layer >= 0) print_view(src->expert(a.lookup_layer, a.lookup_expert, a.lookup));
+  else if (!a.lookup.empty()) print_view(src->get(a.lookup));
+  else
+    for (const std::string& n : src->names()) print_view(src->get(n));
+  return 0;
+}
+
+int dsv4_config_tool(const Args& a) {
+  pk::Dsv4Config cfg;
+  if (pk::is_gguf_path(a.dsv4_config)) {
+    pk::GgufFile f(a.dsv4_config);
+    cfg = pk::Dsv4Config::from_gguf(f);
+  } else {
+    const bool is_file = a.dsv4_config.size() > 5 && a.dsv4_config.compare(a.dsv4_config.size() - 5, 5, ".json") == 0;
+    cfg = pk::Dsv4Config::from_file(is_file ? a.dsv4_config : a.dsv4_config + "/config.json");
+  }
+  cfg.validate(a.tp_world);
+  std::printf("%s\n", cfg.to_json().dump().c_str());
+  return 0;
+}
+
 int tokenizer_tool(const Args& a) {
   pk::GgufFile f(a.tokenizer_gguf);
   const pk::BpeTokenizer tok = pk::BpeTokenizer::from_gguf(f);
@@ -280,6 +332,8 @@ int tokenizer_tool(const Args& a) {
 int run(const Args& a) {
   if (!a.tokenizer_gguf.empty() && (a.have_tokenize || !a.detokenize_ids.empty())) return tokenizer_tool(a);
   if (!a.inspect_gguf.empty()) return inspect_gguf(a);
+  if (!a.dsv4_config.empty()) return dsv4_config_tool(a);
+  if (!a.weight_source.empty()) return weight_source_tool(a);
   if (a.serve && a.fake_engine) return serve_scripted(a);
   if (a.inspect) {
     pk::SafetensorsModel st(a.ckpt);
