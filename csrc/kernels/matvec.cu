@@ -678,12 +678,16 @@ int launch_m(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
 // as soon as the warp has read it. Weight scales of the block's (at most four) 128-row blocks sit in shared memory.
 // bf16 rows that follow the FP8 rows are loaded directly, as in the other paths.
 
-constexpr int kRingSlots = 4;                         // per warp
-constexpr int kSlotIters = 2;                         // k-iterations (512 weights) per slot and row
+#ifndef PK_RING_BLOCKS
+#define PK_RING_BLOCKS 3
+#endif
+constexpr int kRingBlocksPerSm = PK_RING_BLOCKS;       // resident blocks per SM the ring variant is sized for
+constexpr int kRingSlots = kRingBlocksPerSm >= 3 ? 2 : 4;   // per warp
+constexpr int kSlotIters = kRingBlocksPerSm >= 4 ? 1 : 2;   // k-iterations (512 weights) per slot and row
 constexpr int kRowSlotBytes = kSlotIters * 512;
 constexpr int kSlotBytes = 2 * kRowSlotBytes;         // a row pair
 constexpr int kRingBytes = kWarps * kRingSlots * kSlotBytes;
-constexpr int kRingSmemLimit = 112 * 1024;
+constexpr int kRingSmemLimit = kRingBlocksPerSm >= 4 ? 55 * 1024 : kRingBlocksPerSm == 3 ? 74 * 1024 : 112 * 1024;
 constexpr int kRingMaxPairsPerBlock = 64;             // keeps a block's rows inside two 128-row scale blocks per side
 
 __device__ uint32_t g_matvec_ring_status = 0;         // first mbarrier wait that ran out (0 = none)
@@ -696,7 +700,7 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
 }
 
 template <int M>
-__global__ void __launch_bounds__(kThreads, 2) matvec_ring_kernel(const MatvecParams p) {
+__global__ void __launch_bounds__(kThreads, kRingBlocksPerSm) matvec_ring_kernel(const MatvecParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __half* xs = reinterpret_cast<__half*>(smem_raw);                            // [M][kc]
   float* scratch = reinterpret_cast<float*>(smem_raw + (size_t)M * p.kc * 2);  // [K] when use_scratch
@@ -973,7 +977,7 @@ __global__ void __launch_bounds__(kThreads, 2) matvec_ring_kernel(const MatvecPa
 template <int M>
 int launch_ring(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
   if (p.N <= 0 || (((uintptr_t)p.W) & 15) != 0) return -1;
-  const int cap = (sm_count > 0 ? sm_count : 148) * 2;
+  const int cap = (sm_count > 0 ? sm_count : 148) * kRingBlocksPerSm;
   const int blocks = groups < cap ? groups : cap;
   const int per_block = (groups + blocks - 1) / blocks;
   if (per_block > kRingMaxPairsPerBlock) return -1;

