@@ -7,6 +7,7 @@
 
 #include "json.hpp"
 #include "gguf_reader.hpp"
+#include "mem_guard.hpp"
 #include "qwen_engine.hpp"
 #include "sampler.hpp"
 #include "tokenizer.hpp"
@@ -30,6 +31,15 @@ int guarded(F&& f) {
   }
 }
 }  // namespace
+
+// Decision of the device-memory floor (POCKET_MIN_FREE_MIB) for given numbers: 0 and an empty message when the request
+// fits, 1 and the refusal text otherwise.
+PK_EAPI int pk_mem_headroom_verdict(unsigned long long free_bytes, unsigned long long total_bytes, unsigned long long request_bytes,
+                                    unsigned long long min_free_bytes, char* msg, int msg_len) {
+  const std::string m = pk::headroom_verdict(free_bytes, total_bytes, request_bytes, min_free_bytes, "request");
+  if (msg && msg_len > 0) std::snprintf(msg, (size_t)msg_len, "%s", m.c_str());
+  return m.empty() ? 0 : 1;
+}
 
 PK_EAPI const char* pk_engine_last_error() { return g_err.c_str(); }
 

@@ -8,6 +8,7 @@
 #include <stdexcept>
 #include <vector>
 
+#include "mem_guard.hpp"
 #include "pk_kernels.h"
 #include "safetensors.hpp"
 
@@ -123,9 +124,11 @@ void QwenEngine::check(int status, const char* what) const {
 
 void* QwenEngine::dalloc(size_t bytes, bool weight) {
   void* p = nullptr;
+  if (bytes >= (size_t(64) << 20)) require_headroom(bytes, weight ? "engine weights" : "engine buffers");
   cuda_check(cudaMalloc(&p, std::max<size_t>(bytes, 16)), "cudaMalloc");
   allocs_.push_back(p);
   if (weight) weight_bytes_ += bytes;
+  alloc_bytes_ += bytes;
   return p;
 }
 
@@ -178,7 +181,9 @@ QwenEngine::QwenEngine(const QwenConfig& cfg, const QwenEngineOptions& opt) : cf
     mtp_norm_ = (float*)dalloc(hidden_ * sizeof(float), true);
     mtp_fc_ = dalloc((size_t)hidden_ * 2 * hidden_ * 2, true);
   }
+  log_device_memory("weights_allocated", alloc_bytes_);
   alloc_buffers();
+  log_device_memory("buffers_allocated", alloc_bytes_);
   reset();
 }
 
@@ -351,6 +356,7 @@ void QwenEngine::build_prefill_shadow() {
   }
   cuda_check(cudaStreamSynchronize(stream_), "prefill shadow");
   shadow_bytes_ = need;
+  log_device_memory("prefill_shadow_built", alloc_bytes_);
 }
 
 void QwenEngine::init_random(uint64_t seed, float sigma) {

@@ -195,6 +195,7 @@ class QwenEngine {
   float* final_norm_ = nullptr;
   void* lm_head_ = nullptr;   // bf16 [vocab_l, hidden]
   size_t weight_bytes_ = 0;
+  size_t alloc_bytes_ = 0;   // everything obtained through dalloc
   size_t shadow_bytes_ = 0;
   std::vector<void*> allocs_;
 

@@ -47,3 +47,23 @@ def test_roofline_arithmetic():
     with t.section("x"):
         pass
     assert t.summary() == {}
+
+
+def test_device_memory_floor_decision():
+    """POCKET_MIN_FREE_MIB: the engine refuses allocations that would leave less than the floor free (pure decision
+    function of the native library, so no GPU is needed)."""
+    import ctypes
+    from pocketllm_b200.ops import lib
+    if not lib.available("engine"):
+        import pytest
+        pytest.skip("libpocket_engine.so not built")
+    L = lib.engine()
+    buf = ctypes.create_string_buffer(400)
+    MiB = 1 << 20
+    fn = L.pk_mem_headroom_verdict
+    fn.argtypes = [ctypes.c_ulonglong] * 4 + [ctypes.c_char_p, ctypes.c_int]
+    assert fn(10000 * MiB, 180000 * MiB, 2000 * MiB, 4096 * MiB, buf, 400) == 0 and buf.value == b""
+    assert fn(10000 * MiB, 180000 * MiB, 7000 * MiB, 4096 * MiB, buf, 400) == 1
+    assert b"POCKET_MIN_FREE_MIB" in buf.value and b"7000.0 MiB" in buf.value and b"3000.0 MiB" in buf.value
+    assert fn(1000 * MiB, 180000 * MiB, 7000 * MiB, 1 * MiB, buf, 400) == 1          # larger than what is free
+    assert fn(1000 * MiB, 180000 * MiB, 7000 * MiB, 0, buf, 400) == 0                # no floor configured: cudaMalloc decides
