@@ -10,6 +10,7 @@
 #include "mem_guard.hpp"
 #include "qwen_engine.hpp"
 #include "sampler.hpp"
+#include "staging.hpp"
 #include "tokenizer.hpp"
 
 #define PK_EAPI extern "C" __attribute__((visibility("default")))
@@ -288,4 +289,64 @@ PK_EAPI const char* pk_tokenizer_decode(void* t, const int* ids, int n, int skip
   thread_local std::string text;
   const int rc = guarded([&] { text = ((pk::BpeTokenizer*)t)->decode(std::vector<int>(ids, ids + n), skip_special != 0); });
   return rc == 0 ? text.c_str() : nullptr;
+}
+
+// ---- host-to-device expert staging -----------------------------------------------------------------------------------
+
+PK_EAPI void* pk_lru_create(int slots) {
+  pk::LruSlotMap* m = nullptr;
+  guarded([&] { m = new pk::LruSlotMap(slots); });
+  return m;
+}
+PK_EAPI void pk_lru_destroy(void* h) { delete (pk::LruSlotMap*)h; }
+// out_slots[n]; load_keys / load_slots receive up to n entries, *n_loads their count; stats = {hits, misses, evictions}.
+PK_EAPI int pk_lru_assign(void* h, const long long* keys, int n, int* out_slots, long long* load_keys, int* load_slots, int* n_loads,
+                          long long* stats) {
+  return guarded([&] {
+    auto* m = (pk::LruSlotMap*)h;
+    std::vector<std::pair<long long, int>> loads;
+    const std::vector<int> slots = m->assign(std::vector<long long>(keys, keys + n), &loads);
+    for (int i = 0; i < n; ++i) out_slots[i] = slots[i];
+    for (size_t i = 0; i < loads.size(); ++i) {
+      load_keys[i] = loads[i].first;
+      load_slots[i] = loads[i].second;
+    }
+    *n_loads = (int)loads.size();
+    if (stats) {
+      stats[0] = m->hits;
+      stats[1] = m->misses;
+      stats[2] = m->evictions;
+    }
+  });
+}
+
+PK_EAPI void* pk_expert_arena_create(int device_slots, unsigned long long expert_bytes, int ring_slots) {
+  pk::ExpertSlotArena* a = nullptr;
+  guarded([&] { a = new pk::ExpertSlotArena(device_slots, (size_t)expert_bytes, ring_slots); });
+  return a;
+}
+PK_EAPI void pk_expert_arena_destroy(void* h) { delete (pk::ExpertSlotArena*)h; }
+PK_EAPI int pk_expert_arena_set_host_store(void* h, const void* base, long long n_experts) {
+  return guarded([&] { ((pk::ExpertSlotArena*)h)->set_host_store(base, n_experts); });
+}
+// stats = {hits, misses, evictions, bytes copied, ring waits}
+PK_EAPI int pk_expert_arena_ensure(void* h, const long long* keys, int n, void** out_ptrs, cudaStream_t stream, long long* stats) {
+  return guarded([&] {
+    auto* a = (pk::ExpertSlotArena*)h;
+    a->ensure(keys, n, out_ptrs, stream);
+    if (stats) {
+      stats[0] = a->map().hits;
+      stats[1] = a->map().misses;
+      stats[2] = a->map().evictions;
+      stats[3] = a->bytes_copied;
+      stats[4] = a->ring().waits;
+    }
+  });
+}
+
+// Synchronous device-to-host copy of raw bytes (tests and tools that hold device addresses returned by this library).
+PK_EAPI int pk_device_read(const void* device_ptr, void* host_out, unsigned long long bytes) {
+  return guarded([&] {
+    if (cudaMemcpy(host_out, device_ptr, (size_t)bytes, cudaMemcpyDeviceToHost) != cudaSuccess) throw std::runtime_error("pk_device_read: copy failed");
+  });
 }
