@@ -30,6 +30,7 @@
 #include "safetensors.hpp"
 #include "tokenizer.hpp"
 #include "weight_source.hpp"
+#include "nccl_comm.hpp"
 
 namespace {
 
@@ -37,7 +38,7 @@ struct Args {
   std::string ckpt, token_ids, token_ids_file, id_path = "/tmp/pocket_engine.rdv";
   int max_new_tokens = 16, tp_world = 1, tp_rank = 0, device = -1, max_context = 4096, prefill_chunk = 512;
   int window = 0, sink = 0;
-  bool mtp = false;
+  bool mtp = false, nccl_smoke = false;
   int mtp_tokens = 4;
   long random_seed = -1;
   bool benchmark_27b = false, dump_config = false, inspect = false, persistent_stdin = false, no_graph = false;
@@ -62,6 +63,7 @@ void usage() {
                "  --qwen-mtp [--qwen-mtp-tokens K]   speculative decode with the checkpoint's multi-token predictor\n"
                "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
                "  --tokenizer-gguf FILE --tokenize TEXT | --detokenize 1,2,3\n"
+               "  --nccl-smoke --tp-world N --tp-rank R [--nccl-id-path PATH]   NCCL baseline path: all-reduce, broadcast, all-gather, top-1\n"
                "  --dsv4-config DIR|FILE.gguf [--tp-world N]   parse, validate and print a DeepSeek-V4 config\n"
                "  --weight-source DIR|FILE.gguf [--lookup NAME | --lookup-expert LAYER,EXPERT,w1|w2|w3]   tensor lookup by model name\n"
                "  --serve [--host H --port P --model-name N --tokenizer chars|hf:DIR|gguf:FILE --chat-format qwen|glm|minimax|dsv4\n"
@@ -89,6 +91,7 @@ Args parse(int argc, char** argv) {
     else if (f == "--prefill-chunk-tokens") a.prefill_chunk = std::stoi(need(i));
     else if (f == "--qwen-attention-window") a.window = std::stoi(need(i));
     else if (f == "--qwen-attention-sink-tokens") a.sink = std::stoi(need(i));
+    else if (f == "--nccl-smoke") a.nccl_smoke = true;
     else if (f == "--qwen-mtp") a.mtp = true;
     else if (f == "--qwen-mtp-tokens") { a.mtp_tokens = std::stoi(need(i)); a.mtp = true; }
     else if (f == "--random-init") a.random_seed = std::stol(need(i));
@@ -316,6 +319,50 @@ int dsv4_config_tool(const Args& a) {
   return 0;
 }
 
+// Sum, broadcast, gather and global top-1 through the NCCL baseline path; every rank prints its verdict.
+int nccl_smoke(const Args& a) {
+  if (!pk::NcclComm::available()) {
+    std::printf("nccl_smoke=1 available=0\n");
+    return 0;
+  }
+  pk::NcclComm comm(a.id_path, a.tp_rank, a.tp_world, a.device);
+  cudaStream_t stream;
+  cudaStreamCreate(&stream);
+  const int n = 4096, W = a.tp_world, R = a.tp_rank;
+  std::vector<float> host(n, (float)(R + 1));
+  float* buf = nullptr;
+  float* all = nullptr;
+  int* tok = nullptr;
+  cudaMalloc((void**)&buf, n * sizeof(float));
+  cudaMalloc((void**)&all, (size_t)n * W * sizeof(float));
+  cudaMalloc((void**)&tok, sizeof(int));
+  cudaMemcpy(buf, host.data(), n * sizeof(float), cudaMemcpyHostToDevice);
+  comm.all_gather(buf, all, n, pk::NcclComm::Dtype::F32, stream);
+  comm.all_reduce_sum(buf, n, pk::NcclComm::Dtype::F32, stream);
+  int t = R == 0 ? 4242 : -1;
+  cudaMemcpy(tok, &t, sizeof(int), cudaMemcpyHostToDevice);
+  comm.broadcast(tok, 1, pk::NcclComm::Dtype::I32, 0, stream);
+  cudaStreamSynchronize(stream);
+  std::vector<float> gathered((size_t)n * W);
+  cudaMemcpy(host.data(), buf, n * sizeof(float), cudaMemcpyDeviceToHost);
+  cudaMemcpy(gathered.data(), all, gathered.size() * sizeof(float), cudaMemcpyDeviceToHost);
+  cudaMemcpy(&t, tok, sizeof(int), cudaMemcpyDeviceToHost);
+  const float want = (float)(W * (W + 1) / 2);
+  bool ok = t == 4242;
+  for (int i = 0; i < n; ++i) ok = ok && host[i] == want;
+  for (int r = 0; r < W; ++r) ok = ok && gathered[(size_t)r * n] == (float)(r + 1) && gathered[(size_t)r * n + n - 1] == (float)(r + 1);
+  // the highest rank holds the best logit; equal logits on the others resolve to the lowest token
+  float best = 0.f;
+  const int top = comm.global_top1(R == W - 1 ? 9.f : 1.f, 1000 + R, stream, &best);
+  ok = ok && top == 1000 + W - 1 && best == 9.f;
+  std::printf("nccl_smoke=1 available=1 tp_world=%d tp_rank=%d ok=%d sum=%.1f broadcast=%d top1=%d\n", W, R, ok ? 1 : 0, host[0], t, top);
+  cudaFree(buf);
+  cudaFree(all);
+  cudaFree(tok);
+  cudaStreamDestroy(stream);
+  return ok ? 0 : 1;
+}
+
 int tokenizer_tool(const Args& a) {
   pk::GgufFile f(a.tokenizer_gguf);
   const pk::BpeTokenizer tok = pk::BpeTokenizer::from_gguf(f);
@@ -332,6 +379,7 @@ int tokenizer_tool(const Args& a) {
 int run(const Args& a) {
   if (!a.tokenizer_gguf.empty() && (a.have_tokenize || !a.detokenize_ids.empty())) return tokenizer_tool(a);
   if (!a.inspect_gguf.empty()) return inspect_gguf(a);
+  if (a.nccl_smoke) return nccl_smoke(a);
   if (!a.dsv4_config.empty()) return dsv4_config_tool(a);
   if (!a.weight_source.empty()) return weight_source_tool(a);
   if (a.serve && a.fake_engine) return serve_scripted(a);

@@ -63,3 +63,28 @@ def test_tp2_mtp_speculative_decode_equals_plain(tmp_path):
     assert two["ranks_agree"] and two["comm_status"] == [0, 0]
     assert two["spec_tokens"] == two["tokens"] and two["replay_tokens"] == two["tokens"]
     assert two["replay_stats"]["accepted"] == two["replay_stats"]["proposed"] > 0 and two["replay_stats"]["rollbacks"] == 0
+
+
+def _nccl_smoke(world: int, tmp_path) -> list[str]:
+    exe = ROOT / "pocketllm_b200" / "_C" / "pocket_engine"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([str(exe), "--nccl-smoke", "--tp-world", str(world), "--tp-rank", str(r), "--nccl-id-path", str(tmp_path / "id")],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env) for r in range(world)]
+    outs = []
+    for p in procs:
+        out, err = p.communicate(timeout=300)
+        assert p.returncode == 0, out + err
+        outs.append([l for l in out.splitlines() if l.startswith("nccl_smoke=1")][-1])
+    return outs
+
+
+def test_native_nccl_baseline_single_rank(tmp_path):
+    """The NCCL path of the native side (library opened at run time): sum, broadcast, gather, global top-1."""
+    (line,) = _nccl_smoke(1, tmp_path)
+    assert "available=1" in line and "ok=1" in line and "sum=1.0" in line and "top1=1000" in line
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_native_nccl_baseline_two_ranks(tmp_path):
+    lines = _nccl_smoke(2, tmp_path)
+    assert all("ok=1" in l and "sum=3.0" in l and "broadcast=4242" in l and "top1=1001" in l for l in lines), lines
