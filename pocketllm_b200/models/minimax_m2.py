@@ -223,6 +223,67 @@ class MiniMaxM2Model:
         self.max_context = max_context
         self.pos = 0
 
+    @classmethod
+    def synthetic(cls, cfg: MiniMaxM2Config, *, device: str = "cuda", rank: int = 0, world: int = 1, max_context: int = 4096,
+                  seed: int = 0, group=None) -> "MiniMaxM2Model":
+        """A model of shape `cfg` whose quantised tensors are random block payloads made on the device (block scales set
+        to a small constant so that every weight is finite): for timing full-size shapes that no file on disk provides.
+        Only block types whose scale is a leading fp16 field are accepted (q4_k, q5_k, q8_0, iq2_xxs, iq2_xs, iq3_xxs)."""
+        from ..ops import gguf_ops as go
+        if cfg.n_experts % world:
+            raise ValueError("expert count must divide by the world size")
+        self = cls.__new__(cls)
+        self.go, self.bundle, self.cfg = go, None, cfg
+        self.device, self.rank, self.world, self.group = torch.device(device), rank, world, group
+        self.e_local = cfg.n_experts // world
+        self.e_start = rank * self.e_local
+        self._combiner = None
+        self.types = {n: t for n, _, t in tensor_plan(cfg)}
+        g = torch.Generator(device=self.device).manual_seed(seed)             # replicated tensors: the same draw on every rank
+        ge = torch.Generator(device=self.device).manual_seed(seed * 1000 + 17 + rank)
+        scale_bytes = torch.tensor([0x00, 0x10], dtype=torch.uint8, device=self.device)   # fp16 2^-11
+        n_scale_fields = {"q4_k": 2, "q5_k": 2, "q8_0": 1, "iq2_xxs": 1, "iq2_xs": 1, "iq3_xxs": 1}
+
+        def blocks(typ: str, rows: int, K: int, gen) -> torch.Tensor:
+            if typ not in n_scale_fields:
+                raise ValueError(f"synthetic blocks of type {typ} are not supported")
+            rb = go.row_bytes(typ, K)
+            per_block = rb * (32 if typ == "q8_0" else 256) // K
+            out = torch.empty(rows * rb, dtype=torch.uint8, device=self.device)
+            step = max(1, (256 << 20) // rb)
+            for r0 in range(0, rows, step):                                        # 256 MB at a time
+                n = min(step, rows - r0) * rb
+                out[r0 * rb: r0 * rb + n] = torch.randint(0, 256, (n,), dtype=torch.uint8, device=self.device, generator=gen)
+            v = out.view(-1, per_block)
+            for f in range(n_scale_fields[typ]):
+                v[:, 2 * f: 2 * f + 2] = scale_bytes
+            return out
+
+        def f32(*shape, mean=0.0, std=0.02) -> torch.Tensor:
+            return mean + std * torch.randn(*shape, device=self.device, generator=g)
+
+        c = cfg
+        D = c.head_dim
+        self.embed = blocks(c.embed_type, c.vocab_size, c.dim, g)
+        self.head = blocks(c.embed_type, c.vocab_size, c.dim, g)
+        self.final_norm = f32(c.dim, mean=1.0, std=0.05)
+        self.layers = []
+        for i in range(c.n_layers):
+            L = {"attn_norm": f32(c.dim, mean=1.0, std=0.05), "ffn_norm": f32(c.dim, mean=1.0, std=0.05),
+                 "q": blocks(c.attn_type, c.n_heads * D, c.dim, g), "k": blocks(c.attn_type, c.n_kv_heads * D, c.dim, g),
+                 "v": blocks(c.attn_type, c.n_kv_heads * D, c.dim, g), "o": blocks(c.attn_type, c.dim, c.n_heads * D, g),
+                 "q_norm": f32(c.n_heads * D, mean=1.0, std=0.05), "k_norm": f32(c.n_kv_heads * D, mean=1.0, std=0.05),
+                 "router": f32(c.n_experts, c.dim), "bias": f32(c.n_experts),
+                 "w13": torch.cat([blocks(c.expert_type, self.e_local * c.expert_inter, c.dim, ge).view(self.e_local, -1),
+                                   blocks(c.expert_type, self.e_local * c.expert_inter, c.dim, ge).view(self.e_local, -1)], dim=1).contiguous(),
+                 "w2": blocks(c.expert_down_type, self.e_local * c.dim, c.expert_inter, ge),
+                 "kc": torch.zeros(c.n_kv_heads, max_context, D, device=self.device, dtype=torch.bfloat16),
+                 "vc": torch.zeros(c.n_kv_heads, max_context, D, device=self.device, dtype=torch.bfloat16)}
+            self.layers.append(L)
+        self.max_context = max_context
+        self.pos = 0
+        return self
+
     def _combine(self, y: torch.Tensor) -> torch.Tensor:
         """Sum the ranks' expert outputs (peer-memory all-reduce for small payloads, NCCL for large ones)."""
         if self._combiner is None:

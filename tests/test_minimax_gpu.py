@@ -35,3 +35,14 @@ def test_generate_cli_runtime(tiny_gguf):
     res = gen.greedy_generate(rt, [1, 2, 3, 4], 6)
     assert len(res.tokens) == 6 and res.prefill_seconds > 0 and res.decode_tps > 0
     assert res.result_line().startswith("RESULT prefill_seconds=")
+
+
+def test_synthetic_full_shape_constructor_runs_small():
+    """Random block payloads made on the device (constant block scales): the model runs and produces finite logits."""
+    from pocketllm_b200.models import minimax_m2 as mm
+    cfg = mm.MiniMaxM2Config(vocab_size=1024, dim=512, n_layers=2, n_heads=8, n_kv_heads=2, n_experts=16, n_experts_used=4, expert_inter=256)
+    m = mm.MiniMaxM2Model.synthetic(cfg, max_context=96)
+    logits = m.forward(torch.arange(40, dtype=torch.int32, device="cuda"))      # 40 rows: tensor-core linears
+    assert logits.shape == (cfg.vocab_size,) and torch.isfinite(logits).all()
+    tok = m.decode_one(int(logits.argmax()))
+    assert 0 <= tok < cfg.vocab_size and m.pos == 41
