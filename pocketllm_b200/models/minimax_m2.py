@@ -13,6 +13,7 @@ attention core on the split-context GQA kernel, experts are partitioned over ran
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Sequence
@@ -113,6 +114,23 @@ def _rope(x: torch.Tensor, pos: torch.Tensor, rope_dim: int, theta: float) -> to
     inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rope_dim)
     ang = pos.double().cpu()[:, None] * inv[None, :]
     cs, sn = torch.cos(ang).float().to(x.device)[:, None, :], torch.sin(ang).float().to(x.device)[:, None, :]
+    x1, x2 = x[..., :half], x[..., half:rope_dim]
+    return torch.cat([x1 * cs - x2 * sn, x2 * cs + x1 * sn, x[..., rope_dim:]], dim=-1)
+
+
+def _rope_tables(max_context: int, rope_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin [max_context, rope_dim / 2] in fp32 from fp64 angles (what `_rope` computes per call on the host)."""
+    half = rope_dim // 2
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rope_dim)
+    ang = torch.arange(max_context, dtype=torch.float64)[:, None] * inv[None, :]
+    return torch.cos(ang).float().to(device), torch.sin(ang).float().to(device)
+
+
+def _rope_lookup(x: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, rope_dim: int) -> torch.Tensor:
+    """`_rope` with the angles taken from device tables: no host round trip, usable under stream capture."""
+    half = rope_dim // 2
+    idx = pos.long()
+    cs, sn = cos_t[idx][:, None, :], sin_t[idx][:, None, :]
     x1, x2 = x[..., :half], x[..., half:rope_dim]
     return torch.cat([x1 * cs - x2 * sn, x2 * cs + x1 * sn, x[..., rope_dim:]], dim=-1)
 
@@ -222,6 +240,7 @@ class MiniMaxM2Model:
             self.layers.append(L)
         self.max_context = max_context
         self.pos = 0
+        self._finish_init()
 
     @classmethod
     def synthetic(cls, cfg: MiniMaxM2Config, *, device: str = "cuda", rank: int = 0, world: int = 1, max_context: int = 4096,
@@ -282,7 +301,15 @@ class MiniMaxM2Model:
             self.layers.append(L)
         self.max_context = max_context
         self.pos = 0
+        self._finish_init()
         return self
+
+    def _finish_init(self) -> None:
+        c = self.cfg
+        self.rope_cos, self.rope_sin = _rope_tables(self.max_context, c.rope_dim, c.rope_theta, self.device)
+        # single-token decode replays one captured CUDA graph (one rank; POCKET_GGUF_DECODE_GRAPH=0 turns it off)
+        self.use_graph = self.world == 1 and self.device.type == "cuda" and os.environ.get("POCKET_GGUF_DECODE_GRAPH", "1") != "0"
+        self._graph = None
 
     def _combine(self, y: torch.Tensor) -> torch.Tensor:
         """Sum the ranks' expert outputs (peer-memory all-reduce for small payloads, NCCL for large ones)."""
@@ -309,6 +336,18 @@ class MiniMaxM2Model:
         if self.pos + T > self.max_context:
             raise ValueError("context exceeds max_context")
         pos = torch.arange(self.pos, self.pos + T, device=self.device, dtype=torch.int32)
+        logits = self._forward_at(tokens, pos)
+        self.pos += T
+        return logits
+
+    @torch.no_grad()
+    def _forward_at(self, tokens: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """The forward pass with the positions given as a device tensor (nothing here depends on host-side position
+        arithmetic, so a single-token call can be captured into a CUDA graph)."""
+        from .. import ops
+        c, go = self.cfg, self.go
+        T = tokens.numel()
+        idx = pos.long()
         h = go.gguf_dequant_rows(self.embed, self.types["token_embd.weight"], c.dim, tokens)
         for i, L in enumerate(self.layers):
             b = f"blk.{i}."
@@ -318,10 +357,10 @@ class MiniMaxM2Model:
             v = go.gguf_linear(h, L["v"], self.types[b + "attn_v.weight"], c.n_kv_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
             q = _rms(q.float(), L["q_norm"], c.norm_eps).view(T, c.n_heads, c.head_dim)
             k = _rms(k.float(), L["k_norm"], c.norm_eps).view(T, c.n_kv_heads, c.head_dim)
-            q = _rope(q, pos, c.rope_dim, c.rope_theta).to(torch.bfloat16).contiguous()
-            k = _rope(k, pos, c.rope_dim, c.rope_theta).to(torch.bfloat16)
-            L["kc"][:, self.pos:self.pos + T] = k.transpose(0, 1)
-            L["vc"][:, self.pos:self.pos + T] = v.view(T, c.n_kv_heads, c.head_dim).transpose(0, 1)
+            q = _rope_lookup(q, pos, self.rope_cos, self.rope_sin, c.rope_dim).to(torch.bfloat16).contiguous()
+            k = _rope_lookup(k, pos, self.rope_cos, self.rope_sin, c.rope_dim).to(torch.bfloat16)
+            L["kc"].index_copy_(1, idx, k.transpose(0, 1).contiguous())
+            L["vc"].index_copy_(1, idx, v.view(T, c.n_kv_heads, c.head_dim).transpose(0, 1).contiguous())
             o = ops.gqa_decode(q, L["kc"], L["vc"], pos, nsplit=1 if T > 8 else 8)
             att = go.gguf_linear(o, L["o"], self.types[b + "attn_output.weight"], c.dim, epi=2)
             h = (h.float() + att).to(torch.bfloat16)
@@ -334,7 +373,6 @@ class MiniMaxM2Model:
             if self.world > 1:
                 self._combine(y)
             h = (h.float() + y).to(torch.bfloat16)
-        self.pos += T
         return go.gguf_linear(h[-1:], self.head, self.types["output.weight"], c.vocab_size, gamma=self.final_norm, eps=c.norm_eps, epi=2)[0]
 
     # protocol of the generic generation runtime
@@ -342,5 +380,32 @@ class MiniMaxM2Model:
         t = torch.tensor(list(tokens), dtype=torch.int32, device=self.device)
         return int(torch.argmax(self.forward(t)))
 
+    @torch.no_grad()
+    def _capture_decode(self) -> None:
+        self._tok_buf = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._pos_buf = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._next_buf = torch.zeros((), dtype=torch.int64, device=self.device)
+        self._pos_buf.fill_(self.pos)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):                       # warm-up outside the capture: lazy kernel attributes, allocator
+            self._forward_at(self._tok_buf, self._pos_buf)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._next_buf.copy_(torch.argmax(self._forward_at(self._tok_buf, self._pos_buf)))
+        self._graph = g
+
     def decode_one(self, token: int) -> int:
-        return int(torch.argmax(self.forward(torch.tensor([token], dtype=torch.int32, device=self.device))))
+        if not self.use_graph:
+            return int(torch.argmax(self.forward(torch.tensor([token], dtype=torch.int32, device=self.device))))
+        if self.pos + 1 > self.max_context:
+            raise ValueError("context exceeds max_context")
+        if self._graph is None:
+            self._capture_decode()
+        self._tok_buf.fill_(int(token))
+        self._pos_buf.fill_(self.pos)
+        self._graph.replay()
+        self.pos += 1
+        return int(self._next_buf)
