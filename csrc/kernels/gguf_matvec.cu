@@ -10,6 +10,8 @@
 // q2_k 1, iq1_m 2, q4_k 3, q5_k 4, iq2_xs 5, iq3_xxs 6, iq4_xs 7, q6_k 8, plus q8_0 9 and
 // bf16 10 here. Replaces its DP4A / float kernels (src/csrc/cuda_kernel_impl.cu:6545-6632,
 // 7039-8275: gguf_quant_gemm*, gguf_moe_w13*, gguf_moe_w2*, gguf_moe_single_*).
+#include <mutex>
+
 #include "../common/pk_common.cuh"
 
 namespace {
@@ -275,6 +277,48 @@ struct MoeParams {
   float* ybuf;          // [R, H] per-route outputs for the fixed-order reduce; null = atomics into y
 };
 
+// Gate/up rows of one expert against MB staged tokens (MB = 1, 2, 4 or 8: a decode step has one token per expert, and
+// decoding a weight once per token slot that is not there would be wasted arithmetic).
+template <int MB>
+__device__ __forceinline__ void moe_w13_rows(const MoeParams& p, const uint8_t* base, size_t rb, const float* xs, int rs, int cnt, int lane,
+                                             int warp) {
+  for (int j = blockIdx.x * kWarps + warp; j < p.I; j += gridDim.x * kWarps) {
+    float g[MB], u[MB];
+#pragma unroll
+    for (int m = 0; m < MB; ++m) { g[m] = 0.f; u[m] = 0.f; }
+    dispatch_row<MB>(p.type13, base + (size_t)j * rb, xs, p.H, lane, g);
+    dispatch_row<MB>(p.type13, base + (size_t)(p.I + j) * rb, xs, p.H, lane, u);
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      float gv = warp_sum(g[m]), uv = warp_sum(u[m]);
+      if (p.limit > 0.f) {
+        gv = fminf(gv, p.limit);
+        uv = fminf(fmaxf(uv, -p.limit), p.limit);
+      }
+      if (lane == 0 && m < cnt) p.hbuf[(size_t)(rs + m) * p.I + j] = silu(gv) * uv * p.route_weight[rs + m];
+    }
+  }
+}
+
+template <int MB>
+__device__ __forceinline__ void moe_w2_rows(const MoeParams& p, const uint8_t* base, size_t rb, const float* hs, int rs, int cnt, int lane,
+                                            int warp) {
+  for (int n = blockIdx.x * kWarps + warp; n < p.H; n += gridDim.x * kWarps) {
+    float a[MB];
+#pragma unroll
+    for (int m = 0; m < MB; ++m) a[m] = 0.f;
+    dispatch_row<MB>(p.type2, base + (size_t)n * rb, hs, p.I, lane, a);
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      const float v = warp_sum(a[m]);
+      if (lane == 0 && m < cnt) {
+        if (p.ybuf != nullptr) p.ybuf[(size_t)(rs + m) * p.H + n] = v;
+        else atomicAdd(p.y + (size_t)p.route_token[rs + m] * p.H + n, v);
+      }
+    }
+  }
+}
+
 // grid: (row tiles, local experts). Each block stages up to 8 routed tokens of its expert at a
 // time and lets its warps walk gate/up row pairs.
 __global__ void __launch_bounds__(kThreads) gguf_moe_w13_kernel(const MoeParams p) {
@@ -288,26 +332,15 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w13_kernel(const MoeParams 
   for (int rs = r0; rs < r1; rs += 8) {
     const int cnt = min(8, r1 - rs);
     __syncthreads();
-    for (int m = 0; m < 8; ++m)
+    const int mb = cnt <= 1 ? 1 : cnt <= 2 ? 2 : cnt <= 4 ? 4 : 8;
+    for (int m = 0; m < mb; ++m)
       for (int k = tid; k < p.H; k += kThreads)
         xs[m * p.H + k] = m < cnt ? __bfloat162float(p.x[(size_t)p.route_token[rs + m] * p.H + k]) : 0.f;
     __syncthreads();
-    for (int j = blockIdx.x * kWarps + warp; j < p.I; j += gridDim.x * kWarps) {
-      float g[8], u[8];
-#pragma unroll
-      for (int m = 0; m < 8; ++m) { g[m] = 0.f; u[m] = 0.f; }
-      dispatch_row<8>(p.type13, base + (size_t)j * rb, xs, p.H, lane, g);
-      dispatch_row<8>(p.type13, base + (size_t)(p.I + j) * rb, xs, p.H, lane, u);
-#pragma unroll
-      for (int m = 0; m < 8; ++m) {
-        float gv = warp_sum(g[m]), uv = warp_sum(u[m]);
-        if (p.limit > 0.f) {
-          gv = fminf(gv, p.limit);
-          uv = fminf(fmaxf(uv, -p.limit), p.limit);
-        }
-        if (lane == 0 && m < cnt) p.hbuf[(size_t)(rs + m) * p.I + j] = silu(gv) * uv * p.route_weight[rs + m];
-      }
-    }
+    if (mb == 1) moe_w13_rows<1>(p, base, rb, xs, rs, cnt, lane, warp);
+    else if (mb == 2) moe_w13_rows<2>(p, base, rb, xs, rs, cnt, lane, warp);
+    else if (mb == 4) moe_w13_rows<4>(p, base, rb, xs, rs, cnt, lane, warp);
+    else moe_w13_rows<8>(p, base, rb, xs, rs, cnt, lane, warp);
   }
 }
 
@@ -322,23 +355,14 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w2_kernel(const MoeParams p
   for (int rs = r0; rs < r1; rs += 8) {
     const int cnt = min(8, r1 - rs);
     __syncthreads();
-    for (int m = 0; m < 8; ++m)
+    const int mb = cnt <= 1 ? 1 : cnt <= 2 ? 2 : cnt <= 4 ? 4 : 8;
+    for (int m = 0; m < mb; ++m)
       for (int k = tid; k < p.I; k += kThreads) hs[m * p.I + k] = m < cnt ? p.hbuf[(size_t)(rs + m) * p.I + k] : 0.f;
     __syncthreads();
-    for (int n = blockIdx.x * kWarps + warp; n < p.H; n += gridDim.x * kWarps) {
-      float a[8];
-#pragma unroll
-      for (int m = 0; m < 8; ++m) a[m] = 0.f;
-      dispatch_row<8>(p.type2, base + (size_t)n * rb, hs, p.I, lane, a);
-#pragma unroll
-      for (int m = 0; m < 8; ++m) {
-        const float v = warp_sum(a[m]);
-        if (lane == 0 && m < cnt) {
-          if (p.ybuf != nullptr) p.ybuf[(size_t)(rs + m) * p.H + n] = v;
-          else atomicAdd(p.y + (size_t)p.route_token[rs + m] * p.H + n, v);
-        }
-      }
-    }
+    if (mb == 1) moe_w2_rows<1>(p, base, rb, hs, rs, cnt, lane, warp);
+    else if (mb == 2) moe_w2_rows<2>(p, base, rb, hs, rs, cnt, lane, warp);
+    else if (mb == 4) moe_w2_rows<4>(p, base, rb, hs, rs, cnt, lane, warp);
+    else moe_w2_rows<8>(p, base, rb, hs, rs, cnt, lane, warp);
   }
 }
 
@@ -363,25 +387,51 @@ __global__ void invert_routes_kernel(const int* __restrict__ route_src, int R, i
 }
 
 // ---- routing ----
-// One block per token: scores over E experts, top-k with lowest-id tie break.
+// Router logits: grid (expert groups of 8, token tiles of up to 8); one warp per expert, which reads its weight row
+// once for the tile's tokens. A single token spreads over E / 8 blocks instead of streaming the whole router matrix
+// through one block.
+__global__ void __launch_bounds__(256) router_logits_kernel(const bf16* x, const float* rw, int H, int E, int T, float* logits) {
+  extern __shared__ float xs[];  // [tokens of the tile][H]
+  const int t0 = blockIdx.y * 8, nt = min(8, T - t0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int m = 0; m < nt; ++m)
+    for (int k = tid; k < H; k += 256) xs[m * H + k] = __bfloat162float(x[(size_t)(t0 + m) * H + k]);
+  __syncthreads();
+  const int e = blockIdx.x * 8 + warp;
+  if (e >= E) return;
+  float a[8];
+#pragma unroll
+  for (int m = 0; m < 8; ++m) a[m] = 0.f;
+  const float* w = rw + (size_t)e * H;
+  if (nt == 1) {
+    for (int k = lane; k < H; k += 32) a[0] = fmaf(w[k], xs[k], a[0]);
+  } else {
+    for (int k = lane; k < H; k += 32) {
+      const float wv = w[k];
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+        if (m < nt) a[m] = fmaf(wv, xs[m * H + k], a[m]);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    if (m >= nt) break;
+    const float v = warp_sum(a[m]);
+    if (lane == 0) logits[(size_t)(t0 + m) * E + e] = v;
+  }
+}
+
+// One block per token: scores from the logits, top-k with lowest-id tie break.
 // score_func 0 softmax, 1 sigmoid, 2 sqrt(softplus); selection on score + bias.
-__global__ void __launch_bounds__(256) router_topk_kernel(const bf16* x, const float* rw, const float* bias, int H, int E,
+__global__ void __launch_bounds__(256) router_topk_kernel(const float* logits, const float* bias, int E,
                                                           int topk, int score_func, int norm_topk, float route_scale,
                                                           int* ids, float* weights) {
-  extern __shared__ float sm[];  // [H] activations, [E] scores, [E] selection keys
-  float* xs = sm;
-  float* sc = sm + H;
+  extern __shared__ float sm[];  // [E] scores, [E] selection keys
+  float* sc = sm;
   float* key = sc + E;
   __shared__ float red[40];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int k = tid; k < H; k += 256) xs[k] = __bfloat162float(x[(size_t)t * H + k]);
-  __syncthreads();
-  for (int e = warp; e < E; e += 8) {
-    float a = 0.f;
-    for (int k = lane; k < H; k += 32) a = fmaf(rw[(size_t)e * H + k], xs[k], a);
-    a = warp_sum(a);
-    if (lane == 0) sc[e] = a;
-  }
+  for (int e = tid; e < E; e += 256) sc[e] = logits[(size_t)t * E + e];
   __syncthreads();
   if (score_func == 0) {
     float mx = -INFINITY;
@@ -535,14 +585,49 @@ PK_API int pk_gguf_linear(const void* W, int type, int N, int K, int M, const vo
   }
 }
 
+// Per-device scratch for the router logits [T, E]; grows on demand (a growth inside a stream capture fails: run one
+// step of the same size before capturing, which callers do anyway to warm the kernels up).
+static float* router_scratch(size_t floats) {
+  static float* buf[64] = {};
+  static size_t cap[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cap[dev] < floats) {
+    float* nb = nullptr;
+    const size_t want = floats < 4096 ? 4096 : floats;
+    if (cudaMalloc((void**)&nb, want * sizeof(float)) != cudaSuccess) return nullptr;
+    // the old buffer may still be in use by kernels in flight: it is left to the process lifetime (sizes settle quickly)
+    buf[dev] = nb;
+    cap[dev] = want;
+  }
+  return buf[dev];
+}
+
 PK_API int pk_router_topk(const void* x, const float* router_w, const float* bias, int T, int H, int E, int topk,
                           int score_func, int norm_topk, float route_scale, int* ids, float* weights,
                           cudaStream_t stream) {
   if (T < 1 || topk < 1 || topk > 32 || topk > E) return PK_ERR_BAD_ARG;
-  const size_t smem = (size_t)(H + 2 * E) * sizeof(float);
-  if (smem > 48 * 1024) return PK_ERR_UNSUPPORTED;
-  router_topk_kernel<<<T, 256, smem, stream>>>((const pk::bf16*)x, router_w, bias, H, E, topk, score_func, norm_topk,
-                                               route_scale, ids, weights);
+  const int tile = T < 8 ? T : 8;
+  const size_t smem_x = (size_t)tile * H * sizeof(float);
+  if (smem_x > 200 * 1024 || (size_t)2 * E * sizeof(float) > 48 * 1024) return PK_ERR_UNSUPPORTED;
+  if (smem_x > 48 * 1024) {
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+        pk_set_last_cuda_error((int)cudaGetLastError());
+        return PK_ERR_CUDA;
+      }
+      configured = true;
+    }
+  }
+  float* logits = router_scratch((size_t)T * E);
+  if (logits == nullptr) return PK_ERR_CUDA;
+  router_logits_kernel<<<dim3((E + 7) / 8, (T + 7) / 8), 256, smem_x, stream>>>((const pk::bf16*)x, router_w, H, E, T, logits);
+  PK_CHECK_LAUNCH();
+  router_topk_kernel<<<T, 256, (size_t)2 * E * sizeof(float), stream>>>(logits, bias, E, topk, score_func, norm_topk, route_scale, ids,
+                                                                        weights);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
