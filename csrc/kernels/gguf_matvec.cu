@@ -260,6 +260,8 @@ __global__ void __launch_bounds__(kThreads) gguf_linear_kernel(const LinearParam
 
 // ---- routed experts ----
 // Routes are sorted by expert: seg_start[e] .. seg_start[e+1] index into route_token / route_weight.
+constexpr int kRouteParallelMax = 64;   // up to this many routes in a step, every route gets its own blocks
+
 struct MoeParams {
   const uint8_t* W13;  // [E, 2I, H] raw rows (gate rows then up rows per expert)
   const uint8_t* W2;   // [E, H, I]
@@ -364,6 +366,46 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w2_kernel(const MoeParams p
     else if (mb == 4) moe_w2_rows<4>(p, base, rb, hs, rs, cnt, lane, warp);
     else moe_w2_rows<8>(p, base, rb, hs, rs, cnt, lane, warp);
   }
+}
+
+// Few routes (decode, speculative verify): grid (row tiles, routes of this rank). Every block serves ONE route, so all
+// blocks have work and an expert's rows spread over as many blocks as there are tiles; the expert of a route comes
+// from a binary search in seg_start.
+__device__ __forceinline__ int expert_of_route(const int* seg_start, int lo_e, int hi_e, int r) {
+  while (hi_e - lo_e > 1) {   // invariant: seg_start[lo_e] <= r < seg_start[hi_e]
+    const int mid = (lo_e + hi_e) >> 1;
+    if (seg_start[mid] <= r) lo_e = mid;
+    else hi_e = mid;
+  }
+  return lo_e;
+}
+
+__global__ void __launch_bounds__(kThreads) gguf_moe_w13_route_kernel(const MoeParams p) {
+  extern __shared__ __align__(16) float xs[];  // [H]
+  const int lo = p.seg_start[p.expert_offset], hi = p.seg_start[p.expert_offset + p.local_experts];
+  const int r = lo + blockIdx.y;
+  if (r >= hi) return;
+  const int e = expert_of_route(p.seg_start, p.expert_offset, p.expert_offset + p.local_experts, r);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t rb = row_bytes(p.type13, p.H);
+  const uint8_t* base = p.W13 + (size_t)(e - p.expert_offset) * 2 * p.I * rb;
+  for (int k = tid; k < p.H; k += kThreads) xs[k] = __bfloat162float(p.x[(size_t)p.route_token[r] * p.H + k]);
+  __syncthreads();
+  moe_w13_rows<1>(p, base, rb, xs, r, 1, lane, warp);
+}
+
+__global__ void __launch_bounds__(kThreads) gguf_moe_w2_route_kernel(const MoeParams p) {
+  extern __shared__ __align__(16) float hs[];  // [I]
+  const int lo = p.seg_start[p.expert_offset], hi = p.seg_start[p.expert_offset + p.local_experts];
+  const int r = lo + blockIdx.y;
+  if (r >= hi) return;
+  const int e = expert_of_route(p.seg_start, p.expert_offset, p.expert_offset + p.local_experts, r);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t rb = row_bytes(p.type2, p.I);
+  const uint8_t* base = p.W2 + (size_t)(e - p.expert_offset) * p.H * rb;
+  for (int k = tid; k < p.I; k += kThreads) hs[k] = p.hbuf[(size_t)r * p.I + k];
+  __syncthreads();
+  moe_w2_rows<1>(p, base, rb, hs, r, 1, lane, warp);
 }
 
 // Fixed-order reduce: y[t] += sum over k = 0..topk-1 of the output of route (t, k), skipping routes whose
@@ -645,7 +687,8 @@ PK_API int pk_group_routes(const int* ids, const float* weights, int T, int topk
 // W13 / W2. y (fp32 [T, H]) must be zeroed by the caller; hbuf holds R * I floats.
 static int moe_forward_impl(const void* W13, const void* W2, int type13, int type2, int E, int H, int I, const void* x,
                             const int* seg_start, const int* route_token, const float* route_weight, float* hbuf, float* y,
-                            float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream);
+                            float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream,
+                            int total_routes = 0);
 
 PK_API int pk_gguf_moe_forward(const void* W13, const void* W2, int type13, int type2, int E, int H, int I,
                                const void* x, const int* seg_start, const int* route_token, const float* route_weight,
@@ -663,10 +706,10 @@ PK_API int pk_gguf_moe_forward_det(const void* W13, const void* W2, int type13, 
                                    float* hbuf, float* ybuf, int* route_pos, float* y, int T, int topk, float limit,
                                    int expert_offset, int local_experts, int sm_count, cudaStream_t stream) {
   if (route_src == nullptr || ybuf == nullptr || route_pos == nullptr || T < 1 || topk < 1) return PK_ERR_BAD_ARG;
-  const int rc = moe_forward_impl(W13, W2, type13, type2, E, H, I, x, seg_start, route_token, route_weight, hbuf, y, limit,
-                                  expert_offset, local_experts, sm_count, ybuf, stream);
-  if (rc != PK_OK) return rc;
   const int R = T * topk;
+  const int rc = moe_forward_impl(W13, W2, type13, type2, E, H, I, x, seg_start, route_token, route_weight, hbuf, y, limit,
+                                  expert_offset, local_experts, sm_count, ybuf, stream, R);
+  if (rc != PK_OK) return rc;
   invert_routes_kernel<<<(R + 255) / 256, 256, 0, stream>>>(route_src, R, route_pos);
   PK_CHECK_LAUNCH();
   moe_reduce_routes_kernel<<<dim3((H + 255) / 256, T), 256, 0, stream>>>(ybuf, route_pos, seg_start, topk, H, expert_offset,
@@ -677,7 +720,8 @@ PK_API int pk_gguf_moe_forward_det(const void* W13, const void* W2, int type13, 
 
 static int moe_forward_impl(const void* W13, const void* W2, int type13, int type2, int E, int H, int I, const void* x,
                             const int* seg_start, const int* route_token, const float* route_weight, float* hbuf, float* y,
-                            float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream) {
+                            float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream,
+                            int total_routes) {
   if ((H & 255) || (I & 255) || local_experts < 1) return PK_ERR_BAD_ARG;
   if ((size_t)8 * H * 4 > 200 * 1024 || (size_t)8 * I * 4 > 200 * 1024) return PK_ERR_UNSUPPORTED;
   MoeParams p{(const uint8_t*)W13, (const uint8_t*)W2, type13, type2, E, H, I, (const pk::bf16*)x, seg_start, route_token,
@@ -691,8 +735,18 @@ static int moe_forward_impl(const void* W13, const void* W2, int type13, int typ
     }
     configured = true;
   }
-  const int tiles13 = min((I + kWarps - 1) / kWarps, 32), tiles2 = min((H + kWarps - 1) / kWarps, 32);
   (void)sm_count;
+  if (total_routes > 0 && total_routes <= kRouteParallelMax) {
+    // one block set per route: at most total_routes of them belong to this rank
+    MoeParams q = p;
+    const int t13 = (I + kWarps - 1) / kWarps, t2 = (H + kWarps - 1) / kWarps;
+    gguf_moe_w13_route_kernel<<<dim3(t13 < 256 ? t13 : 256, total_routes), kThreads, (size_t)H * 4, stream>>>(q);
+    PK_CHECK_LAUNCH();
+    gguf_moe_w2_route_kernel<<<dim3(t2 < 256 ? t2 : 256, total_routes), kThreads, (size_t)I * 4, stream>>>(q);
+    PK_CHECK_LAUNCH();
+    return PK_OK;
+  }
+  const int tiles13 = min((I + kWarps - 1) / kWarps, 32), tiles2 = min((H + kWarps - 1) / kWarps, 32);
   gguf_moe_w13_kernel<<<dim3(tiles13, local_experts), kThreads, (size_t)8 * H * 4, stream>>>(p);
   PK_CHECK_LAUNCH();
   gguf_moe_w2_kernel<<<dim3(tiles2, local_experts), kThreads, (size_t)8 * I * 4, stream>>>(p);
