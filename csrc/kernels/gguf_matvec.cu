@@ -162,20 +162,59 @@ __device__ __forceinline__ void decode8(const uint8_t* b, int p, float (&w)[8]) 
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 
-// One warp: dot products of one raw row with M staged activation rows (fp32, [M][K]).
+// The decoders read single bytes; from global memory that is one load instruction per byte, each a round trip to L2.
+// A warp therefore first brings a stretch of its row into shared memory with 16-byte loads and decodes from there.
+constexpr int kStageBlocks = 8;                                  // 2048 weights per stretch
+constexpr int kStageBytes = kStageBlocks * 512 + 16;             // the largest block type (bf16: 512 B) plus the misalignment
+constexpr int kStageSmem = kWarps * kStageBytes;                 // per thread block
+
+// One warp: dot products of one raw row with M staged activation rows (fp32, [M][K]). `stage` is this warp's
+// kStageBytes of shared memory.
 template <int TYPE, int M>
-__device__ __forceinline__ void row_dot(const uint8_t* wrow, const float* xs, int K, int lane, float (&acc)[M]) {
+__device__ __forceinline__ void row_dot(const uint8_t* wrow, const float* xs, int K, int lane, float (&acc)[M], uint8_t* stage) {
   constexpr int BB = block_bytes(TYPE);
   const int nblk = K >> 8;
-  for (int blk = 0; blk < nblk; ++blk) {
-    float w[8];
-    decode8<TYPE>(wrow + (size_t)blk * BB, lane, w);
-    const int k = (blk << 8) + (lane << 3);
+  if (stage == nullptr) {
+    // Several activation rows share every decoded weight, which hides the byte loads: decode straight from global memory
+    // (and keep the shared memory for a second resident block).
+    for (int blk = 0; blk < nblk; ++blk) {
+      float w[8];
+      decode8<TYPE>(wrow + (size_t)blk * BB, lane, w);
+      const int k = (blk << 8) + (lane << 3);
 #pragma unroll
-    for (int m = 0; m < M; ++m) {
-      const float4 a = *reinterpret_cast<const float4*>(xs + m * K + k);
-      const float4 c = *reinterpret_cast<const float4*>(xs + m * K + k + 4);
-      acc[m] += w[0] * a.x + w[1] * a.y + w[2] * a.z + w[3] * a.w + w[4] * c.x + w[5] * c.y + w[6] * c.z + w[7] * c.w;
+      for (int m = 0; m < M; ++m) {
+        const float4 a = *reinterpret_cast<const float4*>(xs + m * K + k);
+        const float4 c = *reinterpret_cast<const float4*>(xs + m * K + k + 4);
+        acc[m] += w[0] * a.x + w[1] * a.y + w[2] * a.z + w[3] * a.w + w[4] * c.x + w[5] * c.y + w[6] * c.z + w[7] * c.w;
+      }
+    }
+    return;
+  }
+  for (int blk0 = 0; blk0 < nblk; blk0 += kStageBlocks) {
+    const int nb = min(kStageBlocks, nblk - blk0);
+    const uint8_t* src = wrow + (size_t)blk0 * BB;
+    const int mis = (int)((uintptr_t)src & 15);
+    const uint8_t* src_al = src - mis;           // the bytes before `src` belong to the previous row or block of the same tensor
+    const int total = mis + nb * BB;
+    __syncwarp();                                // the previous stretch has been decoded by every lane
+    for (int off = lane << 4; off < total; off += 512) {
+      if (off + 16 <= total) {
+        *reinterpret_cast<uint4*>(stage + off) = __ldg(reinterpret_cast<const uint4*>(src_al + off));
+      } else {
+        for (int i = off < mis ? mis - off : 0; off + i < total; ++i) stage[off + i] = src_al[off + i];   // never past the row's end
+      }
+    }
+    __syncwarp();
+    for (int b = 0; b < nb; ++b) {
+      float w[8];
+      decode8<TYPE>(stage + mis + b * BB, lane, w);
+      const int k = ((blk0 + b) << 8) + (lane << 3);
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const float4 a = *reinterpret_cast<const float4*>(xs + m * K + k);
+        const float4 c = *reinterpret_cast<const float4*>(xs + m * K + k + 4);
+        acc[m] += w[0] * a.x + w[1] * a.y + w[2] * a.z + w[3] * a.w + w[4] * c.x + w[5] * c.y + w[6] * c.z + w[7] * c.w;
+      }
     }
   }
 }
@@ -192,20 +231,20 @@ struct LinearParams {
 };
 
 template <int M>
-__device__ __forceinline__ void dispatch_row(int type, const uint8_t* wrow, const float* xs, int K, int lane, float (&acc)[M]) {
+__device__ __forceinline__ void dispatch_row(int type, const uint8_t* wrow, const float* xs, int K, int lane, float (&acc)[M], uint8_t* stage) {
   switch (type) {
-    case T_IQ2_XXS: row_dot<T_IQ2_XXS, M>(wrow, xs, K, lane, acc); break;
-    case T_Q2_K: row_dot<T_Q2_K, M>(wrow, xs, K, lane, acc); break;
-    case T_IQ1_M: row_dot<T_IQ1_M, M>(wrow, xs, K, lane, acc); break;
-    case T_Q4_K: row_dot<T_Q4_K, M>(wrow, xs, K, lane, acc); break;
-    case T_Q5_K: row_dot<T_Q5_K, M>(wrow, xs, K, lane, acc); break;
-    case T_IQ2_XS: row_dot<T_IQ2_XS, M>(wrow, xs, K, lane, acc); break;
-    case T_IQ3_XXS: row_dot<T_IQ3_XXS, M>(wrow, xs, K, lane, acc); break;
-    case T_IQ4_XS: row_dot<T_IQ4_XS, M>(wrow, xs, K, lane, acc); break;
-    case T_Q6_K: row_dot<T_Q6_K, M>(wrow, xs, K, lane, acc); break;
-    case T_Q8_0: row_dot<T_Q8_0, M>(wrow, xs, K, lane, acc); break;
-    case T_MXFP4: row_dot<T_MXFP4, M>(wrow, xs, K, lane, acc); break;
-    default: row_dot<T_BF16, M>(wrow, xs, K, lane, acc); break;
+    case T_IQ2_XXS: row_dot<T_IQ2_XXS, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_Q2_K: row_dot<T_Q2_K, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_IQ1_M: row_dot<T_IQ1_M, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_Q4_K: row_dot<T_Q4_K, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_Q5_K: row_dot<T_Q5_K, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_IQ2_XS: row_dot<T_IQ2_XS, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_IQ3_XXS: row_dot<T_IQ3_XXS, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_IQ4_XS: row_dot<T_IQ4_XS, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_Q6_K: row_dot<T_Q6_K, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_Q8_0: row_dot<T_Q8_0, M>(wrow, xs, K, lane, acc, stage); break;
+    case T_MXFP4: row_dot<T_MXFP4, M>(wrow, xs, K, lane, acc, stage); break;
+    default: row_dot<T_BF16, M>(wrow, xs, K, lane, acc, stage); break;
   }
 }
 
@@ -215,7 +254,10 @@ template <int M>
 __global__ void __launch_bounds__(kThreads) gguf_linear_kernel(const LinearParams p) {
   extern __shared__ __align__(16) float xs[];  // [M][K]
   __shared__ float red[40];
+  constexpr bool kStaged = M <= 2;     // one or two rows: the byte loads of the decoders dominate, stage the weights
+  __shared__ __align__(16) uint8_t stage_all[kStaged ? kStageSmem : 16];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint8_t* stage = kStaged ? stage_all + warp * kStageBytes : nullptr;
   for (int m = 0; m < M; ++m) {
     float ss = 0.f;
     for (int k = tid; k < p.K; k += kThreads) {
@@ -239,8 +281,8 @@ __global__ void __launch_bounds__(kThreads) gguf_linear_kernel(const LinearParam
     float a0[M], a1[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) { a0[m] = 0.f; a1[m] = 0.f; }
-    dispatch_row<M>(p.type, p.W + (size_t)g * rb, xs, p.K, lane, a0);
-    if (p.epi == 1) dispatch_row<M>(p.type, p.W + (size_t)(g + half_n) * rb, xs, p.K, lane, a1);
+    dispatch_row<M>(p.type, p.W + (size_t)g * rb, xs, p.K, lane, a0, stage);
+    if (p.epi == 1) dispatch_row<M>(p.type, p.W + (size_t)(g + half_n) * rb, xs, p.K, lane, a1, stage);
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       a0[m] = warp_sum(a0[m]);
@@ -283,13 +325,13 @@ struct MoeParams {
 // decoding a weight once per token slot that is not there would be wasted arithmetic).
 template <int MB>
 __device__ __forceinline__ void moe_w13_rows(const MoeParams& p, const uint8_t* base, size_t rb, const float* xs, int rs, int cnt, int lane,
-                                             int warp) {
+                                             int warp, uint8_t* stage) {
   for (int j = blockIdx.x * kWarps + warp; j < p.I; j += gridDim.x * kWarps) {
     float g[MB], u[MB];
 #pragma unroll
     for (int m = 0; m < MB; ++m) { g[m] = 0.f; u[m] = 0.f; }
-    dispatch_row<MB>(p.type13, base + (size_t)j * rb, xs, p.H, lane, g);
-    dispatch_row<MB>(p.type13, base + (size_t)(p.I + j) * rb, xs, p.H, lane, u);
+    dispatch_row<MB>(p.type13, base + (size_t)j * rb, xs, p.H, lane, g, stage);
+    dispatch_row<MB>(p.type13, base + (size_t)(p.I + j) * rb, xs, p.H, lane, u, stage);
 #pragma unroll
     for (int m = 0; m < MB; ++m) {
       float gv = warp_sum(g[m]), uv = warp_sum(u[m]);
@@ -304,12 +346,12 @@ __device__ __forceinline__ void moe_w13_rows(const MoeParams& p, const uint8_t* 
 
 template <int MB>
 __device__ __forceinline__ void moe_w2_rows(const MoeParams& p, const uint8_t* base, size_t rb, const float* hs, int rs, int cnt, int lane,
-                                            int warp) {
+                                            int warp, uint8_t* stage) {
   for (int n = blockIdx.x * kWarps + warp; n < p.H; n += gridDim.x * kWarps) {
     float a[MB];
 #pragma unroll
     for (int m = 0; m < MB; ++m) a[m] = 0.f;
-    dispatch_row<MB>(p.type2, base + (size_t)n * rb, hs, p.I, lane, a);
+    dispatch_row<MB>(p.type2, base + (size_t)n * rb, hs, p.I, lane, a, stage);
 #pragma unroll
     for (int m = 0; m < MB; ++m) {
       const float v = warp_sum(a[m]);
@@ -339,10 +381,10 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w13_kernel(const MoeParams 
       for (int k = tid; k < p.H; k += kThreads)
         xs[m * p.H + k] = m < cnt ? __bfloat162float(p.x[(size_t)p.route_token[rs + m] * p.H + k]) : 0.f;
     __syncthreads();
-    if (mb == 1) moe_w13_rows<1>(p, base, rb, xs, rs, cnt, lane, warp);
-    else if (mb == 2) moe_w13_rows<2>(p, base, rb, xs, rs, cnt, lane, warp);
-    else if (mb == 4) moe_w13_rows<4>(p, base, rb, xs, rs, cnt, lane, warp);
-    else moe_w13_rows<8>(p, base, rb, xs, rs, cnt, lane, warp);
+    if (mb == 1) moe_w13_rows<1>(p, base, rb, xs, rs, cnt, lane, warp, nullptr);
+    else if (mb == 2) moe_w13_rows<2>(p, base, rb, xs, rs, cnt, lane, warp, nullptr);
+    else if (mb == 4) moe_w13_rows<4>(p, base, rb, xs, rs, cnt, lane, warp, nullptr);
+    else moe_w13_rows<8>(p, base, rb, xs, rs, cnt, lane, warp, nullptr);
   }
 }
 
@@ -361,10 +403,10 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w2_kernel(const MoeParams p
     for (int m = 0; m < mb; ++m)
       for (int k = tid; k < p.I; k += kThreads) hs[m * p.I + k] = m < cnt ? p.hbuf[(size_t)(rs + m) * p.I + k] : 0.f;
     __syncthreads();
-    if (mb == 1) moe_w2_rows<1>(p, base, rb, hs, rs, cnt, lane, warp);
-    else if (mb == 2) moe_w2_rows<2>(p, base, rb, hs, rs, cnt, lane, warp);
-    else if (mb == 4) moe_w2_rows<4>(p, base, rb, hs, rs, cnt, lane, warp);
-    else moe_w2_rows<8>(p, base, rb, hs, rs, cnt, lane, warp);
+    if (mb == 1) moe_w2_rows<1>(p, base, rb, hs, rs, cnt, lane, warp, nullptr);
+    else if (mb == 2) moe_w2_rows<2>(p, base, rb, hs, rs, cnt, lane, warp, nullptr);
+    else if (mb == 4) moe_w2_rows<4>(p, base, rb, hs, rs, cnt, lane, warp, nullptr);
+    else moe_w2_rows<8>(p, base, rb, hs, rs, cnt, lane, warp, nullptr);
   }
 }
 
@@ -382,6 +424,7 @@ __device__ __forceinline__ int expert_of_route(const int* seg_start, int lo_e, i
 
 __global__ void __launch_bounds__(kThreads) gguf_moe_w13_route_kernel(const MoeParams p) {
   extern __shared__ __align__(16) float xs[];  // [H]
+  __shared__ __align__(16) uint8_t stage_all[kStageSmem];
   const int lo = p.seg_start[p.expert_offset], hi = p.seg_start[p.expert_offset + p.local_experts];
   const int r = lo + blockIdx.y;
   if (r >= hi) return;
@@ -391,11 +434,12 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w13_route_kernel(const MoeP
   const uint8_t* base = p.W13 + (size_t)(e - p.expert_offset) * 2 * p.I * rb;
   for (int k = tid; k < p.H; k += kThreads) xs[k] = __bfloat162float(p.x[(size_t)p.route_token[r] * p.H + k]);
   __syncthreads();
-  moe_w13_rows<1>(p, base, rb, xs, r, 1, lane, warp);
+  moe_w13_rows<1>(p, base, rb, xs, r, 1, lane, warp, stage_all + warp * kStageBytes);
 }
 
 __global__ void __launch_bounds__(kThreads) gguf_moe_w2_route_kernel(const MoeParams p) {
   extern __shared__ __align__(16) float hs[];  // [I]
+  __shared__ __align__(16) uint8_t stage_all[kStageSmem];
   const int lo = p.seg_start[p.expert_offset], hi = p.seg_start[p.expert_offset + p.local_experts];
   const int r = lo + blockIdx.y;
   if (r >= hi) return;
@@ -405,7 +449,7 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w2_route_kernel(const MoePa
   const uint8_t* base = p.W2 + (size_t)(e - p.expert_offset) * p.H * rb;
   for (int k = tid; k < p.I; k += kThreads) hs[k] = p.hbuf[(size_t)r * p.I + k];
   __syncthreads();
-  moe_w2_rows<1>(p, base, rb, hs, r, 1, lane, warp);
+  moe_w2_rows<1>(p, base, rb, hs, r, 1, lane, warp, stage_all + warp * kStageBytes);
 }
 
 // Fixed-order reduce: y[t] += sum over k = 0..topk-1 of the output of route (t, k), skipping routes whose
@@ -592,13 +636,14 @@ __global__ void __launch_bounds__(256) gguf_dequant_rows_kernel(const uint8_t* W
 template <int M>
 int launch_linear(const LinearParams& p, int sm_count, cudaStream_t stream) {
   const size_t smem = (size_t)M * p.K * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    if (cudaFuncSetAttribute(gguf_linear_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+  // static (the warps' stage buffers) plus dynamic shared memory passes 48 KB already for small K: always opt in
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gguf_linear_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = 200 * 1024;
+    configured = true;
   }
   const int groups = p.epi == 1 ? p.N / 2 : p.N;
   int blocks = (groups + kWarps - 1) / kWarps;
@@ -616,7 +661,7 @@ PK_API int pk_gguf_block_bytes(int type) { return (type >= 0 && type <= T_LAST) 
 PK_API int pk_gguf_linear(const void* W, int type, int N, int K, int M, const void* x, const float* gamma, float eps,
                           int epi, void* y, int ldy, int sm_count, cudaStream_t stream) {
   if (type < 0 || type > T_LAST || M < 1 || M > 8 || (K & 255) != 0 || N < 1) return PK_ERR_BAD_ARG;
-  if ((size_t)M * K * 4 > 200 * 1024) return PK_ERR_UNSUPPORTED;
+  if ((size_t)M * K * 4 > 184 * 1024) return PK_ERR_UNSUPPORTED;   // plus the warps' stage buffers
   if (epi == 1 && (N & 1)) return PK_ERR_BAD_ARG;
   LinearParams p{(const uint8_t*)W, type, N, K, M, (const pk::bf16*)x, gamma, eps, epi, y, ldy};
   switch (M) {
@@ -723,13 +768,15 @@ static int moe_forward_impl(const void* W13, const void* W2, int type13, int typ
                             float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream,
                             int total_routes) {
   if ((H & 255) || (I & 255) || local_experts < 1) return PK_ERR_BAD_ARG;
-  if ((size_t)8 * H * 4 > 200 * 1024 || (size_t)8 * I * 4 > 200 * 1024) return PK_ERR_UNSUPPORTED;
+  if ((size_t)8 * H * 4 > 184 * 1024 || (size_t)8 * I * 4 > 184 * 1024) return PK_ERR_UNSUPPORTED;   // plus the warps' stage buffers
   MoeParams p{(const uint8_t*)W13, (const uint8_t*)W2, type13, type2, E, H, I, (const pk::bf16*)x, seg_start, route_token,
               route_weight, hbuf, y, limit, expert_offset, local_experts, ybuf};
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gguf_moe_w13_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(gguf_moe_w2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gguf_moe_w13_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gguf_moe_w2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gguf_moe_w13_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gguf_moe_w2_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }

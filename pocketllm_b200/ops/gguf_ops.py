@@ -35,7 +35,7 @@ def gguf_linear(x: torch.Tensor, w_raw: torch.Tensor, type_name: str, N: int, *,
         xin = x.contiguous() if gamma is None else rmsnorm(x.contiguous(), gamma, mode=2, eps=eps)
         return gemm_bf16(xin, w, epi={0: EPI_BF16, 1: EPI_SWIGLU, 2: EPI_F32}[epi])
     y = torch.empty(M, ncols, device=x.device, dtype=torch.float32 if epi == 2 else torch.bfloat16)
-    step = max(1, min(8, (200 * 1024) // (K * 4)))
+    step = max(1, min(8, (184 * 1024) // (K * 4)))
     step = 8 if step >= 8 else 4 if step >= 4 else 2 if step >= 2 else 1
     for m0 in range(0, M, step):
         m = min(step, M - m0)
