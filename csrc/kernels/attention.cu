@@ -230,6 +230,76 @@ __global__ void __launch_bounds__(kD) gqa_merge_kernel(const MergeParams p) {
   p.out[((size_t)m * p.Hq + h) * kD + d] = __float2bfloat16(o);
 }
 
+// Whole-vector variant (MiniMax-M2): the RMS statistic runs over all heads of q (or k) together with one gamma per
+// element, the rotation is the half-split form on the first rope_dim dims of every head with angles from tables
+// [ctx, rope_dim / 2], and k / v go to position pos[t] of caches [Hkv, ctx_cap, 128]. Inputs are the bf16 projections.
+struct FullQkParams {
+  const bf16* q;   // [T, Hq * D]
+  const bf16* k;   // [T, Hkv * D]
+  const bf16* v;   // [T, Hkv * D]
+  int Hq, Hkv;
+  const int* pos;
+  const float* q_gamma;
+  const float* k_gamma;
+  float eps;
+  int rope_dim;
+  const float* cos_t;
+  const float* sin_t;
+  bf16* q_out;     // [T, Hq, D]
+  bf16* kcache;
+  bf16* vcache;
+  int ctx_cap;
+};
+
+__global__ void __launch_bounds__(256) full_qk_norm_rope_append_kernel(const FullQkParams p) {
+  __shared__ float red[40];
+  const int t = blockIdx.x, is_k = blockIdx.y, tid = threadIdx.x;
+  const int H = is_k ? p.Hkv : p.Hq, n = H * kD;
+  const bf16* x = (is_k ? p.k : p.q) + (size_t)t * n;
+  const float* gamma = is_k ? p.k_gamma : p.q_gamma;
+  float ss = 0.f;
+  for (int i = tid; i < n; i += 256) {
+    const float v = __bfloat162float(x[i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float rs = rsqrtf(ss / (float)n + p.eps);
+  const int pos = p.pos[t], half = p.rope_dim >> 1;
+  const bool in_cache = pos >= 0 && pos < p.ctx_cap;
+  for (int i = tid; i < n; i += 256) {
+    const int head = i >> 7, d = i & (kD - 1);
+    float y = __bfloat162float(x[i]) * rs * gamma[i];
+    if (d < p.rope_dim) {
+      const int j = d < half ? d : d - half, o = d < half ? i + half : i - half;
+      const float yo = __bfloat162float(x[o]) * rs * gamma[o];
+      const float cs = p.cos_t[(size_t)pos * half + j], sn = p.sin_t[(size_t)pos * half + j];
+      y = d < half ? y * cs - yo * sn : y * cs + yo * sn;
+    }
+    if (!is_k) {
+      p.q_out[((size_t)t * p.Hq + head) * kD + d] = __float2bfloat16(y);
+    } else if (in_cache) {
+      const size_t ci = ((size_t)head * p.ctx_cap + pos) * kD + d;
+      p.kcache[ci] = __float2bfloat16(y);
+      p.vcache[ci] = p.v[(size_t)t * n + i];
+    }
+  }
+}
+
+}  // namespace
+
+PK_API int pk_full_qk_norm_rope_append(const void* q, const void* k, const void* v, int T, int Hq, int Hkv, int head_dim, const int* pos,
+                                       const float* q_gamma, const float* k_gamma, float eps, int rope_dim, const float* cos_t,
+                                       const float* sin_t, void* q_out, void* kcache, void* vcache, int ctx_cap, cudaStream_t stream) {
+  if (head_dim != kD) return PK_ERR_UNSUPPORTED;
+  if (T < 1 || rope_dim < 0 || rope_dim > kD || (rope_dim & 1)) return PK_ERR_BAD_ARG;
+  FullQkParams p{(const pk::bf16*)q, (const pk::bf16*)k, (const pk::bf16*)v, Hq, Hkv, pos, q_gamma, k_gamma, eps, rope_dim, cos_t, sin_t,
+                 (pk::bf16*)q_out, (pk::bf16*)kcache, (pk::bf16*)vcache, ctx_cap};
+  full_qk_norm_rope_append_kernel<<<dim3(T, 2), 256, 0, stream>>>(p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+namespace {
 }  // namespace
 
 PK_API int pk_qk_norm_rope_append(const void* proj, int ld, int M, int Hq, int Hkv, int head_dim,

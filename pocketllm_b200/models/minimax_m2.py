@@ -347,7 +347,6 @@ class MiniMaxM2Model:
         from .. import ops
         c, go = self.cfg, self.go
         T = tokens.numel()
-        idx = pos.long()
         h = go.gguf_dequant_rows(self.embed, self.types["token_embd.weight"], c.dim, tokens)
         for i, L in enumerate(self.layers):
             b = f"blk.{i}."
@@ -355,16 +354,13 @@ class MiniMaxM2Model:
             q = go.gguf_linear(h, L["q"], ta, c.n_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
             k = go.gguf_linear(h, L["k"], self.types[b + "attn_k.weight"], c.n_kv_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
             v = go.gguf_linear(h, L["v"], self.types[b + "attn_v.weight"], c.n_kv_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
-            q = _rms(q.float(), L["q_norm"], c.norm_eps).view(T, c.n_heads, c.head_dim)
-            k = _rms(k.float(), L["k_norm"], c.norm_eps).view(T, c.n_kv_heads, c.head_dim)
-            q = _rope_lookup(q, pos, self.rope_cos, self.rope_sin, c.rope_dim).to(torch.bfloat16).contiguous()
-            k = _rope_lookup(k, pos, self.rope_cos, self.rope_sin, c.rope_dim).to(torch.bfloat16)
-            L["kc"].index_copy_(1, idx, k.transpose(0, 1).contiguous())
-            L["vc"].index_copy_(1, idx, v.view(T, c.n_kv_heads, c.head_dim).transpose(0, 1).contiguous())
+            # whole-vector RMS with per-element gamma, rotation at `pos`, k / v appended to the caches: one kernel
+            q = ops.full_qk_norm_rope_append(q, k, v, pos, L["q_norm"], L["k_norm"], self.rope_cos, self.rope_sin, L["kc"], L["vc"],
+                                             n_heads=c.n_heads, n_kv_heads=c.n_kv_heads, rope_dim=c.rope_dim, eps=c.norm_eps)
             o = ops.gqa_decode(q, L["kc"], L["vc"], pos, nsplit=1 if T > 8 else 8)
             att = go.gguf_linear(o, L["o"], self.types[b + "attn_output.weight"], c.dim, epi=2)
-            h = (h.float() + att).to(torch.bfloat16)
-            xn = _rms(h.float(), L["ffn_norm"], c.norm_eps).to(torch.bfloat16)
+            h = (h + att).to(torch.bfloat16)                     # bf16 + fp32 promotes to fp32: the sum is rounded once
+            xn = ops.rmsnorm(h, L["ffn_norm"], mode=2, eps=c.norm_eps)
             ids, wt = go.router_topk(xn, L["router"], c.n_experts_used, bias=L["bias"], score_func="sigmoid", norm_topk=True)
             routes = go.group_routes(ids, wt, c.n_experts)
             seg, tok, rw = routes
@@ -372,7 +368,7 @@ class MiniMaxM2Model:
                                     c.n_experts, c.expert_inter, seg, tok, rw, expert_offset=self.e_start, local_experts=self.e_local, routes=routes)
             if self.world > 1:
                 self._combine(y)
-            h = (h.float() + y).to(torch.bfloat16)
+            h = (h + y).to(torch.bfloat16)
         return go.gguf_linear(h[-1:], self.head, self.types["output.weight"], c.vocab_size, gamma=self.final_norm, eps=c.norm_eps, epi=2)[0]
 
     # protocol of the generic generation runtime

@@ -360,3 +360,29 @@ def test_gqa_append_and_decode(M, ctx, Hq, Hkv, nsplit):
         sc = torch.einsum("hd,htd->ht", q[m].float(), K) * D ** -0.5
         o = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), V) * torch.sigmoid(gate)
         assert _rel_err(out[m].view(Hq, D), o) < 1e-2
+
+
+def test_full_qk_norm_rope_append_matches_torch():
+    """Whole-vector RMS (one gamma per element) + half-split rotation from tables + KV append, against plain PyTorch."""
+    from pocketllm_b200 import ops
+    from pocketllm_b200.models.minimax_m2 import _rms, _rope, _rope_tables
+    torch.manual_seed(0)
+    T, Hq, Hkv, D, rope_dim, ctx = 5, 6, 2, 128, 64, 40
+    q = torch.randn(T, Hq * D, device="cuda").to(torch.bfloat16)
+    k = torch.randn(T, Hkv * D, device="cuda").to(torch.bfloat16)
+    v = torch.randn(T, Hkv * D, device="cuda").to(torch.bfloat16)
+    gq, gk = 1 + torch.randn(Hq * D, device="cuda") * 0.1, 1 + torch.randn(Hkv * D, device="cuda") * 0.1
+    pos = torch.tensor([3, 4, 5, 17, 39], device="cuda", dtype=torch.int32)
+    cos_t, sin_t = _rope_tables(ctx, rope_dim, 5e6, "cuda")
+    kc = torch.zeros(Hkv, ctx, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    out = ops.full_qk_norm_rope_append(q, k, v, pos, gq, gk, cos_t, sin_t, kc, vc, n_heads=Hq, n_kv_heads=Hkv, rope_dim=rope_dim, eps=1e-6)
+    want_q = _rope(_rms(q.float(), gq, 1e-6).view(T, Hq, D), pos, rope_dim, 5e6).to(torch.bfloat16)
+    want_k = _rope(_rms(k.float(), gk, 1e-6).view(T, Hkv, D), pos, rope_dim, 5e6).to(torch.bfloat16)
+    assert _rel_err(out, want_q) < 4e-3 and (out.float() - want_q.float()).abs().max() < 0.05
+    idx = pos.long()
+    assert _rel_err(kc[:, idx], want_k.transpose(0, 1)) < 4e-3
+    assert torch.equal(vc[:, idx], v.view(T, Hkv, D).transpose(0, 1))
+    untouched = torch.ones(ctx, dtype=torch.bool, device="cuda")
+    untouched[idx] = False
+    assert kc[:, untouched].abs().sum() == 0 and vc[:, untouched].abs().sum() == 0
