@@ -234,9 +234,10 @@ __global__ void __launch_bounds__(kD) gqa_merge_kernel(const MergeParams p) {
 // element, the rotation is the half-split form on the first rope_dim dims of every head with angles from tables
 // [ctx, rope_dim / 2], and k / v go to position pos[t] of caches [Hkv, ctx_cap, 128]. Inputs are the bf16 projections.
 struct FullQkParams {
-  const bf16* q;   // [T, Hq * D]
-  const bf16* k;   // [T, Hkv * D]
-  const bf16* v;   // [T, Hkv * D]
+  const bf16* q;   // [T, Hq * D], row stride ldq
+  const bf16* k;   // [T, Hkv * D], row stride ldk
+  const bf16* v;   // [T, Hkv * D], row stride ldv
+  int ldq, ldk, ldv;
   int Hq, Hkv;
   const int* pos;
   const float* q_gamma;
@@ -255,7 +256,7 @@ __global__ void __launch_bounds__(256) full_qk_norm_rope_append_kernel(const Ful
   __shared__ float red[40];
   const int t = blockIdx.x, is_k = blockIdx.y, tid = threadIdx.x;
   const int H = is_k ? p.Hkv : p.Hq, n = H * kD;
-  const bf16* x = (is_k ? p.k : p.q) + (size_t)t * n;
+  const bf16* x = is_k ? p.k + (size_t)t * p.ldk : p.q + (size_t)t * p.ldq;
   const float* gamma = is_k ? p.k_gamma : p.q_gamma;
   float ss = 0.f;
   for (int i = tid; i < n; i += 256) {
@@ -280,19 +281,20 @@ __global__ void __launch_bounds__(256) full_qk_norm_rope_append_kernel(const Ful
     } else if (in_cache) {
       const size_t ci = ((size_t)head * p.ctx_cap + pos) * kD + d;
       p.kcache[ci] = __float2bfloat16(y);
-      p.vcache[ci] = p.v[(size_t)t * n + i];
+      p.vcache[ci] = p.v[(size_t)t * p.ldv + i];
     }
   }
 }
 
 }  // namespace
 
-PK_API int pk_full_qk_norm_rope_append(const void* q, const void* k, const void* v, int T, int Hq, int Hkv, int head_dim, const int* pos,
+PK_API int pk_full_qk_norm_rope_append(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, int T, int Hq, int Hkv,
+                                       int head_dim, const int* pos,
                                        const float* q_gamma, const float* k_gamma, float eps, int rope_dim, const float* cos_t,
                                        const float* sin_t, void* q_out, void* kcache, void* vcache, int ctx_cap, cudaStream_t stream) {
   if (head_dim != kD) return PK_ERR_UNSUPPORTED;
   if (T < 1 || rope_dim < 0 || rope_dim > kD || (rope_dim & 1)) return PK_ERR_BAD_ARG;
-  FullQkParams p{(const pk::bf16*)q, (const pk::bf16*)k, (const pk::bf16*)v, Hq, Hkv, pos, q_gamma, k_gamma, eps, rope_dim, cos_t, sin_t,
+  FullQkParams p{(const pk::bf16*)q, (const pk::bf16*)k, (const pk::bf16*)v, ldq, ldk, ldv, Hq, Hkv, pos, q_gamma, k_gamma, eps, rope_dim, cos_t, sin_t,
                  (pk::bf16*)q_out, (pk::bf16*)kcache, (pk::bf16*)vcache, ctx_cap};
   full_qk_norm_rope_append_kernel<<<dim3(T, 2), 256, 0, stream>>>(p);
   PK_CHECK_LAUNCH();

@@ -306,6 +306,10 @@ class MiniMaxM2Model:
 
     def _finish_init(self) -> None:
         c = self.cfg
+        for i, L in enumerate(self.layers):
+            b = f"blk.{i}."
+            if self.types[b + "attn_q.weight"] == self.types[b + "attn_k.weight"] == self.types[b + "attn_v.weight"]:
+                L["qkv"] = torch.cat([L.pop("q"), L.pop("k"), L.pop("v")])       # raw rows are contiguous per tensor: row-wise concat
         self.rope_cos, self.rope_sin = _rope_tables(self.max_context, c.rope_dim, c.rope_theta, self.device)
         # single-token decode replays one captured CUDA graph (one rank; POCKET_GGUF_DECODE_GRAPH=0 turns it off)
         self.use_graph = self.world == 1 and self.device.type == "cuda" and os.environ.get("POCKET_GGUF_DECODE_GRAPH", "1") != "0"
@@ -324,7 +328,7 @@ class MiniMaxM2Model:
     def weight_bytes(self) -> int:
         n = self.embed.numel() + self.head.numel()
         for L in self.layers:
-            n += sum(L[k].numel() * L[k].element_size() for k in ("q", "k", "v", "o", "w13", "w2", "router"))
+            n += sum(L[k].numel() * L[k].element_size() for k in ("q", "k", "v", "qkv", "o", "w13", "w2", "router") if k in L)
         return n
 
     @torch.no_grad()
@@ -351,9 +355,14 @@ class MiniMaxM2Model:
         for i, L in enumerate(self.layers):
             b = f"blk.{i}."
             ta = self.types[b + "attn_q.weight"]
-            q = go.gguf_linear(h, L["q"], ta, c.n_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
-            k = go.gguf_linear(h, L["k"], self.types[b + "attn_k.weight"], c.n_kv_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
-            v = go.gguf_linear(h, L["v"], self.types[b + "attn_v.weight"], c.n_kv_heads * c.head_dim, gamma=L["attn_norm"], eps=c.norm_eps)
+            nq, nkv = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
+            if "qkv" in L:                                       # one projection for q, k and v (same block type): rows q | k | v
+                qkv = go.gguf_linear(h, L["qkv"], ta, nq + 2 * nkv, gamma=L["attn_norm"], eps=c.norm_eps)
+                q, k, v = qkv[:, :nq], qkv[:, nq:nq + nkv], qkv[:, nq + nkv:]
+            else:
+                q = go.gguf_linear(h, L["q"], ta, nq, gamma=L["attn_norm"], eps=c.norm_eps)
+                k = go.gguf_linear(h, L["k"], self.types[b + "attn_k.weight"], nkv, gamma=L["attn_norm"], eps=c.norm_eps)
+                v = go.gguf_linear(h, L["v"], self.types[b + "attn_v.weight"], nkv, gamma=L["attn_norm"], eps=c.norm_eps)
             # whole-vector RMS with per-element gamma, rotation at `pos`, k / v appended to the caches: one kernel
             q = ops.full_qk_norm_rope_append(q, k, v, pos, L["q_norm"], L["k_norm"], self.rope_cos, self.rope_sin, L["kc"], L["vc"],
                                              n_heads=c.n_heads, n_kv_heads=c.n_kv_heads, rope_dim=c.rope_dim, eps=c.norm_eps)

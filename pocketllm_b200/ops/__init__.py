@@ -167,12 +167,13 @@ def gqa_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos:
 def full_qk_norm_rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: torch.Tensor, q_gamma: torch.Tensor, k_gamma: torch.Tensor,
                              cos_t: torch.Tensor, sin_t: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, *, n_heads: int, n_kv_heads: int,
                              rope_dim: int, eps: float = 1e-6) -> torch.Tensor:
-    """bf16 projections q [T, Hq * 128], k / v [T, Hkv * 128] -> RMS over the whole vector with per-element gamma, half-split
+    """bf16 projections q [T, Hq * 128], k / v [T, Hkv * 128] (rows may be strided views of one fused projection) -> RMS over the whole vector with per-element gamma, half-split
     rotation at `pos` (tables [ctx, rope_dim / 2]), k and v written to the caches [Hkv, ctx, 128]; returns bf16 q [T, Hq, 128]."""
     T = q.shape[0]
     out = torch.empty(T, n_heads, 128, device=q.device, dtype=torch.bfloat16)
     st = _lib.kernels().pk_full_qk_norm_rope_append(
-        _ptr(q), _ptr(k), _ptr(v), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(128), _ptr(pos), _ptr(q_gamma), _ptr(k_gamma),
+        _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), _ptr(v), c_int(v.stride(0)), c_int(T), c_int(n_heads), c_int(n_kv_heads),
+        c_int(128), _ptr(pos), _ptr(q_gamma), _ptr(k_gamma),
         c_float(eps), c_int(rope_dim), _ptr(cos_t), _ptr(sin_t), _ptr(out), _ptr(kcache), _ptr(vcache), c_int(kcache.shape[1]), _stream())
     _check(st, "pk_full_qk_norm_rope_append")
     return out
