@@ -151,7 +151,7 @@ def rope_interleaved(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.
     """Rotate pairs (2i, 2i+1) of the last dim. x [T, ..., R], pos [T]."""
     R = x.shape[-1]
     inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -torch.arange(0, R, 2, dtype=torch.float64) / R)
-    ang = pos.double().cpu()[:, None] * inv[None, :]
+    ang = pos.double()[:, None] * inv.to(pos.device)[None, :]          # fp64 angles where `pos` lives: no host round trip
     shape = [x.shape[0]] + [1] * (x.dim() - 2) + [R // 2]
     cs, sn = torch.cos(ang).float().to(x.device).view(shape), torch.sin(ang).float().to(x.device).view(shape)
     x0, x1 = x[..., 0::2], x[..., 1::2]
