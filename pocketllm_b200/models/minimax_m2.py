@@ -311,8 +311,11 @@ class MiniMaxM2Model:
             if self.types[b + "attn_q.weight"] == self.types[b + "attn_k.weight"] == self.types[b + "attn_v.weight"]:
                 L["qkv"] = torch.cat([L.pop("q"), L.pop("k"), L.pop("v")])       # raw rows are contiguous per tensor: row-wise concat
         self.rope_cos, self.rope_sin = _rope_tables(self.max_context, c.rope_dim, c.rope_theta, self.device)
-        # single-token decode replays one captured CUDA graph (one rank; POCKET_GGUF_DECODE_GRAPH=0 turns it off)
-        self.use_graph = self.world == 1 and self.device.type == "cuda" and os.environ.get("POCKET_GGUF_DECODE_GRAPH", "1") != "0"
+        # single-token decode replays one captured CUDA graph: on by default on one rank (POCKET_GGUF_DECODE_GRAPH=0 turns
+        # it off), opt-in with several ranks (=2: the expert combine is then captured too, all ranks replay in step)
+        self.balanced_routes = False
+        mode = os.environ.get("POCKET_GGUF_DECODE_GRAPH", "1")
+        self.use_graph = self.device.type == "cuda" and (mode == "2" or (mode != "0" and self.world == 1))
         self._graph = None
 
     def _combine(self, y: torch.Tensor) -> torch.Tensor:
@@ -371,6 +374,12 @@ class MiniMaxM2Model:
             h = (h + att).to(torch.bfloat16)                     # bf16 + fp32 promotes to fp32: the sum is rounded once
             xn = ops.rmsnorm(h, L["ffn_norm"], mode=2, eps=c.norm_eps)
             ids, wt = go.router_topk(xn, L["router"], c.n_experts_used, bias=L["bias"], score_func="sigmoid", norm_topk=True)
+            if self.balanced_routes:
+                # benchmark aid for random weights (whose hidden states collapse and send every token to the same few
+                # experts): the router still runs, but token t uses experts (t * k + j + 37 * layer) mod E with equal weights
+                kk = c.n_experts_used
+                ids = ((pos.view(-1, 1) * kk + torch.arange(kk, device=self.device, dtype=torch.int32).view(1, -1) + 37 * i) % c.n_experts).to(torch.int32).contiguous()
+                wt = torch.full_like(wt, 1.0 / kk)
             routes = go.group_routes(ids, wt, c.n_experts)
             seg, tok, rw = routes
             y = go.gguf_moe_forward(xn, L["w13"], L["w2"], self.types[b + "ffn_gate_exps.weight"], self.types[b + "ffn_down_exps.weight"],

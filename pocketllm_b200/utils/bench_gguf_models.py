@@ -23,6 +23,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run only the first N layers (0 = all)")
     ap.add_argument("--prompt-len", type=int, default=256)
     ap.add_argument("--decode-len", type=int, default=128)
+    ap.add_argument("--routing", default="balanced", choices=["balanced", "model"],
+                    help="balanced: token t goes to experts (t * k + j + 37 * layer) mod E, as a trained load-balanced router spreads them; "
+                         "model: the random router's own picks (with random weights the hidden states collapse and all tokens share 8 experts)")
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=1)
     args = ap.parse_args()
@@ -39,6 +42,7 @@ def main() -> int:
         cfg.n_layers = args.layers
     model = mm.MiniMaxM2Model.synthetic(cfg, device=f"cuda:{local}", rank=rank, world=world, max_context=args.prompt_len + args.decode_len + 8,
                                         group=group)
+    model.balanced_routes = args.routing == "balanced"
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
     e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
@@ -68,7 +72,7 @@ def main() -> int:
         print(json.dumps({"model": args.model, "n_gpus": world, "layers": cfg.n_layers, "prompt_len": args.prompt_len, "decode_len": args.decode_len,
                           "prefill_ms": round(pre, 2), "prefill_tok_s": round(args.prompt_len / pre * 1e3, 1),
                           "decode_ms_per_token": round(dec / args.decode_len, 3), "decode_tok_s": round(args.decode_len / dec * 1e3, 2),
-                          "weight_bytes_per_rank": model.weight_bytes(), "expert_type": cfg.expert_type, "attn_type": cfg.attn_type,
+                          "weight_bytes_per_rank": model.weight_bytes(), "routing": args.routing, "expert_type": cfg.expert_type, "attn_type": cfg.attn_type,
                           "data": "synthetic: uniform-random prompt, random block payloads with constant block scales", "last_tokens": last}), flush=True)
     if world > 1:
         dist.destroy_process_group()
