@@ -26,6 +26,9 @@ def main() -> int:
     ap.add_argument("--routing", default="balanced", choices=["balanced", "model"],
                     help="balanced: token t goes to experts (t * k + j + 37 * layer) mod E, as a trained load-balanced router spreads them; "
                          "model: the random router's own picks (with random weights the hidden states collapse and all tokens share 8 experts)")
+    ap.add_argument("--kernel-table", type=int, default=0,
+                    help="after the timed runs, decode 4 more tokens without the captured graph under torch.profiler and print the N kernels "
+                         "with the largest share of device time (shares only: times under a profiler are not benchmark numbers)")
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=1)
     args = ap.parse_args()
@@ -74,6 +77,20 @@ def main() -> int:
                           "decode_ms_per_token": round(dec / args.decode_len, 3), "decode_tok_s": round(args.decode_len / dec * 1e3, 2),
                           "weight_bytes_per_rank": model.weight_bytes(), "routing": args.routing, "expert_type": cfg.expert_type, "attn_type": cfg.attn_type,
                           "data": "synthetic: uniform-random prompt, random block payloads with constant block scales", "last_tokens": last}), flush=True)
+    if args.kernel_table > 0 and rank == 0 and world == 1:
+        from torch.profiler import ProfilerActivity, profile
+        model.use_graph = False
+        tok = last[-1]
+        tok = model.decode_one(tok)
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(4):
+                tok = model.decode_one(tok)
+            torch.cuda.synchronize()
+        rows = sorted(prof.key_averages(), key=lambda e: -e.self_device_time_total)
+        total = sum(e.self_device_time_total for e in rows) or 1.0
+        for e in rows[: args.kernel_table]:
+            print(f"kernel_share={100.0 * e.self_device_time_total / total:5.1f}% calls={e.count:4d} avg_us={e.self_device_time_total / max(e.count, 1):8.1f} name={e.key[:90]}")
     if world > 1:
         dist.destroy_process_group()
     return 0
