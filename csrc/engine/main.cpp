@@ -146,11 +146,15 @@ std::vector<int> parse_ids(const std::string& text) {
   return out;
 }
 
-enum Op : int32_t { OP_GENERATE = 1, OP_RESET = 2, OP_SHUTDOWN = 3, OP_PREFILL = 4, OP_NEXT = 5 };
+enum Op : int32_t { OP_GENERATE = 1, OP_RESET = 2, OP_SHUTDOWN = 3, OP_PREFILL = 4, OP_NEXT = 5, OP_SPEC = 6 };
+
+int g_mtp_tokens = 4;   // draft length limit of speculative runs (--qwen-mtp-tokens)
 
 // The Qwen engine behind the server. Greedy requests run the device sampler; with a temperature the
 // logits of each step come back to the host sampler (single rank only: logits are vocabulary shards).
-// With tensor parallelism rank 0 replays every step to the workers over the command channel.
+// With tensor parallelism rank 0 replays every step to the workers over the command channel. An engine built with the
+// multi-token predictor serves greedy requests through speculative decode: tokens are produced a chunk at a time and
+// handed out one by one (a request that stops inside a chunk simply leaves the rest unused; the next request resets).
 class QwenTokenEngine : public pk::TokenEngine {
  public:
   QwenTokenEngine(pk::QwenEngine& e, pk::CmdChannel& chan, int world) : e_(e), chan_(chan), world_(world) {}
@@ -166,10 +170,34 @@ class QwenTokenEngine : public pk::TokenEngine {
       chan_.broadcast(m);
     }
     e_.reset();
+    buf_.clear();
+    buf_pos_ = 0;
     const int first = e_.prefill(prompt.data(), (int)prompt.size());
     return host_sampling_ ? resample(first) : first;
   }
   int next() override {
+    if (!host_sampling_ && e_.mtp_enabled()) {
+      if (buf_pos_ < buf_.size()) return buf_[buf_pos_++];
+      const int room = e_.options().max_context - e_.position() - 10;
+      const int chunk = std::min(kSpecChunk, room);
+      if (chunk >= 2) {
+        if (world_ > 1) {
+          pk::CmdChannel::Message m;
+          m.op = OP_SPEC;
+          m.payload = {chunk};
+          chan_.broadcast(m);
+        }
+        buf_.assign((size_t)chunk, 0);
+        pk::QwenSpecStats st;
+        e_.spec_decode(chunk, g_mtp_tokens, buf_.data(), &st);
+        spec_total_.rounds += st.rounds;
+        spec_total_.proposed += st.proposed;
+        spec_total_.accepted += st.accepted;
+        spec_total_.rollbacks += st.rollbacks;
+        buf_pos_ = 1;
+        return buf_[0];
+      }
+    }
     if (world_ > 1) {
       pk::CmdChannel::Message m;
       m.op = OP_NEXT;
@@ -184,6 +212,7 @@ class QwenTokenEngine : public pk::TokenEngine {
     e_.decode(1, &out, true);
     return out;
   }
+  const pk::QwenSpecStats& spec_stats() const { return spec_total_; }
 
  private:
   int resample(int greedy) {
@@ -201,6 +230,10 @@ class QwenTokenEngine : public pk::TokenEngine {
   bool host_sampling_ = false;
   int last_ = 0;
   std::vector<float> logits_;
+  static constexpr int kSpecChunk = 8;   // tokens produced per speculative call
+  std::vector<int> buf_;                 // tokens of the current chunk not yet handed out
+  size_t buf_pos_ = 0;
+  pk::QwenSpecStats spec_total_;
 };
 
 std::vector<std::string> sidecar_command(const Args& a) {
@@ -250,8 +283,6 @@ struct RunResult {
   double prefill_s = 0, decode_s = 0;
   pk::QwenSpecStats spec;
 };
-
-int g_mtp_tokens = 4;   // draft length limit of speculative runs (--qwen-mtp-tokens)
 
 RunResult generate(pk::QwenEngine& eng, const std::vector<int>& prompt, int max_new) {
   RunResult r;
@@ -447,6 +478,9 @@ int run(const Args& a) {
       so.model_name = a.model_name;
       so.allow_shutdown = a.allow_shutdown;
       pk::run_openai_server(http, te, sidecar, so);
+      if (eng.mtp_enabled())
+        std::printf("serve_mtp_rounds=%lld serve_mtp_proposed=%lld serve_mtp_accepted=%lld serve_mtp_rollbacks=%lld\n", te.spec_stats().rounds,
+                    te.spec_stats().proposed, te.spec_stats().accepted, te.spec_stats().rollbacks);
       pk::CmdChannel::Message bye;
       bye.op = OP_SHUTDOWN;
       chan.broadcast(bye);
@@ -462,6 +496,8 @@ int run(const Args& a) {
           } else if (m.op == OP_NEXT) {
             int out = 0;
             eng.decode(1, &out, true);
+          } else if (m.op == OP_SPEC && !m.payload.empty()) {
+            eng.spec_decode(m.payload[0], g_mtp_tokens, nullptr, nullptr);
           }
         } catch (const std::exception& e) {
           std::fprintf(stderr, "worker %d: %s\n", a.tp_rank, e.what());

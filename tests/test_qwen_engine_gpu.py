@@ -319,3 +319,52 @@ def test_engine_without_predictor_rejects_spec_decode(tiny):
     eng.close()
     with pytest.raises(qh.EngineError):
         qh.QwenEngine(cfg, max_context=128, prefill_chunk=32, mtp=True).load(d)      # checkpoint has no mtp.* tensors
+
+
+def test_native_server_with_multi_token_predictor(tiny_mtp):
+    """pocket_engine --serve --qwen-mtp: greedy requests run through speculative decode in chunks and return the same text
+    as plain greedy decoding; the speculative counters are printed when the server stops."""
+    import http.client
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    from pocketllm_b200.models import qwen_hybrid as qh
+    from pocketllm_b200.server.cpp_sidecar import CharTokenizer
+    cfg, variants = tiny_mtp
+    tensors, d = variants["fp8"]
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    proc = subprocess.Popen([str(root / "pocketllm_b200" / "_C" / "pocket_engine"), "--ckpt", str(d), "--serve", "--port", "0", "--tokenizer", "chars",
+                             "--chat-format", "plain", "--sidecar-python", sys.executable, "--allow-shutdown", "--max-context", "512",
+                             "--qwen-mtp-tokens", "3"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+    port = None
+    try:
+        line = proc.stdout.readline()
+        assert line.startswith("openai_server_listening"), proc.stderr.read()
+        port = int(dict(kv.split("=") for kv in line.split()[1:])["port"])
+        eng = qh.QwenEngine(cfg, max_context=512).load(d)
+        for content, n in (("hello there", 21), ("abc", 9)):
+            body = {"messages": [{"role": "user", "content": content}], "max_tokens": n}
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+            c.request("POST", "/v1/chat/completions", json.dumps(body), {"Content-Type": "application/json"})
+            out = json.loads(c.getresponse().read())
+            c.close()
+            eng.reset()
+            want = eng.generate(CharTokenizer("plain").encode_chat(body["messages"]), n)
+            if 0 in want:
+                want = want[:want.index(0)]
+            assert out["choices"][0]["message"]["content"] == "".join(chr(t) for t in want)
+        eng.close()
+    finally:
+        try:
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=20)
+            c.request("POST", "/shutdown", "{}")
+            c.getresponse().read()
+            rest = proc.communicate(timeout=30)[0]
+        except Exception:
+            proc.kill()
+            rest = ""
+    stats = dict(kv.split("=") for l in rest.splitlines() if l.startswith("serve_mtp_rounds") for kv in l.split())
+    assert int(stats["serve_mtp_rounds"]) > 0 and int(stats["serve_mtp_proposed"]) >= int(stats["serve_mtp_accepted"])
