@@ -179,11 +179,14 @@ def full_qk_norm_rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     return out
 
 
-def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, *, mode: int = 1, eps: float = 1e-6) -> torch.Tensor:
+def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, *, mode: int = 1, eps: float = 1e-6, parts: torch.Tensor | None = None,
+            hidden_out: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm of bf16 x [M, K] (mode 1: times 1 + gamma, mode 2: times gamma). With `parts` (fp32 [R, M, K]) the input is
+    bf16(x + sum of parts), which is also written to `hidden_out` when given: a residual add fused into the norm."""
     M, K = x.shape
     y = torch.empty_like(x)
-    st = _lib.kernels().pk_rmsnorm(_ptr(x), c_void_p(0), c_int(0), c_int(M), c_int(K), c_void_p(0), _ptr(gamma),
-                                   c_int(mode), c_float(eps), _ptr(y), c_void_p(0), _stream())
+    st = _lib.kernels().pk_rmsnorm(_ptr(x), _ptr(parts), c_int(0 if parts is None else parts.shape[0]), c_int(M), c_int(K), _ptr(hidden_out),
+                                   _ptr(gamma), c_int(mode), c_float(eps), _ptr(y), c_void_p(0), _stream())
     _check(st, "pk_rmsnorm")
     return y
 
