@@ -165,11 +165,15 @@ constexpr int kWarps = 8;
 // The decoders read single bytes; from global memory that is one load instruction per byte, each a round trip to L2.
 // A warp therefore first brings a stretch of its row into shared memory with 16-byte loads and decodes from there.
 constexpr int kStageBlocks = 8;                                  // 2048 weights per stretch
-constexpr int kStageBytes = kStageBlocks * 512 + 16;             // the largest block type (bf16: 512 B) plus the misalignment
-constexpr int kStageSmem = kWarps * kStageBytes;                 // per thread block
+// Bytes of one warp's stage buffer for rows of `type` with K weights: a stretch of up to kStageBlocks blocks plus the
+// misalignment of its start, rounded to 16. Sized per launch so that small block types leave room for more resident blocks.
+__host__ __device__ inline int stage_bytes_per_warp(int type, int K) {
+  const int nb = (K >> 8) < kStageBlocks ? (K >> 8) : kStageBlocks;
+  return ((nb * block_bytes(type) + 15) & ~15) + 16;
+}
 
 // One warp: dot products of one raw row with M staged activation rows (fp32, [M][K]). `stage` is this warp's
-// kStageBytes of shared memory.
+// stage_bytes_per_warp(TYPE, K) bytes of shared memory.
 template <int TYPE, int M>
 __device__ __forceinline__ void row_dot(const uint8_t* wrow, const float* xs, int K, int lane, float (&acc)[M], uint8_t* stage) {
   constexpr int BB = block_bytes(TYPE);
@@ -228,6 +232,7 @@ struct LinearParams {
   int epi;            // 0 bf16, 1 swiglu (rows j and j + N/2), 2 fp32
   void* y;
   int ldy;
+  int stage_bytes;    // per warp, behind the staged activations in dynamic shared memory (one- and two-row launches)
 };
 
 template <int M>
@@ -255,9 +260,8 @@ __global__ void __launch_bounds__(kThreads) gguf_linear_kernel(const LinearParam
   extern __shared__ __align__(16) float xs[];  // [M][K]
   __shared__ float red[40];
   constexpr bool kStaged = M <= 2;     // one or two rows: the byte loads of the decoders dominate, stage the weights
-  __shared__ __align__(16) uint8_t stage_all[kStaged ? kStageSmem : 16];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  uint8_t* stage = kStaged ? stage_all + warp * kStageBytes : nullptr;
+  uint8_t* stage = kStaged ? reinterpret_cast<uint8_t*>(xs + (size_t)M * p.K) + (size_t)warp * p.stage_bytes : nullptr;
   for (int m = 0; m < M; ++m) {
     float ss = 0.f;
     for (int k = tid; k < p.K; k += kThreads) {
@@ -423,8 +427,7 @@ __device__ __forceinline__ int expert_of_route(const int* seg_start, int lo_e, i
 }
 
 __global__ void __launch_bounds__(kThreads) gguf_moe_w13_route_kernel(const MoeParams p) {
-  extern __shared__ __align__(16) float xs[];  // [H]
-  __shared__ __align__(16) uint8_t stage_all[kStageSmem];
+  extern __shared__ __align__(16) float xs[];  // [H], then the warps' stage buffers
   const int lo = p.seg_start[p.expert_offset], hi = p.seg_start[p.expert_offset + p.local_experts];
   const int r = lo + blockIdx.y;
   if (r >= hi) return;
@@ -434,12 +437,12 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w13_route_kernel(const MoeP
   const uint8_t* base = p.W13 + (size_t)(e - p.expert_offset) * 2 * p.I * rb;
   for (int k = tid; k < p.H; k += kThreads) xs[k] = __bfloat162float(p.x[(size_t)p.route_token[r] * p.H + k]);
   __syncthreads();
-  moe_w13_rows<1>(p, base, rb, xs, r, 1, lane, warp, stage_all + warp * kStageBytes);
+  moe_w13_rows<1>(p, base, rb, xs, r, 1, lane, warp,
+                  reinterpret_cast<uint8_t*>(xs + p.H) + (size_t)warp * stage_bytes_per_warp(p.type13, p.H));
 }
 
 __global__ void __launch_bounds__(kThreads) gguf_moe_w2_route_kernel(const MoeParams p) {
-  extern __shared__ __align__(16) float hs[];  // [I]
-  __shared__ __align__(16) uint8_t stage_all[kStageSmem];
+  extern __shared__ __align__(16) float hs[];  // [I], then the warps' stage buffers
   const int lo = p.seg_start[p.expert_offset], hi = p.seg_start[p.expert_offset + p.local_experts];
   const int r = lo + blockIdx.y;
   if (r >= hi) return;
@@ -449,7 +452,8 @@ __global__ void __launch_bounds__(kThreads) gguf_moe_w2_route_kernel(const MoePa
   const uint8_t* base = p.W2 + (size_t)(e - p.expert_offset) * p.H * rb;
   for (int k = tid; k < p.I; k += kThreads) hs[k] = p.hbuf[(size_t)r * p.I + k];
   __syncthreads();
-  moe_w2_rows<1>(p, base, rb, hs, r, 1, lane, warp, stage_all + warp * kStageBytes);
+  moe_w2_rows<1>(p, base, rb, hs, r, 1, lane, warp,
+                 reinterpret_cast<uint8_t*>(hs + p.I) + (size_t)warp * stage_bytes_per_warp(p.type2, p.I));
 }
 
 // Fixed-order reduce: y[t] += sum over k = 0..topk-1 of the output of route (t, k), skipping routes whose
@@ -634,9 +638,10 @@ __global__ void __launch_bounds__(256) gguf_dequant_rows_kernel(const uint8_t* W
 }
 
 template <int M>
-int launch_linear(const LinearParams& p, int sm_count, cudaStream_t stream) {
-  const size_t smem = (size_t)M * p.K * sizeof(float);
-  // static (the warps' stage buffers) plus dynamic shared memory passes 48 KB already for small K: always opt in
+int launch_linear(const LinearParams& p_in, int sm_count, cudaStream_t stream) {
+  LinearParams p = p_in;
+  p.stage_bytes = M <= 2 ? stage_bytes_per_warp(p.type, p.K) : 0;
+  const size_t smem = (size_t)M * p.K * sizeof(float) + (size_t)kWarps * p.stage_bytes;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gguf_linear_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess) {
@@ -647,7 +652,7 @@ int launch_linear(const LinearParams& p, int sm_count, cudaStream_t stream) {
   }
   const int groups = p.epi == 1 ? p.N / 2 : p.N;
   int blocks = (groups + kWarps - 1) / kWarps;
-  blocks = min(blocks, (sm_count > 0 ? sm_count : 148) * 4);
+  blocks = min(blocks, (sm_count > 0 ? sm_count : 148) * 8);
   gguf_linear_kernel<M><<<blocks, kThreads, smem, stream>>>(p);
   PK_CHECK_LAUNCH();
   return PK_OK;
@@ -663,7 +668,7 @@ PK_API int pk_gguf_linear(const void* W, int type, int N, int K, int M, const vo
   if (type < 0 || type > T_LAST || M < 1 || M > 8 || (K & 255) != 0 || N < 1) return PK_ERR_BAD_ARG;
   if ((size_t)M * K * 4 > 184 * 1024) return PK_ERR_UNSUPPORTED;   // plus the warps' stage buffers
   if (epi == 1 && (N & 1)) return PK_ERR_BAD_ARG;
-  LinearParams p{(const uint8_t*)W, type, N, K, M, (const pk::bf16*)x, gamma, eps, epi, y, ldy};
+  LinearParams p{(const uint8_t*)W, type, N, K, M, (const pk::bf16*)x, gamma, eps, epi, y, ldy, 0};
   switch (M) {
     case 1: return launch_linear<1>(p, sm_count, stream);
     case 2: return launch_linear<2>(p, sm_count, stream);
@@ -787,9 +792,11 @@ static int moe_forward_impl(const void* W13, const void* W2, int type13, int typ
     // one block set per route: at most total_routes of them belong to this rank
     MoeParams q = p;
     const int t13 = (I + kWarps - 1) / kWarps, t2 = (H + kWarps - 1) / kWarps;
-    gguf_moe_w13_route_kernel<<<dim3(t13 < 256 ? t13 : 256, total_routes), kThreads, (size_t)H * 4, stream>>>(q);
+    gguf_moe_w13_route_kernel<<<dim3(t13 < 256 ? t13 : 256, total_routes), kThreads,
+                                (size_t)H * 4 + (size_t)kWarps * stage_bytes_per_warp(type13, H), stream>>>(q);
     PK_CHECK_LAUNCH();
-    gguf_moe_w2_route_kernel<<<dim3(t2 < 256 ? t2 : 256, total_routes), kThreads, (size_t)I * 4, stream>>>(q);
+    gguf_moe_w2_route_kernel<<<dim3(t2 < 256 ? t2 : 256, total_routes), kThreads,
+                               (size_t)I * 4 + (size_t)kWarps * stage_bytes_per_warp(type2, I), stream>>>(q);
     PK_CHECK_LAUNCH();
     return PK_OK;
   }
