@@ -154,3 +154,66 @@ PK_CAPI void pk_cpu_fp4_dequant(const uint8_t* q, const uint8_t* s, long rows, i
       }
     }
 }
+
+// ---- INT8 routed experts (one fp32 scale per weight row) ------------------------------------------------------------------
+// Same layout rules as the FP4 entry: w13 int8 [E, 2I, H] (gate rows then up rows) with s13 fp32 [E, 2I],
+// w2 int8 [E, H, I] with s2 fp32 [E, H]. Counterpart of the reference's routed_int8_moe_forward
+// (src/csrc/deepseek_cpu_moe_ext.cpp:2000-2115).
+namespace {
+inline float dot_i8_row(const int8_t* w, float scale, const float* x, int K) {
+  float acc = 0.f;
+#pragma omp simd reduction(+ : acc)
+  for (int k = 0; k < K; ++k) acc += (float)w[k] * x[k];
+  return acc * scale;
+}
+}  // namespace
+
+PK_CAPI int pk_cpu_moe_int8_forward(const float* x, int T, int H, int I, int E, int topk, const int* ids, const float* weights,
+                                    const int8_t* w13, const float* s13, const int8_t* w2, const float* s2, float swiglu_limit, float* y,
+                                    int* counts) {
+  if (T < 0 || H < 1 || I < 1 || topk < 1) return 1;
+  std::memset(y, 0, sizeof(float) * (size_t)T * H);
+  if (counts) std::memset(counts, 0, sizeof(int) * E);
+  std::vector<float> hidden(I);
+  for (int t = 0; t < T; ++t) {
+    const float* xt = x + (size_t)t * H;
+    float* yt = y + (size_t)t * H;
+    for (int j = 0; j < topk; ++j) {
+      const int e = ids[(size_t)t * topk + j];
+      if (e < 0 || e >= E) return 2;
+      if (counts) counts[e] += 1;
+      const int8_t* g_rows = w13 + (size_t)e * 2 * I * H;
+      const int8_t* u_rows = g_rows + (size_t)I * H;
+      const float* g_sc = s13 + (size_t)e * 2 * I;
+      const float* u_sc = g_sc + I;
+      const float rw = weights[(size_t)t * topk + j];
+#pragma omp parallel for schedule(static)
+      for (int r = 0; r < I; ++r) {
+        float g = dot_i8_row(g_rows + (size_t)r * H, g_sc[r], xt, H);
+        float u = dot_i8_row(u_rows + (size_t)r * H, u_sc[r], xt, H);
+        if (swiglu_limit > 0.f) {
+          g = std::min(g, swiglu_limit);
+          u = std::max(-swiglu_limit, std::min(u, swiglu_limit));
+        }
+        hidden[r] = silu(g) * u;
+      }
+      const int8_t* d_rows = w2 + (size_t)e * H * I;
+      const float* d_sc = s2 + (size_t)e * H;
+#pragma omp parallel for schedule(static)
+      for (int n = 0; n < H; ++n) yt[n] += rw * dot_i8_row(d_rows + (size_t)n * I, d_sc[n], hidden.data(), I);
+    }
+  }
+  return 0;
+}
+
+// fp32 [rows, K] -> int8 codes and one scale per row (absmax / 127, round to nearest)
+PK_CAPI void pk_cpu_quantize_int8_rows(const float* w, long rows, int K, int8_t* q, float* scale) {
+#pragma omp parallel for schedule(static)
+  for (long r = 0; r < rows; ++r) {
+    float amax = 0.f;
+    for (int k = 0; k < K; ++k) amax = std::max(amax, std::fabs(w[r * K + k]));
+    const float s = amax > 0.f ? amax / 127.f : 1.f;
+    scale[r] = s;
+    for (int k = 0; k < K; ++k) q[r * K + k] = (int8_t)std::lrint(w[r * K + k] / s);
+  }
+}

@@ -74,3 +74,33 @@ def test_dot_microbench_runs():
     formats = {l.split("format=")[1].split()[0] for l in lines[1:]}
     assert formats == {"f32", "bf16", "int8", "fp4_e2m1"}
     assert subprocess.run([str(exe), "--k", "100"], capture_output=True).returncode == 2
+
+
+def test_int8_routed_experts_match_dequantised_reference(cpu):
+    """INT8 experts with one scale per weight row: the native loop against fp32 math on the dequantised weights."""
+    g = torch.Generator().manual_seed(4)
+    T, H, I, E, k = 6, 96, 64, 5, 2
+    x = torch.randn(T, H, generator=g)
+    w13, w2 = torch.randn(E, 2 * I, H, generator=g) * 0.05, torch.randn(E, H, I, generator=g) * 0.05
+    q13, s13 = torch.empty(E, 2 * I, H, dtype=torch.int8), torch.empty(E, 2 * I)
+    q2, s2 = torch.empty(E, H, I, dtype=torch.int8), torch.empty(E, H)
+    cpu.pk_cpu_quantize_int8_rows(_p(w13), ctypes.c_long(E * 2 * I), H, _p(q13), _p(s13))
+    cpu.pk_cpu_quantize_int8_rows(_p(w2), ctypes.c_long(E * H), I, _p(q2), _p(s2))
+    d13, d2 = q13.float() * s13.unsqueeze(-1), q2.float() * s2.unsqueeze(-1)
+    assert (d13 - w13).abs().max() <= s13.max() * 0.5 + 1e-7
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, k, generator=g)
+    y, counts = torch.empty(T, H), torch.zeros(E, dtype=torch.int32)
+    rc = cpu.pk_cpu_moe_int8_forward(_p(x), T, H, I, E, k, _p(ids), _p(wts), _p(q13), _p(s13), _p(q2), _p(s2), ctypes.c_float(7.0), _p(y), _p(counts))
+    assert rc == 0
+    ref = torch.zeros(T, H)
+    for t in range(T):
+        for j in range(k):
+            e = int(ids[t, j])
+            gate, up = d13[e, :I] @ x[t], d13[e, I:] @ x[t]
+            ref[t] += wts[t, j] * (d2[e] @ d4.swiglu(gate, up, 7.0))
+    assert torch.allclose(y, ref, atol=1e-4, rtol=1e-4)
+    assert counts.tolist() == torch.bincount(ids.flatten().long(), minlength=E).tolist()
+    bad = ids.clone()
+    bad[0, 0] = E
+    assert cpu.pk_cpu_moe_int8_forward(_p(x), T, H, I, E, k, _p(bad), _p(wts), _p(q13), _p(s13), _p(q2), _p(s2), ctypes.c_float(0.0), _p(y), None) == 2
