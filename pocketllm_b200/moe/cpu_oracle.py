@@ -98,7 +98,37 @@ def _p(t: torch.Tensor | None, ctype):
     return ctypes.cast(t.data_ptr(), ctypes.POINTER(ctype))
 
 
-def forward_native(x: torch.Tensor, w: Fp4MoEWeights, topk: int = 2, score_func: str = "softmax", norm_topk: bool = True,
+@dataclass
+class Int8MoEWeights:
+    """Routed experts as int8 codes with one fp32 scale per weight row (no shared expert in this format)."""
+    router: torch.Tensor                 # [E, H] fp32
+    w13: torch.Tensor                    # int8 [E, 2I, H]  gate rows then up rows
+    s13: torch.Tensor                    # fp32 [E, 2I]
+    w2: torch.Tensor                     # int8 [E, H, I]
+    s2: torch.Tensor                     # fp32 [E, H]
+    bias: torch.Tensor | None = None
+
+    @property
+    def dims(self) -> tuple[int, int, int]:
+        E, two_i, H = self.w13.shape
+        return E, two_i // 2, H
+
+    @classmethod
+    def quantize(cls, router: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, bias: torch.Tensor | None = None) -> "Int8MoEWeights":
+        """fp32 w13 [E, 2I, H], w2 [E, H, I] -> int8 rows through the native row quantiser (absmax / 127)."""
+        L = _lib.cpu()
+        out = []
+        for w in (w13, w2):
+            wf = w.float().contiguous()
+            q = torch.empty(wf.shape, dtype=torch.int8)
+            sc = torch.empty(wf.shape[:-1], dtype=torch.float32)
+            L.pk_cpu_quantize_int8_rows(_p(wf, ctypes.c_float), ctypes.c_long(wf.numel() // wf.shape[-1]), wf.shape[-1], _p(q, ctypes.c_int8),
+                                        _p(sc, ctypes.c_float))
+            out += [q, sc]
+        return cls(router.float().contiguous(), out[0], out[1], out[2], out[3], bias)
+
+
+def forward_native(x: torch.Tensor, w: "Fp4MoEWeights | Int8MoEWeights", topk: int = 2, score_func: str = "softmax", norm_topk: bool = True,
                    route_scale: float = 1.0, swiglu_limit: float = 0.0) -> tuple[torch.Tensor, torch.Tensor, float]:
     """Same block on the native CPU oracle; returns (y, counts, seconds of the expert pass)."""
     L = _lib.cpu()
@@ -115,6 +145,16 @@ def forward_native(x: torch.Tensor, w: Fp4MoEWeights, topk: int = 2, score_func:
         raise RuntimeError(f"pk_cpu_route: status {st}")
     y = torch.empty(T, H, dtype=torch.float32)
     counts = torch.zeros(E, dtype=torch.int32)
+    if isinstance(w, Int8MoEWeights):
+        t0 = time.perf_counter()
+        st = L.pk_cpu_moe_int8_forward(
+            _p(xf, ctypes.c_float), T, H, I, E, topk, _p(ids, ctypes.c_int), _p(wt, ctypes.c_float), _p(w.w13.contiguous(), ctypes.c_int8),
+            _p(w.s13.contiguous(), ctypes.c_float), _p(w.w2.contiguous(), ctypes.c_int8), _p(w.s2.contiguous(), ctypes.c_float),
+            ctypes.c_float(swiglu_limit), _p(y, ctypes.c_float), _p(counts, ctypes.c_int))
+        dt = time.perf_counter() - t0
+        if st != 0:
+            raise RuntimeError(f"pk_cpu_moe_int8_forward: status {st}")
+        return y, counts, dt
     sh_i = 0 if w.shared_w13 is None else w.shared_w13.shape[1] // 2
     u8 = ctypes.c_uint8
     t0 = time.perf_counter()

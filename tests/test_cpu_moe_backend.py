@@ -91,3 +91,37 @@ def test_client_times_out_when_nobody_serves():
             c.request(0, torch.zeros(2, 64), timeout_s=0.2)
     finally:
         c.close()
+
+
+def test_backend_runs_int8_experts():
+    """The asynchronous CPU backend takes INT8 experts (per-row scales) as well as FP4 ones."""
+    import torch
+    from pocketllm_b200.moe import cpu_oracle as co
+    from pocketllm_b200.moe.cpu_backend import CPURoutedExpertsBackend
+    from pocketllm_b200.ops import lib
+    import pytest
+    if not lib.available("cpu"):
+        pytest.skip("libpocket_cpu.so not built")
+    g = torch.Generator().manual_seed(2)
+    E, I, H, k, T = 6, 64, 96, 2, 5
+    router = torch.randn(E, H, generator=g) * 0.05
+    w13, w2 = torch.randn(E, 2 * I, H, generator=g) * 0.05, torch.randn(E, H, I, generator=g) * 0.05
+    w = co.Int8MoEWeights.quantize(router, w13, w2)
+    assert w.dims == (E, I, H) and w.w13.dtype == torch.int8
+    be = CPURoutedExpertsBackend({3: w}, k, score_func="sigmoid", norm_topk=True)
+    x = torch.randn(T, H, generator=g)
+    y = be.forward(3, x)
+    be.close()
+    # fp32 math on the dequantised weights
+    d13, d2 = w.w13.float() * w.s13.unsqueeze(-1), w.w2.float() * w.s2.unsqueeze(-1)
+    sc = torch.sigmoid(x @ router.T)
+    top = sc.topk(k, -1)
+    wt = top.values / top.values.sum(-1, keepdim=True)
+    ref = torch.zeros(T, H)
+    for t in range(T):
+        for j in range(k):
+            e = int(top.indices[t, j])
+            gu = d13[e] @ x[t]
+            ref[t] += wt[t, j] * (d2[e] @ (torch.nn.functional.silu(gu[:I]) * gu[I:]))
+    assert torch.allclose(y, ref, atol=1e-4, rtol=1e-3)
+    assert int(be.last_counts.sum()) == T * k
