@@ -44,7 +44,7 @@ class CacheConfig:
 
 @dataclass
 class SpeculativeConfig:
-    mode: str = "off"                    # off | ngram | mtp
+    mode: str = "off"                    # off | ngram | mtp (the checkpoint's multi-token predictor) | dspark (DSV4 block drafter)
     draft_len: int = 4
     gate: bool = True
 
@@ -141,12 +141,37 @@ class Config:
             raise ValueError("parallel.world must be between 1 and 8 (one NVSwitch node)")
         if p.policy not in ("replicated", "tp", "layer_pp"):
             raise ValueError(f"parallel.policy {p.policy!r} is not one of replicated, tp, layer_pp")
-        if s.mode not in ("off", "ngram", "mtp") or not 1 <= s.draft_len <= 7:
-            raise ValueError("speculative.mode must be off | ngram | mtp and draft_len between 1 and 7")
-        if p.policy == "layer_pp" and s.mode == "mtp":
-            raise ValueError("MTP drafting needs the last layer's hidden state on every rank: not available with layer_pp")
+        if s.mode not in ("off", "ngram", "mtp", "dspark") or not 1 <= s.draft_len <= 7:
+            raise ValueError("speculative.mode must be off | ngram | mtp | dspark and draft_len between 1 and 7")
+        if p.policy == "layer_pp" and s.mode in ("mtp", "dspark"):
+            raise ValueError("MTP / DSpark drafting needs the last layers' hidden states on every rank: not available with layer_pp")
+        if s.mode == "dspark" and self.model.family not in ("auto", "deepseek_v4"):
+            raise ValueError("speculative.mode dspark is the DeepSeek-V4 block drafter; the Qwen hybrid uses mtp")
         if c.prefill_chunk < 8 or self.model.max_context < c.prefill_chunk:
             raise ValueError("cache.prefill_chunk must be at least 8 and at most model.max_context")
+
+    def native_engine_args(self, rank: int = 0) -> list[str]:
+        """Flags of the native CLI (`pocket_engine`) that realise this configuration for tensor-parallel rank `rank`:
+        what `serving.native` launches, and the one place where config names meet flag names."""
+        m, p, c, s, v = self.model, self.parallel, self.cache, self.speculative, self.serving
+        if p.policy != "tp" and p.world > 1:
+            raise ValueError("the native engine shards by tensor parallelism only")
+        args = ["--ckpt", m.path, "--max-context", str(m.max_context), "--prefill-chunk-tokens", str(c.prefill_chunk),
+                "--tp-world", str(p.world), "--tp-rank", str(rank)]
+        if not c.cuda_graph:
+            args.append("--no-cuda-graph")
+        if s.mode == "mtp":
+            args += ["--qwen-mtp-tokens", str(s.draft_len)]
+        elif s.mode != "off":
+            raise ValueError(f"the native engine drafts with the checkpoint's multi-token predictor only (speculative.mode {s.mode!r})")
+        if v.native:
+            args += ["--serve", "--host", v.host, "--port", str(v.port), "--model-name", v.model_name]
+            if m.tokenizer:
+                args += ["--tokenizer", m.tokenizer if m.tokenizer == "chars" or ":" in m.tokenizer
+                         else ("gguf:" if m.tokenizer.endswith(".gguf") else "hf:") + m.tokenizer]
+            if m.chat_format != "auto":
+                args += ["--chat-format", m.chat_format]
+        return args
 
     def to_dict(self) -> dict:
         return asdict(self)

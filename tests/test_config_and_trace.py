@@ -67,3 +67,22 @@ def test_device_memory_floor_decision():
     assert b"POCKET_MIN_FREE_MIB" in buf.value and b"7000.0 MiB" in buf.value and b"3000.0 MiB" in buf.value
     assert fn(1000 * MiB, 180000 * MiB, 7000 * MiB, 1 * MiB, buf, 400) == 1          # larger than what is free
     assert fn(1000 * MiB, 180000 * MiB, 7000 * MiB, 0, buf, 400) == 0                # no floor configured: cudaMalloc decides
+
+
+def test_config_to_native_engine_flags():
+    from pocketllm_b200.config import Config
+    import pytest
+    cfg = Config.load(overrides=["model.path=/ckpt/qwen", "model.max_context=8192", "parallel.world=2", "speculative.mode=mtp",
+                                 "speculative.draft_len=3", "serving.native=true", "serving.port=9000", "model.tokenizer=/tok/dir",
+                                 "model.chat_format=qwen", "cache.cuda_graph=false"])
+    a = cfg.native_engine_args(rank=1)
+    assert a[:2] == ["--ckpt", "/ckpt/qwen"] and a[a.index("--tp-rank") + 1] == "1" and a[a.index("--tp-world") + 1] == "2"
+    assert "--no-cuda-graph" in a and a[a.index("--qwen-mtp-tokens") + 1] == "3"
+    assert a[a.index("--tokenizer") + 1] == "hf:/tok/dir" and a[a.index("--port") + 1] == "9000" and "--serve" in a
+    plain = Config.load(overrides=["model.path=/m"]).native_engine_args()
+    assert "--serve" not in plain and "--qwen-mtp-tokens" not in plain
+    with pytest.raises(ValueError):
+        Config.load(overrides=["speculative.mode=ngram"]).native_engine_args()
+    with pytest.raises(ValueError):
+        Config.load(overrides=["speculative.mode=dspark", "model.family=qwen_hybrid"])
+    Config.load(overrides=["speculative.mode=dspark", "model.family=deepseek_v4"])
