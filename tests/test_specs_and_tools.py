@@ -79,3 +79,16 @@ def test_imatrix_collect_merge(tmp_path):
 def test_prewarm_reads_all_bytes(files):
     r = prewarm.prewarm(files / "mm.gguf", chunk_mib=1)
     assert r["bytes"] == (files / "mm.gguf").stat().st_size and r["files"] == 1
+
+
+def test_minimax_rope_table_lookup_equals_direct_rotation():
+    """The device-table rotation used by the MiniMax runtime gives the values of the direct (fp64 angle) rotation."""
+    import torch
+    from pocketllm_b200.models.minimax_m2 import _rope, _rope_lookup, _rope_tables
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(7, 3, 128, generator=g)
+    pos = torch.tensor([0, 1, 5, 17, 63, 64, 99], dtype=torch.int32)
+    cos_t, sin_t = _rope_tables(128, 64, 5.0e6, "cpu")
+    assert cos_t.shape == (128, 32) and cos_t.dtype == torch.float32
+    assert torch.equal(_rope_lookup(x, pos, cos_t, sin_t, 64), _rope(x, pos, 64, 5.0e6))
+    assert torch.equal(_rope_lookup(x, pos, cos_t, sin_t, 64)[..., 64:], x[..., 64:])      # dims past rope_dim pass through
