@@ -11,6 +11,7 @@
 #include "mem_guard.hpp"
 #include "pk_kernels.h"
 #include "safetensors.hpp"
+#include "spec_policy.hpp"
 
 namespace pk {
 
@@ -1145,7 +1146,7 @@ void QwenEngine::spec_decode(int steps, int max_draft, int* out_host, QwenSpecSt
       ++st.plain_steps;
       continue;
     }
-    const int k = std::min(K, std::min(remaining - 1, max_draft));
+    const int k = drafts_this_round(K, remaining, max_draft);
     const int committed = pos_, input = last_token_;
     draft_tokens(k, input, (int)out.size(), drafts, st);
     update_snapshot(*txn_);
@@ -1173,7 +1174,7 @@ void QwenEngine::spec_decode(int steps, int max_draft, int* out_host, QwenSpecSt
     for (int i = 0; i < correct; ++i) out.push_back(drafts[i]);
     out.push_back(bonus);
     last_token_ = bonus;
-    K = correct == k ? std::min(2 * K, max_draft) : std::max(1, std::min(K / 2, correct + 1));
+    K = next_draft_len(K, k, correct, max_draft);
   }
   // a round may overshoot by nothing: k <= remaining - 1, so at most `remaining` tokens are added
   cuda_check(cudaEventRecord(ev1_, stream_), "event");

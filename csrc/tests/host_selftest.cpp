@@ -17,6 +17,7 @@
 #include "../engine/json.hpp"
 #include "../engine/safetensors.hpp"
 #include "../engine/sampler.hpp"
+#include "../engine/spec_policy.hpp"
 
 #define CHECK(cond)                                                             \
   do {                                                                          \
@@ -183,6 +184,36 @@ static int test_protocol() {
   return 0;
 }
 
+// Draft-length policy of speculative decode: a whole request simulated on the host.
+static int test_spec_policy() {
+  using pk::drafts_this_round;
+  using pk::next_draft_len;
+  CHECK(next_draft_len(1, 1, 1, 4) == 2 && next_draft_len(2, 2, 2, 4) == 4 && next_draft_len(4, 4, 4, 4) == 4);   // doubles up to the limit
+  CHECK(next_draft_len(4, 4, 0, 4) == 1 && next_draft_len(4, 4, 1, 4) == 2 && next_draft_len(4, 4, 3, 4) == 2);   // max(1, min(K/2, ok+1))
+  CHECK(next_draft_len(1, 1, 0, 4) == 1 && next_draft_len(7, 7, 6, 7) == 3);
+  CHECK(next_draft_len(4, 2, 2, 4) == 4);   // a round cut short by the end of the request still counts as accepted
+  CHECK(drafts_this_round(4, 10, 4) == 4 && drafts_this_round(4, 3, 4) == 2 && drafts_this_round(4, 1, 4) == 0 && drafts_this_round(2, 9, 1) == 1);
+  // every request length ends exactly, whatever the drafts are worth: perfect drafts, useless drafts, alternating
+  for (int pattern = 0; pattern < 3; ++pattern)
+    for (int steps = 1; steps <= 40; ++steps) {
+      int produced = 0, K = 1, rounds = 0;
+      while (produced < steps) {
+        const int k = drafts_this_round(K, steps - produced, 7);
+        if (k == 0) {
+          produced += 1;   // plain step
+          continue;
+        }
+        const int accepted = pattern == 0 ? k : pattern == 1 ? 0 : (rounds & 1 ? k : k / 2);
+        produced += accepted + 1;
+        K = next_draft_len(K, k, accepted, 7);
+        CHECK(K >= 1 && K <= 7);
+        ++rounds;
+      }
+      CHECK(produced == steps);
+    }
+  return 0;
+}
+
 int main(int argc, char** argv) {
   if (argc < 4) {
     std::fprintf(stderr, "usage: host_selftest file.gguf safetensors_dir scratch_dir\n");
@@ -194,6 +225,7 @@ int main(int argc, char** argv) {
     if (test_sampler()) return 1;
     if (test_control_plane(argv[3])) return 1;
     if (test_protocol()) return 1;
+    if (test_spec_policy()) return 1;
   } catch (const std::exception& e) {
     std::fprintf(stderr, "host_selftest: unexpected exception: %s\n", e.what());
     return 1;
