@@ -161,6 +161,19 @@ PK_EAPI int pk_qwen_copy_logits(void* h, float* out, int row) {
   return guarded([&] { ((pk::QwenEngine*)h)->copy_logits(out, row); });
 }
 
+// 1 when single-row decode steps run on the persistent whole-token kernel (known after the first decode call).
+PK_EAPI int pk_qwen_persistent_decode_active(void* h) { return ((pk::QwenEngine*)h)->persistent_decode_active() ? 1 : 0; }
+
+PK_EAPI int pk_qwen_set_persistent_decode(void* h, int mode) {
+  return guarded([&] { ((pk::QwenEngine*)h)->set_persistent_decode(mode); });
+}
+
+PK_EAPI int pk_qwen_decode_trace(void* h, unsigned long long* out, int cap) {
+  int n = 0;
+  guarded([&] { n = ((pk::QwenEngine*)h)->copy_decode_trace(out, cap); });
+  return n;
+}
+
 PK_EAPI int pk_qwen_vocab_local(void* h) { return ((pk::QwenEngine*)h)->vocab_local(); }
 PK_EAPI int pk_qwen_position(void* h) { return ((pk::QwenEngine*)h)->position(); }
 PK_EAPI int pk_qwen_last_token(void* h) { return ((pk::QwenEngine*)h)->last_token(); }

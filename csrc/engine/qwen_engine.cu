@@ -273,6 +273,8 @@ void QwenEngine::alloc_buffers() {
   off_epoch_ = off; off = align_up(off + 4, 256);
   off_status_ = off; off = align_up(off + 4, 256);
   off_counter_ = off; off = align_up(off + 4, 256);
+  // {value, sequence number} slots of the persistent decode kernel: [world][hidden] 8-byte words per site parity
+  for (int s = 0; s < 2; ++s) { off_ll_[s] = off; off = align_up(off + (size_t)W * hidden_ * 8, 256); }
   arena_bytes_ = off;
   arena_ = dalloc(arena_bytes_);
   cuda_check(cudaMemset(arena_, 0, std::min<size_t>(arena_bytes_, off_bslot_[0] + 4096)), "memset arena head");
@@ -300,6 +302,7 @@ void QwenEngine::set_peer_arenas(void* const* arenas) {
   cuda_check(cudaMemcpy(peer_cval_dev_, cv, sizeof cv, cudaMemcpyHostToDevice), "peer table");
   cuda_check(cudaMemcpy(peer_cidx_dev_, ci, sizeof ci, cudaMemcpyHostToDevice), "peer table");
   peers_set_ = true;
+  persistent_built_ = false;   // the kernel's parameter block holds peer addresses
   if (decode_graph_) {
     cudaGraphExecDestroy(decode_graph_);
     decode_graph_ = nullptr;
@@ -991,15 +994,190 @@ int QwenEngine::prefill(const int* tokens_host, int n) {
   return last_token_;
 }
 
+// The persistent kernel's view of the model: one descriptor per layer in device memory and a parameter block with
+// the activation buffers, the grid barrier words and every rank's slots and flags.
+void QwenEngine::build_persistent() {
+  persistent_built_ = true;
+  persistent_ok_ = false;
+  int mode = opt_.persistent_decode;
+  if (const char* v = getenv("POCKET_DECODE_PERSISTENT")) mode = atoi(v);
+  // The predictor's verify rows run on the per-projection kernels; plain decode then uses them too, so that both
+  // see the same rounding and speculative tokens equal plain ones.
+  if (mode == 0 || (mode < 0 && opt_.mtp)) return;
+  if (!peers_set_) throw std::runtime_error("peer arenas not registered");
+  int max_k = hidden_, max_rows = vocab_l_;
+  auto lin = [&](const Fp8Linear& l) {
+    PkDecLinear d{};
+    d.w = l.w;
+    d.scale = l.scale;
+    d.N = l.N;
+    d.K = l.K;
+    d.elem = 1;
+    max_k = std::max(max_k, l.K);
+    max_rows = std::max(max_rows, l.N);
+    return d;
+  };
+  std::vector<PkDecLayer> hl(cfg_.num_layers);
+  for (int i = 0; i < cfg_.num_layers; ++i) {
+    const QwenLayer& L = layers_[i];
+    PkDecLayer& d = hl[i];
+    memset(&d, 0, sizeof d);
+    d.full = L.full ? 1 : 0;
+    d.input_norm = L.input_norm;
+    d.post_norm = L.post_norm;
+    if (L.full) {
+      d.lin[0] = lin(L.qkv);
+      d.lin[1].elem = 2;
+      d.lin[1].K = hidden_;
+      d.lin[2] = lin(L.o_proj);
+      d.q_norm = L.q_norm;
+      d.k_norm = L.k_norm;
+      d.kcache = L.kcache;
+      d.vcache = L.vcache;
+    } else {
+      d.lin[0] = lin(L.in_proj);
+      d.lin[1].w = L.in_proj_ab;
+      d.lin[1].N = 2 * vh_l_;
+      d.lin[1].K = hidden_;
+      d.lin[1].elem = 2;
+      d.lin[2] = lin(L.out_proj);
+      d.conv_w = L.conv_w;
+      d.conv_state = L.conv_state;
+      d.A_log = L.A_log;
+      d.dt_bias = L.dt_bias;
+      d.lin_norm = L.lin_norm;
+      d.lin_state = L.lin_state;
+    }
+    d.lin[3] = lin(L.gate_up);
+    d.lin[4] = lin(L.down);
+  }
+  if (dec_layers_dev_ == nullptr) {
+    dec_layers_dev_ = (PkDecLayer*)dalloc(hl.size() * sizeof(PkDecLayer));
+    dec_o_raw_ = (float*)dalloc((size_t)std::max(vd_l_, 1) * sizeof(float));
+    dec_cand_val_ = (float*)dalloc((size_t)sm_count_ * sizeof(float));
+    dec_cand_idx_ = (int*)dalloc((size_t)sm_count_ * sizeof(int));
+    dec_bar_ = (unsigned long long*)dalloc(2 * sizeof(unsigned long long));
+    cuda_check(cudaMemset(dec_bar_, 0, 2 * sizeof(unsigned long long)), "memset");
+  }
+  cuda_check(cudaMemcpy(dec_layers_dev_, hl.data(), hl.size() * sizeof(PkDecLayer), cudaMemcpyHostToDevice), "decode table");
+
+  PkDecParams& p = dec_params_;
+  memset(&p, 0, sizeof p);
+  p.layers = dec_layers_dev_;
+  p.n_layers = cfg_.num_layers;
+  p.hidden = hidden_;
+  p.inter_l = inter_l_;
+  p.vocab_l = vocab_l_;
+  p.vocab_start = vocab_start_;
+  p.hq_l = hq_l_;
+  p.hkv_l = hkv_l_;
+  p.kh_l = kh_l_;
+  p.vh_l = vh_l_;
+  p.ld_proj = ld_proj_;
+  p.eps = (float)cfg_.rms_norm_eps;
+  p.rotary_dim = cfg_.rotary_dim();
+  p.theta = (float)cfg_.rope_theta;
+  p.ctx_cap = opt_.max_context;
+  p.max_splits = std::min(64, kSmallRows * opt_.decode_splits);
+  p.window = opt_.attention_window;
+  p.sink = opt_.attention_sink;
+  p.attn_gate = cfg_.attn_output_gate ? 1 : 0;
+  p.max_k = max_k;
+  p.max_rows = max_rows;
+  p.embed = embed_;
+  p.final_norm = final_norm_;
+  p.lm_head.w = lm_head_;
+  p.lm_head.scale = nullptr;
+  p.lm_head.N = vocab_l_;
+  p.lm_head.K = hidden_;
+  p.lm_head.elem = 2;
+  p.token = tokens_dev_;
+  p.pos = pos_dev_;
+  p.hidden_buf[0] = hidden_buf_[0];
+  p.hidden_buf[1] = hidden_buf_[1];
+  p.proj = proj_;
+  p.o_raw = dec_o_raw_;
+  p.attn_out = attn_out_;
+  p.mlp_h = mlp_h_;
+  p.attn_ws = attn_ws_;
+  p.logits = logits_;
+  p.norm_out = opt_.mtp ? tgt_hid_ : nullptr;
+  p.cand_val = dec_cand_val_;
+  p.cand_idx = dec_cand_idx_;
+  p.next_tok = next_tok_dev_;
+  p.out_tokens = out_tokens_dev_;
+  p.out_counter = out_counter_dev_;
+  p.out_cap = out_cap_;
+  p.bar_count = dec_bar_;
+  p.bar_base = dec_bar_ + 1;
+  p.world = opt_.tp_world;
+  p.rank = opt_.tp_rank;
+  for (int r = 0; r < opt_.tp_world; ++r) {
+    for (int s = 0; s < 2; ++s) p.slot[s][r] = (uint2*)((char*)peers_[r] + off_ll_[s]);
+    p.cand_val_peer[r] = (float*)((char*)peers_[r] + off_cval_);
+    p.cand_idx_peer[r] = (int*)((char*)peers_[r] + off_cidx_);
+    p.cand_flag[r] = (uint32_t*)((char*)peers_[r] + off_cflag_);
+  }
+  p.epoch = (const uint32_t*)((char*)arena_ + off_epoch_);
+  p.sites_per_epoch = sites_per_epoch_;
+  p.status = (uint32_t*)((char*)arena_ + off_status_);
+  p.timeout_us = opt_.comm_timeout_us;
+  if (const char* t = getenv("POCKET_DECODE_TRACE")) {
+    if (t[0] == '1' && dec_dbg_ == nullptr) {
+      dec_dbg_cap_ = 32 * cfg_.num_layers + 64;
+      dec_dbg_ = (unsigned long long*)dalloc((size_t)dec_dbg_cap_ * 2 * sizeof(unsigned long long));
+    }
+  }
+  if (dec_dbg_) cuda_check(cudaMemset(dec_dbg_, 0, (size_t)dec_dbg_cap_ * 2 * sizeof(unsigned long long)), "memset");
+  p.dbg = dec_dbg_;
+  p.dbg_cap = dec_dbg_cap_;
+  dec_grid_ = sm_count_;
+  persistent_ok_ = pk_decode_persistent_smem(&p, dec_grid_) != 0;
+  if (!persistent_ok_ && mode > 0) throw std::runtime_error("the persistent decode kernel does not take these shapes");
+}
+
+void QwenEngine::set_persistent_decode(int mode) {
+  opt_.persistent_decode = mode;
+  persistent_built_ = false;
+  if (decode_graph_) {
+    cudaStreamSynchronize(stream_);
+    cudaGraphExecDestroy(decode_graph_);
+    decode_graph_ = nullptr;
+  }
+}
+
+int QwenEngine::copy_decode_trace(unsigned long long* out, int cap) {
+  if (dec_dbg_ == nullptr) return 0;
+  cuda_check(cudaStreamSynchronize(stream_), "sync");
+  const int n = std::min(cap, dec_dbg_cap_);
+  cuda_check(cudaMemcpy(out, dec_dbg_, (size_t)n * 2 * sizeof(unsigned long long), cudaMemcpyDeviceToHost), "trace");
+  int used = 0;
+  while (used < n && out[2 * used + 1] != 0ull) ++used;
+  return used;
+}
+
+void QwenEngine::enqueue_decode_step() {
+  if (!persistent_built_) build_persistent();
+  if (persistent_ok_) {
+    check(pk_decode_persistent_prepare((uint32_t*)((char*)arena_ + off_epoch_), next_tok_dev_, tokens_dev_, dec_bar_, dec_bar_ + 1, stream_),
+          "decode prepare");
+    check(pk_decode_persistent_step(&dec_params_, dec_grid_, stream_), "persistent decode step");
+    return;
+  }
+  check(pk_copy_int(next_tok_dev_, tokens_dev_, 1, stream_), "copy token");
+  run_small(1, true);
+  check(pk_add_int(pos_dev_, 1, 1, stream_), "advance pos");
+  check(pk_store_token(next_tok_dev_, out_tokens_dev_, out_counter_dev_, out_cap_, stream_), "store token");
+}
+
 void QwenEngine::capture_decode_graph() {
   cudaGraph_t g = nullptr;
+  if (!persistent_built_) build_persistent();   // allocations and copies stay outside the capture
   const long long l0 = launches_;
   cuda_check(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal), "begin capture");
   try {
-    check(pk_copy_int(next_tok_dev_, tokens_dev_, 1, stream_), "copy token");
-    run_small(1, true);
-    check(pk_add_int(pos_dev_, 1, 1, stream_), "advance pos");
-    check(pk_store_token(next_tok_dev_, out_tokens_dev_, out_counter_dev_, out_cap_, stream_), "store token");
+    cur_ = 0;
+    enqueue_decode_step();
   } catch (...) {
     cudaStreamEndCapture(stream_, &g);
     if (g) cudaGraphDestroy(g);
@@ -1033,10 +1211,7 @@ void QwenEngine::decode(int steps, int* out_host, bool sync_each_step) {
       launches_ += graph_nodes_;
     } else {
       cur_ = 0;
-      check(pk_copy_int(next_tok_dev_, tokens_dev_, 1, stream_), "copy token");
-      run_small(1, true);
-      check(pk_add_int(pos_dev_, 1, 1, stream_), "advance pos");
-      check(pk_store_token(next_tok_dev_, out_tokens_dev_, out_counter_dev_, out_cap_, stream_), "store token");
+      enqueue_decode_step();
     }
     if (sync_each_step) {
       cuda_check(cudaMemcpyAsync(pinned_tok_ + s, next_tok_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h");

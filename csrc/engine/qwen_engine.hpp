@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "../common/pk_comm_types.h"
+#include "../kernels/pk_decode_persistent.h"
 #include "qwen_config.hpp"
 
 namespace pk {
@@ -35,6 +36,10 @@ struct QwenEngineOptions {
   int prefill_bf16_shadow = -1;
   // Multi-token predictor (`mtp.*` tensors: two input norms, fc, one full-attention layer, norm) for speculative decoding.
   bool mtp = false;
+  // Single-row decode steps as one persistent cooperative kernel per token (weights ring that never drains, grid and
+  // peer-flag barriers instead of kernel boundaries): -1 = when the shapes fit its shared-memory plan, 0 = never
+  // (one launch per projection), 1 = required. POCKET_DECODE_PERSISTENT in the environment overrides.
+  int persistent_decode = -1;
 };
 
 // Counters of spec_decode().
@@ -142,6 +147,13 @@ class QwenEngine {
   const QwenEngineOptions& options() const { return opt_; }
   size_t weight_bytes() const { return weight_bytes_; }
   size_t shadow_bytes() const { return shadow_bytes_; }
+  // true once a decode step has been planned on the persistent kernel
+  bool persistent_decode_active() const { return persistent_built_ && persistent_ok_; }
+  // -1 automatic, 0 one launch per projection, 1 persistent kernel required; takes effect at the next decode.
+  void set_persistent_decode(int mode);
+  // Phase trace of the last persistent decode step (POCKET_DECODE_TRACE=1 when the engine first decodes): up to `cap`
+  // pairs {phase id, ns}; returns the number of pairs.
+  int copy_decode_trace(unsigned long long* out, int cap);
   cudaStream_t stream() const { return stream_; }
 
   // Recurrent-state snapshot (DeltaNet state + conv tails of every linear layer); KV is
@@ -174,6 +186,8 @@ class QwenEngine {
   void draft_tokens(int count, int input_token, int produced, std::vector<int>& drafts, QwenSpecStats& st);
   void alloc_layer(QwenLayer& L, bool full);
   void capture_decode_graph();
+  void enqueue_decode_step();      // one greedy single-row step on stream_ (persistent kernel or per-projection launches)
+  void build_persistent();         // descriptor table and parameters of the persistent decode kernel
   PkWait make_wait(int site) const;
   PkPush make_push(int site, bool big = false) const;
   float* slot_parts(int site, bool big = false) const;
@@ -227,6 +241,7 @@ class QwenEngine {
   void* arena_ = nullptr;
   size_t arena_bytes_ = 0;
   size_t off_bslot_[2];   // prefill-size slots [world][rows_cap][hidden] fp32
+  size_t off_ll_[2];
   size_t off_slot_[2], off_flag_[2], off_cval_, off_cidx_, off_cflag_, off_epoch_, off_status_, off_counter_;
   void* peers_[PK_MAX_RANKS] = {nullptr};
   float** peer_cval_dev_ = nullptr;
@@ -258,6 +273,19 @@ class QwenEngine {
   bool mtp_ready_ = false;
   std::unique_ptr<Snapshot> txn_;
   std::vector<int> replay_;
+
+  // persistent decode kernel
+  bool persistent_built_ = false;
+  bool persistent_ok_ = false;
+  PkDecParams dec_params_{};
+  PkDecLayer* dec_layers_dev_ = nullptr;
+  float* dec_o_raw_ = nullptr;
+  float* dec_cand_val_ = nullptr;
+  int* dec_cand_idx_ = nullptr;
+  unsigned long long* dec_bar_ = nullptr;   // [0] arrival counter, [1] its value before the current step
+  unsigned long long* dec_dbg_ = nullptr;   // phase trace of the last step (POCKET_DECODE_TRACE=1)
+  int dec_dbg_cap_ = 0;
+  int dec_grid_ = 0;
 
   int pos_ = 0;
   int last_token_ = -1;

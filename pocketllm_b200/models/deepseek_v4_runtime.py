@@ -326,6 +326,8 @@ class DSV4Runtime:
 
     def forward_rows(self, tokens: Sequence[int]) -> list[int]:
         nxt = self.forward_logits(tokens).argmax(-1).tolist()
+        # collective verdict on the peer all-reduces of this forward: raises on every rank, no token is returned
+        self.combine.check_step("cuda")
         self.last_token = nxt[-1]
         return nxt
 

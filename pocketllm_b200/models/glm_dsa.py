@@ -377,8 +377,14 @@ class GLMDSAModel:
             raise ValueError("context exceeds max_context")
         return _forward(self.cfg, self.w, self.cache, self, list(tokens), self._lin)
 
+    def _checked(self, token: int) -> int:
+        """The step's token, or `StepFailed` on every rank when a peer all-reduce timed out (collective check)."""
+        if self._combiner is not None:
+            self._combiner.check_step(self.device)
+        return token
+
     def prefill(self, tokens: Sequence[int]) -> int:
-        return int(torch.argmax(self.forward(tokens)))
+        return self._checked(int(torch.argmax(self.forward(tokens))))
 
     def decode_one(self, token: int) -> int:
-        return int(torch.argmax(self.forward([token])))
+        return self._checked(int(torch.argmax(self.forward([token]))))

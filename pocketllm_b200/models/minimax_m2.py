@@ -390,9 +390,16 @@ class MiniMaxM2Model:
         return go.gguf_linear(h[-1:], self.head, self.types["output.weight"], c.vocab_size, gamma=self.final_norm, eps=c.norm_eps, epi=2)[0]
 
     # protocol of the generic generation runtime
+    def _checked(self, token: int) -> int:
+        """The step's token, or `StepFailed` on every rank when a peer all-reduce timed out (collective check; the
+        token was read from the device just before, so the step is complete)."""
+        if self._combiner is not None:
+            self._combiner.check_step(self.device)
+        return token
+
     def prefill(self, tokens: Sequence[int]) -> int:
         t = torch.tensor(list(tokens), dtype=torch.int32, device=self.device)
-        return int(torch.argmax(self.forward(t)))
+        return self._checked(int(torch.argmax(self.forward(t))))
 
     @torch.no_grad()
     def _capture_decode(self) -> None:
@@ -413,7 +420,7 @@ class MiniMaxM2Model:
 
     def decode_one(self, token: int) -> int:
         if not self.use_graph:
-            return int(torch.argmax(self.forward(torch.tensor([token], dtype=torch.int32, device=self.device))))
+            return self._checked(int(torch.argmax(self.forward(torch.tensor([token], dtype=torch.int32, device=self.device)))))
         if self.pos + 1 > self.max_context:
             raise ValueError("context exceeds max_context")
         if self._graph is None:
@@ -422,4 +429,9 @@ class MiniMaxM2Model:
         self._pos_buf.fill_(self.pos)
         self._graph.replay()
         self.pos += 1
-        return int(self._next_buf)
+        nxt = int(self._next_buf)
+        try:
+            return self._checked(nxt)
+        except TimeoutError:
+            self._graph = None     # the captured graph holds the peer all-reduce; recapture on the NCCL path
+            raise

@@ -377,7 +377,10 @@ class QwenEngine:
 
     def __init__(self, cfg: QwenHybridConfig | str, *, tp_rank: int = 0, tp_world: int = 1, device: int = 0,
                  max_context: int = 4096, prefill_chunk: int = 512, use_cuda_graph: bool = True, decode_splits: int = 0,
-                 mtp: bool = False):
+                 mtp: bool = False, persistent_decode: int | None = None):
+        """`persistent_decode`: 1 runs every single-row decode step as one persistent kernel, 0 as one launch per
+        projection (the kernels that also serve verify rows, so speculative loops that compare tokens of the two must use
+        0), None lets the engine choose."""
         self._L = _lib.engine()
         L = self._L
         L.pk_qwen_create_ex.restype = ctypes.c_void_p
@@ -397,6 +400,8 @@ class QwenEngine:
         if not self._h:
             raise EngineError(L.pk_engine_last_error().decode())
         self._h = ctypes.c_void_p(self._h)
+        if persistent_decode is not None:
+            self._ck(L.pk_qwen_set_persistent_decode(self._h, int(persistent_decode)))
 
     def _ck(self, status: int) -> None:
         if status != 0:
@@ -540,6 +545,30 @@ class QwenEngine:
     def prefill_shadow_bytes(self) -> int:
         """Bytes of the bf16 weight copies used by the tensor-core prefill path (0 when off)."""
         return int(self._L.pk_qwen_shadow_bytes(self._h))
+
+    @property
+    def persistent_decode(self) -> bool:
+        """True when single-row decode steps run as one persistent kernel per token (known after the first `decode`).
+        `POCKET_DECODE_PERSISTENT=0` in the environment keeps one launch per projection."""
+        return bool(self._L.pk_qwen_persistent_decode_active(self._h))
+
+    PHASE_NAMES = {0: "start", 1: "stage_norm", 8: "stage_plain", 9: "stage_headnorm", 10: "in_proj", 11: "in_proj_ab", 12: "out_proj",
+                   13: "gate_up", 14: "down", 20: "lm_head", 3: "grid_barrier", 4: "site_barrier", 5: "deltanet", 6: "attn_split",
+                   7: "attn_merge"}
+
+    def decode_trace(self) -> dict[str, float]:
+        """Microseconds block 0 spent per phase kind in the last persistent decode step (engine created with
+        `POCKET_DECODE_TRACE=1` in the environment); empty otherwise."""
+        cap = 4096
+        buf = (ctypes.c_ulonglong * (2 * cap))()
+        n = self._L.pk_qwen_decode_trace(self._h, buf, cap)
+        out: dict[str, float] = {}
+        for i in range(1, n):
+            name = self.PHASE_NAMES.get(int(buf[2 * i]), str(int(buf[2 * i])))
+            out[name] = out.get(name, 0.0) + (buf[2 * i + 1] - buf[2 * i - 1]) / 1e3
+        if n > 1:
+            out["total"] = (buf[2 * n - 1] - buf[1]) / 1e3
+        return out
 
     def comm_status(self) -> int:
         return int(self._L.pk_qwen_comm_status(self._h)) & 0xFFFFFFFF

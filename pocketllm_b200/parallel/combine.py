@@ -1,19 +1,31 @@
 """Sum of per-rank expert outputs: peer-memory all-reduce when the payload fits its arena (decode rows and
-moderate prefill chunks), NCCL otherwise or when the peer path reported a timeout."""
+moderate prefill chunks), NCCL otherwise or after the peer path reported a timeout.
+
+A peer wait that runs out leaves a sticky status word on the rank that waited; later peer all-reduces of that rank
+return without reducing, so the step's result is wrong on at least one rank. `check_step()` is therefore called by
+the model runtimes once per forward, after the step's device synchronisation and before any token is returned: it
+takes the MAX of the status words over the group, so every rank reaches the same verdict, and on a failure every
+rank clears its word, drops the peer path (NCCL from then on) and raises `StepFailed`. Reference behaviour:
+src/models/deepseek_v4/runtime.py:4191-4196 (custom all-reduce timeout -> NCCL)."""
 from __future__ import annotations
 
 import torch
 import torch.distributed as dist
 
-from .peer_allreduce import PeerAllReduce
+
+class StepFailed(TimeoutError):
+    """The current step must be discarded: a peer all-reduce of some rank gave up waiting."""
 
 
 class ExpertCombine:
-    def __init__(self, world: int, group=None, capacity: int = 4 << 20, use_peer: bool = True):
+    def __init__(self, world: int, group=None, capacity: int = 4 << 20, use_peer: bool = True, peer=None):
+        """`peer`: an object with `all_reduce`, `status(clear=False)` and `capacity` (tests inject one)."""
         self.world, self.group = world, group
-        self.peer: PeerAllReduce | None = None
+        self.peer = peer
         self.calls = {"peer": 0, "nccl": 0}
-        if world > 1 and use_peer:
+        self.fallbacks = 0
+        if world > 1 and use_peer and peer is None:
+            from .peer_allreduce import PeerAllReduce
             self.peer = PeerAllReduce(capacity, group)
 
     def __call__(self, y: torch.Tensor) -> torch.Tensor:
@@ -27,9 +39,25 @@ class ExpertCombine:
         dist.all_reduce(y, group=self.group)
         return y
 
+    def check_step(self, device: torch.device | str | None = None) -> None:
+        """Collective over the group (every rank calls it once per forward, also ranks whose own word is clean).
+        Raises `StepFailed` on every rank when any rank's peer wait ran out; the peer path is off afterwards."""
+        if self.world == 1 or self.peer is None:
+            return
+        local = int(self.peer.status())
+        if device is None:
+            device = "cuda" if dist.get_backend(self.group) == "nccl" else "cpu"
+        word = torch.tensor([local], dtype=torch.int32, device=device)
+        dist.all_reduce(word, op=dist.ReduceOp.MAX, group=self.group)
+        worst = int(word.item())
+        if worst == 0:
+            return
+        self.peer.status(clear=True)
+        self.peer = None
+        self.fallbacks += 1
+        raise StepFailed(f"a peer all-reduce gave up waiting (status {worst}, this rank {local}): the step is discarded "
+                         "and the following steps use NCCL")
+
+    # kept for callers of the earlier, rank-local API
     def check(self) -> None:
-        """Raise if a peer wait ran out since the last check; the peer path is switched off after that."""
-        if self.peer is not None and self.peer.status() != 0:
-            self.peer.status(clear=True)
-            self.peer = None
-            raise TimeoutError("peer all-reduce timed out; falling back to NCCL for the following steps")
+        self.check_step()
