@@ -42,14 +42,15 @@ __device__ __forceinline__ float* slot(float* arena, size_t capacity, int world,
 __device__ __forceinline__ uint32_t* ctl(float* arena, size_t capacity, int world) {
   return reinterpret_cast<uint32_t*>(arena + (size_t)2 * world * capacity);
 }
-// ctl layout: flags[2][world], seq, done, status
+// ctl layout: flags[2][world], seq, pushed, status, left
 
 __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ParParams p) {
   float* mine = p.slot_base[p.rank];
   uint32_t* c = ctl(mine, p.capacity, p.world);
   uint32_t* seq_p = c + 2 * p.world;
-  uint32_t* done_p = seq_p + 1;
+  uint32_t* pushed_p = seq_p + 1;   // blocks that have stored their part (first pass)
   uint32_t* status_p = seq_p + 2;
+  uint32_t* left_p = seq_p + 3;     // blocks that have finished reading (second pass)
   const uint32_t seq = *((volatile uint32_t*)seq_p) + 1u;
   const int parity = (int)(seq & 1u);
   const size_t n4 = p.n >> 2;
@@ -68,8 +69,11 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ParParams p) 
   // 2. publish (last block)
   __shared__ bool s_ok;
   if (threadIdx.x == 0) {
-    const uint32_t done = atomicAdd(done_p, 1u) + 1u;
-    if (done == gridDim.x) {
+    // Two counters: with one, a block that skips the wait (status already set) could add its second-pass
+    // increment before another block's first-pass one, and "every block has pushed" would be declared early.
+    const uint32_t pushed = atomicAdd(pushed_p, 1u) + 1u;
+    if (pushed == gridDim.x) {
+      *pushed_p = 0u;   // every block has added exactly once: re-arm for the next launch
       __threadfence_system();
       for (int r = 0; r < p.world; ++r)
         st_release_sys(ctl(p.slot_base[r], p.capacity, p.world) + parity * p.world + p.rank, seq);
@@ -106,13 +110,12 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ParParams p) 
       p.out[i] = a;
     }
   }
-  // The last block to leave advances the sequence number and re-arms the counter. A second counter
-  // pass is needed: `done` reaching gridDim.x only says that every block has pushed.
+  // The last block to leave advances the sequence number and re-arms its counter.
   __syncthreads();
   if (threadIdx.x == 0) {
-    const uint32_t left = atomicAdd(done_p, 1u) + 1u;
-    if (left == 2u * gridDim.x) {
-      *done_p = 0u;
+    const uint32_t left = atomicAdd(left_p, 1u) + 1u;
+    if (left == gridDim.x) {
+      *left_p = 0u;
       *seq_p = seq;
       __threadfence();
     }

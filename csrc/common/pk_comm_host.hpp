@@ -62,4 +62,27 @@ inline bool host_allreduce(std::vector<HostArena*>& arenas, int rank, const floa
   return ok;
 }
 
+// Host model of the block counters of one launch of the peer all-reduce kernel. Every block makes two
+// announcements: "my part is stored" (first pass) and "I am done reading" (second pass). The flag may be published
+// only when EVERY block has stored. `two_counters == false` models a single shared counter compared against the
+// grid size: a block that skips its wait (the status word was already set) can make its second announcement before
+// another block's first, and the count reaches the grid size too early. Returns the number of blocks that had
+// stored when the publish decision fired, or -1 when it never fired.
+struct BlockEvent { int block; int pass; };   // pass 1 or 2, in the order the atomics are served
+inline int stored_at_publish(int grid, const std::vector<BlockEvent>& order, bool two_counters) {
+  int pushed = 0, left = 0, shared = 0, stored = 0;
+  for (const BlockEvent& e : order) {
+    if (e.pass == 1) ++stored;
+    if (two_counters) {
+      if (e.pass == 1) { if (++pushed == grid) return stored; }
+      else ++left;
+    } else {
+      if (++shared == grid && e.pass == 1) return stored;   // the kernel publishes from the first-pass increment only
+    }
+  }
+  (void)left;
+  return -1;
+}
+
+
 }  // namespace pk

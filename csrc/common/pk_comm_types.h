@@ -30,4 +30,6 @@ struct PkWait {
 };
 
 #define PK_COMM_TIMEOUT 1u
+// another rank reported a timeout in the same step (learned through the sampler exchange)
+#define PK_COMM_PEER_FAILED 4u
 

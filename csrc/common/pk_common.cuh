@@ -154,6 +154,33 @@ __device__ __forceinline__ uint2 ld_stream_u2(const void* p) {
 
 }  // namespace pk
 
+// Per-device one-time set-up of a kernel (cudaFuncSetAttribute applies to the current device only, so a process that
+// drives several GPUs must repeat it on each). Usage:
+//   static PkDeviceOnce once;
+//   if (PkDeviceOnceGuard g{once}; g.needed()) { ...set attributes...; g.done(); }
+// The guard holds the object's mutex for the length of the if statement, so two host threads cannot race.
+struct PkDeviceOnce {
+  std::mutex mu;
+  unsigned long long configured[4] = {0, 0, 0, 0};   // one bit per device ordinal (256 devices)
+};
+class PkDeviceOnceGuard {
+ public:
+  explicit PkDeviceOnceGuard(PkDeviceOnce& o) : o_(o), lock_(o.mu) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+    word_ = (dev >> 6) & 3;
+    bit_ = 1ull << (dev & 63);
+  }
+  bool needed() const { return (o_.configured[word_] & bit_) == 0ull; }
+  void done() { o_.configured[word_] |= bit_; }
+
+ private:
+  PkDeviceOnce& o_;
+  std::lock_guard<std::mutex> lock_;
+  int word_ = 0;
+  unsigned long long bit_ = 1ull;
+};
+
 // On by default (about 4% on the 27B decode graph in same-box A/B runs); POCKET_PDL=0 in the
 // environment falls back to plain stream order.
 PK_API int pk_pdl_enabled();
@@ -161,14 +188,20 @@ PK_API int pk_pdl_enabled();
 // Every kernel of the decode graph asks for the same shared-memory carve-out (the maximum): a kernel
 // boundary where the preferred L1 / shared split changes makes the SMs drain and reconfigure.
 inline void pk_prefer_max_smem(const void* fn) {
-  static const void* seen[256];
+  static const void* seen_fn[1024];
+  static int seen_dev[1024];
   static int n = 0;
   static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
   std::lock_guard<std::mutex> lock(mu);
   for (int i = 0; i < n; ++i)
-    if (seen[i] == fn) return;
+    if (seen_fn[i] == fn && seen_dev[i] == dev) return;   // the hint belongs to one device
   cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  if (n < 256) seen[n++] = fn;
+  if (n < 1024) {
+    seen_fn[n] = fn;
+    seen_dev[n++] = dev;
+  }
 }
 
 // Launch through cudaLaunchKernelEx; `pdl` adds programmatic stream serialization (see pdl_wait /

@@ -45,10 +45,12 @@ class Cursor {
     return s;
   }
   uint64_t offset() const { return off_; }
+  uint64_t remaining() const { return n_ - off_; }
 
  private:
+  // written so that a huge `k` from an untrusted file cannot wrap around
   void need(uint64_t k) const {
-    if (off_ + k > n_) throw std::runtime_error("gguf: truncated file");
+    if (k > n_ - off_) throw std::runtime_error("gguf: truncated file");
   }
   const uint8_t* p_;
   uint64_t n_, off_ = 0;
@@ -69,6 +71,8 @@ Json read_value(Cursor& c, uint32_t type, int depth) {
       if (depth > 4) throw std::runtime_error("gguf: arrays nested too deeply");
       const uint32_t et = c.get<uint32_t>();
       const uint64_t n = c.get<uint64_t>();
+      // every element takes at least one byte: a count beyond the bytes left is a corrupt file, not a reservation
+      if (n > c.remaining()) throw std::runtime_error("gguf: array length exceeds the file");
       Json arr = Json::array();
       arr.items().reserve((size_t)n);
       for (uint64_t i = 0; i < n; ++i) arr.push_back(read_value(c, et, depth + 1));
@@ -85,7 +89,10 @@ Json read_value(Cursor& c, uint32_t type, int depth) {
 
 uint64_t GgufTensor::elements() const {
   uint64_t n = 1;
-  for (uint64_t d : dims) n *= d;
+  for (uint64_t d : dims) {
+    if (d != 0 && n > UINT64_MAX / d) throw std::runtime_error("gguf: tensor " + name + " has more elements than fit 64 bits");
+    n *= d;
+  }
   return n;
 }
 
@@ -101,12 +108,30 @@ std::pair<uint32_t, uint32_t> ggml_type_block(uint32_t type) {
   return {0, 0};
 }
 
+void GgufFile::release() {
+  if (base_) munmap((void*)base_, size_);
+  if (fd_ >= 0) ::close(fd_);
+  base_ = nullptr;
+  fd_ = -1;
+}
+
 GgufFile::GgufFile(const std::string& path) : path_(path) {
   fd_ = ::open(path.c_str(), O_RDONLY);
   if (fd_ < 0) throw std::runtime_error("gguf: cannot open " + path);
+  // a constructor that throws does not run the destructor: the descriptor and the mapping are released here
+  try {
+    parse(path);
+  } catch (...) {
+    release();
+    throw;
+  }
+}
+
+void GgufFile::parse(const std::string& path) {
   struct stat st;
   if (fstat(fd_, &st) != 0) throw std::runtime_error("gguf: cannot stat " + path);
   size_ = (uint64_t)st.st_size;
+  if (size_ < 24) throw std::runtime_error("gguf: file too small: " + path);
   void* m = mmap(nullptr, size_, PROT_READ, MAP_PRIVATE, fd_, 0);
   if (m == MAP_FAILED) throw std::runtime_error("gguf: mmap failed for " + path);
   base_ = (const uint8_t*)m;
@@ -122,6 +147,8 @@ GgufFile::GgufFile(const std::string& path) : path_(path) {
   }
   alignment_ = (uint64_t)meta_.get_int("general.alignment", 32);
   if (alignment_ == 0 || (alignment_ & (alignment_ - 1))) throw std::runtime_error("gguf: alignment is not a power of two");
+  // a tensor entry takes at least 24 bytes (name length, rank, type, offset)
+  if (n_tensors > c.remaining() / 24) throw std::runtime_error("gguf: tensor count exceeds the file");
   tensors_.reserve((size_t)n_tensors);
   for (uint64_t i = 0; i < n_tensors; ++i) {
     GgufTensor t;
@@ -134,21 +161,27 @@ GgufFile::GgufFile(const std::string& path) : path_(path) {
     const auto blk = ggml_type_block(t.type);
     if (blk.first == 0) throw std::runtime_error("gguf: tensor " + t.name + " has unknown type " + std::to_string(t.type));
     if (t.dims.empty() || t.dims[0] % blk.first) throw std::runtime_error("gguf: tensor " + t.name + " row is not a whole number of blocks");
-    t.nbytes = t.elements() / blk.first * blk.second;
+    const uint64_t blocks = t.elements() / blk.first;
+    if (blocks > UINT64_MAX / blk.second) throw std::runtime_error("gguf: tensor " + t.name + " is larger than 64 bits of bytes");
+    t.nbytes = blocks * blk.second;
     index_[t.name] = tensors_.size();
     tensors_.push_back(std::move(t));
   }
   data_offset_ = (c.offset() + alignment_ - 1) / alignment_ * alignment_;
+  if (data_offset_ > size_) {
+    if (!tensors_.empty()) throw std::runtime_error("gguf: the data section starts past the end of the file");
+    data_offset_ = size_;
+  }
+  const uint64_t data_bytes = size_ - data_offset_;
   for (const auto& t : tensors_) {
     if (t.offset % alignment_) throw std::runtime_error("gguf: tensor " + t.name + " is not aligned");
-    if (data_offset_ + t.offset + t.nbytes > size_) throw std::runtime_error("gguf: tensor " + t.name + " runs past the end of the file");
+    // subtraction form: an offset near 2^64 cannot wrap the sum back into range
+    if (t.offset > data_bytes || t.nbytes > data_bytes - t.offset)
+      throw std::runtime_error("gguf: tensor " + t.name + " runs past the end of the file");
   }
 }
 
-GgufFile::~GgufFile() {
-  if (base_) munmap((void*)base_, size_);
-  if (fd_ >= 0) ::close(fd_);
-}
+GgufFile::~GgufFile() { release(); }
 
 const GgufTensor* GgufFile::find(const std::string& name) const {
   auto it = index_.find(name);

@@ -43,6 +43,8 @@ class GgufFile {
   uint64_t file_size() const { return size_; }
 
  private:
+  void parse(const std::string& path);
+  void release();
   std::string path_;
   int fd_ = -1;
   const uint8_t* base_ = nullptr;

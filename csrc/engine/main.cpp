@@ -172,10 +172,23 @@ class QwenTokenEngine : public pk::TokenEngine {
     e_.reset();
     buf_.clear();
     buf_pos_ = 0;
-    const int first = e_.prefill(prompt.data(), (int)prompt.size());
-    return host_sampling_ ? resample(first) : first;
+    try {
+      const int first = e_.prefill(prompt.data(), (int)prompt.size());
+      return host_sampling_ ? resample(first) : first;
+    } catch (const pk::CommTimeout& t) {
+      throw pk::EngineStepFailed(t.what());   // HTTP 500; the status words are already cleared
+    }
   }
   int next() override {
+    try {
+      return next_token();
+    } catch (const pk::CommTimeout& t) {
+      buf_.clear();
+      buf_pos_ = 0;
+      throw pk::EngineStepFailed(t.what());
+    }
+  }
+  int next_token() {
     if (!host_sampling_ && e_.mtp_enabled()) {
       if (buf_pos_ < buf_.size()) return buf_[buf_pos_++];
       const int room = e_.options().max_context - e_.position() - 10;

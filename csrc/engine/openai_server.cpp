@@ -107,7 +107,13 @@ class ScriptedEngine : public TokenEngine {
     pos_ = 0;
     return next();
   }
-  int next() override { return pos_ < cps_.size() ? cps_[pos_++] : 0; }
+  int next() override {
+    if (pos_ < cps_.size() && cps_[pos_] == 0x2620) {
+      ++pos_;
+      throw EngineStepFailed("scripted step failure");
+    }
+    return pos_ < cps_.size() ? cps_[pos_++] : 0;
+  }
 
  private:
   std::vector<int> cps_;
@@ -238,15 +244,18 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
       endq["op"] = Json("end");
       endq["finish_reason"] = Json("stop");
       sidecar.call(endq);
+      const bool lost = dynamic_cast<const EngineStepFailed*>(&e) != nullptr;
       if (!stream) {
-        res.send(400, "application/json", error_json(e.what(), "invalid_request_error"));
+        res.send(lost ? 500 : 400, "application/json", error_json(e.what(), lost ? "engine_error" : "invalid_request_error"));
       } else {
-        res.event(error_json(e.what(), "invalid_request_error"));
+        res.event(error_json(e.what(), lost ? "engine_error" : "invalid_request_error"));
         res.event("[DONE]");
         res.end_sse();
       }
       return;
     }
+    bool step_lost = false;
+    std::string step_error;
     while (true) {
       ++generated;
       bool is_eos = false;
@@ -270,7 +279,28 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
         break;
       }
       if (generated >= max_tokens) break;
-      tok = engine.next();
+      try {
+        tok = engine.next();
+      } catch (const std::exception& e) {
+        // the step's result is gone (a rank timed out, or the engine refused): nothing of it is sent
+        step_lost = true;
+        step_error = e.what();
+        break;
+      }
+    }
+    if (step_lost) {
+      Json endq = Json::object();
+      endq["op"] = Json("end");
+      endq["finish_reason"] = Json("stop");
+      sidecar.call(endq);
+      if (!stream) {
+        res.send(500, "application/json", error_json(step_error, "engine_error"));
+      } else {
+        res.event(error_json(step_error, "engine_error"));
+        res.event("[DONE]");
+        res.end_sse();
+      }
+      return;
     }
     Json endq = Json::object();
     endq["op"] = Json("end");

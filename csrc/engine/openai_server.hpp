@@ -8,6 +8,7 @@
 
 #include <atomic>
 #include <memory>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -16,6 +17,13 @@
 #include "sampler.hpp"
 
 namespace pk {
+
+// Thrown by a TokenEngine when the result of a step must be discarded (for example a peer-memory wait that ran out
+// on some rank): the request ends with HTTP 500 (or an error event on a stream), no further token of it is sent and the
+// next request starts from a fresh state.
+struct EngineStepFailed : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
 
 // What the server needs from a model.
 class TokenEngine {
@@ -50,6 +58,7 @@ struct OpenAIServerOptions {
 void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, const OpenAIServerOptions& opt);
 
 // Deterministic stand-in for a model: replays `script` code points, then token 0 (EOS), for every request.
+// The code point U+2620 in the script makes that step throw EngineStepFailed (to test the error path).
 std::unique_ptr<TokenEngine> make_scripted_engine(const std::string& script, int max_context);
 
 }  // namespace pk

@@ -68,9 +68,9 @@ int pk_fill_f32_gauss(float* w, size_t n, float mean, float sigma, uint64_t seed
 int pk_iota_int(int* p, int n, const int* base_dev, int base_host, cudaStream_t stream);
 int pk_store_token(const int* token, int* out, int* counter, int cap, cudaStream_t stream);
 int pk_cand_push(const float* val, const int* idx, int M, const PkPush* push, float* const* peer_val,
-                 int* const* peer_idx, cudaStream_t stream);
+                 int* const* peer_idx, const uint32_t* status, int stride, cudaStream_t stream);
 int pk_cand_merge_wait(const float* cand_val, const int* cand_idx, int M, int world, const PkWait* wait,
-                       int* out_idx, cudaStream_t stream);
+                       int* out_idx, uint32_t* status, int stride, cudaStream_t stream);
 int pk_fp8_to_bf16(const void* w, const float* scale, int N, int K, void* out, cudaStream_t stream);
 int pk_gemm_bf16(const void* A, int lda, const void* W, int M, int N, int K, int epi, void* C, const void* resid, int ldc,
                  uint32_t* status, const PkPush* push, int sm_count, cudaStream_t stream);

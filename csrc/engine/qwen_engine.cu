@@ -20,6 +20,7 @@ namespace {
 constexpr int kHeadDim = 128;
 constexpr int kSmallRows = 8;
 constexpr int kArgmaxBlocks = 64;
+constexpr int kCandStride = 32;   // sampler candidates per rank in the exchange arrays; entry 31 of the index row is the rank's status word
 
 void cuda_check(cudaError_t e, const char* what) {
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
@@ -258,6 +259,8 @@ void QwenEngine::alloc_buffers() {
     mtp_seed_ = mtp_out_;
   }
   cuda_check(cudaMallocHost((void**)&pinned_tok_, (size_t)std::max<int>(rows_cap_, out_cap_) * sizeof(int)), "pinned");
+  cuda_check(cudaMallocHost((void**)&pinned_status_, 2 * sizeof(uint32_t)), "pinned");
+  pinned_status_[0] = pinned_status_[1] = 0u;
 
   // comm arena: [slot0][slot1][flags0][flags1][cand val][cand idx][cand flags][epoch][status][counter]
   const int W = opt_.tp_world;
@@ -267,8 +270,8 @@ void QwenEngine::alloc_buffers() {
   for (int s = 0; s < 2; ++s) { off_flag_[s] = off; off = align_up(off + PK_MAX_RANKS * 4, 256); }
   const size_t bslot_bytes = W > 1 ? (size_t)W * rows_cap_ * hidden_ * sizeof(float) : 0;
   for (int s = 0; s < 2; ++s) { off_bslot_[s] = off; off = align_up(off + bslot_bytes, 256); }
-  off_cval_ = off; off = align_up(off + (size_t)W * kSmallRows * 4, 256);
-  off_cidx_ = off; off = align_up(off + (size_t)W * kSmallRows * 4, 256);
+  off_cval_ = off; off = align_up(off + (size_t)W * kCandStride * 4, 256);
+  off_cidx_ = off; off = align_up(off + (size_t)W * kCandStride * 4, 256);
   off_cflag_ = off; off = align_up(off + PK_MAX_RANKS * 4, 256);
   off_epoch_ = off; off = align_up(off + 4, 256);
   off_status_ = off; off = align_up(off + 4, 256);
@@ -315,6 +318,7 @@ QwenEngine::~QwenEngine() {
   if (decode_graph_) cudaGraphExecDestroy(decode_graph_);
   for (void* p : allocs_) cudaFree(p);
   if (pinned_tok_) cudaFreeHost(pinned_tok_);
+  if (pinned_status_) cudaFreeHost(pinned_status_);
   if (pinned_mtp_) cudaFreeHost(pinned_mtp_);
   if (txn_) {
     for (void* p : txn_->bufs) cudaFree(p);
@@ -658,6 +662,30 @@ uint32_t QwenEngine::comm_status() {
   return v[0] | (v[1] << 8) | ((pk_matvec_ring_status() & 0xffu) << 16);
 }
 
+void QwenEngine::clear_comm_status() {
+  cuda_check(cudaMemsetAsync((char*)arena_ + off_status_, 0, 4, stream_), "clear status");
+  cuda_check(cudaMemsetAsync(gemm_status_, 0, 4, stream_), "clear status");
+  cuda_check(cudaStreamSynchronize(stream_), "clear status");
+  (void)pk_matvec_ring_status();   // reading clears it
+  pinned_status_[0] = pinned_status_[1] = 0u;
+}
+
+void QwenEngine::queue_status_read() {
+  cuda_check(cudaMemcpyAsync(&pinned_status_[0], (char*)arena_ + off_status_, 4, cudaMemcpyDeviceToHost, stream_), "status");
+  cuda_check(cudaMemcpyAsync(&pinned_status_[1], gemm_status_, 4, cudaMemcpyDeviceToHost, stream_), "status");
+}
+
+void QwenEngine::raise_if_step_failed(const char* what) {
+  if (pinned_status_[0] == 0u && pinned_status_[1] == 0u) return;
+  const uint32_t peer = pinned_status_[0], gemm = pinned_status_[1];
+  clear_comm_status();
+  // tokens of this step are not handed out; a graph that holds the failed kernels' state is rebuilt on the next decode
+  last_token_ = -1;
+  char buf[200];
+  snprintf(buf, sizeof buf, "%s: a bounded device wait ran out (peer word %u, tensor-core word %u); the step is discarded", what, peer, gemm);
+  throw CommTimeout(buf);
+}
+
 void QwenEngine::copy_logits(float* out_host, int row) {
   cuda_check(cudaStreamSynchronize(stream_), "sync");
   cuda_check(cudaMemcpy(out_host, logits_ + (size_t)row * vocab_l_, (size_t)vocab_l_ * sizeof(float), cudaMemcpyDeviceToHost), "logits");
@@ -818,11 +846,12 @@ void QwenEngine::sample_rows(int M, const float* logits, int* out) {
     const int site = 2 * cfg_.num_layers;
     PkPush ps = make_push(site);
     for (int r = 0; r < W; ++r) ps.flag[r] = (uint32_t*)((char*)peers_[r] + off_cflag_);
-    check(pk_cand_push(best_val_, best_idx_, M, &ps, peer_cval_dev_, peer_cidx_dev_, stream_), "cand_push");
+    uint32_t* status = (uint32_t*)((char*)arena_ + off_status_);
+    check(pk_cand_push(best_val_, best_idx_, M, &ps, peer_cval_dev_, peer_cidx_dev_, status, kCandStride, stream_), "cand_push");
     PkWait wt = make_wait(site);
     wt.flag = (const uint32_t*)((char*)arena_ + off_cflag_);
     check(pk_cand_merge_wait((const float*)((char*)arena_ + off_cval_), (const int*)((char*)arena_ + off_cidx_), M, W,
-                             &wt, out, stream_),
+                             &wt, out, status, kCandStride, stream_),
           "cand_merge");
   }
 }
@@ -979,7 +1008,9 @@ int QwenEngine::prefill(const int* tokens_host, int n) {
   cuda_check(cudaMemcpyAsync(pinned_tok_, next_tok_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h token");
   if (opt_.mtp) cuda_check(cudaMemcpyAsync(pinned_mtp_, mtp_next_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h draft");
   cuda_check(cudaEventRecord(ev1_, stream_), "event");
+  queue_status_read();
   cuda_check(cudaStreamSynchronize(stream_), "prefill");
+  raise_if_step_failed("prefill");
   float ms = 0;
   cudaEventElapsedTime(&ms, ev0_, ev1_);
   timings_.prefill_ms = ms;
@@ -1221,7 +1252,9 @@ void QwenEngine::decode(int steps, int* out_host, bool sync_each_step) {
   if (!sync_each_step)
     cuda_check(cudaMemcpyAsync(pinned_tok_, out_tokens_dev_, (size_t)steps * sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h");
   cuda_check(cudaEventRecord(ev1_, stream_), "event");
+  queue_status_read();
   cuda_check(cudaStreamSynchronize(stream_), "decode");
+  raise_if_step_failed("decode");
   float ms = 0;
   cudaEventElapsedTime(&ms, ev0_, ev1_);
   timings_.decode_ms = ms;
@@ -1247,7 +1280,9 @@ void QwenEngine::forward_rows(const int* tokens_host, int M, int* out_tokens_hos
   cuda_check(cudaMemcpyAsync(pinned_tok_, next_tok_dev_, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h");
   // decode() continues from slot 0 of the token buffer
   if (M > 1) check(pk_copy_int(next_tok_dev_ + (M - 1), next_tok_dev_, 1, stream_), "copy token");
+  queue_status_read();
   cuda_check(cudaStreamSynchronize(stream_), "forward_rows");
+  raise_if_step_failed("forward_rows");
   pos_ += M;
   last_token_ = pinned_tok_[M - 1];
   mtp_ready_ = false;
@@ -1270,7 +1305,9 @@ int QwenEngine::mtp_row(int token, const void* hidden_row, int position) {
   check(pk_iota_int(mtp_tok_dev_, 1, nullptr, token, stream_), "token");
   mtp_forward(1, hidden_row, position);
   cuda_check(cudaMemcpyAsync(pinned_mtp_, mtp_next_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "d2h draft");
+  queue_status_read();
   cuda_check(cudaStreamSynchronize(stream_), "mtp row");
+  raise_if_step_failed("predictor row");
   mtp_seed_token_ = token;
   mtp_next_token_ = pinned_mtp_[0];
   mtp_ready_ = true;

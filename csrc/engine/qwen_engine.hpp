@@ -10,6 +10,7 @@
 
 #include <cstdint>
 #include <memory>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -86,6 +87,13 @@ struct QwenLayer {
   Fp8Linear down;
 };
 
+// Thrown by the engine's step functions when a bounded device wait ran out during the step (this rank's or, learned
+// through the sampler exchange, another rank's): the step's tokens are not returned, the status words are cleared and
+// the request state is undefined until reset().
+struct CommTimeout : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
 struct QwenTimings {
   double prefill_ms = 0;      // device time of the last prefill
   double decode_ms = 0;       // device time of the last decode run
@@ -140,6 +148,7 @@ class QwenEngine {
   int last_token() const { return last_token_; }
   const QwenTimings& timings() const { return timings_; }
   uint32_t comm_status();
+  void clear_comm_status();
   // fp32 logits of the last forward's final row: this rank's vocab shard.
   void copy_logits(float* out_host, int row);
   int vocab_local() const { return vocab_l_; }
@@ -186,6 +195,8 @@ class QwenEngine {
   void draft_tokens(int count, int input_token, int produced, std::vector<int>& drafts, QwenSpecStats& st);
   void alloc_layer(QwenLayer& L, bool full);
   void capture_decode_graph();
+  void queue_status_read();        // async copy of the status words into pinned memory (before the step's last sync)
+  void raise_if_step_failed(const char* what);   // after that sync
   void enqueue_decode_step();      // one greedy single-row step on stream_ (persistent kernel or per-projection launches)
   void build_persistent();         // descriptor table and parameters of the persistent decode kernel
   PkWait make_wait(int site) const;
@@ -236,6 +247,7 @@ class QwenEngine {
   int out_cap_ = 0;
   uint32_t* gemm_status_ = nullptr;
   int* pinned_tok_ = nullptr;   // pinned host staging for token ids / results
+  uint32_t* pinned_status_ = nullptr;   // [2]: peer-wait word of the arena, tensor-core GEMM word
 
   // comm arena layout (all inside arena_): slots, flags, sampler candidates, epoch, status
   void* arena_ = nullptr;

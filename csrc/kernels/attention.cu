@@ -322,7 +322,8 @@ PK_API int pk_gqa_decode(const void* q, const void* kcache, const void* vcache, 
                          int sink, float* ws, const void* gate_proj, int ld, void* out,
                          cudaStream_t stream) {
   if (head_dim != kD) return PK_ERR_UNSUPPORTED;
-  if (M < 1 || nsplit < 1 || Hq % Hkv != 0) return PK_ERR_BAD_ARG;
+  if (M < 1 || nsplit < 1 || Hkv < 1 || Hq < Hkv || ctx_cap < 1) return PK_ERR_BAD_ARG;   // before any division by Hkv
+  if (Hq % Hkv != 0) return PK_ERR_BAD_ARG;
   DecodeParams p{(const pk::bf16*)q, (const pk::bf16*)kcache, (const pk::bf16*)vcache, pos, M, Hq, Hkv,
                  ctx_cap, scale, nsplit, window, sink, ws};
   const dim3 grid(Hkv, nsplit, M);
@@ -368,6 +369,12 @@ PK_API int pk_gqa_decode_static(const void* q, const void* kcache, const void* v
   g_gqa_static_msg[0] = 0;
   if (M < 1 || Hq < 1 || nsplit < 1 || head_dim < 1) {
     snprintf(g_gqa_static_msg, sizeof g_gqa_static_msg, "pk_gqa_decode_static: M, Hq, nsplit and head_dim must be positive");
+    return PK_ERR_BAD_ARG;
+  }
+  if (Hkv < 1 || Hq < Hkv || Hq % Hkv != 0 || ctx_cap < 1) {
+    snprintf(g_gqa_static_msg, sizeof g_gqa_static_msg,
+             "pk_gqa_decode_static: Hkv must be positive and divide Hq, ctx_cap must be positive (Hq %d, Hkv %d, ctx_cap %d)", Hq, Hkv,
+             ctx_cap);
     return PK_ERR_BAD_ARG;
   }
   const unsigned long long need = (unsigned long long)M * Hq * nsplit * (head_dim + 2);

@@ -1204,9 +1204,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_persistent_kernel(const Pk
         if (p.world > 1) {
           // sampler exchange: {logit, token} of every rank through peer memory
           const uint32_t seq = c.epoch * p.sites_per_epoch + (uint32_t)(2 * n_layers) + 1u;
+          // rows of 32 entries per rank; entry 31 of the index row carries this rank's status word, so that a rank
+          // whose wait ran out earlier in the step takes the others with it
+          const int my_status = (int)*((volatile uint32_t*)p.status);
           for (int r = 0; r < p.world; ++r) {
-            p.cand_val_peer[r][p.rank] = best;
-            p.cand_idx_peer[r][p.rank] = bi;
+            p.cand_val_peer[r][p.rank * 32] = best;
+            p.cand_idx_peer[r][p.rank * 32] = bi;
+            p.cand_idx_peer[r][p.rank * 32 + 31] = my_status;
           }
           __threadfence_system();
           for (int r = 0; r < p.world; ++r) st_release_sys(p.cand_flag[r] + p.rank, seq);
@@ -1225,8 +1229,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_persistent_kernel(const Pk
             best = -INFINITY;
             bi = 0x7fffffff;
             for (int r = 0; r < p.world; ++r) {
-              const float v = __ldcg(p.cand_val_peer[p.rank] + r);
-              const int id = __ldcg(p.cand_idx_peer[p.rank] + r);
+              if (__ldcg(p.cand_idx_peer[p.rank] + r * 32 + 31) != 0) atomicCAS(p.status, 0u, PK_COMM_PEER_FAILED);
+              const float v = __ldcg(p.cand_val_peer[p.rank] + r * 32);
+              const int id = __ldcg(p.cand_idx_peer[p.rank] + r * 32);
               if (v > best || (v == best && id < bi)) {
                 best = v;
                 bi = id;

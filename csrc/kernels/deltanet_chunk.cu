@@ -371,16 +371,16 @@ PK_API int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, i
   deltanet_tail_kernel<<<(channels + 255) / 256, 256, 0, stream>>>((const pk::bf16*)proj, ld, T, channels, conv_state);
   PK_CHECK_LAUNCH();
 
-  static bool configured = false;
+  static PkDeviceOnce once;
   const size_t smem_chunk = (size_t)(2 * CH * KS + CH * CH + 2 * CH) * sizeof(float);
   const size_t smem_state = (size_t)(3 * CH * D + CH * CH + 2 * CH * SL + D * SL + CH) * sizeof(float);
-  if (!configured) {
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(deltanet_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_chunk) != cudaSuccess ||
         cudaFuncSetAttribute(deltanet_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   ChunkParams cp{qn, kn, v, g, beta, key_heads, value_heads, Tpad, U, W, P, G};
   deltanet_chunk_kernel<<<dim3(nchunks, value_heads), 256, smem_chunk, stream>>>(cp);

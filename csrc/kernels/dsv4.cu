@@ -591,13 +591,13 @@ PK_API int pk_dsv4_hc_pre(const float* h, const float* fn, const float* scale, c
   if (M < 1 || hc < 1 || hc > kHcMax || mix > kMixMax || (dim & 3) != 0 || dim * 4 > 160 * 1024) return PK_ERR_BAD_ARG;
   if (!head_mode && (post == nullptr || comb == nullptr)) return PK_ERR_BAD_ARG;
   HcPreParams p{h, fn, scale, base, gamma, M, dim, hc, mix, iters, head_mode, hc_eps, norm_eps, (pk::bf16*)x_out, x_raw, post, comb};
-  static bool configured = false;
-  if (!configured) {
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(hc_pre_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   hc_pre_kernel<<<M, kHcThreads, (size_t)dim * 4, stream>>>(p);
   PK_CHECK_LAUNCH();
@@ -665,13 +665,13 @@ PK_API int pk_dsv4_index_score(const void* q, const void* k, const float* w, con
                                int ldw, float wscale, float* score, cudaStream_t stream) {
   if (M < 1 || ih < 1 || ld < 1 || (size_t)ih * 129 * 4 > 96 * 1024) return PK_ERR_BAD_ARG;
   IndexScoreParams p{(const pk::bf16*)q, (const pk::bf16*)k, w, pos, ih, ratio, ld, ldw, wscale, score};
-  static bool configured = false;
-  if (!configured) {
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(index_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   index_score_kernel<<<dim3((ld + 127) / 128, M), 128, (size_t)ih * 129 * 4, stream>>>(p);
   PK_CHECK_LAUNCH();

@@ -498,13 +498,13 @@ PK_API int pk_gemm_bf16(const void* A, int lda, const void* W, int M, int N, int
   p.status = status;
   if (push) p.push = *push;
   const size_t smem = sizeof(Smem) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int sms = sm_count > 0 ? sm_count : 148;

@@ -392,13 +392,13 @@ PK_API int pk_gemm_umma(const void* A, int lda, const void* W, const float* scal
   if (push) p.push = *push;
 
   const size_t smem = sizeof(SmemLayout) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(gemm_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   const dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
   if (grid.y > 65535 || (K + 127) / 128 > kMaxScaleKb) return PK_ERR_UNSUPPORTED;

@@ -642,13 +642,13 @@ int launch_linear(const LinearParams& p_in, int sm_count, cudaStream_t stream) {
   LinearParams p = p_in;
   p.stage_bytes = M <= 2 ? stage_bytes_per_warp(p.type, p.K) : 0;
   const size_t smem = (size_t)M * p.K * sizeof(float) + (size_t)kWarps * p.stage_bytes;
-  static bool configured = false;
-  if (!configured) {
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(gguf_linear_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   const int groups = p.epi == 1 ? p.N / 2 : p.N;
   int blocks = (groups + kWarps - 1) / kWarps;
@@ -705,13 +705,13 @@ PK_API int pk_router_topk(const void* x, const float* router_w, const float* bia
   const size_t smem_x = (size_t)tile * H * sizeof(float);
   if (smem_x > 200 * 1024 || (size_t)2 * E * sizeof(float) > 48 * 1024) return PK_ERR_UNSUPPORTED;
   if (smem_x > 48 * 1024) {
-    static bool configured = false;
-    if (!configured) {
+    static PkDeviceOnce once;
+    if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
       if (cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
         pk_set_last_cuda_error((int)cudaGetLastError());
         return PK_ERR_CUDA;
       }
-      configured = true;
+      once_guard.done();
     }
   }
   float* logits = router_scratch((size_t)T * E);
@@ -776,8 +776,8 @@ static int moe_forward_impl(const void* W13, const void* W2, int type13, int typ
   if ((size_t)8 * H * 4 > 184 * 1024 || (size_t)8 * I * 4 > 184 * 1024) return PK_ERR_UNSUPPORTED;   // plus the warps' stage buffers
   MoeParams p{(const uint8_t*)W13, (const uint8_t*)W2, type13, type2, E, H, I, (const pk::bf16*)x, seg_start, route_token,
               route_weight, hbuf, y, limit, expert_offset, local_experts, ybuf};
-  static bool configured = false;
-  if (!configured) {
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(gguf_moe_w13_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(gguf_moe_w2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(gguf_moe_w13_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 184 * 1024) != cudaSuccess ||
@@ -785,7 +785,7 @@ static int moe_forward_impl(const void* W13, const void* W2, int type13, int typ
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   (void)sm_count;
   if (total_routes > 0 && total_routes <= kRouteParallelMax) {

@@ -657,13 +657,13 @@ int launch_m(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) {
     }
   }  // chunked: exactly one group per warp (one accumulator set per warp)
   if (blocks < 1) blocks = 1;
-  static bool configured = false;
-  if (!configured) {
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(matvec_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   PK_LAUNCH_PDL(matvec_kernel<M>, dim3(blocks), dim3(kThreads), smem, stream, p);
   return PK_OK;
@@ -999,13 +999,13 @@ int launch_ring(MatvecParams& p, int groups, int sm_count, cudaStream_t stream) 
   p.scale_off = (int)off;
   off += (size_t)4 * kb_count * sizeof(float);
   if (off > (size_t)kRingSmemLimit) return -1;
-  static bool configured = false;
-  if (!configured) {
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(matvec_ring_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmemLimit) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
-    configured = true;
+    once_guard.done();
   }
   PK_LAUNCH_PDL(matvec_ring_kernel<M>, dim3(blocks), dim3(kThreads), off, stream, p);
   return PK_OK;

@@ -209,13 +209,10 @@ PK_API int pk_rmsnorm(const void* x, const float* parts, int nparts, int M, int 
   const size_t smem = (size_t)K * sizeof(float);
   if (smem > 200 * 1024) return PK_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
-    static size_t configured = 0;
-    if (smem > configured) {
-      if (cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        pk_set_last_cuda_error((int)cudaGetLastError());
-        return PK_ERR_CUDA;
-      }
-      configured = smem;
+    // rows beyond 12288 elements only; the attribute is per device, so it is simply set on every such call
+    if (cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      pk_set_last_cuda_error((int)cudaGetLastError());
+      return PK_ERR_CUDA;
     }
   }
   PK_LAUNCH(rmsnorm_kernel, dim3(M), dim3(256), smem, stream, p);
@@ -333,29 +330,41 @@ __global__ void store_token_kernel(const int* token, int* out, int* counter, int
   *counter = c + 1;
 }
 
+// Besides {logit, token} every rank sends its status word: a rank whose wait ran out earlier in the step tells the
+// others here, so that all ranks give the step up together (slot 31 of the rank's candidate-index row).
 __global__ void cand_push_kernel(const float* val, const int* idx, int M, const PkPush push,
-                                 float* const* peer_val, int* const* peer_idx) {
+                                 float* const* peer_val, int* const* peer_idx, const uint32_t* status, int stride) {
   const int m = threadIdx.x;
   if (m < M) {
     for (int r = 0; r < push.world; ++r) {
-      peer_val[r][push.rank * M + m] = val[m];
-      peer_idx[r][push.rank * M + m] = idx[m];
+      peer_val[r][push.rank * stride + m] = val[m];
+      peer_idx[r][push.rank * stride + m] = idx[m];
     }
+  }
+  if (m == 31 && status != nullptr) {
+    const int st = (int)*((const volatile uint32_t*)status);
+    for (int r = 0; r < push.world; ++r) peer_idx[r][push.rank * stride + 31] = st;
   }
   publish_when_grid_done(push);
 }
 
 __global__ void cand_merge_wait_kernel(const float* cand_val, const int* cand_idx, int M, int world,
-                                       const PkWait wait, int* out_idx) {
-  if (threadIdx.x == 0) wait_all_ranks(wait);
+                                       const PkWait wait, int* out_idx, uint32_t* status, int stride) {
+  if (threadIdx.x == 0) {
+    wait_all_ranks(wait);
+    if (status != nullptr && *((volatile uint32_t*)status) == 0u) {
+      for (int r = 0; r < world; ++r)
+        if (cand_idx[r * stride + 31] != 0) atomicCAS(status, 0u, PK_COMM_PEER_FAILED);
+    }
+  }
   __syncthreads();
   const int m = threadIdx.x;
   if (m >= M) return;
   float best = -INFINITY;
   int bi = 0x7fffffff;
   for (int r = 0; r < world; ++r) {
-    const float v = cand_val[r * M + m];
-    const int id = cand_idx[r * M + m];
+    const float v = cand_val[r * stride + m];
+    const int id = cand_idx[r * stride + m];
     if (v > best || (v == best && id < bi)) {
       best = v;
       bi = id;
@@ -391,17 +400,19 @@ PK_API int pk_store_token(const int* token, int* out, int* counter, int cap, cud
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
+// Candidate rows are `stride` (>= 32) entries apart per rank; entry 31 of a rank's index row carries its status word
+// (`status` may be null: nothing is sent then).
 PK_API int pk_cand_push(const float* val, const int* idx, int M, const PkPush* push, float* const* peer_val,
-                        int* const* peer_idx, cudaStream_t stream) {
-  if (M > 32 || push == nullptr) return PK_ERR_BAD_ARG;
-  cand_push_kernel<<<1, 32, 0, stream>>>(val, idx, M, *push, peer_val, peer_idx);
+                        int* const* peer_idx, const uint32_t* status, int stride, cudaStream_t stream) {
+  if (M > 31 || stride < 32 || push == nullptr) return PK_ERR_BAD_ARG;
+  cand_push_kernel<<<1, 32, 0, stream>>>(val, idx, M, *push, peer_val, peer_idx, status, stride);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
 PK_API int pk_cand_merge_wait(const float* cand_val, const int* cand_idx, int M, int world, const PkWait* wait,
-                              int* out_idx, cudaStream_t stream) {
-  if (M > 32 || wait == nullptr) return PK_ERR_BAD_ARG;
-  cand_merge_wait_kernel<<<1, 32, 0, stream>>>(cand_val, cand_idx, M, world, *wait, out_idx);
+                              int* out_idx, uint32_t* status, int stride, cudaStream_t stream) {
+  if (M > 31 || stride < 32 || wait == nullptr) return PK_ERR_BAD_ARG;
+  cand_merge_wait_kernel<<<1, 32, 0, stream>>>(cand_val, cand_idx, M, world, *wait, out_idx, status, stride);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }

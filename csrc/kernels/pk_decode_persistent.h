@@ -98,7 +98,7 @@ struct PkDecParams {
   // writes value and sequence number with ONE 8-byte store, so the arrival of the sequence number is the arrival of
   // the value: no fence, no separate flag, and the consumer's wait on the data is the only synchronisation of a site.
   uint2* slot[2][PK_MAX_RANKS];
-  float* cand_val_peer[PK_MAX_RANKS];   // peer r's sampler candidate values [world * 8]
+  float* cand_val_peer[PK_MAX_RANKS];   // peer r's sampler candidates: rows of 32 per rank (index row: entry 31 = status)
   int* cand_idx_peer[PK_MAX_RANKS];
   uint32_t* cand_flag[PK_MAX_RANKS];    // peer r's sampler flags [world]
   const uint32_t* epoch;                // local word, bumped once per forward

@@ -184,6 +184,25 @@ static int test_protocol() {
   return 0;
 }
 
+// Block counters of the peer all-reduce kernel when blocks skip their wait (status word already set): with one shared
+// counter the publish fires before every block has stored, or never; with one counter per pass it fires exactly when
+// the last block has stored.
+static int test_block_counters() {
+  using pk::BlockEvent;
+  // grid 3: b0 stores, b0 leaves (no wait: failed state), b1 stores -> a shared counter says "3 of 3" with b2 missing
+  const std::vector<BlockEvent> a = {{0, 1}, {0, 2}, {1, 1}, {1, 2}, {2, 1}, {2, 2}};
+  CHECK(pk::stored_at_publish(3, a, false) == 2);
+  CHECK(pk::stored_at_publish(3, a, true) == 3);
+  // grid 2: b0 stores, b0 leaves, b1 stores -> the shared counter jumps from 2 (a second-pass increment) to 3: never published
+  const std::vector<BlockEvent> b = {{0, 1}, {0, 2}, {1, 1}, {1, 2}};
+  CHECK(pk::stored_at_publish(2, b, false) == -1);
+  CHECK(pk::stored_at_publish(2, b, true) == 2);
+  // the healthy order is fine either way
+  const std::vector<BlockEvent> c = {{0, 1}, {1, 1}, {2, 1}, {0, 2}, {1, 2}, {2, 2}};
+  CHECK(pk::stored_at_publish(3, c, false) == 3 && pk::stored_at_publish(3, c, true) == 3);
+  return 0;
+}
+
 // Draft-length policy of speculative decode: a whole request simulated on the host.
 static int test_spec_policy() {
   using pk::drafts_this_round;
@@ -225,6 +244,7 @@ int main(int argc, char** argv) {
     if (test_sampler()) return 1;
     if (test_control_plane(argv[3])) return 1;
     if (test_protocol()) return 1;
+    if (test_block_counters()) return 1;
     if (test_spec_policy()) return 1;
   } catch (const std::exception& e) {
     std::fprintf(stderr, "host_selftest: unexpected exception: %s\n", e.what());

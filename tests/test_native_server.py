@@ -121,6 +121,21 @@ def test_reasoning_goes_to_its_own_channel(server):
     assert "".join(c["choices"][0]["delta"].get("reasoning_content", "") for c in chunks if c["choices"]) == "because"
 
 
+@pytest.mark.parametrize("server", ["ab\u2620cd"], indirect=True)
+def test_step_failure_ends_the_request_with_500_and_the_next_request_is_served(server):
+    """An engine step whose result is lost (a rank's peer wait ran out) must not produce tokens: plain requests get
+    HTTP 500, streams an error event, and the server keeps serving."""
+    st, _, data = server.request("POST", "/v1/chat/completions", _chat())
+    assert st == 500 and json.loads(data)["error"]["type"] == "engine_error"
+    st, ct, data = server.request("POST", "/v1/chat/completions", _chat(stream=True))
+    assert st == 200 and "event-stream" in ct
+    events = [e[6:] for e in data.split("\n\n") if e.startswith("data: ")]
+    assert events[-1] == "[DONE]" and any('"engine_error"' in e for e in events)
+    text = "".join(json.loads(e)["choices"][0]["delta"].get("content", "") for e in events if e.startswith("{") and "choices" in e)
+    assert text in ("", "a", "ab")           # nothing after the failed step
+    assert server.request("GET", "/health")[0] == 200
+
+
 def test_native_gguf_inspect(tmp_path):
     from pocketllm_b200.models import minimax_m2
     p = tmp_path / "mm.gguf"
@@ -142,6 +157,35 @@ def test_native_gguf_inspect(tmp_path):
     bad = tmp_path / "bad.gguf"
     bad.write_bytes(p.read_bytes()[:200])
     assert subprocess.run([str(BINARY), "--inspect-gguf", str(bad)], capture_output=True, text=True).returncode == 1
+
+
+def test_native_gguf_reader_rejects_hostile_sizes(tmp_path):
+    """Lengths, counts, dimensions and offsets near 2^64 must be refused with a message, not wrapped into range."""
+    import struct
+
+    def header(n_tensors: int, n_kv: int) -> bytes:
+        return struct.pack("<IIQQ", 0x46554747, 3, n_tensors, n_kv)
+
+    def kv_str(key: str, length: int, payload: bytes = b"") -> bytes:
+        return struct.pack("<Q", len(key)) + key.encode() + struct.pack("<IQ", 8, length) + payload
+
+    def tensor(name: str, dims: list[int], typ: int, offset: int) -> bytes:
+        return (struct.pack("<Q", len(name)) + name.encode() + struct.pack("<I", len(dims)) +
+                b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", typ, offset))
+
+    cases = {
+        "string length wraps": header(0, 1) + kv_str("k", 2**64 - 8),
+        "array count huge": header(0, 1) + struct.pack("<Q", 1) + b"a" + struct.pack("<IIQ", 9, 4, 2**62),
+        "tensor count huge": header(2**60, 0),
+        "dims overflow": header(1, 0) + tensor("t", [2**33, 2**33], 0, 0) + b"\0" * 64,
+        "offset wraps": header(1, 0) + tensor("t", [32], 0, 2**64 - 32) + b"\0" * 256,
+        "past the end": header(1, 0) + tensor("t", [1024], 0, 0) + b"\0" * 64,
+    }
+    for what, blob in cases.items():
+        f = tmp_path / "h.gguf"
+        f.write_bytes(blob)
+        r = subprocess.run([str(BINARY), "--inspect-gguf", str(f)], capture_output=True, text=True, timeout=60)
+        assert r.returncode == 1 and "gguf:" in (r.stdout + r.stderr), (what, r.stdout, r.stderr)
 
 
 def _engine_lib():

@@ -66,3 +66,13 @@ def test_static_scratch_rejects_oversize_problem():
     assert "exceeds the fixed scratch" in msg and str(STATIC_WS_FLOATS) in msg
     torch.cuda.synchronize()
     assert (out == 7.0).all()
+    # a kv head count of zero (or one that does not divide the q heads) is refused the same way, before any launch
+    for bad_hkv in (0, -3, 5):
+        kc_bad = torch.zeros(max(bad_hkv, 1), 64, D, device="cuda", dtype=torch.bfloat16)
+        rc = L.pk_gqa_decode_static(
+            c_void_p(q.data_ptr()), c_void_p(kc_bad.data_ptr()), c_void_p(kc_bad.data_ptr()), c_void_p(pos.data_ptr()), c_int(M), c_int(Hq),
+            c_int(bad_hkv), c_int(D), c_int(64), c_float(D ** -0.5), c_int(2), c_int(0), c_int(0), c_void_p(gate.data_ptr()),
+            c_int(gate.stride(0)), c_void_p(out.data_ptr()), c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 1 and "Hkv" in L.pk_gqa_decode_static_error().decode()
+    torch.cuda.synchronize()
+    assert (out == 7.0).all()
