@@ -16,6 +16,10 @@ struct PkPush {
   uint32_t site;
   int world;
   int rank;
+  // Reduce-scatter form (prefill GEMM epilogues): rows are owned in blocks of `rows_per_rank`; row m goes ONLY to rank
+  // m / rows_per_rank, at row (rank * rows_per_rank + m % rows_per_rank) of its slot [world][rows_per_rank][cols].
+  // 0 = every row to every rank (slot [world][rows][cols]).
+  int rows_per_rank;
 };
 
 // What a consumer waits on before reading its local slot buffer.

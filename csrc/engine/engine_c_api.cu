@@ -99,6 +99,30 @@ PK_EAPI int pk_qwen_prefill(void* h, const int* tokens, int n, int* first_token)
   });
 }
 
+// A new request with exact prefix reuse (see prefix_plan.hpp). stats (may be null): [reused, computed, prompt, matched,
+// source (0 empty, 1 live, 2 snapshot), snapshots, snapshot_bytes, hits, misses].
+PK_EAPI int pk_qwen_prefill_cached(void* h, const int* tokens, int n, int* first_token, long long* stats) {
+  return guarded([&] {
+    auto* e = (pk::QwenEngine*)h;
+    const int t = e->prefill_cached(tokens, n);
+    if (first_token) *first_token = t;
+    if (stats) {
+      const pk::QwenPrefixStats& ps = e->prefix_stats();
+      const std::string src = ps.resume_source;
+      const long long v[9] = {ps.reused_tokens, ps.computed_tokens, ps.prompt_tokens, ps.matched_tokens,
+                              src == "live" ? 1 : src == "snapshot" ? 2 : 0, ps.snapshots, (long long)ps.snapshot_bytes, ps.hits, ps.misses};
+      for (int i = 0; i < 9; ++i) stats[i] = v[i];
+    }
+  });
+}
+// interval 0: recurrent-state copies at request boundaries only; max_snapshots 0: live continuation only; enable 0: off.
+PK_EAPI int pk_qwen_configure_prefix_cache(void* h, int enable, int snapshot_interval, int max_snapshots) {
+  return guarded([&] { ((pk::QwenEngine*)h)->configure_prefix_cache(enable != 0, snapshot_interval, max_snapshots); });
+}
+PK_EAPI int pk_qwen_clear_prefix_cache(void* h) {
+  return guarded([&] { ((pk::QwenEngine*)h)->clear_prefix_cache(); });
+}
+
 PK_EAPI int pk_qwen_decode(void* h, int steps, int* out_tokens, int sync_each_step) {
   return guarded([&] { ((pk::QwenEngine*)h)->decode(steps, out_tokens, sync_each_step != 0); });
 }
@@ -284,6 +308,12 @@ PK_EAPI void* pk_tokenizer_from_gguf(const char* path) {
     pk::GgufFile f(path);
     out = new pk::BpeTokenizer(pk::BpeTokenizer::from_gguf(f));
   });
+  return out;
+}
+// ... or from a Hugging Face tokenizer directory / tokenizer.json file.
+PK_EAPI void* pk_tokenizer_from_hf(const char* dir_or_file) {
+  void* out = nullptr;
+  guarded([&] { out = new pk::BpeTokenizer(pk::BpeTokenizer::from_hf_dir(dir_or_file)); });
   return out;
 }
 PK_EAPI void pk_tokenizer_destroy(void* t) { delete (pk::BpeTokenizer*)t; }

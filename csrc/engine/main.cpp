@@ -40,12 +40,16 @@ struct Args {
   int window = 0, sink = 0;
   bool mtp = false, nccl_smoke = false;
   int mtp_tokens = 4;
+  bool prefix_cache = true;
+  int snapshot_interval = 4096, max_snapshots = 82;
+  int persistent_decode = -1;
+  std::string prompt_text, kv_cache_dtype = "bf16";
   long random_seed = -1;
   bool benchmark_27b = false, dump_config = false, inspect = false, persistent_stdin = false, no_graph = false;
   // serving
   bool serve = false, allow_shutdown = false, list_tensors = false;
   std::string host = "127.0.0.1", sidecar_python = "python", tokenizer = "chars", chat_format = "qwen", model_name = "pocketllm-b200";
-  std::string fake_script, inspect_gguf, tokenizer_gguf, tokenize_text, detokenize_ids;
+  std::string fake_script, inspect_gguf, tokenizer_gguf, tokenizer_dir, tokenize_text, detokenize_ids;
   std::string weight_source, lookup, dsv4_config;
   int lookup_layer = -1, lookup_expert = -1;
   bool have_tokenize = false;
@@ -61,8 +65,12 @@ void usage() {
                "  --max-context N --prefill-chunk-tokens N --no-cuda-graph\n"
                "  --qwen-attention-window N --qwen-attention-sink-tokens N\n"
                "  --qwen-mtp [--qwen-mtp-tokens K]   speculative decode with the checkpoint's multi-token predictor\n"
+               "  --qwen-no-prefix-cache | --qwen-snapshot-interval N (4096, 0 = request boundaries only) --qwen-max-snapshots N (82)\n"
+               "      exact prefix reuse across the requests of --qwen-persistent-stdin and --serve\n"
+               "  --kv-cache-dtype bf16|fp8   --decode-kernel auto|persistent|per-projection\n"
+               "  --prompt TEXT --tokenizer-gguf FILE   tokenise the prompt with the GGUF file's BPE vocabulary\n"
                "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
-               "  --tokenizer-gguf FILE --tokenize TEXT | --detokenize 1,2,3\n"
+               "  --tokenizer-gguf FILE | --tokenizer-dir DIR (tokenizer.json)   --tokenize TEXT | --detokenize 1,2,3\n"
                "  --nccl-smoke --tp-world N --tp-rank R [--nccl-id-path PATH]   NCCL baseline path: all-reduce, broadcast, all-gather, top-1\n"
                "  --dsv4-config DIR|FILE.gguf [--tp-world N]   parse, validate and print a DeepSeek-V4 config\n"
                "  --weight-source DIR|FILE.gguf [--lookup NAME | --lookup-expert LAYER,EXPERT,w1|w2|w3]   tensor lookup by model name\n"
@@ -93,6 +101,19 @@ Args parse(int argc, char** argv) {
     else if (f == "--qwen-attention-sink-tokens") a.sink = std::stoi(need(i));
     else if (f == "--nccl-smoke") a.nccl_smoke = true;
     else if (f == "--qwen-mtp") a.mtp = true;
+    else if (f == "--qwen-no-prefix-cache") a.prefix_cache = false;
+    else if (f == "--qwen-snapshot-interval") a.snapshot_interval = std::stoi(need(i));
+    else if (f == "--qwen-max-snapshots") a.max_snapshots = std::stoi(need(i));
+    else if (f == "--kv-cache-dtype") {
+      a.kv_cache_dtype = need(i);
+      if (a.kv_cache_dtype == "fp16") a.kv_cache_dtype = "bf16";   // the reference's name for its 16-bit cache
+      if (a.kv_cache_dtype != "bf16" && a.kv_cache_dtype != "fp8") throw std::runtime_error("--kv-cache-dtype must be bf16 (fp16) or fp8");
+    }
+    else if (f == "--decode-kernel") {
+      const std::string v = need(i);
+      a.persistent_decode = v == "persistent" ? 1 : v == "per-projection" ? 0 : -1;
+    }
+    else if (f == "--prompt") a.prompt_text = need(i);
     else if (f == "--qwen-mtp-tokens") { a.mtp_tokens = std::stoi(need(i)); a.mtp = true; }
     else if (f == "--random-init") a.random_seed = std::stol(need(i));
     else if (f == "--benchmark-27b") a.benchmark_27b = true;
@@ -112,6 +133,7 @@ Args parse(int argc, char** argv) {
     else if (f == "--inspect-gguf") a.inspect_gguf = need(i);
     else if (f == "--tensors") a.list_tensors = true;
     else if (f == "--tokenizer-gguf") a.tokenizer_gguf = need(i);
+    else if (f == "--tokenizer-dir") a.tokenizer_dir = need(i);
     else if (f == "--dsv4-config") a.dsv4_config = need(i);
     else if (f == "--weight-source") a.weight_source = need(i);
     else if (f == "--lookup") a.lookup = need(i);
@@ -169,11 +191,10 @@ class QwenTokenEngine : public pk::TokenEngine {
       m.payload.assign(prompt.begin(), prompt.end());
       chan_.broadcast(m);
     }
-    e_.reset();
     buf_.clear();
     buf_pos_ = 0;
     try {
-      const int first = e_.prefill(prompt.data(), (int)prompt.size());
+      const int first = e_.prefill_cached(prompt.data(), (int)prompt.size());   // reset + prefill when the cache is off
       return host_sampling_ ? resample(first) : first;
     } catch (const pk::CommTimeout& t) {
       throw pk::EngineStepFailed(t.what());   // HTTP 500; the status words are already cleared
@@ -297,10 +318,17 @@ struct RunResult {
   pk::QwenSpecStats spec;
 };
 
-RunResult generate(pk::QwenEngine& eng, const std::vector<int>& prompt, int max_new) {
+// One request. `reuse` keeps the engine's state between requests and lets prefill_cached() skip the prefix it has
+// already consumed (every rank takes the same decision: it depends on the token sequences only).
+RunResult generate(pk::QwenEngine& eng, const std::vector<int>& prompt, int max_new, bool reuse = false) {
   RunResult r;
-  eng.reset();
-  const int first = eng.prefill(prompt.data(), (int)prompt.size());
+  int first;
+  if (reuse) {
+    first = eng.prefill_cached(prompt.data(), (int)prompt.size());
+  } else {
+    eng.reset();
+    first = eng.prefill(prompt.data(), (int)prompt.size());
+  }
   r.tokens.push_back(first);
   r.prefill_s = eng.timings().prefill_ms / 1e3;
   if (max_new > 1) {
@@ -323,6 +351,12 @@ void print_result(const char* tag, const Args& a, const pk::QwenEngine& eng, siz
   if (eng.mtp_enabled())
     std::printf(" mtp_rounds=%lld mtp_proposed=%lld mtp_accepted=%lld mtp_rollbacks=%lld mtp_replay_tokens=%lld mtp_plain_steps=%lld",
                 r.spec.rounds, r.spec.proposed, r.spec.accepted, r.spec.rollbacks, r.spec.replay_tokens, r.spec.plain_steps);
+  if (eng.options().prefix_cache && std::strcmp(tag, "qwen_runtime") != 0) {
+    const pk::QwenPrefixStats& ps = eng.prefix_stats();
+    std::printf(" prefix_reused_tokens=%d prefix_computed_tokens=%d prefix_matched_tokens=%d prefix_resume=%s prefix_snapshots=%d "
+                "prefix_snapshot_bytes=%llu prefix_hits=%lld prefix_misses=%lld",
+                ps.reused_tokens, ps.computed_tokens, ps.matched_tokens, ps.resume_source, ps.snapshots, ps.snapshot_bytes, ps.hits, ps.misses);
+  }
   std::printf("\n");
   std::fflush(stdout);
 }
@@ -407,9 +441,15 @@ int nccl_smoke(const Args& a) {
   return ok ? 0 : 1;
 }
 
-int tokenizer_tool(const Args& a) {
+pk::BpeTokenizer load_tokenizer(const Args& a) {
+  if (!a.tokenizer_dir.empty()) return pk::BpeTokenizer::from_hf_dir(a.tokenizer_dir);
+  if (a.tokenizer_gguf.empty()) throw std::runtime_error("give --tokenizer-gguf FILE or --tokenizer-dir DIR for the vocabulary");
   pk::GgufFile f(a.tokenizer_gguf);
-  const pk::BpeTokenizer tok = pk::BpeTokenizer::from_gguf(f);
+  return pk::BpeTokenizer::from_gguf(f);
+}
+
+int tokenizer_tool(const Args& a) {
+  const pk::BpeTokenizer tok = load_tokenizer(a);
   if (a.have_tokenize) {
     const std::vector<int> ids = tok.encode(a.tokenize_text);
     std::printf("token_ids=");
@@ -421,7 +461,7 @@ int tokenizer_tool(const Args& a) {
 }
 
 int run(const Args& a) {
-  if (!a.tokenizer_gguf.empty() && (a.have_tokenize || !a.detokenize_ids.empty())) return tokenizer_tool(a);
+  if ((!a.tokenizer_gguf.empty() || !a.tokenizer_dir.empty()) && (a.have_tokenize || !a.detokenize_ids.empty())) return tokenizer_tool(a);
   if (!a.inspect_gguf.empty()) return inspect_gguf(a);
   if (a.nccl_smoke) return nccl_smoke(a);
   if (!a.dsv4_config.empty()) return dsv4_config_tool(a);
@@ -452,6 +492,10 @@ int run(const Args& a) {
   opt.attention_window = a.window;
   opt.attention_sink = a.sink;
   opt.mtp = a.mtp;
+  opt.prefix_cache = a.prefix_cache;
+  opt.snapshot_interval = a.snapshot_interval;
+  opt.max_snapshots = a.max_snapshots;
+  opt.persistent_decode = a.persistent_decode;
   g_mtp_tokens = a.mtp_tokens;
   pk::QwenEngine eng(cfg, opt);
   if (a.random_seed >= 0 || a.benchmark_27b) eng.init_random((uint64_t)std::max(0L, a.random_seed), 0.02f);
@@ -504,8 +548,7 @@ int run(const Args& a) {
         try {
           if (m.op == OP_PREFILL) {
             std::vector<int> prompt(m.payload.begin(), m.payload.end());
-            eng.reset();
-            eng.prefill(prompt.data(), (int)prompt.size());
+            eng.prefill_cached(prompt.data(), (int)prompt.size());
           } else if (m.op == OP_NEXT) {
             int out = 0;
             eng.decode(1, &out, true);
@@ -528,6 +571,7 @@ int run(const Args& a) {
         if (line == "reset") {
           m.op = OP_RESET;
           chan.broadcast(m);
+          eng.clear_prefix_cache();
           eng.reset();
           std::printf("qwen_persistent_reset=1\n");
           std::fflush(stdout);
@@ -544,7 +588,7 @@ int run(const Args& a) {
         chan.broadcast(m);
         std::vector<int> prompt(nums.begin() + 1, nums.end());
         try {
-          RunResult r = generate(eng, prompt, nums[0]);
+          RunResult r = generate(eng, prompt, nums[0], true);
           print_result("qwen_persistent_result", a, eng, prompt.size(), r);
         } catch (const std::exception& e) {
           std::printf("qwen_persistent_error=1 message=%s\n", e.what());
@@ -558,11 +602,15 @@ int run(const Args& a) {
       pk::CmdChannel::Message m;
       while (chan.receive(m)) {  // blocks in recv(): an idle worker uses no GPU and no CPU
         if (m.op == OP_SHUTDOWN) break;
-        if (m.op == OP_RESET) { eng.reset(); continue; }
+        if (m.op == OP_RESET) {
+          eng.clear_prefix_cache();
+          eng.reset();
+          continue;
+        }
         if (m.op == OP_GENERATE && m.payload.size() >= 2) {
           std::vector<int> prompt(m.payload.begin() + 1, m.payload.end());
           try {
-            generate(eng, prompt, m.payload[0]);
+            generate(eng, prompt, m.payload[0], true);
           } catch (const std::exception& e) {
             std::fprintf(stderr, "worker %d: %s\n", a.tp_rank, e.what());
           }
@@ -576,10 +624,12 @@ int run(const Args& a) {
       std::stringstream ss;
       ss << in.rdbuf();
       prompt = parse_ids(ss.str());
+    } else if (!a.prompt_text.empty()) {
+      prompt = load_tokenizer(a).encode(a.prompt_text);
     } else {
       prompt = parse_ids(a.token_ids);
     }
-    if (prompt.empty()) throw std::runtime_error("no prompt: give --token-ids or --token-ids-file");
+    if (prompt.empty()) throw std::runtime_error("no prompt: give --token-ids, --token-ids-file or --prompt");
     RunResult r = generate(eng, prompt, a.max_new_tokens);
     if (eng.comm_status() != 0) {
       std::printf("qwen_comm_status=%u\n", eng.comm_status());

@@ -48,6 +48,10 @@ int pk_embedding(const int* tokens, int M, const void* table, int dim, int vocab
 int pk_rmsnorm(const void* x, const float* parts, int nparts, int M, int K, void* hidden_out,
                const float* gamma, int mode, float eps, void* y, const PkWait* wait, cudaStream_t stream);
 
+int pk_rmsnorm_rs_ag(void* hidden, const float* parts, int world, int rank, int rows_per_rank, int M, int K, const float* gamma,
+                     int mode, float eps, void* const* y_peer, const PkWait* wait_rs, const PkPush* pub_ag, const PkWait* wait_ag,
+                     int sm_count, cudaStream_t stream);
+
 int pk_mtp_concat_norm(const int* tokens, int M, const void* table, const void* hidden, int K, const float* gamma_e,
                        const float* gamma_h, float eps, void* out, cudaStream_t stream);
 

@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "mem_guard.hpp"
+#include "prefix_plan.hpp"
 #include "pk_kernels.h"
 #include "safetensors.hpp"
 #include "spec_policy.hpp"
@@ -222,7 +223,7 @@ void QwenEngine::alloc_layer(QwenLayer& L, bool full) {
 void QwenEngine::alloc_buffers() {
   const size_t R = rows_cap_;
   for (int i = 0; i < 2; ++i) hidden_buf_[i] = dalloc(R * hidden_ * 2);
-  xn_ = dalloc(R * hidden_ * 2);
+  xn_ = opt_.tp_world > 1 ? nullptr : dalloc(R * hidden_ * 2);   // several ranks: inside the comm arena (set below)
   proj_ = dalloc(R * ld_proj_ * 2);
   const int attn_w = std::max(vd_l_, hq_l_ * kHeadDim);
   attn_out_ = dalloc(R * attn_w * 2);
@@ -278,12 +279,16 @@ void QwenEngine::alloc_buffers() {
   off_counter_ = off; off = align_up(off + 4, 256);
   // {value, sequence number} slots of the persistent decode kernel: [world][hidden] 8-byte words per site parity
   for (int s = 0; s < 2; ++s) { off_ll_[s] = off; off = align_up(off + (size_t)W * hidden_ * 8, 256); }
+  // tensor-parallel prefill: flags of the all-gather and the buffer of normalised rows that every owner writes into
+  for (int s = 0; s < 2; ++s) { off_agflag_[s] = off; off = align_up(off + PK_MAX_RANKS * 4, 256); }
+  if (W > 1) { off_xn_ = off; off = align_up(off + (size_t)rows_cap_ * hidden_ * 2, 256); }
   arena_bytes_ = off;
   arena_ = dalloc(arena_bytes_);
   cuda_check(cudaMemset(arena_, 0, std::min<size_t>(arena_bytes_, off_bslot_[0] + 4096)), "memset arena head");
   cuda_check(cudaMemset((char*)arena_ + off_cval_, 0, arena_bytes_ - off_cval_), "memset arena tail");
   for (int r = 0; r < PK_MAX_RANKS; ++r) peers_[r] = nullptr;
   peers_[opt_.tp_rank] = arena_;
+  if (W > 1) xn_ = (char*)arena_ + off_xn_;
   peer_cval_dev_ = (float**)dalloc(PK_MAX_RANKS * sizeof(void*));
   peer_cidx_dev_ = (int**)dalloc(PK_MAX_RANKS * sizeof(void*));
   peers_set_ = W == 1;
@@ -301,6 +306,7 @@ void QwenEngine::set_peer_arenas(void* const* arenas) {
     if (peers_[r] == nullptr) throw std::runtime_error("set_peer_arenas: null arena");
     cv[r] = (float*)((char*)peers_[r] + off_cval_);
     ci[r] = (int*)((char*)peers_[r] + off_cidx_);
+    xn_peer_[r] = opt_.tp_world > 1 ? (char*)peers_[r] + off_xn_ : nullptr;
   }
   cuda_check(cudaMemcpy(peer_cval_dev_, cv, sizeof cv, cudaMemcpyHostToDevice), "peer table");
   cuda_check(cudaMemcpy(peer_cidx_dev_, ci, sizeof ci, cudaMemcpyHostToDevice), "peer table");
@@ -315,6 +321,10 @@ void QwenEngine::set_peer_arenas(void* const* arenas) {
 QwenEngine::~QwenEngine() {
   cudaSetDevice(opt_.device);
   cudaStreamSynchronize(stream_);
+  for (auto& st : stored_) {
+    for (void* p : st.snap->bufs) cudaFree(p);
+    for (void* p : st.snap->kv) cudaFree(p);
+  }
   if (decode_graph_) cudaGraphExecDestroy(decode_graph_);
   for (void* p : allocs_) cudaFree(p);
   if (pinned_tok_) cudaFreeHost(pinned_tok_);
@@ -570,6 +580,7 @@ void QwenEngine::reset() {
   cuda_check(cudaMemsetAsync(out_counter_dev_, 0, sizeof(int), stream_), "memset");
   cuda_check(cudaStreamSynchronize(stream_), "reset");
   pos_ = 0;
+  history_.clear();
   last_token_ = -1;
   pending_site_ = -1;
   mtp_pos_ = 0;
@@ -641,6 +652,7 @@ void QwenEngine::restore(const Snapshot& s) {
   cuda_check(cudaMemcpyAsync(next_tok_dev_, &s.last_token, sizeof(int), cudaMemcpyHostToDevice, stream_), "restore token");
   cuda_check(cudaStreamSynchronize(stream_), "restore");
   pos_ = s.pos;
+  if ((int)history_.size() > s.pos) history_.resize((size_t)s.pos);
   last_token_ = s.last_token;
   mtp_ready_ = false;     // the predictor's boundary row belongs to the abandoned position
   mtp_pos_ = s.pos;
@@ -716,8 +728,9 @@ PkWait QwenEngine::make_wait(int site) const {
   return w;
 }
 
-PkPush QwenEngine::make_push(int site, bool big) const {
+PkPush QwenEngine::make_push(int site, bool big, int rows_per_rank) const {
   PkPush p{};
+  p.rows_per_rank = rows_per_rank;
   for (int r = 0; r < opt_.tp_world; ++r) {
     p.dst[r] = (float*)((char*)peers_[r] + (big ? off_bslot_[site & 1] : off_slot_[site & 1]));
     p.flag[r] = opt_.tp_world > 1 ? (uint32_t*)((char*)peers_[r] + off_flag_[site & 1]) : nullptr;
@@ -885,14 +898,18 @@ void QwenEngine::run_chunk(int M, bool mtp) {
     } else
       check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, stream_), "gemm_umma");
   };
-  // Row-parallel projection back into the residual stream. One rank: residual add in the
-  // epilogue. Several ranks: the epilogue pushes the fp32 partial tiles into every rank's
-  // slot and the next norm kernel sums them (all-reduce fused on both sides).
+  // Row-parallel projection back into the residual stream. One rank: residual add in the epilogue. Several ranks:
+  // reduce-scatter + all-gather around the norm. Rows are owned in blocks of rpr = ceil(M / W); the GEMM epilogue
+  // stores each fp32 partial row into its OWNER's slot only, tile by tile (1 / W of the bytes of a push to everyone);
+  // the owner's norm kernel adds the W partials and the residual for its rows, keeps the new residual rows to itself,
+  // and writes the normalised bf16 rows into every rank's activation buffer (the all-gather), then waits until the
+  // other owners' rows have arrived. The residual stream of rows a rank does not own is never needed there.
+  const int rpr = (M + W - 1) / W;
   auto gemm_out = [&](const void* A, int lda, const Fp8Linear& w, int site) {
     if (W == 1) {
       gemm(A, lda, w, 2, hid, hid, hidden_);
     } else {
-      PkPush ps = make_push(site, true);
+      PkPush ps = make_push(site, true, rpr);
       if (w.wb != nullptr)
         check(pk_gemm_bf16(A, lda, w.wb, M, w.N, w.K, 4, nullptr, nullptr, hidden_, gemm_status_, &ps, sm_count_, stream_), "gemm_bf16(push)");
       else
@@ -900,10 +917,20 @@ void QwenEngine::run_chunk(int M, bool mtp) {
       pending = site;
     }
   };
+  // y == nullptr with pending partials folds them into the owners' residual rows only.
   auto norm = [&](const float* gamma, void* y) {
     if (pending >= 0) {
-      PkWait wt = make_wait(pending);
-      check(pk_rmsnorm(hid, slot_parts(pending, true), W, M, hidden_, hid, gamma, 1, eps, y, &wt, stream_), "rmsnorm(reduce)");
+      PkWait wrs = make_wait(pending);
+      PkPush pag = make_push(pending, true);
+      PkWait wag = make_wait(pending);
+      for (int r = 0; r < W; ++r) pag.flag[r] = (uint32_t*)((char*)peers_[r] + off_agflag_[pending & 1]);
+      wag.flag = (const uint32_t*)((char*)arena_ + off_agflag_[pending & 1]);
+      check(pk_rmsnorm_rs_ag(hid, slot_parts(pending, true), W, opt_.tp_rank, rpr, M, hidden_, gamma, 1, eps, xn_peer_, &wrs, &pag, &wag,
+                             sm_count_, stream_),
+            "rmsnorm(reduce-scatter, all-gather)");
+      // the gathered rows live in the arena buffer; callers that want them elsewhere get a copy
+      if (y != nullptr && y != xn_)
+        cuda_check(cudaMemcpyAsync(y, xn_, (size_t)M * hidden_ * 2, cudaMemcpyDeviceToDevice, stream_), "copy normalised rows");
       pending = -1;
     } else {
       check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, gamma, 1, eps, y, nullptr, stream_), "rmsnorm");
@@ -956,7 +983,27 @@ void QwenEngine::run_chunk(int M, bool mtp) {
     sample_rows(1, logits_, next_tok_dev_);
     return;
   }
-  if (pending >= 0) norm(final_norm_, nullptr);  // fold the last partials into the residual stream
+  if (W > 1) {
+    // several ranks: only the owner of the last row has its residual; the final norm is the reduce-scatter /
+    // all-gather kind, and every rank reads the gathered last row
+    const char* xlast = (const char*)xn_ + (size_t)(M - 1) * hidden_ * 2;
+    if (mtp) {
+      norm(mtp_norm_, xn_);
+      cuda_check(cudaMemcpyAsync(mtp_out_, xlast, (size_t)hidden_ * 2, cudaMemcpyDeviceToDevice, stream_), "copy predictor row");
+      check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, mtp_out_, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 2,
+                      mtp_logits_, vocab_l_, nullptr, sm_count_, stream_),
+            "lm_head(mtp)");
+      sample_rows(1, mtp_logits_, mtp_next_dev_);
+      mtp_seed_ = mtp_out_;
+      return;
+    }
+    norm(final_norm_, xn_);
+    check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, xlast, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 2, logits_,
+                    vocab_l_, nullptr, sm_count_, stream_),
+          "lm_head");
+    sample_rows(1, logits_, next_tok_dev_);
+    return;
+  }
   const char* last = (const char*)hid + (size_t)(M - 1) * hidden_ * 2;
   if (mtp) {
     check(pk_rmsnorm(last, nullptr, 0, 1, hidden_, nullptr, mtp_norm_, 1, eps, mtp_out_, nullptr, stream_), "mtp norm");
@@ -1016,6 +1063,7 @@ int QwenEngine::prefill(const int* tokens_host, int n) {
   timings_.prefill_ms = ms;
   timings_.prefill_tokens = n;
   timings_.kernel_launches += launches_ - l0;
+  history_.insert(history_.end(), tokens_host, tokens_host + n);
   last_token_ = pinned_tok_[0];
   if (opt_.mtp) {
     mtp_ready_ = true;
@@ -1201,6 +1249,109 @@ void QwenEngine::enqueue_decode_step() {
   check(pk_store_token(next_tok_dev_, out_tokens_dev_, out_counter_dev_, out_cap_, stream_), "store token");
 }
 
+// ---------------------------------------------------------------------------------------
+// prefix reuse across requests
+
+void QwenEngine::clear_prefix_cache() {
+  for (auto& st : stored_) {
+    free_snapshot(*st.snap);
+  }
+  stored_.clear();
+  prefix_stats_.snapshots = 0;
+  prefix_stats_.snapshot_bytes = 0;
+}
+
+void QwenEngine::drop_states_after(int pos) {
+  for (size_t i = 0; i < stored_.size();) {
+    if (stored_[i].snap->pos > pos) {
+      free_snapshot(*stored_[i].snap);
+      stored_.erase(stored_.begin() + (long)i);
+    } else {
+      ++i;
+    }
+  }
+}
+
+void QwenEngine::store_state() {
+  if (opt_.max_snapshots <= 0 || pos_ <= 0) return;
+  for (auto& st : stored_)
+    if (st.snap->pos == pos_) {   // same position again (a repeated prompt): refresh its age
+      st.stamp = ++stamp_;
+      return;
+    }
+  if ((int)stored_.size() >= opt_.max_snapshots) {
+    std::vector<int> positions;
+    std::vector<long long> stamps;
+    for (auto& st : stored_) {
+      positions.push_back(st.snap->pos);
+      stamps.push_back(st.stamp);
+    }
+    const int v = snapshot_to_evict(positions, stamps, opt_.snapshot_interval);
+    if (v >= 0) {
+      free_snapshot(*stored_[(size_t)v].snap);
+      stored_.erase(stored_.begin() + v);
+    }
+  }
+  StoredState st;
+  st.snap = snapshot(false);
+  st.stamp = ++stamp_;
+  stored_.push_back(std::move(st));
+}
+
+int QwenEngine::prefill_cached(const int* tokens_host, int n) {
+  if (n < 1) throw std::runtime_error("prefill: empty prompt");
+  QwenPrefixStats& ps = prefix_stats_;
+  ps.prompt_tokens = n;
+  if (!opt_.prefix_cache) {
+    reset();
+    ps.reused_tokens = 0;
+    ps.computed_tokens = n;
+    ps.matched_tokens = 0;
+    ps.resume_source = "empty";
+    return prefill(tokens_host, n);
+  }
+  std::vector<int> positions;
+  for (auto& st : stored_) positions.push_back(st.snap->pos);
+  const PrefixDecision d = plan_prefix(history_, pos_, positions, tokens_host, n);
+  ps.matched_tokens = d.matched;
+  ps.resume_source = prefix_source_name(d.source);
+  if (d.source == PrefixDecision::kLive) {
+    // continue where the engine stands; the pending token (generated, not yet consumed) is simply dropped
+  } else if (d.source == PrefixDecision::kSnapshot) {
+    StoredState& st = stored_[(size_t)d.snapshot_index];
+    st.stamp = ++stamp_;
+    restore(*st.snap);
+  } else {
+    // nothing reusable: the stored states describe another sequence from position 0 on
+    const std::vector<int> keep;
+    (void)keep;
+    clear_prefix_cache();
+    reset();
+  }
+  drop_states_after(d.resume_pos);   // positions past the resume point are about to be overwritten
+  if (d.resume_pos > 0) ++ps.hits; else ++ps.misses;
+  ps.reused_tokens = d.resume_pos;
+  ps.computed_tokens = n - d.resume_pos;
+  int first = -1;
+  double ms = 0;
+  int from = d.resume_pos;
+  for (int to : snapshot_points(d.resume_pos, n, opt_.snapshot_interval)) {
+    // the last piece ends at the request boundary; its state is stored too, for prompts that share this one as a prefix
+    first = prefill(tokens_host + from, to - from);
+    ms += timings_.prefill_ms;
+    store_state();
+    from = to;
+  }
+  timings_.prefill_ms = ms;
+  timings_.prefill_tokens = n - d.resume_pos;
+  ps.snapshots = (int)stored_.size();
+  unsigned long long bytes = 0;
+  for (auto& L : layers_)
+    if (!L.full) bytes += (unsigned long long)vh_l_ * kHeadDim * kHeadDim * sizeof(float) + (unsigned long long)conv_c_l_ * 3 * sizeof(float);
+  ps.snapshot_bytes = bytes * stored_.size();
+  return first;
+}
+
 void QwenEngine::capture_decode_graph() {
   cudaGraph_t g = nullptr;
   if (!persistent_built_) build_persistent();   // allocations and copies stay outside the capture
@@ -1261,6 +1412,9 @@ void QwenEngine::decode(int steps, int* out_host, bool sync_each_step) {
   timings_.decode_tokens = steps;
   timings_.kernel_launches += launches_ - l0;
   pos_ += steps;
+  // consumed by these steps: the token that was pending, then every new token but the last
+  history_.push_back(last_token_);
+  history_.insert(history_.end(), pinned_tok_, pinned_tok_ + (steps - 1));
   last_token_ = pinned_tok_[steps - 1];
   mtp_ready_ = false;   // the predictor has not seen these positions
   mtp_pos_ = pos_;
@@ -1284,6 +1438,7 @@ void QwenEngine::forward_rows(const int* tokens_host, int M, int* out_tokens_hos
   cuda_check(cudaStreamSynchronize(stream_), "forward_rows");
   raise_if_step_failed("forward_rows");
   pos_ += M;
+  history_.insert(history_.end(), tokens_host, tokens_host + M);
   last_token_ = pinned_tok_[M - 1];
   mtp_ready_ = false;
   mtp_pos_ = pos_;

@@ -41,6 +41,24 @@ struct QwenEngineOptions {
   // peer-flag barriers instead of kernel boundaries): -1 = when the shapes fit its shared-memory plan, 0 = never
   // (one launch per projection), 1 = required. POCKET_DECODE_PERSISTENT in the environment overrides.
   int persistent_decode = -1;
+  // Exact prefix reuse across sequential requests (prefill_cached): the KV cache is position indexed and stays, the
+  // recurrent state continues live or rolls back to a stored copy. Copies are taken every `snapshot_interval` tokens
+  // of a prefill (0: only at request boundaries), at most `max_snapshots` of them.
+  bool prefix_cache = true;
+  int snapshot_interval = 4096;
+  int max_snapshots = 82;
+};
+
+// Outcome of the last prefill_cached().
+struct QwenPrefixStats {
+  int reused_tokens = 0;        // prompt tokens that needed no forward pass
+  int computed_tokens = 0;
+  int prompt_tokens = 0;
+  int matched_tokens = 0;       // common prefix with the consumed sequence, before rounding to a resume point
+  const char* resume_source = "empty";   // "empty", "live" or "snapshot"
+  int snapshots = 0;
+  unsigned long long snapshot_bytes = 0;
+  long long hits = 0, misses = 0;
 };
 
 // Counters of spec_decode().
@@ -123,6 +141,17 @@ class QwenEngine {
   void reset();
   // Runs the prompt in chunks; returns the first generated token (greedy).
   int prefill(const int* tokens_host, int n);
+  // A new request: reuses the longest prefix of `tokens_host` that the engine has already consumed (see prefix_plan.hpp),
+  // runs the rest, and stores recurrent-state copies on the way. With the cache switched off: reset() + prefill().
+  int prefill_cached(const int* tokens_host, int n);
+  const QwenPrefixStats& prefix_stats() const { return prefix_stats_; }
+  void clear_prefix_cache();
+  void configure_prefix_cache(bool enable, int snapshot_interval, int max_snapshots) {
+    clear_prefix_cache();
+    opt_.prefix_cache = enable;
+    opt_.snapshot_interval = snapshot_interval;
+    opt_.max_snapshots = max_snapshots;
+  }
   // Greedy decode of `steps` tokens following the last generated one. Tokens are
   // written to out_host (may be null). `sync_each_step` reads every token back as soon as
   // its step ends (streaming); otherwise one read at the end.
@@ -200,7 +229,7 @@ class QwenEngine {
   void enqueue_decode_step();      // one greedy single-row step on stream_ (persistent kernel or per-projection launches)
   void build_persistent();         // descriptor table and parameters of the persistent decode kernel
   PkWait make_wait(int site) const;
-  PkPush make_push(int site, bool big = false) const;
+  PkPush make_push(int site, bool big = false, int rows_per_rank = 0) const;
   float* slot_parts(int site, bool big = false) const;
   void check(int status, const char* what) const;
 
@@ -254,6 +283,9 @@ class QwenEngine {
   size_t arena_bytes_ = 0;
   size_t off_bslot_[2];   // prefill-size slots [world][rows_cap][hidden] fp32
   size_t off_ll_[2];
+  size_t off_agflag_[2] = {0, 0}, off_xn_ = 0;   // all-gather flags and the peer-visible buffer of normalised prefill rows
+  void** xn_peer_dev_ = nullptr;   // unused on the device; host table below
+  void* xn_peer_[PK_MAX_RANKS] = {nullptr};
   size_t off_slot_[2], off_flag_[2], off_cval_, off_cidx_, off_cflag_, off_epoch_, off_status_, off_counter_;
   void* peers_[PK_MAX_RANKS] = {nullptr};
   float** peer_cval_dev_ = nullptr;
@@ -298,6 +330,18 @@ class QwenEngine {
   unsigned long long* dec_dbg_ = nullptr;   // phase trace of the last step (POCKET_DECODE_TRACE=1)
   int dec_dbg_cap_ = 0;
   int dec_grid_ = 0;
+
+  // prefix reuse: tokens consumed so far (positions 0 .. pos_-1) and stored recurrent states
+  std::vector<int> history_;
+  struct StoredState {
+    std::unique_ptr<Snapshot> snap;
+    long long stamp = 0;
+  };
+  std::vector<StoredState> stored_;
+  long long stamp_ = 0;
+  QwenPrefixStats prefix_stats_;
+  void store_state();            // copy of the recurrent state at pos_
+  void drop_states_after(int pos);
 
   int pos_ = 0;
   int last_token_ = -1;

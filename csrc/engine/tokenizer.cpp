@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <climits>
+#include <cstdio>
 #include <stdexcept>
 
 namespace pk {
@@ -93,6 +94,53 @@ BpeTokenizer BpeTokenizer::from_gguf(const GgufFile& file) {
       ++i;
     }
   }
+  return BpeTokenizer(std::move(tokens), merges, special);
+}
+
+BpeTokenizer BpeTokenizer::from_hf_dir(const std::string& dir_or_file) {
+  std::string path = dir_or_file;
+  const std::string suffix = ".json";
+  if (path.size() < suffix.size() || path.compare(path.size() - suffix.size(), suffix.size(), suffix) != 0) path += "/tokenizer.json";
+  FILE* f = std::fopen(path.c_str(), "rb");
+  if (f == nullptr) throw std::runtime_error("tokenizer: cannot open " + path);
+  std::string text;
+  char buf[1 << 16];
+  size_t got;
+  while ((got = std::fread(buf, 1, sizeof buf, f)) > 0) text.append(buf, got);
+  std::fclose(f);
+  const Json root = Json::parse(text);
+  const Json* model = root.find("model");
+  if (model == nullptr || !model->is_object()) throw std::runtime_error("tokenizer: " + path + " has no model section");
+  const std::string type = model->get_string("type", "BPE");
+  if (type != "BPE") throw std::runtime_error("tokenizer: unsupported model type " + type + " (byte-level BPE only)");
+  const Json* vocab = model->find("vocab");
+  if (vocab == nullptr || !vocab->is_object()) throw std::runtime_error("tokenizer: model.vocab is missing");
+  int64_t max_id = -1;
+  for (const auto& kv : vocab->members()) max_id = std::max<int64_t>(max_id, kv.second.as_int());
+  const Json* added = root.find("added_tokens");
+  if (added != nullptr && added->is_array())
+    for (const Json& a : added->items()) max_id = std::max<int64_t>(max_id, a.get_int("id", -1));
+  if (max_id < 0 || max_id > (1 << 24)) throw std::runtime_error("tokenizer: implausible vocabulary size");
+  std::vector<std::string> tokens((size_t)max_id + 1);
+  for (const auto& kv : vocab->members()) {
+    const int64_t id = kv.second.as_int();
+    if (id < 0) throw std::runtime_error("tokenizer: negative token id");
+    tokens[(size_t)id] = kv.first;
+  }
+  std::vector<int> special;
+  if (added != nullptr && added->is_array())
+    for (const Json& a : added->items()) {
+      const int64_t id = a.get_int("id", -1);
+      if (id < 0) continue;
+      tokens[(size_t)id] = a.get_string("content", tokens[(size_t)id]);
+      special.push_back((int)id);   // added tokens are matched verbatim, whether flagged special or not
+    }
+  std::vector<std::string> merges;
+  if (const Json* m = model->find("merges"))
+    for (const Json& x : m->items()) {
+      if (x.is_string()) merges.push_back(x.as_string());
+      else if (x.is_array() && x.size() == 2) merges.push_back(x.items()[0].as_string() + " " + x.items()[1].as_string());
+    }
   return BpeTokenizer(std::move(tokens), merges, special);
 }
 

@@ -1,5 +1,5 @@
 // Byte-level BPE tokenizer for the native front end: vocabulary, merges and special tokens from GGUF metadata
-// (tokenizer.ggml.tokens / merges / token_type), GPT-2 style byte-to-unicode mapping and pre-tokenisation.
+// (tokenizer.ggml.tokens / merges / token_type) or from a Hugging Face tokenizer.json, GPT-2 style byte-to-unicode mapping and pre-tokenisation.
 // Role of the reference's cpp_engine/src/tokenizer.cpp and tools/minimax_gguf_tokenizer.
 //
 // Pre-tokenisation follows the GPT-2 pattern
@@ -22,6 +22,9 @@ class BpeTokenizer {
   // tokens in the byte-level unicode alphabet; merges as "left right"; special = ids matched verbatim in the input
   BpeTokenizer(std::vector<std::string> tokens, const std::vector<std::string>& merges, const std::vector<int>& special);
   static BpeTokenizer from_gguf(const GgufFile& file);
+  // A Hugging Face tokenizer directory (or the tokenizer.json file itself): model.vocab, model.merges (strings "a b" or
+  // pairs ["a", "b"]) and added_tokens of a byte-level BPE tokenizer (reference: cpp_engine/include/tokenizer.hpp:14-40).
+  static BpeTokenizer from_hf_dir(const std::string& dir_or_file);
 
   std::vector<int> encode(const std::string& text, bool parse_special = true) const;
   std::string decode(const std::vector<int>& ids, bool skip_special = false) const;

@@ -345,8 +345,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (n + i < p.N) dst[i] = __uint_as_float(r[i]);
             }
           } else if (p.epi == EPI_PUSH) {
-            const size_t off = ((size_t)p.push.rank * p.M + m) * p.ldc + n;
-            for (int pr = 0; pr < p.push.world; ++pr) {
+            // rows_per_rank > 0: reduce-scatter, the row goes to its owner only (1 / world of the bytes of push-to-all)
+            const int rpr = p.push.rows_per_rank;
+            const int owner = rpr > 0 ? m / rpr : 0;
+            const size_t off = rpr > 0 ? ((size_t)p.push.rank * rpr + (m - owner * rpr)) * p.ldc + n
+                                       : ((size_t)p.push.rank * p.M + m) * p.ldc + n;
+            const int pr_lo = rpr > 0 ? owner : 0, pr_hi = rpr > 0 ? owner + 1 : p.push.world;
+            for (int pr = pr_lo; pr < pr_hi; ++pr) {
               float* dst = p.push.dst[pr] + off;
               if (n + 32 <= p.N) {
 #pragma unroll

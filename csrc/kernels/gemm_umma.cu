@@ -265,8 +265,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         } else if (p.epi == EPI_PUSH) {
           // The scatter side of the all-reduce, issued tile by tile from the epilogue: this
           // rank's fp32 partial goes straight into every peer's slot over NVLink.
-          const size_t off = ((size_t)p.push.rank * p.M + m) * p.ldc + n;
-          for (int pr = 0; pr < p.push.world; ++pr) {
+          // rows_per_rank > 0: reduce-scatter, the row goes to its owner only (1 / world of the bytes of push-to-all)
+          const int rpr = p.push.rows_per_rank;
+          const int owner = rpr > 0 ? m / rpr : 0;
+          const size_t off = rpr > 0 ? ((size_t)p.push.rank * rpr + (m - owner * rpr)) * p.ldc + n
+                                     : ((size_t)p.push.rank * p.M + m) * p.ldc + n;
+          const int pr_lo = rpr > 0 ? owner : 0, pr_hi = rpr > 0 ? owner + 1 : p.push.world;
+          for (int pr = pr_lo; pr < pr_hi; ++pr) {
             float* dst = p.push.dst[pr] + off;
             if (n + 32 <= p.N) {
 #pragma unroll

@@ -64,6 +64,57 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const NormParams p) {
   }
 }
 
+// Reduce-scatter / all-gather form of the tensor-parallel RMSNorm (prefill): this rank owns rows
+// [rank * rpr, rank * rpr + rows_mine). For each of them: x = hidden + sum_r parts[r] (fp32 partial rows that the
+// row-parallel GEMM epilogues of every rank pushed here), hidden = bf16(x) (kept on the owner only), y = rmsnorm(x),
+// and y is stored as bf16 into EVERY rank's copy of the normalised activations (the all-gather, fused into the norm).
+// Then the rank publishes its all-gather flag and waits for the others', so that the kernel's end means "all rows of y
+// are here". Per site a rank sends (world-1)/world of one fp32 row block plus (world-1) bf16 row blocks instead of
+// world fp32 copies of everything.
+struct NormAgParams {
+  bf16* hidden;          // local [M, K] residual stream; only the owned rows are read and written
+  const float* parts;    // local slot [world][rpr][K] fp32
+  int world, rank, rpr, rows_mine, K;
+  const float* gamma;
+  int mode;
+  float eps;
+  bf16* y_peer[PK_MAX_RANKS];      // every rank's [M, K] bf16 buffer of normalised rows (own one included)
+  PkWait wait_rs;        // flags of the reduce-scatter pushes (all ranks have stored their partials)
+  PkPush pub_ag;         // flags of the all-gather (dst unused)
+  PkWait wait_ag;
+};
+
+__global__ void __launch_bounds__(256) rmsnorm_rs_ag_kernel(const NormAgParams p) {
+  extern __shared__ float row[];
+  __shared__ float red[40];
+  if (threadIdx.x == 0) wait_all_ranks(p.wait_rs);
+  __syncthreads();
+  for (int ml = blockIdx.x; ml < p.rows_mine; ml += gridDim.x) {
+    const int m = p.rank * p.rpr + ml;
+    float ss = 0.f;
+    for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
+      float v = __bfloat162float(p.hidden[(size_t)m * p.K + k]);
+      for (int r = 0; r < p.world; ++r) v += p.parts[((size_t)r * p.rpr + ml) * p.K + k];
+      const bf16 hv = __float2bfloat16(v);
+      p.hidden[(size_t)m * p.K + k] = hv;
+      v = __bfloat162float(hv);
+      row[k] = v;
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)p.K + p.eps);
+    for (int k2 = threadIdx.x * 2; k2 < p.K; k2 += blockDim.x * 2) {
+      const float g0 = p.gamma[k2], g1 = p.gamma[k2 + 1];
+      const __nv_bfloat162 yv = __floats2bfloat162_rn(row[k2] * rs * (p.mode == 1 ? 1.f + g0 : g0),
+                                                      row[k2 + 1] * rs * (p.mode == 1 ? 1.f + g1 : g1));
+      for (int r = 0; r < p.world; ++r) *reinterpret_cast<__nv_bfloat162*>(p.y_peer[r] + (size_t)m * p.K + k2) = yv;
+    }
+    __syncthreads();   // `row` is reused by the block's next row
+  }
+  publish_when_grid_done(p.pub_ag);
+  if (threadIdx.x == 0) wait_all_ranks(p.wait_ag);
+}
+
 __global__ void silu_mul_kernel(const bf16* gu, int inter, bf16* out, float limit) {
   // gu: [M, 2*inter] = gate | up
   const int m = blockIdx.y;
@@ -216,6 +267,44 @@ PK_API int pk_rmsnorm(const void* x, const float* parts, int nparts, int M, int 
     }
   }
   PK_LAUNCH(rmsnorm_kernel, dim3(M), dim3(256), smem, stream, p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
+// See rmsnorm_rs_ag_kernel. `y_peer[r]` is rank r's buffer of normalised rows (peer memory for r != rank); K even.
+PK_API int pk_rmsnorm_rs_ag(void* hidden, const float* parts, int world, int rank, int rows_per_rank, int M, int K, const float* gamma,
+                            int mode, float eps, void* const* y_peer, const PkWait* wait_rs, const PkPush* pub_ag, const PkWait* wait_ag,
+                            int sm_count, cudaStream_t stream) {
+  if (world < 1 || world > PK_MAX_RANKS || rank < 0 || rank >= world || rows_per_rank < 1 || M < 1 || K < 2 || (K & 1)) return PK_ERR_BAD_ARG;
+  if (wait_rs == nullptr || pub_ag == nullptr || wait_ag == nullptr || y_peer == nullptr) return PK_ERR_BAD_ARG;
+  NormAgParams p{};
+  p.hidden = (pk::bf16*)hidden;
+  p.parts = parts;
+  p.world = world;
+  p.rank = rank;
+  p.rpr = rows_per_rank;
+  const int lo = rank * rows_per_rank;
+  p.rows_mine = lo >= M ? 0 : (M - lo < rows_per_rank ? M - lo : rows_per_rank);
+  p.K = K;
+  p.gamma = gamma;
+  p.mode = mode;
+  p.eps = eps;
+  for (int r = 0; r < world; ++r) p.y_peer[r] = (pk::bf16*)y_peer[r];
+  p.wait_rs = *wait_rs;
+  p.pub_ag = *pub_ag;
+  p.wait_ag = *wait_ag;
+  const size_t smem = (size_t)K * sizeof(float);
+  if (smem > 200 * 1024) return PK_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(rmsnorm_rs_ag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    pk_set_last_cuda_error((int)cudaGetLastError());
+    return PK_ERR_CUDA;
+  }
+  // at least one block even without rows: every rank publishes and waits
+  int blocks = p.rows_mine > 0 ? p.rows_mine : 1;
+  const int cap = (sm_count > 0 ? sm_count : 148) * 4;
+  if (blocks > cap) blocks = cap;
+  PK_LAUNCH(rmsnorm_rs_ag_kernel, dim3(blocks), dim3(256), smem, stream, p);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }

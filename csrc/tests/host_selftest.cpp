@@ -17,6 +17,7 @@
 #include "../engine/json.hpp"
 #include "../engine/safetensors.hpp"
 #include "../engine/sampler.hpp"
+#include "../engine/prefix_plan.hpp"
 #include "../engine/spec_policy.hpp"
 
 #define CHECK(cond)                                                             \
@@ -203,6 +204,48 @@ static int test_block_counters() {
   return 0;
 }
 
+// Prefix reuse decisions: live continuation, roll back to a stored state, start from zero; snapshot placement and eviction.
+static int test_prefix_plan() {
+  using pk::PrefixDecision;
+  const std::vector<int> hist = {1, 2, 3, 4, 5, 6, 7, 8};   // the engine has consumed 8 tokens and stands at position 8
+  const std::vector<int> snaps = {4, 6, 8};
+  {  // the new prompt extends the whole consumed sequence: continue live, nothing restored
+    const int p[] = {1, 2, 3, 4, 5, 6, 7, 8, 9, 10};
+    const PrefixDecision d = pk::plan_prefix(hist, 8, snaps, p, 10);
+    CHECK(d.source == PrefixDecision::kLive && d.resume_pos == 8 && d.matched == 8);
+  }
+  {  // the same prompt again: one token must still run, so the state at 8 is too far; the one at 6 serves
+    const int p[] = {1, 2, 3, 4, 5, 6, 7, 8};
+    const PrefixDecision d = pk::plan_prefix(hist, 8, snaps, p, 8);
+    CHECK(d.source == PrefixDecision::kSnapshot && d.resume_pos == 6 && d.snapshot_index == 1 && d.matched == 8);
+  }
+  {  // divergence at position 5: roll back to the state stored at 4
+    const int p[] = {1, 2, 3, 4, 5, 99, 98, 97};
+    const PrefixDecision d = pk::plan_prefix(hist, 8, snaps, p, 8);
+    CHECK(d.source == PrefixDecision::kSnapshot && d.resume_pos == 4 && d.matched == 5);
+  }
+  {  // divergence before the first stored state, or no state at all: from zero
+    const int p[] = {1, 2, 3, 77};
+    CHECK(pk::plan_prefix(hist, 8, snaps, p, 4).source == PrefixDecision::kEmpty);
+    const int q[] = {1, 2, 3, 4, 5, 6};
+    CHECK(pk::plan_prefix(hist, 8, {}, q, 6).source == PrefixDecision::kEmpty);
+    CHECK(pk::plan_prefix({}, 0, {}, q, 6).resume_pos == 0);
+  }
+  {  // a shorter history than the live position (state restored by other means) can only match what it records
+    const int p[] = {1, 2, 3, 4, 5};
+    const PrefixDecision d = pk::plan_prefix({1, 2}, 8, {2}, p, 5);
+    CHECK(d.matched == 2 && d.source == PrefixDecision::kSnapshot && d.resume_pos == 2);
+  }
+  CHECK((pk::snapshot_points(0, 10, 4) == std::vector<int>{4, 8, 10}));
+  CHECK((pk::snapshot_points(4, 8, 4) == std::vector<int>{8}));
+  CHECK((pk::snapshot_points(3, 9, 0) == std::vector<int>{9}));
+  CHECK(pk::snapshot_points(5, 5, 4).empty());
+  // eviction: request boundaries (not multiples of the interval) go first, oldest first; else the oldest of all
+  CHECK(pk::snapshot_to_evict({4, 8, 10, 13}, {1, 2, 4, 3}, 4) == 3);
+  CHECK(pk::snapshot_to_evict({4, 8, 12}, {5, 2, 9}, 4) == 1);
+  return 0;
+}
+
 // Draft-length policy of speculative decode: a whole request simulated on the host.
 static int test_spec_policy() {
   using pk::drafts_this_round;
@@ -245,6 +288,7 @@ int main(int argc, char** argv) {
     if (test_control_plane(argv[3])) return 1;
     if (test_protocol()) return 1;
     if (test_block_counters()) return 1;
+    if (test_prefix_plan()) return 1;
     if (test_spec_policy()) return 1;
   } catch (const std::exception& e) {
     std::fprintf(stderr, "host_selftest: unexpected exception: %s\n", e.what());

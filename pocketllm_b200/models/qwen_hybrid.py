@@ -435,6 +435,25 @@ class QwenEngine:
         self._ck(self._L.pk_qwen_prefill(self._h, arr, len(tokens), ctypes.byref(first)))
         return first.value
 
+    def prefill_reusing(self, tokens: Sequence[int]) -> tuple[int, dict]:
+        """A new request with the engine's native prefix reuse: the KV cache is position indexed and stays between
+        requests, the recurrent state continues live or rolls back to a stored copy (reference behaviour:
+        cpp_engine/src/qwen_engine.cpp:662-826). Returns (first token, statistics)."""
+        arr = (ctypes.c_int * len(tokens))(*[int(t) for t in tokens])
+        first = ctypes.c_int(0)
+        st = (ctypes.c_longlong * 9)()
+        self._ck(self._L.pk_qwen_prefill_cached(self._h, arr, len(tokens), ctypes.byref(first), st))
+        names = ("reused_tokens", "computed_tokens", "prompt_tokens", "matched_tokens", "source", "snapshots", "snapshot_bytes", "hits", "misses")
+        d = dict(zip(names, (int(v) for v in st)))
+        d["source"] = ("empty", "live", "snapshot")[d["source"]]
+        return first.value, d
+
+    def clear_prefix_cache(self) -> None:
+        self._ck(self._L.pk_qwen_clear_prefix_cache(self._h))
+
+    def configure_prefix_cache(self, enable: bool = True, snapshot_interval: int = 4096, max_snapshots: int = 82) -> None:
+        self._ck(self._L.pk_qwen_configure_prefix_cache(self._h, int(enable), snapshot_interval, max_snapshots))
+
     def decode(self, steps: int, sync_each_step: bool = False) -> list[int]:
         out = (ctypes.c_int * steps)()
         self._ck(self._L.pk_qwen_decode(self._h, steps, out, int(sync_each_step)))

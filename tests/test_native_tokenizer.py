@@ -37,6 +37,7 @@ def trained(tmp_path_factory):
     import numpy as np
     w.add_tensor("dummy", np.zeros(32, np.float32), "f32")
     w.write(path)
+    tok.save(str(path.parent / "tokenizer.json"))
     return path, gguf_tokenizer.build_tokenizer(gguf_tokenizer.read_metadata(path))
 
 
@@ -60,6 +61,27 @@ def test_native_tokenizer_matches_library(trained):
     assert list(buf[:n]) != [ref.token_to_id("<|eos|>"), ref.token_to_id("x")]
     assert L.pk_tokenizer_decode(h, (ctypes.c_int * 2)(ref.token_to_id("<|eos|>"), ref.token_to_id("a")), 2, 1).decode() == "a"
     L.pk_tokenizer_destroy(h)
+
+
+def test_native_tokenizer_from_tokenizer_json(trained):
+    """The same vocabulary read from a Hugging Face tokenizer.json directory gives the same ids."""
+    from pocketllm_b200.ops import lib
+    path, ref = trained
+    L = lib.engine()
+    L.pk_tokenizer_from_hf.restype = ctypes.c_void_p
+    L.pk_tokenizer_decode.restype = ctypes.c_char_p
+    h = ctypes.c_void_p(L.pk_tokenizer_from_hf(str(path.parent).encode()))
+    assert h.value, L.pk_engine_last_error()
+    buf = (ctypes.c_int * 4096)()
+    for text in TEXTS + CORPUS[:7]:
+        n = L.pk_tokenizer_encode(h, text.encode(), 1, buf, 4096)
+        assert list(buf[:n]) == ref.encode(text, add_special_tokens=False).ids, text
+        assert L.pk_tokenizer_decode(h, (ctypes.c_int * n)(*buf[:n]), n, 0).decode() == text
+    L.pk_tokenizer_destroy(h)
+    assert not L.pk_tokenizer_from_hf(str(path.parent / "missing").encode())
+    exe = ROOT / "pocketllm_b200" / "_C" / "pocket_engine"
+    out = subprocess.run([str(exe), "--tokenizer-dir", str(path.parent), "--tokenize", "Hello, world!"], capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0 and [int(t) for t in out.stdout.strip().split("=", 1)[1].split(",")] == ref.encode("Hello, world!", add_special_tokens=False).ids
 
 
 def test_tokenizer_cli_tool(trained):

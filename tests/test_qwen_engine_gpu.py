@@ -410,3 +410,56 @@ def test_native_server_with_multi_token_predictor(tiny_mtp):
             rest = ""
     stats = dict(kv.split("=") for l in rest.splitlines() if l.startswith("serve_mtp_rounds") for kv in l.split())
     assert int(stats["serve_mtp_rounds"]) > 0 and int(stats["serve_mtp_proposed"]) >= int(stats["serve_mtp_accepted"])
+
+
+def test_native_prefix_reuse_across_requests(tiny):
+    """Sequential requests through the engine's own prefix reuse: a chat that grows (live continuation), a prompt that
+    diverges in the middle (roll back to a stored recurrent state), an unrelated prompt (from zero). Tokens always
+    equal those of a fresh engine."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    fresh = qh.QwenEngine(cfg, max_context=512, prefill_chunk=64, persistent_decode=0).load(d)
+    eng = qh.QwenEngine(cfg, max_context=512, prefill_chunk=64, persistent_decode=0).load(d)
+    eng.configure_prefix_cache(True, snapshot_interval=16, max_snapshots=6)
+    fresh.configure_prefix_cache(True, snapshot_interval=16, max_snapshots=6)
+    torch.manual_seed(11)
+    base = torch.randint(0, cfg.vocab_size, (70,)).tolist()
+
+    def want(prompt, n):
+        # from zero, cut into the same pieces (a piece of other length takes other kernels and rounds differently)
+        fresh.clear_prefix_cache()
+        fresh.reset()
+        first, st = fresh.prefill_reusing(prompt)
+        assert st["reused_tokens"] == 0
+        return [first] + fresh.decode(n - 1)
+
+    def got(prompt, n):
+        first, st = eng.prefill_reusing(prompt)
+        return [first] + eng.decode(n - 1), st
+
+    out1, st = got(base, 6)
+    assert out1 == want(base, 6) and st["source"] == "empty" and st["reused_tokens"] == 0 and st["snapshots"] == 5   # 16, 32, 48, 64, 70
+    # the conversation continues: old prompt + the reply + a new turn -> everything consumed so far is reused
+    turn2 = base + out1[:5] + [7, 8, 9]
+    out2, st = got(turn2, 5)
+    assert out2 == want(turn2, 5)
+    assert st["source"] == "live" and st["reused_tokens"] == 75 and st["computed_tokens"] == 3
+    # a prompt that shares 40 tokens: the state stored at 32 serves, 32 tokens are not recomputed
+    fork = base[:40] + [1, 2, 3, 4, 5, 6]
+    out3, st = got(fork, 4)
+    assert out3 == want(fork, 4)
+    assert st["source"] == "snapshot" and st["reused_tokens"] == 32 and st["matched_tokens"] == 40
+    # the same prompt once more: its own boundary state (46) is one token too far, the one at 32 serves again
+    out4, st = got(fork, 4)
+    assert out4 == out3 and st["source"] == "snapshot" and st["reused_tokens"] == 32
+    # nothing in common
+    other = [(t + 1) % cfg.vocab_size for t in base[:20]]
+    out5, st = got(other, 4)
+    assert out5 == want(other, 4) and st["source"] == "empty" and st["hits"] == 3 and st["misses"] == 2
+    # switched off: reset + one prefill of the whole prompt
+    eng.configure_prefix_cache(False)
+    out6, st = got(other, 4)
+    assert len(out6) == 4 and st["reused_tokens"] == 0 and st["source"] == "empty"
+    assert eng.comm_status() == 0
+    fresh.close()
+    eng.close()
