@@ -141,8 +141,14 @@ def run(args) -> dict:
             "vs_baseline": round(dec / PUBLISHED_DECODE_TOK_S, 3), "dtype": "fp16 activations, fp8 e4m3 weights (reference default path)",
             "data": "synthetic: uniform-random token prompts, random-init FP8 checkpoint in the reference's Safetensors layout",
             "prefill_tok_s": round(pre, 1), "timing": "reference's own host wall clock per request",
+            # the same keys as the other arm's config
             "config": {"model": "Qwen3.8-27B-FP8-shaped hybrid (64L, hidden 5120, inter 17408, vocab 151936)" if args.model == "qwen27b" else "tiny",
                        "global_batch": 1, "seq_len": args.prompt_len, "decode_len": args.decode_len, "parallelism": f"tp{world}",
-                       "engine": "dsv4_cpp_engine --qwen-persistent-stdin (NCCL)"},
-            "e2e": {"value": round(dec, 2), "unit": "tok/s", "note": "the reference's CLI is its public API; tokens enter and leave through the host"},
+                       "l2": "inputs larger than L2 (27 GB of weights streamed per token)", "prefill_chunk": 512},
+            "engine": "dsv4_cpp_engine --qwen-persistent-stdin (NCCL)",
+            # the prompt's token ids go in as text on stdin and the generated ids come back as text on stdout; counted as
+            # 4-byte ids like the other arm's pinned-memory copies
+            "e2e": {"value": round(dec, 2), "unit": "tok/s", "h2d_bytes_per_step": args.prompt_len * 4, "d2h_bytes_per_step": (args.decode_len + 1) * 4,
+                    "note": "the reference's CLI is its public API; tokens enter and leave through the host"},
+            "first_tokens": [int(t) for t in timed[-1].split("generated_token_ids=")[-1].split()[0].split(",")[:16]] if "generated_token_ids=" in timed[-1] else [],
             "total_wall_s": round(wall, 1)}

@@ -150,7 +150,9 @@ def run_ours(args) -> dict:
         "metric": "single-request decode tok/s (Qwen3.8-27B-FP8 shape, 512-token prompt, 256 greedy steps)",
         "value": round(decode_tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round((pre_ms + dec_ms) / args.steps, 3), "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": round(decode_tok_s / PUBLISHED_DECODE_TOK_S, 3), "dtype": "bf16 activations, fp8 e4m3 weights (128x128 scales)",
+        "vs_baseline": round(decode_tok_s / PUBLISHED_DECODE_TOK_S, 3),
+        "dtype": ("bf16 activations; decode streams the fp8 e4m3 weights (128x128 scales); prefill GEMMs read "
+                  + ("bf16 copies of them (see prefill_bf16_shadow_bytes_per_rank)" if eng.prefill_shadow_bytes else "the same fp8 weights")),
         "data": "synthetic: uniform-random token prompts, random-init N(0,0.02) weights quantised to FP8",
         "prefill_tok_s": round(prefill_tok_s, 1), "prefill_vs_baseline": round(prefill_tok_s / PUBLISHED_PREFILL_TOK_S, 2),
         "prefill_ms": round(pre_ms / args.steps, 3), "decode_ms_per_token": round(dec_ms / args.steps / args.decode_len, 4),
@@ -163,7 +165,9 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": args.prompt_len * 4, "d2h_bytes_per_step": (args.decode_len + 1) * 4,
                 "wall_ms_per_step": round(e2e_wall_ms / args.steps, 3)},
         "gpu_launches": int(launches), "wall_ms": round(wall_ms, 1), "comm_status": status,
-        "weight_bytes_per_rank": eng.weight_bytes, "prefill_bf16_shadow_bytes_per_rank": eng.prefill_shadow_bytes, "last_tokens": toks[-4:],
+        "weight_bytes_per_rank": eng.weight_bytes, "prefill_bf16_shadow_bytes_per_rank": eng.prefill_shadow_bytes,
+        "decode_kernel": "persistent (2 launches per token)" if eng.persistent_decode else "one launch per projection",
+        "first_tokens": toks[:16], "last_tokens": toks[-4:],
     }
     eng.close()
     if world > 1:

@@ -48,6 +48,8 @@ PK_EAPI const char* pk_engine_last_error() { return g_err.c_str(); }
 // "benchmark_27b" for the 64-layer benchmark shape.
 PK_EAPI void* pk_qwen_create_ex(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
                                 int prefill_chunk, int use_cuda_graph, int decode_splits, int mtp);
+PK_EAPI void* pk_qwen_create_ex2(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
+                                 int prefill_chunk, int use_cuda_graph, int decode_splits, int mtp, int kv_fp8);
 
 PK_EAPI void* pk_qwen_create(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
                              int prefill_chunk, int use_cuda_graph, int decode_splits) {
@@ -57,6 +59,12 @@ PK_EAPI void* pk_qwen_create(const char* config_json, int tp_rank, int tp_world,
 // mtp != 0 also builds the multi-token predictor (`mtp.*` tensors) used by pk_qwen_spec_decode.
 PK_EAPI void* pk_qwen_create_ex(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
                                 int prefill_chunk, int use_cuda_graph, int decode_splits, int mtp) {
+  return pk_qwen_create_ex2(config_json, tp_rank, tp_world, device, max_context, prefill_chunk, use_cuda_graph, decode_splits, mtp, 0);
+}
+
+// kv_fp8 != 0: FP8 KV cache (E4M3 codes, one scale per 64 channels) instead of bf16.
+PK_EAPI void* pk_qwen_create_ex2(const char* config_json, int tp_rank, int tp_world, int device, int max_context,
+                                 int prefill_chunk, int use_cuda_graph, int decode_splits, int mtp, int kv_fp8) {
   pk::QwenEngine* eng = nullptr;
   guarded([&] {
     pk::QwenConfig cfg = std::string(config_json) == "benchmark_27b"
@@ -73,6 +81,7 @@ PK_EAPI void* pk_qwen_create_ex(const char* config_json, int tp_rank, int tp_wor
     else opt.decode_splits = std::min(64, std::max(8, max_context / 2048));
     opt.use_cuda_graph = use_cuda_graph != 0;
     opt.mtp = mtp != 0;
+    opt.kv_fp8 = kv_fp8 != 0;
     eng = new pk::QwenEngine(cfg, opt);
   });
   return eng;
@@ -206,6 +215,7 @@ PK_EAPI unsigned pk_qwen_comm_status(void* h) {
   guarded([&] { s = ((pk::QwenEngine*)h)->comm_status(); });
   return s;
 }
+PK_EAPI unsigned long long pk_qwen_kv_cache_bytes(void* h) { return ((pk::QwenEngine*)h)->kv_cache_bytes(); }
 PK_EAPI unsigned long long pk_qwen_weight_bytes(void* h) { return ((pk::QwenEngine*)h)->weight_bytes(); }
 // bytes of the bf16 copies kept for the prefill GEMM (0 when they are off)
 PK_EAPI unsigned long long pk_qwen_shadow_bytes(void* h) { return ((pk::QwenEngine*)h)->shadow_bytes(); }

@@ -492,6 +492,7 @@ int run(const Args& a) {
   opt.attention_window = a.window;
   opt.attention_sink = a.sink;
   opt.mtp = a.mtp;
+  opt.kv_fp8 = a.kv_cache_dtype == "fp8";
   opt.prefix_cache = a.prefix_cache;
   opt.snapshot_interval = a.snapshot_interval;
   opt.max_snapshots = a.max_snapshots;

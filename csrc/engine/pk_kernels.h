@@ -42,6 +42,13 @@ int pk_gqa_decode(const void* q, const void* kcache, const void* vcache, const i
                   int Hkv, int head_dim, int ctx_cap, float scale, int nsplit, int window, int sink, float* ws,
                   const void* gate_proj, int ld, void* out, cudaStream_t stream);
 
+int pk_qk_norm_rope_append_kv(const void* proj, int ld, int M, int Hq, int Hkv, int head_dim, const int* pos,
+                              const float* q_gamma, const float* k_gamma, float eps, int rotary_dim, float theta,
+                              void* q_out, void* kcache, void* vcache, float* kscale, float* vscale, int ctx_cap, cudaStream_t stream);
+int pk_gqa_decode_kv(const void* q, const void* kcache, const void* vcache, const float* kscale, const float* vscale, const int* pos,
+                     int M, int Hq, int Hkv, int head_dim, int ctx_cap, float scale, int nsplit, int window, int sink, float* ws,
+                     const void* gate_proj, int ld, void* out, cudaStream_t stream);
+
 int pk_embedding(const int* tokens, int M, const void* table, int dim, int vocab_start, int vocab_rows,
                  void* out_bf16, float* out_f32, cudaStream_t stream);
 

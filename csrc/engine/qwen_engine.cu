@@ -201,9 +201,16 @@ void QwenEngine::alloc_layer(QwenLayer& L, bool full) {
       alloc_fp8(L.o_proj, hidden_, hq_l_ * kHeadDim);
       L.q_norm = (float*)dalloc(kHeadDim * sizeof(float), true);
       L.k_norm = (float*)dalloc(kHeadDim * sizeof(float), true);
-      const size_t kv = (size_t)hkv_l_ * opt.max_context * kHeadDim * 2;
+      const size_t kv = (size_t)hkv_l_ * opt.max_context * kHeadDim * (opt.kv_fp8 ? 1 : 2);
       L.kcache = dalloc(kv);
       L.vcache = dalloc(kv);
+      kv_bytes_ += 2 * kv;
+      if (opt.kv_fp8) {
+        const size_t sc = (size_t)hkv_l_ * opt.max_context * 2 * sizeof(float);
+        L.kscale = (float*)dalloc(sc);
+        L.vscale = (float*)dalloc(sc);
+        kv_bytes_ += 2 * sc;
+      }
     } else {
       alloc_fp8(L.in_proj, 2 * kd_l_ + 2 * vd_l_, hidden_);
       L.in_proj_ab = dalloc((size_t)2 * vh_l_ * hidden_ * 2, true);
@@ -591,7 +598,10 @@ void QwenEngine::reset() {
 std::unique_ptr<QwenEngine::Snapshot> QwenEngine::snapshot(bool with_kv) {
   auto s = std::make_unique<Snapshot>();
   if (with_kv && pos_ > 0) {
-    const size_t row = (size_t)pos_ * kHeadDim * sizeof(uint16_t), pitch = (size_t)opt_.max_context * kHeadDim * sizeof(uint16_t);
+    // rows [0, pos) of every head: codes (1 or 2 bytes per channel) and, with the FP8 cache, the scales
+    const size_t esz = opt_.kv_fp8 ? 1 : 2;
+    const size_t row = (size_t)pos_ * kHeadDim * esz, pitch = (size_t)opt_.max_context * kHeadDim * esz;
+    const size_t srow = (size_t)pos_ * 2 * sizeof(float), spitch = (size_t)opt_.max_context * 2 * sizeof(float);
     for (auto& L : layers_) {
       if (!L.full) continue;
       for (void* cache : {L.kcache, L.vcache}) {
@@ -600,6 +610,13 @@ std::unique_ptr<QwenEngine::Snapshot> QwenEngine::snapshot(bool with_kv) {
         cuda_check(cudaMemcpy2DAsync(b, row, cache, pitch, row, (size_t)hkv_l_, cudaMemcpyDeviceToDevice, stream_), "snapshot kv");
         s->kv.push_back(b);
       }
+      if (opt_.kv_fp8)
+        for (float* sc : {L.kscale, L.vscale}) {
+          void* b = nullptr;
+          cuda_check(cudaMalloc(&b, srow * hkv_l_), "snapshot kv alloc");
+          cuda_check(cudaMemcpy2DAsync(b, srow, sc, spitch, srow, (size_t)hkv_l_, cudaMemcpyDeviceToDevice, stream_), "snapshot kv");
+          s->kv.push_back(b);
+        }
     }
   }
   for (auto& L : layers_) {
@@ -640,12 +657,17 @@ void QwenEngine::restore(const Snapshot& s) {
     cuda_check(cudaMemcpyAsync(L.conv_state, s.bufs[i++], cb, cudaMemcpyDeviceToDevice, stream_), "restore");
   }
   if (!s.kv.empty()) {
-    const size_t row = (size_t)s.pos * kHeadDim * sizeof(uint16_t), pitch = (size_t)opt_.max_context * kHeadDim * sizeof(uint16_t);
+    const size_t esz = opt_.kv_fp8 ? 1 : 2;
+    const size_t row = (size_t)s.pos * kHeadDim * esz, pitch = (size_t)opt_.max_context * kHeadDim * esz;
+    const size_t srow = (size_t)s.pos * 2 * sizeof(float), spitch = (size_t)opt_.max_context * 2 * sizeof(float);
     size_t k = 0;
     for (auto& L : layers_) {
       if (!L.full) continue;
       for (void* cache : {L.kcache, L.vcache})
         cuda_check(cudaMemcpy2DAsync(cache, pitch, s.kv[k++], row, row, (size_t)hkv_l_, cudaMemcpyDeviceToDevice, stream_), "restore kv");
+      if (opt_.kv_fp8)
+        for (float* sc : {L.kscale, L.vscale})
+          cuda_check(cudaMemcpy2DAsync(sc, spitch, s.kv[k++], srow, srow, (size_t)hkv_l_, cudaMemcpyDeviceToDevice, stream_), "restore kv");
     }
   }
   // decode() reads its input token from slot 0 of the device token buffer
@@ -788,13 +810,13 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
     QwenLayer& L = mtp ? mtp_layer_ : layers_[i];
     if (L.full) {
       consume(&L.qkv, nullptr, 0, L.input_norm, 0, proj_, ld_proj_, nullptr);
-      check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, posd, L.q_norm, L.k_norm, eps,
-                                   cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache,
-                                   opt_.max_context, stream_),
+      check(pk_qk_norm_rope_append_kv(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, posd, L.q_norm, L.k_norm, eps,
+                                      cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache, L.kscale, L.vscale,
+                                      opt_.max_context, stream_),
             "qk_norm_rope_append");
-      check(pk_gqa_decode(q_buf_, L.kcache, L.vcache, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
-                          1.f / sqrtf((float)kHeadDim), opt_.decode_splits, opt_.attention_window, opt_.attention_sink,
-                          attn_ws_, cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
+      check(pk_gqa_decode_kv(q_buf_, L.kcache, L.vcache, L.kscale, L.vscale, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
+                             1.f / sqrtf((float)kHeadDim), opt_.decode_splits, opt_.attention_window, opt_.attention_sink,
+                             attn_ws_, cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
             "gqa_decode");
       ++launches_;  // two kernels in that call
       produce(L.o_proj, attn_out_, 2 * i);
@@ -941,13 +963,13 @@ void QwenEngine::run_chunk(int M, bool mtp) {
     norm(L.input_norm, xn_);
     if (L.full) {
       gemm(xn_, hidden_, L.qkv, 0, proj_, nullptr, ld_proj_);
-      check(pk_qk_norm_rope_append(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, posd, L.q_norm, L.k_norm, eps,
-                                   cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache,
-                                   opt_.max_context, stream_),
+      check(pk_qk_norm_rope_append_kv(proj_, ld_proj_, M, hq_l_, hkv_l_, kHeadDim, posd, L.q_norm, L.k_norm, eps,
+                                      cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache, L.kscale, L.vscale,
+                                      opt_.max_context, stream_),
             "qk_norm_rope_append");
-      check(pk_gqa_decode(q_buf_, L.kcache, L.vcache, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
-                          1.f / sqrtf((float)kHeadDim), 1, opt_.attention_window, opt_.attention_sink, attn_ws_,
-                          cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
+      check(pk_gqa_decode_kv(q_buf_, L.kcache, L.vcache, L.kscale, L.vscale, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
+                             1.f / sqrtf((float)kHeadDim), 1, opt_.attention_window, opt_.attention_sink, attn_ws_,
+                             cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
             "gqa_prefill");
       ++launches_;
       gemm_out(attn_out_, hq_l_ * kHeadDim, L.o_proj, 2 * i);
@@ -1113,6 +1135,8 @@ void QwenEngine::build_persistent() {
       d.k_norm = L.k_norm;
       d.kcache = L.kcache;
       d.vcache = L.vcache;
+      d.kscale = L.kscale;
+      d.vscale = L.vscale;
     } else {
       d.lin[0] = lin(L.in_proj);
       d.lin[1].w = L.in_proj_ab;
@@ -1161,6 +1185,7 @@ void QwenEngine::build_persistent() {
   p.window = opt_.attention_window;
   p.sink = opt_.attention_sink;
   p.attn_gate = cfg_.attn_output_gate ? 1 : 0;
+  p.kv_fp8 = opt_.kv_fp8 ? 1 : 0;
   p.max_k = max_k;
   p.max_rows = max_rows;
   p.embed = embed_;

@@ -44,6 +44,9 @@ struct QwenEngineOptions {
   // Exact prefix reuse across sequential requests (prefill_cached): the KV cache is position indexed and stays, the
   // recurrent state continues live or rolls back to a stored copy. Copies are taken every `snapshot_interval` tokens
   // of a prefill (0: only at request boundaries), at most `max_snapshots` of them.
+  // FP8 KV cache: E4M3 codes with one fp32 scale per 64 channels (amax / 448) instead of bf16; a little over half the bytes
+  // per position (reference: --kv-cache-dtype fp8, cpp_engine/src/qwen_engine.cpp:410-438).
+  bool kv_fp8 = false;
   bool prefix_cache = true;
   int snapshot_interval = 4096;
   int max_snapshots = 82;
@@ -98,8 +101,10 @@ struct QwenLayer {
   float* q_norm = nullptr;
   float* k_norm = nullptr;
   Fp8Linear o_proj;
-  void* kcache = nullptr;      // bf16 [Hkv_l, ctx, 128]
+  void* kcache = nullptr;      // bf16 [Hkv_l, ctx, 128], or E4M3 codes [Hkv_l, ctx, 128] with the FP8 cache
   void* vcache = nullptr;
+  float* kscale = nullptr;     // FP8 cache: [Hkv_l, ctx, 2]
+  float* vscale = nullptr;
   // mlp
   Fp8Linear gate_up;
   Fp8Linear down;
@@ -185,6 +190,7 @@ class QwenEngine {
   const QwenEngineOptions& options() const { return opt_; }
   size_t weight_bytes() const { return weight_bytes_; }
   size_t shadow_bytes() const { return shadow_bytes_; }
+  size_t kv_cache_bytes() const { return kv_bytes_; }   // K and V of every full-attention layer, scales included
   // true once a decode step has been planned on the persistent kernel
   bool persistent_decode_active() const { return persistent_built_ && persistent_ok_; }
   // -1 automatic, 0 one launch per projection, 1 persistent kernel required; takes effect at the next decode.
@@ -251,6 +257,7 @@ class QwenEngine {
   size_t weight_bytes_ = 0;
   size_t alloc_bytes_ = 0;   // everything obtained through dalloc
   size_t shadow_bytes_ = 0;
+  size_t kv_bytes_ = 0;
   std::vector<void*> allocs_;
 
   // activations

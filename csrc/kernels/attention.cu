@@ -25,9 +25,14 @@ struct QkParams {
   int rotary_dim;
   float theta;
   bf16* q_out;        // [M, Hq, D]
-  bf16* kcache;       // [Hkv, ctx_cap, D]
+  bf16* kcache;       // [Hkv, ctx_cap, D] bf16, or E4M3 codes (one byte per channel) when kv_fp8
   bf16* vcache;
   int ctx_cap;
+  // FP8 KV cache (reference: cpp_engine/cuda/qwen_half_ops.cu:1010-1055, append_kv_fp8_kernel): every row of a head is
+  // stored as E4M3 codes with one fp32 scale per 64 channels, scale = amax / 448 (1 when the group is all zero).
+  int kv_fp8;
+  float* kscale;      // [Hkv, ctx_cap, D / 64]
+  float* vscale;
 };
 
 __global__ void __launch_bounds__(kD) qk_norm_rope_append_kernel(const QkParams p) {
@@ -59,6 +64,29 @@ __global__ void __launch_bounds__(kD) qk_norm_rope_append_kernel(const QkParams 
   }
   if (is_q) {
     p.q_out[((size_t)m * p.Hq + hh) * kD + d] = __float2bfloat16(y);
+  } else if (p.kv_fp8) {
+    // block-uniform branch (k heads): quantise the bf16-rounded key and the value per 64 channels
+    const float kvv = __bfloat162float(__float2bfloat16(y));
+    const float vv = __bfloat162float(row[p.Hq * 2 * kD + p.Hkv * kD + hk * kD + d]);
+    const float ka = warp_max(fabsf(kvv)), va = warp_max(fabsf(vv));
+    __syncthreads();   // `red` was used by the norm
+    if ((d & 31) == 0) {
+      red[d >> 5] = ka;
+      red[4 + (d >> 5)] = va;
+    }
+    __syncthreads();
+    const int half = d >> 6;
+    const float kmax = fmaxf(red[2 * half], red[2 * half + 1]), vmax = fmaxf(red[4 + 2 * half], red[4 + 2 * half + 1]);
+    const float ks = kmax > 0.f ? kmax / 448.f : 1.f, vs = vmax > 0.f ? vmax / 448.f : 1.f;
+    if (pos >= 0 && pos < p.ctx_cap) {
+      const size_t ri = (size_t)hk * p.ctx_cap + pos;
+      reinterpret_cast<uint8_t*>(p.kcache)[ri * kD + d] = float_to_e4m3(kvv / ks);
+      reinterpret_cast<uint8_t*>(p.vcache)[ri * kD + d] = float_to_e4m3(vv / vs);
+      if ((d & 63) == 0) {
+        p.kscale[ri * 2 + half] = ks;
+        p.vscale[ri * 2 + half] = vs;
+      }
+    }
   } else if (pos >= 0 && pos < p.ctx_cap) {
     const size_t ci = ((size_t)hk * p.ctx_cap + pos) * kD + d;
     p.kcache[ci] = __float2bfloat16(y);
@@ -77,7 +105,36 @@ struct DecodeParams {
   int window;          // 0 = full; else keys in (pos-window, pos] plus the first `sink` keys
   int sink;
   float* ws;           // [M, Hq, nsplit, D + 2]
+  int kv_fp8;          // caches hold E4M3 codes with one fp32 scale per 64 channels
+  const float* kscale; // [Hkv, ctx_cap, 2]
+  const float* vscale;
 };
+
+// Eight consecutive channels of one cached row as floats. bf16: one 16-byte load; fp8: one 8-byte load and the scale of
+// the 64-channel group the lane's channels belong to.
+__device__ __forceinline__ void load_kv8(const void* base, const float* scale, size_t row, int l16, bool fp8, float (&f)[8]) {
+  if (!fp8) {
+    const uint4 r = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(base) + row * kD + l16 * 8);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      f[2 * j] = __uint_as_float(w[j] << 16);
+      f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  } else {
+    const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(base) + row * kD + l16 * 8);
+    const float sc = scale[row * 2 + (l16 >> 3)];
+    const uint32_t w[2] = {r.x, r.y};
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float2 a = e4m3x2_to_float2((uint16_t)(w[j] & 0xffffu)), b = e4m3x2_to_float2((uint16_t)(w[j] >> 16));
+      f[4 * j] = a.x * sc;
+      f[4 * j + 1] = a.y * sc;
+      f[4 * j + 2] = b.x * sc;
+      f[4 * j + 3] = b.y * sc;
+    }
+  }
+}
 
 template <int G>
 __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const DecodeParams p) {
@@ -112,27 +169,17 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const DecodeParam
     for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
   }
 
-  const bf16* kbase = p.kcache + (size_t)hk * p.ctx_cap * kD;
-  const bf16* vbase = p.vcache + (size_t)hk * p.ctx_cap * kD;
+  const size_t head_row0 = (size_t)hk * p.ctx_cap;
+  const bool fp8 = p.kv_fp8 != 0;
   for (int t0 = start + warp * 2; t0 < end; t0 += 8) {
     const int t = t0 + khalf;
     const bool valid = t < end && (p.window == 0 || t >= win_lo || t < p.sink);
-    uint4 kr = make_uint4(0, 0, 0, 0), vr = kr;
-    if (valid) {
-      kr = *reinterpret_cast<const uint4*>(kbase + (size_t)t * kD + l16 * 8);
-      vr = *reinterpret_cast<const uint4*>(vbase + (size_t)t * kD + l16 * 8);
-    }
     float kf[8], vf[8];
-    {
-      const uint32_t w[4] = {kr.x, kr.y, kr.z, kr.w};
-      const uint32_t u[4] = {vr.x, vr.y, vr.z, vr.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        kf[2 * j] = __uint_as_float(w[j] << 16);
-        kf[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-        vf[2 * j] = __uint_as_float(u[j] << 16);
-        vf[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
-      }
+    for (int j = 0; j < 8; ++j) kf[j] = vf[j] = 0.f;
+    if (valid) {
+      load_kv8(p.kcache, p.kscale, head_row0 + t, l16, fp8, kf);
+      load_kv8(p.vcache, p.vscale, head_row0 + t, l16, fp8, vf);
     }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -304,28 +351,50 @@ PK_API int pk_full_qk_norm_rope_append(const void* q, int ldq, const void* k, in
 namespace {
 }  // namespace
 
-PK_API int pk_qk_norm_rope_append(const void* proj, int ld, int M, int Hq, int Hkv, int head_dim,
-                                  const int* pos, const float* q_gamma, const float* k_gamma, float eps,
-                                  int rotary_dim, float theta, void* q_out, void* kcache, void* vcache,
-                                  int ctx_cap, cudaStream_t stream) {
+// kscale / vscale non-null: FP8 KV cache (kcache / vcache hold one E4M3 code per channel, the scales one fp32 per 64
+// channels: [Hkv, ctx_cap, 2]); null: bf16 caches.
+PK_API int pk_qk_norm_rope_append_kv(const void* proj, int ld, int M, int Hq, int Hkv, int head_dim,
+                                     const int* pos, const float* q_gamma, const float* k_gamma, float eps,
+                                     int rotary_dim, float theta, void* q_out, void* kcache, void* vcache, float* kscale,
+                                     float* vscale, int ctx_cap, cudaStream_t stream) {
   if (head_dim != kD) return PK_ERR_UNSUPPORTED;
-  if (M < 1 || rotary_dim < 0 || rotary_dim > kD || (rotary_dim & 1)) return PK_ERR_BAD_ARG;
+  if (M < 1 || rotary_dim < 0 || rotary_dim > kD || (rotary_dim & 1) || (kscale == nullptr) != (vscale == nullptr)) return PK_ERR_BAD_ARG;
   QkParams p{(const pk::bf16*)proj, ld, M, Hq, Hkv, pos, q_gamma, k_gamma, eps, rotary_dim, theta,
-             (pk::bf16*)q_out, (pk::bf16*)kcache, (pk::bf16*)vcache, ctx_cap};
+             (pk::bf16*)q_out, (pk::bf16*)kcache, (pk::bf16*)vcache, ctx_cap, kscale != nullptr ? 1 : 0, kscale, vscale};
   PK_LAUNCH_PDL(qk_norm_rope_append_kernel, dim3(M, Hq + Hkv), dim3(kD), 0, stream, p);
   return PK_OK;
 }
 
-// ws must hold M * Hq * nsplit * (head_dim + 2) floats.
+PK_API int pk_qk_norm_rope_append(const void* proj, int ld, int M, int Hq, int Hkv, int head_dim,
+                                  const int* pos, const float* q_gamma, const float* k_gamma, float eps,
+                                  int rotary_dim, float theta, void* q_out, void* kcache, void* vcache,
+                                  int ctx_cap, cudaStream_t stream) {
+  return pk_qk_norm_rope_append_kv(proj, ld, M, Hq, Hkv, head_dim, pos, q_gamma, k_gamma, eps, rotary_dim, theta, q_out, kcache, vcache,
+                                   nullptr, nullptr, ctx_cap, stream);
+}
+
+PK_API int pk_gqa_decode_kv(const void* q, const void* kcache, const void* vcache, const float* kscale, const float* vscale,
+                            const int* pos, int M, int Hq, int Hkv, int head_dim, int ctx_cap, float scale, int nsplit,
+                            int window, int sink, float* ws, const void* gate_proj, int ld, void* out, cudaStream_t stream);
+
 PK_API int pk_gqa_decode(const void* q, const void* kcache, const void* vcache, const int* pos, int M,
                          int Hq, int Hkv, int head_dim, int ctx_cap, float scale, int nsplit, int window,
                          int sink, float* ws, const void* gate_proj, int ld, void* out,
                          cudaStream_t stream) {
+  return pk_gqa_decode_kv(q, kcache, vcache, nullptr, nullptr, pos, M, Hq, Hkv, head_dim, ctx_cap, scale, nsplit, window, sink, ws,
+                          gate_proj, ld, out, stream);
+}
+
+// ws must hold M * Hq * nsplit * (head_dim + 2) floats. kscale / vscale non-null: FP8 KV cache (see the append).
+PK_API int pk_gqa_decode_kv(const void* q, const void* kcache, const void* vcache, const float* kscale, const float* vscale,
+                            const int* pos, int M, int Hq, int Hkv, int head_dim, int ctx_cap, float scale, int nsplit,
+                            int window, int sink, float* ws, const void* gate_proj, int ld, void* out, cudaStream_t stream) {
   if (head_dim != kD) return PK_ERR_UNSUPPORTED;
   if (M < 1 || nsplit < 1 || Hkv < 1 || Hq < Hkv || ctx_cap < 1) return PK_ERR_BAD_ARG;   // before any division by Hkv
   if (Hq % Hkv != 0) return PK_ERR_BAD_ARG;
+  if ((kscale == nullptr) != (vscale == nullptr)) return PK_ERR_BAD_ARG;
   DecodeParams p{(const pk::bf16*)q, (const pk::bf16*)kcache, (const pk::bf16*)vcache, pos, M, Hq, Hkv,
-                 ctx_cap, scale, nsplit, window, sink, ws};
+                 ctx_cap, scale, nsplit, window, sink, ws, kscale != nullptr ? 1 : 0, kscale, vscale};
   const dim3 grid(Hkv, nsplit, M);
   switch (Hq / Hkv) {
     case 1: PK_LAUNCH_PDL(gqa_decode_split_kernel<1>, grid, dim3(128), 0, stream, p); break;

@@ -808,6 +808,8 @@ struct AttnArgs {
   float* attn_ws;
   const float* rope_cs;   // [rotary_dim / 2] cos / sin of pos * inv_freq (shared memory, built once per token)
   const float* rope_sn;
+  float* kscale;          // FP8 KV cache: one fp32 scale per 64 channels [Hkv, ctx_cap, 2]; null = bf16 caches
+  float* vscale;
   int hq_l, hkv_l, ctx_cap, window, sink, rotary_dim;
   float eps;
 };
@@ -879,10 +881,37 @@ __device__ __noinline__ void attn_split_phase(const AttnArgs p, int pos, int S, 
       }
     }
     s_vn[t] = vnew;
-    if (split == 0 && pos >= 0 && pos < p.ctx_cap) {
-      const size_t ci = ((size_t)hk * p.ctx_cap + pos) * kD + t;
-      p.kcache[ci] = __float2bfloat16(s_kn[t]);
-      p.vcache[ci] = __float2bfloat16(vnew);
+    if (p.kscale == nullptr) {
+      if (split == 0 && pos >= 0 && pos < p.ctx_cap) {
+        const size_t ci = ((size_t)hk * p.ctx_cap + pos) * kD + t;
+        p.kcache[ci] = __float2bfloat16(s_kn[t]);
+        p.vcache[ci] = __float2bfloat16(vnew);
+      }
+    } else if (split == 0) {
+      // FP8 cache: E4M3 codes with one scale per 64 channels (amax / 448); the step attends to the stored values
+      const float kvv = s_kn[t];
+      const float ka = warp_max(fabsf(kvv)), va = warp_max(fabsf(vnew));
+      group_bar(grp);   // the norm sums in `red` have been read by every thread
+      if (lane == 0) {
+        red[wg] = ka;
+        red[4 + wg] = va;
+      }
+      group_bar(grp);
+      const int half = t >> 6;
+      const float kmax = fmaxf(red[2 * half], red[2 * half + 1]), vmax = fmaxf(red[4 + 2 * half], red[4 + 2 * half + 1]);
+      const float ks = kmax > 0.f ? kmax / 448.f : 1.f, vs = vmax > 0.f ? vmax / 448.f : 1.f;
+      const uint8_t kc = float_to_e4m3(kvv / ks), vc = float_to_e4m3(vnew / vs);
+      s_kn[t] = e4m3_to_float(kc) * ks;
+      s_vn[t] = e4m3_to_float(vc) * vs;
+      if (pos >= 0 && pos < p.ctx_cap) {
+        const size_t ri = (size_t)hk * p.ctx_cap + pos;
+        reinterpret_cast<uint8_t*>(p.kcache)[ri * kD + t] = kc;
+        reinterpret_cast<uint8_t*>(p.vcache)[ri * kD + t] = vc;
+        if ((t & 63) == 0) {
+          p.kscale[ri * 2 + half] = ks;
+          p.vscale[ri * 2 + half] = vs;
+        }
+      }
     }
     group_bar(grp);
 
@@ -920,6 +949,7 @@ __device__ __noinline__ void attn_split_phase(const AttnArgs p, int pos, int S, 
     // cached keys: a warp takes keys t0 + khalf, two such pairs per iteration so that four 16-byte loads are in flight
     for (int t0 = start + wg * 2; t0 < end; t0 += 16) {
       uint4 kr[2], vr[2];
+      float ksc[2] = {1.f, 1.f}, vsc[2] = {1.f, 1.f};
       bool valid[2];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
@@ -927,16 +957,38 @@ __device__ __noinline__ void attn_split_phase(const AttnArgs p, int pos, int S, 
         valid[u] = tt < end && (p.window == 0 || tt >= win_lo || tt < p.sink);
         kr[u] = vr[u] = make_uint4(0, 0, 0, 0);
         if (valid[u]) {
-          kr[u] = __ldcg(reinterpret_cast<const uint4*>(kbase + (size_t)tt * kD + l16 * 8));
-          vr[u] = __ldcg(reinterpret_cast<const uint4*>(vbase + (size_t)tt * kD + l16 * 8));
+          if (p.kscale == nullptr) {
+            kr[u] = __ldcg(reinterpret_cast<const uint4*>(kbase + (size_t)tt * kD + l16 * 8));
+            vr[u] = __ldcg(reinterpret_cast<const uint4*>(vbase + (size_t)tt * kD + l16 * 8));
+          } else {
+            // one byte per channel: 8 bytes per lane, and the scale of the lane's 64-channel group
+            const size_t ri = (size_t)hk * p.ctx_cap + tt;
+            const uint2 k8 = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.kcache) + ri * kD + l16 * 8));
+            const uint2 v8 = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.vcache) + ri * kD + l16 * 8));
+            kr[u] = make_uint4(k8.x, k8.y, 0, 0);
+            vr[u] = make_uint4(v8.x, v8.y, 0, 0);
+            ksc[u] = __ldcg(p.kscale + ri * 2 + (l16 >> 3));
+            vsc[u] = __ldcg(p.vscale + ri * 2 + (l16 >> 3));
+          }
         }
       }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         if (t0 + u * 8 >= end) break;   // warp-uniform
         float kf[8], vf[8];
-        unpack8(kr[u], kf);
-        unpack8(vr[u], vf);
+        if (p.kscale == nullptr) {
+          unpack8(kr[u], kf);
+          unpack8(vr[u], vf);
+        } else {
+          const uint32_t kw[2] = {kr[u].x, kr[u].y}, vw[2] = {vr[u].x, vr[u].y};
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const float2 a = e4m3x2_to_float2((uint16_t)(kw[j] & 0xffffu)), b = e4m3x2_to_float2((uint16_t)(kw[j] >> 16));
+            const float2 c2 = e4m3x2_to_float2((uint16_t)(vw[j] & 0xffffu)), d2 = e4m3x2_to_float2((uint16_t)(vw[j] >> 16));
+            kf[4 * j] = a.x * ksc[u]; kf[4 * j + 1] = a.y * ksc[u]; kf[4 * j + 2] = b.x * ksc[u]; kf[4 * j + 3] = b.y * ksc[u];
+            vf[4 * j] = c2.x * vsc[u]; vf[4 * j + 1] = c2.y * vsc[u]; vf[4 * j + 2] = d2.x * vsc[u]; vf[4 * j + 3] = d2.y * vsc[u];
+          }
+        }
         step(kf, vf, valid[u]);
       }
     }
@@ -1126,7 +1178,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_persistent_kernel(const Pk
         mark(p, c, 5);
       } else if (pre == 2) {
         const AttnArgs aa{(const bf16*)p.proj, L.q_norm, L.k_norm, (bf16*)L.kcache, (bf16*)L.vcache, p.attn_ws,
-                          sh.rope_cs, sh.rope_sn, p.hq_l, p.hkv_l, p.ctx_cap, p.window, p.sink, p.rotary_dim, p.eps};
+                          sh.rope_cs, sh.rope_sn, p.kv_fp8 ? L.kscale : nullptr, p.kv_fp8 ? L.vscale : nullptr, p.hq_l, p.hkv_l,
+                          p.ctx_cap, p.window, p.sink, p.rotary_dim, p.eps};
         attn_split_phase<G>(aa, pos, S, gsm, plan.group_floats);
         mark(p, c, 6);
       } else if (pre == 3) {

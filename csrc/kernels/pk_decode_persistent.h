@@ -50,8 +50,10 @@ struct PkDecLayer {
   // full attention
   const float* q_norm;
   const float* k_norm;
-  void* kcache;           // bf16 [Hkv, ctx_cap, 128]
+  void* kcache;           // bf16 [Hkv, ctx_cap, 128], or E4M3 codes (one byte per channel) with kv_fp8
   void* vcache;
+  float* kscale;          // kv_fp8: fp32 [Hkv, ctx_cap, 2], one scale per 64 channels (amax / 448)
+  float* vscale;
 };
 
 struct PkDecParams {
@@ -67,6 +69,7 @@ struct PkDecParams {
   int max_splits;             // attention context splits the workspace allows
   int window, sink;
   int attn_gate;              // 1: sigmoid gate from the q projection
+  int kv_fp8;                 // 1: FP8 KV cache
   int max_k;                  // largest K of any segment (sizes the staged activation row)
   int max_rows;               // largest row count of any segment (sizes the per-block accumulators)
   const void* embed;          // bf16 [vocab, hidden]

@@ -377,13 +377,17 @@ class QwenEngine:
 
     def __init__(self, cfg: QwenHybridConfig | str, *, tp_rank: int = 0, tp_world: int = 1, device: int = 0,
                  max_context: int = 4096, prefill_chunk: int = 512, use_cuda_graph: bool = True, decode_splits: int = 0,
-                 mtp: bool = False, persistent_decode: int | None = None):
+                 mtp: bool = False, persistent_decode: int | None = None, kv_cache_dtype: str = "bf16"):
         """`persistent_decode`: 1 runs every single-row decode step as one persistent kernel, 0 as one launch per
         projection (the kernels that also serve verify rows, so speculative loops that compare tokens of the two must use
-        0), None lets the engine choose."""
+        0), None lets the engine choose. `kv_cache_dtype`: "bf16", or "fp8" (E4M3 codes with one scale per 64 channels: a little
+        over half the bytes per cached position)."""
+        if kv_cache_dtype not in ("bf16", "fp8"):
+            raise ValueError("kv_cache_dtype must be 'bf16' or 'fp8'")
         self._L = _lib.engine()
         L = self._L
-        L.pk_qwen_create_ex.restype = ctypes.c_void_p
+        L.pk_qwen_create_ex2.restype = ctypes.c_void_p
+        L.pk_qwen_kv_cache_bytes.restype = ctypes.c_ulonglong
         L.pk_engine_last_error.restype = ctypes.c_char_p
         L.pk_qwen_comm_arena.restype = ctypes.c_void_p
         L.pk_qwen_weight_bytes.restype = ctypes.c_ulonglong
@@ -395,8 +399,9 @@ class QwenEngine:
         text = cfg if isinstance(cfg, str) else cfg.to_json()
         self.tp_rank, self.tp_world, self.device = tp_rank, tp_world, device
         self.mtp = bool(mtp)
-        self._h = L.pk_qwen_create_ex(text.encode(), tp_rank, tp_world, device, max_context, prefill_chunk,
-                                      int(use_cuda_graph), decode_splits, int(self.mtp))
+        self.kv_cache_dtype = kv_cache_dtype
+        self._h = L.pk_qwen_create_ex2(text.encode(), tp_rank, tp_world, device, max_context, prefill_chunk,
+                                       int(use_cuda_graph), decode_splits, int(self.mtp), int(kv_cache_dtype == "fp8"))
         if not self._h:
             raise EngineError(L.pk_engine_last_error().decode())
         self._h = ctypes.c_void_p(self._h)
@@ -559,6 +564,11 @@ class QwenEngine:
     @property
     def weight_bytes(self) -> int:
         return int(self._L.pk_qwen_weight_bytes(self._h))
+
+    @property
+    def kv_cache_bytes(self) -> int:
+        """Bytes of the K and V caches of every full-attention layer on this rank (scales included)."""
+        return int(self._L.pk_qwen_kv_cache_bytes(self._h))
 
     @property
     def prefill_shadow_bytes(self) -> int:

@@ -138,29 +138,32 @@ def deltanet_chunked(proj: torch.Tensor, key_heads: int, value_heads: int, conv_
 
 def qk_norm_rope_append(proj: torch.Tensor, Hq: int, Hkv: int, pos: torch.Tensor, q_gamma: torch.Tensor,
                         k_gamma: torch.Tensor, eps: float, rotary_dim: int, theta: float, kcache: torch.Tensor,
-                        vcache: torch.Tensor) -> torch.Tensor:
+                        vcache: torch.Tensor, kscale: torch.Tensor | None = None, vscale: torch.Tensor | None = None) -> torch.Tensor:
+    """`kscale` / `vscale` (fp32 [Hkv, ctx, 2]) select the FP8 KV cache: `kcache` / `vcache` are then uint8 E4M3 codes
+    [Hkv, ctx, 128] with one scale per 64 channels (amax / 448)."""
     M, ld = proj.shape
     q = torch.empty(M, Hq, 128, device=proj.device, dtype=torch.bfloat16)
-    st = _lib.kernels().pk_qk_norm_rope_append(
+    st = _lib.kernels().pk_qk_norm_rope_append_kv(
         _ptr(proj), c_int(ld), c_int(M), c_int(Hq), c_int(Hkv), c_int(128), _ptr(pos), _ptr(q_gamma), _ptr(k_gamma),
-        c_float(eps), c_int(rotary_dim), c_float(theta), _ptr(q), _ptr(kcache), _ptr(vcache), c_int(kcache.shape[1]),
-        _stream())
-    _check(st, "pk_qk_norm_rope_append")
+        c_float(eps), c_int(rotary_dim), c_float(theta), _ptr(q), _ptr(kcache), _ptr(vcache), _ptr(kscale), _ptr(vscale),
+        c_int(kcache.shape[1]), _stream())
+    _check(st, "pk_qk_norm_rope_append_kv")
     return q
 
 
 def gqa_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor, *, nsplit: int = 4,
-               gate_proj: torch.Tensor | None = None, window: int = 0, sink: int = 0) -> torch.Tensor:
+               gate_proj: torch.Tensor | None = None, window: int = 0, sink: int = 0, kscale: torch.Tensor | None = None,
+               vscale: torch.Tensor | None = None) -> torch.Tensor:
     M, Hq, D = q.shape
     Hkv, cap, _ = kcache.shape
     ws = torch.empty(M * Hq * nsplit * (D + 2), device=q.device, dtype=torch.float32)
     out = torch.empty(M, Hq * D, device=q.device, dtype=torch.bfloat16)
     ld = 0 if gate_proj is None else gate_proj.stride(0)
-    st = _lib.kernels().pk_gqa_decode(
-        _ptr(q), _ptr(kcache), _ptr(vcache), _ptr(pos), c_int(M), c_int(Hq), c_int(Hkv), c_int(D), c_int(cap),
+    st = _lib.kernels().pk_gqa_decode_kv(
+        _ptr(q), _ptr(kcache), _ptr(vcache), _ptr(kscale), _ptr(vscale), _ptr(pos), c_int(M), c_int(Hq), c_int(Hkv), c_int(D), c_int(cap),
         c_float(D ** -0.5), c_int(nsplit), c_int(window), c_int(sink), _ptr(ws), _ptr(gate_proj), c_int(ld), _ptr(out),
         _stream())
-    _check(st, "pk_gqa_decode")
+    _check(st, "pk_gqa_decode_kv")
     return out
 
 

@@ -59,6 +59,30 @@ class GGUFBackend:
             yield tok
 
 
+class DSV4Backend:
+    """DeepSeek-V4 runtime (`models.deepseek_v4_runtime.DSV4Runtime`): prefill, then one row per step; sampled requests
+    take the logits of each step through the host sampler."""
+
+    def __init__(self, runtime):
+        self.rt = runtime
+
+    def generate(self, prompt_ids: Sequence[int], p: SamplingParams) -> Iterator[int]:
+        rt = self.rt
+        rt.reset()
+        greedy = p.temperature <= 0 and p.repetition_penalty == 1.0 and p.frequency_penalty == 0 and p.presence_penalty == 0
+        gen = torch.Generator().manual_seed(p.seed) if p.seed is not None else None
+        logits = rt.forward_logits(list(prompt_ids))[-1]
+        produced: list[int] = []
+        while True:
+            tok = int(torch.argmax(logits)) if greedy else sample_token(apply_penalties(logits.clone(), produced, p), p, gen)
+            rt.combine.check_step("cuda")
+            produced.append(tok)
+            yield tok
+            if len(produced) >= p.max_tokens or tok in p.stop_token_ids:
+                return
+            logits = rt.forward_logits([tok])[-1]
+
+
 class HFChatTokenizer:
     """`tokenizers.Tokenizer` + a chat renderer + a completion parser."""
 
@@ -87,12 +111,32 @@ class HFChatTokenizer:
 
 
 def build(kind: str, ckpt: str, max_context: int):
-    """(backend, tokenizer) for `--model qwen|gguf`."""
+    """(backend, tokenizer) for `--model qwen|gguf|dsv4`. Under torchrun every rank builds its shard (rank and world come
+    from the environment)."""
+    import os
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    if kind == "dsv4":
+        from tokenizers import Tokenizer
+        from ..models import deepseek_v4_loader as loader
+        from ..models.deepseek_v4_runtime import DSV4Runtime
+        cfg, weights = loader.load_checkpoint(ckpt)
+        rt = DSV4Runtime(cfg, weights, max_context=max_context, rank=rank, world=world)
+        tok = Tokenizer.from_file(str(Path(ckpt) / "tokenizer.json"))
+        eos = [i for i in (tok.token_to_id(dsv4.EOS),) if i is not None]
+
+        def render(messages, *, tools=None, thinking=False, reasoning_effort=None, response_format=None, **_):
+            return dsv4.encode_messages(messages, tools=tools, thinking_mode="thinking" if thinking else "chat",
+                                        reasoning_effort=reasoning_effort, response_format=response_format)
+        parse = lambda text, thinking: dsv4.parse_completion(("<think>" if thinking else "") + text, "thinking" if thinking else "chat")
+        return DSV4Backend(rt), HFChatTokenizer(tok, render, eos, parse)
     if kind == "qwen":
         from tokenizers import Tokenizer
         from ..models import qwen_hybrid as qh
         cfg = qh.QwenHybridConfig.from_json((Path(ckpt) / "config.json").read_text())
-        eng = qh.QwenEngine(cfg, max_context=max_context).load(ckpt)
+        eng = qh.QwenEngine(cfg, tp_rank=rank, tp_world=world, device=local, max_context=max_context).load(ckpt)
+        if world > 1:
+            from ..parallel import tp
+            tp.connect_engine(eng)
         tok = Tokenizer.from_file(str(Path(ckpt) / "tokenizer.json"))
         eos = [i for i in (tok.token_to_id("<|im_end|>"), tok.token_to_id("<|endoftext|>")) if i is not None]
 

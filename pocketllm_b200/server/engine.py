@@ -1,9 +1,10 @@
 """Serving engine: a request queue in front of one model worker thread.
 
-The model runs one request at a time (single-request latency is what the engines are built
-for); HTTP handler threads submit work and wait on a future, streaming requests receive
-their tokens through a per-request queue. Same role as the reference's
-`DeepSeekServingEngine` (src/server/engine.py: queue + one worker thread).
+HTTP handler threads submit work and read their tokens from a per-request queue. A backend that declares
+`max_batch_size > 1` and implements `generate_batch` gets compatible non-streaming requests together: the worker
+waits a short window (`batch_wait_ms`) for more requests with the same sampling parameters and runs them as one call;
+every other request runs alone. Same role as the reference's `DeepSeekServingEngine` (src/server/engine.py:
+queue + one worker thread, `_collect_batch`, `_is_batch_compatible`).
 """
 from __future__ import annotations
 
@@ -29,7 +30,8 @@ class SamplingParams:
 
 
 class TokenBackend(Protocol):
-    """What the server needs from a model: stream greedy/sampled tokens for a prompt."""
+    """What the server needs from a model: stream greedy/sampled tokens for a prompt. Optional: `max_batch_size` and
+    `generate_batch(prompts, params_list) -> list[list[int]]` for backends that run several requests in one pass."""
 
     def generate(self, prompt_ids: Sequence[int], params: SamplingParams) -> Iterator[int]: ...
 
@@ -41,24 +43,80 @@ class _Job:
     out: "queue.Queue[object]" = field(default_factory=queue.Queue)
     submitted: float = field(default_factory=time.perf_counter)
     cancelled: threading.Event = field(default_factory=threading.Event)
+    batchable: bool = False      # the caller reads the whole completion at once (not a stream)
 
 
 _DONE = object()
 
 
+def batch_compatible(a: SamplingParams, b: SamplingParams) -> bool:
+    """Requests share a batch when one sampler setting serves both (lengths and seeds may differ for greedy runs)."""
+    same = (a.temperature, a.top_p, a.top_k, a.min_p, a.frequency_penalty, a.presence_penalty, a.repetition_penalty, a.stop_token_ids) == \
+           (b.temperature, b.top_p, b.top_k, b.min_p, b.frequency_penalty, b.presence_penalty, b.repetition_penalty, b.stop_token_ids)
+    return same and (a.temperature <= 0 or a.seed == b.seed)
+
+
 class ServingEngine:
-    def __init__(self, backend: TokenBackend, max_queue: int = 64):
+    def __init__(self, backend: TokenBackend, max_queue: int = 64, batch_wait_ms: float = 2.0):
         self.backend = backend
+        self.batch_wait_ms = batch_wait_ms
+        self.max_batch = int(getattr(backend, "max_batch_size", 1)) if hasattr(backend, "generate_batch") else 1
         self._q: "queue.Queue[_Job | None]" = queue.Queue(max_queue)
+        self._held: list[_Job] = []          # taken off the queue while looking for batch partners, to run next
+        self.stats = {"requests": 0, "tokens": 0, "errors": 0, "batches": 0, "batched_requests": 0}
         self._thread = threading.Thread(target=self._loop, name="pocket-serving", daemon=True)
         self._thread.start()
-        self.stats = {"requests": 0, "tokens": 0, "errors": 0}
+
+    def _collect_batch(self, first: _Job) -> list[_Job]:
+        batch = [first]
+        deadline = time.monotonic() + self.batch_wait_ms / 1000.0
+        while len(batch) < self.max_batch:
+            left = deadline - time.monotonic()
+            try:
+                cand = self._q.get(timeout=max(left, 0.0)) if left > 0 else self._q.get_nowait()
+            except queue.Empty:
+                break
+            if cand is None:
+                self._q.put(None)            # shutdown marker: leave it for the main loop
+                break
+            if cand.batchable and batch_compatible(first.params, cand.params):
+                batch.append(cand)
+            else:
+                self._held.append(cand)      # runs right after this batch, in arrival order
+                break
+        return batch
+
+    def _run_batch(self, batch: list[_Job]) -> None:
+        try:
+            outs = self.backend.generate_batch([j.prompt_ids for j in batch], [j.params for j in batch])
+            if len(outs) != len(batch):
+                raise RuntimeError("batched backend returned a result list of the wrong length")
+            self.stats["batches"] += 1
+            self.stats["batched_requests"] += len(batch)
+            for job, toks in zip(batch, outs):
+                job.out.put(("ttft", time.perf_counter() - job.submitted))
+                for t in toks:
+                    job.out.put(int(t))
+                self.stats["tokens"] += len(toks)
+                self.stats["requests"] += 1
+        except Exception as e:
+            self.stats["errors"] += len(batch)
+            for job in batch:
+                job.out.put(e)
+        finally:
+            for job in batch:
+                job.out.put(_DONE)
 
     def _loop(self) -> None:
         while True:
-            job = self._q.get()
+            job = self._held.pop(0) if self._held else self._q.get()
             if job is None:
                 return
+            if job.batchable and self.max_batch > 1:
+                batch = self._collect_batch(job)
+                if len(batch) > 1:
+                    self._run_batch(batch)
+                    continue
             try:
                 first = True
                 for tok in self.backend.generate(job.prompt_ids, job.params):
@@ -76,9 +134,10 @@ class ServingEngine:
             finally:
                 job.out.put(_DONE)
 
-    def stream(self, prompt_ids: Sequence[int], params: SamplingParams) -> Iterator[object]:
-        """Yields ("ttft", seconds) once, then token ids; raises what the backend raised."""
-        job = _Job(list(prompt_ids), params)
+    def stream(self, prompt_ids: Sequence[int], params: SamplingParams, batchable: bool = False) -> Iterator[object]:
+        """Yields ("ttft", seconds) once, then token ids; raises what the backend raised. `batchable`: the caller does
+        not need tokens one by one, so the request may share a pass with compatible ones."""
+        job = _Job(list(prompt_ids), params, batchable=batchable)
         try:
             self._q.put(job, timeout=1.0)
         except queue.Full:

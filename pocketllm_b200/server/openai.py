@@ -137,14 +137,14 @@ class OpenAIApp:
         params.max_tokens = min(params.max_tokens, self.max_context - len(ids))
         return params, opts, ids
 
-    def _run(self, ids: list[int], params: SamplingParams, opts: dict) -> Iterator[tuple[str, Any]]:
+    def _run(self, ids: list[int], params: SamplingParams, opts: dict, batchable: bool = False) -> Iterator[tuple[str, Any]]:
         """Yields ("delta", text) pieces and finally ("done", info)."""
         dec = StreamingDecoder(self.tok, opts["stop"])
         t0 = time.perf_counter()
         ttft = None
         n_tok = 0
         finish = "length"
-        for item in self.engine.stream(ids, params):
+        for item in self.engine.stream(ids, params, batchable=batchable):
             if isinstance(item, tuple):
                 ttft = item[1]
                 continue
@@ -172,10 +172,11 @@ class OpenAIApp:
     def complete(self, body: dict) -> dict:
         params, opts, ids = self._prepare(body)
         choices, completion_tokens, timings = [], 0, None
-        with self.inflight:
+        # no lock here: whole completions may share a batch in the serving engine, which serialises everything else
+        if True:
             for i in range(opts["n"]):
                 info = None
-                for kind, val in self._run(ids, params, opts):
+                for kind, val in self._run(ids, params, opts, batchable=True):
                     if kind == "done":
                         info = val
                 msg = self.tok.parse(info["text"], opts["thinking"])
@@ -310,14 +311,30 @@ def serve(app: OpenAIApp, host: str = "127.0.0.1", port: int = 8000) -> Threadin
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="qwen", choices=["qwen", "gguf"])
+    ap.add_argument("--model", default="qwen", choices=["qwen", "gguf", "dsv4"])
     ap.add_argument("--ckpt", required=True)
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--max-context", type=int, default=4096)
     args = ap.parse_args(argv)
-    from . import backends
+    import os
+    from . import backends, distributed
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    group = None
+    if world > 1:
+        # started by torchrun: rank 0 serves HTTP and announces every request, the other ranks follow it
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        group = distributed.control_group()
     backend, tokenizer = backends.build(args.model, args.ckpt, args.max_context)
+    if world > 1 and rank != 0:
+        served = distributed.worker_loop(backend, group)
+        print(f"worker {rank}: served {served} requests", flush=True)
+        return 0
+    if world > 1:
+        backend = distributed.DistributedBackend(backend, group)
     app = OpenAIApp(ServingEngine(backend), tokenizer, model_name=args.model, max_context=args.max_context)
     httpd = serve(app, args.host, args.port)
     print(f"listening on http://{args.host}:{httpd.server_address[1]}", flush=True)
@@ -325,6 +342,8 @@ def main(argv=None) -> int:
         httpd.serve_forever()
     except KeyboardInterrupt:
         pass
+    if world > 1:
+        backend.shutdown()
     return 0
 
 

@@ -362,6 +362,57 @@ def test_gqa_append_and_decode(M, ctx, Hq, Hkv, nsplit):
         assert _rel_err(out[m].view(Hq, D), o) < 1e-2
 
 
+def test_gqa_fp8_kv_cache_append_and_decode():
+    """FP8 KV cache: E4M3 codes with one scale per 64 channels (amax / 448). The appended rows must be the quantised
+    keys / values, and attention over the cache must equal attention over its dequantised contents."""
+    from pocketllm_b200 import ops
+    torch.manual_seed(5)
+    M, ctx, Hq, Hkv, D, cap, rd, theta, nsplit = 3, 200, 8, 2, 128, 512, 32, 1e6, 4
+    ld = Hq * 2 * D + 2 * Hkv * D
+    base = ctx - 1
+
+    def quant(x):                                   # [..., 128] -> codes uint8, scales [..., 2]
+        g = x.float().view(*x.shape[:-1], 2, 64)
+        sc = g.abs().amax(-1) / 448.0
+        sc = torch.where(sc > 0, sc, torch.ones_like(sc))
+        codes = (g / sc.unsqueeze(-1)).to(torch.float8_e4m3fn)
+        return codes.view(torch.uint8).view(*x.shape), sc
+
+    def dequant(codes, sc):
+        return (codes.view(torch.float8_e4m3fn).float().view(*codes.shape[:-1], 2, 64) * sc.unsqueeze(-1)).view(*codes.shape)
+
+    kc = torch.zeros(Hkv, cap, D, device="cuda", dtype=torch.uint8)
+    vc = torch.zeros_like(kc)
+    ks = torch.ones(Hkv, cap, 2, device="cuda")
+    vs = torch.ones_like(ks)
+    kc[:, :base], ks[:, :base] = quant(torch.randn(Hkv, base, D, device="cuda").to(torch.bfloat16))
+    vc[:, :base], vs[:, :base] = quant(torch.randn(Hkv, base, D, device="cuda").to(torch.bfloat16))
+    proj = torch.randn(M, ld, device="cuda").to(torch.bfloat16)
+    pos = torch.arange(base, base + M, device="cuda", dtype=torch.int32)
+    qg, kg = torch.randn(D, device="cuda") * 0.1, torch.randn(D, device="cuda") * 0.1
+    # the same rows through the bf16 cache give the unquantised keys to compare with
+    kb = torch.zeros(Hkv, cap, D, device="cuda", dtype=torch.bfloat16)
+    vb = torch.zeros_like(kb)
+    ops.qk_norm_rope_append(proj, Hq, Hkv, pos, qg, kg, 1e-6, rd, theta, kb, vb)
+    q = ops.qk_norm_rope_append(proj, Hq, Hkv, pos, qg, kg, 1e-6, rd, theta, kc, vc, ks, vs)
+    for m in range(M):
+        p = base + m
+        wc, ws_ = quant(kb[:, p])
+        assert torch.equal(ks[:, p], ws_) and (kc[:, p].int() - wc.int()).abs().max() <= 1      # at most one code apart (division rounding)
+        wc, ws_ = quant(vb[:, p])
+        assert torch.equal(vs[:, p], ws_) and (vc[:, p].int() - wc.int()).abs().max() <= 1
+    out = ops.gqa_decode(q, kc, vc, pos, nsplit=nsplit, gate_proj=proj, kscale=ks, vscale=vs)
+    Kd, Vd = dequant(kc, ks), dequant(vc, vs)
+    for m in range(M):
+        p = base + m
+        gate = proj[m, : Hq * 2 * D].float().view(Hq, 2 * D)[:, D:]
+        K = Kd[:, : p + 1].repeat_interleave(Hq // Hkv, 0)
+        V = Vd[:, : p + 1].repeat_interleave(Hq // Hkv, 0)
+        sc = torch.einsum("hd,htd->ht", q[m].float(), K) * D ** -0.5
+        o = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), V) * torch.sigmoid(gate)
+        assert _rel_err(out[m].view(Hq, D), o) < 1e-2
+
+
 def test_full_qk_norm_rope_append_matches_torch():
     """Whole-vector RMS (one gamma per element) + half-split rotation from tables + KV append, against plain PyTorch."""
     from pocketllm_b200 import ops

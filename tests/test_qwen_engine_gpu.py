@@ -463,3 +463,27 @@ def test_native_prefix_reuse_across_requests(tiny):
     assert eng.comm_status() == 0
     fresh.close()
     eng.close()
+
+
+@pytest.mark.parametrize("persistent", [0, 1])
+def test_fp8_kv_cache_tracks_the_bf16_cache(tiny, persistent):
+    """The FP8 KV cache (E4M3 codes, one scale per 64 channels) changes the logits only slightly and takes a little over
+    half the bytes; prefill, the per-projection decode and the persistent decode kernel all read and write it."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    torch.manual_seed(21)
+    prompt = torch.randint(0, cfg.vocab_size, (90,)).tolist()
+    outs = {}
+    for dt in ("bf16", "fp8"):
+        eng = qh.QwenEngine(cfg, max_context=512, prefill_chunk=64, persistent_decode=persistent, kv_cache_dtype=dt).load(d)
+        first = eng.prefill(prompt)
+        l0 = eng.logits(0)
+        toks = [first] + eng.decode(6)
+        outs[dt] = (toks, l0, eng.logits(0), eng.kv_cache_bytes)
+        assert eng.persistent_decode == bool(persistent) and eng.comm_status() == 0
+        eng.close()
+    assert _close(outs["fp8"][1], outs["bf16"][1], 5e-2)          # after prefill
+    if outs["fp8"][0] == outs["bf16"][0]:
+        assert _close(outs["fp8"][2], outs["bf16"][2], 5e-2)      # after six decode steps on the same tokens
+    assert outs["fp8"][0][0] == outs["bf16"][0][0]
+    assert outs["fp8"][3] * 32 == outs["bf16"][3] * 17            # (128 + 2 * 4) bytes per row against 256
