@@ -201,6 +201,12 @@ PK_EAPI int pk_qwen_set_persistent_decode(void* h, int mode) {
   return guarded([&] { ((pk::QwenEngine*)h)->set_persistent_decode(mode); });
 }
 
+// mode as QwenEngineOptions::prefill_gemm; call before loading or initialising the weights
+PK_EAPI int pk_qwen_set_prefill_gemm(void* h, int mode) {
+  return guarded([&] { ((pk::QwenEngine*)h)->set_prefill_gemm(mode); });
+}
+PK_EAPI int pk_qwen_prefill_gemm_mode(void* h) { return ((pk::QwenEngine*)h)->prefill_gemm_mode(); }
+
 PK_EAPI int pk_qwen_decode_trace(void* h, unsigned long long* out, int cap) {
   int n = 0;
   guarded([&] { n = ((pk::QwenEngine*)h)->copy_decode_trace(out, cap); });

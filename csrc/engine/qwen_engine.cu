@@ -350,9 +350,34 @@ QwenEngine::~QwenEngine() {
 // weights
 
 void QwenEngine::build_prefill_shadow() {
+  if (shadow_bytes_ > 0 || act_q_ != nullptr) return;
   int mode = opt_.prefill_bf16_shadow;
   if (const char* v = getenv("POCKET_PREFILL_SHADOW")) mode = atoi(v);
-  if (mode == 0 || shadow_bytes_ > 0) return;
+  int gm = opt_.prefill_gemm;
+  if (const char* v = getenv("POCKET_PREFILL_GEMM")) {
+    const std::string s(v);
+    gm = s == "umma" ? 0 : s == "shadow" ? 1 : s == "fp8x2" ? 2 : s == "fp8" ? 3 : gm;
+  } else if (gm < 0 && getenv("POCKET_PREFILL_SHADOW") != nullptr) {
+    gm = mode != 0 ? 1 : 0;
+  }
+  if (gm < 0) gm = mode == 1 ? 1 : 2;
+  gemm_mode_ = gm;
+  if (gm == 2 || gm == 3) {
+    // the stored codes are the tensor-core operand: only the activations of the GEMM at hand are quantised, into this scratch
+    int kmax = hidden_;
+    for (int k : {inter_l_, vd_l_, hq_l_ * kHeadDim}) kmax = std::max(kmax, k);
+    kmax = (int)align_up(kmax, 128);
+    act_rows_ = (int)align_up(rows_cap_, 128);
+    const size_t qb = (size_t)2 * act_rows_ * kmax;
+    act_q_ = dalloc(qb);
+    act_scale_ = (float*)dalloc((size_t)(kmax / 128) * act_rows_ * sizeof(float));
+    cuda_check(cudaMemsetAsync(act_q_, 0, qb, stream_), "memset");
+    cuda_check(cudaMemsetAsync(act_scale_, 0, (size_t)(kmax / 128) * act_rows_ * sizeof(float), stream_), "memset");
+    cuda_check(cudaStreamSynchronize(stream_), "prefill scratch");
+    return;
+  }
+  if (gm == 0) return;
+  if (mode == 0) mode = 1;
   size_t need = 0;
   auto count = [&](const Fp8Linear& l) { need += (size_t)l.N * l.K * 2; };
   std::vector<QwenLayer*> all;
@@ -911,7 +936,19 @@ void QwenEngine::run_chunk(int M, bool mtp) {
     check(pk_embedding(tokens_dev_, M, embed_, hidden_, 0, (int)cfg_.vocab_size, hid, nullptr, stream_), "embedding");
   }
   int pending = -1;  // site whose partial sums still wait to be added to the residual stream
+  // Native FP8: quantise the rows of A (one or two E4M3 terms per value, a scale per row and 128-wide k block), then run
+  // tcgen05 kind::f8f6f4 on them and on the stored weight codes. Shapes the kernel does not take fall through.
+  auto gemm_native = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc, const PkPush* ps) -> bool {
+    if (act_q_ == nullptr || (w.K & 127) != 0 || (lda & 3) != 0 || M > act_rows_) return false;
+    if (epi == 1 && ((w.N >> 1) & 127) != 0) return false;
+    const int terms = gemm_mode_ == 3 ? 1 : 2;
+    check(pk_quant_act_fp8(A, lda, M, w.K, terms, act_q_, act_rows_, act_scale_, act_rows_, stream_), "quant_act_fp8");
+    check(pk_gemm_fp8(act_q_, terms, act_rows_, act_scale_, act_rows_, w.w, w.scale, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, ps, sm_count_,
+                      stream_), "gemm_fp8");
+    return true;
+  };
   auto gemm = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc) {
+    if (gemm_native(A, lda, w, epi, C, resid, ldc, nullptr)) return;
     if (w.wb != nullptr) {
       // persistent 128x256 kernel; shapes it does not take (SwiGLU halves not a multiple of 128) go to the 128x128 one
       int rc = pk_gemm_bf16(A, lda, w.wb, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, nullptr, sm_count_, stream_);
@@ -932,7 +969,8 @@ void QwenEngine::run_chunk(int M, bool mtp) {
       gemm(A, lda, w, 2, hid, hid, hidden_);
     } else {
       PkPush ps = make_push(site, true, rpr);
-      if (w.wb != nullptr)
+      if (gemm_native(A, lda, w, 4, nullptr, nullptr, hidden_, &ps)) {
+      } else if (w.wb != nullptr)
         check(pk_gemm_bf16(A, lda, w.wb, M, w.N, w.K, 4, nullptr, nullptr, hidden_, gemm_status_, &ps, sm_count_, stream_), "gemm_bf16(push)");
       else
         check(pk_gemm_umma(A, lda, w.w, w.scale, 0, M, w.N, w.K, 4, nullptr, nullptr, hidden_, gemm_status_, &ps, stream_), "gemm_umma(push)");

@@ -35,6 +35,14 @@ struct QwenEngineOptions {
   // -1 = when HBM has room for them (twice the FP8 bytes plus a reserve), 0 = never, 1 = always.
   // POCKET_PREFILL_SHADOW in the environment overrides.
   int prefill_bf16_shadow = -1;
+  // Which GEMM the many-row (prefill, verify) path uses on the FP8 linears:
+  //   -1  automatic: the native FP8 kernel with two-term activations, unless prefill_bf16_shadow == 1 asks for the copies
+  //    0  weights decoded to bf16 inside shared memory (128 x 128 tiles), bf16 activations
+  //    1  bf16 copies of the weights in HBM (see prefill_bf16_shadow), bf16 activations
+  //    2  native FP8 tensor-core math on the stored codes, activations as two E4M3 terms per value (bf16-like accuracy)
+  //    3  native FP8, one E4M3 term per activation (fastest; activations carry 4 significant bits)
+  // POCKET_PREFILL_GEMM = umma | shadow | fp8x2 | fp8 in the environment overrides.
+  int prefill_gemm = -1;
   // Multi-token predictor (`mtp.*` tensors: two input norms, fc, one full-attention layer, norm) for speculative decoding.
   bool mtp = false;
   // Single-row decode steps as one persistent cooperative kernel per token (weights ring that never drains, grid and
@@ -190,6 +198,12 @@ class QwenEngine {
   const QwenEngineOptions& options() const { return opt_; }
   size_t weight_bytes() const { return weight_bytes_; }
   size_t shadow_bytes() const { return shadow_bytes_; }
+  int prefill_gemm_mode() const { return gemm_mode_; }
+  // Before the weights are loaded or initialised: choose the many-row GEMM (QwenEngineOptions::prefill_gemm).
+  void set_prefill_gemm(int mode) {
+    if (shadow_bytes_ > 0 || act_q_ != nullptr) throw std::runtime_error("prefill GEMM already set up");
+    opt_.prefill_gemm = mode;
+  }   // 0 umma, 1 bf16 copies, 2 FP8 two terms, 3 FP8 one term
   size_t kv_cache_bytes() const { return kv_bytes_; }   // K and V of every full-attention layer, scales included
   // true once a decode step has been planned on the persistent kernel
   bool persistent_decode_active() const { return persistent_built_ && persistent_ok_; }
@@ -257,6 +271,10 @@ class QwenEngine {
   size_t weight_bytes_ = 0;
   size_t alloc_bytes_ = 0;   // everything obtained through dalloc
   size_t shadow_bytes_ = 0;
+  int gemm_mode_ = 0;
+  void* act_q_ = nullptr;        // [2][rows_cap_ up to 128][K max] E4M3 terms of the GEMM input being multiplied
+  float* act_scale_ = nullptr;   // [K max / 128][that row count]
+  int act_rows_ = 0;
   size_t kv_bytes_ = 0;
   std::vector<void*> allocs_;
 

@@ -240,8 +240,7 @@ class DSV4Runtime:
                 iq = b.i_wq_b(qr).view(M, ih, idim)
                 dk.head_prep(iq, pos_t, cos_t, sin_t, rd, dk.PREP_ROPE | dk.PREP_HADAMARD_FP4)
                 score = dk.index_score(iq, st.ik, A[:, off:], pos_t, 4, nmax, idim ** -0.5 * ih ** -0.5)
-                top, sel = score.topk(cfg.index_topk, dim=-1)
-                sel = torch.where(torch.isinf(top), torch.full_like(sel, -1), sel).to(torch.int32).contiguous()
+                sel = dk.topk_select(score, cfg.index_topk)      # device radix select; entries a row cannot see score -inf
                 nvalid = ((pos_t + 1) // 4).unsqueeze(1)
                 # rows that see at most index_topk entries take all of them
                 few = nvalid <= cfg.index_topk

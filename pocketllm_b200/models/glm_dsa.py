@@ -174,9 +174,16 @@ def indexer_select(qi: torch.Tensor, ki: torch.Tensor, wh: torch.Tensor, pos: to
     score = score.masked_fill(~causal, float("-inf"))
     if topk <= 0 or topk >= S:
         return causal
+    mask = torch.zeros_like(causal)
+    if score.is_cuda:
+        # device radix select: the same set as the stable sort (ties to the lower position), -1 padded
+        from ..ops import dsv4_ops as dk
+        sel = dk.topk_select(score.contiguous(), topk).long()
+        pad = torch.zeros(sel.shape[0], 1, dtype=torch.bool, device=sel.device)
+        mask = torch.cat([mask, pad], 1).scatter_(1, torch.where(sel < 0, S, sel), True)[:, :S]
+        return mask & causal
     # stable top-k: sort by (-score, position)
     order = torch.sort(-score, dim=-1, stable=True).indices[:, :topk]
-    mask = torch.zeros_like(causal)
     mask.scatter_(1, order, True)
     return mask & causal
 

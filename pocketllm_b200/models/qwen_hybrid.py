@@ -339,6 +339,10 @@ class ReferenceModel:
 # --------------------------------------------------------------------------------------
 # native engine
 
+# order = the engine's mode numbers
+PREFILL_GEMMS = ("umma", "shadow", "fp8x2", "fp8")
+
+
 class EngineError(RuntimeError):
     pass
 
@@ -377,11 +381,17 @@ class QwenEngine:
 
     def __init__(self, cfg: QwenHybridConfig | str, *, tp_rank: int = 0, tp_world: int = 1, device: int = 0,
                  max_context: int = 4096, prefill_chunk: int = 512, use_cuda_graph: bool = True, decode_splits: int = 0,
-                 mtp: bool = False, persistent_decode: int | None = None, kv_cache_dtype: str = "bf16"):
+                 mtp: bool = False, persistent_decode: int | None = None, kv_cache_dtype: str = "bf16",
+                 prefill_gemm: str | None = None):
         """`persistent_decode`: 1 runs every single-row decode step as one persistent kernel, 0 as one launch per
         projection (the kernels that also serve verify rows, so speculative loops that compare tokens of the two must use
         0), None lets the engine choose. `kv_cache_dtype`: "bf16", or "fp8" (E4M3 codes with one scale per 64 channels: a little
-        over half the bytes per cached position)."""
+        over half the bytes per cached position). `prefill_gemm`: how rows beyond eight are multiplied with the FP8 linears:
+        "fp8x2" (default: tcgen05 FP8 math on the stored codes, activations as two E4M3 terms per value), "fp8" (one term:
+        fastest, 4 significant bits per activation), "shadow" (bf16 copies of the weights in HBM) or "umma" (weights
+        decoded to bf16 in shared memory)."""
+        if prefill_gemm not in (None,) + PREFILL_GEMMS:
+            raise ValueError(f"prefill_gemm must be one of {PREFILL_GEMMS}")
         if kv_cache_dtype not in ("bf16", "fp8"):
             raise ValueError("kv_cache_dtype must be 'bf16' or 'fp8'")
         self._L = _lib.engine()
@@ -407,6 +417,8 @@ class QwenEngine:
         self._h = ctypes.c_void_p(self._h)
         if persistent_decode is not None:
             self._ck(L.pk_qwen_set_persistent_decode(self._h, int(persistent_decode)))
+        if prefill_gemm is not None:
+            self._ck(L.pk_qwen_set_prefill_gemm(self._h, PREFILL_GEMMS.index(prefill_gemm)))
 
     def _ck(self, status: int) -> None:
         if status != 0:
@@ -569,6 +581,11 @@ class QwenEngine:
     def kv_cache_bytes(self) -> int:
         """Bytes of the K and V caches of every full-attention layer on this rank (scales included)."""
         return int(self._L.pk_qwen_kv_cache_bytes(self._h))
+
+    @property
+    def prefill_gemm(self) -> str:
+        """The GEMM that multiplies more than eight rows with the FP8 linears (known once the weights are in place)."""
+        return PREFILL_GEMMS[int(self._L.pk_qwen_prefill_gemm_mode(self._h))]
 
     @property
     def prefill_shadow_bytes(self) -> int:

@@ -108,6 +108,38 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, epi: int = EPI_BF16, resid: t
     return c
 
 
+def quant_act_fp8(x: torch.Tensor, terms: int = 1) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 rows [M, K] -> (E4M3 codes uint8 [terms, m_pad, K], scales fp32 [K / 128, m_pad]); one scale (amax / 448) per
+    row and 128-wide k block. With two terms the second plane holds the codes of the rounding residue of the first, so
+    that (plane 0 + plane 1) * scale reproduces x to about 8 significant bits."""
+    M, K = x.shape
+    m_pad = (M + 127) // 128 * 128
+    q = torch.zeros(terms, m_pad, K, device=x.device, dtype=torch.uint8)
+    sc = torch.ones(K // 128, m_pad, device=x.device, dtype=torch.float32)
+    st = _lib.kernels().pk_quant_act_fp8(_ptr(x), c_int(x.stride(0)), c_int(M), c_int(K), c_int(terms), _ptr(q), c_int(m_pad), _ptr(sc),
+                                         c_int(m_pad), _stream())
+    _check(st, "pk_quant_act_fp8")
+    return q, sc
+
+
+def gemm_fp8(aq: torch.Tensor, a_scale: torch.Tensor, M: int, w: torch.Tensor, w_scale: torch.Tensor, *, epi: int = EPI_BF16,
+             resid: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """Persistent tcgen05 kind::f8f6f4 GEMM: C = A @ W^T with A from `quant_act_fp8` (one or two E4M3 terms) and W as raw
+    E4M3 codes [N, K] with fp32 scales per 128 x 128 block; every k block is scaled and added in fp32. Epilogues as in
+    `gemm_bf16`."""
+    terms, m_pad, K = aq.shape
+    N = w.shape[0]
+    ncols = N // 2 if epi == EPI_SWIGLU else N
+    c = torch.empty(M, ncols, device=aq.device, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16)
+    if status is None:
+        status = torch.zeros(1, device=aq.device, dtype=torch.int32)
+    st = _lib.kernels().pk_gemm_fp8(_ptr(aq), c_int(terms), c_int(m_pad), _ptr(a_scale), c_int(a_scale.stride(0)), _ptr(w), _ptr(w_scale),
+                                    c_int(M), c_int(N), c_int(K), c_int(epi), _ptr(c), _ptr(resid), c_int(ncols), _ptr(status), c_void_p(0),
+                                    c_int(_sm_count()), _stream())
+    _check(st, "pk_gemm_fp8")
+    return c
+
+
 def deltanet_seq(proj: torch.Tensor, key_heads: int, value_heads: int, conv_w: torch.Tensor, conv_state: torch.Tensor,
                  A_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, eps: float, state: torch.Tensor) -> torch.Tensor:
     """Gated DeltaNet over T tokens in order; updates `state` and `conv_state` in place."""

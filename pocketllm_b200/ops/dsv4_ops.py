@@ -81,6 +81,19 @@ def index_score(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, pos: torch.Te
     return score
 
 
+def topk_select(score: torch.Tensor, k: int, lengths: torch.Tensor | None = None) -> torch.Tensor:
+    """Indices (int32 [M, k], ascending index order, -1 padded) of the k largest entries of every row of fp32 `score`
+    [M, n]; `lengths` [M] limits each row to its first entries; -inf scores are never selected; among equal scores the
+    lowest indices win. A device radix select (five streaming passes) instead of a sort of the row."""
+    if score.dtype != torch.float32 or score.dim() != 2 or score.stride(1) != 1:
+        raise ValueError("topk_select takes a 2-D fp32 tensor with contiguous rows")
+    M, n = score.shape
+    out = torch.empty(M, k, device=score.device, dtype=torch.int32)
+    st = _lib.kernels().pk_topk_select(_ptr(score), _ptr(lengths), c_int(M), c_int(n), c_int(score.stride(0)), c_int(k), _ptr(out), _stream())
+    _check(st, "pk_topk_select")
+    return out
+
+
 def sparse_attn(q: torch.Tensor, kv: torch.Tensor, pos: torch.Tensor, sink: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, *,
                 win: int, ring: int, ratio: int, rd: int, sel: torch.Tensor | None = None, all_entries: bool = False,
                 rope_pos: torch.Tensor | None = None) -> torch.Tensor:

@@ -220,6 +220,80 @@ def test_gemm_bf16_many_tiles_per_cta():
     assert torch.equal(c, ops.gemm_bf16(a, w))
 
 
+def _fp8_gemm_inputs(M, N, K, seed):
+    from pocketllm_b200.formats import fp8 as f8
+    torch.manual_seed(seed)
+    a = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 2).to(torch.bfloat16)
+    a[:, ::37] *= 8                                                     # outliers that set the block scale
+    wq, ws = f8.quantize_block128(torch.randn(N, K) * 0.05, scale_dtype=torch.float32)
+    wq, ws = wq.cuda(), ws.cuda().contiguous()
+    return a, wq, ws, f8.dequantize_block128(wq, ws)
+
+
+@pytest.mark.parametrize("terms", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 512), (300, 768, 1024), (130, 256, 256), (1, 256, 128), (700, 2304, 384)])
+def test_gemm_fp8_native_tiles(M, N, K, terms):
+    """Weights stay E4M3 codes; activations are one or two E4M3 terms with a scale per row and k block. The kernel must
+    reproduce (sum of the terms * scale) @ dequantised weights to fp32 accuracy, and with two terms the bf16 product."""
+    from pocketllm_b200 import ops
+    a, wq, ws, wd = _fp8_gemm_inputs(M, N, K, M + N + K)
+    aq, asc = ops.quant_act_fp8(a, terms)
+    m_pad = aq.shape[1]
+    planes = aq.view(torch.float8_e4m3fn).float().sum(0)[:M]             # [M, K]
+    a_deq = planes * asc.t()[:M].repeat_interleave(128, 1)
+    # quantiser: scale = amax / 448 per (row, block), first term is the nearest code
+    blocks = a.float().view(M, K // 128, 128)
+    want_s = blocks.abs().amax(-1) / 448.0
+    want_s = torch.where(want_s > 0, want_s, torch.ones_like(want_s))
+    assert torch.allclose(asc.t()[:M], want_s, rtol=1e-6, atol=0)
+    assert aq[:, M:].abs().sum() == 0 and m_pad % 128 == 0
+    assert _rel_err(a_deq, a.float()) < (4e-2 if terms == 1 else 3e-3)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    c = ops.gemm_fp8(aq, asc, M, wq, ws, epi=ops.EPI_F32, status=status)
+    torch.cuda.synchronize()
+    exact = a_deq @ wd.t()
+    assert status.item() == 0 and _rel_err(c, exact) < 2e-5
+    ref = a.float() @ wd.t()
+    assert _rel_err(c, ref) < (4e-2 if terms == 1 else 3e-3)
+    assert _rel_err(ops.gemm_fp8(aq, asc, M, wq, ws), exact) < 6e-3
+    resid = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    assert _rel_err(ops.gemm_fp8(aq, asc, M, wq, ws, epi=ops.EPI_RESID, resid=resid), resid.float() + exact) < 6e-3
+    if (N // 2) % 128 == 0:
+        got = ops.gemm_fp8(aq, asc, M, wq, ws, epi=ops.EPI_SWIGLU)
+        want = torch.nn.functional.silu(exact[:, : N // 2]) * exact[:, N // 2:]
+        assert got.shape == (M, N // 2) and _rel_err(got, want) < 1.5e-2
+
+
+@pytest.mark.parametrize("M,N,K,epi", [(512, 5120, 1024, 0), (384, 5120, 2048, 1), (512, 1536, 4096, 3), (200, 2304, 3072, 2)])
+def test_gemm_fp8_stream_k_and_many_tiles(M, N, K, epi):
+    import os
+    from pocketllm_b200 import ops
+    a, wq, ws, wd = _fp8_gemm_inputs(M, N, K, M + N + K + epi)
+    aq, asc = ops.quant_act_fp8(a, 2)
+    resid = torch.randn(M, N, device="cuda").to(torch.bfloat16) if epi == ops.EPI_RESID else None
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    os.environ["POCKET_GEMM_STREAMK"] = "1"
+    try:
+        got = [ops.gemm_fp8(aq, asc, M, wq, ws, epi=epi, resid=resid, status=status) for _ in range(3)]
+        torch.cuda.synchronize()
+    finally:
+        del os.environ["POCKET_GEMM_STREAMK"]
+    assert status.item() == 0
+    ref = a.float() @ wd.t()
+    if epi == ops.EPI_RESID:
+        ref = ref + resid.float()
+    if epi == ops.EPI_SWIGLU:
+        ref = torch.nn.functional.silu(ref[:, : N // 2]) * ref[:, N // 2:]
+    assert _rel_err(got[0], ref) < (1.5e-2 if epi == 1 else 6e-3)
+    assert torch.equal(got[0], got[1]) and torch.equal(got[1], got[2])
+    # more tiles than SMs: both accumulators and every stage are reused many times
+    a2, wq2, ws2, wd2 = _fp8_gemm_inputs(1024, 12288, 256, 9)
+    aq2, asc2 = ops.quant_act_fp8(a2, 1)
+    c2 = ops.gemm_fp8(aq2, asc2, 1024, wq2, ws2)
+    planes = aq2.view(torch.float8_e4m3fn).float().sum(0) * asc2.t().repeat_interleave(128, 1)
+    assert _rel_err(c2, planes @ wd2.t()) < 6e-3
+
+
 def test_rmsnorm_embedding_argmax():
     from pocketllm_b200 import ops
     x = torch.randn(5, 640, device="cuda").to(torch.bfloat16)
@@ -412,6 +486,34 @@ def test_gqa_fp8_kv_cache_append_and_decode():
         sc = torch.einsum("hd,htd->ht", q[m].float(), K) * D ** -0.5
         o = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), V) * torch.sigmoid(gate)
         assert _rel_err(out[m].view(Hq, D), o) < 1e-2
+
+
+@pytest.mark.parametrize("M,n,k", [(3, 5000, 512), (2, 70000, 2048), (4, 300, 64), (1, 40, 64)])
+def test_topk_select_matches_torch_topk(M, n, k):
+    from pocketllm_b200.ops import dsv4_ops as dk
+    torch.manual_seed(n)
+    score = torch.randn(M, n, device="cuda")
+    score[0, ::7] = float("-inf")                       # entries a row cannot see
+    score[-1, :n // 2] = score[-1, n // 2: 2 * (n // 2)]   # many exact ties
+    lengths = torch.tensor([n, max(n - 17, 1), n, n][:M], device="cuda", dtype=torch.int32)
+    got = dk.topk_select(score, k, lengths)
+    for m in range(M):
+        row = score[m, : int(lengths[m])]
+        finite = int((~torch.isinf(row)).sum())
+        want_n = min(k, finite)
+        g = got[m]
+        sel = g[g >= 0]
+        assert sel.numel() == want_n and (g[want_n:] == -1).all()
+        assert torch.equal(sel, torch.sort(sel).values) and sel.unique().numel() == want_n       # ascending, no repeats
+        if want_n:
+            kth = torch.topk(row, want_n).values[-1]
+            assert (row[sel.long()] >= kth).all()                         # nothing below the k-th largest
+            assert int((row > kth).sum()) == int((row[sel.long()] > kth).sum())   # everything above it is in
+            ties = torch.nonzero(row == kth).flatten()
+            taken = sel[row[sel.long()] == kth]
+            assert torch.equal(taken.long(), ties[: taken.numel()])      # lowest indices win ties
+    all_rows = dk.topk_select(score, k)
+    assert all_rows.shape == (M, k)
 
 
 def test_full_qk_norm_rope_append_matches_torch():
