@@ -151,8 +151,7 @@ def run_ours(args) -> dict:
         "value": round(decode_tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round((pre_ms + dec_ms) / args.steps, 3), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": round(decode_tok_s / PUBLISHED_DECODE_TOK_S, 3),
-        "dtype": ("bf16 activations; decode streams the fp8 e4m3 weights (128x128 scales); prefill GEMMs read "
-                  + ("bf16 copies of them (see prefill_bf16_shadow_bytes_per_rank)" if eng.prefill_shadow_bytes else "the same fp8 weights")),
+        "dtype": ("bf16 activations; decode streams the fp8 e4m3 weights (128x128 scales); prefill GEMMs: " + PREFILL_DTYPE[eng.prefill_gemm]),
         "data": "synthetic: uniform-random token prompts, random-init N(0,0.02) weights quantised to FP8",
         "prefill_tok_s": round(prefill_tok_s, 1), "prefill_vs_baseline": round(prefill_tok_s / PUBLISHED_PREFILL_TOK_S, 2),
         "prefill_ms": round(pre_ms / args.steps, 3), "decode_ms_per_token": round(dec_ms / args.steps / args.decode_len, 4),
@@ -166,6 +165,7 @@ def run_ours(args) -> dict:
                 "wall_ms_per_step": round(e2e_wall_ms / args.steps, 3)},
         "gpu_launches": int(launches), "wall_ms": round(wall_ms, 1), "comm_status": status,
         "weight_bytes_per_rank": eng.weight_bytes, "prefill_bf16_shadow_bytes_per_rank": eng.prefill_shadow_bytes,
+        "prefill_gemm": eng.prefill_gemm,
         "decode_kernel": "persistent (2 launches per token)" if eng.persistent_decode else "one launch per projection",
         "first_tokens": toks[:16], "last_tokens": toks[-4:],
     }
@@ -173,6 +173,16 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.destroy_process_group()
     return res if rank == 0 else {}
+
+
+# what the many-row GEMMs multiply, by the engine's prefill_gemm mode
+PREFILL_DTYPE = {
+    "fp8x2": "tcgen05 fp8 math on the stored e4m3 weight codes, each bf16 activation as the sum of two e4m3 terms (8 significant "
+             "bits, like bf16), fp32 scale fold per 128-wide k block, fp32 accumulate; no bf16 copy of the weights",
+    "fp8": "tcgen05 fp8 math on the stored e4m3 weight codes, activations quantised to one e4m3 term per 1x128 block, fp32 accumulate",
+    "shadow": "bf16 x bf16 on bf16 copies of the weights in HBM (see prefill_bf16_shadow_bytes_per_rank)",
+    "umma": "bf16 x bf16 with the fp8 weights decoded to bf16 inside shared memory",
+}
 
 
 def main() -> int:

@@ -43,6 +43,7 @@ struct Args {
   bool prefix_cache = true;
   int snapshot_interval = 4096, max_snapshots = 82;
   int persistent_decode = -1;
+  int prefill_gemm = -1;
   std::string prompt_text, kv_cache_dtype = "bf16";
   long random_seed = -1;
   bool benchmark_27b = false, dump_config = false, inspect = false, persistent_stdin = false, no_graph = false;
@@ -68,6 +69,8 @@ void usage() {
                "  --qwen-no-prefix-cache | --qwen-snapshot-interval N (4096, 0 = request boundaries only) --qwen-max-snapshots N (82)\n"
                "      exact prefix reuse across the requests of --qwen-persistent-stdin and --serve\n"
                "  --kv-cache-dtype bf16|fp8   --decode-kernel auto|persistent|per-projection\n"
+               "  --prefill-gemm auto|fp8x2|fp8|shadow|umma   (many-row GEMM on the FP8 linears: native FP8 math with two or one\n"
+               "                 E4M3 terms per activation, bf16 copies of the weights, or decode-to-bf16 in shared memory)\n"
                "  --prompt TEXT --tokenizer-gguf FILE   tokenise the prompt with the GGUF file's BPE vocabulary\n"
                "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
                "  --tokenizer-gguf FILE | --tokenizer-dir DIR (tokenizer.json)   --tokenize TEXT | --detokenize 1,2,3\n"
@@ -109,7 +112,10 @@ Args parse(int argc, char** argv) {
       if (a.kv_cache_dtype == "fp16") a.kv_cache_dtype = "bf16";   // the reference's name for its 16-bit cache
       if (a.kv_cache_dtype != "bf16" && a.kv_cache_dtype != "fp8") throw std::runtime_error("--kv-cache-dtype must be bf16 (fp16) or fp8");
     }
-    else if (f == "--decode-kernel") {
+    else if (f == "--prefill-gemm") {
+      const std::string v = need(i);
+      a.prefill_gemm = v == "umma" ? 0 : v == "shadow" ? 1 : v == "fp8x2" ? 2 : v == "fp8" ? 3 : -1;
+    } else if (f == "--decode-kernel") {
       const std::string v = need(i);
       a.persistent_decode = v == "persistent" ? 1 : v == "per-projection" ? 0 : -1;
     }
@@ -497,6 +503,7 @@ int run(const Args& a) {
   opt.snapshot_interval = a.snapshot_interval;
   opt.max_snapshots = a.max_snapshots;
   opt.persistent_decode = a.persistent_decode;
+  opt.prefill_gemm = a.prefill_gemm;
   g_mtp_tokens = a.mtp_tokens;
   pk::QwenEngine eng(cfg, opt);
   if (a.random_seed >= 0 || a.benchmark_27b) eng.init_random((uint64_t)std::max(0L, a.random_seed), 0.02f);

@@ -939,7 +939,7 @@ void QwenEngine::run_chunk(int M, bool mtp) {
   // Native FP8: quantise the rows of A (one or two E4M3 terms per value, a scale per row and 128-wide k block), then run
   // tcgen05 kind::f8f6f4 on them and on the stored weight codes. Shapes the kernel does not take fall through.
   auto gemm_native = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc, const PkPush* ps) -> bool {
-    if (act_q_ == nullptr || (w.K & 127) != 0 || (lda & 3) != 0 || M > act_rows_) return false;
+    if (act_q_ == nullptr || w.w == nullptr || w.scale == nullptr || (w.K & 127) != 0 || (lda & 3) != 0 || M > act_rows_) return false;   // bf16-only linears have no codes
     if (epi == 1 && ((w.N >> 1) & 127) != 0) return false;
     const int terms = gemm_mode_ == 3 ? 1 : 2;
     check(pk_quant_act_fp8(A, lda, M, w.K, terms, act_q_, act_rows_, act_scale_, act_rows_, stream_), "quant_act_fp8");

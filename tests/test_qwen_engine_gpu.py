@@ -66,7 +66,7 @@ def test_persistent_decode_kernel_matches_per_projection_launches(tiny, shape, m
         runs.append((toks, lgs))
         eng.close()
     (t0, l0), (t1, l1) = runs
-    assert t0[:4] == t1[:4], (t0, t1)
+    assert t0[0] == t1[0], (t0, t1)                  # the prefill is the same code in both runs
     for i in range(steps):
         # same inputs so far: the logits must be close; the picks may differ only on a near-tie (the two paths add
         # partial sums in different orders, and a flipped bf16 rounding moves the logits by a few 1e-3)
@@ -106,6 +106,28 @@ def test_tensor_core_prefill_matches_streaming_prefill(tiny):
         assert tb == ts
     # continuing from either state gives the same greedy continuation
     assert big.position == small.position == 100
+    big.close()
+    small.close()
+
+
+@pytest.mark.parametrize("mode,tol", [("fp8x2", 3e-2), ("fp8", 2.5e-1), ("shadow", 3e-2), ("umma", 3e-2)])
+def test_prefill_gemm_modes_agree_with_streaming_prefill(tiny, mode, tol):
+    """Every many-row GEMM of the engine against the eight-row weight-streaming path. The native FP8 modes keep no bf16
+    copy of the weights; with two E4M3 terms per activation they stay inside the band of the bf16 modes."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    torch.manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (150,)).tolist()
+    big = qh.QwenEngine(cfg, max_context=512, prefill_chunk=128, prefill_gemm=mode).load(d)
+    small = qh.QwenEngine(cfg, max_context=512, prefill_chunk=8).load(d)
+    assert big.prefill_gemm == mode
+    assert (big.prefill_shadow_bytes > 0) == (mode == "shadow")
+    tb, ts = big.prefill(prompt), small.prefill(prompt)
+    lb, ls = big.logits(0), small.logits(0)
+    assert _close(lb, ls, tol)
+    assert big.comm_status() == 0
+    if mode != "fp8" and (ls.topk(2).values[0] - ls.topk(2).values[1]) > 0.05 * ls.abs().max():
+        assert tb == ts
     big.close()
     small.close()
 
@@ -295,12 +317,17 @@ def test_mtp_predictor_matches_oracle(tiny_mtp, variant, n_prompt):
     for t in prompt:
         logits = ref.step(t)
         hid.append(ref.last_hidden)
-    first = int(logits.argmax())
+    eng = qh.QwenEngine(cfg, max_context=256, prefill_chunk=32, mtp=True).load(d)
+    first = eng.prefill(prompt)
+    if first != int(logits.argmax()):
+        # only a near-tie of the target's logits may be decided differently; the predictor is then compared on the
+        # engine's pick (its last row takes the token the target has just produced)
+        top2 = logits.topk(2).values
+        assert (top2[0] - top2[1]).item() < 0.02 * logits.abs().max().item()
+        assert first == int(logits.topk(2).indices[1])
     shifted = prompt[1:] + [first]
     for i, (t, h) in enumerate(zip(shifted, hid)):
         mlogits, _ = ref.mtp_step(t, h, i)
-    eng = qh.QwenEngine(cfg, max_context=256, prefill_chunk=32, mtp=True).load(d)
-    assert eng.prefill(prompt) == first
     got = eng.mtp_logits()
     assert _close(got, mlogits, 5e-2)
     top2 = mlogits.topk(2).values
