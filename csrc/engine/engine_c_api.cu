@@ -10,6 +10,7 @@
 #include "mem_guard.hpp"
 #include "qwen_engine.hpp"
 #include "sampler.hpp"
+#include "kv_swap.hpp"
 #include "staging.hpp"
 #include "tokenizer.hpp"
 
@@ -351,6 +352,30 @@ PK_EAPI const char* pk_tokenizer_decode(void* t, const int* ids, int n, int skip
 }
 
 // ---- host-to-device expert staging -----------------------------------------------------------------------------------
+
+// ---- KV swap tier ----
+PK_EAPI void* pk_kvswap_create(int capacity, int device_slots, unsigned long long row_bytes, int window, int host_only) {
+  void* out = nullptr;
+  guarded([&] { out = new pk::KvSwapTier(capacity, device_slots, (size_t)row_bytes, window, host_only != 0); });
+  return out;
+}
+PK_EAPI void pk_kvswap_destroy(void* h) { delete (pk::KvSwapTier*)h; }
+PK_EAPI int pk_kvswap_store(void* h, int first, int count, const void* rows_device, void* stream) {
+  return guarded([&] { ((pk::KvSwapTier*)h)->store(first, count, rows_device, (cudaStream_t)stream); });
+}
+PK_EAPI int pk_kvswap_swap_in(void* h, const int* selected_device, int n, void* pool_device, int* physical_device, void* stream) {
+  return guarded([&] { ((pk::KvSwapTier*)h)->swap_in(selected_device, n, pool_device, physical_device, (cudaStream_t)stream); });
+}
+PK_EAPI int pk_kvswap_reset(void* h) {
+  return guarded([&] { ((pk::KvSwapTier*)h)->reset(); });
+}
+// out[0] hits, [1] misses, [2] h2d bytes, [3] d2h bytes, [4] evictions, [5] steps, [6] stored rows, [7] host bytes
+PK_EAPI void pk_kvswap_stats(void* h, unsigned long long* out) {
+  const pk::KvSwapTier* t = (const pk::KvSwapTier*)h;
+  const pk::KvSwapStats& s = t->stats();
+  out[0] = s.hits; out[1] = s.misses; out[2] = s.h2d_bytes; out[3] = s.d2h_bytes; out[4] = s.evictions; out[5] = s.steps;
+  out[6] = (unsigned long long)t->stored_rows(); out[7] = (unsigned long long)t->host_bytes();
+}
 
 PK_EAPI void* pk_lru_create(int slots) {
   pk::LruSlotMap* m = nullptr;

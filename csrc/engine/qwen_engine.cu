@@ -1092,10 +1092,19 @@ int QwenEngine::prefill(const int* tokens_host, int n) {
   cuda_check(cudaEventRecord(ev0_, stream_), "event");
   const long long l0 = launches_;
   int done = 0;
+  // The prompt is staged in pinned memory once (in pieces only when it is longer than the staging buffer), so the chunks
+  // queue back to back and the host never waits for the device inside the loop.
+  const int stage_cap = std::max<int>(rows_cap_, out_cap_);
+  int stage_base = 0, stage_end = 0;
   while (done < n) {
-    int M = std::min(n - done, rows_cap_);
-    memcpy(pinned_tok_, tokens_host + done, (size_t)M * sizeof(int));
-    cuda_check(cudaMemcpyAsync(tokens_dev_, pinned_tok_, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, stream_), "h2d tokens");
+    if (done >= stage_end) {
+      if (stage_end > 0) cuda_check(cudaStreamSynchronize(stream_), "prefill staging");   // copies out of the buffer are over
+      stage_base = done;
+      stage_end = done + std::min(n - done, stage_cap);
+      memcpy(pinned_tok_, tokens_host + stage_base, (size_t)(stage_end - stage_base) * sizeof(int));
+    }
+    int M = std::min(std::min(n - done, rows_cap_), stage_end - done);
+    cuda_check(cudaMemcpyAsync(tokens_dev_, pinned_tok_ + (done - stage_base), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, stream_), "h2d tokens");
     check(pk_iota_int(pos_dev_, M, nullptr, pos_, stream_), "iota");
     if (M <= kSmallRows) run_small(M, false);
     else run_chunk(M);
@@ -1107,8 +1116,6 @@ int QwenEngine::prefill(const int* tokens_host, int n) {
       else check(pk_copy_int(next_tok_dev_, mtp_tok_dev_ + (M - 1), 1, stream_), "first output token");
       mtp_forward(M, tgt_hid_, pos_);
     }
-    // The pinned staging buffer is reused by the next chunk.
-    cuda_check(cudaStreamSynchronize(stream_), "prefill chunk");
     pos_ += M;
     done += M;
   }

@@ -1,5 +1,7 @@
 #include "staging.hpp"
 
+#include <unordered_set>
+
 #include <algorithm>
 #include <cstring>
 #include <stdexcept>
@@ -22,8 +24,9 @@ LruSlotMap::LruSlotMap(int slots) : n_(slots) {
 
 std::vector<int> LruSlotMap::assign(const std::vector<long long>& needed, std::vector<std::pair<long long, int>>* loads) {
   std::vector<long long> uniq;
+  std::unordered_set<long long> in_step;
   for (long long k : needed)
-    if (std::find(uniq.begin(), uniq.end(), k) == uniq.end()) uniq.push_back(k);
+    if (in_step.insert(k).second) uniq.push_back(k);
   if ((int)uniq.size() > n_)
     throw std::runtime_error(std::to_string(uniq.size()) + " distinct keys do not fit in " + std::to_string(n_) + " slots; split the step into waves");
   // touch the residents first so that none of them is the eviction victim of another key of this step
@@ -44,7 +47,7 @@ std::vector<int> LruSlotMap::assign(const std::vector<long long>& needed, std::v
       free_.pop_back();
     } else {
       auto victim = order_.begin();
-      while (victim != order_.end() && std::find(uniq.begin(), uniq.end(), *victim) != uniq.end()) ++victim;
+      while (victim != order_.end() && in_step.count(*victim) != 0) ++victim;
       if (victim == order_.end()) throw std::runtime_error("LruSlotMap: no evictable slot");
       slot = where_[*victim].first;
       where_.erase(*victim);

@@ -51,13 +51,14 @@ constexpr int kEpiWarps = 16;
 constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr uint32_t kTmemCols = 512;       // two accumulators of 256 columns
 
-enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_RESID = 2, EPI_F32 = 3, EPI_PUSH = 4 };
+enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_RESID = 2, EPI_F32 = 3, EPI_PUSH = 4, EPI_SCORE = 5 };
 
 struct Params {
   int M, N, K, epi;
   bf16* C;
   float* Cf;
   const bf16* resid;
+  const float* head_w;     // EPI_SCORE: weight of each of the 128 query heads
   int ldc;
   int tiles_m, tiles_n;
   int m_pad;               // rows of one term plane in the A tensor map
@@ -426,6 +427,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           for (int i = 0; i < 32; ++i)
             if (j0 + i < half_n) dst[i] = __float2bfloat16(silu(acc0[i]) * acc1[i]);
         }
+      } else if (p.epi == EPI_SCORE) {
+        // Chunk scorer: column h holds q_hi[h] . k and column 128 + h holds q_lo[h] . k; this thread's share of
+        // sum_h relu(q[h] . k) * w[h] goes to partial[cq][row] (four partials per row, added by the caller's next kernel).
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) part = fmaf(fmaxf(acc0[i] + acc1[i], 0.f), __ldg(p.head_w + cq * 32 + i), part);
+        p.Cf[(size_t)cq * p.ldc + m] = part;
       } else {
         emit32(p, m, tn * BN + cq * 32, acc0);
         emit32(p, m, tn * BN + 128 + cq * 32, acc1);
@@ -623,4 +631,39 @@ PK_API int pk_gemm_fp8(const void* Aq, int terms, int m_pad, const float* a_scal
     }
   }
   return terms == 1 ? launch<1>(tmap_a, tmap_w, p, grid, stream) : launch<2>(tmap_a, tmap_w, p, grid, stream);
+}
+
+// Chunk scorer of the long-context retriever as one FP8 GEMM: keys [n_chunks, 128] E4M3 codes with one fp32 scale per
+// chunk, queries as 256 rows of E4M3 codes (row h: first term of head h, row 128 + h: its rounding residue; unused rows
+// zero) whose per-head scale is already folded into head_w[128]. partial [4][ld] receives four partial sums per chunk of
+// sum_h relu(q[h] . k) * head_w[h]. ones2: two floats equal to 1 (the weight-scale operand of the GEMM).
+PK_API int pk_fp8_chunk_scores(const void* keys, const float* key_scale, int n_chunks, const void* qcodes, const float* head_w, const float* ones2,
+                               float* partial, int ld, uint32_t* status, int sm_count, cudaStream_t stream) {
+  if (n_chunks < 1 || ld < n_chunks || keys == nullptr || key_scale == nullptr || qcodes == nullptr || head_w == nullptr || ones2 == nullptr ||
+      partial == nullptr)
+    return PK_ERR_BAD_ARG;
+  if (((uintptr_t)keys & 15) != 0 || ((uintptr_t)qcodes & 15) != 0) return PK_ERR_BAD_ARG;
+  EncodeTiledFn encode = encode_fn();
+  if (encode == nullptr) return PK_ERR_UNSUPPORTED;
+  CUtensorMap tmap_a, tmap_w;
+  if (!encode_u8_2d(encode, &tmap_a, keys, 128, (uint64_t)n_chunks, 128)) return PK_ERR_CUDA;
+  if (!encode_u8_2d(encode, &tmap_w, qcodes, 128, 256, 128)) return PK_ERR_CUDA;
+  Params p{};
+  p.M = n_chunks;
+  p.N = 256;
+  p.K = 128;
+  p.epi = EPI_SCORE;
+  p.Cf = partial;
+  p.ldc = ld;
+  p.head_w = head_w;
+  p.tiles_m = (n_chunks + BM - 1) / BM;
+  p.tiles_n = 1;
+  p.m_pad = n_chunks;
+  p.a_scale = key_scale;
+  p.a_ld = n_chunks;
+  p.w_scale = ones2;
+  p.w_ld = 1;
+  p.status = status;
+  const int sms = sm_count > 0 ? sm_count : 148;
+  return launch<1>(tmap_a, tmap_w, p, p.tiles_m < sms ? p.tiles_m : sms, stream);
 }

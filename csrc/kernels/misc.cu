@@ -540,3 +540,20 @@ PK_API int pk_fp8_to_bf16(const void* w, const float* scale, int N, int K, void*
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
+
+// pool[slots[j]] = src[j] for j < n: rows of row_bytes (a multiple of 16), one warp per 512 bytes of a row.
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ slots, int n, int row_vec, uint4* __restrict__ pool) {
+  const int j = blockIdx.y;
+  const int v = blockIdx.x * 256 + threadIdx.x;
+  if (j >= n || v >= row_vec) return;
+  pool[(size_t)slots[j] * row_vec + v] = src[(size_t)j * row_vec + v];
+}
+
+PK_API int pk_scatter_rows(const void* src, const int* slots, int n, int row_bytes, void* pool, cudaStream_t stream) {
+  if (src == nullptr || slots == nullptr || pool == nullptr || n < 1 || row_bytes < 16 || (row_bytes & 15) != 0) return PK_ERR_BAD_ARG;
+  if (((uintptr_t)src & 15) != 0 || ((uintptr_t)pool & 15) != 0 || n > 65535) return PK_ERR_BAD_ARG;
+  const int row_vec = row_bytes / 16;
+  scatter_rows_kernel<<<dim3((row_vec + 255) / 256, n), 256, 0, stream>>>((const uint4*)src, slots, n, row_vec, (uint4*)pool);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}

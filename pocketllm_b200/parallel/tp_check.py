@@ -38,10 +38,22 @@ def main() -> int:
                         prefill_chunk=args.prefill_chunk, use_cuda_graph=not args.no_graph, mtp=args.mtp > 0).load(args.ckpt)
     tp.connect_engine(eng)
     prompt = [int(t) for t in args.prompt.split(",")]
-    tokens = eng.generate(prompt, args.new)
+    first = eng.prefill(prompt)
+    # the prefill logits of the whole vocabulary (every rank holds one shard), as a digest that runs of different world
+    # sizes can be compared by: the eight largest entries and the norm
+    shard = eng.logits(0).float().contiguous()
+    if world > 1:
+        parts = [torch.empty_like(shard) for _ in range(world)]
+        dist.all_gather(parts, shard)
+        full = torch.cat(parts)
+    else:
+        full = shard
+    top = full.topk(8)
+    tokens = [first] + eng.decode(args.new - 1) if args.new > 1 else [first]
     logits = eng.logits(0)
     out = {"world": world, "tokens": tokens, "comm_status": eng.comm_status(), "timings": eng.timings(),
-           "logit_shard_sum": float(logits.double().sum())}
+           "logit_shard_sum": float(logits.double().sum()), "prefill_logits_top": [[int(i), float(v)] for v, i in zip(top.values, top.indices)],
+           "prefill_logits_norm": float(full.double().norm()), "prefill_logits_head": [float(v) for v in full[:64]]}
     if args.mtp > 0:
         eng.reset()
         out["spec_tokens"], out["spec_stats"] = eng.generate_mtp(prompt, args.new, args.mtp)
@@ -60,7 +72,9 @@ def main() -> int:
         if extra:
             same = same and all(g["spec_tokens"] == gathered[0]["spec_tokens"] and g["replay_tokens"] == gathered[0]["replay_tokens"] for g in gathered)
         print(json.dumps({"world": world, "tokens": gathered[0]["tokens"], "ranks_agree": same,
-                          "comm_status": [g["comm_status"] for g in gathered], "timings": gathered[0]["timings"], **extra}), flush=True)
+                          "comm_status": [g["comm_status"] for g in gathered], "timings": gathered[0]["timings"],
+                          "prefill_logits_top": gathered[0]["prefill_logits_top"], "prefill_logits_norm": gathered[0]["prefill_logits_norm"],
+                          "prefill_logits_head": gathered[0]["prefill_logits_head"], **extra}), flush=True)
     eng.close()
     if world > 1:
         dist.destroy_process_group()

@@ -65,6 +65,36 @@ def test_tp2_mtp_speculative_decode_equals_plain(tmp_path):
     assert two["replay_stats"]["accepted"] == two["replay_stats"]["proposed"] > 0 and two["replay_stats"]["rollbacks"] == 0
 
 
+def _wide_cfg():
+    """Heads and widths that divide by eight, every per-rank K a multiple of 128 (so the native FP8 GEMM runs at every world)."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    return qh.QwenHybridConfig(vocab_size=2048, hidden_size=256, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=8,
+                               num_key_value_heads=8, linear_num_key_heads=8, linear_num_value_heads=8, max_position_embeddings=4096)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+@pytest.mark.parametrize("prompt", ["short", "long"])
+def test_tp4_tp8_tokens_and_prefill_logits_match_tp1(tmp_path, world, prompt):
+    """The first 16 greedy tokens and the prefill logits of TP4 / TP8 against one rank: streaming prefill (short prompt)
+    and the tensor-core prefill with reduce-scatter + all-gather (long prompt), both followed by the persistent decode."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg = _wide_cfg()
+    qh.save_checkpoint(tmp_path, cfg, qh.random_checkpoint(cfg, seed=8, sigma=0.05))
+    text = PROMPT_SHORT if prompt == "short" else PROMPT_LONG
+    one = _run(1, tmp_path, 29541, text, new=16)
+    many = _run(world, tmp_path, 29542 + world, text, new=16)
+    assert many["ranks_agree"] and many["comm_status"] == [0] * world
+    a, b = torch.tensor(one["prefill_logits_head"]), torch.tensor(many["prefill_logits_head"])
+    assert ((a - b).norm() / a.norm()).item() < 3e-2
+    assert abs(one["prefill_logits_norm"] - many["prefill_logits_norm"]) < 3e-2 * one["prefill_logits_norm"]
+    assert one["prefill_logits_top"][0][0] in [i for i, _ in many["prefill_logits_top"][:3]]
+    # partial sums are added in a different order: the picks may part ways on a near-tie, not early and not often
+    same = sum(1 for x, y in zip(one["tokens"], many["tokens"]) if x == y)
+    assert one["tokens"][:3] == many["tokens"][:3] and same >= 8, (one["tokens"], many["tokens"])
+
+
 def _nccl_smoke(world: int, tmp_path) -> list[str]:
     exe = ROOT / "pocketllm_b200" / "_C" / "pocket_engine"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
