@@ -208,6 +208,17 @@ PK_EAPI int pk_qwen_set_prefill_gemm(void* h, int mode) {
 }
 PK_EAPI int pk_qwen_prefill_gemm_mode(void* h) { return ((pk::QwenEngine*)h)->prefill_gemm_mode(); }
 
+PK_EAPI int pk_qwen_enable_nccl_fallback(void* h, const char* id_path, int timeout_ms) {
+  return guarded([&] { ((pk::QwenEngine*)h)->enable_nccl_fallback(id_path, timeout_ms > 0 ? timeout_ms : 600000); });
+}
+PK_EAPI int pk_qwen_switch_to_nccl(void* h) {
+  return guarded([&] { ((pk::QwenEngine*)h)->switch_to_nccl(); });
+}
+PK_EAPI int pk_qwen_nccl_mode(void* h) { return ((pk::QwenEngine*)h)->nccl_mode() ? 1 : 0; }
+PK_EAPI int pk_qwen_set_comm_timeout_us(void* h, unsigned us) {
+  return guarded([&] { ((pk::QwenEngine*)h)->set_comm_timeout_us(us); });
+}
+
 PK_EAPI int pk_qwen_decode_trace(void* h, unsigned long long* out, int cap) {
   int n = 0;
   guarded([&] { n = ((pk::QwenEngine*)h)->copy_decode_trace(out, cap); });

@@ -38,7 +38,7 @@ struct Args {
   std::string ckpt, token_ids, token_ids_file, id_path = "/tmp/pocket_engine.rdv";
   int max_new_tokens = 16, tp_world = 1, tp_rank = 0, device = -1, max_context = 4096, prefill_chunk = 512;
   int window = 0, sink = 0;
-  bool mtp = false, nccl_smoke = false;
+  bool mtp = false, nccl_smoke = false, nccl_fallback = false;
   int mtp_tokens = 4;
   bool prefix_cache = true;
   int snapshot_interval = 4096, max_snapshots = 82;
@@ -74,6 +74,8 @@ void usage() {
                "  --prompt TEXT --tokenizer-gguf FILE   tokenise the prompt with the GGUF file's BPE vocabulary\n"
                "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
                "  --tokenizer-gguf FILE | --tokenizer-dir DIR (tokenizer.json)   --tokenize TEXT | --detokenize 1,2,3\n"
+               "  --nccl-fallback   (with --tp-world > 1) join an NCCL communicator at start; after a peer wait times out the failed\n"
+               "                 step is reported and later steps run their collectives through NCCL\n"
                "  --nccl-smoke --tp-world N --tp-rank R [--nccl-id-path PATH]   NCCL baseline path: all-reduce, broadcast, all-gather, top-1\n"
                "  --dsv4-config DIR|FILE.gguf [--tp-world N]   parse, validate and print a DeepSeek-V4 config\n"
                "  --weight-source DIR|FILE.gguf [--lookup NAME | --lookup-expert LAYER,EXPERT,w1|w2|w3]   tensor lookup by model name\n"
@@ -103,6 +105,7 @@ Args parse(int argc, char** argv) {
     else if (f == "--qwen-attention-window") a.window = std::stoi(need(i));
     else if (f == "--qwen-attention-sink-tokens") a.sink = std::stoi(need(i));
     else if (f == "--nccl-smoke") a.nccl_smoke = true;
+    else if (f == "--nccl-fallback") a.nccl_fallback = true;
     else if (f == "--qwen-mtp") a.mtp = true;
     else if (f == "--qwen-no-prefix-cache") a.prefix_cache = false;
     else if (f == "--qwen-snapshot-interval") a.snapshot_interval = std::stoi(need(i));
@@ -527,6 +530,8 @@ int run(const Args& a) {
       opened.push_back(arenas[r]);
     }
     eng.set_peer_arenas(arenas.data());
+    // joined now, while every rank is known to be up; used only after a bounded peer wait has run out
+    if (a.nccl_fallback) eng.enable_nccl_fallback(a.id_path + ".nccl");
   }
   pk::CmdChannel chan(a.id_path + ".cmdsock", a.tp_rank, a.tp_world);
   if (a.tp_world > 1) pk::file_rendezvous_cleanup(a.id_path, a.tp_rank);

@@ -740,9 +740,36 @@ void QwenEngine::raise_if_step_failed(const char* what) {
   clear_comm_status();
   // tokens of this step are not handed out; a graph that holds the failed kernels' state is rebuilt on the next decode
   last_token_ = -1;
-  char buf[200];
-  snprintf(buf, sizeof buf, "%s: a bounded device wait ran out (peer word %u, tensor-core word %u); the step is discarded", what, peer, gemm);
+  // The status word travels with the sampler exchange, so every rank arrives here in the same step: all of them leave
+  // the peer-store path together.
+  const bool to_nccl = peer != 0u && nccl_ != nullptr && !nccl_mode_;
+  if (to_nccl) switch_to_nccl();
+  char buf[260];
+  snprintf(buf, sizeof buf, "%s: a bounded device wait ran out (peer word %u, tensor-core word %u); the step is discarded%s", what, peer, gemm,
+           to_nccl ? "; later steps use NCCL collectives" : "");
   throw CommTimeout(buf);
+}
+
+void QwenEngine::enable_nccl_fallback(const std::string& id_path, int timeout_ms) {
+  if (opt_.tp_world < 2) return;
+  if (!NcclComm::available()) throw std::runtime_error("NCCL was not found (libnccl.so.2)");
+  nccl_ = std::make_shared<NcclComm>(id_path, opt_.tp_rank, opt_.tp_world, opt_.device, timeout_ms);
+}
+
+void QwenEngine::switch_to_nccl() {
+  if (nccl_mode_) return;
+  if (nccl_ == nullptr) throw std::runtime_error("switch_to_nccl: enable_nccl_fallback was not called");
+  cuda_check(cudaStreamSynchronize(stream_), "sync");
+  nccl_mode_ = true;
+  // one launch per projection from here on: the persistent kernel and a captured graph hold peer pointers and flags
+  persistent_built_ = true;
+  persistent_ok_ = false;
+  if (decode_graph_) {
+    cudaGraphExecDestroy(decode_graph_);
+    decode_graph_ = nullptr;
+  }
+  opt_.use_cuda_graph = false;
+  clear_comm_status();
 }
 
 void QwenEngine::copy_logits(float* out_host, int row) {
@@ -777,6 +804,17 @@ PkWait QwenEngine::make_wait(int site) const {
 
 PkPush QwenEngine::make_push(int site, bool big, int rows_per_rank) const {
   PkPush p{};
+  if (nccl_mode_) {
+    // this rank's partial rows go to the first slot of its own arena, unflagged; NCCL adds the ranks' slots in place
+    p.dst[0] = (float*)((char*)arena_ + (big ? off_bslot_[site & 1] : off_slot_[site & 1]));
+    p.block_counter = (uint32_t*)((char*)arena_ + off_counter_);
+    p.epoch = (const uint32_t*)((char*)arena_ + off_epoch_);
+    p.sites_per_epoch = sites_per_epoch_;
+    p.site = site;
+    p.world = 1;
+    p.rank = 0;
+    return p;
+  }
   p.rows_per_rank = rows_per_rank;
   for (int r = 0; r < opt_.tp_world; ++r) {
     p.dst[r] = (float*)((char*)peers_[r] + (big ? off_bslot_[site & 1] : off_slot_[site & 1]));
@@ -818,7 +856,7 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
     PkWait wt = make_wait(pending >= 0 ? pending : 0);
     void* hout = pending >= 0 ? hidden_buf_[cur_ ^ 1] : nullptr;
     check(pk_matvec(w ? w->w : nullptr, w ? w->scale : nullptr, wb, w ? w->N : 0, nb, hidden_, M, hidden_buf_[cur_], parts,
-                    W, hout, gamma, 1, eps, pending >= 0 ? &wt : nullptr, epi, y, ldy, push, sm_count_, stream_),
+                    kernel_world(), hout, gamma, 1, eps, pending >= 0 && !nccl_mode_ ? &wt : nullptr, epi, y, ldy, push, sm_count_, stream_),
           "matvec(consume)");
     if (pending >= 0) cur_ ^= 1;
     pending = -1;
@@ -828,6 +866,7 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
     check(pk_matvec(w.w, w.scale, nullptr, w.N, 0, w.K, M, x, nullptr, 0, nullptr, nullptr, 0, eps, nullptr, 3,
                     nullptr, hidden_, &ps, sm_count_, stream_),
           "matvec(produce)");
+    if (nccl_mode_) nccl_->all_reduce_sum(slot_parts(site), (size_t)M * hidden_, NcclComm::Dtype::F32, stream_);
     pending = site;
   };
 
@@ -860,7 +899,8 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
     const float* parts = slot_parts(pending);
     PkWait wt = make_wait(pending);
     void* y = mtp ? mtp_out_ : tgt_hid_;
-    check(pk_rmsnorm(hidden_buf_[cur_], parts, W, M, hidden_, hidden_buf_[cur_], mtp ? mtp_norm_ : final_norm_, 1, eps, y, &wt, stream_),
+    check(pk_rmsnorm(hidden_buf_[cur_], parts, kernel_world(), M, hidden_, hidden_buf_[cur_], mtp ? mtp_norm_ : final_norm_, 1, eps, y,
+                     nccl_mode_ ? nullptr : &wt, stream_),
           "final norm");
     pending = -1;
     const bool all = !mtp && (all_logits || M == 1);
@@ -883,7 +923,8 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
     // Fold the pending partials into the hidden state first, then project the last row.
     const float* parts = slot_parts(pending);
     PkWait wt = make_wait(pending);
-    check(pk_rmsnorm(hidden_buf_[cur_], parts, W, M, hidden_, hidden_buf_[cur_], final_norm_, 1, eps, nullptr, &wt, stream_),
+    check(pk_rmsnorm(hidden_buf_[cur_], parts, kernel_world(), M, hidden_, hidden_buf_[cur_], final_norm_, 1, eps, nullptr,
+                     nccl_mode_ ? nullptr : &wt, stream_),
           "fold");
     pending = -1;
     const char* last = (const char*)hidden_buf_[cur_] + (size_t)(M - 1) * hidden_ * 2;
@@ -901,7 +942,24 @@ void QwenEngine::sample_rows(int M, const float* logits, int* out) {
                   cand_idx_, best_val_, W == 1 ? out : best_idx_, stream_),
         "argmax");
   ++launches_;
-  if (W > 1) {
+  if (W > 1 && nccl_mode_) {
+    // each rank's row of candidates into its own arena, then one all-gather per array, then the same merge
+    PkPush ps{};
+    ps.world = 1;
+    ps.rank = opt_.tp_rank;
+    ps.block_counter = (uint32_t*)((char*)arena_ + off_counter_);
+    ps.epoch = (const uint32_t*)((char*)arena_ + off_epoch_);
+    ps.sites_per_epoch = sites_per_epoch_;
+    uint32_t* status = (uint32_t*)((char*)arena_ + off_status_);
+    check(pk_cand_push(best_val_, best_idx_, M, &ps, peer_cval_dev_ + opt_.tp_rank, peer_cidx_dev_ + opt_.tp_rank, status, kCandStride, stream_), "cand_push");
+    float* cval = (float*)((char*)arena_ + off_cval_);
+    int* cidx = (int*)((char*)arena_ + off_cidx_);
+    nccl_->all_gather(cval + (size_t)opt_.tp_rank * kCandStride, cval, kCandStride, NcclComm::Dtype::F32, stream_);
+    nccl_->all_gather(cidx + (size_t)opt_.tp_rank * kCandStride, cidx, kCandStride, NcclComm::Dtype::I32, stream_);
+    PkWait wt = make_wait(2 * cfg_.num_layers);
+    wt.flag = nullptr;
+    check(pk_cand_merge_wait(cval, cidx, M, W, &wt, out, status, kCandStride, stream_), "cand_merge");
+  } else if (W > 1) {
     // Exchange {logit, token} of every rank through peer memory and merge (lowest id on ties).
     const int site = 2 * cfg_.num_layers;
     PkPush ps = make_push(site);
@@ -967,6 +1025,12 @@ void QwenEngine::run_chunk(int M, bool mtp) {
   auto gemm_out = [&](const void* A, int lda, const Fp8Linear& w, int site) {
     if (W == 1) {
       gemm(A, lda, w, 2, hid, hid, hidden_);
+    } else if (nccl_mode_) {
+      // fp32 partial rows into this rank's slot, summed over the ranks in place; the next norm adds them to the residual
+      float* slot = slot_parts(site, true);
+      gemm(A, lda, w, 3, slot, nullptr, hidden_);
+      nccl_->all_reduce_sum(slot, (size_t)M * hidden_, NcclComm::Dtype::F32, stream_);
+      pending = site;
     } else {
       PkPush ps = make_push(site, true, rpr);
       if (gemm_native(A, lda, w, 4, nullptr, nullptr, hidden_, &ps)) {
@@ -979,7 +1043,10 @@ void QwenEngine::run_chunk(int M, bool mtp) {
   };
   // y == nullptr with pending partials folds them into the owners' residual rows only.
   auto norm = [&](const float* gamma, void* y) {
-    if (pending >= 0) {
+    if (pending >= 0 && nccl_mode_) {
+      check(pk_rmsnorm(hid, slot_parts(pending, true), 1, M, hidden_, hid, gamma, 1, eps, y, nullptr, stream_), "rmsnorm(+reduced rows)");
+      pending = -1;
+    } else if (pending >= 0) {
       PkWait wrs = make_wait(pending);
       PkPush pag = make_push(pending, true);
       PkWait wag = make_wait(pending);
@@ -1149,7 +1216,7 @@ void QwenEngine::build_persistent() {
   if (const char* v = getenv("POCKET_DECODE_PERSISTENT")) mode = atoi(v);
   // The predictor's verify rows run on the per-projection kernels; plain decode then uses them too, so that both
   // see the same rounding and speculative tokens equal plain ones.
-  if (mode == 0 || (mode < 0 && opt_.mtp)) return;
+  if (mode == 0 || (mode < 0 && opt_.mtp) || nccl_mode_) return;   // NCCL collectives sit between launches: one launch per projection
   if (!peers_set_) throw std::runtime_error("peer arenas not registered");
   int max_k = hidden_, max_rows = vocab_l_;
   auto lin = [&](const Fp8Linear& l) {

@@ -16,6 +16,7 @@
 
 #include "../common/pk_comm_types.h"
 #include "../kernels/pk_decode_persistent.h"
+#include "nccl_comm.hpp"
 #include "qwen_config.hpp"
 
 namespace pk {
@@ -198,6 +199,18 @@ class QwenEngine {
   const QwenEngineOptions& options() const { return opt_; }
   size_t weight_bytes() const { return weight_bytes_; }
   size_t shadow_bytes() const { return shadow_bytes_; }
+  // Fallback collectives: joins the NCCL communicator of this tensor-parallel group now (every rank must call it;
+  // rendezvous through files under `id_path`). After a bounded peer wait has run out, the failed step raises CommTimeout
+  // as before and every later step runs its row-parallel sums, the prefill gathers and the sampler exchange through
+  // NCCL instead of peer stores (role of the reference's NCCL path, cpp_engine/src/tp_comm.cpp:40-269, which is its only one).
+  void enable_nccl_fallback(const std::string& id_path, int timeout_ms = 600000);
+  void switch_to_nccl();               // also callable directly (a rank that learnt of the failure on the host)
+  // Budget of every device-side wait on a peer (microseconds); takes effect with the next step.
+  void set_comm_timeout_us(uint32_t us) {
+    opt_.comm_timeout_us = us;
+    set_persistent_decode(opt_.persistent_decode);   // the persistent kernel's parameter block and the graph carry the old budget
+  }
+  bool nccl_mode() const { return nccl_mode_; }
   int prefill_gemm_mode() const { return gemm_mode_; }
   // Before the weights are loaded or initialised: choose the many-row GEMM (QwenEngineOptions::prefill_gemm).
   void set_prefill_gemm(int mode) {
@@ -271,6 +284,9 @@ class QwenEngine {
   size_t weight_bytes_ = 0;
   size_t alloc_bytes_ = 0;   // everything obtained through dalloc
   size_t shadow_bytes_ = 0;
+  std::shared_ptr<NcclComm> nccl_;
+  bool nccl_mode_ = false;
+  int kernel_world() const { return nccl_mode_ ? 1 : opt_.tp_world; }   // what the kernels see as the number of slots to add
   int gemm_mode_ = 0;
   void* act_q_ = nullptr;        // [2][rows_cap_ up to 128][K max] E4M3 terms of the GEMM input being multiplied
   float* act_scale_ = nullptr;   // [K max / 128][that row count]

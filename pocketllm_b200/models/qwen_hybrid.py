@@ -582,6 +582,23 @@ class QwenEngine:
         """Bytes of the K and V caches of every full-attention layer on this rank (scales included)."""
         return int(self._L.pk_qwen_kv_cache_bytes(self._h))
 
+    def enable_nccl_fallback(self, id_path: str, timeout_ms: int = 600000) -> None:
+        """Join the group's NCCL communicator (every rank calls this; file rendezvous under `id_path`). From then on a
+        step that fails on a bounded peer wait still raises, and all later steps run their collectives through NCCL."""
+        self._ck(self._L.pk_qwen_enable_nccl_fallback(self._h, str(id_path).encode(), int(timeout_ms)))
+
+    def switch_to_nccl(self) -> None:
+        """Leave the peer-store path now (a rank that learnt of another rank's failure on the host)."""
+        self._ck(self._L.pk_qwen_switch_to_nccl(self._h))
+
+    @property
+    def nccl_mode(self) -> bool:
+        return bool(self._L.pk_qwen_nccl_mode(self._h))
+
+    def set_comm_timeout_us(self, us: int) -> None:
+        """Budget of every device-side wait on a peer."""
+        self._ck(self._L.pk_qwen_set_comm_timeout_us(self._h, int(us)))
+
     @property
     def prefill_gemm(self) -> str:
         """The GEMM that multiplies more than eight rows with the FP8 linears (known once the weights are in place)."""

@@ -186,6 +186,10 @@ def qk_norm_rope_append(proj: torch.Tensor, Hq: int, Hkv: int, pos: torch.Tensor
 def gqa_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor, *, nsplit: int = 4,
                gate_proj: torch.Tensor | None = None, window: int = 0, sink: int = 0, kscale: torch.Tensor | None = None,
                vscale: torch.Tensor | None = None) -> torch.Tensor:
+    """Split-context GQA attention of M query rows [M, Hq, 128] at positions `pos` over the position-indexed caches.
+    Every row is worked by the same code path, split boundaries and summation order as a single-row call at its position,
+    so the M rows of a speculative verify equal M successive decode steps bit for bit (the role of the reference's
+    exact-order verify kernels, cpp_engine/cuda/qwen_gqa_optimized.cu:567-716)."""
     M, Hq, D = q.shape
     Hkv, cap, _ = kcache.shape
     ws = torch.empty(M * Hq * nsplit * (D + 2), device=q.device, dtype=torch.float32)

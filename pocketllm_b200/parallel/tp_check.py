@@ -41,13 +41,14 @@ def main() -> int:
     first = eng.prefill(prompt)
     # the prefill logits of the whole vocabulary (every rank holds one shard), as a digest that runs of different world
     # sizes can be compared by: the eight largest entries and the norm
-    shard = eng.logits(0).float().contiguous()
+    shard = eng.logits(0).float().cuda().contiguous()
     if world > 1:
         parts = [torch.empty_like(shard) for _ in range(world)]
         dist.all_gather(parts, shard)
         full = torch.cat(parts)
     else:
         full = shard
+    full = full.cpu()
     top = full.topk(8)
     tokens = [first] + eng.decode(args.new - 1) if args.new > 1 else [first]
     logits = eng.logits(0)

@@ -516,6 +516,35 @@ def test_topk_select_matches_torch_topk(M, n, k):
     assert all_rows.shape == (M, k)
 
 
+@pytest.mark.parametrize("fp8_kv", [False, True])
+def test_verify_rows_equal_single_row_decode_bit_for_bit(fp8_kv):
+    """Exact-order verify: M draft rows through one call == M single-row calls at the same positions, bitwise, with and
+    without the output gate, for the bf16 and the FP8 cache."""
+    from pocketllm_b200 import ops
+    torch.manual_seed(11)
+    M, Hq, Hkv, D, cap, nsplit = 5, 8, 2, 128, 1024, 8
+    base = 700
+    q = torch.randn(M, Hq, D, device="cuda").to(torch.bfloat16)
+    pos = torch.arange(base, base + M, device="cuda", dtype=torch.int32)
+    proj = torch.randn(M, Hq * 2 * D + 2 * Hkv * D, device="cuda").to(torch.bfloat16)
+    if fp8_kv:
+        kc = torch.randint(0, 120, (Hkv, cap, D), device="cuda", dtype=torch.uint8)
+        vc = torch.randint(0, 120, (Hkv, cap, D), device="cuda", dtype=torch.uint8)
+        ks, vs = torch.rand(Hkv, cap, 2, device="cuda") * 0.02, torch.rand(Hkv, cap, 2, device="cuda") * 0.02
+        kw = dict(kscale=ks, vscale=vs)
+    else:
+        kc = torch.randn(Hkv, cap, D, device="cuda").to(torch.bfloat16)
+        vc = torch.randn(Hkv, cap, D, device="cuda").to(torch.bfloat16)
+        kw = {}
+    for gate in (None, proj):
+        for window, sink in ((0, 0), (256, 4)):
+            rows = ops.gqa_decode(q, kc, vc, pos, nsplit=nsplit, gate_proj=gate, window=window, sink=sink, **kw)
+            for m in range(M):
+                one = ops.gqa_decode(q[m:m + 1], kc, vc, pos[m:m + 1], nsplit=nsplit, gate_proj=None if gate is None else gate[m:m + 1],
+                                     window=window, sink=sink, **kw)
+                assert torch.equal(rows[m:m + 1], one), (m, window)
+
+
 def test_full_qk_norm_rope_append_matches_torch():
     """Whole-vector RMS (one gamma per element) + half-split rotation from tables + KV append, against plain PyTorch."""
     from pocketllm_b200 import ops

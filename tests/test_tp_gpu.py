@@ -95,6 +95,28 @@ def test_tp4_tp8_tokens_and_prefill_logits_match_tp1(tmp_path, world, prompt):
     assert one["tokens"][:3] == many["tokens"][:3] and same >= 8, (one["tokens"], many["tokens"])
 
 
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_peer_wait_timeout_switches_the_engine_to_nccl(tmp_path):
+    """Rank 0 runs a step that rank 1 never joins: bounded waits run out, the step raises, rank 0 moves to NCCL by itself,
+    rank 1 follows on the host's word, and the next request comes out of the NCCL path with the same tokens."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=4, hidden=256, inter=512, vocab=1024)
+    qh.save_checkpoint(tmp_path, cfg, qh.random_checkpoint(cfg, seed=2, sigma=0.05))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29561",
+           "-m", "pocketllm_b200.parallel.nccl_fallback_check", "--ckpt", str(tmp_path)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert r.returncode == 0, r.stderr[-3000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    r0, r1 = res["ranks"]
+    assert r0["peer_status"] == 0 and "bounded device wait ran out" in r0["error"] and "NCCL" in r0["error"]
+    assert r0["switched_by_itself"] and not r1["switched_by_itself"] and r0["nccl_mode"] and r1["nccl_mode"]
+    assert r0["status_after"] == 0 and r1["status_after"] == 0
+    assert r0["nccl_tokens"] == r1["nccl_tokens"] and r0["peer_tokens"] == r1["peer_tokens"]
+    same = sum(1 for a, b in zip(r0["peer_tokens"], r0["nccl_tokens"]) if a == b)
+    assert r0["peer_tokens"][:3] == r0["nccl_tokens"][:3] and same >= 6, (r0["peer_tokens"], r0["nccl_tokens"])
+
+
 def _nccl_smoke(world: int, tmp_path) -> list[str]:
     exe = ROOT / "pocketllm_b200" / "_C" / "pocket_engine"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
