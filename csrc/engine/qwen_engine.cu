@@ -1659,18 +1659,28 @@ void QwenEngine::spec_decode(int steps, int max_draft, int* out_host, QwenSpecSt
     forward_rows(rows.data(), k + 1, preds.data());
     int correct = 0;
     while (correct < k && preds[correct] == drafts[correct]) ++correct;
-    const int bonus = preds[correct];
+    int bonus = preds[correct];
     ++st.rounds;
     st.proposed += k;
-    st.accepted += correct;
     if (correct < k) {
-      // rows after the first mismatch have advanced the recurrent state: rewind and replay the accepted prefix
-      ++st.rollbacks;
-      st.replay_tokens += correct + 1;
-      restore(*txn_);
-      forward_rows(rows.data(), correct + 1, preds.data());
-      if (preds[correct] != bonus) throw std::runtime_error("spec_decode: the replay disagrees with the verify pass");
+      // rows after the first mismatch have advanced the recurrent state: rewind and replay the accepted prefix.
+      // The replay is what the state ends up holding, so its picks are the ones handed out. A pass over fewer rows may
+      // run other kernels than the verify pass (1-2 rows stream through the rings, 3-8 through registers) and add in a
+      // different order: on a near-tie a pick can fall the other way. Then only the prefix both passes agree on is kept
+      // and the replay runs again over it (each round is shorter, so this ends).
+      for (;;) {
+        ++st.rollbacks;
+        st.replay_tokens += correct + 1;
+        restore(*txn_);
+        forward_rows(rows.data(), correct + 1, preds.data());
+        int agree = 0;
+        while (agree < correct && preds[agree] == drafts[agree]) ++agree;
+        if (agree == correct) break;
+        correct = agree;
+      }
+      bonus = preds[correct];
     }
+    st.accepted += correct;
     // pos_ == committed + correct + 1; the target's hidden of the last committed row is row `correct` of tgt_hid_.
     // Rebind the predictor's boundary row to the bonus token (not yet consumed by the target).
     mtp_row(bonus, (const char*)tgt_hid_ + (size_t)correct * hidden_ * 2, committed + correct);

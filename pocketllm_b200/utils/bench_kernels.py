@@ -68,11 +68,15 @@ def bench_gemm(M: int, N: int, K: int, epi: int, iters: int, wfmt: str = "fp8") 
         fns = [(lambda w=w: torch.matmul(a, w.t())) for w, _ in ws]
     elif wfmt == "bf16p":
         fns = [(lambda w=w: ops.gemm_bf16(a, w, epi=epi, resid=resid)) for w, _ in ws]
+    elif wfmt in ("fp8n1", "fp8n2"):
+        # the native FP8 GEMM on the stored codes; the activation quantiser runs once, outside the timed calls
+        aq, asc = ops.quant_act_fp8(a, 1 if wfmt == "fp8n1" else 2)
+        fns = [(lambda w=w, s=s: ops.gemm_fp8(aq, asc, M, w.view(torch.uint8), s, epi=epi, resid=resid)) for w, s in ws]
     else:
         fns = [(lambda w=w, s=s: ops.gemm_umma(a, w, s, epi=epi, resid=resid)) for w, s in ws]
     us = _time(fns, iters)
     flops = 2.0 * M * N * K
-    return {"op": "torch.matmul" if wfmt == "cublas" else "gemm_bf16" if wfmt == "bf16p" else "gemm_umma", "wfmt": wfmt, "M": M, "N": N, "K": K, "epi": epi, "us": round(us, 2),
+    return {"op": "torch.matmul" if wfmt == "cublas" else "gemm_bf16" if wfmt == "bf16p" else "gemm_fp8" if wfmt.startswith("fp8n") else "gemm_umma", "wfmt": wfmt, "M": M, "N": N, "K": K, "epi": epi, "us": round(us, 2),
             "tflops": round(flops / us / 1e6, 1), "frac_of_peak": round(flops / us / 1e6 / tf, 3), "peak": f"{tf} TFLOP/s bf16 ({src})",
             "weight_gbs": round(N * K / us / 1e3, 1)}
 
@@ -97,7 +101,9 @@ def main() -> int:
     ap.add_argument("--K", type=int, default=5120)
     ap.add_argument("--epi", type=int, default=0)
     ap.add_argument("--iters", type=int, default=40)
-    ap.add_argument("--wfmt", default="fp8", choices=["fp8", "bf16", "bf16p", "cublas"], help="gemm: weight format (cublas = torch.matmul on bf16, the library baseline)")
+    ap.add_argument("--wfmt", default="fp8", choices=["fp8", "bf16", "bf16p", "fp8n1", "fp8n2", "cublas"],
+                    help="gemm: fp8 = codes decoded in shared memory, bf16p = persistent bf16 kernel, fp8n1 / fp8n2 = native FP8 math with one / two "
+                         "activation terms, cublas = torch.matmul on bf16 (the library baseline)")
     ap.add_argument("--suite", action="store_true", help="all projections of the 27B-shaped model")
     args = ap.parse_args()
     if args.suite:
