@@ -169,6 +169,10 @@ QwenEngine::QwenEngine(const QwenConfig& cfg, const QwenEngineOptions& opt) : cf
   ld_full_ = hq_l_ * 2 * kHeadDim + 2 * hkv_l_ * kHeadDim;
   ld_proj_ = std::max(ld_lin_, ld_full_);
   rows_cap_ = std::max(opt.prefill_chunk, kSmallRows);
+  {
+    const char* v = getenv("POCKET_PREFILL_ATTN");   // "simt" keeps the split-context kernel for prefill chunks
+    tc_prefill_attn_ = !opt.kv_fp8 && opt.attention_window == 0 && !(v != nullptr && std::string(v) == "simt");
+  }
   sites_per_epoch_ = 2 * cfg_.num_layers + 1;
 
   // ---- weights ----
@@ -204,6 +208,9 @@ void QwenEngine::alloc_layer(QwenLayer& L, bool full) {
       const size_t kv = (size_t)hkv_l_ * opt.max_context * kHeadDim * (opt.kv_fp8 ? 1 : 2);
       L.kcache = dalloc(kv);
       L.vcache = dalloc(kv);
+      // finite from the start: the tensor-core prefill attention reads (and masks) rows behind the last position
+      cuda_check(cudaMemset(L.kcache, 0, kv), "memset");
+      cuda_check(cudaMemset(L.vcache, 0, kv), "memset");
       kv_bytes_ += 2 * kv;
       if (opt.kv_fp8) {
         const size_t sc = (size_t)hkv_l_ * opt.max_context * 2 * sizeof(float);
@@ -1072,11 +1079,19 @@ void QwenEngine::run_chunk(int M, bool mtp) {
                                       cfg_.rotary_dim(), (float)cfg_.rope_theta, q_buf_, L.kcache, L.vcache, L.kscale, L.vscale,
                                       opt_.max_context, stream_),
             "qk_norm_rope_append");
-      check(pk_gqa_decode_kv(q_buf_, L.kcache, L.vcache, L.kscale, L.vscale, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
-                             1.f / sqrtf((float)kHeadDim), 1, opt_.attention_window, opt_.attention_sink, attn_ws_,
-                             cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
-            "gqa_prefill");
-      ++launches_;
+      if (tc_prefill_attn_ && M >= 16) {
+        // causal flash attention on the tensor cores (bf16 cache, full attention); the rows behind the chunk that its last
+        // tile reads are masked and were zeroed when the cache was allocated
+        check(pk_gqa_prefill_umma(q_buf_, L.kcache, L.vcache, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context, 1.f / sqrtf((float)kHeadDim),
+                                  cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, gemm_status_, stream_),
+              "gqa_prefill_umma");
+      } else {
+        check(pk_gqa_decode_kv(q_buf_, L.kcache, L.vcache, L.kscale, L.vscale, posd, M, hq_l_, hkv_l_, kHeadDim, opt_.max_context,
+                               1.f / sqrtf((float)kHeadDim), 1, opt_.attention_window, opt_.attention_sink, attn_ws_,
+                               cfg_.attn_output_gate ? proj_ : nullptr, ld_proj_, attn_out_, stream_),
+              "gqa_prefill");
+        ++launches_;
+      }
       gemm_out(attn_out_, hq_l_ * kHeadDim, L.o_proj, 2 * i);
     } else {
       gemm(xn_, hidden_, L.in_proj, 0, proj_, nullptr, ld_proj_);

@@ -288,6 +288,7 @@ class QwenEngine {
   bool nccl_mode_ = false;
   int kernel_world() const { return nccl_mode_ ? 1 : opt_.tp_world; }   // what the kernels see as the number of slots to add
   int gemm_mode_ = 0;
+  bool tc_prefill_attn_ = false;   // prefill chunks through pk_gqa_prefill_umma (bf16 cache, no window)
   void* act_q_ = nullptr;        // [2][rows_cap_ up to 128][K max] E4M3 terms of the GEMM input being multiplied
   float* act_scale_ = nullptr;   // [K max / 128][that row count]
   int act_rows_ = 0;

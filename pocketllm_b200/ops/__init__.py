@@ -203,6 +203,23 @@ def gqa_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos:
     return out
 
 
+def gqa_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor, *, gate_proj: torch.Tensor | None = None,
+                status: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal GQA attention of a prefill chunk on the tensor cores (tcgen05: S = Q K^T and P V per 128 x 128 tile, online
+    softmax in between): q bf16 [M, Hq, 128] at consecutive positions `pos`, bf16 caches [Hkv, cap, 128] that already hold
+    the chunk's rows. Same output as `gqa_decode` over the same rows."""
+    M, Hq, D = q.shape
+    Hkv, cap, _ = kcache.shape
+    out = torch.empty(M, Hq * D, device=q.device, dtype=torch.bfloat16)
+    if status is None:
+        status = torch.zeros(1, device=q.device, dtype=torch.int32)
+    ld = 0 if gate_proj is None else gate_proj.stride(0)
+    st = _lib.kernels().pk_gqa_prefill_umma(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(pos), c_int(M), c_int(Hq), c_int(Hkv), c_int(D), c_int(cap),
+                                            c_float(D ** -0.5), _ptr(gate_proj), c_int(ld), _ptr(out), _ptr(status), _stream())
+    _check(st, "pk_gqa_prefill_umma")
+    return out
+
+
 def full_qk_norm_rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: torch.Tensor, q_gamma: torch.Tensor, k_gamma: torch.Tensor,
                              cos_t: torch.Tensor, sin_t: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, *, n_heads: int, n_kv_heads: int,
                              rope_dim: int, eps: float = 1e-6) -> torch.Tensor:

@@ -545,6 +545,40 @@ def test_verify_rows_equal_single_row_decode_bit_for_bit(fp8_kv):
                 assert torch.equal(rows[m:m + 1], one), (m, window)
 
 
+@pytest.mark.parametrize("M,pos0,Hq,Hkv", [(128, 0, 4, 2), (200, 77, 5, 1), (512, 1000, 8, 2), (37, 300, 6, 6), (300, 0, 2, 1)])
+def test_gqa_prefill_tensor_core_attention_matches_fp32(M, pos0, Hq, Hkv):
+    """tcgen05 flash attention of a prefill chunk against fp32 softmax attention, ragged chunk lengths, chunk offsets
+    that are not multiples of the tile, with and without the output gate; and against the split-context SIMT kernel."""
+    from pocketllm_b200 import ops
+    torch.manual_seed(M + pos0)
+    D, cap = 128, 2048
+    ctx = pos0 + M
+    kc = torch.zeros(Hkv, cap, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc[:, :ctx] = torch.randn(Hkv, ctx, D, device="cuda").to(torch.bfloat16)
+    vc[:, :ctx] = torch.randn(Hkv, ctx, D, device="cuda").to(torch.bfloat16)
+    kc[:, ctx:ctx + 64] = 7.0                       # rows behind the chunk: read by the last tile, must be masked
+    vc[:, ctx:ctx + 64] = -9.0
+    q = torch.randn(M, Hq, D, device="cuda").to(torch.bfloat16)
+    proj = torch.randn(M, Hq * 2 * D + 2 * Hkv * D, device="cuda").to(torch.bfloat16)
+    pos = torch.arange(pos0, pos0 + M, device="cuda", dtype=torch.int32)
+    rep = Hq // Hkv
+    K, V = kc[:, :ctx].float().repeat_interleave(rep, 0), vc[:, :ctx].float().repeat_interleave(rep, 0)
+    sc = torch.einsum("mhd,htd->mht", q.float(), K) * D ** -0.5
+    mask = torch.arange(ctx, device="cuda")[None, None, :] > pos[:, None, None]
+    want = torch.einsum("mht,htd->mhd", torch.softmax(sc.masked_fill(mask, float("-inf")), -1), V)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    got = ops.gqa_prefill(q, kc, vc, pos, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert _rel_err(got.view(M, Hq, D), want) < 1e-2
+    gated = ops.gqa_prefill(q, kc, vc, pos, gate_proj=proj)
+    gate = proj[:, : Hq * 2 * D].float().view(M, Hq, 2 * D)[:, :, D:]
+    assert _rel_err(gated.view(M, Hq, D), want * torch.sigmoid(gate)) < 1e-2
+    simt = ops.gqa_decode(q, kc, vc, pos, nsplit=1, gate_proj=proj)
+    assert _rel_err(gated, simt) < 1e-2
+
+
 def test_full_qk_norm_rope_append_matches_torch():
     """Whole-vector RMS (one gamma per element) + half-split rotation from tables + KV append, against plain PyTorch."""
     from pocketllm_b200 import ops
