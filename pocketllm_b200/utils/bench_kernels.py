@@ -81,6 +81,21 @@ def bench_gemm(M: int, N: int, K: int, epi: int, iters: int, wfmt: str = "fp8") 
             "weight_gbs": round(N * K / us / 1e3, 1)}
 
 
+def bench_attention(M: int, ctx: int, Hq: int, Hkv: int, iters: int, simt: bool = False) -> dict:
+    """A prefill chunk of M rows ending at position ctx - 1: tcgen05 flash attention (or the split-context SIMT kernel)."""
+    hbm, tf, src = peaks()
+    D = 128
+    kc = torch.randn(Hkv, ctx + 128, D, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(Hkv, ctx + 128, D, device="cuda").to(torch.bfloat16)
+    q = torch.randn(M, Hq, D, device="cuda").to(torch.bfloat16)
+    pos = torch.arange(ctx - M, ctx, device="cuda", dtype=torch.int32)
+    fn = (lambda: ops.gqa_decode(q, kc, vc, pos, nsplit=1)) if simt else (lambda: ops.gqa_prefill(q, kc, vc, pos))
+    us = _time([fn], iters)
+    flops = 4.0 * D * Hq * sum(min(ctx - M + m + 1, ctx) for m in range(M))          # QK^T and PV over the causal extent
+    return {"op": "gqa_decode(nsplit=1)" if simt else "gqa_prefill_umma", "M": M, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "us": round(us, 2),
+            "tflops": round(flops / us / 1e6, 1), "frac_of_peak": round(flops / us / 1e6 / tf, 3), "peak": f"{tf} TFLOP/s bf16 ({src})"}
+
+
 def bench_matvec(M: int, N: int, K: int, epi: int, iters: int) -> dict:
     hbm, tf, src = peaks()
     ws = [_fp8(N, K) for _ in range(_copies(N * K))]
@@ -95,7 +110,9 @@ def bench_matvec(M: int, N: int, K: int, epi: int, iters: int) -> dict:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "matvec"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "matvec", "attention", "attention-simt"])
+    ap.add_argument("--ctx", type=int, default=8192, help="attention: position after the chunk's last row")
+    ap.add_argument("--heads", default="24,4", help="attention: query heads, KV heads")
     ap.add_argument("--M", type=int, default=512)
     ap.add_argument("--N", type=int, default=34816)
     ap.add_argument("--K", type=int, default=5120)
@@ -115,6 +132,10 @@ def main() -> int:
             r = bench_matvec(1, n, k, epi, args.iters)
             r["name"] = name
             print(json.dumps(r))
+        return 0
+    if args.op.startswith("attention"):
+        hq, hkv = (int(v) for v in args.heads.split(","))
+        print(json.dumps(bench_attention(args.M, args.ctx, hq, hkv, args.iters, simt=args.op == "attention-simt")))
         return 0
     r = bench_gemm(args.M, args.N, args.K, args.epi, args.iters, args.wfmt) if args.op == "gemm" else bench_matvec(args.M if args.op != "matvec" or args.M <= 8 else 1, args.N, args.K, args.epi, args.iters)
     print(json.dumps(r))
