@@ -29,6 +29,42 @@ enum PkStatus : int {
     }                                                       \
   } while (0)
 
+// ---- debug build (-DPK_DEBUG_BOUNDS=1): index checks that record instead of faulting ----
+// The release kernels either guard an index silently (a KV position outside the cache is not written) or trust the
+// caller (route ids). The debug library records the first bad index of every translation unit as
+// {code, index, limit, count} in a device word that the host reads with pk_debug_bounds_read(), and skips the access.
+// Codes: 101 KV-cache position, 102 routed expert id, 103 selected row.
+#if defined(PK_DEBUG_BOUNDS) && PK_DEBUG_BOUNDS && defined(__CUDACC__)
+extern "C" void pk_debug_register(int (*read)(unsigned*), int (*clear)());
+namespace pk {
+namespace dbg {
+static __device__ unsigned int g_word[4];
+__device__ __forceinline__ void record(unsigned code, long long index, long long limit) {
+  if (atomicCAS(&g_word[0], 0u, code) == 0u) {
+    g_word[1] = (unsigned)index;
+    g_word[2] = (unsigned)limit;
+  }
+  atomicAdd(&g_word[3], 1u);
+}
+static int read_tu(unsigned* out)   // internal linkage: one per translation unit, next to its own word
+ { return cudaMemcpyFromSymbol(out, g_word, sizeof(unsigned) * 4) == cudaSuccess ? 0 : 1; }
+static int clear_tu() {
+  const unsigned z[4] = {0, 0, 0, 0};
+  return cudaMemcpyToSymbol(g_word, z, sizeof z) == cudaSuccess ? 0 : 1;
+}
+struct Registrar {
+  Registrar() { pk_debug_register(&read_tu, &clear_tu); }
+};
+static Registrar g_registrar;
+}  // namespace dbg
+}  // namespace pk
+#define PK_DEBUG_RECORD(code, index, limit) pk::dbg::record((code), (long long)(index), (long long)(limit))
+#define PK_DEBUG_BUILD 1
+#else
+#define PK_DEBUG_RECORD(code, index, limit) ((void)0)
+#define PK_DEBUG_BUILD 0
+#endif
+
 PK_API void pk_set_last_cuda_error(int code);
 PK_API int pk_last_cuda_error();
 

@@ -219,6 +219,16 @@ PK_EAPI int pk_qwen_set_comm_timeout_us(void* h, unsigned us) {
   return guarded([&] { ((pk::QwenEngine*)h)->set_comm_timeout_us(us); });
 }
 
+// -1: every guard intact (or canaries off); else the index of the damaged buffer, described in pk_engine_last_error()
+PK_EAPI int pk_qwen_verify_canaries(void* h) {
+  int idx = -1;
+  std::string what;
+  if (guarded([&] { idx = ((pk::QwenEngine*)h)->verify_canaries(&what); }) != 0) return -2;
+  if (idx >= 0) g_err = what;
+  return idx;
+}
+PK_EAPI int pk_qwen_canaries_enabled(void* h) { return ((pk::QwenEngine*)h)->canaries_enabled() ? 1 : 0; }
+
 PK_EAPI int pk_qwen_decode_trace(void* h, unsigned long long* out, int cap) {
   int n = 0;
   guarded([&] { n = ((pk::QwenEngine*)h)->copy_decode_trace(out, cap); });

@@ -128,11 +128,45 @@ void QwenEngine::check(int status, const char* what) const {
 void* QwenEngine::dalloc(size_t bytes, bool weight) {
   void* p = nullptr;
   if (bytes >= (size_t(64) << 20)) require_headroom(bytes, weight ? "engine weights" : "engine buffers");
-  cuda_check(cudaMalloc(&p, std::max<size_t>(bytes, 16)), "cudaMalloc");
-  allocs_.push_back(p);
+  if (canaries_) {
+    // guard words on both sides of every buffer (POCKET_CANARY=1): verify_canaries() tells which one was written across
+    const size_t body = (std::max<size_t>(bytes, 16) + 255) / 256 * 256;
+    cuda_check(cudaMalloc(&p, body + 2 * kCanaryBytes), "cudaMalloc");
+    cuda_check(cudaMemset(p, kCanaryByte, kCanaryBytes), "canary");
+    cuda_check(cudaMemset((char*)p + kCanaryBytes + body, kCanaryByte, kCanaryBytes), "canary");
+    allocs_.push_back(p);
+    guarded_.push_back({(char*)p, body, bytes});
+    p = (char*)p + kCanaryBytes;
+  } else {
+    cuda_check(cudaMalloc(&p, std::max<size_t>(bytes, 16)), "cudaMalloc");
+    allocs_.push_back(p);
+  }
   if (weight) weight_bytes_ += bytes;
   alloc_bytes_ += bytes;
   return p;
+}
+
+// Index of the first buffer (in allocation order) whose guard words were overwritten, or -1. Synchronises the device.
+int QwenEngine::verify_canaries(std::string* what) {
+  if (!canaries_) return -1;
+  cuda_check(cudaDeviceSynchronize(), "sync");
+  std::vector<uint8_t> host(2 * kCanaryBytes);
+  for (size_t i = 0; i < guarded_.size(); ++i) {
+    const Guarded& g = guarded_[i];
+    cuda_check(cudaMemcpy(host.data(), g.base, kCanaryBytes, cudaMemcpyDeviceToHost), "canary read");
+    cuda_check(cudaMemcpy(host.data() + kCanaryBytes, g.base + kCanaryBytes + g.body, kCanaryBytes, cudaMemcpyDeviceToHost), "canary read");
+    for (size_t b = 0; b < host.size(); ++b)
+      if (host[b] != kCanaryByte) {
+        if (what) {
+          char buf[160];
+          snprintf(buf, sizeof buf, "buffer %zu (%zu bytes): guard byte %zu %s the buffer was overwritten", i, g.bytes,
+                   b < kCanaryBytes ? kCanaryBytes - b : b - kCanaryBytes, b < kCanaryBytes ? "before" : "behind");
+          *what = buf;
+        }
+        return (int)i;
+      }
+  }
+  return -1;
 }
 
 void QwenEngine::alloc_fp8(Fp8Linear& l, int N, int K) {
@@ -143,6 +177,7 @@ void QwenEngine::alloc_fp8(Fp8Linear& l, int N, int K) {
 }
 
 QwenEngine::QwenEngine(const QwenConfig& cfg, const QwenEngineOptions& opt) : cfg_(cfg), opt_(opt) {
+  if (const char* cv = getenv("POCKET_CANARY")) canaries_ = cv[0] != '\0' && cv[0] != '0';
   cfg_.validate(opt.tp_world);
   if (opt.tp_world > PK_MAX_RANKS) throw std::runtime_error("tp_world > 8");
   cuda_check(cudaSetDevice(opt.device), "cudaSetDevice");

@@ -211,6 +211,10 @@ class QwenEngine {
     set_persistent_decode(opt_.persistent_decode);   // the persistent kernel's parameter block and the graph carry the old budget
   }
   bool nccl_mode() const { return nccl_mode_; }
+  // POCKET_CANARY=1 at construction puts 256 guard bytes before and behind every device buffer of the engine; returns the
+  // index of the first buffer whose guards changed (-1: all intact, or canaries off).
+  int verify_canaries(std::string* what = nullptr);
+  bool canaries_enabled() const { return canaries_; }
   int prefill_gemm_mode() const { return gemm_mode_; }
   // Before the weights are loaded or initialised: choose the many-row GEMM (QwenEngineOptions::prefill_gemm).
   void set_prefill_gemm(int mode) {
@@ -284,6 +288,11 @@ class QwenEngine {
   size_t weight_bytes_ = 0;
   size_t alloc_bytes_ = 0;   // everything obtained through dalloc
   size_t shadow_bytes_ = 0;
+  static constexpr size_t kCanaryBytes = 256;
+  static constexpr int kCanaryByte = 0xC5;
+  struct Guarded { char* base; size_t body, bytes; };
+  std::vector<Guarded> guarded_;
+  bool canaries_ = false;
   std::shared_ptr<NcclComm> nccl_;
   bool nccl_mode_ = false;
   int kernel_world() const { return nccl_mode_ ? 1 : opt_.tp_world; }   // what the kernels see as the number of slots to add

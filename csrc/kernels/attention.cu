@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(kD) qk_norm_rope_append_kernel(const QkParams 
   sy[d] = y;
   __syncthreads();
   const int pos = p.pos[m];
+  if (!is_q && d == 0 && (pos < 0 || pos >= p.ctx_cap)) PK_DEBUG_RECORD(101, pos, p.ctx_cap);   // the row is not written (below)
   const int hr = p.rotary_dim >> 1;
   if (d < p.rotary_dim) {
     const int i = d < hr ? d : d - hr;
@@ -314,6 +315,7 @@ __global__ void __launch_bounds__(256) full_qk_norm_rope_append_kernel(const Ful
   const float rs = rsqrtf(ss / (float)n + p.eps);
   const int pos = p.pos[t], half = p.rope_dim >> 1;
   const bool in_cache = pos >= 0 && pos < p.ctx_cap;
+  if (!in_cache && threadIdx.x == 0) PK_DEBUG_RECORD(101, pos, p.ctx_cap);
   for (int i = tid; i < n; i += 256) {
     const int head = i >> 7, d = i & (kD - 1);
     float y = __bfloat162float(x[i]) * rs * gamma[i];

@@ -577,7 +577,15 @@ __global__ void __launch_bounds__(256) group_routes_kernel(const int* ids, const
   const int tid = threadIdx.x, R = T * topk;
   for (int e = tid; e <= E; e += 256) cnt[e] = 0;
   __syncthreads();
-  for (int r = tid; r < R; r += 256) atomicAdd(&cnt[ids[r]], 1);
+  for (int r = tid; r < R; r += 256) {
+#if PK_DEBUG_BUILD
+    if (ids[r] < 0 || ids[r] >= E) {
+      PK_DEBUG_RECORD(102, ids[r], E);
+      continue;
+    }
+#endif
+    atomicAdd(&cnt[ids[r]], 1);
+  }
   __syncthreads();
   if (tid == 0) {
     int run = 0;

@@ -4,6 +4,8 @@
 (`-gencode arch=compute_100a,code=sm_100a -lineinfo`) into
 
 * `pocketllm_b200/_C/libpocket_kernels.so`  -- the CUDA kernels behind `pocketllm_b200.ops`
+* `pocketllm_b200/_C/libpocket_kernels_debug.so` -- the same kernels compiled with `-DPK_DEBUG_BOUNDS=1`: bad KV positions and
+  route ids are recorded in a status word and the access is skipped (`POCKET_KERNELS_DEBUG=1` makes `ops` load it)
 * `pocketllm_b200/_C/libpocket_engine.so`   -- the native engine (links the kernels)
 * `pocketllm_b200/_C/pocket_engine`         -- the engine CLI
 * `pocketllm_b200/_C/libpocket_cpu.so`      -- host-only code (CPU MoE oracle, GGUF block codecs)
@@ -80,6 +82,8 @@ def build(verbose: bool = False, jobs: int | None = None) -> dict[str, Path]:
     cpu_flags = ["-Xcompiler", "-fopenmp", "-Xcompiler", "-mavx2", "-Xcompiler", "-mfma"]
 
     work: list[tuple[Path, list[str]]] = [(s, []) for s in kernel_srcs + engine_srcs]
+    debug_flags = ["-DPK_DEBUG_BOUNDS=1"]
+    work += [(s, debug_flags) for s in kernel_srcs]          # the same kernels with recording index checks
     work += [(s, cpu_flags) for s in cpu_srcs]
     if main_src.exists():
         work.append((main_src, []))
@@ -87,15 +91,20 @@ def build(verbose: bool = False, jobs: int | None = None) -> dict[str, Path]:
 
     jobs = jobs or max(1, (os.cpu_count() or 4))
     objs: dict[Path, Path] = {}
+    dbg_objs: dict[Path, Path] = {}
     with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
-        futs = {ex.submit(_compile_one, s, hdr, extra, verbose): s for s, extra in work}
+        futs = {ex.submit(_compile_one, s, hdr, extra, verbose): (s, extra) for s, extra in work}
         for f in cf.as_completed(futs):
-            objs[futs[f]] = f.result()
+            s, extra = futs[f]
+            (dbg_objs if extra == debug_flags else objs)[s] = f.result()
 
     arts: dict[str, Path] = {}
     kern_so = OUT / "libpocket_kernels.so"
     _link([objs[s] for s in kernel_srcs], kern_so, True, ["-lcudart"], verbose)
     arts["kernels"] = kern_so
+    dbg_so = OUT / "libpocket_kernels_debug.so"
+    _link([dbg_objs[s] for s in kernel_srcs], dbg_so, True, ["-lcudart"], verbose)
+    arts["kernels_debug"] = dbg_so
     rpath = ["-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
     eng_so = OUT / "libpocket_engine.so"
     _link([objs[s] for s in engine_srcs], eng_so, True, ["-L" + str(OUT), "-lpocket_kernels", "-lcudart", "-ldl", *rpath], verbose)

@@ -582,6 +582,14 @@ class QwenEngine:
         """Bytes of the K and V caches of every full-attention layer on this rank (scales included)."""
         return int(self._L.pk_qwen_kv_cache_bytes(self._h))
 
+    def verify_canaries(self) -> None:
+        """With POCKET_CANARY=1 in the environment when the engine was created, every device buffer has guard bytes on both
+        sides; raises EngineError naming the first buffer whose guards were overwritten."""
+        if not self._L.pk_qwen_canaries_enabled(self._h):
+            raise EngineError("canaries are off: set POCKET_CANARY=1 before creating the engine")
+        if self._L.pk_qwen_verify_canaries(self._h) != -1:
+            raise EngineError(self._L.pk_engine_last_error().decode())
+
     def enable_nccl_fallback(self, id_path: str, timeout_ms: int = 600000) -> None:
         """Join the group's NCCL communicator (every rank calls this; file rendezvous under `id_path`). From then on a
         step that fails on a bounded peer wait still raises, and all later steps run their collectives through NCCL."""

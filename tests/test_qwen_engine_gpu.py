@@ -514,3 +514,25 @@ def test_fp8_kv_cache_tracks_the_bf16_cache(tiny, persistent):
         assert _close(outs["fp8"][2], outs["bf16"][2], 5e-2)      # after six decode steps on the same tokens
     assert outs["fp8"][0][0] == outs["bf16"][0][0]
     assert outs["fp8"][3] * 32 == outs["bf16"][3] * 17            # (128 + 2 * 4) bytes per row against 256
+
+
+def test_canary_words_around_every_engine_buffer_stay_intact(tiny, monkeypatch):
+    """POCKET_CANARY=1: guard bytes before and behind every device buffer; prefill (tensor-core and streaming paths),
+    decode (persistent and per-projection) and verify rows leave all of them untouched."""
+    from pocketllm_b200.models import qwen_hybrid as qh
+    cfg, tensors, d = tiny
+    monkeypatch.setenv("POCKET_CANARY", "1")
+    torch.manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab_size, (150,)).tolist()
+    for persistent in (1, 0):
+        eng = qh.QwenEngine(cfg, max_context=512, prefill_chunk=64, persistent_decode=persistent).load(d)
+        eng.prefill(prompt)
+        toks = eng.decode(12)
+        eng.forward_rows(toks[:5])
+        eng.verify_canaries()
+        eng.close()
+    monkeypatch.delenv("POCKET_CANARY")
+    plain = qh.QwenEngine(cfg, max_context=512, prefill_chunk=64).load(d)
+    with pytest.raises(qh.EngineError, match="canaries are off"):
+        plain.verify_canaries()
+    plain.close()
