@@ -88,6 +88,8 @@ int pk_gemm_fp8(const void* Aq, int terms, int m_pad, const float* a_scale, int 
                 int K, int epi, void* C, const void* resid, int ldc, uint32_t* status, const PkPush* push, int sm_count, cudaStream_t stream);
 int pk_gqa_prefill_umma(const void* q, const void* kcache, const void* vcache, const int* pos, int M, int Hq, int Hkv, int head_dim, int ctx_cap,
                         float scale, const void* gate_proj, int ld, void* out, uint32_t* status, cudaStream_t stream);
+int pk_gemm_bf16_grouped(const void* A, int lda, const void* W, const int* seg, int n_groups, int R, int N, int K, int epi, void* C, int ldc,
+                         uint32_t* status, int sm_count, cudaStream_t stream);
 int pk_scatter_rows(const void* src, const int* slots, int n, int row_bytes, void* pool, cudaStream_t stream);
 int pk_topk_select(const float* score, const int* lengths, int M, int n, int ld, int k, int* out, cudaStream_t stream);
 int pk_gemm_bf16(const void* A, int lda, const void* W, int M, int N, int K, int epi, void* C, const void* resid, int ldc,

@@ -49,7 +49,14 @@ struct Params {
   uint32_t* flags;      // [gridDim.x] sequence number of the launch whose partial is in ws
   uint32_t seq;
   uint32_t timeout_us;
+  // grouped mode (routed experts): rows seg[g] .. seg[g + 1] of A belong to group g, whose weights are rows
+  // g * N .. (g + 1) * N of W; m-tiles never cross a group boundary on the output side (rows past the group's end are
+  // computed and not stored)
+  const int* seg;
+  int n_groups;
 };
+
+constexpr int kMaxGroups = 512;
 
 // One stretch of k-steps of one tile. A CTA's first segment may start in the middle of a tile (the CTA before it
 // owns that tile and adds this partial); its last one may end early (then this CTA owns the tile and adds the
@@ -66,9 +73,10 @@ struct WorkIter {
   int num_kb, num_tiles, streamk, tiles_m, tm;
   long long pos, end;     // stream-K: flattened (column block, k-step) of this CTA's group
   int t, stride;          // tile mode
-  __device__ WorkIter(const Params& p, int nkb) : num_kb(nkb), num_tiles(p.tiles_m * p.tiles_n), streamk(p.streamk), tiles_m(p.tiles_m) {
-    const int groups = gridDim.x / p.tiles_m, g = blockIdx.x / p.tiles_m;
-    tm = blockIdx.x % p.tiles_m;
+  __device__ WorkIter(const Params& p, int nkb, int tiles_m_) : num_kb(nkb), num_tiles(tiles_m_ * p.tiles_n), streamk(p.streamk), tiles_m(tiles_m_) {
+    const int tmd = tiles_m_ > 0 ? tiles_m_ : 1;
+    const int groups = gridDim.x / tmd, g = blockIdx.x / tmd;
+    tm = blockIdx.x % tmd;
     const long long total = (long long)p.tiles_n * num_kb;
     pos = streamk ? total * g / groups : 0;
     end = streamk ? total * (g + 1) / groups : 0;
@@ -105,7 +113,29 @@ struct __align__(1024) Smem {
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   uint32_t part_done;     // epilogue warps that have stored their share of this CTA's partial
+  int mt_prefix[kMaxGroups + 1];   // grouped mode: m-tiles before each group
 };
+
+// Where tile `tile` reads and writes: column block, first A row, row offset into W, rows that are real.
+__device__ __forceinline__ void tile_coords(const Params& p, const Smem& sm, int tile, int tiles_m, int& tn, int& a_row, int& w_off, int& rows) {
+  tn = tile / tiles_m;
+  const int g = tile - tn * tiles_m;
+  if (p.seg == nullptr) {
+    a_row = g * BM;
+    w_off = 0;
+    rows = p.M - a_row;
+    return;
+  }
+  int lo = 0, hi = p.n_groups;   // mt_prefix[lo] <= g < mt_prefix[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (sm.mt_prefix[mid] <= g) lo = mid;
+    else hi = mid;
+  }
+  a_row = __ldg(p.seg + lo) + (g - sm.mt_prefix[lo]) * BM;
+  rows = __ldg(p.seg + lo + 1) - a_row;
+  w_off = lo * p.N;
+}
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -129,7 +159,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = p.K / BK;
-  const int num_tiles = p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -143,6 +172,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     sm.abort_flag = 0;
     sm.part_done = 0;
     mbar_fence_init();
+    if (p.seg != nullptr) {
+      int run = 0;
+      for (int g = 0; g < p.n_groups; ++g) {
+        sm.mt_prefix[g] = run;
+        run += (p.seg[g + 1] - p.seg[g] + BM - 1) / BM;
+      }
+      sm.mt_prefix[p.n_groups] = run;
+    }
   }
   if (warp == 1) {
     tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -152,6 +189,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
+  const int tiles_m = p.seg != nullptr ? sm.mt_prefix[p.n_groups] : p.tiles_m;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -159,17 +197,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_w);
       uint32_t it = 0, issued = 0;
-      WorkIter work(p, num_kb);
+      WorkIter work(p, num_kb, tiles_m);
       Seg sg;
       while (!sm.abort_flag && work.next(sg)) {
-        const int tm = sg.tile % p.tiles_m, tn = sg.tile / p.tiles_m;
+        int tn, a_row, w_off, rows;
+        tile_coords(p, sm, sg.tile, tiles_m, tn, a_row, w_off, rows);
         int r0, r1;
         weight_rows(p, tn, r0, r1);
+        r0 += w_off;
+        r1 += w_off;
         for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const int s = it % kStages;
           if (!mbar_wait(&sm.empty[s], ((it / kStages) & 1) ^ 1, &sm.abort_flag, p.status, 21)) break;
           mbar_arrive_expect_tx(&sm.full[s], kABytes + kBBytes);
-          tma_load_2d(sm.a[s], &tmap_a, &sm.full[s], kb * BK, tm * BM);
+          tma_load_2d(sm.a[s], &tmap_a, &sm.full[s], kb * BK, a_row);
           tma_load_2d(sm.b[s], &tmap_w, &sm.full[s], kb * BK, r0);
           tma_load_2d(sm.b[s] + kBBytes / 2, &tmap_w, &sm.full[s], kb * BK, r1);
           issued = it + 1;
@@ -190,7 +231,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       constexpr uint32_t idesc = umma_idesc(1, 1, BM, BN);
       uint32_t it = 0;
       int local = 0;
-      WorkIter work(p, num_kb);
+      WorkIter work(p, num_kb, tiles_m);
       Seg sg;
       for (; !sm.abort_flag && work.next(sg); ++local) {
         const int buf = local & 1;
@@ -217,16 +258,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int ch = (warp - 2) >> 2;         // which half of the tile's columns
     int local = 0;
-    WorkIter work(p, num_kb);
+    WorkIter work(p, num_kb, tiles_m);
     Seg sg;
     for (; work.next(sg); ++local) {
       const int buf = local & 1;
       const uint32_t use = (uint32_t)local >> 1;
-      const int tm = sg.tile % p.tiles_m, tn = sg.tile / p.tiles_m;
+      int tn, a_row, w_off, rows;
+      tile_coords(p, sm, sg.tile, tiles_m, tn, a_row, w_off, rows);
       if (!mbar_wait(&sm.acc_full[buf], use & 1, &sm.abort_flag, p.status, 24)) break;
       tc_fence_after();
-      const int m = tm * BM + q * 32 + lane;
-      const bool row_ok = m < p.M;
+      const int m = a_row + q * 32 + lane;
+      const bool row_ok = q * 32 + lane < rows;
       const uint32_t lane_addr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(q * 32) << 16);
       const int row_in_tile = q * 32 + lane;
       if (sg.kb0 > 0) {
@@ -472,6 +514,52 @@ bool encode_bf16_2d(EncodeTiledFn encode, CUtensorMap* map, const void* base, ui
 }
 
 }  // namespace
+
+// Grouped form for routed experts: A [R, K] bf16 rows sorted by group, seg [n_groups + 1] (device) the first row of every
+// group, W [n_groups * N, K] bf16 (group g's [N, K] matrix at row g * N). C rows are A's rows. Epilogues 0 (bf16),
+// 1 (SwiGLU: every group's matrix holds N / 2 gate rows then N / 2 up rows) and 3 (fp32). One persistent launch walks
+// every (group, row tile, column block) that has rows; the tile list is derived from seg on the device, so the host
+// never reads the routing.
+PK_API int pk_gemm_bf16_grouped(const void* A, int lda, const void* W, const int* seg, int n_groups, int R, int N, int K, int epi, void* C, int ldc,
+                                uint32_t* status, int sm_count, cudaStream_t stream) {
+  if (R < 1 || N < 1 || K < BK || (K % BK) != 0 || seg == nullptr || n_groups < 1 || n_groups > kMaxGroups) return PK_ERR_BAD_ARG;
+  if (((uintptr_t)A & 15) != 0 || ((size_t)lda * 2) % 16 != 0 || ((uintptr_t)W & 15) != 0) return PK_ERR_BAD_ARG;
+  if (epi != EPI_BF16 && epi != EPI_SWIGLU && epi != EPI_F32) return PK_ERR_BAD_ARG;
+  if (epi == EPI_SWIGLU && ((N & 1) != 0)) return PK_ERR_BAD_ARG;
+  if (epi == EPI_SWIGLU && ((N >> 1) % 128) != 0) return PK_ERR_UNSUPPORTED;
+  if (epi != EPI_SWIGLU && (N % 128) != 0) return PK_ERR_UNSUPPORTED;      // a column block must not reach into the next group's rows
+  if ((ldc & 7) != 0 && epi != EPI_F32) return PK_ERR_BAD_ARG;
+  EncodeTiledFn encode = encode_fn();
+  if (encode == nullptr) return PK_ERR_UNSUPPORTED;
+  CUtensorMap tmap_a, tmap_w;
+  if (!encode_bf16_2d(encode, &tmap_a, A, (uint64_t)K, (uint64_t)R, (uint64_t)lda * 2, BK, BM)) return PK_ERR_CUDA;
+  if (!encode_bf16_2d(encode, &tmap_w, W, (uint64_t)K, (uint64_t)n_groups * N, (uint64_t)K * 2, BK, 128)) return PK_ERR_CUDA;
+  Params p{};
+  p.M = R;
+  p.N = N;
+  p.K = K;
+  p.epi = epi;
+  p.C = (pk::bf16*)C;
+  p.Cf = (float*)C;
+  p.ldc = ldc;
+  p.tiles_m = 0;
+  p.tiles_n = epi == EPI_SWIGLU ? ((N >> 1) + 127) / 128 : (N + BN - 1) / BN;
+  p.status = status;
+  p.seg = seg;
+  p.n_groups = n_groups;
+  const size_t smem = sizeof(Smem) + 1024;
+  static PkDeviceOnce once;
+  if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      pk_set_last_cuda_error((int)cudaGetLastError());
+      return PK_ERR_CUDA;
+    }
+    once_guard.done();
+  }
+  gemm_bf16_kernel<<<sm_count > 0 ? sm_count : 148, kThreads, smem, stream>>>(tmap_a, tmap_w, p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
 
 // A [M, K] bf16 (row stride lda elements), W [N, K] bf16 row-major, K a multiple of 64. Epilogues as in pk_gemm_umma;
 // for SwiGLU (epi 1) W holds N/2 gate rows then N/2 up rows and N/2 must be a multiple of 128 (else PK_ERR_UNSUPPORTED).

@@ -471,6 +471,21 @@ __global__ void moe_reduce_routes_kernel(const float* __restrict__ ybuf, const i
   y[(size_t)t * H + n] = acc;
 }
 
+// The same reduce with the route weight applied here (ybuf holds unweighted expert outputs, e.g. from the grouped GEMM).
+__global__ void moe_reduce_routes_weighted_kernel(const float* __restrict__ ybuf, const float* __restrict__ route_weight,
+                                                  const int* __restrict__ route_pos, const int* __restrict__ seg_start, int topk, int H,
+                                                  int expert_offset, int local_experts, float* y) {
+  const int t = blockIdx.y, n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= H) return;
+  const int lo = seg_start[expert_offset], hi = seg_start[expert_offset + local_experts];
+  float acc = y[(size_t)t * H + n];
+  for (int k = 0; k < topk; ++k) {
+    const int pos = route_pos[t * topk + k];
+    if (pos >= lo && pos < hi) acc = fmaf(route_weight[pos], ybuf[(size_t)pos * H + n], acc);
+  }
+  y[(size_t)t * H + n] = acc;
+}
+
 __global__ void invert_routes_kernel(const int* __restrict__ route_src, int R, int* route_pos) {
   const int pos = blockIdx.x * blockDim.x + threadIdx.x;
   if (pos < R) route_pos[route_src[pos]] = pos;
@@ -615,11 +630,16 @@ __global__ void __launch_bounds__(256) group_routes_kernel(const int* ids, const
 // Quantised embedding: decode selected rows to bf16 (one warp per 256 weights).
 __global__ void __launch_bounds__(256) gguf_dequant_rows_kernel(const uint8_t* W, int type, const int* rows, int nrows,
                                                                 int K, int row_offset, int table_rows, bf16* out) {
-  const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int src = (rows ? rows[r] : r) - row_offset;
-  const bool mine = src >= 0 && src < table_rows;
+  // one warp per 256-weight block, walking (row, block) units with a grid stride; a lane's eight weights leave as one
+  // 16-byte store
+  const int lane = threadIdx.x & 31;
+  const int nblk = K >> 8;
   const size_t rb = row_bytes(type, K);
-  for (int blk = warp; blk < (K >> 8); blk += 8) {
+  const long long units = (long long)nrows * nblk;
+  for (long long u = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * 8) {
+    const int r = (int)(u / nblk), blk = (int)(u - (long long)r * nblk);
+    const int src = (rows ? rows[r] : r) - row_offset;
+    const bool mine = src >= 0 && src < table_rows;
     float w[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) w[i] = 0.f;
@@ -640,8 +660,13 @@ __global__ void __launch_bounds__(256) gguf_dequant_rows_kernel(const uint8_t* W
         default: decode8<T_BF16>(b, lane, w); break;
       }
     }
+    uint32_t o[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) out[(size_t)r * K + (blk << 8) + (lane << 3) + i] = __float2bfloat16(w[i]);
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 pr = __floats2bfloat162_rn(w[2 * i], w[2 * i + 1]);
+      o[i] = *reinterpret_cast<const uint32_t*>(&pr);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)r * K + (blk << 8) + (lane << 3)) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -743,6 +768,21 @@ PK_API int pk_group_routes(const int* ids, const float* weights, int T, int topk
 
 // Routed experts of one rank: experts [expert_offset, expert_offset + local_experts) live in
 // W13 / W2. y (fp32 [T, H]) must be zeroed by the caller; hbuf holds R * I floats.
+// y[t] += sum over the token's routes (in route order) of route_weight * ybuf[route]; routes of experts outside
+// [expert_offset, expert_offset + local_experts) are skipped. route_pos: int scratch [T * topk].
+PK_API int pk_moe_reduce_routes(const float* ybuf, const float* route_weight, const int* route_src, const int* seg_start, int T, int topk, int H,
+                                int expert_offset, int local_experts, int* route_pos, float* y, cudaStream_t stream) {
+  if (ybuf == nullptr || route_weight == nullptr || route_src == nullptr || seg_start == nullptr || route_pos == nullptr || y == nullptr || T < 1 || topk < 1)
+    return PK_ERR_BAD_ARG;
+  const int R = T * topk;
+  invert_routes_kernel<<<(R + 255) / 256, 256, 0, stream>>>(route_src, R, route_pos);
+  PK_CHECK_LAUNCH();
+  moe_reduce_routes_weighted_kernel<<<dim3((H + 255) / 256, T), 256, 0, stream>>>(ybuf, route_weight, route_pos, seg_start, topk, H, expert_offset,
+                                                                                  local_experts, y);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
 static int moe_forward_impl(const void* W13, const void* W2, int type13, int type2, int E, int H, int I, const void* x,
                             const int* seg_start, const int* route_token, const float* route_weight, float* hbuf, float* y,
                             float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream,
@@ -821,8 +861,12 @@ static int moe_forward_impl(const void* W13, const void* W2, int type13, int typ
 PK_API int pk_gguf_dequant_rows(const void* W, int type, const int* rows, int nrows, int K, int row_offset,
                                 int table_rows, void* out, cudaStream_t stream) {
   if (type < 0 || type > T_LAST || (K & 255) != 0 || nrows < 1) return PK_ERR_BAD_ARG;
-  gguf_dequant_rows_kernel<<<nrows, 256, 0, stream>>>((const uint8_t*)W, type, rows, nrows, K, row_offset, table_rows,
-                                                     (pk::bf16*)out);
+  if (((uintptr_t)out & 15) != 0) return PK_ERR_BAD_ARG;
+  const long long units = (long long)nrows * (K >> 8);
+  const long long want = (units + 7) / 8;
+  const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
+  gguf_dequant_rows_kernel<<<grid, 256, 0, stream>>>((const uint8_t*)W, type, rows, nrows, K, row_offset, table_rows,
+                                                    (pk::bf16*)out);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }

@@ -370,10 +370,9 @@ class GLMDSAModel:
         ids, wt = go.router_topk(xb, self.w[b + "ffn_gate_inp.weight"], c.top_k, bias=self.w[b + "exp_probs_b.bias"],
                                  score_func="sigmoid", norm_topk=c.expert_weights_norm, route_scale=c.expert_weights_scale)
         routes = go.group_routes(ids, wt, c.n_experts)
-        seg, tok, rw = routes
-        y = go.gguf_moe_forward(xb, self.raw[b + "w13"], self.raw[b + "ffn_down_exps.weight"], self.types[b + "ffn_gate_exps.weight"],
-                                self.types[b + "ffn_down_exps.weight"], c.n_experts, c.expert_inter, seg, tok, rw,
-                                expert_offset=self.e_start, local_experts=self.e_local, routes=routes)
+        y = go.moe_forward(xb, self.raw[b + "w13"], self.raw[b + "ffn_down_exps.weight"], self.types[b + "ffn_gate_exps.weight"],
+                           self.types[b + "ffn_down_exps.weight"], c.n_experts, c.expert_inter, routes,
+                           expert_offset=self.e_start, local_experts=self.e_local)
         if self.world > 1:
             self._combine(y)
         return y

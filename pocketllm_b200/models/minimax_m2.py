@@ -369,7 +369,8 @@ class MiniMaxM2Model:
             # whole-vector RMS with per-element gamma, rotation at `pos`, k / v appended to the caches: one kernel
             q = ops.full_qk_norm_rope_append(q, k, v, pos, L["q_norm"], L["k_norm"], self.rope_cos, self.rope_sin, L["kc"], L["vc"],
                                              n_heads=c.n_heads, n_kv_heads=c.n_kv_heads, rope_dim=c.rope_dim, eps=c.norm_eps)
-            o = ops.gqa_decode(q, L["kc"], L["vc"], pos, nsplit=1 if T > 8 else 8)
+            # prefill chunks (consecutive positions) through the tcgen05 flash kernel, decode steps through the split kernel
+            o = ops.gqa_prefill(q, L["kc"], L["vc"], pos) if T >= 16 else ops.gqa_decode(q, L["kc"], L["vc"], pos, nsplit=1 if T > 8 else 8)
             att = go.gguf_linear(o, L["o"], self.types[b + "attn_output.weight"], c.dim, epi=2)
             h = (h + att).to(torch.bfloat16)                     # bf16 + fp32 promotes to fp32: the sum is rounded once
             xn = ops.rmsnorm(h, L["ffn_norm"], mode=2, eps=c.norm_eps)
@@ -381,9 +382,9 @@ class MiniMaxM2Model:
                 ids = ((pos.view(-1, 1) * kk + torch.arange(kk, device=self.device, dtype=torch.int32).view(1, -1) + 37 * i) % c.n_experts).to(torch.int32).contiguous()
                 wt = torch.full_like(wt, 1.0 / kk)
             routes = go.group_routes(ids, wt, c.n_experts)
-            seg, tok, rw = routes
-            y = go.gguf_moe_forward(xn, L["w13"], L["w2"], self.types[b + "ffn_gate_exps.weight"], self.types[b + "ffn_down_exps.weight"],
-                                    c.n_experts, c.expert_inter, seg, tok, rw, expert_offset=self.e_start, local_experts=self.e_local, routes=routes)
+            # many routes per expert (prefill): grouped tensor-core GEMMs; else the per-route streaming kernels
+            y = go.moe_forward(xn, L["w13"], L["w2"], self.types[b + "ffn_gate_exps.weight"], self.types[b + "ffn_down_exps.weight"],
+                               c.n_experts, c.expert_inter, routes, expert_offset=self.e_start, local_experts=self.e_local)
             if self.world > 1:
                 self._combine(y)
             h = (h + y).to(torch.bfloat16)

@@ -129,6 +129,69 @@ def gguf_moe_forward(x: torch.Tensor, w13_raw: torch.Tensor, w2_raw: torch.Tenso
     return out
 
 
+_GROUPED_SCRATCH: dict = {}
+
+
+def gguf_moe_forward_grouped(x: torch.Tensor, w13_raw: torch.Tensor, w2_raw: torch.Tensor, type13: str, type2: str, E: int, inter: int,
+                             routes: "Routes", *, expert_offset: int = 0, local_experts: int | None = None,
+                             out: torch.Tensor | None = None) -> torch.Tensor:
+    """Routed experts of this rank on the tensor cores, for steps with many routes (prefill): the rank's experts are decoded
+    to bf16 once per call into a scratch that is reused across layers, token rows are gathered in expert order, and two
+    grouped tcgen05 GEMMs (gate|up with the SwiGLU epilogue, then down) run one persistent launch each over every
+    (expert, row tile, column block) that has rows; the tile list comes from the route segments on the device. The
+    per-token sum runs in route order (bitwise reproducible). Same result as `gguf_moe_forward` up to bf16 rounding of the
+    hidden activations."""
+    from . import EPI_F32, EPI_SWIGLU
+    seg, tok, rw = routes
+    T, H = x.shape
+    R = tok.numel()
+    local = E if local_experts is None else local_experts
+    dev = x.device
+    if out is None:
+        out = torch.zeros(T, H, device=dev, dtype=torch.float32)
+    key = (dev.index, local, H, inter)
+    sc = _GROUPED_SCRATCH.get(key)
+    if sc is None:
+        sc = (torch.empty(local * 2 * inter, H, device=dev, dtype=torch.bfloat16), torch.empty(local * H, inter, device=dev, dtype=torch.bfloat16))
+        _GROUPED_SCRATCH.clear()          # one shape at a time: the scratch is as large as the layer's experts in bf16
+        _GROUPED_SCRATCH[key] = sc
+    w13, w2 = sc
+    K = _lib.kernels()
+    _check(K.pk_gguf_dequant_rows(_ptr(w13_raw), c_int(DEVICE_TYPE[type13]), c_void_p(0), c_int(local * 2 * inter), c_int(H), c_int(0),
+                                  c_int(local * 2 * inter), _ptr(w13), _stream()), "pk_gguf_dequant_rows(w13)")
+    _check(K.pk_gguf_dequant_rows(_ptr(w2_raw), c_int(DEVICE_TYPE[type2]), c_void_p(0), c_int(local * H), c_int(inter), c_int(0), c_int(local * H),
+                                  _ptr(w2), _stream()), "pk_gguf_dequant_rows(w2)")
+    xg = x.index_select(0, tok.long())                                   # [R, H] rows in expert order
+    hbuf = torch.empty(R, inter, device=dev, dtype=torch.bfloat16)
+    ybuf = torch.empty(R, H, device=dev, dtype=torch.float32)
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    segl = seg[expert_offset:]
+    _check(K.pk_gemm_bf16_grouped(_ptr(xg), c_int(H), _ptr(w13), _ptr(segl), c_int(local), c_int(R), c_int(2 * inter), c_int(H), c_int(EPI_SWIGLU),
+                                  _ptr(hbuf), c_int(inter), _ptr(status), c_int(_sm_count()), _stream()), "pk_gemm_bf16_grouped(w13)")
+    _check(K.pk_gemm_bf16_grouped(_ptr(hbuf), c_int(inter), _ptr(w2), _ptr(segl), c_int(local), c_int(R), c_int(H), c_int(inter), c_int(EPI_F32),
+                                  _ptr(ybuf), c_int(H), _ptr(status), c_int(_sm_count()), _stream()), "pk_gemm_bf16_grouped(w2)")
+    pos = torch.empty(R, device=dev, dtype=torch.int32)
+    _check(K.pk_moe_reduce_routes(_ptr(ybuf), _ptr(rw), _ptr(routes.src), _ptr(seg), c_int(T), c_int(routes.topk), c_int(H), c_int(expert_offset),
+                                  c_int(local), _ptr(pos), _ptr(out), _stream()), "pk_moe_reduce_routes")
+    return out
+
+
+GROUPED_MIN_ROUTES_PER_EXPERT = 4     # below this the decode of every local expert costs more than the route kernels' per-route decode
+
+
+def moe_forward(x: torch.Tensor, w13_raw: torch.Tensor, w2_raw: torch.Tensor, type13: str, type2: str, E: int, inter: int, routes: "Routes", *,
+                limit: float = 0.0, expert_offset: int = 0, local_experts: int | None = None) -> torch.Tensor:
+    """Routed experts of this rank, fp32 [T, H]: the grouped tensor-core path for steps with many routes per expert
+    (prefill), the per-route streaming kernels otherwise (decode, clamped SwiGLU)."""
+    seg, tok, rw = routes
+    local = E if local_experts is None else local_experts
+    H = x.shape[1]
+    if (limit == 0.0 and tok.numel() >= GROUPED_MIN_ROUTES_PER_EXPERT * local and inter % 128 == 0 and H % 128 == 0 and local <= 512):
+        return gguf_moe_forward_grouped(x, w13_raw, w2_raw, type13, type2, E, inter, routes, expert_offset=expert_offset, local_experts=local)
+    return gguf_moe_forward(x, w13_raw, w2_raw, type13, type2, E, inter, seg, tok, rw, limit=limit, expert_offset=expert_offset,
+                            local_experts=local, routes=routes)
+
+
 def gguf_dequant_rows(w_raw: torch.Tensor, type_name: str, K: int, rows: torch.Tensor | None = None, *, nrows: int | None = None,
                       row_offset: int = 0) -> torch.Tensor:
     """Decode rows of a quantised table to bf16 (quantised embedding gather, or a whole

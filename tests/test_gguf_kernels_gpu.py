@@ -125,6 +125,37 @@ def test_moe_forward_matches_dequantised_reference(t13, t2, T):
     assert _rel(lo + hi, ref) < 3e-3
 
 
+@pytest.mark.parametrize("T,E,topk", [(300, 8, 3), (64, 16, 2), (700, 4, 2)])
+def test_grouped_tensor_core_experts_match_the_route_kernels(T, E, topk):
+    """Prefill-sized steps: experts decoded once to bf16, rows gathered in expert order, two grouped tcgen05 GEMMs (SwiGLU,
+    then down) over the (expert, row tile, column block) list built from the route segments on the device; ragged groups
+    (some empty, some longer than one tile), expert-parallel halves, bitwise reproducible."""
+    import numpy as np
+    from pocketllm_b200.formats import gguf_quants as gq
+    from pocketllm_b200.ops import gguf_ops as go
+    torch.manual_seed(T)
+    H, I = 512, 256
+    rng = np.random.default_rng(T)
+    w13 = torch.from_numpy(gq.quantize((rng.standard_normal((E * 2 * I, H)) * 0.05).astype(np.float32), "q4_k")).cuda().view(-1)
+    w2 = torch.from_numpy(gq.quantize((rng.standard_normal((E * H, I)) * 0.05).astype(np.float32), "iq2_xxs")).cuda().view(-1)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E - 1)[:topk] for _ in range(T)]).int().cuda()      # the last expert gets no route
+    ids[: T // 2] = torch.where(ids[: T // 2] == 1, torch.zeros_like(ids[: T // 2]), ids[: T // 2]) if topk == 1 else ids[: T // 2]
+    wts = torch.rand(T, topk, device="cuda")
+    routes = go.group_routes(ids, wts, E)
+    seg, tok, rw = routes
+    want = go.gguf_moe_forward(x, w13, w2, "q4_k", "iq2_xxs", E, I, seg, tok, rw, routes=routes)
+    got = [go.gguf_moe_forward_grouped(x, w13, w2, "q4_k", "iq2_xxs", E, I, routes) for _ in range(2)]
+    assert torch.equal(got[0], got[1])
+    assert _rel(got[0], want) < 6e-3                       # hidden activations pass through bf16 between the two GEMMs
+    half = E // 2
+    lo = go.gguf_moe_forward_grouped(x, w13[: w13.numel() // 2], w2[: w2.numel() // 2], "q4_k", "iq2_xxs", E, I, routes, expert_offset=0,
+                                     local_experts=half)
+    hi = go.gguf_moe_forward_grouped(x, w13[w13.numel() // 2:], w2[w2.numel() // 2:], "q4_k", "iq2_xxs", E, I, routes, expert_offset=half,
+                                     local_experts=half)
+    assert _rel(lo + hi, got[0]) < 1e-5
+
+
 def test_moe_forward_fixed_order_reduce_is_bitwise_reproducible():
     """Per-route outputs summed in route order: two runs agree bit for bit and match the atomic path closely."""
     import numpy as np
