@@ -53,6 +53,9 @@ def run(args) -> dict:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if getattr(args, "model", "qwen27b") == "minimax-m2":
+        # the reference's GGUF runtime loads a checkpoint file; a 60 GB MiniMax-M2 GGUF cannot be produced offline within the run
+        return _unavailable("MiniMax-M2: the reference's loader needs a full GGUF checkpoint file (about 60 GB), which cannot be made offline here") if rank == 0 else {}
     if not BINARY.exists():
         return _unavailable("baseline/_ref/cpp_build/dsv4_cpp_engine is not built (offline cmake build of the reference missing)") if rank == 0 else {}
     import torch
