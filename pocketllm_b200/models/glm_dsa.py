@@ -301,7 +301,11 @@ class GLMDSAModel:
     """GPU runtime: projections and experts on raw blocks, MLA core and indexer in PyTorch."""
 
     def __init__(self, path: str | Path, *, device: str = "cuda", rank: int = 0, world: int = 1, max_context: int = 4096,
-                 layers: int | None = None, group=None, dsa_topk: int | None = None):
+                 layers: int | None = None, group=None, dsa_topk: int | None = None, routed_tp: bool = False):
+        """`routed_tp`: with several ranks, every rank keeps ALL experts but only its slice of the expert intermediate
+        dimension (gate / up rows and the matching block columns of down, slices aligned to the 256-weight block), and the
+        ranks' partial outputs are summed; the default splits whole experts over the ranks. (Reference: GLM_ROUTED_TP,
+        src/models/glm_dsa/architecture.py:528-877, tests/test_glm_dsa_tp_routed.py.)"""
         from ..ops import gguf_ops as go
         self.go = go
         self.bundle = gguf.GGUFBundle(path)
@@ -316,6 +320,13 @@ class GLMDSAModel:
             raise ValueError("expert count must divide by the world size")
         self.device, self.rank, self.world, self.group = torch.device(device), rank, world, group
         self.e_local, self.e_start = c.n_experts // world, rank * (c.n_experts // world)
+        self.routed_tp = bool(routed_tp) and world > 1
+        self.inter_local = c.expert_inter
+        if self.routed_tp:
+            if c.expert_inter % (256 * world):
+                raise ValueError("routed TP needs the expert intermediate size to be a multiple of 256 * world (block-aligned slices)")
+            self.e_local, self.e_start = c.n_experts, 0
+            self.inter_local = c.expert_inter // world
         self._combiner = None
         self.types = {n: t.type_name for n, t in self.bundle.tensors.items()}
         self.shapes = {n: t.shape for n, t in self.bundle.tensors.items()}
@@ -329,7 +340,13 @@ class GLMDSAModel:
             if t.type_name == "f32":
                 self.w[n] = W.f32(n).to(self.device)
             elif "_exps." in n:
-                blk = self.bundle.blocks(n)[self.e_start:self.e_start + self.e_local]
+                blk = self.bundle.blocks(n)[self.e_start:self.e_start + self.e_local]       # [experts, rows, blocks per row, block bytes]
+                if self.routed_tp:
+                    il = self.inter_local
+                    if "ffn_down_exps" in n:                                             # K slice: whole 256-weight blocks of every row
+                        blk = blk[:, :, rank * il // 256:(rank + 1) * il // 256]
+                    else:                                                                # gate / up: this rank's rows
+                        blk = blk[:, rank * il:(rank + 1) * il]
                 self.raw[n] = torch.from_numpy(np.ascontiguousarray(blk).reshape(self.e_local, -1)).to(self.device)
             else:
                 self.raw[n] = torch.from_numpy(np.ascontiguousarray(self.bundle.blocks(n)).reshape(-1)).to(self.device)
@@ -371,7 +388,7 @@ class GLMDSAModel:
                                  score_func="sigmoid", norm_topk=c.expert_weights_norm, route_scale=c.expert_weights_scale)
         routes = go.group_routes(ids, wt, c.n_experts)
         y = go.moe_forward(xb, self.raw[b + "w13"], self.raw[b + "ffn_down_exps.weight"], self.types[b + "ffn_gate_exps.weight"],
-                           self.types[b + "ffn_down_exps.weight"], c.n_experts, c.expert_inter, routes,
+                           self.types[b + "ffn_down_exps.weight"], c.n_experts, self.inter_local, routes,
                            expert_offset=self.e_start, local_experts=self.e_local)
         if self.world > 1:
             self._combine(y)

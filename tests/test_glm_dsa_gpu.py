@@ -41,3 +41,28 @@ def test_indexer_selects_topk_causal():
     t = 2
     allowed = score[t, : int(pos[t]) + 1]
     assert set(m[t].nonzero().flatten().tolist()) == set(torch.topk(allowed, 4).indices.tolist())
+
+
+@pytest.mark.parametrize("mode", ["routed_tp", "expert_parallel"])
+def test_two_rank_expert_sharding_adds_up_to_one_rank(tmp_path, mode):
+    """Routed TP (every rank holds all experts but a block-aligned slice of the intermediate dimension) and expert
+    parallelism (whole experts per rank): the ranks' partial MoE outputs add up to the one-rank output. The two ranks are
+    two runtime objects in one process; the cross-rank sum is done here."""
+    import dataclasses
+    from pocketllm_b200.models import glm_dsa as glm
+    cfg = dataclasses.replace(glm.GLMDSAConfig.tiny(), expert_inter=512)
+    path = tmp_path / "glm.gguf"
+    glm.write_random_gguf(path, cfg, seed=3)
+    one = glm.GLMDSAModel(path, max_context=64)
+    ranks = [glm.GLMDSAModel(path, max_context=64, rank=r, world=2, routed_tp=mode == "routed_tp") for r in range(2)]
+    for m in ranks:
+        m._combine = lambda y: y                                     # the sum over ranks happens below
+        assert m.routed_tp == (mode == "routed_tp")
+        assert m.inter_local == (256 if mode == "routed_tp" else 512) and m.e_local == (cfg.n_experts if mode == "routed_tp" else cfg.n_experts // 2)
+    torch.manual_seed(0)
+    layer = cfg.leading_dense_layers
+    for T in (3, 70):                                                # per-route kernels and the grouped tensor-core path
+        x = torch.randn(T, cfg.dim, device="cuda")
+        want = one.moe(layer, x)
+        got = ranks[0].moe(layer, x) + ranks[1].moe(layer, x)
+        assert ((got - want).norm() / want.norm()).item() < (2e-5 if T == 3 else 6e-3)
