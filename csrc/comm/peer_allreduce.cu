@@ -34,7 +34,26 @@ struct ParParams {
   const float* in;
   float* out;
   size_t n;
+  // MoE combine (in == nullptr): the value pushed for element (t, h) is this rank's weighted sum of the token's routes
+  // through its local experts, taken from the per-route outputs in route order; the kernel is then dispatch (stores into
+  // every rank), signal, wait and sum in one launch, with the per-token reduce as its producer.
+  const float* ybuf;        // [routes, H] per-route expert outputs, expert-sorted
+  const float* route_w;     // [routes] weight of each route (expert-sorted)
+  const int* route_pos;     // [T * topk] position of route (t, k) in the expert-sorted order
+  const int* seg;           // [E + 1]
+  int topk, H, expert_offset, local_experts;
 };
+
+// This rank's contribution to element i = t * H + h of the MoE output.
+__device__ __forceinline__ float moe_value(const ParParams& p, size_t i, int lo, int hi) {
+  const int t = (int)(i / (size_t)p.H), h = (int)(i - (size_t)t * p.H);
+  float acc = 0.f;
+  for (int k = 0; k < p.topk; ++k) {
+    const int pos = p.route_pos[t * p.topk + k];
+    if (pos >= lo && pos < hi) acc = fmaf(p.route_w[pos], p.ybuf[(size_t)pos * p.H + h], acc);
+  }
+  return acc;
+}
 
 __device__ __forceinline__ float* slot(float* arena, size_t capacity, int world, int parity, int r) {
   return arena + ((size_t)parity * world + r) * capacity;
@@ -56,13 +75,22 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ParParams p) 
   const size_t n4 = p.n >> 2;
 
   // 1. push
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-    const float4 v = reinterpret_cast<const float4*>(p.in)[i];
-    for (int r = 0; r < p.world; ++r) reinterpret_cast<float4*>(slot(p.slot_base[r], p.capacity, p.world, parity, p.rank))[i] = v;
-  }
-  for (size_t i = (n4 << 2) + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += (size_t)gridDim.x * blockDim.x) {
-    const float v = p.in[i];
-    for (int r = 0; r < p.world; ++r) slot(p.slot_base[r], p.capacity, p.world, parity, p.rank)[i] = v;
+  if (p.in != nullptr) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+      const float4 v = reinterpret_cast<const float4*>(p.in)[i];
+      for (int r = 0; r < p.world; ++r) reinterpret_cast<float4*>(slot(p.slot_base[r], p.capacity, p.world, parity, p.rank))[i] = v;
+    }
+    for (size_t i = (n4 << 2) + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += (size_t)gridDim.x * blockDim.x) {
+      const float v = p.in[i];
+      for (int r = 0; r < p.world; ++r) slot(p.slot_base[r], p.capacity, p.world, parity, p.rank)[i] = v;
+    }
+  } else {
+    // H is a multiple of 4, so a float4 never straddles two tokens
+    const int lo = p.seg[p.expert_offset], hi = p.seg[p.expert_offset + p.local_experts];
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+      const float4 v = make_float4(moe_value(p, 4 * i, lo, hi), moe_value(p, 4 * i + 1, lo, hi), moe_value(p, 4 * i + 2, lo, hi), moe_value(p, 4 * i + 3, lo, hi));
+      for (int r = 0; r < p.world; ++r) reinterpret_cast<float4*>(slot(p.slot_base[r], p.capacity, p.world, parity, p.rank))[i] = v;
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -182,4 +210,43 @@ PK_API unsigned pk_par_status(void* arena, int world, size_t capacity, int clear
   if (cudaMemcpy(&v, status, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return 0xffffffffu;
   if (clear && v != 0u) cudaMemset(status, 0, 4);
   return v;
+}
+
+// MoE combine over peer memory: out [T, H] fp32 = sum over ranks of each rank's weighted per-token sum of its local
+// experts' route outputs. ybuf [routes, H] and route_w [routes] are expert-sorted, route_pos [T * topk] maps route (t, k)
+// to its sorted position, seg [E + 1] are the expert segments; this rank's experts are [expert_offset,
+// expert_offset + local_experts). One launch: per-token reduce -> stores into every rank -> signal -> wait -> sum.
+PK_API int pk_par_moe_combine(void* const* arenas, int world, int rank, size_t capacity, const float* ybuf, const float* route_w, const int* route_pos,
+                              const int* seg, int expert_offset, int local_experts, int T, int topk, int H, float* out, uint32_t timeout_us,
+                              int sm_count, cudaStream_t stream) {
+  if (world < 1 || world > PK_MAX_RANKS || rank < 0 || rank >= world || T < 1 || topk < 1 || H < 4 || (H & 3) != 0) return PK_ERR_BAD_ARG;
+  if (ybuf == nullptr || route_w == nullptr || route_pos == nullptr || seg == nullptr || out == nullptr) return PK_ERR_BAD_ARG;
+  const size_t n = (size_t)T * H;
+  if (n > capacity || ((uintptr_t)out & 15) != 0) return PK_ERR_BAD_ARG;
+  ParParams p{};
+  for (int r = 0; r < world; ++r) {
+    if (arenas[r] == nullptr) return PK_ERR_BAD_ARG;
+    p.slot_base[r] = (float*)arenas[r];
+  }
+  p.world = world;
+  p.rank = rank;
+  p.capacity = capacity;
+  p.timeout_us = timeout_us;
+  p.in = nullptr;
+  p.out = out;
+  p.n = n;
+  p.ybuf = ybuf;
+  p.route_w = route_w;
+  p.route_pos = route_pos;
+  p.seg = seg;
+  p.topk = topk;
+  p.H = H;
+  p.expert_offset = expert_offset;
+  p.local_experts = local_experts;
+  const size_t want = (n / 4 + 255) / 256;
+  const int cap = sm_count > 0 ? sm_count : 148;
+  const int grid = (int)(want < (size_t)cap ? (want ? want : 1) : (size_t)cap);
+  peer_allreduce_kernel<<<grid, 256, 0, stream>>>(p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
 }

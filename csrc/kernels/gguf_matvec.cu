@@ -783,6 +783,14 @@ PK_API int pk_moe_reduce_routes(const float* ybuf, const float* route_weight, co
   return PK_OK;
 }
 
+// route_pos[route_src[pos]] = pos: where route (t, k) sits in the expert-sorted order.
+PK_API int pk_invert_routes(const int* route_src, int R, int* route_pos, cudaStream_t stream) {
+  if (route_src == nullptr || route_pos == nullptr || R < 1) return PK_ERR_BAD_ARG;
+  invert_routes_kernel<<<(R + 255) / 256, 256, 0, stream>>>(route_src, R, route_pos);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
 static int moe_forward_impl(const void* W13, const void* W2, int type13, int type2, int E, int H, int I, const void* x,
                             const int* seg_start, const int* route_token, const float* route_weight, float* hbuf, float* y,
                             float limit, int expert_offset, int local_experts, int sm_count, float* ybuf, cudaStream_t stream,

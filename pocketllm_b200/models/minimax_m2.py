@@ -325,6 +325,16 @@ class MiniMaxM2Model:
             self._combiner = ExpertCombine(self.world, self.group)
         return self._combiner(y)
 
+    def _peer(self):
+        """The peer-memory context of the expert-parallel group (None on one rank or after the peer path was dropped): the
+        grouped expert path finishes with its combine kernel instead of a separate all-reduce."""
+        if self.world == 1:
+            return None
+        if self._combiner is None:
+            from ..parallel.combine import ExpertCombine
+            self._combiner = ExpertCombine(self.world, self.group)
+        return self._combiner.peer
+
     def reset(self) -> None:
         self.pos = 0
 
@@ -384,8 +394,8 @@ class MiniMaxM2Model:
             routes = go.group_routes(ids, wt, c.n_experts)
             # many routes per expert (prefill): grouped tensor-core GEMMs; else the per-route streaming kernels
             y = go.moe_forward(xn, L["w13"], L["w2"], self.types[b + "ffn_gate_exps.weight"], self.types[b + "ffn_down_exps.weight"],
-                               c.n_experts, c.expert_inter, routes, expert_offset=self.e_start, local_experts=self.e_local)
-            if self.world > 1:
+                               c.n_experts, c.expert_inter, routes, expert_offset=self.e_start, local_experts=self.e_local, peer=self._peer())
+            if self.world > 1 and not routes.combined:
                 self._combine(y)
             h = (h + y).to(torch.bfloat16)
         return go.gguf_linear(h[-1:], self.head, self.types["output.weight"], c.vocab_size, gamma=self.final_norm, eps=c.norm_eps, epi=2)[0]

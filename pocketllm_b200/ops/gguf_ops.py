@@ -134,13 +134,14 @@ _GROUPED_SCRATCH: dict = {}
 
 def gguf_moe_forward_grouped(x: torch.Tensor, w13_raw: torch.Tensor, w2_raw: torch.Tensor, type13: str, type2: str, E: int, inter: int,
                              routes: "Routes", *, expert_offset: int = 0, local_experts: int | None = None,
-                             out: torch.Tensor | None = None) -> torch.Tensor:
+                             out: torch.Tensor | None = None, peer=None) -> torch.Tensor:
     """Routed experts of this rank on the tensor cores, for steps with many routes (prefill): the rank's experts are decoded
     to bf16 once per call into a scratch that is reused across layers, token rows are gathered in expert order, and two
     grouped tcgen05 GEMMs (gate|up with the SwiGLU epilogue, then down) run one persistent launch each over every
     (expert, row tile, column block) that has rows; the tile list comes from the route segments on the device. The
     per-token sum runs in route order (bitwise reproducible). Same result as `gguf_moe_forward` up to bf16 rounding of the
-    hidden activations."""
+    hidden activations. With `peer` (a `PeerAllReduce` of the expert-parallel group) whose arena holds T * H floats the result
+    is already summed over the ranks (`routes.combined` is set): the combine runs as peer stores out of the reduce."""
     from . import EPI_F32, EPI_SWIGLU
     seg, tok, rw = routes
     T, H = x.shape
@@ -171,6 +172,14 @@ def gguf_moe_forward_grouped(x: torch.Tensor, w13_raw: torch.Tensor, w2_raw: tor
     _check(K.pk_gemm_bf16_grouped(_ptr(hbuf), c_int(inter), _ptr(w2), _ptr(segl), c_int(local), c_int(R), c_int(H), c_int(inter), c_int(EPI_F32),
                                   _ptr(ybuf), c_int(H), _ptr(status), c_int(_sm_count()), _stream()), "pk_gemm_bf16_grouped(w2)")
     pos = torch.empty(R, device=dev, dtype=torch.int32)
+    routes.combined = False
+    if peer is not None and T * H <= peer.capacity:
+        # several ranks: the per-token reduce is the producer of the combine kernel, which stores this rank's sums into every
+        # rank's arena, signals, waits (bounded) and adds the ranks' slots: `out` is the sum over all ranks' experts
+        _check(K.pk_invert_routes(_ptr(routes.src), c_int(R), _ptr(pos), _stream()), "pk_invert_routes")
+        peer.moe_combine(ybuf, rw, pos, seg, expert_offset, local, T, routes.topk, out)
+        routes.combined = True
+        return out
     _check(K.pk_moe_reduce_routes(_ptr(ybuf), _ptr(rw), _ptr(routes.src), _ptr(seg), c_int(T), c_int(routes.topk), c_int(H), c_int(expert_offset),
                                   c_int(local), _ptr(pos), _ptr(out), _stream()), "pk_moe_reduce_routes")
     return out
@@ -180,14 +189,16 @@ GROUPED_MIN_ROUTES_PER_EXPERT = 4     # below this the decode of every local exp
 
 
 def moe_forward(x: torch.Tensor, w13_raw: torch.Tensor, w2_raw: torch.Tensor, type13: str, type2: str, E: int, inter: int, routes: "Routes", *,
-                limit: float = 0.0, expert_offset: int = 0, local_experts: int | None = None) -> torch.Tensor:
+                limit: float = 0.0, expert_offset: int = 0, local_experts: int | None = None, peer=None) -> torch.Tensor:
     """Routed experts of this rank, fp32 [T, H]: the grouped tensor-core path for steps with many routes per expert
     (prefill), the per-route streaming kernels otherwise (decode, clamped SwiGLU)."""
     seg, tok, rw = routes
     local = E if local_experts is None else local_experts
     H = x.shape[1]
     if (limit == 0.0 and tok.numel() >= GROUPED_MIN_ROUTES_PER_EXPERT * local and inter % 128 == 0 and H % 128 == 0 and local <= 512):
-        return gguf_moe_forward_grouped(x, w13_raw, w2_raw, type13, type2, E, inter, routes, expert_offset=expert_offset, local_experts=local)
+        return gguf_moe_forward_grouped(x, w13_raw, w2_raw, type13, type2, E, inter, routes, expert_offset=expert_offset, local_experts=local,
+                                        peer=peer)
+    routes.combined = False
     return gguf_moe_forward(x, w13_raw, w2_raw, type13, type2, E, inter, seg, tok, rw, limit=limit, expert_offset=expert_offset,
                             local_experts=local, routes=routes)
 

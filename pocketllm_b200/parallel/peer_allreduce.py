@@ -68,6 +68,23 @@ class PeerAllReduce:
             raise RuntimeError(f"pk_par_allreduce: status {st}")
         return out
 
+    def moe_combine(self, ybuf: torch.Tensor, route_w: torch.Tensor, route_pos: torch.Tensor, seg: torch.Tensor, expert_offset: int,
+                    local_experts: int, T: int, topk: int, out: torch.Tensor) -> torch.Tensor:
+        """MoE combine as peer stores from the per-token reduce: out [T, H] fp32 = sum over ranks of every rank's weighted sum
+        of the token's routes through its own experts (ybuf [routes, H] per-route outputs and route_w [routes] in expert
+        order, route_pos [T * topk] the sorted position of route (t, k)). One launch per rank: reduce, stores into every
+        rank, signal, bounded wait, sum."""
+        H = ybuf.shape[1]
+        if T * H > self.capacity or out.dtype != torch.float32 or not out.is_contiguous():
+            raise ValueError("moe_combine: payload exceeds the arena or the output is not contiguous fp32")
+        st = self.K.pk_par_moe_combine(self._ptrs, c_int(self.world), c_int(self.rank), c_size_t(self.capacity), c_void_p(ybuf.data_ptr()),
+                                       c_void_p(route_w.data_ptr()), c_void_p(route_pos.data_ptr()), c_void_p(seg.data_ptr()), c_int(expert_offset),
+                                       c_int(local_experts), c_int(T), c_int(topk), c_int(H), c_void_p(out.data_ptr()), c_uint(self.timeout_us),
+                                       c_int(self._sm), c_void_p(torch.cuda.current_stream().cuda_stream))
+        if st != 0:
+            raise RuntimeError(f"pk_par_moe_combine: status {st}")
+        return out
+
     def status(self, clear: bool = False) -> int:
         return int(self.K.pk_par_status(c_void_p(self.arena), c_int(self.world), c_size_t(self.capacity), c_int(int(clear))))
 

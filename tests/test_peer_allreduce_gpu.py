@@ -70,3 +70,26 @@ def test_dsv4_expert_parallel_matches_single_gpu(tmp_path):
     assert nccl["combine_calls"]["peer"] == 0
     assert one["tokens"] == two["tokens"] == nccl["tokens"]
     assert abs(one["logit_checksum"] - two["logit_checksum"]) < 1e-3
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_moe_combine_as_peer_stores_from_the_reduce(world):
+    """Expert-parallel grouped experts ending in the combine kernel (reduce -> peer stores -> signal -> wait -> sum): every
+    rank gets the one-rank result; world 1 exercises the kernel through a single arena."""
+    import json, os, subprocess, sys
+    from pathlib import Path
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(root))
+    if world == 1:
+        cmd = [sys.executable, "-m", "pocketllm_b200.parallel.moe_combine_check"]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+               "--master-port", "29571", "-m", "pocketllm_b200.parallel.moe_combine_check"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=str(root))
+    assert r.returncode == 0, r.stderr[-3000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert res["world"] == world and len(res["ranks"]) == world
+    for rk in res["ranks"]:
+        assert rk["combined"] and rk["status"] == 0 and rk["rel_err"] < 1e-5
