@@ -66,3 +66,16 @@ def test_yarn_frequencies():
     assert torch.allclose(plain, 1.0 / (10000.0 ** (torch.arange(0, 64, 2).float() / 64)))
     y = fm.yarn_inv_freqs(64, 10000.0, 16.0, 4096, 32, 1)
     assert torch.allclose(y[0], plain[0]) and torch.allclose(y[-1], plain[-1] / 16) and (y <= plain + 1e-12).all()
+
+
+def test_retrieval_attention_chain_scores_selects_swaps_and_attends(capsys):
+    """The whole long-context chain (three scorer layers -> ensemble -> top-k -> KV swap -> sparse attention over window +
+    slots) gives exactly the attention over a fully resident cache, while only the slots live on the device."""
+    import json
+    from pocketllm_b200.cli import flashmemory_kv_swap as demo
+    assert demo.main(["--context", "8192", "--gpu-chunks", "320", "--keep", "256", "--steps", "6", "--heads", "16", "--hidden", "1024",
+                      "--q-lora-rank", "256", "--check"]) == 0
+    res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert res["max_abs_diff_vs_resident"] == 0.0
+    assert res["kv_swap"]["misses"] >= 256 and res["kv_swap"]["hits"] + res["kv_swap"]["misses"] == 6 * 256
+    assert res["kv_swap"]["device_mib"] < res["resident_cache_mib"]
