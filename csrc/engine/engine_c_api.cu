@@ -229,6 +229,15 @@ PK_EAPI int pk_qwen_verify_canaries(void* h) {
 }
 PK_EAPI int pk_qwen_canaries_enabled(void* h) { return ((pk::QwenEngine*)h)->canaries_enabled() ? 1 : 0; }
 
+PK_EAPI int pk_qwen_set_tap_layers(void* h, const int* layers, int n) {
+  return guarded([&] { ((pk::QwenEngine*)h)->set_tap_layers(layers, n); });
+}
+PK_EAPI int pk_qwen_tap_rows(void* h) { return ((pk::QwenEngine*)h)->tap_rows(); }
+// rows [first_row, first_row + rows) of the last forward's taps, [rows, taps * hidden] bf16, into device memory
+PK_EAPI int pk_qwen_copy_taps(void* h, void* dst_device, int first_row, int rows) {
+  return guarded([&] { ((pk::QwenEngine*)h)->copy_taps(dst_device, first_row, rows); });
+}
+
 PK_EAPI int pk_qwen_decode_trace(void* h, unsigned long long* out, int cap) {
   int n = 0;
   guarded([&] { n = ((pk::QwenEngine*)h)->copy_decode_trace(out, cap); });

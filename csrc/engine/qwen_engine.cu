@@ -814,6 +814,37 @@ void QwenEngine::switch_to_nccl() {
   clear_comm_status();
 }
 
+void QwenEngine::set_tap_layers(const int* layers, int n) {
+  if (opt_.tp_world > 1) throw std::runtime_error("target taps are captured on one rank only");
+  for (int i = 0; i < n; ++i)
+    if (layers[i] < 0 || layers[i] >= cfg_.num_layers) throw std::runtime_error("tap layer outside the model");
+  cuda_check(cudaStreamSynchronize(stream_), "sync");
+  tap_layers_.assign(layers, layers + n);
+  taps_ = nullptr;
+  if (n > 0) taps_ = dalloc((size_t)rows_cap_ * n * hidden_ * 2);
+  tap_rows_ = 0;
+  set_persistent_decode(n > 0 ? 0 : opt_.persistent_decode);   // per-projection decode while taps are on; drops a captured graph
+}
+
+void QwenEngine::capture_tap(int layer, const void* rows, int M) {
+  for (size_t s = 0; s < tap_layers_.size(); ++s)
+    if (tap_layers_[s] == layer) {
+      const size_t pitch = tap_layers_.size() * (size_t)hidden_ * 2;
+      cuda_check(cudaMemcpy2DAsync((char*)taps_ + s * (size_t)hidden_ * 2, pitch, rows, (size_t)hidden_ * 2, (size_t)hidden_ * 2, (size_t)M,
+                                   cudaMemcpyDeviceToDevice, stream_),
+                 "tap copy");
+      ++launches_;
+    }
+}
+
+void QwenEngine::copy_taps(void* dst_device, int first_row, int rows) {
+  if (tap_layers_.empty()) throw std::runtime_error("no tap layers set");
+  if (first_row < 0 || rows < 1 || first_row + rows > tap_rows_) throw std::runtime_error("copy_taps: rows outside the last forward");
+  const size_t pitch = tap_layers_.size() * (size_t)hidden_ * 2;
+  cuda_check(cudaMemcpyAsync(dst_device, (char*)taps_ + (size_t)first_row * pitch, (size_t)rows * pitch, cudaMemcpyDeviceToDevice, stream_), "taps");
+  cuda_check(cudaStreamSynchronize(stream_), "taps");
+}
+
 void QwenEngine::copy_logits(float* out_host, int row) {
   cuda_check(cudaStreamSynchronize(stream_), "sync");
   cuda_check(cudaMemcpy(out_host, logits_ + (size_t)row * vocab_l_, (size_t)vocab_l_ * sizeof(float), cudaMemcpyDeviceToHost), "logits");
@@ -880,6 +911,7 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
   const int W = opt_.tp_world;
   const int* posd = mtp ? mtp_pos_dev_ : pos_dev_;
   const int n_layers = mtp ? 1 : cfg_.num_layers;
+  if (!mtp) tap_rows_ = tap_layers_.empty() ? 0 : M;
   check(pk_bump_epoch((uint32_t*)((char*)arena_ + off_epoch_), stream_), "epoch");
   if (mtp) {
     check(pk_mtp_concat_norm(mtp_tok_dev_, M, embed_, mtp_in_, hidden_, mtp_norm_e_, mtp_norm_h_, eps, mtp_cat_, stream_), "mtp_concat_norm");
@@ -901,6 +933,8 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
                     kernel_world(), hout, gamma, 1, eps, pending >= 0 && !nccl_mode_ ? &wt : nullptr, epi, y, ldy, push, sm_count_, stream_),
           "matvec(consume)");
     if (pending >= 0) cur_ ^= 1;
+    // the summed residual stream now holds the output of the layer whose down projection was pending
+    if (!mtp && !tap_layers_.empty() && pending >= 0 && (pending & 1)) capture_tap(pending >> 1, hidden_buf_[cur_], M);
     pending = -1;
   };
   auto produce = [&](const Fp8Linear& w, const void* x, int site) {
@@ -944,6 +978,7 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
     check(pk_rmsnorm(hidden_buf_[cur_], parts, kernel_world(), M, hidden_, hidden_buf_[cur_], mtp ? mtp_norm_ : final_norm_, 1, eps, y,
                      nccl_mode_ ? nullptr : &wt, stream_),
           "final norm");
+    if (!mtp && !tap_layers_.empty() && (pending & 1)) capture_tap(pending >> 1, hidden_buf_[cur_], M);
     pending = -1;
     const bool all = !mtp && (all_logits || M == 1);
     const int rows = all ? M : 1;
@@ -968,6 +1003,7 @@ void QwenEngine::run_small(int M, bool all_logits, bool mtp) {
     check(pk_rmsnorm(hidden_buf_[cur_], parts, kernel_world(), M, hidden_, hidden_buf_[cur_], final_norm_, 1, eps, nullptr,
                      nccl_mode_ ? nullptr : &wt, stream_),
           "fold");
+    if (!tap_layers_.empty() && (pending & 1)) capture_tap(pending >> 1, hidden_buf_[cur_], M);
     pending = -1;
     const char* last = (const char*)hidden_buf_[cur_] + (size_t)(M - 1) * hidden_ * 2;
     check(pk_matvec(nullptr, nullptr, lm_head_, 0, vocab_l_, hidden_, 1, last, nullptr, 0, nullptr, final_norm_, 1, eps,
@@ -1026,6 +1062,7 @@ void QwenEngine::run_chunk(int M, bool mtp) {
   const int* posd = mtp ? mtp_pos_dev_ : pos_dev_;
   const int n_layers = mtp ? 1 : cfg_.num_layers;
   void* hid = hidden_buf_[cur_];
+  if (!mtp) tap_rows_ = tap_layers_.empty() ? 0 : M;
   if (W > 1) check(pk_bump_epoch((uint32_t*)((char*)arena_ + off_epoch_), stream_), "epoch");
   if (mtp) {
     check(pk_mtp_concat_norm(mtp_tok_dev_, M, embed_, mtp_in_, hidden_, mtp_norm_e_, mtp_norm_h_, eps, mtp_cat_, stream_), "mtp_concat_norm");
@@ -1148,6 +1185,7 @@ void QwenEngine::run_chunk(int M, bool mtp) {
     norm(L.post_norm, xn_);
     gemm(xn_, hidden_, L.gate_up, 1, mlp_h_, nullptr, inter_l_);
     gemm_out(mlp_h_, inter_l_, L.down, 2 * i + 1);
+    if (!mtp && W == 1 && !tap_layers_.empty()) capture_tap(i, hid, M);   // one rank: the epilogue added the residual in place
   }
   if (opt_.mtp && !mtp) {
     // every normalised row feeds the predictor; the last one also gives the logits

@@ -215,6 +215,14 @@ class QwenEngine {
   // index of the first buffer whose guards changed (-1: all intact, or canaries off).
   int verify_canaries(std::string* what = nullptr);
   bool canaries_enabled() const { return canaries_; }
+  // Target taps for an external block drafter: the residual stream after each of the given layers, for every row of the
+  // last forward (prefill chunk, verify rows, decode step), concatenated per row in the order given: [rows, n * hidden]
+  // bf16. One rank only. Decode steps run one launch per projection while taps are on (the persistent kernel keeps the
+  // residual stream in shared memory). Reference: cpp_engine/src/qwen_engine.cpp:1555-1726 (tap capture for DSpark).
+  void set_tap_layers(const int* layers, int n);
+  int tap_count() const { return (int)tap_layers_.size(); }
+  int tap_rows() const { return tap_rows_; }                       // rows written by the last forward
+  void copy_taps(void* dst_device, int first_row, int rows);       // [rows, n * hidden] bf16 into device memory
   int prefill_gemm_mode() const { return gemm_mode_; }
   // Before the weights are loaded or initialised: choose the many-row GEMM (QwenEngineOptions::prefill_gemm).
   void set_prefill_gemm(int mode) {
@@ -297,6 +305,10 @@ class QwenEngine {
   bool nccl_mode_ = false;
   int kernel_world() const { return nccl_mode_ ? 1 : opt_.tp_world; }   // what the kernels see as the number of slots to add
   int gemm_mode_ = 0;
+  std::vector<int> tap_layers_;
+  void* taps_ = nullptr;           // [rows_cap_, taps * hidden] bf16
+  int tap_rows_ = 0;
+  void capture_tap(int layer, const void* rows, int M);   // rows [M, hidden] bf16 = the residual stream after `layer`
   bool tc_prefill_attn_ = false;   // prefill chunks through pk_gqa_prefill_umma (bf16 cache, no window)
   void* act_q_ = nullptr;        // [2][rows_cap_ up to 128][K max] E4M3 terms of the GEMM input being multiplied
   float* act_scale_ = nullptr;   // [K max / 128][that row count]

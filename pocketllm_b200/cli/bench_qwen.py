@@ -1,10 +1,11 @@
 """Benchmark drivers of the hybrid decoder beyond the headline run of `bench.py`: long contexts, the multi-token
 predictor, and prefix reuse across requests. Roles of the reference's scripts/bench_qwen_long_context.py,
-bench_qwen_mtp.py and bench_qwen_prefix_cache.py. One JSON object is printed (and written with --out).
+bench_qwen_mtp.py, bench_qwen_dspark.py and bench_qwen_prefix_cache.py. One JSON object is printed (and written with --out).
 
     python -m pocketllm_b200.cli.bench_qwen long-context --gpus 1 --prompt-lens 4096,8192,32768 --decode-len 64
     python -m pocketllm_b200.cli.bench_qwen mtp --gpus 1 --prompt-len 512 --decode-len 256 --max-draft 4
     python -m pocketllm_b200.cli.bench_qwen prefix-cache --gpus 1 --prompt-len 4096 --turns 4
+    python -m pocketllm_b200.cli.bench_qwen dspark --gpus 1 --prompt-len 512 --decode-len 64 --max-draft 7
 
 With --gpus N > 1 the driver starts itself under `torch.distributed.run` (one rank per GPU, 127.0.0.1 rendezvous);
 every rank generates the same tokens or the run fails. Weights are random (N(0, 0.02) quantised to FP8) in the
@@ -120,6 +121,67 @@ def run_mtp(args) -> dict:
     return res if rank == 0 else {}
 
 
+def run_dspark(args) -> dict:
+    """Block drafter on one GPU: the published drafter shape (5 layers, block 7) with random weights next to the target. Random
+    drafts are almost never right, so the row of interest is the cost model: drafting time, verify time for k + 1 rows and the
+    plain step time give the acceptance at which drafting breaks even; `perfect_drafts` replays the known continuation."""
+    import time
+    import torch
+    from ..models import qwen_dspark as qd
+    from ..models.qwen_dspark_runtime import QwenDSparkRuntime, QwenDSparkSpeculator
+    if args.gpus != 1:
+        raise SystemExit("the block drafter's taps are captured on one rank")
+    cfg, eng, rank, world = _engine(args, max_context=args.prompt_len + args.decode_len + 64)
+    tiny = args.model == "tiny"
+    dcfg = qd.QwenDSparkConfig(hidden_size=cfg.hidden_size, intermediate_size=256 if tiny else 17408, num_hidden_layers=2 if tiny else 5,
+                               num_attention_heads=2 if tiny else 40, num_key_value_heads=1 if tiny else 8, head_dim=128, vocab_size=cfg.vocab_size,
+                               block_size=7, markov_rank=64 if tiny else 256, mask_token_id=cfg.vocab_size - 1,
+                               target_layer_ids=tuple(sorted({min(i, cfg.num_hidden_layers - 1) for i in ((1, 3) if tiny else (4, 16, 28, 40, 52))})))
+    W = {}
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for name, shape in qd.tensor_names(dcfg):                       # made on the device: the 5-layer drafter is 3.6 G parameters
+        if name.endswith("norm.weight"):
+            W[name] = torch.ones(*shape, device="cuda", dtype=torch.bfloat16)
+        else:
+            W[name] = (torch.randn(*shape, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    embed = (torch.randn(cfg.vocab_size, cfg.hidden_size, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    drafter = QwenDSparkRuntime(dcfg, W, embed, embed, max_context=args.prompt_len + args.decode_len + 64)
+    prompt = _prompt(cfg, args.prompt_len, 7)
+    eng.reset()
+    first = eng.prefill(prompt)
+    plain = [first] + eng.decode(args.decode_len)
+    plain_ms = eng.timings()["decode_ms"]
+    spec = QwenDSparkSpeculator(eng, drafter, max_draft=args.max_draft)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    got = spec.generate(prompt, args.decode_len + 1, chunk=args.prefill_chunk)
+    torch.cuda.synchronize()
+    spec_s = time.perf_counter() - t0
+    # cost of the parts, timed on the device
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        drafter.propose(plain[-1])
+    e1.record()
+    torch.cuda.synchronize()
+    propose_ms = e0.elapsed_time(e1) / 5
+    eng.reset()
+    eng.prefill(prompt)
+    t0 = time.perf_counter()
+    eng.forward_rows(plain[: args.max_draft + 1])
+    verify_ms = (time.perf_counter() - t0) * 1e3
+    step_ms = plain_ms / args.decode_len
+    res = {"bench": "qwen_dspark", "n_gpus": 1, "prompt_tokens": args.prompt_len, "decode_tokens": args.decode_len, "block_size": dcfg.block_size,
+           "max_draft": args.max_draft, "drafter_layers": dcfg.num_hidden_layers, "plain_decode_tok_s": round(1e3 / step_ms, 2),
+           "plain_step_ms": round(step_ms, 3), "propose_ms": round(propose_ms, 3), f"verify_{args.max_draft + 1}_rows_ms": round(verify_ms, 3),
+           "break_even_tokens_per_round": round((propose_ms + verify_ms) / step_ms, 2),
+           "random_drafter": {"tokens_equal_plain": got == plain, "rounds": spec.stats["rounds"], "proposed": spec.stats["proposed"],
+                              "accepted": spec.stats["accepted"], "rollbacks": spec.stats["rollbacks"],
+                              "wall_tok_s_incl_prefill": round(args.decode_len / spec_s, 2)}}
+    eng.close()
+    return res
+
+
 def run_prefix_cache(args) -> dict:
     ctx = args.prompt_len + args.turns * (args.turn_tokens + args.decode_len) + 64
     cfg, eng, rank, world = _engine(args, max_context=ctx)
@@ -148,7 +210,7 @@ def run_prefix_cache(args) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("bench", choices=["long-context", "mtp", "prefix-cache"])
+    ap.add_argument("bench", choices=["long-context", "mtp", "prefix-cache", "dspark"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--model", default="qwen27b", choices=["qwen27b", "tiny"])
     ap.add_argument("--ckpt", default="")
@@ -174,7 +236,7 @@ def main(argv=None) -> int:
         return subprocess.run(cmd, env=dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "0"))).returncode
     if args.gpus != world:
         ap.error(f"--gpus {args.gpus} but WORLD_SIZE is {world}")
-    res = {"long-context": run_long_context, "mtp": run_mtp, "prefix-cache": run_prefix_cache}[args.bench](args)
+    res = {"long-context": run_long_context, "mtp": run_mtp, "prefix-cache": run_prefix_cache, "dspark": run_dspark}[args.bench](args)
     if res:
         text = json.dumps(res)
         print(text, flush=True)

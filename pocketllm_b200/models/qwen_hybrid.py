@@ -294,6 +294,7 @@ class ReferenceModel:
         """Feed one token; returns fp32 logits [vocab]."""
         r = self.r
         h = self.embed[token].clone()
+        layer_out = []
         for L, st in zip(self.layers, self.state):
             x = r(self._rms(h, L["in_norm"]))
             att = self._linear_attn(L, st, x) if L["kind"] == "linear_attention" else self._full_attn(L, st, x, self.pos)
@@ -301,6 +302,8 @@ class ReferenceModel:
             x = r(self._rms(h, L["post_norm"]))
             mid = r(torch.nn.functional.silu(L["gate"] @ x) * (L["up"] @ x))
             h = r(h + L["down"] @ mid)
+            layer_out.append(h)
+        self.layer_hidden = layer_out        # residual stream after every layer (the taps of an external drafter)
         self.pos += 1
         self.last_hidden = r(self._rms(h, self.norm))
         return self.lm_head @ self.last_hidden
@@ -408,6 +411,7 @@ class QwenEngine:
         self.cfg = cfg
         text = cfg if isinstance(cfg, str) else cfg.to_json()
         self.tp_rank, self.tp_world, self.device = tp_rank, tp_world, device
+        self.prefill_chunk = prefill_chunk
         self.mtp = bool(mtp)
         self.kv_cache_dtype = kv_cache_dtype
         self._h = L.pk_qwen_create_ex2(text.encode(), tp_rank, tp_world, device, max_context, prefill_chunk,
@@ -581,6 +585,21 @@ class QwenEngine:
     def kv_cache_bytes(self) -> int:
         """Bytes of the K and V caches of every full-attention layer on this rank (scales included)."""
         return int(self._L.pk_qwen_kv_cache_bytes(self._h))
+
+    def set_tap_layers(self, layers) -> None:
+        """Capture the residual stream after each of `layers` for every row of every following forward (one rank only;
+        decode steps then run one launch per projection). `taps()` reads them."""
+        arr = (ctypes.c_int * len(layers))(*[int(v) for v in layers])
+        self._ck(self._L.pk_qwen_set_tap_layers(self._h, arr, len(layers)))
+        self._n_taps = len(layers)
+
+    def taps(self, first_row: int = 0, rows: int | None = None) -> torch.Tensor:
+        """bf16 [rows, taps * hidden] on the device: the taps of the last forward (prefill chunk, verify rows or decode step)."""
+        total = int(self._L.pk_qwen_tap_rows(self._h))
+        rows = total - first_row if rows is None else rows
+        out = torch.empty(rows, self._n_taps * self.cfg.hidden_size, device=f"cuda:{self.device}", dtype=torch.bfloat16)
+        self._ck(self._L.pk_qwen_copy_taps(self._h, ctypes.c_void_p(out.data_ptr()), first_row, rows))
+        return out
 
     def verify_canaries(self) -> None:
         """With POCKET_CANARY=1 in the environment when the engine was created, every device buffer has guard bytes on both
