@@ -30,6 +30,7 @@ constexpr int kGroups = kThreads / 128;
 // chip whatever the ring depth, 2 KB copies reach 5.7-5.9 TB/s with two slots per warp), so a slot holds 2 KB per row.
 constexpr int kSlots = 2;
 constexpr int kRowSlot = 2048;             // bytes of one row in a slot
+constexpr int kAhead = 0;                  // L2 window behind the ring, in items per warp; 0 = off (measured slower, see ring_window)
 constexpr int kSlotBytes = 2 * kRowSlot;   // a row pair
 constexpr int kD = 128;                    // head dim of attention and DeltaNet
 constexpr int kSmemMax = 227 * 1024;
@@ -50,14 +51,22 @@ struct Seg {
   int half_n, g_lo, g_hi, cpr, rowbytes, begin, end;
 };
 
+// Where a warp is in its fixed walk over the token's weights: segment, flat item index inside it, and the segment's geometry.
+struct Cursor {
+  int seg;             // segment the cursor is in (-1 before the first)
+  int pos, end;        // flat item index of this warp inside that segment
+  int cpr, glo, half, N, rowbytes, swiglu;
+  const uint8_t* w;
+  bool done;
+};
+
 struct Ring {
   uint8_t* base;
   uint64_t* bars;
   uint32_t pk, ck;     // slots requested / slots consumed
-  int pseg;            // segment the producer cursor is in
-  int ppos, pend;      // cursor and end inside that segment (flat item index of this warp)
-  int p_cpr, p_glo, p_half, p_N, p_rowbytes, p_swiglu;
-  const uint8_t* p_w;
+  uint32_t qk;         // items the L2 prefetch cursor has passed (>= pk)
+  Cursor f;            // fill cursor: next item to copy into the ring
+  Cursor q;            // prefetch cursor: runs kAhead items ahead of the fill cursor and pulls their bytes into L2
   bool done;
 };
 
@@ -193,41 +202,85 @@ __device__ __forceinline__ bool load_seg(const PkDecParams& p, int seg, int warp
 }
 
 // Requests copies until the ring is full or the token's last segment is exhausted. Warp-uniform; lane 0 issues.
-__device__ __forceinline__ void ring_fill(const PkDecParams& p, Ring& r, int warp, int lane) {
-  while (!r.done && r.pk - r.ck < (uint32_t)kSlots) {
-    if (r.ppos >= r.pend) {
-      Seg s;
-      ++r.pseg;
-      if (!load_seg(p, r.pseg, warp, s)) {
-        r.done = true;
-        return;
-      }
-      r.ppos = s.begin;
-      r.pend = s.end;
-      r.p_cpr = s.cpr;
-      r.p_glo = s.g_lo;
-      r.p_half = s.half_n;
-      r.p_N = s.N;
-      r.p_rowbytes = s.rowbytes;
-      r.p_swiglu = s.swiglu;
-      r.p_w = s.w;
-      continue;
+// Moves the cursor to its next item (loading the next segment's geometry when the current one is finished); false at the end.
+__device__ __forceinline__ bool cursor_ready(const PkDecParams& p, Cursor& c, int warp) {
+  while (!c.done && c.pos >= c.end) {
+    Seg s;
+    ++c.seg;
+    if (!load_seg(p, c.seg, warp, s)) {
+      c.done = true;
+      break;
     }
-    const int gl = r.ppos / r.p_cpr, ch = r.ppos - gl * r.p_cpr;
-    const int g = r.p_glo + gl;
-    const int r0 = r.p_swiglu ? g : 2 * g;
-    const int r1 = r.p_swiglu ? g + r.p_half : (2 * g + 1 < r.p_N ? 2 * g + 1 : 2 * g);
+    c.pos = s.begin;
+    c.end = s.end;
+    c.cpr = s.cpr;
+    c.glo = s.g_lo;
+    c.half = s.half_n;
+    c.N = s.N;
+    c.rowbytes = s.rowbytes;
+    c.swiglu = s.swiglu;
+    c.w = s.w;
+  }
+  return !c.done;
+}
+
+// The two row pieces of the cursor's item: addresses and byte count.
+__device__ __forceinline__ void cursor_item(const Cursor& c, const uint8_t*& a0, const uint8_t*& a1, uint32_t& bytes) {
+  const int gl = c.pos / c.cpr, ch = c.pos - gl * c.cpr;
+  const int g = c.glo + gl;
+  const int r0 = c.swiglu ? g : 2 * g;
+  const int r1 = c.swiglu ? g + c.half : (2 * g + 1 < c.N ? 2 * g + 1 : 2 * g);
+  const int kb0 = ch * kRowSlot;
+  bytes = (uint32_t)min(kRowSlot, c.rowbytes - kb0);
+  a0 = c.w + (size_t)r0 * c.rowbytes + kb0;
+  a1 = c.w + (size_t)r1 * c.rowbytes + kb0;
+}
+
+__device__ __forceinline__ void l2_prefetch(const void* gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
+}
+
+// Keeps the warp's ring full. The ring (128 KB per SM) drains in about 3 us, a phase boundary takes 5-10: ring_window()
+// below uses the rest of the boundary.
+__device__ __forceinline__ void ring_fill(const PkDecParams& p, Ring& r, int warp, int lane) {
+  while (r.pk - r.ck < (uint32_t)kSlots && cursor_ready(p, r.f, warp)) {
     if (lane == 0) {
-      const int kb0 = ch * kRowSlot;
-      const uint32_t bytes = (uint32_t)min(kRowSlot, r.p_rowbytes - kb0);
+      const uint8_t *a0, *a1;
+      uint32_t bytes;
+      cursor_item(r.f, a0, a1, bytes);
       const int slot = (int)(r.pk % kSlots);
       uint8_t* dst = r.base + slot * kSlotBytes;
       sm100::mbar_arrive_expect_tx(&r.bars[slot], 2 * bytes);
-      bulk_load(dst, r.p_w + (size_t)r0 * r.p_rowbytes + kb0, bytes, &r.bars[slot]);
-      bulk_load(dst + kRowSlot, r.p_w + (size_t)r1 * r.p_rowbytes + kb0, bytes, &r.bars[slot]);
+      bulk_load(dst, a0, bytes, &r.bars[slot]);
+      bulk_load(dst + kRowSlot, a1, bytes, &r.bars[slot]);
     }
     ++r.pk;
-    ++r.ppos;
+    ++r.f.pos;
+  }
+  r.done = r.f.done;
+}
+
+// Experiment kept behind kAhead: when the warp is about to wait at a phase boundary (grid barrier, other ranks' words) the next
+// kAhead items behind the ring are pulled into L2 (`cp.async.bulk.prefetch.L2`), on the idea that HBM idles for most of a
+// 5-10 us boundary once the 128 KB ring per SM is full. Measured on the 27B shape, one GPU, ms per token: off 6.73; four
+// items per warp (38 MB per chip) at boundaries only 7.61; the same window kept up during streaming 7.75. Every byte is
+// then requested twice and the per-SM request rate is what bounds the ring, so the window costs more than the idle time.
+__device__ __forceinline__ void ring_window(const PkDecParams& p, Ring& r, int warp, int lane) {
+  if (kAhead <= 0) return;
+  if (r.qk < r.pk) {
+    r.q = r.f;
+    r.qk = r.pk;
+  }
+  while (r.qk < r.pk + (uint32_t)kAhead && cursor_ready(p, r.q, warp)) {
+    if (lane == 0) {
+      const uint8_t *a0, *a1;
+      uint32_t bytes;
+      cursor_item(r.q, a0, a1, bytes);
+      l2_prefetch(a0, bytes);
+      l2_prefetch(a1, bytes);
+    }
+    ++r.qk;
+    ++r.q.pos;
   }
 }
 
@@ -1094,8 +1147,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_persistent_kernel(const Pk
   ring.base = smem + plan.off_ring + warp * (kSlots * kSlotBytes);
   ring.bars = reinterpret_cast<uint64_t*>(smem + plan.off_bar) + warp * kSlots;
   ring.pk = ring.ck = 0;
-  ring.pseg = -1;
-  ring.ppos = ring.pend = 0;
+  ring.qk = 0;
+  ring.f.seg = -1;
+  ring.f.pos = ring.f.end = 0;
+  ring.f.done = false;
+  ring.q = ring.f;
   ring.done = false;
   if (tid == 0) sh.abort = *((volatile uint32_t*)p.status) != 0u ? 1u : 0u;
   if (tid < (p.rotary_dim >> 1) && tid < 64) {
@@ -1188,6 +1244,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_persistent_kernel(const Pk
       }
       // ---- activation staging ----
       if (stage == 1) {
+        ring_window(p, ring, warp, lane);     // the wait for the pushed words is a boundary too
         const bool has_parts = site >= 0;
         const uint2* parts = has_parts ? p.slot[site & 1][p.rank] : nullptr;
         bf16* hout = has_parts ? (bf16*)p.hidden_buf[cur] : nullptr;
@@ -1214,6 +1271,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_persistent_kernel(const Pk
         mark(p, c, head ? 20 : 10 + (seg - 5 * li));
       }
       if (bar) {
+        ring_window(p, ring, warp, lane);
         ok = bar_grid(p, c, sh);
         mark(p, c, 3);
       }
