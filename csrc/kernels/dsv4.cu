@@ -501,7 +501,8 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(const SparseAttnParams
   }
   const int nwin = min(pos + 1, p.win);
   const int ncomp = p.mode == 1 ? (pos + 1) / p.ratio : p.mode == 2 ? p.ksel : 0;
-  float mx = p.sink[hh], l = 1.f;             // the sink contributes exp(sink - mx) to the denominator only
+  // the sink contributes exp(sink - mx) to the denominator only; without one the running maximum starts at -inf
+  float mx = p.sink ? p.sink[hh] : -INFINITY, l = p.sink ? 1.f : 0.f;
   for (int r = 0; r < nwin + ncomp; ++r) {
     int row;
     if (r < nwin) {
@@ -529,7 +530,7 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(const SparseAttnParams
     for (int i = 0; i < DPL; ++i) acc[i] = acc[i] * cs + e * kf[i];
     mx = nm;
   }
-  const float inv = 1.f / l;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] *= inv;
   // inverse RoPE on the last rd dims (pairs never straddle lanes: DPL is even)
@@ -693,13 +694,18 @@ PK_API int pk_dsv4_sparse_attn(const void* q, const void* kv, const int* pos, co
 PK_API int pk_dsv4_sparse_attn_ex(const void* q, const void* kv, const int* pos, const int* rope_pos, const int* sel, const float* sink,
                                   const float* cos_t, const float* sin_t, int M, int H, int hd, int win, int ring, int ratio,
                                   int mode, int ksel, int rd, float scale, void* out, cudaStream_t stream) {
-  if (M < 1 || H < 1 || win < 1 || ring < win || (mode == 2 && sel == nullptr) || (mode == 1 && ratio < 1)) return PK_ERR_BAD_ARG;
+  // win == 0 (no window rows, entries start at row `ring`) serves latent attention over a plain position-indexed cache:
+  // mode 1 with ratio 1 is dense causal attention, mode 2 attends the selected rows; sink may be null then
+  if (M < 1 || H < 1 || win < 0 || ring < win || (win == 0 && mode == 0) || (mode == 2 && sel == nullptr) || (mode == 1 && ratio < 1)) return PK_ERR_BAD_ARG;
+  if (sink == nullptr && win > 0) return PK_ERR_BAD_ARG;
   SparseAttnParams p{(const pk::bf16*)q, (const pk::bf16*)kv, pos, rope_pos, sel, sink, cos_t, sin_t, H, win, ring, ratio, mode, ksel, rd,
                      scale, (pk::bf16*)out};
   const int wpb = H >= 8 ? 8 : H;
   const dim3 grid(M, (H + wpb - 1) / wpb);
   if (hd == 512) sparse_attn_kernel<16><<<grid, wpb * 32, 0, stream>>>(p);
   else if (hd == 128) sparse_attn_kernel<4><<<grid, wpb * 32, 0, stream>>>(p);
+  else if (hd == 576) sparse_attn_kernel<18><<<grid, wpb * 32, 0, stream>>>(p);     // MLA latent 512 + rope 64 (GLM-DSA)
+  else if (hd == 320) sparse_attn_kernel<10><<<grid, wpb * 32, 0, stream>>>(p);     // latent 256 + rope 64 (toy shapes)
   else return PK_ERR_UNSUPPORTED;
   PK_CHECK_LAUNCH();
   return PK_OK;

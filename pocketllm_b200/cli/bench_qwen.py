@@ -95,7 +95,16 @@ def run_long_context(args) -> dict:
     return out if rank == 0 else {}
 
 
+def _row_count_independent_kernels() -> None:
+    """Speculative loops compare picks of passes over different numbers of rows (plain step, verify, replay). One and two rows
+    normally stream through the shared-memory rings and three to eight through registers, which add in different orders;
+    with random weights the logits are nearly flat and such a difference flips picks. POCKET_MATVEC_RING=0 keeps every row
+    count on the register-streaming kernel, whose arithmetic per row does not depend on the row count."""
+    os.environ.setdefault("POCKET_MATVEC_RING", "0")
+
+
 def run_mtp(args) -> dict:
+    _row_count_independent_kernels()
     cfg, eng, rank, world = _engine(args, max_context=args.prompt_len + args.decode_len + 32, mtp=True)
     prompt = _prompt(cfg, args.prompt_len, 7)
     eng.reset()
@@ -121,6 +130,11 @@ def run_mtp(args) -> dict:
     return res if rank == 0 else {}
 
 
+def _continue(spec, first: int, n: int) -> list[int]:
+    """n more tokens after a prefill that produced `first`, through the speculator's rounds (decode time only)."""
+    return spec.decode(first, n)
+
+
 def run_dspark(args) -> dict:
     """Block drafter on one GPU: the published drafter shape (5 layers, block 7) with random weights next to the target. Random
     drafts are almost never right, so the row of interest is the cost model: drafting time, verify time for k + 1 rows and the
@@ -131,7 +145,8 @@ def run_dspark(args) -> dict:
     from ..models.qwen_dspark_runtime import QwenDSparkRuntime, QwenDSparkSpeculator
     if args.gpus != 1:
         raise SystemExit("the block drafter's taps are captured on one rank")
-    cfg, eng, rank, world = _engine(args, max_context=args.prompt_len + args.decode_len + 64)
+    _row_count_independent_kernels()
+    cfg, eng, rank, world = _engine(args, max_context=args.prompt_len + args.decode_len + 64, persistent_decode=0)
     tiny = args.model == "tiny"
     dcfg = qd.QwenDSparkConfig(hidden_size=cfg.hidden_size, intermediate_size=256 if tiny else 17408, num_hidden_layers=2 if tiny else 5,
                                num_attention_heads=2 if tiny else 40, num_key_value_heads=1 if tiny else 8, head_dim=128, vocab_size=cfg.vocab_size,
@@ -171,10 +186,32 @@ def run_dspark(args) -> dict:
     eng.forward_rows(plain[: args.max_draft + 1])
     verify_ms = (time.perf_counter() - t0) * 1e3
     step_ms = plain_ms / args.decode_len
+    # the known continuation as drafts (acceptance 1): what a perfect drafter buys with this verify path
+    class _Replay:
+        cfg = dcfg
+        def __init__(self, seq): self.seq, self.at = seq, 0
+        def reset(self): self.at = 0
+        def append_target_taps(self, taps, position): pass
+        def propose(self, anchor):
+            self.at = self.seq.index(anchor, self.at) + 1 if anchor in self.seq[self.at:] else len(self.seq)
+            nxt = self.seq[self.at:self.at + dcfg.block_size]
+            nxt = nxt + [0] * (dcfg.block_size - len(nxt))
+            return torch.tensor(nxt, dtype=torch.int32), torch.ones(dcfg.block_size), None
+    perfect = QwenDSparkSpeculator(eng, _Replay(plain), max_draft=args.max_draft)
+    eng.reset()
+    first2 = perfect.prefill(prompt, chunk=args.prefill_chunk)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    got2 = [first2] + _continue(perfect, first2, args.decode_len)
+    torch.cuda.synchronize()
+    perfect_s = time.perf_counter() - t0
     res = {"bench": "qwen_dspark", "n_gpus": 1, "prompt_tokens": args.prompt_len, "decode_tokens": args.decode_len, "block_size": dcfg.block_size,
            "max_draft": args.max_draft, "drafter_layers": dcfg.num_hidden_layers, "plain_decode_tok_s": round(1e3 / step_ms, 2),
            "plain_step_ms": round(step_ms, 3), "propose_ms": round(propose_ms, 3), f"verify_{args.max_draft + 1}_rows_ms": round(verify_ms, 3),
            "break_even_tokens_per_round": round((propose_ms + verify_ms) / step_ms, 2),
+           "perfect_drafts": {"tokens_equal_plain": got2 == plain, "decode_tok_s": round(args.decode_len / perfect_s, 2),
+                              "speedup_vs_plain": round((args.decode_len / perfect_s) / (1e3 / step_ms), 3), "rounds": perfect.stats["rounds"],
+                              "accepted": perfect.stats["accepted"], "proposed": perfect.stats["proposed"], "rollbacks": perfect.stats["rollbacks"]},
            "random_drafter": {"tokens_equal_plain": got == plain, "rounds": spec.stats["rounds"], "proposed": spec.stats["proposed"],
                               "accepted": spec.stats["accepted"], "rollbacks": spec.stats["rollbacks"],
                               "wall_tok_s_incl_prefill": round(args.decode_len / spec_s, 2)}}

@@ -297,8 +297,26 @@ def _moe_ref(self, i: int, xn: torch.Tensor) -> torch.Tensor:
 ReferenceModel.moe = _moe_ref
 
 
+def _mla_attn(qk: torch.Tensor, kv_cache: torch.Tensor, pos: torch.Tensor, sel: torch.Tensor | None, scale: float) -> torch.Tensor:
+    """Latent attention of bf16 q rows [T, H, D] over the position-indexed cache [ctx, D] (K row = V row): the rows `sel`
+    names (int32 [T, k], -1 padded), or every row up to the query's position; bf16 [T, H, D]."""
+    from ctypes import c_float, c_int
+    from ..ops import _check, _ptr, _stream
+    from ..ops import lib as _lib
+    T, H, D = qk.shape
+    out = torch.empty_like(qk)
+    st = _lib.kernels().pk_dsv4_sparse_attn_ex(_ptr(qk), _ptr(kv_cache), _ptr(pos), _ptr(None), _ptr(sel), _ptr(None), _ptr(None), _ptr(None), c_int(T),
+                                            c_int(H), c_int(D), c_int(0), c_int(0), c_int(1), c_int(2 if sel is not None else 1),
+                                            c_int(0 if sel is None else sel.shape[1]), c_int(0), c_float(scale), _ptr(out), _stream())
+    _check(st, "pk_dsv4_sparse_attn")
+    return out
+
+
 class GLMDSAModel:
-    """GPU runtime: projections and experts on raw blocks, MLA core and indexer in PyTorch."""
+    """GPU runtime: projections and experts on raw blocks; position-indexed latent and indexer-key caches allocated once; the
+    lightning indexer through the index-score kernel and the device radix select, absorbed MLA attention through the
+    latent sparse-attention kernel (`_forward_kernels`). Shapes the kernels do not take (indexer key dim other than 128,
+    latent + rope width outside 128 / 320 / 512 / 576) run the shared PyTorch body."""
 
     def __init__(self, path: str | Path, *, device: str = "cuda", rank: int = 0, world: int = 1, max_context: int = 4096,
                  layers: int | None = None, group=None, dsa_topk: int | None = None, routed_tp: bool = False):
@@ -394,11 +412,83 @@ class GLMDSAModel:
             self._combine(y)
         return y
 
+    def _kernel_attention_ok(self) -> bool:
+        c = self.cfg
+        return c.indexer_key_dim == 128 and (c.kv_lora_rank + c.rope_dim) in (128, 320, 512, 576)
+
+    def _alloc_kernel_caches(self) -> None:
+        c = self.cfg
+        self.kv_cache = [torch.zeros(self.max_context, c.kv_lora_rank + c.rope_dim, device=self.device, dtype=torch.bfloat16) for _ in range(c.n_layers)]
+        self.ki_cache = [torch.zeros(self.max_context, c.indexer_key_dim, device=self.device, dtype=torch.bfloat16) for _ in range(c.n_layers)]
+
     @torch.no_grad()
     def forward(self, tokens: Sequence[int]) -> torch.Tensor:
         if self.pos + len(tokens) > self.max_context:
             raise ValueError("context exceeds max_context")
-        return _forward(self.cfg, self.w, self.cache, self, list(tokens), self._lin)
+        if not self._kernel_attention_ok():
+            return _forward(self.cfg, self.w, self.cache, self, list(tokens), self._lin)
+        return self._forward_kernels(list(tokens))
+
+    @torch.no_grad()
+    def _forward_kernels(self, tokens: list[int]) -> torch.Tensor:
+        """The model body on the framework's kernels: raw-block linears, position-indexed latent / rope and indexer-key caches
+        allocated once (nothing is concatenated per step), the lightning indexer as the index-score kernel + device radix
+        select, and absorbed MLA attention as the sparse-attention kernel over the latent cache (a key row is
+        [latent | rotated rope part], the value is its latent part). Same numerics as `_forward` (the oracle's body)."""
+        from ..ops import dsv4_ops as dk
+        c, w, lin = self.cfg, self.w, self._lin
+        if not hasattr(self, "kv_cache"):
+            self._alloc_kernel_caches()
+        T, dev = len(tokens), self.device
+        r16 = lambda t: t.to(torch.bfloat16).float()
+        p0 = self.pos
+        pos = torch.arange(p0, p0 + T, device=dev)
+        pos32 = pos.to(torch.int32)
+        S = p0 + T
+        h = self.embed(tokens)
+        L, R = c.kv_lora_rank, c.rope_dim
+        for i in range(c.n_layers):
+            b = f"blk.{i}."
+            an = w[b + "attn_norm.weight"]
+            qa = r16(lin(h, b + "attn_q_a.weight", gamma=an, eps=c.norm_eps))
+            qr = r16(_rms(qa, w[b + "attn_q_a_norm.weight"], c.norm_eps))
+            q = r16(lin(qr, b + "attn_q_b.weight")).view(T, c.n_heads, c.key_mla_dim)
+            kv = r16(lin(h, b + "attn_kv_a_mqa.weight", gamma=an, eps=c.norm_eps))
+            latent = _rms(kv[:, :L], w[b + "attn_kv_a_norm.weight"], c.norm_eps)
+            krope = rope_interleaved(kv[:, L:], pos, c.rope_theta)
+            self.kv_cache[i][p0:S] = torch.cat([latent, krope], -1).to(torch.bfloat16)
+            q_rope = r16(rope_interleaved(q[..., c.nope_dim:], pos, c.rope_theta))
+            # indexer keys of the new rows
+            ki = lin(h, b + "indexer.attn_k.weight", gamma=an, eps=c.norm_eps).float()
+            mu = ki.mean(-1, keepdim=True)
+            ki = (ki - mu) * torch.rsqrt(((ki - mu) ** 2).mean(-1, keepdim=True) + c.norm_eps) * w[b + "indexer.k_norm.weight"] + w[b + "indexer.k_norm.bias"]
+            ki = torch.cat([rope_interleaved(ki[:, :R], pos, c.rope_theta), ki[:, R:]], dim=-1)
+            self.ki_cache[i][p0:S] = ki.to(torch.bfloat16)
+            sel = None
+            if 0 < c.dsa_topk < S:
+                qi = lin(qr, b + "indexer.attn_q_b.weight").float().view(T, c.indexer_heads, c.indexer_key_dim)
+                qi = torch.cat([rope_interleaved(qi[..., :R], pos, c.rope_theta), qi[..., R:]], dim=-1).to(torch.bfloat16).contiguous()
+                xn = _rms(h.float(), an, c.norm_eps).to(torch.bfloat16).float()
+                wh = (xn @ w[b + "indexer.proj.weight"].t()).contiguous()
+                score = dk.index_score(qi, self.ki_cache[i], wh, pos32, 1, S, (c.indexer_heads * c.indexer_key_dim) ** -0.5)
+                sel = dk.topk_select(score, c.dsa_topk)                   # positions a row cannot see score -inf and are never picked
+            # absorbed MLA: q against [latent | rope] rows, output in latent space
+            q_lat = torch.einsum("thn,hnl->thl", q[..., :c.nope_dim], w[b + "attn_k_b.weight"])
+            qk = torch.cat([q_lat, q_rope], -1).to(torch.bfloat16).contiguous()
+            o_lat = _mla_attn(qk, self.kv_cache[i], pos32, sel, c.key_mla_dim ** -0.5)[..., :L].float()
+            o = r16(torch.einsum("thl,hvl->thv", o_lat, w[b + "attn_v_b.weight"]).reshape(T, -1))
+            h = r16(h + lin(o, b + "attn_output.weight").float())
+            fn = w[b + "ffn_norm.weight"]
+            if i < c.leading_dense_layers:
+                mid = lin(h, b + "ffn_gate.weight", gamma=fn, eps=c.norm_eps, swiglu_with=b + "ffn_up.weight")
+                h = r16(h + lin(mid, b + "ffn_down.weight").float())
+            else:
+                xn = _rms(h.float(), fn, c.norm_eps).to(torch.bfloat16)
+                y = self.moe(i, xn)
+                sh = lin(h, b + "ffn_gate_shexp.weight", gamma=fn, eps=c.norm_eps, swiglu_with=b + "ffn_up_shexp.weight")
+                h = r16(h + y + lin(sh, b + "ffn_down_shexp.weight").float())
+        self.pos += T
+        return lin(h[-1:], "output.weight", gamma=w["output_norm.weight"], eps=c.norm_eps).float()[0]
 
     def _checked(self, token: int) -> int:
         """The step's token, or `StepFailed` on every rank when a peer all-reduce timed out (collective check)."""

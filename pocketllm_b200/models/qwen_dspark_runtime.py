@@ -146,9 +146,15 @@ class QwenDSparkSpeculator:
         return first
 
     def generate(self, prompt, max_new_tokens: int, chunk: int = 512) -> list[int]:
+        self.eng.reset()
+        first = self.prefill(prompt, chunk)
+        return ([first] + self.decode(first, max_new_tokens - 1))[:max_new_tokens]
+
+    def decode(self, first: int, n: int) -> list[int]:
+        """`n` tokens after `first` (the token the prefill produced, not yet consumed by the target)."""
         eng, d = self.eng, self.d
-        eng.reset()
-        out = [self.prefill(prompt, chunk)]
+        max_new_tokens = n + 1
+        out = [first]
         snap = eng.snapshot()
         try:
             while len(out) < max_new_tokens:
@@ -186,4 +192,4 @@ class QwenDSparkSpeculator:
                 out += drafts[:correct] + [preds[correct]]
         finally:
             snap.free()
-        return out[:max_new_tokens]
+        return out[1:max_new_tokens]
