@@ -1422,6 +1422,21 @@ void QwenEngine::build_persistent() {
     p.cand_idx_peer[r] = (int*)((char*)peers_[r] + off_cidx_);
     p.cand_flag[r] = (uint32_t*)((char*)peers_[r] + off_cflag_);
   }
+  // two-stage sums from eight ranks on (POCKET_DECODE_TWO_STAGE=0 / 1 overrides): this GPU's own buffer of reduced words
+  {
+    int two = opt_.tp_world >= 8 ? 1 : 0;
+    if (const char* v = getenv("POCKET_DECODE_TWO_STAGE")) two = atoi(v) != 0 && opt_.tp_world > 1;
+    p.two_stage = two;
+    p.red[0] = p.red[1] = nullptr;
+    if (two) {
+      if (dec_red_ == nullptr) {
+        dec_red_ = dalloc((size_t)2 * hidden_ * sizeof(uint2));
+        cuda_check(cudaMemset(dec_red_, 0, (size_t)2 * hidden_ * sizeof(uint2)), "memset");
+      }
+      p.red[0] = (uint2*)dec_red_;
+      p.red[1] = (uint2*)dec_red_ + hidden_;
+    }
+  }
   p.epoch = (const uint32_t*)((char*)arena_ + off_epoch_);
   p.sites_per_epoch = sites_per_epoch_;
   p.status = (uint32_t*)((char*)arena_ + off_status_);

@@ -309,6 +309,7 @@ class QwenEngine {
   void* taps_ = nullptr;           // [rows_cap_, taps * hidden] bf16
   int tap_rows_ = 0;
   void capture_tap(int layer, const void* rows, int M);   // rows [M, hidden] bf16 = the residual stream after `layer`
+  void* dec_red_ = nullptr;        // persistent decode, two-stage sums: [2][hidden] {value, sequence} words
   bool tc_prefill_attn_ = false;   // prefill chunks through pk_gqa_prefill_umma (bf16 cache, no window)
   void* act_q_ = nullptr;        // [2][rows_cap_ up to 128][K max] E4M3 terms of the GEMM input being multiplied
   float* act_scale_ = nullptr;   // [K max / 128][that row count]

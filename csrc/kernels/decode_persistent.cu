@@ -401,9 +401,63 @@ __device__ __forceinline__ bool stage_norm(const PkDecParams& p, const Ctx& c, S
   const uint64_t t0 = nparts > 0 ? global_timer_ns() : 0ull;
   float ss = 0.f, amax = 0.f;
   bool good = true;
+  // Two stages on many ranks: with W slots a block would read W x hidden words per site (320 KB at W = 8, 47 MB over the
+  // grid). Instead every block adds the W partials and the residual for ITS slice of the columns only, publishes the
+  // rounded sums as {value, sequence} words in this GPU's own buffer, and then every block polls those hidden words.
+  const bool two_stage = nparts > 0 && p.two_stage != 0 && p.red[site & 1] != nullptr;
+  if (two_stage) {
+    uint2* red = p.red[site & 1];
+    const int c_lo = (int)(((long long)blockIdx.x * nch) / gridDim.x), c_hi = (int)(((long long)(blockIdx.x + 1) * nch) / gridDim.x);
+    for (int c8 = c_lo + tid; c8 < c_hi && good; c8 += kThreads) {
+      const int k = c8 * 8;
+      float v[8];
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(x_in + k)), v);
+      for (int r = 0; r < nparts && good; ++r) {
+        float lo[4], hi[4];
+        good = ll_load4(parts + (size_t)r * K + k, seq, lo, p, c, t0) && ll_load4(parts + (size_t)r * K + k + 4, seq, hi, p, c, t0);
+        if (good) {
+          v[0] += lo[0]; v[1] += lo[1]; v[2] += lo[2]; v[3] += lo[3];
+          v[4] += hi[0]; v[5] += hi[1]; v[6] += hi[2]; v[7] += hi[3];
+        }
+      }
+      if (!good) break;
+      uint32_t packed[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        packed[j] = *reinterpret_cast<const uint32_t*>(&h2);
+      }
+      if (hidden_out != nullptr) *reinterpret_cast<uint4*>(hidden_out + k) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // the bf16-rounded sums as fp32 bit patterns, two words per 16-byte store
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(red + k + 2 * j), "r"(packed[j] << 16), "r"(seq), "r"(packed[j] & 0xffff0000u), "r"(seq)
+                     : "memory");
+      }
+    }
+  }
   for (int c8 = tid; c8 < nch; c8 += kThreads) {
     const int k = c8 * 8;
     float v[8];
+    if (two_stage) {
+      float lo[4], hi[4];
+      const uint2* red = p.red[site & 1];
+      const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + k));
+      const float4 gb = __ldg(reinterpret_cast<const float4*>(gamma + k + 4));
+      good = good && ll_load4(red + k, seq, lo, p, c, t0) && ll_load4(red + k + 4, seq, hi, p, c, t0);
+      if (!good) break;
+      v[0] = lo[0]; v[1] = lo[1]; v[2] = lo[2]; v[3] = lo[3];
+      v[4] = hi[0]; v[5] = hi[1]; v[6] = hi[2]; v[7] = hi[3];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+      v[0] *= 1.f + ga.x; v[1] *= 1.f + ga.y; v[2] *= 1.f + ga.z; v[3] *= 1.f + ga.w;
+      v[4] *= 1.f + gb.x; v[5] *= 1.f + gb.y; v[6] *= 1.f + gb.z; v[7] *= 1.f + gb.w;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      *reinterpret_cast<float4*>(scratch + k) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(scratch + k + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      continue;
+    }
     // everything that does not depend on the pushed rows is requested before the first poll
     const uint4 xraw = __ldcg(reinterpret_cast<const uint4*>(x_in + k));
     const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + k));

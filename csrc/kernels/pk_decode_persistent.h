@@ -101,6 +101,10 @@ struct PkDecParams {
   // writes value and sequence number with ONE 8-byte store, so the arrival of the sequence number is the arrival of
   // the value: no fence, no separate flag, and the consumer's wait on the data is the only synchronisation of a site.
   uint2* slot[2][PK_MAX_RANKS];
+  // two-stage sums on many ranks: this GPU's own {value, sequence} words of the reduced residual stream, by site parity
+  // ([hidden] words each; null or two_stage == 0: every block adds the world's slots itself)
+  uint2* red[2];
+  int two_stage;
   float* cand_val_peer[PK_MAX_RANKS];   // peer r's sampler candidates: rows of 32 per rank (index row: entry 31 = status)
   int* cand_idx_peer[PK_MAX_RANKS];
   uint32_t* cand_flag[PK_MAX_RANKS];    // peer r's sampler flags [world]
