@@ -93,6 +93,39 @@ def random_checkpoint(cfg: QwenDSparkConfig, seed: int = 0, sigma: float = 0.05)
     return out
 
 
+def save_checkpoint(directory, cfg: QwenDSparkConfig, weights: dict[str, torch.Tensor]) -> None:
+    """A drafter directory: `config.json` (the dataclass fields) and the tensors of `tensor_names` as Safetensors."""
+    import dataclasses
+    import json
+    from pathlib import Path
+    from ..formats import safetensors_io as st_io
+    d = Path(directory)
+    d.mkdir(parents=True, exist_ok=True)
+    fields = dataclasses.asdict(cfg)
+    fields["target_layer_ids"] = list(cfg.target_layer_ids)
+    (d / "config.json").write_text(json.dumps(fields, indent=1))
+    st_io.write_sharded(d, {k: v.contiguous() for k, v in weights.items()})
+
+
+def load_checkpoint(directory) -> tuple[QwenDSparkConfig, dict[str, torch.Tensor]]:
+    """(config, tensors) of a drafter directory; every tensor of `tensor_names` must be present with its shape."""
+    import json
+    from pathlib import Path
+    from ..formats import safetensors_io as st_io
+    d = Path(directory)
+    fields = json.loads((d / "config.json").read_text())
+    known = {f for f in QwenDSparkConfig.__dataclass_fields__}
+    cfg = QwenDSparkConfig(**{k: (tuple(v) if k == "target_layer_ids" else v) for k, v in fields.items() if k in known})
+    model = st_io.SafetensorsModel(d)
+    tensors = {k: model.get(k).clone() for k in model.keys()}
+    for name, shape in tensor_names(cfg):
+        if name not in tensors:
+            raise ValueError(f"drafter checkpoint lacks {name}")
+        if tuple(tensors[name].shape) != tuple(shape):
+            raise ValueError(f"{name}: shape {tuple(tensors[name].shape)} where {tuple(shape)} is expected")
+    return cfg, tensors
+
+
 def yarn_inv_freq(cfg: QwenDSparkConfig) -> torch.Tensor:
     """Inverse frequencies of the rotation [head_dim / 2] (fp64): plain for factor 1, else the YaRN blend of
     interpolated and extrapolated frequencies between the beta_fast / beta_slow correction dims."""

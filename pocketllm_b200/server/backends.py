@@ -15,12 +15,27 @@ class QwenBackend:
     """Greedy requests run on the engine's CUDA-graph decode in bursts; sampled requests read
     the logits back after every step."""
 
-    def __init__(self, engine, burst: int = 8):
-        self.eng, self.burst = engine, burst
+    def __init__(self, engine, burst: int = 8, speculator=None):
+        """`speculator`: a `QwenDSparkSpeculator` over the same engine; greedy requests then run as block-drafted speculative
+        rounds (same tokens as plain greedy decode)."""
+        self.eng, self.burst, self.spec = engine, burst, speculator
 
     def generate(self, prompt_ids: Sequence[int], p: SamplingParams) -> Iterator[int]:
         eng = self.eng
         eng.reset()
+        plain = p.temperature <= 0 and p.repetition_penalty == 1.0 and p.frequency_penalty == 0 and p.presence_penalty == 0
+        if self.spec is not None and plain:
+            first = self.spec.prefill(list(prompt_ids))
+            yield first
+            n, last = 1, first
+            while n < p.max_tokens and last not in p.stop_token_ids:
+                for t in self.spec.decode(last, min(self.burst, p.max_tokens - n)):
+                    n += 1
+                    last = t
+                    yield t
+                    if t in p.stop_token_ids:
+                        return
+            return
         tok = eng.prefill(list(prompt_ids))
         produced = [tok]
         yield tok
@@ -110,7 +125,7 @@ class HFChatTokenizer:
         return self._eos
 
 
-def build(kind: str, ckpt: str, max_context: int):
+def build(kind: str, ckpt: str, max_context: int, qwen_dspark: str | None = None):
     """(backend, tokenizer) for `--model qwen|gguf|dsv4`. Under torchrun every rank builds its shard (rank and world come
     from the environment)."""
     import os
@@ -145,7 +160,23 @@ def build(kind: str, ckpt: str, max_context: int):
             for m in messages:
                 out += f"<|im_start|>{m['role']}\n{dsv4._text(m.get('content'))}<|im_end|>\n"
             return out + "<|im_start|>assistant\n" + ("<think>\n" if thinking else "")
-        return QwenBackend(eng), HFChatTokenizer(tok, render, eos)
+        spec = None
+        if qwen_dspark:
+            # external block drafter (one rank): its layers run on the GPU next to the engine, coupled through target taps
+            if world > 1:
+                raise ValueError("--qwen-dspark runs on one rank (the target taps are captured on one rank)")
+            from ..formats import safetensors_io as st_io
+            from ..models import qwen_dspark as qd
+            from ..models.qwen_dspark_runtime import QwenDSparkRuntime, QwenDSparkSpeculator
+            dcfg, dw = qd.load_checkpoint(qwen_dspark)
+            dcfg.validate_for_target(cfg.hidden_size, cfg.vocab_size, cfg.num_hidden_layers)
+            model = st_io.SafetensorsModel(ckpt)
+            names = set(model.keys())
+            embed_name = next(n for n in ("model.language_model.embed_tokens.weight", "model.embed_tokens.weight") if n in names)
+            embed = model.get(embed_name)
+            lm_head = model.get("lm_head.weight") if "lm_head.weight" in names else embed
+            spec = QwenDSparkSpeculator(eng, QwenDSparkRuntime(dcfg, dw, embed, lm_head, max_context=max_context, device=f"cuda:{local}"))
+        return QwenBackend(eng, speculator=spec), HFChatTokenizer(tok, render, eos)
     from ..models import registry
     md = gguf_tokenizer.read_metadata(ckpt)
     tok = gguf_tokenizer.build_tokenizer(md)

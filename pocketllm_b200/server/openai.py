@@ -316,6 +316,7 @@ def main(argv=None) -> int:
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--max-context", type=int, default=4096)
+    ap.add_argument("--qwen-dspark", default="", help="qwen: directory of an external DSpark block drafter; greedy requests run as speculative rounds")
     args = ap.parse_args(argv)
     import os
     from . import backends, distributed
@@ -328,7 +329,7 @@ def main(argv=None) -> int:
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         group = distributed.control_group()
-    backend, tokenizer = backends.build(args.model, args.ckpt, args.max_context)
+    backend, tokenizer = backends.build(args.model, args.ckpt, args.max_context, qwen_dspark=args.qwen_dspark or None)
     if world > 1 and rank != 0:
         served = distributed.worker_loop(backend, group)
         print(f"worker {rank}: served {served} requests", flush=True)

@@ -102,3 +102,29 @@ def test_speculative_generation_with_the_block_drafter_equals_greedy(tmp_path):
     assert got == plain
     assert spec.stats["rounds"] > 0 and spec.stats["proposed"] >= spec.stats["accepted"] >= 0
     eng.close()
+
+
+def test_server_backend_with_drafter_streams_the_greedy_tokens(tmp_path):
+    """`--qwen-dspark DIR` of the Python server: the Qwen backend runs greedy requests as block-drafted speculative rounds
+    and yields exactly the plain backend's tokens."""
+    from pocketllm_b200.models import qwen_dspark as qd
+    from pocketllm_b200.models import qwen_hybrid as qh
+    from pocketllm_b200.models.qwen_dspark_runtime import QwenDSparkRuntime, QwenDSparkSpeculator
+    from pocketllm_b200.server.backends import QwenBackend
+    from pocketllm_b200.server.engine import SamplingParams
+    cfg, tensors = _target(tmp_path)
+    dcfg = _drafter_cfg()
+    ddir = tmp_path / "drafter"
+    qd.save_checkpoint(ddir, dcfg, qd.random_checkpoint(dcfg, seed=9))
+    dcfg2, dw = qd.load_checkpoint(ddir)
+    pre = "model.language_model."
+    embed, lm_head = tensors[pre + "embed_tokens.weight"], tensors["lm_head.weight"]
+    torch.manual_seed(6)
+    prompt = torch.randint(0, cfg.vocab_size - 1, (45,)).tolist()
+    eng = qh.QwenEngine(cfg, max_context=512, prefill_chunk=32, persistent_decode=0).load(tmp_path)
+    params = SamplingParams(max_tokens=30, temperature=0.0)
+    plain = list(QwenBackend(eng).generate(prompt, params))
+    spec = QwenDSparkSpeculator(eng, QwenDSparkRuntime(dcfg2, dw, embed, lm_head, max_context=512))
+    drafted = list(QwenBackend(eng, speculator=spec).generate(prompt, params))
+    assert drafted == plain and len(plain) == 30
+    eng.close()
