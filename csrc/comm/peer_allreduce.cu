@@ -102,23 +102,23 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ParParams p) 
     const uint32_t pushed = atomicAdd(pushed_p, 1u) + 1u;
     if (pushed == gridDim.x) {
       *pushed_p = 0u;   // every block has added exactly once: re-arm for the next launch
+      // one fence, then the flag stores leave back to back (a release store per rank would wait for the one before it)
       __threadfence_system();
       for (int r = 0; r < p.world; ++r)
-        st_release_sys(ctl(p.slot_base[r], p.capacity, p.world) + parity * p.world + p.rank, seq);
+        st_relaxed_sys(ctl(p.slot_base[r], p.capacity, p.world) + parity * p.world + p.rank, seq);
     }
-    // 3a. wait for every rank (own arena)
+    // 3a. wait for every rank (own arena): all flags polled together
     bool ok = *((volatile uint32_t*)status_p) == 0u;
     const uint64_t t0 = global_timer_ns(), budget = (uint64_t)p.timeout_us * 1000ull;
-    for (int r = 0; ok && r < p.world; ++r) {
-      while ((int32_t)(ld_acquire_sys(c + parity * p.world + r) - seq) < 0) {
-        if (global_timer_ns() - t0 > budget) {
-          atomicExch(status_p, PK_COMM_TIMEOUT);
-          ok = false;
-          break;
-        }
-        __nanosleep(40);
+    while (ok && !all_reached(c + parity * p.world, p.world, seq)) {
+      if (global_timer_ns() - t0 > budget) {
+        atomicExch(status_p, PK_COMM_TIMEOUT);
+        ok = false;
+        break;
       }
+      __nanosleep(40);
     }
+    __threadfence_system();
     s_ok = ok;
   }
   __syncthreads();

@@ -29,6 +29,37 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Publishing a sequence number to every rank: ONE system fence, then one relaxed store per rank. A release store per
+// rank would wait for the acknowledgement of the store before it (a round trip over NVLink each): at eight ranks that
+// was most of the latency of a small all-reduce. The fence followed by relaxed stores is the same release pattern.
+__device__ __forceinline__ void publish_seq(uint32_t* const* flag, int world, int rank, uint32_t seq) {
+  __threadfence_system();
+  for (int r = 0; r < world; ++r) st_relaxed_sys(flag[r] + rank, seq);
+}
+
+// One polling round over the `world` words at `flag`: the loads are issued together, then compared. True when every
+// word has reached `target` (sequence numbers only grow; a later one also satisfies the wait). The caller runs
+// __threadfence_system() after the round that succeeded (relaxed loads + fence = acquire).
+__device__ __forceinline__ bool all_reached(const uint32_t* flag, int world, uint32_t target) {
+  uint32_t v[PK_MAX_RANKS];
+#pragma unroll
+  for (int r = 0; r < PK_MAX_RANKS; ++r) v[r] = r < world ? ld_relaxed_sys(flag + r) : target;
+  bool all = true;
+#pragma unroll
+  for (int r = 0; r < PK_MAX_RANKS; ++r) all = all && (int32_t)(v[r] - target) >= 0;
+  return all;
+}
+
 __device__ __forceinline__ uint32_t comm_seq(const uint32_t* epoch, uint32_t sites, uint32_t site) {
   return (*((const volatile uint32_t*)epoch)) * sites + site + 1u;
 }
@@ -42,16 +73,14 @@ __device__ __forceinline__ bool wait_all_ranks(const PkWait& w) {
   const uint32_t target = comm_seq(w.epoch, w.sites_per_epoch, w.site);
   const uint64_t t0 = global_timer_ns();
   const uint64_t budget = (uint64_t)w.timeout_us * 1000ull;
-  for (int r = 0; r < w.world; ++r) {
-    // Sequence numbers only grow; a later one also satisfies the wait.
-    while ((int32_t)(ld_acquire_sys(w.flag + r) - target) < 0) {
-      if (global_timer_ns() - t0 > budget) {
-        atomicExch(w.status, PK_COMM_TIMEOUT);
-        return false;
-      }
-      __nanosleep(40);
+  while (!all_reached(w.flag, w.world, target)) {
+    if (global_timer_ns() - t0 > budget) {
+      atomicExch(w.status, PK_COMM_TIMEOUT);
+      return false;
     }
+    __nanosleep(40);
   }
+  __threadfence_system();
   return true;
 }
 
@@ -65,9 +94,7 @@ __device__ __forceinline__ void publish_when_grid_done(const PkPush& p) {
     const uint32_t done = atomicAdd(p.block_counter, 1u) + 1u;
     if (done == nblocks) {
       *p.block_counter = 0u;  // ready for the next launch (stream-ordered)
-      __threadfence_system();
-      const uint32_t seq = comm_seq(p.epoch, p.sites_per_epoch, p.site);
-      for (int r = 0; r < p.world; ++r) st_release_sys(p.flag[r] + p.rank, seq);
+      publish_seq(p.flag, p.world, p.rank, comm_seq(p.epoch, p.sites_per_epoch, p.site));
     }
   }
 }
@@ -80,9 +107,7 @@ __device__ __forceinline__ void publish_after_block_sync(const PkPush& p) {
   const uint32_t done = atomicAdd(p.block_counter, 1u) + 1u;
   if (done == nblocks) {
     *p.block_counter = 0u;
-    __threadfence_system();
-    const uint32_t seq = comm_seq(p.epoch, p.sites_per_epoch, p.site);
-    for (int r = 0; r < p.world; ++r) st_release_sys(p.flag[r] + p.rank, seq);
+    publish_seq(p.flag, p.world, p.rank, comm_seq(p.epoch, p.sites_per_epoch, p.site));
   }
 }
 

@@ -1378,19 +1378,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_persistent_kernel(const Pk
             p.cand_idx_peer[r][p.rank * 32] = bi;
             p.cand_idx_peer[r][p.rank * 32 + 31] = my_status;
           }
-          __threadfence_system();
-          for (int r = 0; r < p.world; ++r) st_release_sys(p.cand_flag[r] + p.rank, seq);
+          publish_seq(p.cand_flag, p.world, p.rank, seq);
           const uint64_t t0 = global_timer_ns();
           uint32_t iter = 0;
-          for (int r = 0; r < p.world && good; ++r) {
-            while ((int32_t)(ld_acquire_sys(p.cand_flag[p.rank] + r) - seq) < 0) {
-              if (wait_failed(p, c, t0, iter)) {
-                atomicCAS(p.status, 0u, PK_COMM_TIMEOUT);
-                good = false;
-                break;
-              }
+          while (!all_reached(p.cand_flag[p.rank], p.world, seq)) {
+            if (wait_failed(p, c, t0, iter)) {
+              atomicCAS(p.status, 0u, PK_COMM_TIMEOUT);
+              good = false;
+              break;
             }
           }
+          __threadfence_system();
           if (good) {
             best = -INFINITY;
             bi = 0x7fffffff;

@@ -574,10 +574,6 @@ class QwenEngine:
         return torch.tensor(list(buf), dtype=torch.float32)
 
     @property
-    def position(self) -> int:
-        return self._L.pk_qwen_position(self._h)
-
-    @property
     def weight_bytes(self) -> int:
         return int(self._L.pk_qwen_weight_bytes(self._h))
 

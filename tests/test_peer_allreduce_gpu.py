@@ -48,6 +48,21 @@ def test_matches_nccl_on_two_gpus():
     assert out["status"] == 0 and max(out["max_abs_err"]) < 1e-5
 
 
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_multimem_all_reduce_matches_nccl_on_two_gpus():
+    """The in-switch all-reduce (multimem.ld_reduce, and multimem.st for the two-shot form) against NCCL; skipped where
+    the machine offers no multicast mapping. No rank leaves early here: every rank runs to the final barrier."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29553",
+           "-m", "pocketllm_b200.parallel.par_check", "--sizes", "1001,4096,262144", "--iters", "20", "--multimem"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert r.returncode == 0, r.stderr[-3000:]
+    out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    if out["multimem"] != "ok":
+        pytest.skip(out["multimem"])
+    assert out["status"] == 0 and max(out["mm_max_abs_err"]) < 1e-5
+
+
 def _ep(world: int, ckpt, port: int, extra=()):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(port),
