@@ -553,7 +553,12 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* logits, c
     for (int e = tid; e < E; e += 256) sc[e] = score_func == 1 ? sigmoidf_(sc[e]) : sqrtf(softplusf_(sc[e]));
   }
   __syncthreads();
-  for (int e = tid; e < E; e += 256) key[e] = sc[e] + (bias ? bias[e] : 0.f);
+  // keys stay finite: a NaN or -inf key would never win a comparison below, the pick would keep its initial invalid id
+  // and index shared memory with it
+  for (int e = tid; e < E; e += 256) {
+    const float k = sc[e] + (bias ? bias[e] : 0.f);
+    key[e] = k > -3.0e38f ? k : -3.0e38f;
+  }
   __syncthreads();
   if (warp == 0) {
     float wsum = 0.f;

@@ -23,6 +23,7 @@ def main() -> int:
     ap.add_argument("--prompt", default="1,2,3,4,5,6,7,8,9,10")
     ap.add_argument("--new", type=int, default=8)
     ap.add_argument("--nccl", action="store_true")
+    ap.add_argument("--multimem", action="store_true", help="combine through the in-switch all-reduce (every payload size)")
     args = ap.parse_args()
     rank, world, local = tp.env_rank_world()
     torch.cuda.set_device(local)
@@ -30,11 +31,14 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg, W = ld.load_checkpoint(args.ckpt)
     rt = DSV4Runtime(cfg, W, max_context=256, max_rows=16, rank=rank, world=world, use_peer_allreduce=not args.nccl)
+    if args.multimem and world > 1:
+        from .combine import ExpertCombine
+        rt.combine = ExpertCombine(world, None, capacity=16 * cfg.dim, multimem=True, multimem_min_floats=1)
     prompt = [int(t) for t in args.prompt.split(",")]
     logits = rt.forward_logits(prompt)
     rt.last_token = int(logits[-1].argmax())
     tokens = [rt.last_token] + rt.decode(args.new - 1)
-    status = rt.combine.peer.status() if rt.combine.peer is not None else 0
+    status = max(rt.combine.peer.status() if rt.combine.peer is not None else 0, rt.combine.mm.status() if rt.combine.mm is not None else 0)
     agree = True
     if world > 1:
         t = torch.tensor(tokens, device="cuda")
@@ -47,6 +51,10 @@ def main() -> int:
         print(json.dumps({"world": world, "tokens": tokens, "ranks_agree": agree, "status": status, "combine_calls": rt.combine.calls,
                           "logit_checksum": round(float(logits.float().abs().mean()), 6)}))
     if world > 1:
+        # every rank lets go of a multicast-bound buffer together
+        torch.cuda.synchronize()
+        dist.barrier()
+        rt.combine.mm = None
         dist.destroy_process_group()
     return 0
 
