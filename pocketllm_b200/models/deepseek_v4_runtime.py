@@ -153,10 +153,15 @@ class DSV4Runtime:
     greedy token after each row; `rollback(position)` rewinds to an earlier position."""
 
     def __init__(self, cfg: d4.DSV4Config, weights: dict[str, torch.Tensor], *, max_context: int | None = None, max_rows: int = 64,
-                 rank: int = 0, world: int = 1, group=None, use_peer_allreduce: bool = True, raw_experts: dict | None = None):
+                 rank: int = 0, world: int = 1, group=None, use_peer_allreduce: bool = True, raw_experts: dict | None = None, pipeline=None):
         """`raw_experts` (from `deepseek_v4_gguf.load_gguf`) supplies routed experts as GGUF blocks instead of FP4 tensors in `weights`.
         With `world > 1` the routed experts are split over the ranks in contiguous ranges (everything else is
-        replicated) and their outputs are summed across ranks; every rank feeds the same tokens."""
+        replicated) and their outputs are summed across ranks; every rank feeds the same tokens.
+        With `pipeline` (a `parallel.pipeline.PipelineStage` built for `cfg.n_layers`) this rank holds only the blocks of
+        its layer range: the hidden state [rows, hc, dim] travels stage to stage by send / recv and the last stage
+        broadcasts the logits, so every rank returns the same tokens (the reference's layer pipeline,
+        src/models/deepseek_v4/runtime.py:4832-4838,4873). MTP drafting and taps need the last hidden state on every
+        rank and are not offered under a pipeline."""
         self.cfg = cfg
         if cfg.n_routed_experts % world:
             raise ValueError("the expert count must divide by the world size")
@@ -179,12 +184,14 @@ class DSV4Runtime:
         W = weights
         f32 = lambda n: W[n].float().cuda().contiguous()
         self.embed = W["embed.weight"].float().cuda()
-        self.blocks = [_BlockWeights(cfg, W, f"layers.{i}", i, e_lo, e_hi, raw_experts) for i in range(cfg.n_layers)]
+        self.pipeline = pipeline
+        self.layer_lo, self.layer_hi = (pipeline.lo, pipeline.hi) if pipeline is not None else (0, cfg.n_layers)
+        self.blocks = [_BlockWeights(cfg, W, f"layers.{i}", i, e_lo, e_hi, raw_experts) for i in range(self.layer_lo, self.layer_hi)]
         self.hc_head = (f32("hc_head_fn"), f32("hc_head_scale"), f32("hc_head_base"))
         self.norm = f32("norm.weight")
         self.head = _Lin(W["head.weight"])
         self.mtp = []
-        for m in range(cfg.n_mtp_layers):
+        for m in range(cfg.n_mtp_layers if pipeline is None else 0):
             p = f"mtp.{m}"
             if f"{p}.e_proj.weight" not in W:
                 break
@@ -312,6 +319,10 @@ class DSV4Runtime:
                 raise ValueError("exceeds max_context")
             tok_t = torch.tensor(part, device="cuda", dtype=torch.int32)
             pos_t = torch.arange(pos0, pos0 + M, device="cuda", dtype=torch.int32)
+            if self.pipeline is not None:
+                out.append(self._pipeline_chunk(tok_t, pos_t, pos0))
+                self.pos += M
+                continue
             h = self.embed[tok_t.long()].unsqueeze(1).repeat(1, self.cfg.hc_mult, 1).contiguous()
             taps = []
             for li, (b, st) in enumerate(zip(self.blocks, self.state)):
@@ -323,9 +334,32 @@ class DSV4Runtime:
             hidden.append(h)
             out.append(self._logits(h, self.hc_head, self.norm))
             self.pos += M
+        if self.pipeline is not None:
+            self.last_hidden = self.last_taps = None
+            return torch.cat(out, 0)
         self.last_hidden = torch.cat(hidden, 0)
         self.last_taps = torch.cat(taps_all, 0) if taps_all else None
         return torch.cat(out, 0)
+
+    def _pipeline_chunk(self, tok_t: torch.Tensor, pos_t: torch.Tensor, pos0: int) -> torch.Tensor:
+        """One call of up to max_rows rows through this rank's layer range; fp32 logits on every rank."""
+        import torch.distributed as dist
+        cfg, pl = self.cfg, self.pipeline
+        M = tok_t.shape[0]
+        if pl.first:
+            h = self.embed[tok_t.long()].unsqueeze(1).repeat(1, cfg.hc_mult, 1).contiguous()
+        else:
+            h = torch.empty(M, cfg.hc_mult, cfg.dim, device="cuda", dtype=torch.float32)
+            pl._p2p(dist.recv, h, pl.rank - 1)
+        for b, st in zip(self.blocks, self.state):
+            h = self._block(b, st, h, pos_t, tok_t, pos0)
+        if pl.last:
+            logits = self._logits(h, self.hc_head, self.norm).contiguous()
+        else:
+            pl._p2p(dist.send, h.contiguous(), pl.rank + 1)
+            logits = torch.empty(M, cfg.vocab_size, device="cuda", dtype=torch.float32)
+        dist.broadcast(logits, src=dist.get_global_rank(pl.group, pl.world - 1) if pl.group is not None else pl.world - 1, group=pl.group)
+        return logits
 
     def forward_rows(self, tokens: Sequence[int]) -> list[int]:
         nxt = self.forward_logits(tokens).argmax(-1).tolist()

@@ -1,5 +1,7 @@
 """Expert-parallel consistency run for the DeepSeek-V4 runtime (launch with torchrun): every rank holds a slice of
-the routed experts, the combine runs over peer memory (or NCCL with --nccl), and rank 0 prints one JSON line.
+the routed experts, the combine runs over peer memory (or NCCL with --nccl, or the in-switch all-reduce with --multimem);
+with --pp every rank holds a contiguous layer range instead and the hidden state travels stage to stage. Rank 0 prints
+one JSON line.
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29571 \
         -m pocketllm_b200.parallel.dsv4_ep_check --ckpt DIR --prompt 1,2,3 --new 8
@@ -24,13 +26,18 @@ def main() -> int:
     ap.add_argument("--new", type=int, default=8)
     ap.add_argument("--nccl", action="store_true")
     ap.add_argument("--multimem", action="store_true", help="combine through the in-switch all-reduce (every payload size)")
+    ap.add_argument("--pp", action="store_true", help="layer pipeline instead of expert parallelism: each rank holds a contiguous layer range")
     args = ap.parse_args()
     rank, world, local = tp.env_rank_world()
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg, W = ld.load_checkpoint(args.ckpt)
-    rt = DSV4Runtime(cfg, W, max_context=256, max_rows=16, rank=rank, world=world, use_peer_allreduce=not args.nccl)
+    if args.pp and world > 1:
+        from .pipeline import PipelineStage
+        rt = DSV4Runtime(cfg, W, max_context=256, max_rows=16, pipeline=PipelineStage(cfg.n_layers))
+    else:
+        rt = DSV4Runtime(cfg, W, max_context=256, max_rows=16, rank=rank, world=world, use_peer_allreduce=not args.nccl)
     if args.multimem and world > 1:
         from .combine import ExpertCombine
         rt.combine = ExpertCombine(world, None, capacity=16 * cfg.dim, multimem=True, multimem_min_floats=1)

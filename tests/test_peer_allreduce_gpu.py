@@ -85,6 +85,9 @@ def test_dsv4_expert_parallel_matches_single_gpu(tmp_path):
     assert nccl["combine_calls"]["peer"] == 0
     assert one["tokens"] == two["tokens"] == nccl["tokens"]
     assert abs(one["logit_checksum"] - two["logit_checksum"]) < 1e-3
+    # two pipeline stages of two layers each: same tokens, same logits
+    pp = _ep(2, tmp_path, 29585, ["--pp"])
+    assert pp["ranks_agree"] and pp["tokens"] == one["tokens"] and abs(one["logit_checksum"] - pp["logit_checksum"]) < 1e-5
     # the same run with every combine through the in-switch all-reduce (where the machine offers multicast)
     mm = _ep(2, tmp_path, 29584, ["--multimem"])
     if mm["combine_calls"]["multimem"] > 0:
