@@ -6,6 +6,7 @@ as a fraction of the measured peaks (`MEASURED_PEAKS.json` at the repository roo
     python -m pocketllm_b200.utils.bench_kernels --op gemm --M 512 --N 34816 --K 5120 --epi 1
     python -m pocketllm_b200.utils.bench_kernels --op matvec --N 34816 --K 5120 --epi 1
     python -m pocketllm_b200.utils.bench_kernels --suite
+    python -m pocketllm_b200.utils.bench_kernels --op dsv4 --M 64 --ctx 32768      # indexer scores, top-k, sparse attention
 """
 from __future__ import annotations
 
@@ -96,6 +97,44 @@ def bench_attention(M: int, ctx: int, Hq: int, Hkv: int, iters: int, simt: bool 
             "tflops": round(flops / us / 1e6, 1), "frac_of_peak": round(flops / us / 1e6 / tf, 3), "peak": f"{tf} TFLOP/s bf16 ({src})"}
 
 
+def bench_dsv4_select_attend(M: int, ctx: int, iters: int) -> list[dict]:
+    """The sparse-attention step of a DeepSeek-V4-Flash-shaped ratio-4 layer for M rows ending at position ctx - 1:
+    lightning-indexer scores over ctx / 4 compressed keys (64 index heads of 128), radix-select top-512, and sink-softmax
+    attention of 64 heads of 512 over 128 window rows + the 512 selected rows (K == V)."""
+    from ..ops import dsv4_ops as dk
+    hbm, tf, src = peaks()
+    H, hd, rd, win, ratio, ih, idim, topk = 64, 512, 64, 128, 4, 64, 128, 512
+    n_ent, ring = ctx // ratio, win + M
+    pos = torch.arange(ctx - M, ctx, device="cuda", dtype=torch.int32)
+    ang = torch.rand(ctx + M, rd // 2, device="cuda") * 6.28
+    cos_t, sin_t = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    iq = torch.randn(M, ih, idim, device="cuda").to(torch.bfloat16)
+    ik = torch.randn(n_ent, idim, device="cuda").to(torch.bfloat16)
+    iw = torch.rand(M, ih, device="cuda")
+    q = torch.randn(M, H, hd, device="cuda").to(torch.bfloat16)
+    kv = torch.randn(ring + n_ent, hd, device="cuda").to(torch.bfloat16)
+    sink = torch.zeros(H, device="cuda")
+    score = dk.index_score(iq, ik, iw, pos, ratio, n_ent, 1.0 / (idim ** 0.5 * ih ** 0.5))
+    sel = dk.topk_select(score, topk)
+    out = []
+    us = _time([lambda: dk.index_score(iq, ik, iw, pos, ratio, n_ent, 1.0)], iters)
+    flops = 2.0 * M * ih * n_ent * idim
+    out.append({"op": "dsv4 index_score", "M": M, "entries": n_ent, "us": round(us, 2), "tflops_fp32_simt": round(flops / us / 1e6, 1),
+                "key_bytes_over_time_gbs": round(n_ent * idim * 2 / us / 1e3, 1)})
+    us = _time([lambda: dk.topk_select(score, topk)], iters)
+    nbytes = 5.0 * M * n_ent * 4                                           # five streaming passes over the scores
+    out.append({"op": "topk_select", "M": M, "n": n_ent, "k": topk, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                "frac_of_peak": round(nbytes / us / 1e3 / hbm, 3), "peak": f"{hbm} GB/s copy ({src}); the scores ({M * n_ent * 4 >> 10} KiB) stay in L2"})
+    fn = lambda: dk.sparse_attn(q, kv, pos, sink, cos_t, sin_t, win=win, ring=ring, ratio=ratio, rd=rd, sel=sel)
+    us = _time([fn], iters)
+    flops = 4.0 * M * H * (win + topk) * hd
+    nbytes = M * (win + topk) * hd * 2.0 + 2.0 * M * H * hd * 2
+    out.append({"op": "dsv4 sparse_attn", "M": M, "H": H, "hd": hd, "rows_per_query": win + topk, "us": round(us, 2),
+                "tflops_fp32_simt": round(flops / us / 1e6, 1), "unique_kv_gbs": round(nbytes / us / 1e3, 1),
+                "note": "every head's warp re-reads the query row's KV rows (L1 / L2 hits): 64 x the unique bytes"})
+    return out
+
+
 def bench_matvec(M: int, N: int, K: int, epi: int, iters: int) -> dict:
     hbm, tf, src = peaks()
     ws = [_fp8(N, K) for _ in range(_copies(N * K))]
@@ -110,7 +149,7 @@ def bench_matvec(M: int, N: int, K: int, epi: int, iters: int) -> dict:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "matvec", "attention", "attention-simt"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "matvec", "attention", "attention-simt", "dsv4"])
     ap.add_argument("--ctx", type=int, default=8192, help="attention: position after the chunk's last row")
     ap.add_argument("--heads", default="24,4", help="attention: query heads, KV heads")
     ap.add_argument("--M", type=int, default=512)
@@ -131,6 +170,10 @@ def main() -> int:
             print(json.dumps(r))
             r = bench_matvec(1, n, k, epi, args.iters)
             r["name"] = name
+            print(json.dumps(r))
+        return 0
+    if args.op == "dsv4":
+        for r in bench_dsv4_select_attend(min(args.M, 64), args.ctx, args.iters):
             print(json.dumps(r))
         return 0
     if args.op.startswith("attention"):
