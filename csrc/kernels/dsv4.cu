@@ -16,6 +16,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "../common/pk_common.cuh"
 
 namespace {
@@ -483,26 +485,30 @@ struct SparseAttnParams {
   bf16* out;            // [M, H, hd]
 };
 
-template <int DPL>   // dims per lane: hd = 32 * DPL
+// One warp serves G consecutive heads of a query row: the key row is loaded once per warp and used for all G heads.
+template <int DPL, int G>   // dims per lane: hd = 32 * DPL
 __global__ void __launch_bounds__(256) sparse_attn_kernel(const SparseAttnParams p) {
   constexpr int HD = 32 * DPL;
   const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int hh = blockIdx.y * (blockDim.x >> 5) + warp;
+  const int hh = (blockIdx.y * (blockDim.x >> 5) + warp) * G;     // first head of this warp
   if (hh >= p.H) return;
   const int pos = p.pos[m];
-  float qv[DPL], acc[DPL];
-  {
-    const bf16* q = p.q + ((size_t)m * p.H + hh) * HD + lane * DPL;
+  float qv[G][DPL], acc[G][DPL], mx[G], l[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const int hg = min(hh + g, p.H - 1);     // a warp past the last head repeats it and stores nothing
+    const bf16* q = p.q + ((size_t)m * p.H + hg) * HD + lane * DPL;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
-      qv[i] = __bfloat162float(q[i]) * p.scale;
-      acc[i] = 0.f;
+      qv[g][i] = __bfloat162float(q[i]) * p.scale;
+      acc[g][i] = 0.f;
     }
+    // the sink contributes exp(sink - mx) to the denominator only; without one the running maximum starts at -inf
+    mx[g] = p.sink ? p.sink[hg] : -INFINITY;
+    l[g] = p.sink ? 1.f : 0.f;
   }
   const int nwin = min(pos + 1, p.win);
   const int ncomp = p.mode == 1 ? (pos + 1) / p.ratio : p.mode == 2 ? p.ksel : 0;
-  // the sink contributes exp(sink - mx) to the denominator only; without one the running maximum starts at -inf
-  float mx = p.sink ? p.sink[hh] : -INFINITY, l = p.sink ? 1.f : 0.f;
   for (int r = 0; r < nwin + ncomp; ++r) {
     int row;
     if (r < nwin) {
@@ -515,43 +521,79 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(const SparseAttnParams
       row = p.ring + c;
     }
     const bf16* k = p.kv + (size_t)row * HD + lane * DPL;
-    float kf[DPL], dot = 0.f;
+    float kf[DPL], dot[G];
+    uint32_t kw[DPL / 2];
+    // a lane's DPL * 2 bytes start on a multiple of their own size: 16-byte loads where that size allows
+    if constexpr (DPL % 8 == 0) {
+#pragma unroll
+      for (int v = 0; v < DPL / 8; ++v) {
+        const uint4 t = reinterpret_cast<const uint4*>(k)[v];
+        kw[4 * v] = t.x; kw[4 * v + 1] = t.y; kw[4 * v + 2] = t.z; kw[4 * v + 3] = t.w;
+      }
+    } else if constexpr (DPL % 4 == 0) {
+#pragma unroll
+      for (int v = 0; v < DPL / 4; ++v) {
+        const uint2 t = reinterpret_cast<const uint2*>(k)[v];
+        kw[2 * v] = t.x; kw[2 * v + 1] = t.y;
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < DPL / 2; ++v) kw[v] = reinterpret_cast<const uint32_t*>(k)[v];
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) dot[g] = 0.f;
 #pragma unroll
     for (int i = 0; i < DPL; i += 2) {
-      const uint32_t u = *reinterpret_cast<const uint32_t*>(k + i);
+      const uint32_t u = kw[i >> 1];
       kf[i] = __uint_as_float(u << 16);
       kf[i + 1] = __uint_as_float(u & 0xffff0000u);
-      dot += qv[i] * kf[i] + qv[i + 1] * kf[i + 1];
+#pragma unroll
+      for (int g = 0; g < G; ++g) dot[g] += qv[g][i] * kf[i] + qv[g][i + 1] * kf[i + 1];
     }
-    dot = warp_sum(dot);
-    const float nm = fmaxf(mx, dot), cs = __expf(mx - nm), e = __expf(dot - nm);
-    l = l * cs + e;
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) acc[i] = acc[i] * cs + e * kf[i];
-    mx = nm;
-  }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int g = 0; g < G; ++g) {
+      const float d = warp_sum(dot[g]);
+      // d is the same in every lane, so the branch is uniform: most keys do not raise the maximum
+      if (d > mx[g]) {
+        const float cs = __expf(mx[g] - d);
+        l[g] = l[g] * cs + 1.f;
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) acc[i] *= inv;
-  // inverse RoPE on the last rd dims (pairs never straddle lanes: DPL is even)
-  const int off = HD - p.rd, half = p.rd / 2;
-  if (lane * DPL + DPL > off) {
+        for (int i = 0; i < DPL; ++i) acc[g][i] = acc[g][i] * cs + kf[i];
+        mx[g] = d;
+      } else {
+        const float e = __expf(d - mx[g]);
+        l[g] += e;
 #pragma unroll
-    for (int i = 0; i < DPL; i += 2) {
-      const int d = lane * DPL + i;
-      if (d >= off) {
-        const int pi = (d - off) >> 1;
-        const int rp = p.rope_pos ? p.rope_pos[m] : pos;
-        const float c = p.cos_t[(size_t)rp * half + pi], s = -p.sin_t[(size_t)rp * half + pi];
-        const float a = acc[i], b = acc[i + 1];
-        acc[i] = a * c - b * s;
-        acc[i + 1] = a * s + b * c;
+        for (int i = 0; i < DPL; ++i) acc[g][i] = fmaf(e, kf[i], acc[g][i]);
       }
     }
   }
-  bf16* o = p.out + ((size_t)m * p.H + hh) * HD + lane * DPL;
+  // inverse RoPE on the last rd dims (pairs never straddle lanes: DPL is even)
+  const int off = HD - p.rd, half = p.rd / 2;
+  const int rp = p.rope_pos ? p.rope_pos[m] : pos;
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) o[i] = __float2bfloat16(acc[i]);
+  for (int g = 0; g < G; ++g) {
+    if (hh + g >= p.H) break;
+    const float inv = l[g] > 0.f ? 1.f / l[g] : 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[g][i] *= inv;
+    if (lane * DPL + DPL > off) {
+#pragma unroll
+      for (int i = 0; i < DPL; i += 2) {
+        const int d = lane * DPL + i;
+        if (d >= off) {
+          const int pi = (d - off) >> 1;
+          const float c = p.cos_t[(size_t)rp * half + pi], s = -p.sin_t[(size_t)rp * half + pi];
+          const float a = acc[g][i], b = acc[g][i + 1];
+          acc[g][i] = a * c - b * s;
+          acc[g][i + 1] = a * s + b * c;
+        }
+      }
+    }
+    bf16* o = p.out + ((size_t)m * p.H + hh + g) * HD + lane * DPL;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[i] = __float2bfloat16(acc[g][i]);
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -698,15 +740,34 @@ PK_API int pk_dsv4_sparse_attn_ex(const void* q, const void* kv, const int* pos,
   // mode 1 with ratio 1 is dense causal attention, mode 2 attends the selected rows; sink may be null then
   if (M < 1 || H < 1 || win < 0 || ring < win || (win == 0 && mode == 0) || (mode == 2 && sel == nullptr) || (mode == 1 && ratio < 1)) return PK_ERR_BAD_ARG;
   if (sink == nullptr && win > 0) return PK_ERR_BAD_ARG;
+  if (((uintptr_t)kv & 15) != 0 || ((uintptr_t)q & 3) != 0) return PK_ERR_BAD_ARG;     // key rows are read with 16-byte loads
   SparseAttnParams p{(const pk::bf16*)q, (const pk::bf16*)kv, pos, rope_pos, sel, sink, cos_t, sin_t, H, win, ring, ratio, mode, ksel, rd,
                      scale, (pk::bf16*)out};
-  const int wpb = H >= 8 ? 8 : H;
-  const dim3 grid(M, (H + wpb - 1) / wpb);
-  if (hd == 512) sparse_attn_kernel<16><<<grid, wpb * 32, 0, stream>>>(p);
-  else if (hd == 128) sparse_attn_kernel<4><<<grid, wpb * 32, 0, stream>>>(p);
-  else if (hd == 576) sparse_attn_kernel<18><<<grid, wpb * 32, 0, stream>>>(p);     // MLA latent 512 + rope 64 (GLM-DSA)
-  else if (hd == 320) sparse_attn_kernel<10><<<grid, wpb * 32, 0, stream>>>(p);     // latent 256 + rope 64 (toy shapes)
-  else return PK_ERR_UNSUPPORTED;
+  // Heads per warp (the key row is read once for all of them): measured at 64 rows x 64 heads x 640 keys of 512,
+  // one head per warp 380 us, two 427 us, four 647 us (the registers of the extra accumulators cost more residency
+  // than the shared loads save once the row is read with 16-byte loads), so one is the default;
+  // POCKET_SPARSE_ATTN_G = 2 or 4 selects the others.
+  static const int forced_g = [] {
+    const char* e = getenv("POCKET_SPARSE_ATTN_G");
+    return e ? atoi(e) : 0;
+  }();
+  int G = 1;
+  if ((forced_g == 1 || forced_g == 2 || forced_g == 4) && H % forced_g == 0) G = forced_g;
+  const int warps_needed = H / G;
+  const int wpb = warps_needed >= 4 ? 4 : warps_needed;
+  const dim3 grid(M, (warps_needed + wpb - 1) / wpb);
+#define PK_SPARSE_ATTN_LAUNCH(GG)                                                                                  \
+  do {                                                                                                             \
+    if (hd == 512) sparse_attn_kernel<16, GG><<<grid, wpb * 32, 0, stream>>>(p);                                   \
+    else if (hd == 128) sparse_attn_kernel<4, GG><<<grid, wpb * 32, 0, stream>>>(p);                               \
+    else if (hd == 576) sparse_attn_kernel<18, GG><<<grid, wpb * 32, 0, stream>>>(p); /* MLA latent 512 + rope 64 */ \
+    else if (hd == 320) sparse_attn_kernel<10, GG><<<grid, wpb * 32, 0, stream>>>(p); /* latent 256 + rope 64 */    \
+    else return PK_ERR_UNSUPPORTED;                                                                                \
+  } while (0)
+  if (G == 4) PK_SPARSE_ATTN_LAUNCH(4);
+  else if (G == 2) PK_SPARSE_ATTN_LAUNCH(2);
+  else PK_SPARSE_ATTN_LAUNCH(1);
+#undef PK_SPARSE_ATTN_LAUNCH
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
