@@ -13,6 +13,7 @@
 // (cpp_engine/cuda/qwen_half_ops.cu:858-930, one 128-float state column per thread).
 //
 // All matrix products here are fp32 SIMT; they are the next candidates for tcgen05 tiles.
+#include <cstdlib>
 #include "../common/pk_common.cuh"
 
 namespace {
@@ -207,101 +208,152 @@ struct StateParams {
   float* O;      // [Tpad, Hv, 128]
 };
 
-constexpr int SL = 32;  // state columns per block
+constexpr int SL = 32;   // state columns per block
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
-__global__ void __launch_bounds__(256) deltanet_state_kernel(const StateParams p) {
-  extern __shared__ float smem[];
+// ST threads per block: with 512 (16 warps) warp w owns 4 chunk rows and 8 state rows, with 256 it owns 8 and 16.
+// One block per SM (137 KB of shared memory). The three operand tiles of a chunk (W, q, k: 32 KB each) and P arrive by
+// cp.async straight into the buffer that the matching phase of the PREVIOUS chunk has just finished with, so every load
+// has two phases of arithmetic to land in: W(c+1) is issued after the Delta phase of chunk c, q and P after the output
+// phase, k after the state phase. Three groups are always in flight in that order, so "all but the two newest groups
+// have landed" is the right wait before every phase. q and k stay unscaled in shared memory: e^{G_i} multiplies the
+// q.S sums, e^{G_C - G_j} multiplies Delta_j on the way into the state update.
+// Before: loads, then arithmetic, per chunk (20 us per chunk step, a third of it exposed load latency).
+template <int ST>
+__global__ void __launch_bounds__(ST) deltanet_state_kernel(const StateParams p) {
+  constexpr int RW = CH / (ST / 32);   // chunk rows per warp
+  constexpr int SW = D / (ST / 32);    // state rows per warp
+  extern __shared__ __align__(16) float smem[];
   float* Ws = smem;               // [64][128]
-  float* Qe = Ws + CH * D;        // [64][128]  e^{G_i} q_i
-  float* Kd = Qe + CH * D;        // [64][128]  e^{G_C - G_i} k_i
-  float* Ps = Kd + CH * D;        // [64][64]
-  float* Us = Ps + CH * CH;       // [64][32]
-  float* Ds = Us + CH * SL;       // [64][32]   Delta
+  float* Qs = Ws + CH * D;        // [64][128]  q_i (unscaled)
+  float* Ks = Qs + CH * D;        // [64][128]  k_i (unscaled)
+  float* Ps = Ks + CH * D;        // [64][64]
+  float* Ds = Ps + CH * CH;       // [64][32]   Delta
   float* Ss = Ds + CH * SL;       // [128][32]  state slice
   float* Gs = Ss + D * SL;        // [64]
+  float* Eq = Gs + CH;            // [64] e^{G_i}
+  float* Ek = Eq + CH;            // [64] e^{G_C - G_i}
   const int h = blockIdx.x, sl = blockIdx.y, tid = threadIdx.x;
   const int hk = h / (p.Hv / p.Hk);
   const int tx = tid & 31, ty = tid >> 5;
   float* sp = p.state + (size_t)h * D * D + sl * SL;
-  for (int i = tid; i < D * SL; i += 256) Ss[i] = sp[(size_t)(i >> 5) * D + (i & 31)];
+
+  auto issue_w = [&](int c) {
+    if (c < p.nchunks) {
+      const float* src = p.W + ((size_t)h * p.Tpad + (size_t)c * CH) * D;
+      for (int i = tid; i < CH * D / 4; i += ST) cp_async16(Ws + i * 4, src + i * 4);
+    }
+    cp_async_commit();
+  };
+  auto issue_qp = [&](int c) {
+    if (c < p.nchunks) {
+      for (int i = tid; i < CH * D / 4; i += ST) {
+        const int r = i >> 5, d4 = (i & 31) * 4;
+        cp_async16(Qs + r * D + d4, p.qn + ((size_t)(c * CH + r) * p.Hk + hk) * D + d4);
+      }
+      const float* src = p.P + (((size_t)h * p.nchunks + c) * CH) * CH;
+      for (int i = tid; i < CH * CH / 4; i += ST) cp_async16(Ps + i * 4, src + i * 4);
+    }
+    cp_async_commit();
+  };
+  auto issue_k = [&](int c) {
+    if (c < p.nchunks) {
+      for (int i = tid; i < CH * D / 4; i += ST) {
+        const int r = i >> 5, d4 = (i & 31) * 4;
+        cp_async16(Ks + r * D + d4, p.kn + ((size_t)(c * CH + r) * p.Hk + hk) * D + d4);
+      }
+    }
+    cp_async_commit();
+  };
+
+  issue_w(0);
+  issue_qp(0);
+  issue_k(0);
+  for (int i = tid; i < D * SL; i += ST) Ss[i] = sp[(size_t)(i >> 5) * D + (i & 31)];
+  float gnext = tid < CH ? p.G[(size_t)h * p.Tpad + tid] : 0.f;
 
   for (int c = 0; c < p.nchunks; ++c) {
     const int t0 = c * CH;
-    __syncthreads();
-    if (tid < CH) Gs[tid] = p.G[(size_t)h * p.Tpad + t0 + tid];
+    if (tid < CH) Gs[tid] = gnext;
+    if (tid < CH && c + 1 < p.nchunks) gnext = p.G[(size_t)h * p.Tpad + t0 + CH + tid];
+    float acc[RW];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) acc[r] = p.U[((size_t)h * p.Tpad + t0 + ty * RW + r) * D + sl * SL + tx];
     __syncthreads();
     const float gC = Gs[CH - 1];
-    for (int i = tid; i < CH * D / 4; i += 256) {
-      const int r = i >> 5, d4 = (i & 31) * 4;
-      *reinterpret_cast<float4*>(Ws + r * D + d4) =
-          *reinterpret_cast<const float4*>(p.W + ((size_t)h * p.Tpad + t0 + r) * D + d4);
-      float4 q = *reinterpret_cast<const float4*>(p.qn + ((size_t)(t0 + r) * p.Hk + hk) * D + d4);
-      float4 k = *reinterpret_cast<const float4*>(p.kn + ((size_t)(t0 + r) * p.Hk + hk) * D + d4);
-      const float eq = __expf(Gs[r]), ek = __expf(gC - Gs[r]);
-      q.x *= eq; q.y *= eq; q.z *= eq; q.w *= eq;
-      k.x *= ek; k.y *= ek; k.z *= ek; k.w *= ek;
-      *reinterpret_cast<float4*>(Qe + r * D + d4) = q;
-      *reinterpret_cast<float4*>(Kd + r * D + d4) = k;
+    if (tid < CH) {
+      Eq[tid] = __expf(Gs[tid]);
+      Ek[tid] = __expf(gC - Gs[tid]);
     }
-    for (int i = tid; i < CH * CH / 4; i += 256)
-      *reinterpret_cast<float4*>(Ps + i * 4) =
-          *reinterpret_cast<const float4*>(p.P + (((size_t)h * p.nchunks + c) * CH) * CH + i * 4);
-    for (int i = tid; i < CH * SL; i += 256)
-      Us[i] = p.U[((size_t)h * p.Tpad + t0 + (i >> 5)) * D + sl * SL + (i & 31)];
+    cp_async_wait<2>();   // W of this chunk
     __syncthreads();
 
-    // Delta = U - W S, rows ty*8 .. ty*8+7
-    float acc[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r] = Us[(ty * 8 + r) * SL + tx];
+    // Delta = U - W S, rows ty*RW .. ty*RW+RW-1
     for (int k = 0; k < D; k += 4) {
       const float s0 = Ss[(k + 0) * SL + tx], s1 = Ss[(k + 1) * SL + tx], s2 = Ss[(k + 2) * SL + tx],
                   s3 = Ss[(k + 3) * SL + tx];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float4 w = *reinterpret_cast<const float4*>(Ws + (ty * 8 + r) * D + k);
+      for (int r = 0; r < RW; ++r) {
+        const float4 w = *reinterpret_cast<const float4*>(Ws + (ty * RW + r) * D + k);
         acc[r] -= w.x * s0 + w.y * s1 + w.z * s2 + w.w * s3;
       }
     }
 #pragma unroll
-    for (int r = 0; r < 8; ++r) Ds[(ty * 8 + r) * SL + tx] = acc[r];
+    for (int r = 0; r < RW; ++r) Ds[(ty * RW + r) * SL + tx] = acc[r];
+    __syncthreads();
+    issue_w(c + 1);       // Ws is free
+    cp_async_wait<2>();   // q and P of this chunk
     __syncthreads();
 
-    // O = Qe S + P Delta
+    // O = e^{G} (q S) + P Delta
 #pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+    for (int r = 0; r < RW; ++r) acc[r] = 0.f;
     for (int k = 0; k < D; k += 4) {
       const float s0 = Ss[(k + 0) * SL + tx], s1 = Ss[(k + 1) * SL + tx], s2 = Ss[(k + 2) * SL + tx],
                   s3 = Ss[(k + 3) * SL + tx];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float4 w = *reinterpret_cast<const float4*>(Qe + (ty * 8 + r) * D + k);
+      for (int r = 0; r < RW; ++r) {
+        const float4 w = *reinterpret_cast<const float4*>(Qs + (ty * RW + r) * D + k);
         acc[r] += w.x * s0 + w.y * s1 + w.z * s2 + w.w * s3;
       }
     }
+#pragma unroll
+    for (int r = 0; r < RW; ++r) acc[r] *= Eq[ty * RW + r];
     for (int j = 0; j < CH; j += 4) {
       const float d0 = Ds[(j + 0) * SL + tx], d1 = Ds[(j + 1) * SL + tx], d2 = Ds[(j + 2) * SL + tx],
                   d3 = Ds[(j + 3) * SL + tx];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float4 w = *reinterpret_cast<const float4*>(Ps + (ty * 8 + r) * CH + j);
+      for (int r = 0; r < RW; ++r) {
+        const float4 w = *reinterpret_cast<const float4*>(Ps + (ty * RW + r) * CH + j);
         acc[r] += w.x * d0 + w.y * d1 + w.z * d2 + w.w * d3;
       }
     }
 #pragma unroll
-    for (int r = 0; r < 8; ++r)
-      p.O[((size_t)(t0 + ty * 8 + r) * p.Hv + h) * D + sl * SL + tx] = acc[r];
+    for (int r = 0; r < RW; ++r)
+      p.O[((size_t)(t0 + ty * RW + r) * p.Hv + h) * D + sl * SL + tx] = acc[r];
+    __syncthreads();
+    issue_qp(c + 1);      // Qs and Ps are free
+    cp_async_wait<2>();   // k of this chunk
+    __syncthreads();
 
-    // S <- e^{G_C} S + Kd^T Delta, rows ty*16 .. ty*16+15
-    float sn[16];
+    // S <- e^{G_C} S + k^T (e^{G_C - G} Delta), rows ty*SW .. ty*SW+SW-1
+    float sn[SW];
     const float eC = __expf(gC);
 #pragma unroll
-    for (int r = 0; r < 16; ++r) sn[r] = eC * Ss[(ty * 16 + r) * SL + tx];
+    for (int r = 0; r < SW; ++r) sn[r] = eC * Ss[(ty * SW + r) * SL + tx];
     for (int j = 0; j < CH; ++j) {
-      const float dj = Ds[j * SL + tx];
+      const float dj = Ds[j * SL + tx] * Ek[j];
 #pragma unroll
-      for (int r4 = 0; r4 < 4; ++r4) {
-        const float4 k = *reinterpret_cast<const float4*>(Kd + j * D + ty * 16 + r4 * 4);
+      for (int r4 = 0; r4 < SW / 4; ++r4) {
+        const float4 k = *reinterpret_cast<const float4*>(Ks + j * D + ty * SW + r4 * 4);
         sn[r4 * 4 + 0] = fmaf(k.x, dj, sn[r4 * 4 + 0]);
         sn[r4 * 4 + 1] = fmaf(k.y, dj, sn[r4 * 4 + 1]);
         sn[r4 * 4 + 2] = fmaf(k.z, dj, sn[r4 * 4 + 2]);
@@ -310,10 +362,12 @@ __global__ void __launch_bounds__(256) deltanet_state_kernel(const StateParams p
     }
     __syncthreads();
 #pragma unroll
-    for (int r = 0; r < 16; ++r) Ss[(ty * 16 + r) * SL + tx] = sn[r];
+    for (int r = 0; r < SW; ++r) Ss[(ty * SW + r) * SL + tx] = sn[r];
+    issue_k(c + 1);       // Ks is free
+    __syncthreads();
   }
-  __syncthreads();
-  for (int i = tid; i < D * SL; i += 256) sp[(size_t)(i >> 5) * D + (i & 31)] = Ss[i];
+  cp_async_wait<0>();
+  for (int i = tid; i < D * SL; i += ST) sp[(size_t)(i >> 5) * D + (i & 31)] = Ss[i];
 }
 
 // ---------------------------------------------------------------------------------------
@@ -348,7 +402,7 @@ PK_API int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, i
                                const float* dt_bias, const float* norm_w, float eps, float* state, void* out,
                                float* ws, cudaStream_t stream) {
   if (key_dim != D || value_dim != D) return PK_ERR_UNSUPPORTED;
-  if (T < 1 || key_heads < 1 || value_heads % key_heads != 0) return PK_ERR_BAD_ARG;
+  if (T < 1 || key_heads < 1 || value_heads % key_heads != 0 || ((uintptr_t)ws & 15) != 0) return PK_ERR_BAD_ARG;   // cp.async of 16 bytes
   const int rep = value_heads / key_heads;
   if (rep > 2) return PK_ERR_UNSUPPORTED;
   const int nchunks = (T + CH - 1) / CH, Tpad = nchunks * CH;
@@ -373,10 +427,11 @@ PK_API int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, i
 
   static PkDeviceOnce once;
   const size_t smem_chunk = (size_t)(2 * CH * KS + CH * CH + 2 * CH) * sizeof(float);
-  const size_t smem_state = (size_t)(3 * CH * D + CH * CH + 2 * CH * SL + D * SL + CH) * sizeof(float);
+  const size_t smem_state = (size_t)(3 * CH * D + CH * CH + CH * SL + D * SL + 3 * CH) * sizeof(float);
   if (PkDeviceOnceGuard once_guard{once}; once_guard.needed()) {
     if (cudaFuncSetAttribute(deltanet_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_chunk) != cudaSuccess ||
-        cudaFuncSetAttribute(deltanet_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state) != cudaSuccess) {
+        cudaFuncSetAttribute(deltanet_state_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state) != cudaSuccess ||
+        cudaFuncSetAttribute(deltanet_state_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state) != cudaSuccess) {
       pk_set_last_cuda_error((int)cudaGetLastError());
       return PK_ERR_CUDA;
     }
@@ -386,7 +441,12 @@ PK_API int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, i
   deltanet_chunk_kernel<<<dim3(nchunks, value_heads), 256, smem_chunk, stream>>>(cp);
   PK_CHECK_LAUNCH();
   StateParams sp{qn, kn, U, W, P, G, key_heads, value_heads, Tpad, nchunks, state, O};
-  deltanet_state_kernel<<<dim3(value_heads, D / SL), 256, smem_state, stream>>>(sp);
+  static const int state_threads = [] {
+    const char* e = getenv("POCKET_DELTANET_STATE_THREADS");
+    return e && atoi(e) == 256 ? 256 : 512;
+  }();
+  if (state_threads == 256) deltanet_state_kernel<256><<<dim3(value_heads, D / SL), 256, smem_state, stream>>>(sp);
+  else deltanet_state_kernel<512><<<dim3(value_heads, D / SL), 512, smem_state, stream>>>(sp);
   PK_CHECK_LAUNCH();
   deltanet_out_kernel<<<dim3(T, value_heads), 128, 0, stream>>>(O, (const pk::bf16*)proj, ld, key_heads, value_heads,
                                                               norm_w, eps, (pk::bf16*)out);
