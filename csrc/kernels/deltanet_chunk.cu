@@ -41,35 +41,42 @@ struct PrepParams {
   float* beta;  // [Tpad, Hv]
 };
 
-__device__ __forceinline__ float conv_input(const PrepParams& p, int t, int ch) {
-  return t >= 0 ? __bfloat162float(p.proj[(size_t)t * p.ld + ch]) : p.conv_state[(size_t)ch * 3 + (3 + t)];
+// Inputs of channels ch and ch + 1 (ch even) at time t: the projection row, or the remembered tail for t < 0.
+__device__ __forceinline__ float2 conv_input2(const PrepParams& p, int t, int ch) {
+  if (t >= 0) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.proj + (size_t)t * p.ld + ch));
+  return make_float2(p.conv_state[(size_t)ch * 3 + (3 + t)], p.conv_state[(size_t)(ch + 1) * 3 + (3 + t)]);
 }
 
-__global__ void __launch_bounds__(512) deltanet_prep_kernel(const PrepParams p) {
+// One block per (token, key head): 64 threads per 128-channel segment (q, k, then the head's value heads), two
+// adjacent channels per thread.
+__global__ void __launch_bounds__(256) deltanet_prep_kernel(const PrepParams p) {
   const int t = blockIdx.x, hk = blockIdx.y;
   const int rep = p.Hv / p.Hk;
-  const int seg = threadIdx.x >> 7, d = threadIdx.x & 127;  // seg 0: q, 1: k, 2+: value heads
+  const int seg = threadIdx.x >> 6, d = (threadIdx.x & 63) * 2;  // seg 0: q, 1: k, 2+: value heads
   const int KD = p.Hk * D, VD = p.Hv * D;
-  __shared__ float s_sum[4][4];
+  __shared__ float s_sum[4][2];
   const int h = hk * rep + (seg - 2);
-  float y = 0.f;
+  float y0 = 0.f, y1 = 0.f;
   if (t < p.T) {
     const int ch = seg == 0 ? hk * D + d : seg == 1 ? KD + hk * D + d : 2 * KD + h * D + d;
-    const float4 w = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch * 4);
-    y = w.x * conv_input(p, t - 3, ch) + w.y * conv_input(p, t - 2, ch) + w.z * conv_input(p, t - 1, ch) +
-        w.w * conv_input(p, t, ch);
-    y = __bfloat162float(__float2bfloat16(silu(y)));
+    const float4 w0 = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch * 4);
+    const float4 w1 = *reinterpret_cast<const float4*>(p.conv_w + (size_t)(ch + 1) * 4);
+    const float2 a = conv_input2(p, t - 3, ch), b = conv_input2(p, t - 2, ch), c = conv_input2(p, t - 1, ch), e = conv_input2(p, t, ch);
+    y0 = w0.x * a.x + w0.y * b.x + w0.z * c.x + w0.w * e.x;
+    y1 = w1.x * a.y + w1.y * b.y + w1.z * c.y + w1.w * e.y;
+    y0 = __bfloat162float(__float2bfloat16(silu(y0)));
+    y1 = __bfloat162float(__float2bfloat16(silu(y1)));
   }
-  const float ss = warp_sum(y * y);
-  if ((threadIdx.x & 31) == 0) s_sum[seg][(threadIdx.x >> 5) & 3] = ss;
+  const float ss = warp_sum(y0 * y0 + y1 * y1);
+  if ((threadIdx.x & 31) == 0) s_sum[seg][(threadIdx.x >> 5) & 1] = ss;
   __syncthreads();
   if (seg < 2) {
-    const float tot = s_sum[seg][0] + s_sum[seg][1] + s_sum[seg][2] + s_sum[seg][3];
+    const float tot = s_sum[seg][0] + s_sum[seg][1];
     const float n = rsqrtf(tot + 1e-6f) * (seg == 0 ? rsqrtf((float)D) : 1.f);
     float* dst = (seg == 0 ? p.qn : p.kn) + ((size_t)t * p.Hk + hk) * D + d;
-    *dst = y * n;
+    *reinterpret_cast<float2*>(dst) = make_float2(y0 * n, y1 * n);
   } else {
-    p.v[((size_t)t * p.Hv + h) * D + d] = y;
+    *reinterpret_cast<float2*>(p.v + ((size_t)t * p.Hv + h) * D + d) = make_float2(y0, y1);
     if (d == 0) {
       float gg = 0.f, bb = 0.f;
       if (t < p.T) {
@@ -373,15 +380,26 @@ __global__ void __launch_bounds__(ST) deltanet_state_kernel(const StateParams p)
 // ---------------------------------------------------------------------------------------
 // gated RMSNorm of the scan output
 
-__global__ void __launch_bounds__(128) deltanet_out_kernel(const float* O, const bf16* proj, int ld, int Hk, int Hv,
+// One warp per (token, value head), four channels per lane.
+__global__ void __launch_bounds__(256) deltanet_out_kernel(const float* O, const bf16* proj, int ld, int Hk, int Hv, int T,
                                                            const float* norm_w, float eps, bf16* out) {
-  const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-  __shared__ float red[40];
-  const float o = O[((size_t)t * Hv + h) * D + d];
-  const float ss = block_sum(o * o, red);
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= T * Hv) return;
+  const int t = unit / Hv, h = unit - t * Hv, d = (threadIdx.x & 31) * 4;
+  const float4 o = *reinterpret_cast<const float4*>(O + ((size_t)t * Hv + h) * D + d);
+  const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
   const int KD = Hk * D, VD = Hv * D;
-  const float z = __bfloat162float(proj[(size_t)t * ld + 2 * KD + VD + h * D + d]);
-  out[(size_t)t * VD + h * D + d] = __float2bfloat16(o * rsqrtf(ss / (float)D + eps) * norm_w[d] * silu(z));
+  const uint2 zr = *reinterpret_cast<const uint2*>(proj + (size_t)t * ld + 2 * KD + VD + h * D + d);
+  const float z0 = __uint_as_float(zr.x << 16), z1 = __uint_as_float(zr.x & 0xffff0000u), z2 = __uint_as_float(zr.y << 16),
+              z3 = __uint_as_float(zr.y & 0xffff0000u);
+  const float4 w = *reinterpret_cast<const float4*>(norm_w + d);
+  const float r = rsqrtf(ss / (float)D + eps);
+  __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * r * w.x * silu(z0), o.y * r * w.y * silu(z1));
+  __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * r * w.z * silu(z2), o.w * r * w.w * silu(z3));
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(out + (size_t)t * VD + h * D + d) = packed;
 }
 
 }  // namespace
@@ -403,6 +421,7 @@ PK_API int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, i
                                float* ws, cudaStream_t stream) {
   if (key_dim != D || value_dim != D) return PK_ERR_UNSUPPORTED;
   if (T < 1 || key_heads < 1 || value_heads % key_heads != 0 || ((uintptr_t)ws & 15) != 0) return PK_ERR_BAD_ARG;   // cp.async of 16 bytes
+  if ((ld & 3) != 0 || ((uintptr_t)proj & 7) != 0 || ((uintptr_t)out & 7) != 0 || ((uintptr_t)norm_w & 15) != 0) return PK_ERR_BAD_ARG;   // 8-byte row accesses
   const int rep = value_heads / key_heads;
   if (rep > 2) return PK_ERR_UNSUPPORTED;
   const int nchunks = (T + CH - 1) / CH, Tpad = nchunks * CH;
@@ -419,7 +438,7 @@ PK_API int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, i
 
   PrepParams pp{(const pk::bf16*)proj, ld, T, Tpad, key_heads, value_heads, conv_w, conv_state, A_log, dt_bias,
                 qn, kn, v, g, beta};
-  deltanet_prep_kernel<<<dim3(Tpad, key_heads), 128 * (2 + rep), 0, stream>>>(pp);
+  deltanet_prep_kernel<<<dim3(Tpad, key_heads), 64 * (2 + rep), 0, stream>>>(pp);
   PK_CHECK_LAUNCH();
   const int channels = (2 * key_heads + value_heads) * D;
   deltanet_tail_kernel<<<(channels + 255) / 256, 256, 0, stream>>>((const pk::bf16*)proj, ld, T, channels, conv_state);
@@ -448,8 +467,8 @@ PK_API int pk_deltanet_chunked(const void* proj, int ld, int T, int key_heads, i
   if (state_threads == 256) deltanet_state_kernel<256><<<dim3(value_heads, D / SL), 256, smem_state, stream>>>(sp);
   else deltanet_state_kernel<512><<<dim3(value_heads, D / SL), 512, smem_state, stream>>>(sp);
   PK_CHECK_LAUNCH();
-  deltanet_out_kernel<<<dim3(T, value_heads), 128, 0, stream>>>(O, (const pk::bf16*)proj, ld, key_heads, value_heads,
-                                                              norm_w, eps, (pk::bf16*)out);
+  deltanet_out_kernel<<<(T * value_heads + 7) / 8, 256, 0, stream>>>(O, (const pk::bf16*)proj, ld, key_heads, value_heads, T,
+                                                                     norm_w, eps, (pk::bf16*)out);
   PK_CHECK_LAUNCH();
   return PK_OK;
 }
