@@ -83,6 +83,8 @@ int pk_cand_push(const float* val, const int* idx, int M, const PkPush* push, fl
 int pk_cand_merge_wait(const float* cand_val, const int* cand_idx, int M, int world, const PkWait* wait,
                        int* out_idx, uint32_t* status, int stride, cudaStream_t stream);
 int pk_fp8_to_bf16(const void* w, const float* scale, int N, int K, void* out, cudaStream_t stream);
+int pk_rmsnorm_quant(const void* x, int M, int K, const float* gamma, int mode, float eps, void* y, int terms, void* q, int m_pad,
+                     float* scale_t, int s_ld, cudaStream_t stream);
 int pk_quant_act_fp8(const void* x, int ldx, int M, int K, int terms, void* q, int m_pad, float* scale_t, int s_ld, cudaStream_t stream);
 int pk_gemm_fp8(const void* Aq, int terms, int m_pad, const float* a_scale, int a_ld, const void* W, const float* w_scale, int M, int N,
                 int K, int epi, void* C, const void* resid, int ldc, uint32_t* status, const PkPush* push, int sm_count, cudaStream_t stream);

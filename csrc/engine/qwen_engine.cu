@@ -1075,11 +1075,16 @@ void QwenEngine::run_chunk(int M, bool mtp) {
   int pending = -1;  // site whose partial sums still wait to be added to the residual stream
   // Native FP8: quantise the rows of A (one or two E4M3 terms per value, a scale per row and 128-wide k block), then run
   // tcgen05 kind::f8f6f4 on them and on the stored weight codes. Shapes the kernel does not take fall through.
+  // true while act_q_ / act_scale_ hold the quantised rows of xn_ (written by the norm kernel itself)
+  bool xn_quantised = false;
   auto gemm_native = [&](const void* A, int lda, const Fp8Linear& w, int epi, void* C, const void* resid, int ldc, const PkPush* ps) -> bool {
     if (act_q_ == nullptr || w.w == nullptr || w.scale == nullptr || (w.K & 127) != 0 || (lda & 3) != 0 || M > act_rows_) return false;   // bf16-only linears have no codes
     if (epi == 1 && ((w.N >> 1) & 127) != 0) return false;
     const int terms = gemm_mode_ == 3 ? 1 : 2;
-    check(pk_quant_act_fp8(A, lda, M, w.K, terms, act_q_, act_rows_, act_scale_, act_rows_, stream_), "quant_act_fp8");
+    if (!(xn_quantised && A == xn_ && lda == hidden_ && w.K == hidden_)) {
+      check(pk_quant_act_fp8(A, lda, M, w.K, terms, act_q_, act_rows_, act_scale_, act_rows_, stream_), "quant_act_fp8");
+      xn_quantised = false;
+    }
     check(pk_gemm_fp8(act_q_, terms, act_rows_, act_scale_, act_rows_, w.w, w.scale, M, w.N, w.K, epi, C, resid, ldc, gemm_status_, ps, sm_count_,
                       stream_), "gemm_fp8");
     return true;
@@ -1138,8 +1143,14 @@ void QwenEngine::run_chunk(int M, bool mtp) {
       if (y != nullptr && y != xn_)
         cuda_check(cudaMemcpyAsync(y, xn_, (size_t)M * hidden_ * 2, cudaMemcpyDeviceToDevice, stream_), "copy normalised rows");
       pending = -1;
+    } else if (y == xn_ && act_q_ != nullptr && (gemm_mode_ == 2 || gemm_mode_ == 3) && (hidden_ & 127) == 0 && M <= act_rows_) {
+      // the rows feed a native FP8 GEMM next: the norm kernel quantises them on the way out
+      check(pk_rmsnorm_quant(hid, M, hidden_, gamma, 1, eps, y, gemm_mode_ == 3 ? 1 : 2, act_q_, act_rows_, act_scale_, act_rows_, stream_),
+            "rmsnorm(+quantise)");
+      xn_quantised = true;
     } else {
       check(pk_rmsnorm(hid, nullptr, 0, M, hidden_, nullptr, gamma, 1, eps, y, nullptr, stream_), "rmsnorm");
+      xn_quantised = false;
     }
   };
   for (int i = 0; i < n_layers; ++i) {

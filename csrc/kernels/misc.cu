@@ -2,6 +2,8 @@
 // SwiGLU, argmax / top-k candidates over fp32 logits, epoch bump for the comm protocol.
 // Reference counterparts: cpp_engine/cuda/qwen_half_ops.cu:693-709 (rmsnorm, (1+gamma)),
 // 1529 (embedding), cpp_engine/cuda/cuda_ops.cu:40-128 (argmax_fp32, argmax_fp32_rows).
+#include <cuda_fp8.h>
+
 #include "../common/pk_comm.cuh"
 #include "../common/pk_common.cuh"
 
@@ -61,6 +63,85 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const NormParams p) {
   for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
     const float g = p.gamma[k];
     p.y[(size_t)m * p.K + k] = __float2bfloat16(row[k] * r * (p.mode == 1 ? 1.f + g : g));
+  }
+}
+
+// RMSNorm of bf16 rows with 16-byte accesses, optionally followed in the same kernel by the activation quantisation
+// of the native FP8 GEMM (the layout and arithmetic of quant_act_fp8_kernel in gemm_fp8.cu, on the bf16-rounded
+// outputs: one scale per row and 128-wide k block = amax / 448, the E4M3 code of y / scale and, with two terms, the code
+// of the rounding residue). Sixteen consecutive threads hold one k block, so its amax is four shuffles.
+struct NormQuantParams {
+  const bf16* x;   // [M, K]
+  int M, K;
+  const float* gamma;
+  int mode;        // 1: (1+gamma), 2: gamma
+  float eps;
+  bf16* y;         // [M, K]
+  int terms;       // 0: no quantisation
+  uint8_t* q;      // [terms][m_pad][K]
+  int m_pad;
+  float* scale_t;  // [K / 128][s_ld]
+  int s_ld;
+};
+
+__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const NormQuantParams p) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float red[40];
+  const int m = blockIdx.x, tid = threadIdx.x, nvec = p.K >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K);
+  float ss = 0.f;
+  for (int v = tid; v < nvec; v += 256) {
+    const uint4 raw = xr[v];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xffff0000u);
+      row[v * 8 + 2 * j] = a;
+      row[v * 8 + 2 * j + 1] = b;
+      ss += a * a + b * b;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / (float)p.K + p.eps);
+  // every thread runs every iteration: the shuffles below need whole warps
+  for (int v0 = 0; v0 < nvec; v0 += 256) {
+    const int v = v0 + tid;
+    const bool on = v < nvec;
+    float yv[8];
+    uint32_t packed[4] = {0u, 0u, 0u, 0u};
+    float amax = 0.f;
+    if (on) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g = p.gamma[v * 8 + j];
+        const bf16 h = __float2bfloat16(row[v * 8 + j] * r * (p.mode == 1 ? 1.f + g : g));
+        yv[j] = __bfloat162float(h);
+        amax = fmaxf(amax, fabsf(yv[j]));
+        packed[j >> 1] |= (uint32_t)__bfloat16_as_ushort(h) << (16 * (j & 1));
+      }
+      *reinterpret_cast<uint4*>(p.y + (size_t)m * p.K + v * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+    if (p.terms > 0) {
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      if (on) {
+        const float s = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+        const float inv = 1.f / s;
+        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float t = yv[j] * inv;
+          const __nv_fp8_storage_t c = __nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
+          hi[j >> 2] |= (uint32_t)c << (8 * (j & 3));
+          const float back = __half2float(__half(__nv_cvt_fp8_to_halfraw(c, __NV_E4M3)));
+          lo[j >> 2] |= (uint32_t)__nv_cvt_float_to_fp8(t - back, __NV_SATFINITE, __NV_E4M3) << (8 * (j & 3));
+        }
+        const size_t off = (size_t)m * p.K + v * 8;
+        *reinterpret_cast<uint2*>(p.q + off) = make_uint2(hi[0], hi[1]);
+        if (p.terms > 1) *reinterpret_cast<uint2*>(p.q + (size_t)p.m_pad * p.K + off) = make_uint2(lo[0], lo[1]);
+        if ((tid & 15) == 0) p.scale_t[(size_t)(v >> 4) * p.s_ld + m] = s;
+      }
+    }
   }
 }
 
@@ -272,6 +353,27 @@ PK_API int pk_rmsnorm(const void* x, const float* parts, int nparts, int M, int 
 }
 
 // See rmsnorm_rs_ag_kernel. `y_peer[r]` is rank r's buffer of normalised rows (peer memory for r != rank); K even.
+// y = rmsnorm(x) for bf16 x [M, K] (K a multiple of 8, 16-byte aligned rows); with terms = 1 or 2 (K a multiple of 128)
+// the rows are also quantised for pk_gemm_fp8 exactly as pk_quant_act_fp8 would quantise y: q [terms][m_pad][K] codes,
+// scale_t [K / 128][s_ld].
+PK_API int pk_rmsnorm_quant(const void* x, int M, int K, const float* gamma, int mode, float eps, void* y, int terms, void* q, int m_pad,
+                            float* scale_t, int s_ld, cudaStream_t stream) {
+  if (M < 1 || K < 8 || (K & 7) != 0 || x == nullptr || y == nullptr || gamma == nullptr || terms < 0 || terms > 2) return PK_ERR_BAD_ARG;
+  if (((uintptr_t)x & 15) != 0 || ((uintptr_t)y & 15) != 0) return PK_ERR_BAD_ARG;
+  if (terms > 0 && ((K & 127) != 0 || q == nullptr || scale_t == nullptr || m_pad < M || s_ld < M || ((uintptr_t)q & 7) != 0)) return PK_ERR_BAD_ARG;
+  NormQuantParams p{(const pk::bf16*)x, M, K, gamma, mode, eps, (pk::bf16*)y, terms, (uint8_t*)q, m_pad, scale_t, s_ld};
+  const size_t smem = (size_t)K * sizeof(float);
+  if (smem > 200 * 1024) return PK_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    pk_set_last_cuda_error((int)cudaGetLastError());
+    return PK_ERR_CUDA;
+  }
+  rmsnorm_quant_kernel<<<M, 256, smem, stream>>>(p);
+  PK_CHECK_LAUNCH();
+  return PK_OK;
+}
+
 PK_API int pk_rmsnorm_rs_ag(void* hidden, const float* parts, int world, int rank, int rows_per_rank, int M, int K, const float* gamma,
                             int mode, float eps, void* const* y_peer, const PkWait* wait_rs, const PkPush* pub_ag, const PkWait* wait_ag,
                             int sm_count, cudaStream_t stream) {
