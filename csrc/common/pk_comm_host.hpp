@@ -84,5 +84,79 @@ inline int stored_at_publish(int grid, const std::vector<BlockEvent>& order, boo
   return -1;
 }
 
+// Host model of the in-switch all-reduce (csrc/comm/multimem_allreduce.cu): every rank owns data[2][capacity] and
+// flags[2][2][world]; `multimem.ld_reduce` is modelled as a read of the same element of every rank's buffer and
+// `multimem.st` as a write of one value into every rank's buffer. One shot: write own data, publish, wait, read the sum
+// of everything. Two shot: write own data, publish, wait, reduce this rank's slice and store it into EVERY rank's data
+// set in place, publish the second flag, wait, copy out of the own data set. Run under ThreadSanitizer this checks that
+// no rank writes a buffer another rank may still read (two data sets, in-place broadcast of disjoint slices, calls of
+// both kinds mixed).
+struct HostMmBuffer {
+  HostMmBuffer(int world, size_t capacity) : world(world), capacity(capacity), data((size_t)2 * capacity), flags(4 * world) {
+    for (auto& f : flags) f.store(0);
+  }
+  int world;
+  size_t capacity;
+  std::vector<float> data;                        // [2][capacity]
+  std::vector<std::atomic<uint32_t>> flags;       // [2][2][world]
+  uint32_t seq = 0;
+  std::atomic<uint32_t> status{0};
+};
+
+inline bool host_mm_wait(HostMmBuffer& mine, int parity, int round, uint32_t seq, int timeout_ms) {
+  if (mine.status.load() != 0) return false;
+  const auto t0 = std::chrono::steady_clock::now();
+  for (;;) {
+    bool all = true;
+    // one polling round over all flags (the device polls relaxed and fences once; acquire loads are the same ordering
+    // in a form ThreadSanitizer can follow: it does not model stand-alone fences)
+    for (int r = 0; r < mine.world; ++r)
+      all = all && (int32_t)(mine.flags[(parity * 2 + round) * mine.world + r].load(std::memory_order_acquire) - seq) >= 0;
+    if (all) break;
+    if (std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(timeout_ms)) {
+      mine.status.store(1);
+      return false;
+    }
+    std::this_thread::yield();
+  }
+  return true;
+}
+
+inline void host_mm_publish(std::vector<HostMmBuffer*>& bufs, int rank, int parity, int round, uint32_t seq) {
+  // the device runs one system fence and then relaxed stores; release stores are the same ordering
+  for (HostMmBuffer* b : bufs) b->flags[(parity * 2 + round) * b->world + rank].store(seq, std::memory_order_release);
+}
+
+inline bool host_mm_allreduce(std::vector<HostMmBuffer*>& bufs, int rank, const float* in, float* out, size_t n, bool two_shot,
+                              int timeout_ms) {
+  HostMmBuffer& mine = *bufs[rank];
+  const int world = mine.world;
+  const uint32_t seq = mine.seq + 1;
+  const int parity = (int)(seq & 1u);
+  float* data = mine.data.data() + (size_t)parity * mine.capacity;
+  for (size_t i = 0; i < n; ++i) data[i] = in[i];
+  host_mm_publish(bufs, rank, parity, 0, seq);
+  bool ok = host_mm_wait(mine, parity, 0, seq, timeout_ms);
+  if (ok && !two_shot) {
+    for (size_t i = 0; i < n; ++i) {
+      float a = 0.f;
+      for (int r = 0; r < world; ++r) a += bufs[r]->data[(size_t)parity * bufs[r]->capacity + i];
+      out[i] = a;
+    }
+  } else if (ok) {
+    const size_t per = (n + world - 1) / world, lo = (size_t)rank * per, hi = lo + per < n ? lo + per : n;
+    for (size_t i = lo; i < hi; ++i) {
+      float a = 0.f;
+      for (int r = 0; r < world; ++r) a += bufs[r]->data[(size_t)parity * bufs[r]->capacity + i];
+      for (int r = 0; r < world; ++r) bufs[r]->data[(size_t)parity * bufs[r]->capacity + i] = a;
+    }
+    host_mm_publish(bufs, rank, parity, 1, seq);
+    ok = host_mm_wait(mine, parity, 1, seq, timeout_ms);
+    if (ok)
+      for (size_t i = 0; i < n; ++i) out[i] = data[i];
+  }
+  mine.seq = seq;
+  return ok;
+}
 
 }  // namespace pk

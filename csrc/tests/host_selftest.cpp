@@ -185,6 +185,52 @@ static int test_protocol() {
   return 0;
 }
 
+// In-switch all-reduce: one-shot and two-shot calls mixed, ranks drifting apart; then a rank that never joins.
+static int test_multimem_protocol() {
+  const int world = 4, iters = 300;
+  const size_t n = 203;
+  std::vector<std::unique_ptr<pk::HostMmBuffer>> own;
+  std::vector<pk::HostMmBuffer*> bufs;
+  for (int r = 0; r < world; ++r) {
+    own.push_back(std::make_unique<pk::HostMmBuffer>(world, n));
+    bufs.push_back(own.back().get());
+  }
+  std::atomic<int> bad{0};
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r)
+    th.emplace_back([&, r] {
+      std::vector<float> in(n), out(n);
+      for (int it = 0; it < iters; ++it) {
+        for (size_t i = 0; i < n; ++i) in[i] = (float)(r + 1) * (float)(it % 7 + 1) + (float)(i % 3);
+        if ((it + r) % 5 == 0) std::this_thread::sleep_for(std::chrono::microseconds(200));
+        const bool two_shot = (it % 3) != 0;            // the same schedule on every rank, both kinds on both data sets
+        if (!pk::host_mm_allreduce(bufs, r, in.data(), out.data(), n, two_shot, 20000)) bad++;
+        for (size_t i = 0; i < n; ++i) {
+          const float want = 10.f * (float)(it % 7 + 1) + 4.f * (float)(i % 3);
+          if (std::fabs(out[i] - want) > 1e-3f) bad++;
+        }
+      }
+    });
+  for (auto& t : th) t.join();
+  CHECK(bad == 0);
+  std::vector<std::unique_ptr<pk::HostMmBuffer>> own2;
+  std::vector<pk::HostMmBuffer*> bufs2;
+  for (int r = 0; r < world; ++r) {
+    own2.push_back(std::make_unique<pk::HostMmBuffer>(world, n));
+    bufs2.push_back(own2.back().get());
+  }
+  std::atomic<int> timed_out{0};
+  th.clear();
+  for (int r = 0; r < world - 1; ++r)
+    th.emplace_back([&, r] {
+      std::vector<float> in(n, 1.f), out(n);
+      if (!pk::host_mm_allreduce(bufs2, r, in.data(), out.data(), n, true, 100)) timed_out++;
+    });
+  for (auto& t : th) t.join();
+  CHECK(timed_out == world - 1 && bufs2[0]->status.load() == 1);
+  return 0;
+}
+
 // Block counters of the peer all-reduce kernel when blocks skip their wait (status word already set): with one shared
 // counter the publish fires before every block has stored, or never; with one counter per pass it fires exactly when
 // the last block has stored.
@@ -287,6 +333,7 @@ int main(int argc, char** argv) {
     if (test_sampler()) return 1;
     if (test_control_plane(argv[3])) return 1;
     if (test_protocol()) return 1;
+    if (test_multimem_protocol()) return 1;
     if (test_block_counters()) return 1;
     if (test_prefix_plan()) return 1;
     if (test_spec_policy()) return 1;
