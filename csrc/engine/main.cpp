@@ -25,6 +25,9 @@
 #include "gguf_reader.hpp"
 #include "json.hpp"
 #include "openai_server.hpp"
+#include <cmath>
+
+#include "qwen_audit.hpp"
 #include "qwen_config.hpp"
 #include "qwen_engine.hpp"
 #include "safetensors.hpp"
@@ -56,6 +59,10 @@ struct Args {
   bool have_tokenize = false;
   bool fake_engine = false;
   int port = 8000;
+  // checkpoint tools and smoke / bench modes
+  std::string inspect_tensor;
+  bool qwen_audit = false, smoke_forward = false;
+  int smoke_layers = 4, resident_bench = 0;
 };
 
 void usage() {
@@ -72,7 +79,12 @@ void usage() {
                "  --prefill-gemm auto|fp8x2|fp8|shadow|umma   (many-row GEMM on the FP8 linears: native FP8 math with two or one\n"
                "                 E4M3 terms per activation, bf16 copies of the weights, or decode-to-bf16 in shared memory)\n"
                "  --prompt TEXT --tokenizer-gguf FILE   tokenise the prompt with the GGUF file's BPE vocabulary\n"
-               "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-gguf FILE [--tensors]\n"
+               "  --qwen-persistent-stdin | --dump-config | --inspect | --inspect-tensor NAME | --inspect-gguf FILE [--tensors]\n"
+               "  --qwen-audit [--tp-world N] [--qwen-mtp]   check every tensor the engine reads (name, dtype, shape, shard cuts on the\n"
+               "                 128-wide scale blocks) without a GPU; exit code 1 when something is wrong\n"
+               "  --smoke-forward [--smoke-layers N]   random weights in the checkpoint's (or the benchmark) shape cut to N layers: one\n"
+               "                 prefill and two decode steps\n"
+               "  --generate-token   one new token (same as --max-new-tokens 1)   --resident-bench N   the request N times on the resident engine\n"
                "  --tokenizer-gguf FILE | --tokenizer-dir DIR (tokenizer.json)   --tokenize TEXT | --detokenize 1,2,3\n"
                "  --nccl-fallback   (with --tp-world > 1) join an NCCL communicator at start; after a peer wait times out the failed\n"
                "                 step is reported and later steps run their collectives through NCCL\n"
@@ -156,6 +168,21 @@ Args parse(int argc, char** argv) {
     }
     else if (f == "--tokenize") { a.tokenize_text = need(i); a.have_tokenize = true; }
     else if (f == "--detokenize") a.detokenize_ids = need(i);
+    else if (f == "--inspect-tensor") a.inspect_tensor = need(i);
+    else if (f == "--qwen-audit") a.qwen_audit = true;
+    else if (f == "--smoke-forward") a.smoke_forward = true;
+    else if (f == "--smoke-layers") a.smoke_layers = std::stoi(need(i));
+    else if (f == "--generate-token") a.max_new_tokens = 1;
+    else if (f == "--resident-bench") a.resident_bench = std::stoi(need(i));
+    else if (f == "--use-persistent") a.persistent_decode = 1;   // the resident one-kernel-per-token decode path (the default where it applies)
+    else if (f == "--qwen-mtp-adaptive") a.mtp = true;           // draft lengths always adapt (1, doubling after full accepts, halving after rejects)
+    else if (f == "--python") a.sidecar_python = need(i);
+    else if (f == "--sidecar") {}                                // --serve always runs the templating sidecar
+    else if (f == "--forward-token" || f == "--position")
+      throw std::runtime_error(f + ": the hybrid engine consumes positions in order (recurrent state); feed the tokens with --token-ids");
+    else if (f == "--qwen-dspark")
+      throw std::runtime_error("--qwen-dspark: the external block drafter runs beside the engine in the Python server "
+                               "(python -m pocketllm_b200.server.openai --model qwen --ckpt DIR --qwen-dspark DRAFTER_DIR)");
     else if (f == "--help" || f == "-h") { usage(); std::exit(0); }
     else throw std::runtime_error("unknown flag " + f);
   }
@@ -469,6 +496,75 @@ int tokenizer_tool(const Args& a) {
   return 0;
 }
 
+// First values of a tensor as floats (the dtypes checkpoints use).
+double element_as_double(const pk::StTensor& t, int64_t i) {
+  const uint8_t* p = t.data;
+  switch (t.dtype) {
+    case pk::StDtype::F32: { float v; std::memcpy(&v, p + 4 * i, 4); return v; }
+    case pk::StDtype::BF16: { uint16_t h; std::memcpy(&h, p + 2 * i, 2); const uint32_t u = (uint32_t)h << 16; float v; std::memcpy(&v, &u, 4); return v; }
+    case pk::StDtype::F16: {
+      uint16_t h; std::memcpy(&h, p + 2 * i, 2);
+      const int sgn = h >> 15, e = (h >> 10) & 31, m = h & 1023;
+      const double mag = e == 0 ? std::ldexp((double)m, -24) : e == 31 ? (m ? NAN : INFINITY) : std::ldexp((double)(m + 1024), e - 25);
+      return sgn ? -mag : mag;
+    }
+    case pk::StDtype::F8_E4M3: {
+      const uint8_t b = p[i];
+      const int sgn = b >> 7, e = (b >> 3) & 15, m = b & 7;
+      const double mag = e == 0 ? std::ldexp((double)m, -9) : (e == 15 && m == 7) ? NAN : std::ldexp((double)(m + 8), e - 10);
+      return sgn ? -mag : mag;
+    }
+    case pk::StDtype::F8_E8M0: return std::ldexp(1.0, (int)p[i] - 127);
+    case pk::StDtype::I8: return (int8_t)p[i];
+    case pk::StDtype::U8: return p[i];
+    case pk::StDtype::I32: { int32_t v; std::memcpy(&v, p + 4 * i, 4); return v; }
+    case pk::StDtype::I64: { int64_t v; std::memcpy(&v, p + 8 * i, 8); return (double)v; }
+    default: return NAN;
+  }
+}
+
+int inspect_tensor(const Args& a) {
+  pk::SafetensorsModel st(a.ckpt);
+  const pk::StTensor* t = st.find(a.inspect_tensor);
+  if (t == nullptr) {
+    std::printf("tensor=%s found=0\n", a.inspect_tensor.c_str());
+    return 1;
+  }
+  std::printf("tensor=%s found=1 dtype=%s shape=[", t->name.c_str(), pk::st_dtype_name(t->dtype));
+  for (size_t i = 0; i < t->shape.size(); ++i) std::printf(i ? ",%lld" : "%lld", (long long)t->shape[i]);
+  std::printf("] bytes=%zu first=[", t->nbytes);
+  const int64_t n = std::min<int64_t>(8, t->numel());
+  for (int64_t i = 0; i < n; ++i) std::printf(i ? ",%.9g" : "%.9g", element_as_double(*t, i));
+  double sum = 0.0, amax = 0.0;
+  for (int64_t i = 0; i < t->numel(); ++i) {
+    const double v = element_as_double(*t, i);
+    sum += v;
+    amax = std::max(amax, std::fabs(v));
+  }
+  std::printf("] sum=%.9g abs_max=%.9g\n", sum, amax);
+  return 0;
+}
+
+int qwen_audit(const Args& a) {
+  pk::SafetensorsModel st(a.ckpt);
+  const pk::QwenConfig cfg = pk::QwenConfig::from_file(a.ckpt + "/config.json");
+  bool config_ok = true;
+  try {
+    cfg.validate(a.tp_world);
+  } catch (const std::exception& e) {
+    std::printf("qwen_audit_problem=config %s\n", e.what());
+    config_ok = false;
+  }
+  const pk::QwenAuditReport rep = pk::audit_qwen_checkpoint(st, cfg, a.tp_world, a.mtp);
+  for (const std::string& p : rep.problems) std::printf("qwen_audit_problem=%s\n", p.c_str());
+  for (const std::string& u : rep.unused) std::printf("qwen_audit_unused=%s\n", u.c_str());
+  const bool ok = rep.ok() && config_ok;
+  std::printf("qwen_audit=1 ok=%d tp_world=%d layers=%d expected_tensors=%d fp8_linears=%d problems=%zu unused_tensors=%zu expected_bytes=%llu files=%zu\n",
+              ok ? 1 : 0, a.tp_world, cfg.num_layers, rep.expected, rep.fp8_linears, rep.problems.size() + (config_ok ? 0 : 1), rep.unused.size(),
+              (unsigned long long)rep.expected_bytes, st.num_files());
+  return ok ? 0 : 1;
+}
+
 int run(const Args& a) {
   if ((!a.tokenizer_gguf.empty() || !a.tokenizer_dir.empty()) && (a.have_tokenize || !a.detokenize_ids.empty())) return tokenizer_tool(a);
   if (!a.inspect_gguf.empty()) return inspect_gguf(a);
@@ -476,6 +572,8 @@ int run(const Args& a) {
   if (!a.dsv4_config.empty()) return dsv4_config_tool(a);
   if (!a.weight_source.empty()) return weight_source_tool(a);
   if (a.serve && a.fake_engine) return serve_scripted(a);
+  if (!a.inspect_tensor.empty()) return inspect_tensor(a);
+  if (a.qwen_audit) return qwen_audit(a);
   if (a.inspect) {
     pk::SafetensorsModel st(a.ckpt);
     for (const auto& n : st.names()) {
@@ -486,7 +584,14 @@ int run(const Args& a) {
     }
     return 0;
   }
-  pk::QwenConfig cfg = a.benchmark_27b ? pk::QwenConfig::benchmark_27b() : pk::QwenConfig::from_file(a.ckpt + "/config.json");
+  pk::QwenConfig cfg = (a.benchmark_27b || (a.smoke_forward && a.ckpt.empty())) ? pk::QwenConfig::benchmark_27b() : pk::QwenConfig::from_file(a.ckpt + "/config.json");
+  if (a.smoke_forward) {
+    // the shape of the model, the first N layers only, random weights: seconds instead of a full load
+    const int n = std::max(1, std::min(a.smoke_layers, cfg.num_layers));
+    cfg.num_layers = n;
+    cfg.layer_is_full.resize((size_t)n);
+    cfg.mtp_num_hidden_layers = 0;
+  }
   if (a.dump_config) {
     std::printf("%s\n", cfg.to_json().c_str());
     return 0;
@@ -509,7 +614,7 @@ int run(const Args& a) {
   opt.prefill_gemm = a.prefill_gemm;
   g_mtp_tokens = a.mtp_tokens;
   pk::QwenEngine eng(cfg, opt);
-  if (a.random_seed >= 0 || a.benchmark_27b) eng.init_random((uint64_t)std::max(0L, a.random_seed), 0.02f);
+  if (a.random_seed >= 0 || a.benchmark_27b || a.smoke_forward) eng.init_random((uint64_t)std::max(0L, a.random_seed), 0.02f);
   else eng.load_safetensors(a.ckpt);
 
   std::vector<void*> opened;
@@ -642,7 +747,30 @@ int run(const Args& a) {
     } else {
       prompt = parse_ids(a.token_ids);
     }
+    if (prompt.empty() && a.smoke_forward) prompt = {1, 2, 3, 4};
     if (prompt.empty()) throw std::runtime_error("no prompt: give --token-ids, --token-ids-file or --prompt");
+    if (a.smoke_forward) {
+      RunResult r = generate(eng, prompt, 3);
+      const bool fine = r.tokens.size() == 3 && eng.comm_status() == 0;
+      std::printf("smoke_forward=1 ok=%d layers=%d prompt_tokens=%zu generated_token_ids=%d,%d,%d\n", fine ? 1 : 0, cfg.num_layers, prompt.size(),
+                  r.tokens[0], r.tokens.size() > 1 ? r.tokens[1] : -1, r.tokens.size() > 2 ? r.tokens[2] : -1);
+      for (void* p : opened) cudaIpcCloseMemHandle(p);
+      return fine ? 0 : 1;
+    }
+    if (a.resident_bench > 0) {
+      // the same request again and again on the resident engine (weights, caches and graphs stay): one line per run
+      double pf = 0, dc = 0;
+      for (int it = 0; it < a.resident_bench; ++it) {
+        RunResult rr = generate(eng, prompt, a.max_new_tokens);
+        print_result("qwen_resident_run", a, eng, prompt.size(), rr);
+        pf += rr.prefill_s > 0 ? prompt.size() / rr.prefill_s : 0.0;
+        dc += rr.decode_s > 0 ? (rr.tokens.size() - 1) / rr.decode_s : 0.0;
+      }
+      std::printf("qwen_resident_bench=1 runs=%d prefill_tokens_per_s_mean=%.3f decode_tokens_per_s_mean=%.3f comm_status=%u\n", a.resident_bench,
+                  pf / a.resident_bench, dc / a.resident_bench, eng.comm_status());
+      for (void* p : opened) cudaIpcCloseMemHandle(p);
+      return eng.comm_status() == 0 ? 0 : 3;
+    }
     RunResult r = generate(eng, prompt, a.max_new_tokens);
     if (eng.comm_status() != 0) {
       std::printf("qwen_comm_status=%u\n", eng.comm_status());
