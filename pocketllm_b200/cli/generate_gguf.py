@@ -2,6 +2,7 @@
 
     torchrun --nproc-per-node N -m pocketllm_b200.cli.generate_gguf --gguf-path P \
         (--seed-file F | --tokens 1,2,3) --max-new-tokens M [--architecture A] [--layers L]
+        [--gpu-memory-gib G | --expert-slots N] [--dtype bf16] [--prewarm]
 
 Prints `RESULT prefill_seconds=... prefill_tps=... decode_seconds=... decode_tps=...` and
 `generated_token_ids=...` on rank 0 (same surface as the reference's
@@ -25,14 +26,23 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--max-context", type=int, default=4096)
     ap.add_argument("--prewarm", action="store_true", help="read the file once to warm the page cache")
+    ap.add_argument("--gpu-memory-gib", type=float, default=None,
+                    help="HBM this rank may use: experts that do not fit stay in pinned host memory and are staged per step (glm-dsa)")
+    ap.add_argument("--expert-slots", type=int, default=None, help="resident experts per layer (the rest are staged from pinned host memory)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "auto"], help="activation dtype (weights stay in their GGUF block types)")
     args = ap.parse_args(argv)
     rank, world, local = gen.setup_dist()
     if args.prewarm:
         from ..formats import prewarm
         prewarm.prewarm(args.gguf_path)
     prompt = gen.read_seed_tokens(args.seed_file) if args.seed_file else [int(t) for t in (args.tokens or "1").split(",")]
+    extra = {}
+    if args.expert_slots is not None:
+        extra["expert_slots"] = args.expert_slots
+    if args.gpu_memory_gib is not None:
+        extra["gpu_memory_gib"] = args.gpu_memory_gib
     rt = registry.build_runtime(args.gguf_path, args.architecture, rank=rank, world=world, device=f"cuda:{local}",
-                                max_context=args.max_context, layers=args.layers)
+                                max_context=args.max_context, layers=args.layers, **extra)
     res = gen.greedy_generate(rt, prompt, args.max_new_tokens)
     if rank == 0:
         print(res.result_line(), flush=True)

@@ -319,8 +319,13 @@ class GLMDSAModel:
     latent + rope width outside 128 / 320 / 512 / 576) run the shared PyTorch body."""
 
     def __init__(self, path: str | Path, *, device: str = "cuda", rank: int = 0, world: int = 1, max_context: int = 4096,
-                 layers: int | None = None, group=None, dsa_topk: int | None = None, routed_tp: bool = False):
-        """`routed_tp`: with several ranks, every rank keeps ALL experts but only its slice of the expert intermediate
+                 layers: int | None = None, group=None, dsa_topk: int | None = None, routed_tp: bool = False,
+                 expert_slots: int | None = None, gpu_memory_gib: float | None = None):
+        """`expert_slots` (or `gpu_memory_gib`, from which the slots per layer are planned): the routed experts of this
+        rank stay in pinned host memory and only that many per layer are resident in HBM; a step's experts are staged on a
+        side stream into least-recently-used slots (`moe.expert_cache.ExpertStagingCache`), steps that need more distinct
+        experts than slots run in waves. For models whose experts exceed HBM.
+        `routed_tp`: with several ranks, every rank keeps ALL experts but only its slice of the expert intermediate
         dimension (gate / up rows and the matching block columns of down, slices aligned to the 256-weight block), and the
         ranks' partial outputs are summed; the default splits whole experts over the ranks. (Reference: GLM_ROUTED_TP,
         src/models/glm_dsa/architecture.py:528-877, tests/test_glm_dsa_tp_routed.py.)"""
@@ -352,6 +357,18 @@ class GLMDSAModel:
         self.w: dict[str, torch.Tensor] = {}    # fp32 small tensors
         self.raw: dict[str, torch.Tensor] = {}  # raw blocks
         keep = [f"blk.{i}." for i in range(c.n_layers)]
+        n_moe = c.n_layers - c.leading_dense_layers
+        if expert_slots is None and gpu_memory_gib is not None and n_moe > 0:
+            from ..moe.expert_cache import slots_for_budget
+            exp_names = [n for n in self.bundle.tensors if n.startswith(f"blk.{c.leading_dense_layers}.") and "_exps." in n]
+            per_expert = sum(int(self.bundle.tensors[n].nbytes) // c.n_experts for n in exp_names) // (world if self.routed_tp else 1)
+            other = sum(int(t.nbytes) for n, t in self.bundle.tensors.items()
+                        if "_exps." not in n and (not n.startswith("blk.") or any(n.startswith(k) for k in keep)))
+            kv = c.n_layers * max_context * (c.kv_lora_rank + c.rope_dim + c.indexer_key_dim) * 2
+            budget = int(gpu_memory_gib * (1 << 30)) - other - kv - (2 << 30)        # 2 GiB for activations, scratch and the context
+            expert_slots = slots_for_budget(max(budget, 0), per_expert, n_moe, self.e_local, c.top_k)
+        staged = expert_slots is not None and expert_slots < self.e_local
+        self.expert_slots = expert_slots if staged else None
         for n, t in self.bundle.tensors.items():
             if n.startswith("blk.") and not any(n.startswith(k) for k in keep):
                 continue
@@ -365,12 +382,21 @@ class GLMDSAModel:
                         blk = blk[:, :, rank * il // 256:(rank + 1) * il // 256]
                     else:                                                                # gate / up: this rank's rows
                         blk = blk[:, rank * il:(rank + 1) * il]
-                self.raw[n] = torch.from_numpy(np.ascontiguousarray(blk).reshape(self.e_local, -1)).to(self.device)
+                t_host = torch.from_numpy(np.ascontiguousarray(blk).reshape(self.e_local, -1))
+                self.raw[n] = t_host if staged else t_host.to(self.device)
             else:
                 self.raw[n] = torch.from_numpy(np.ascontiguousarray(self.bundle.blocks(n)).reshape(-1)).to(self.device)
         for i in range(c.leading_dense_layers, c.n_layers):
             b = f"blk.{i}."
             self.raw[b + "w13"] = torch.cat([self.raw.pop(b + "ffn_gate_exps.weight"), self.raw.pop(b + "ffn_up_exps.weight")], dim=1).contiguous()
+        self.staging: dict[int, object] = {}
+        if staged:
+            from ..moe.expert_cache import ExpertStagingCache
+            for i in range(c.leading_dense_layers, c.n_layers):
+                b = f"blk.{i}."
+                # the host copies move to pinned memory inside the cache; HBM holds `expert_slots` experts per layer
+                self.staging[i] = ExpertStagingCache({"w13": self.raw.pop(b + "w13"), "w2": self.raw.pop(b + "ffn_down_exps.weight")},
+                                                     slots=expert_slots, device=self.device)
         self.cache = [{"latent": [], "krope": [], "ki": []} for _ in range(c.n_layers)]
         self.max_context, self.pos = max_context, 0
 
@@ -404,6 +430,17 @@ class GLMDSAModel:
         xb = xn.to(torch.bfloat16).contiguous()
         ids, wt = go.router_topk(xb, self.w[b + "ffn_gate_inp.weight"], c.top_k, bias=self.w[b + "exp_probs_b.bias"],
                                  score_func="sigmoid", norm_topk=c.expert_weights_norm, route_scale=c.expert_weights_scale)
+        if i in self.staging:
+            from ..moe.expert_cache import staged_moe_forward
+            # routes to other ranks' experts become weight-0 routes to this rank's first expert: they add exactly nothing
+            mine = (ids >= self.e_start) & (ids < self.e_start + self.e_local)
+            ids_l = torch.where(mine, ids - self.e_start, torch.zeros_like(ids)).contiguous()
+            wt_l = torch.where(mine, wt, torch.zeros_like(wt)).contiguous()
+            y = staged_moe_forward(self.staging[i], xb, ids_l, wt_l, self.types[b + "ffn_gate_exps.weight"],
+                                   self.types[b + "ffn_down_exps.weight"], self.inter_local)
+            if self.world > 1:
+                self._combine(y)
+            return y
         routes = go.group_routes(ids, wt, c.n_experts)
         y = go.moe_forward(xb, self.raw[b + "w13"], self.raw[b + "ffn_down_exps.weight"], self.types[b + "ffn_gate_exps.weight"],
                            self.types[b + "ffn_down_exps.weight"], c.n_experts, self.inter_local, routes,

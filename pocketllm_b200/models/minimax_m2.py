@@ -196,7 +196,9 @@ class MiniMaxM2Model:
     """GPU runtime on raw blocks. `expert range` of rank r: [r * E/W, (r+1) * E/W)."""
 
     def __init__(self, path: str | Path, *, device: str = "cuda", rank: int = 0, world: int = 1, max_context: int = 4096,
-                 layers: int | None = None, group=None):
+                 layers: int | None = None, group=None, expert_slots: int | None = None):
+        """`expert_slots`: keep this rank's routed experts in pinned host memory and only that many per layer in HBM, staged
+        on a side stream into least-recently-used slots (`moe.expert_cache.ExpertStagingCache`)."""
         from ..ops import gguf_ops as go
         self.go = go
         self.bundle = gguf.GGUFBundle(path)
@@ -238,6 +240,11 @@ class MiniMaxM2Model:
                  "kc": torch.zeros(c.n_kv_heads, max_context, c.head_dim, device=self.device, dtype=torch.bfloat16),
                  "vc": torch.zeros(c.n_kv_heads, max_context, c.head_dim, device=self.device, dtype=torch.bfloat16)}
             self.layers.append(L)
+        if expert_slots is not None and expert_slots < self.e_local:
+            from ..moe.expert_cache import ExpertStagingCache
+            for L in self.layers:
+                L["cache"] = ExpertStagingCache({"w13": L.pop("w13").cpu(), "w2": L.pop("w2").view(self.e_local, -1).cpu()}, slots=expert_slots,
+                                                device=self.device)
         self.max_context = max_context
         self.pos = 0
         self._finish_init()
@@ -316,6 +323,8 @@ class MiniMaxM2Model:
         self.balanced_routes = False
         mode = os.environ.get("POCKET_GGUF_DECODE_GRAPH", "1")
         self.use_graph = self.device.type == "cuda" and (mode == "2" or (mode != "0" and self.world == 1))
+        if any("cache" in L for L in self.layers):
+            self.use_graph = False     # staged experts: which experts a step needs is read on the host
         self._graph = None
 
     def _combine(self, y: torch.Tensor) -> torch.Tensor:
@@ -391,6 +400,17 @@ class MiniMaxM2Model:
                 kk = c.n_experts_used
                 ids = ((pos.view(-1, 1) * kk + torch.arange(kk, device=self.device, dtype=torch.int32).view(1, -1) + 37 * i) % c.n_experts).to(torch.int32).contiguous()
                 wt = torch.full_like(wt, 1.0 / kk)
+            if "cache" in L:
+                from ..moe.expert_cache import staged_moe_forward
+                # routes to other ranks' experts become weight-0 routes to this rank's first expert: they add exactly nothing
+                mine = (ids >= self.e_start) & (ids < self.e_start + self.e_local)
+                y = staged_moe_forward(L["cache"], xn, torch.where(mine, ids - self.e_start, torch.zeros_like(ids)).contiguous(),
+                                       torch.where(mine, wt, torch.zeros_like(wt)).contiguous(), self.types[b + "ffn_gate_exps.weight"],
+                                       self.types[b + "ffn_down_exps.weight"], c.expert_inter)
+                if self.world > 1:
+                    self._combine(y)
+                h = (h + y).to(torch.bfloat16)
+                continue
             routes = go.group_routes(ids, wt, c.n_experts)
             # many routes per expert (prefill): grouped tensor-core GEMMs; else the per-route streaming kernels
             y = go.moe_forward(xn, L["w13"], L["w2"], self.types[b + "ffn_gate_exps.weight"], self.types[b + "ffn_down_exps.weight"],

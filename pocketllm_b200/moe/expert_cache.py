@@ -48,6 +48,19 @@ class LRUSlots:
         return {e: self.where[e] for e in uniq}, copies
 
 
+def slots_for_budget(budget_bytes: int, per_expert_bytes: int, n_layers: int, n_experts: int, top_k: int) -> int | None:
+    """Device slots per layer that `budget_bytes` of expert memory allow (every MoE layer gets the same number): None when
+    all experts fit (no staging needed); never fewer than `top_k + 1`, so that one token's experts are resident
+    together and one slot is free for a prefetch. Reference counterpart: the per-GPU expert budget of
+    src/runtime/generation.py (`--gpu-memory-gib`) and src/moe/planning.py."""
+    if per_expert_bytes <= 0 or n_layers <= 0:
+        raise ValueError("per_expert_bytes and n_layers must be positive")
+    fit = int(budget_bytes // (per_expert_bytes * n_layers))
+    if fit >= n_experts:
+        return None
+    return max(min(top_k + 1, n_experts), fit)
+
+
 def waves(ids: torch.Tensor, slots: int) -> list[tuple[int, int]]:
     """Split rows [0, T) of routed ids [T, k] into consecutive ranges whose distinct experts fit into `slots`."""
     out, start, seen = [], 0, set()

@@ -66,3 +66,24 @@ def test_two_rank_expert_sharding_adds_up_to_one_rank(tmp_path, mode):
         want = one.moe(layer, x)
         got = ranks[0].moe(layer, x) + ranks[1].moe(layer, x)
         assert ((got - want).norm() / want.norm()).item() < (2e-5 if T == 3 else 6e-3)
+
+
+def test_experts_staged_from_host_match_resident_experts(tiny_gguf):
+    """`expert_slots`: routed experts in pinned host memory, a few device slots per layer, staged per step (and in waves
+    when a chunk needs more distinct experts than there are slots): same logits as the resident model."""
+    from pocketllm_b200.models import glm_dsa as glm
+    full = glm.GLMDSAModel(tiny_gguf, max_context=128, dsa_topk=8)
+    slots = full.cfg.top_k + 1
+    staged = glm.GLMDSAModel(tiny_gguf, max_context=128, dsa_topk=8, expert_slots=slots)
+    assert staged.expert_slots == slots and len(staged.staging) == full.cfg.n_layers - full.cfg.leading_dense_layers
+    prompt = [3, 77, 140, 9, 255, 31, 8, 500, 64, 2, 19, 33, 21, 400]
+    a, b = full.forward(prompt), staged.forward(prompt)
+    assert ((a - b).norm() / a.norm()).item() < 1e-2
+    nxt = int(a.argmax())
+    a2, b2 = full.forward([nxt]), staged.forward([nxt])
+    assert ((a2 - b2).norm() / a2.norm()).item() < 1e-2
+    cache = next(iter(staged.staging.values()))
+    assert cache.bytes_staged > 0 and cache.lru.stats["evictions"] > 0
+    # a budget that holds everything plans no staging at all
+    roomy = glm.GLMDSAModel(tiny_gguf, max_context=128, dsa_topk=8, gpu_memory_gib=64.0)
+    assert roomy.expert_slots is None and not roomy.staging

@@ -46,3 +46,20 @@ def test_synthetic_full_shape_constructor_runs_small():
     assert logits.shape == (cfg.vocab_size,) and torch.isfinite(logits).all()
     tok = m.decode_one(int(logits.argmax()))
     assert 0 <= tok < cfg.vocab_size and m.pos == 41
+
+
+def test_experts_staged_from_host_match_resident_experts(tiny_gguf):
+    """Experts in pinned host memory with a few device slots per layer: same logits as the resident model, with real evictions."""
+    from pocketllm_b200.models import minimax_m2 as mm
+    full = mm.MiniMaxM2Model(tiny_gguf, max_context=128)
+    slots = full.cfg.n_experts_used + 1
+    staged = mm.MiniMaxM2Model(tiny_gguf, max_context=128, expert_slots=slots)
+    assert all("cache" in L and "w13" not in L for L in staged.layers) and not staged.use_graph
+    prompt = torch.tensor([3, 77, 140, 9, 255, 31, 8, 500, 64, 2, 19], dtype=torch.int32, device="cuda")
+    a, b = full.forward(prompt), staged.forward(prompt)
+    assert ((a - b).norm() / a.norm()).item() < 1e-2
+    nxt = torch.tensor([int(a.argmax())], dtype=torch.int32, device="cuda")
+    a2, b2 = full.forward(nxt), staged.forward(nxt)
+    assert ((a2 - b2).norm() / a2.norm()).item() < 1e-2
+    cache = staged.layers[0]["cache"]
+    assert cache.slab["w13"].shape[0] == slots and cache.bytes_staged > 0 and cache.lru.stats["evictions"] > 0

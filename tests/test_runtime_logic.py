@@ -168,3 +168,16 @@ def test_lru_slots_and_waves():
     ids = torch.tensor([[0, 1], [1, 2], [3, 4], [4, 0], [5, 6]])
     assert waves(ids, 3) == [(0, 2), (2, 4), (4, 5)]
     assert waves(ids, 8) == [(0, 5)]
+
+
+def test_expert_slots_planned_from_a_memory_budget():
+    from pocketllm_b200.moe.expert_cache import slots_for_budget
+    gib = 1 << 30
+    # 40 layers of 256 experts at 20 MiB each = 200 GiB: 100 GiB hold half of them
+    assert slots_for_budget(100 * gib, 20 << 20, 40, 256, 8) == 128
+    assert slots_for_budget(400 * gib, 20 << 20, 40, 256, 8) is None          # everything fits: no staging
+    assert slots_for_budget(1 * gib, 20 << 20, 40, 256, 8) == 9                # never below one token's experts plus a prefetch slot
+    assert slots_for_budget(0, 20 << 20, 40, 4, 8) == 4                        # ... nor above the expert count
+    import pytest
+    with pytest.raises(ValueError):
+        slots_for_budget(gib, 0, 40, 256, 8)
