@@ -533,6 +533,10 @@ class GLMDSAModel:
             self._combiner.check_step(self.device)
         return token
 
+    def forward_logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        """fp32 logits after feeding `tokens` at the current position (for host-side sampling and log-probabilities)."""
+        return self.forward(tokens)
+
     def prefill(self, tokens: Sequence[int]) -> int:
         return self._checked(int(torch.argmax(self.forward(tokens))))
 

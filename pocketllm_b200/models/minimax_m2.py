@@ -420,6 +420,10 @@ class MiniMaxM2Model:
             h = (h + y).to(torch.bfloat16)
         return go.gguf_linear(h[-1:], self.head, self.types["output.weight"], c.vocab_size, gamma=self.final_norm, eps=c.norm_eps, epi=2)[0]
 
+    def forward_logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        """fp32 logits after feeding `tokens` at the current position (for host-side sampling and log-probabilities)."""
+        return self.forward(torch.tensor(list(tokens), dtype=torch.int32, device=self.device))
+
     # protocol of the generic generation runtime
     def _checked(self, token: int) -> int:
         """The step's token, or `StepFailed` on every rank when a peer all-reduce timed out (collective check; the

@@ -8,7 +8,7 @@ from typing import Iterator, Sequence
 import torch
 
 from ..encoding import chat, dsv4, gguf_tokenizer
-from .engine import SamplingParams, apply_penalties, sample_token
+from .engine import SamplingParams, apply_penalties, sample_token, token_logprobs
 
 
 class QwenBackend:
@@ -36,6 +36,21 @@ class QwenBackend:
                     if t in p.stop_token_ids:
                         return
             return
+        if p.logprobs >= 0:
+            # every step's logits come back to the host: sample there and report the model's log-probabilities
+            if getattr(eng, "tp_world", 1) > 1:
+                raise RuntimeError("log-probabilities need the whole vocabulary on one rank (logits are vocabulary shards under tensor parallelism)")
+            gen = torch.Generator().manual_seed(p.seed) if p.seed is not None else None
+            eng.prefill(list(prompt_ids))
+            produced: list[int] = []
+            while True:
+                raw = eng.logits(0)
+                t = sample_token(apply_penalties(raw.clone(), produced, p), p, gen)
+                produced.append(t)
+                yield token_logprobs(raw, t, p.logprobs)
+                if len(produced) >= p.max_tokens or t in p.stop_token_ids:
+                    return
+                eng.forward_rows([t])
         tok = eng.prefill(list(prompt_ids))
         produced = [tok]
         yield tok
@@ -65,6 +80,19 @@ class GGUFBackend:
 
     def generate(self, prompt_ids: Sequence[int], p: SamplingParams) -> Iterator[int]:
         self.rt.reset()
+        if p.logprobs >= 0:
+            if not hasattr(self.rt, "forward_logits"):
+                raise RuntimeError("this runtime does not expose logits: log-probabilities are not available")
+            gen = torch.Generator().manual_seed(p.seed) if p.seed is not None else None
+            raw = self.rt.forward_logits(list(prompt_ids))
+            produced: list[int] = []
+            while True:
+                t = sample_token(apply_penalties(raw.clone(), produced, p), p, gen)
+                produced.append(t)
+                yield token_logprobs(raw, t, p.logprobs)
+                if len(produced) >= p.max_tokens or t in p.stop_token_ids:
+                    return
+                raw = self.rt.forward_logits([t])
         tok = self.rt.prefill(list(prompt_ids))
         n = 1
         yield tok
@@ -92,7 +120,7 @@ class DSV4Backend:
             tok = int(torch.argmax(logits)) if greedy else sample_token(apply_penalties(logits.clone(), produced, p), p, gen)
             rt.combine.check_step("cuda")
             produced.append(tok)
-            yield tok
+            yield token_logprobs(logits, tok, p.logprobs) if p.logprobs >= 0 else tok
             if len(produced) >= p.max_tokens or tok in p.stop_token_ids:
                 return
             logits = rt.forward_logits([tok])[-1]

@@ -27,6 +27,31 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     seed: int | None = None
     stop_token_ids: tuple[int, ...] = ()
+    logprobs: int = -1           # -1: off; k >= 0: log-probability of every generated token and of the k most likely ones
+
+
+@dataclass
+class TokenInfo:
+    """A generated token with the model's log-probabilities at its step (backends yield these instead of plain ids when
+    `SamplingParams.logprobs >= 0`)."""
+    token: int
+    logprob: float
+    top: list[tuple[int, float]] = field(default_factory=list)
+
+    def __int__(self) -> int:
+        return self.token
+
+
+def token_logprobs(logits, token: int, k: int) -> TokenInfo:
+    """log-softmax of a 1-D logits tensor: the chosen token's entry and the k largest (the model's distribution, before
+    temperature, penalties or filtering)."""
+    import torch
+    lp = torch.log_softmax(logits.float(), -1)
+    top = []
+    if k > 0:
+        v, i = torch.topk(lp, min(k, lp.numel()))
+        top = [(int(a), float(b)) for a, b in zip(i.tolist(), v.tolist())]
+    return TokenInfo(int(token), float(lp[int(token)]), top)
 
 
 class TokenBackend(Protocol):
@@ -96,7 +121,7 @@ class ServingEngine:
             for job, toks in zip(batch, outs):
                 job.out.put(("ttft", time.perf_counter() - job.submitted))
                 for t in toks:
-                    job.out.put(int(t))
+                    job.out.put(t if isinstance(t, TokenInfo) else int(t))
                 self.stats["tokens"] += len(toks)
                 self.stats["requests"] += 1
         except Exception as e:
@@ -123,7 +148,7 @@ class ServingEngine:
                     if first:
                         job.out.put(("ttft", time.perf_counter() - job.submitted))
                         first = False
-                    job.out.put(int(tok))
+                    job.out.put(tok if isinstance(tok, TokenInfo) else int(tok))
                     self.stats["tokens"] += 1
                     if job.cancelled.is_set():
                         break
@@ -135,7 +160,7 @@ class ServingEngine:
                 job.out.put(_DONE)
 
     def stream(self, prompt_ids: Sequence[int], params: SamplingParams, batchable: bool = False) -> Iterator[object]:
-        """Yields ("ttft", seconds) once, then token ids; raises what the backend raised. `batchable`: the caller does
+        """Yields ("ttft", seconds) once, then token ids (`TokenInfo` objects when log-probabilities were asked for); raises what the backend raised. `batchable`: the caller does
         not need tokens one by one, so the request may share a pass with compatible ones."""
         job = _Job(list(prompt_ids), params, batchable=batchable)
         try:

@@ -6,7 +6,8 @@ Surface and behaviours follow the reference's Python server (src/server/openai.p
 payload build 431-640, streaming decoder 643-715, HTTP handler 896-1040) and its C++
 twin (cpp_engine/src/openai_server.cpp:179-446): one request in flight, `max_tokens` /
 `max_completion_tokens` default 512, `temperature` 0 means greedy, `stream` needs n = 1,
-`logprobs` is refused with streaming, the context limit is checked before generation.
+`logprobs` / `top_logprobs` (not with streaming) return the model's log-probability of every generated token and of the most
+likely alternatives; the context limit is checked before generation.
 
     python -m pocketllm_b200.server.openai --model qwen --ckpt DIR [--port 8000]
 """
@@ -20,7 +21,7 @@ import uuid
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from typing import Any, Iterator, Protocol, Sequence
 
-from .engine import SamplingParams, ServingEngine
+from .engine import SamplingParams, ServingEngine, TokenInfo
 
 
 class ChatTokenizer(Protocol):
@@ -48,6 +49,11 @@ def build_params(body: dict, eos_ids: tuple[int, ...]) -> tuple[SamplingParams, 
         raise BadRequest("`stream` requires n = 1")
     if stream and body.get("logprobs"):
         raise BadRequest("`logprobs` is not available with `stream`")
+    top_lp = body.get("top_logprobs")
+    if top_lp is not None and (not isinstance(top_lp, int) or not 0 <= top_lp <= 20):
+        raise BadRequest("`top_logprobs` must be an integer between 0 and 20")
+    if top_lp and not body.get("logprobs"):
+        raise BadRequest("`top_logprobs` needs `logprobs` to be true")
     max_tokens = body.get("max_completion_tokens", body.get("max_tokens", 512))
     if not isinstance(max_tokens, int) or max_tokens < 1:
         raise BadRequest("`max_tokens` must be a positive integer")
@@ -63,8 +69,8 @@ def build_params(body: dict, eos_ids: tuple[int, ...]) -> tuple[SamplingParams, 
                        min_p=float(body.get("min_p", 0.0) or 0.0), frequency_penalty=float(body.get("frequency_penalty", 0.0) or 0.0),
                        presence_penalty=float(body.get("presence_penalty", 0.0) or 0.0),
                        repetition_penalty=float(body.get("repetition_penalty", 1.0) or 1.0), seed=body.get("seed"),
-                       stop_token_ids=tuple(eos_ids))
-    opts = {"n": n, "stream": stream, "stop": stop, "thinking": thinking, "reasoning_effort": effort,
+                       stop_token_ids=tuple(eos_ids), logprobs=int(top_lp or 0) if body.get("logprobs") else -1)
+    opts = {"n": n, "logprobs": bool(body.get("logprobs")), "stream": stream, "stop": stop, "thinking": thinking, "reasoning_effort": effort,
             "tools": body.get("tools") if body.get("tool_choice") != "none" else None,
             "response_format": body.get("response_format"),
             "include_usage": bool((body.get("stream_options") or {}).get("include_usage", False))}
@@ -144,11 +150,16 @@ class OpenAIApp:
         ttft = None
         n_tok = 0
         finish = "length"
+        lps: list[TokenInfo] = []
         for item in self.engine.stream(ids, params, batchable=batchable):
             if isinstance(item, tuple):
                 ttft = item[1]
                 continue
             n_tok += 1
+            if isinstance(item, TokenInfo):
+                info_tok, item = item, item.token
+                if item not in params.stop_token_ids:
+                    lps.append(info_tok)
             if item in params.stop_token_ids:
                 finish = "stop"
                 break
@@ -165,9 +176,17 @@ class OpenAIApp:
             yield "delta", tail
         total = time.perf_counter() - t0
         dt = max(total - (ttft or 0.0), 1e-9)
-        yield "done", {"finish_reason": finish, "completion_tokens": n_tok, "text": dec.text, "timings": {
+        yield "done", {"finish_reason": finish, "completion_tokens": n_tok, "text": dec.text, "logprobs": lps, "timings": {
             "prefill_seconds": ttft, "decode_seconds": total - (ttft or 0.0), "prompt_tokens_per_second": (len(ids) / ttft) if ttft else None,
             "decode_tokens_per_second": (max(n_tok - 1, 0) / dt) if n_tok > 1 else None}}
+
+    def _logprob_entry(self, t: TokenInfo) -> dict:
+        def one(tid: int, lp: float) -> dict:
+            text = self.tok.decode([tid])
+            return {"token": text, "logprob": lp, "bytes": list(text.encode("utf-8"))}
+        entry = one(t.token, t.logprob)
+        entry["top_logprobs"] = [one(i, lp) for i, lp in t.top]
+        return entry
 
     def complete(self, body: dict) -> dict:
         params, opts, ids = self._prepare(body)
@@ -176,12 +195,17 @@ class OpenAIApp:
         if True:
             for i in range(opts["n"]):
                 info = None
-                for kind, val in self._run(ids, params, opts, batchable=True):
+                for kind, val in self._run(ids, params, opts, batchable=not opts["logprobs"]):
                     if kind == "done":
                         info = val
                 msg = self.tok.parse(info["text"], opts["thinking"])
                 finish = "tool_calls" if msg.get("tool_calls") else info["finish_reason"]
-                choices.append({"index": i, "message": msg, "finish_reason": finish})
+                choice = {"index": i, "message": msg, "finish_reason": finish}
+                if opts["logprobs"]:
+                    if not info["logprobs"] and info["completion_tokens"] > 1:
+                        raise BadRequest("this model backend does not report log-probabilities")
+                    choice["logprobs"] = {"content": [self._logprob_entry(t) for t in info["logprobs"]]}
+                choices.append(choice)
                 completion_tokens += info["completion_tokens"]
                 timings = info["timings"]
         return {"id": "chatcmpl-" + uuid.uuid4().hex[:24], "object": "chat.completion", "created": int(time.time()),

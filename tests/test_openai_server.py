@@ -142,3 +142,79 @@ def test_sampler_greedy_and_topk():
     assert picks <= {1, 2}
     picks = {sample_token(logits, SamplingParams(temperature=1.0, top_p=0.3), g) for _ in range(20)}
     assert len(picks) == 1
+
+
+class LogitBackend:
+    """Five-token vocabulary whose logits depend on the step; yields `TokenInfo` when log-probabilities are asked for."""
+
+    def generate(self, prompt_ids, params: SamplingParams):
+        import torch
+        from pocketllm_b200.server.engine import token_logprobs
+        for step in range(params.max_tokens):
+            logits = torch.tensor([-9.0, 1.0, 2.0 + step, 0.5, -1.0])
+            tok = int(logits.argmax())
+            yield token_logprobs(logits, tok, params.logprobs) if params.logprobs >= 0 else tok
+
+
+class SmallTokenizer(CharTokenizer):
+    def decode(self, ids):
+        return "".join("?abcd"[i] for i in ids)
+
+
+def test_logprobs_of_every_generated_token_with_alternatives():
+    import math
+    import torch
+    app = oa.OpenAIApp(ServingEngine(LogitBackend()), SmallTokenizer(), model_name="fake")
+    try:
+        out = app.complete({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3, "logprobs": True, "top_logprobs": 2})
+        content = out["choices"][0]["logprobs"]["content"]
+        assert [e["token"] for e in content] == ["b", "b", "b"] and out["usage"]["completion_tokens"] == 3
+        for step, e in enumerate(content):
+            lp = torch.log_softmax(torch.tensor([-9.0, 1.0, 2.0 + step, 0.5, -1.0]), -1)
+            assert math.isclose(e["logprob"], float(lp[2]), rel_tol=1e-5) and e["bytes"] == [ord("b")]
+            assert [t["token"] for t in e["top_logprobs"]] == ["b", "a"]
+            assert math.isclose(e["top_logprobs"][1]["logprob"], float(lp[1]), rel_tol=1e-5)
+        # without the flag nothing is added; the flags are validated
+        plain = app.complete({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2})
+        assert "logprobs" not in plain["choices"][0]
+        for bad in ({"top_logprobs": 3}, {"logprobs": True, "top_logprobs": 21}, {"logprobs": True, "stream": True}):
+            with pytest.raises(oa.BadRequest):
+                app.complete({"messages": [{"role": "user", "content": "hi"}], **bad}) if not bad.get("stream") else next(app.stream({"messages": [{"role": "user", "content": "hi"}], **bad}))
+    finally:
+        app.engine.close()
+
+
+def test_backends_report_logprobs_from_their_logits():
+    """The GGUF and DeepSeek-V4 backends over stand-in runtimes that return CPU logits."""
+    import torch
+    from pocketllm_b200.server.backends import DSV4Backend, GGUFBackend
+
+    class Runtime:
+        def __init__(self):
+            self.fed = []
+            self.combine = type("C", (), {"check_step": staticmethod(lambda dev: None)})()
+
+        def reset(self):
+            self.fed = []
+
+        def forward_logits(self, tokens):
+            self.fed += list(tokens)
+            z = torch.zeros(6)
+            z[(len(self.fed) * 2) % 6] = 3.0
+            return z
+
+    p = SamplingParams(max_tokens=3, logprobs=1, stop_token_ids=(5,))
+    got = list(GGUFBackend(Runtime()).generate([1, 2], p))
+    assert [t.token for t in got] == [4, 0, 2] and all(abs(t.logprob - float(torch.log_softmax(torch.tensor([3.0, 0, 0, 0, 0, 0]), -1)[0])) < 1e-6 for t in got)
+    assert all(t.top[0][0] == t.token for t in got)
+
+    class Runtime2(Runtime):
+        def forward_logits(self, tokens):
+            return super().forward_logits(tokens).unsqueeze(0)          # [rows, vocab]
+
+    got2 = list(DSV4Backend(Runtime2()).generate([1, 2], p))
+    assert [t.token for t in got2] == [4, 0, 2]
+    plain = list(DSV4Backend(Runtime2()).generate([1, 2], SamplingParams(max_tokens=3)))
+    assert plain == [4, 0, 2]
+    with pytest.raises(RuntimeError):
+        list(GGUFBackend(type("R", (), {"reset": lambda self: None})()).generate([1], p))
