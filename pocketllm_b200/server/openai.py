@@ -211,7 +211,7 @@ class OpenAIApp:
         return {"id": "chatcmpl-" + uuid.uuid4().hex[:24], "object": "chat.completion", "created": int(time.time()),
                 "model": self.model_name, "choices": choices,
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": completion_tokens, "total_tokens": len(ids) + completion_tokens},
-                "timings": timings}
+                "timings": timings, "deepseek_timings": timings}      # the second key is the name the reference's clients read
 
     def stream(self, body: dict) -> Iterator[str]:
         """SSE lines (`data: {...}\\n\\n`), ending with `data: [DONE]`."""
@@ -258,7 +258,10 @@ class OpenAIApp:
                 yield chunk({"tool_calls": [dict(tc, index=i) for i, tc in enumerate(msg["tool_calls"])]})
             usage = {"prompt_tokens": len(ids), "completion_tokens": info["completion_tokens"],
                      "total_tokens": len(ids) + info["completion_tokens"]}
-            yield chunk({}, finish, {"usage": usage, "timings": info["timings"]} if opts["include_usage"] else {"timings": info["timings"]})
+            last = {"timings": info["timings"], "deepseek_timings": info["timings"]}
+            if opts["include_usage"]:
+                last["usage"] = usage
+            yield chunk({}, finish, last)
             yield "data: [DONE]\n\n"
 
 
