@@ -92,3 +92,39 @@ def test_minimax_rope_table_lookup_equals_direct_rotation():
     assert cos_t.shape == (128, 32) and cos_t.dtype == torch.float32
     assert torch.equal(_rope_lookup(x, pos, cos_t, sin_t, 64), _rope(x, pos, 64, 5.0e6))
     assert torch.equal(_rope_lookup(x, pos, cos_t, sin_t, 64)[..., 64:], x[..., 64:])      # dims past rope_dim pass through
+
+
+def test_validate_ds4_q2_checks_metadata_and_expert_block_types(tmp_path, capsys):
+    """A minimal deepseek4 file with the published 2-bit layout passes; a wrong expert type, a missing tensor and a
+    missing metadata key are each named."""
+    import json
+    import numpy as np
+    from pocketllm_b200.formats import gguf
+
+    def write(path, down_type="q2_k", drop=None, skip_meta=None):
+        w = gguf.GGUFWriter()
+        w.add_meta("general.architecture", "deepseek4")
+        for k, v in (("deepseek4.block_count", 2), ("deepseek4.embedding_length", 256), ("deepseek4.expert_count", 2),
+                     ("deepseek4.expert_used_count", 1), ("deepseek4.expert_feed_forward_length", 256)):
+            if k != skip_meta:
+                w.add_meta(k, v)
+        for layer in range(2):
+            for suffix, typ in inspect_gguf.DS4_Q2_EXPERT_TYPES:
+                name = f"blk.{layer}.{suffix}"
+                if name == drop:
+                    continue
+                typ = down_type if suffix == "ffn_down_exps.weight" else typ
+                shape = (2, 256, 256) if "_exps" in suffix else (256, 256)
+                nbytes = gguf.tensor_nbytes(gguf.GGML_TYPE_IDS[typ], shape)
+                w.add_tensor(name, np.zeros(nbytes, dtype=np.uint8), typ, shape)
+        w.write(path)
+
+    write(tmp_path / "ok.gguf")
+    assert inspect_gguf.main([str(tmp_path / "ok.gguf"), "--validate-ds4-q2", "--json"]) == 0
+    assert json.loads(capsys.readouterr().out)["ds4_q2_validation"] == {"ok": True, "problems": [], "more": 0}
+    write(tmp_path / "bad.gguf", down_type="q4_k", drop="blk.1.ffn_up_shexp.weight", skip_meta="deepseek4.expert_count")
+    assert inspect_gguf.main([str(tmp_path / "bad.gguf"), "--validate-ds4-q2", "--json"]) == 1
+    problems = json.loads(capsys.readouterr().out)["ds4_q2_validation"]["problems"]
+    assert "missing metadata deepseek4.expert_count" in problems
+    assert "missing tensor blk.1.ffn_up_shexp.weight" in problems
+    assert "blk.0.ffn_down_exps.weight is q4_k, expected q2_k" in problems and len(problems) == 4
