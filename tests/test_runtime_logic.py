@@ -181,3 +181,28 @@ def test_expert_slots_planned_from_a_memory_budget():
     import pytest
     with pytest.raises(ValueError):
         slots_for_budget(gib, 0, 40, 256, 8)
+
+
+def test_gate_overlap_analysis_of_a_router_dump(tmp_path):
+    import json
+    import torch
+    from pocketllm_b200.moe import analyze_gate_overlap as ago
+    # layer 0 repeats its experts from token to token, layer 1 never does
+    capture = {"layers.0.ffn.route_idx": [torch.tensor([[0, 1], [0, 1], [0, 2]]), torch.tensor([[0, 2]]), torch.tensor([[0, 2]])],
+               "layers.1.ffn.route_idx": [torch.tensor([[0, 1], [2, 3], [4, 5]]), torch.tensor([[6, 7]]), torch.tensor([[0, 1]])],
+               "layers.0.attn.index_sel": [[1, 2]]}
+    path = tmp_path / "dump.jsonl"
+    assert ago.dump_capture(capture, path) == 6
+    first = json.loads(path.read_text().splitlines()[0])
+    assert first == {"layer": 0, "ids": [[0, 1], [0, 1], [0, 2]]}
+    with open(path) as f:
+        res = ago.analyze(f, [2, 4])
+    assert res["0"]["tokens"] == 5 and res["0"]["distinct_experts"] == 3
+    assert res["0"]["mean_consecutive_overlap"] == (1.0 + 0.5 + 1.0 + 1.0) / 4
+    assert res["1"]["mean_consecutive_overlap"] == 0.0 and res["1"]["lru_hit_rate"]["2"] == 0.0
+    # layer 0 with 4 slots: 3 cold misses out of 10 uses
+    assert abs(res["0"]["lru_hit_rate"]["4"] - 0.7) < 1e-9
+    with open(path) as f:
+        dec = ago.analyze(f, [1], skip_prefill=True)
+    assert dec["0"]["tokens"] == 3 and dec["0"]["lru_hit_rate"]["1"] is None      # two experts per token do not fit one slot
+    assert ago.main([str(path), "--slots", "2,4"]) == 0
