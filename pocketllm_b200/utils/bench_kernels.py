@@ -7,6 +7,7 @@ as a fraction of the measured peaks (`MEASURED_PEAKS.json` at the repository roo
     python -m pocketllm_b200.utils.bench_kernels --op matvec --N 34816 --K 5120 --epi 1
     python -m pocketllm_b200.utils.bench_kernels --suite
     python -m pocketllm_b200.utils.bench_kernels --op dsv4 --M 64 --ctx 32768      # indexer scores, top-k, sparse attention
+    python -m pocketllm_b200.utils.bench_kernels --op deltanet --M 512 --heads 16,32  # one chunked DeltaNet layer
 """
 from __future__ import annotations
 
@@ -135,6 +136,20 @@ def bench_dsv4_select_attend(M: int, ctx: int, iters: int) -> list[dict]:
     return out
 
 
+def bench_deltanet(T: int, Hk: int, Hv: int, iters: int) -> dict:
+    """The whole chunked Gated DeltaNet layer op (prep, chunk products, state pass, gated norm) for T tokens."""
+    ld = (2 * Hk + 2 * Hv) * 128 + 2 * Hv
+    ld = (ld + 7) // 8 * 8
+    torch.manual_seed(0)
+    proj = (torch.randn(T, ld, device="cuda") * 0.5).to(torch.bfloat16)
+    C = (2 * Hk + Hv) * 128
+    conv_w, conv_state = torch.randn(C, 4, device="cuda") * 0.3, torch.zeros(C, 3, device="cuda")
+    A_log, dt_bias, norm_w = torch.zeros(Hv, device="cuda"), torch.zeros(Hv, device="cuda"), torch.ones(128, device="cuda")
+    state = torch.zeros(Hv, 128, 128, device="cuda")
+    us = _time([lambda: ops.deltanet_chunked(proj, Hk, Hv, conv_w, conv_state, A_log, dt_bias, norm_w, 1e-6, state)], iters, warmup=5)
+    return {"op": "deltanet_chunked (prep + chunk + state + out)", "T": T, "key_heads": Hk, "value_heads": Hv, "us": round(us, 1)}
+
+
 def bench_matvec(M: int, N: int, K: int, epi: int, iters: int) -> dict:
     hbm, tf, src = peaks()
     ws = [_fp8(N, K) for _ in range(_copies(N * K))]
@@ -149,7 +164,7 @@ def bench_matvec(M: int, N: int, K: int, epi: int, iters: int) -> dict:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "matvec", "attention", "attention-simt", "dsv4"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "matvec", "attention", "attention-simt", "dsv4", "deltanet"])
     ap.add_argument("--ctx", type=int, default=8192, help="attention: position after the chunk's last row")
     ap.add_argument("--heads", default="24,4", help="attention: query heads, KV heads")
     ap.add_argument("--M", type=int, default=512)
@@ -171,6 +186,10 @@ def main() -> int:
             r = bench_matvec(1, n, k, epi, args.iters)
             r["name"] = name
             print(json.dumps(r))
+        return 0
+    if args.op == "deltanet":
+        hk, hv = (int(v) for v in args.heads.split(",")) if args.heads != "24,4" else (16, 32)
+        print(json.dumps(bench_deltanet(args.M, hk, hv, args.iters)))
         return 0
     if args.op == "dsv4":
         for r in bench_dsv4_select_attend(min(args.M, 64), args.ctx, args.iters):
