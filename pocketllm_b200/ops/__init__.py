@@ -247,6 +247,23 @@ def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, *, mode: int = 1, eps: float =
     return y
 
 
+def rmsnorm_quant(x: torch.Tensor, gamma: torch.Tensor, *, mode: int = 1, eps: float = 1e-6, terms: int = 2):
+    """RMSNorm of contiguous bf16 x [M, K] that also quantises its output rows for `gemm_fp8` in the same kernel:
+    returns (y bf16 [M, K], codes uint8 [terms, m_pad, K], scales fp32 [K / 128, m_pad]), the codes and scales exactly
+    those `quant_act_fp8(y, terms)` would give. K must be a multiple of 128."""
+    M, K = x.shape
+    if not x.is_contiguous() or x.dtype != torch.bfloat16:
+        raise ValueError("rmsnorm_quant takes a contiguous bf16 matrix")
+    m_pad = (M + 127) // 128 * 128
+    y = torch.empty_like(x)
+    q = torch.zeros(terms, m_pad, K, device=x.device, dtype=torch.uint8)
+    sc = torch.ones(K // 128, m_pad, device=x.device, dtype=torch.float32)
+    st = _lib.kernels().pk_rmsnorm_quant(_ptr(x), c_int(M), c_int(K), _ptr(gamma), c_int(mode), c_float(eps), _ptr(y), c_int(terms), _ptr(q),
+                                         c_int(m_pad), _ptr(sc), c_int(m_pad), _stream())
+    _check(st, "pk_rmsnorm_quant")
+    return y, q, sc
+
+
 def embedding(tokens: torch.Tensor, table: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
     M = tokens.numel()
     out = torch.empty(M, table.shape[1], device=table.device, dtype=torch.bfloat16)
