@@ -153,18 +153,32 @@ class HFChatTokenizer:
         return self._eos
 
 
-def build(kind: str, ckpt: str, max_context: int, qwen_dspark: str | None = None):
+def build(kind: str, ckpt: str, max_context: int, qwen_dspark: str | None = None, tokenizer_path: str | None = None,
+          layer_pipeline: bool = False):
     """(backend, tokenizer) for `--model qwen|gguf|dsv4`. Under torchrun every rank builds its shard (rank and world come
-    from the environment)."""
+    from the environment). `tokenizer_path`: directory with tokenizer.json when it is not the checkpoint directory.
+    `layer_pipeline` (dsv4, several ranks): contiguous layer ranges per rank instead of expert parallelism."""
     import os
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     if kind == "dsv4":
         from tokenizers import Tokenizer
         from ..models import deepseek_v4_loader as loader
         from ..models.deepseek_v4_runtime import DSV4Runtime
-        cfg, weights = loader.load_checkpoint(ckpt)
-        rt = DSV4Runtime(cfg, weights, max_context=max_context, rank=rank, world=world)
-        tok = Tokenizer.from_file(str(Path(ckpt) / "tokenizer.json"))
+        raw_experts = None
+        if str(ckpt).endswith(".gguf"):
+            # deepseek4 GGUF: dense tensors dequantised on load, routed experts kept as raw blocks; the tokenizer needs a directory
+            from ..models import deepseek_v4_gguf as dg
+            cfg, weights, raw_experts = dg.load_gguf(ckpt)
+            if not tokenizer_path:
+                raise ValueError("a deepseek4 GGUF checkpoint needs --tokenizer-path (a directory with tokenizer.json)")
+        else:
+            cfg, weights = loader.load_checkpoint(ckpt)
+        if layer_pipeline and world > 1:
+            from ..parallel.pipeline import PipelineStage
+            rt = DSV4Runtime(cfg, weights, max_context=max_context, pipeline=PipelineStage(cfg.n_layers), raw_experts=raw_experts)
+        else:
+            rt = DSV4Runtime(cfg, weights, max_context=max_context, rank=rank, world=world, raw_experts=raw_experts)
+        tok = Tokenizer.from_file(str(Path(tokenizer_path or ckpt) / "tokenizer.json"))
         eos = [i for i in (tok.token_to_id(dsv4.EOS),) if i is not None]
 
         def render(messages, *, tools=None, thinking=False, reasoning_effort=None, response_format=None, **_):
@@ -180,7 +194,7 @@ def build(kind: str, ckpt: str, max_context: int, qwen_dspark: str | None = None
         if world > 1:
             from ..parallel import tp
             tp.connect_engine(eng)
-        tok = Tokenizer.from_file(str(Path(ckpt) / "tokenizer.json"))
+        tok = Tokenizer.from_file(str(Path(tokenizer_path or ckpt) / "tokenizer.json"))
         eos = [i for i in (tok.token_to_id("<|im_end|>"), tok.token_to_id("<|endoftext|>")) if i is not None]
 
         def render(messages, *, tools=None, thinking=False, **_):

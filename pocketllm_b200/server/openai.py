@@ -336,15 +336,68 @@ def serve(app: OpenAIApp, host: str = "127.0.0.1", port: int = 8000) -> Threadin
     return httpd
 
 
-def main(argv=None) -> int:
+def detect_model_kind(ckpt: str, ckpt_format: str = "auto") -> str:
+    """Backend for a checkpoint path: a GGUF file with the deepseek4 architecture or a DeepSeek-V4 Safetensors directory ->
+    `dsv4`, any other GGUF file -> `gguf`, a directory whose config names Gated DeltaNet fields -> `qwen`."""
+    from pathlib import Path
+    path = Path(ckpt)
+    fmt = ckpt_format
+    if fmt == "auto":
+        fmt = "gguf" if path.suffix == ".gguf" else "safetensors"
+    if fmt == "gguf":
+        from ..formats import gguf
+        arch = gguf.GGUFFile(gguf.shard_paths(str(path))[0]).architecture()
+        return "dsv4" if arch == "deepseek4" else "gguf"
+    cfg_file = path / "config.json"
+    text = cfg_file.read_text() if cfg_file.exists() else "{}"
+    return "qwen" if ("linear_num_value_heads" in text or "linear_num_key_heads" in text) else "dsv4"
+
+
+def parse_server_args(argv=None, env=None):
+    """Command line of the Python server -> (args, settings). Besides this package's own flags it takes the names of the
+    reference's server (src/server/openai.py:1080-1093: --ckpt-path, --ckpt-format, --tokenizer-path, --config,
+    --max-model-len, --partition-policy, --pd-mode, --routed-experts-device) and its profile variable SERVING_PROFILE.
+    `settings` come from the typed config: defaults < profile < file < environment < flags."""
+    import os
+    from ..config import Config
+    env = os.environ if env is None else env
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="qwen", choices=["qwen", "gguf", "dsv4"])
-    ap.add_argument("--ckpt", required=True)
-    ap.add_argument("--host", default="127.0.0.1")
-    ap.add_argument("--port", type=int, default=8000)
-    ap.add_argument("--max-context", type=int, default=4096)
+    ap.add_argument("--model", default=None, help="backend (qwen | gguf | dsv4; default: detected from the checkpoint) or, for any other "
+                                                  "value, the model id reported by /v1/models")
+    ap.add_argument("--ckpt", "--ckpt-path", dest="ckpt", default=env.get("CKPT_PATH"))
+    ap.add_argument("--ckpt-format", choices=["auto", "safetensors", "gguf"], default=env.get("CKPT_FORMAT", "auto"))
+    ap.add_argument("--tokenizer-path", default=env.get("TOKENIZER_PATH"), help="directory with tokenizer.json when it is not the checkpoint's")
+    ap.add_argument("--config", default=None, help="JSON / YAML file of the typed configuration (sections model, parallel, cache, speculative, serving)")
+    ap.add_argument("--serving-profile", default=env.get("SERVING_PROFILE"), help="safe1 | latency2 | throughput4")
+    ap.add_argument("--model-name", default=None)
+    ap.add_argument("--host", default=None)
+    ap.add_argument("--port", type=int, default=None)
+    ap.add_argument("--max-context", "--max-model-len", dest="max_context", type=int, default=None)
+    ap.add_argument("--partition-policy", default=env.get("PARTITION_POLICY", "legacy"),
+                    help="dsv4 under several ranks: legacy / baseline_4gpu = routed experts split over the ranks, layer_pp / layer_pp_4gpu = "
+                         "contiguous layer ranges per rank (layer pipeline)")
+    ap.add_argument("--pd-mode", choices=["off", "scheduler"], default="off",
+                    help="accepted for compatibility: requests run one at a time on the GPUs, so there is no CPU expert server to pause between phases")
+    ap.add_argument("--routed-experts-device", choices=["gpu", "cpu"], default="gpu")
     ap.add_argument("--qwen-dspark", default="", help="qwen: directory of an external DSpark block drafter; greedy requests run as speculative rounds")
     args = ap.parse_args(argv)
+    if not args.ckpt:
+        ap.error("--ckpt (or --ckpt-path / CKPT_PATH) is required")
+    if args.routed_experts_device == "cpu":
+        ap.error("--routed-experts-device cpu: routed experts run on the GPUs here (experts beyond HBM are staged from pinned host memory)")
+    cfg = Config.load(args.config, profile=args.serving_profile or None, env=env)
+    kinds = ("qwen", "gguf", "dsv4")
+    kind = args.model if args.model in kinds else detect_model_kind(args.ckpt, args.ckpt_format)
+    name = args.model_name or (args.model if args.model and args.model not in kinds else None) or cfg.serving.model_name
+    settings = {"kind": kind, "model_name": name, "host": args.host or cfg.serving.host, "port": args.port if args.port is not None else cfg.serving.port,
+                "max_context": args.max_context if args.max_context is not None else cfg.model.max_context, "max_queue": cfg.serving.max_queue,
+                "layer_pipeline": args.partition_policy.startswith("layer_pp") or cfg.parallel.policy == "layer_pp",
+                "profile": args.serving_profile or None}
+    return args, settings
+
+
+def main(argv=None) -> int:
+    args, st = parse_server_args(argv)
     import os
     from . import backends, distributed
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
@@ -356,16 +409,17 @@ def main(argv=None) -> int:
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         group = distributed.control_group()
-    backend, tokenizer = backends.build(args.model, args.ckpt, args.max_context, qwen_dspark=args.qwen_dspark or None)
+    backend, tokenizer = backends.build(st["kind"], args.ckpt, st["max_context"], qwen_dspark=args.qwen_dspark or None,
+                                        tokenizer_path=args.tokenizer_path, layer_pipeline=st["layer_pipeline"])
     if world > 1 and rank != 0:
         served = distributed.worker_loop(backend, group)
         print(f"worker {rank}: served {served} requests", flush=True)
         return 0
     if world > 1:
         backend = distributed.DistributedBackend(backend, group)
-    app = OpenAIApp(ServingEngine(backend), tokenizer, model_name=args.model, max_context=args.max_context)
-    httpd = serve(app, args.host, args.port)
-    print(f"listening on http://{args.host}:{httpd.server_address[1]}", flush=True)
+    app = OpenAIApp(ServingEngine(backend, max_queue=st["max_queue"]), tokenizer, model_name=st["model_name"], max_context=st["max_context"])
+    httpd = serve(app, st["host"], st["port"])
+    print(f"listening on http://{st['host']}:{httpd.server_address[1]} model={st['model_name']} backend={st['kind']} profile={st['profile']}", flush=True)
     try:
         httpd.serve_forever()
     except KeyboardInterrupt:

@@ -218,3 +218,31 @@ def test_backends_report_logprobs_from_their_logits():
     assert plain == [4, 0, 2]
     with pytest.raises(RuntimeError):
         list(GGUFBackend(type("R", (), {"reset": lambda self: None})()).generate([1], p))
+
+
+def test_server_command_line_takes_profiles_config_files_and_the_reference_flag_names(tmp_path):
+    import json
+    ck = tmp_path / "ck"
+    ck.mkdir()
+    (ck / "config.json").write_text(json.dumps({"linear_num_value_heads": 4, "hidden_size": 64}))
+    args, st = oa.parse_server_args(["--ckpt-path", str(ck), "--max-model-len", "2048", "--model", "my-model-id"], env={})
+    assert st["kind"] == "qwen" and st["model_name"] == "my-model-id" and st["max_context"] == 2048 and st["max_queue"] == 64
+    assert st["host"] == "127.0.0.1" and st["port"] == 8000 and not st["layer_pipeline"]
+    # a profile from the environment, a config file on top of it, flags on top of that
+    cfgf = tmp_path / "serve.json"
+    cfgf.write_text(json.dumps({"serving": {"port": 9001, "model_name": "from-file"}, "model": {"max_context": 1024}}))
+    args, st = oa.parse_server_args(["--ckpt", str(ck), "--model", "qwen", "--config", str(cfgf), "--port", "9002"],
+                                    env={"SERVING_PROFILE": "safe1"})
+    assert st["max_queue"] == 1 and st["port"] == 9002 and st["model_name"] == "from-file" and st["max_context"] == 1024 and st["profile"] == "safe1"
+    # a directory without DeltaNet fields is a DeepSeek-V4 checkpoint; its layer pipeline is a partition policy
+    d4dir = tmp_path / "d4"
+    d4dir.mkdir()
+    (d4dir / "config.json").write_text(json.dumps({"n_layers": 4}))
+    args, st = oa.parse_server_args(["--ckpt", str(d4dir), "--partition-policy", "layer_pp_4gpu"], env={})
+    assert st["kind"] == "dsv4" and st["layer_pipeline"]
+    with pytest.raises(SystemExit):
+        oa.parse_server_args(["--ckpt", str(ck), "--routed-experts-device", "cpu"], env={})
+    with pytest.raises(SystemExit):
+        oa.parse_server_args([], env={})
+    with pytest.raises(ValueError):
+        oa.parse_server_args(["--ckpt", str(ck), "--serving-profile", "nope"], env={})
