@@ -220,7 +220,9 @@ class QwenTokenEngine : public pk::TokenEngine {
   int prefill(const std::vector<int>& prompt, const pk::SamplerConfig& sc, uint64_t seed) override {
     sc_ = sc;
     rng_ = seed | 1;
-    host_sampling_ = sc.temperature > 0.f && world_ == 1;
+    // logits come back to the host when the request samples or penalises (one rank: logits are vocabulary shards otherwise)
+    host_sampling_ = (sc.temperature > 0.f || sc.has_penalties()) && world_ == 1;
+    produced_.clear();
     if (world_ > 1) {
       pk::CmdChannel::Message m;
       m.op = OP_PREFILL;
@@ -288,7 +290,9 @@ class QwenTokenEngine : public pk::TokenEngine {
   int resample(int greedy) {
     logits_.resize((size_t)e_.vocab_local());
     e_.copy_logits(logits_.data(), 0);
+    pk::apply_penalties(logits_.data(), (int)logits_.size(), produced_, sc_);
     last_ = pk::sample_token(logits_.data(), (int)logits_.size(), sc_, rng_);
+    produced_.push_back(last_);
     (void)greedy;
     return last_;
   }
@@ -300,6 +304,7 @@ class QwenTokenEngine : public pk::TokenEngine {
   bool host_sampling_ = false;
   int last_ = 0;
   std::vector<float> logits_;
+  std::vector<int> produced_;            // tokens of this request so far (for the penalties)
   static constexpr int kSpecChunk = 8;   // tokens produced per speculative call
   std::vector<int> buf_;                 // tokens of the current chunk not yet handed out
   size_t buf_pos_ = 0;

@@ -209,6 +209,10 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
     sc.temperature = (float)plan.get_double("temperature", 0.0);
     sc.top_p = (float)plan.get_double("top_p", 1.0);
     sc.top_k = (int)plan.get_int("top_k", 0);
+    sc.min_p = (float)plan.get_double("min_p", 0.0);
+    sc.frequency_penalty = (float)plan.get_double("frequency_penalty", 0.0);
+    sc.presence_penalty = (float)plan.get_double("presence_penalty", 0.0);
+    sc.repetition_penalty = (float)plan.get_double("repetition_penalty", 1.0);
     const uint64_t seed = (uint64_t)plan.get_int("seed", 0) * 0x9E3779B97F4A7C15ULL + 0x1234567ULL;
     const std::string id = "chatcmpl-" + std::to_string(now_s()) + "-" + std::to_string(++counter);
     const int64_t created = now_s();

@@ -14,6 +14,23 @@ double next_uniform(uint64_t& s) {
   return (double)((s * 0x2545F4914F6CDD1DULL) >> 11) / (double)(1ULL << 53);
 }
 
+void apply_penalties(float* logits, int n, const std::vector<int>& generated, const SamplerConfig& cfg) {
+  if (!cfg.has_penalties() || generated.empty()) return;
+  std::vector<int> ids(generated);
+  std::sort(ids.begin(), ids.end());
+  for (size_t i = 0; i < ids.size();) {
+    size_t j = i;
+    while (j < ids.size() && ids[j] == ids[i]) ++j;
+    const int t = ids[i];
+    if (t >= 0 && t < n) {
+      float v = logits[t];
+      if (cfg.repetition_penalty != 1.f) v = v > 0.f ? v / cfg.repetition_penalty : v * cfg.repetition_penalty;
+      logits[t] = v - cfg.frequency_penalty * (float)(j - i) - cfg.presence_penalty;
+    }
+    i = j;
+  }
+}
+
 int sample_token(const float* logits, int n, const SamplerConfig& cfg, uint64_t& rng) {
   if (n <= 0) return -1;
   int best = 0;
@@ -25,8 +42,8 @@ int sample_token(const float* logits, int n, const SamplerConfig& cfg, uint64_t&
   std::iota(order.begin(), order.end(), 0);
   int keep = n;
   if (cfg.top_k > 0 && cfg.top_k < n) keep = cfg.top_k;
-  if (keep < n || cfg.top_p < 1.f) {
-    const int limit = (cfg.top_p < 1.f && keep == n) ? std::min(n, 4096) : keep;   // nucleus rarely needs more
+  if (keep < n || cfg.top_p < 1.f || cfg.min_p > 0.f) {
+    const int limit = ((cfg.top_p < 1.f || cfg.min_p > 0.f) && keep == n) ? std::min(n, 4096) : keep;   // the head of the distribution is enough
     std::partial_sort(order.begin(), order.begin() + limit, order.end(),
                       [&](int a, int b) { return logits[a] > logits[b] || (logits[a] == logits[b] && a < b); });
     keep = limit;
@@ -37,6 +54,18 @@ int sample_token(const float* logits, int n, const SamplerConfig& cfg, uint64_t&
   for (int i = 0; i < keep; ++i) {
     p[i] = std::exp((logits[order[i]] - mx) * inv_t);
     total += p[i];
+  }
+  if (cfg.min_p > 0.f) {
+    // candidates are sorted: p[0] is the largest (1 after the shift by the maximum)
+    int cut = keep;
+    for (int i = 1; i < keep; ++i)
+      if (p[i] < (double)cfg.min_p * p[0]) {
+        cut = i;
+        break;
+      }
+    keep = cut;
+    total = 0.0;
+    for (int i = 0; i < keep; ++i) total += p[i];
   }
   if (cfg.top_p < 1.f) {
     // `total` covers only the kept candidates; the tail beyond 4096 sorted entries is negligible.

@@ -1,8 +1,11 @@
-// Host sampler: greedy, temperature and nucleus (top-p) sampling over one row of fp32 logits.
-// Role of the reference's cpp_engine/src/sampler.cpp:11-68.
+// Host sampler: greedy, temperature, top-k, nucleus (top-p) and min-p sampling over one row of fp32 logits, with the
+// frequency / presence / repetition penalties of the OpenAI request applied to the logits first.
+// Role of the reference's cpp_engine/src/sampler.cpp:11-68 (greedy, temperature, top-p) and of the penalty and min-p
+// handling of src/server/openai.py:559-606.
 #pragma once
 
 #include <cstdint>
+#include <vector>
 
 namespace pk {
 
@@ -10,10 +13,18 @@ struct SamplerConfig {
   float temperature = 0.f;   // <= 0: greedy
   float top_p = 1.f;
   int top_k = 0;             // 0: no limit
+  float min_p = 0.f;         // drop candidates whose probability is below min_p times the largest one
+  float frequency_penalty = 0.f, presence_penalty = 0.f;
+  float repetition_penalty = 1.f;
+  bool has_penalties() const { return frequency_penalty != 0.f || presence_penalty != 0.f || repetition_penalty != 1.f; }
 };
 
 // xorshift64*; `state` must be non-zero
 double next_uniform(uint64_t& state);
+
+// logits[t] of every token t generated so far: divided (positive) or multiplied (negative) by the repetition penalty,
+// then lowered by frequency_penalty * count(t) + presence_penalty. Ids outside [0, n) are ignored.
+void apply_penalties(float* logits, int n, const std::vector<int>& generated, const SamplerConfig& cfg);
 
 // Index of the sampled token. Ties in greedy mode go to the lowest index.
 int sample_token(const float* logits, int n, const SamplerConfig& cfg, uint64_t& rng_state);

@@ -78,6 +78,26 @@ static int test_sampler() {
   int seen[5] = {0};
   for (int i = 0; i < 2000; ++i) seen[pk::sample_token(logits, 5, hot, rng)]++;
   CHECK(seen[0] == 0 && seen[3] == 0 && seen[4] == 0 && seen[1] > 0);
+  // min-p: only candidates within a factor of the best survive (e^-2 = 0.135 of the best for token 4, e^-3 for token 0)
+  pk::SamplerConfig mp;
+  mp.temperature = 1.f;
+  mp.min_p = 0.1f;
+  int seen2[5] = {0};
+  for (int i = 0; i < 4000; ++i) seen2[pk::sample_token(logits, 5, mp, rng)]++;
+  CHECK(seen2[0] == 0 && seen2[3] == 0 && seen2[4] > 0 && seen2[1] > 0 && seen2[2] > 0);
+  // penalties: token 1 was generated twice and token 2 once; the greedy pick moves to the untouched runner-up
+  pk::SamplerConfig pen;
+  pen.frequency_penalty = 0.5f;
+  pen.presence_penalty = 0.25f;
+  pen.repetition_penalty = 2.f;
+  CHECK(pen.has_penalties() && !greedy.has_penalties());
+  float l2[5] = {0.f, 3.f, 3.f, -2.f, 1.f};
+  pk::apply_penalties(l2, 5, {1, 2, 1, 77, -3}, pen);
+  CHECK(std::fabs(l2[1] - (1.5f - 1.0f - 0.25f)) < 1e-6f && std::fabs(l2[2] - (1.5f - 0.5f - 0.25f)) < 1e-6f && l2[0] == 0.f && l2[4] == 1.f);
+  CHECK(pk::sample_token(l2, 5, pen, rng) == 4);
+  float l3[2] = {-1.f, -4.f};
+  pk::apply_penalties(l3, 2, {0}, pen);
+  CHECK(std::fabs(l3[0] - (-2.f - 0.5f - 0.25f)) < 1e-6f && l3[1] == -4.f);    // a negative logit is multiplied
   return 0;
 }
 

@@ -5,7 +5,8 @@ cpp_engine/tools/cpp_sidecar.py).
 
     {"op": "hello"}                      -> {"ok": true, "eos": [...]}
     {"op": "begin", "body": <request>}   -> {"ok": true, "tokens": [...], "max_tokens": N, "stop_token_ids": [...],
-                                             "stream": b, "temperature": t, "top_p": p, "top_k": k, "seed": s,
+                                             "stream": b, "temperature": t, "top_p": p, "top_k": k, "min_p": m, "frequency_penalty": f,
+                                             "presence_penalty": q, "repetition_penalty": r, "seed": s,
                                              "include_usage": b}   |  {"ok": false, "status": 400, "error": "..."}
     {"op": "token", "token": id}         -> {"delta": "text", "channel": "content" | "reasoning_content", "stop": b}
     {"op": "end", "finish_reason": r}    -> {"tail": "text", "channel": ..., "message": {...}, "finish_reason": r'}
@@ -75,7 +76,8 @@ class Session:
         self.thinking = self.in_reasoning = bool(opts["thinking"])
         self.carry = ""
         return {"ok": True, "tokens": [int(t) for t in ids], "max_tokens": p.max_tokens, "stop_token_ids": list(p.stop_token_ids),
-                "stream": opts["stream"], "temperature": p.temperature, "top_p": p.top_p, "top_k": p.top_k,
+                "stream": opts["stream"], "temperature": p.temperature, "top_p": p.top_p, "top_k": p.top_k, "min_p": p.min_p,
+                "frequency_penalty": p.frequency_penalty, "presence_penalty": p.presence_penalty, "repetition_penalty": p.repetition_penalty,
                 "seed": int(p.seed or 0), "include_usage": opts["include_usage"]}
 
     def _split(self, text: str, final: bool = False) -> tuple[str, str]:

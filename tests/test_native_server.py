@@ -233,3 +233,16 @@ def test_native_gguf_reader_matches_python_reader(tmp_path):
         assert t["type"] == r.type_name and t["nbytes"] == r.nbytes and tuple(reversed(t["dims"])) == tuple(r.shape)
         assert t["head_sum"] == int(np.frombuffer(ref.raw(t["name"]).tobytes()[:64], dtype=np.uint8).sum())
     assert L.pk_gguf_describe(str(tmp_path / "missing.gguf").encode()) is None
+
+
+def test_sidecar_plan_carries_every_sampling_field_the_native_sampler_reads():
+    from pocketllm_b200.server import cpp_sidecar as sc
+    s = sc.Session(sc.CharTokenizer())
+    plan = s.begin({"messages": [{"role": "user", "content": "hi"}], "temperature": 0.7, "top_p": 0.9, "top_k": 40, "min_p": 0.05,
+                    "frequency_penalty": 0.3, "presence_penalty": 0.2, "repetition_penalty": 1.1, "seed": 7, "max_tokens": 9})
+    assert plan["ok"] and plan["max_tokens"] == 9 and plan["seed"] == 7
+    for key, want in (("temperature", 0.7), ("top_p", 0.9), ("top_k", 40), ("min_p", 0.05), ("frequency_penalty", 0.3),
+                      ("presence_penalty", 0.2), ("repetition_penalty", 1.1)):
+        assert plan[key] == pytest.approx(want), key
+    bad = s.begin({"messages": [{"role": "user", "content": "hi"}], "n": 2})
+    assert not bad["ok"] and bad["status"] == 400
