@@ -221,7 +221,8 @@ class QwenTokenEngine : public pk::TokenEngine {
     sc_ = sc;
     rng_ = seed | 1;
     // logits come back to the host when the request samples or penalises (one rank: logits are vocabulary shards otherwise)
-    host_sampling_ = (sc.temperature > 0.f || sc.has_penalties()) && world_ == 1;
+    host_sampling_ = (sc.temperature > 0.f || sc.has_penalties() || sc.logprobs >= 0) && world_ == 1;
+    have_lp_ = false;
     produced_.clear();
     if (world_ > 1) {
       pk::CmdChannel::Message m;
@@ -285,13 +286,23 @@ class QwenTokenEngine : public pk::TokenEngine {
     return out;
   }
   const pk::QwenSpecStats& spec_stats() const { return spec_total_; }
+  bool last_logprobs(pk::TokenLogprobs* out) override {
+    if (!host_sampling_ || !have_lp_) return false;      // several ranks: logits are vocabulary shards
+    *out = lp_;
+    return true;
+  }
 
  private:
   int resample(int greedy) {
     logits_.resize((size_t)e_.vocab_local());
     e_.copy_logits(logits_.data(), 0);
+    if (sc_.logprobs >= 0) raw_ = logits_;            // the model's distribution, before penalties
     pk::apply_penalties(logits_.data(), (int)logits_.size(), produced_, sc_);
     last_ = pk::sample_token(logits_.data(), (int)logits_.size(), sc_, rng_);
+    if (sc_.logprobs >= 0) {
+      pk::token_logprobs(raw_.data(), (int)raw_.size(), last_, sc_.logprobs, &lp_);
+      have_lp_ = true;
+    }
     produced_.push_back(last_);
     (void)greedy;
     return last_;
@@ -305,6 +316,9 @@ class QwenTokenEngine : public pk::TokenEngine {
   int last_ = 0;
   std::vector<float> logits_;
   std::vector<int> produced_;            // tokens of this request so far (for the penalties)
+  std::vector<float> raw_;               // the step's logits before penalties (log-probability reports)
+  pk::TokenLogprobs lp_;
+  bool have_lp_ = false;
   static constexpr int kSpecChunk = 8;   // tokens produced per speculative call
   std::vector<int> buf_;                 // tokens of the current chunk not yet handed out
   size_t buf_pos_ = 0;

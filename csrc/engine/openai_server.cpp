@@ -103,8 +103,9 @@ class ScriptedEngine : public TokenEngine {
     }
   }
   int max_context() const override { return max_context_; }
-  int prefill(const std::vector<int>&, const SamplerConfig&, uint64_t) override {
+  int prefill(const std::vector<int>&, const SamplerConfig& sc, uint64_t) override {
     pos_ = 0;
+    top_k_ = sc.logprobs;
     return next();
   }
   int next() override {
@@ -112,13 +113,23 @@ class ScriptedEngine : public TokenEngine {
       ++pos_;
       throw EngineStepFailed("scripted step failure");
     }
-    return pos_ < cps_.size() ? cps_[pos_++] : 0;
+    last_ = pos_ < cps_.size() ? cps_[pos_++] : 0;
+    return last_;
+  }
+  // a made-up distribution: the scripted token at ln(0.5), then its successors in code-point order at half of that each
+  bool last_logprobs(TokenLogprobs* out) override {
+    if (top_k_ < 0) return false;
+    out->chosen = -0.6931472f;
+    out->top.clear();
+    for (int i = 0; i < top_k_; ++i) out->top.emplace_back(last_ + i, -0.6931472f * (float)(i + 1));
+    return true;
   }
 
  private:
   std::vector<int> cps_;
   size_t pos_ = 0;
   int max_context_;
+  int top_k_ = -1, last_ = 0;
 };
 
 std::string error_json(const std::string& msg, const std::string& type) {
@@ -213,6 +224,8 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
     sc.frequency_penalty = (float)plan.get_double("frequency_penalty", 0.0);
     sc.presence_penalty = (float)plan.get_double("presence_penalty", 0.0);
     sc.repetition_penalty = (float)plan.get_double("repetition_penalty", 1.0);
+    sc.logprobs = (int)plan.get_int("logprobs", -1);
+    std::vector<std::pair<int, TokenLogprobs>> lps;      // generated tokens (no end-of-sequence token) with their log-probabilities
     const uint64_t seed = (uint64_t)plan.get_int("seed", 0) * 0x9E3779B97F4A7C15ULL + 0x1234567ULL;
     const std::string id = "chatcmpl-" + std::to_string(now_s()) + "-" + std::to_string(++counter);
     const int64_t created = now_s();
@@ -258,7 +271,7 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
       }
       return;
     }
-    bool step_lost = false;
+    bool step_lost = false, logprobs_refused = false;
     std::string step_error;
     while (true) {
       ++generated;
@@ -267,6 +280,16 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
       if (is_eos) {
         finish = "stop";
         break;
+      }
+      if (sc.logprobs >= 0) {
+        TokenLogprobs lp;
+        if (!engine.last_logprobs(&lp)) {
+          step_lost = true;
+          step_error = "this engine does not report log-probabilities";
+          logprobs_refused = true;
+          break;
+        }
+        lps.emplace_back(tok, std::move(lp));
       }
       Json feed = Json::object();
       feed["op"] = Json("token");
@@ -298,7 +321,7 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
       endq["finish_reason"] = Json("stop");
       sidecar.call(endq);
       if (!stream) {
-        res.send(500, "application/json", error_json(step_error, "engine_error"));
+        res.send(logprobs_refused ? 400 : 500, "application/json", error_json(step_error, logprobs_refused ? "invalid_request_error" : "engine_error"));
       } else {
         res.event(error_json(step_error, "engine_error"));
         res.event("[DONE]");
@@ -351,6 +374,38 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
     choice["index"] = Json(0);
     choice["message"] = fin.at("message");
     choice["finish_reason"] = Json(finish);
+    if (sc.logprobs >= 0) {
+      // token texts come from the sidecar (one call for every id that appears)
+      Json ask = Json::object();
+      ask["op"] = Json("token_texts");
+      ask["ids"] = Json::array();
+      for (const auto& e : lps) {
+        ask["ids"].push_back(Json(e.first));
+        for (const auto& t : e.second.top) ask["ids"].push_back(Json(t.first));
+      }
+      const Json texts = sidecar.call(ask);
+      size_t at = 0;
+      auto entry = [&](float lp) {
+        const std::string text = at < texts.at("texts").items().size() ? texts.at("texts").items()[at].as_string() : std::string();
+        ++at;
+        Json e = Json::object();
+        e["token"] = Json(text);
+        e["logprob"] = Json((double)lp);
+        e["bytes"] = Json::array();
+        for (unsigned char ch : text) e["bytes"].push_back(Json((int)ch));
+        return e;
+      };
+      Json content = Json::array();
+      for (const auto& e : lps) {
+        Json one = entry(e.second.chosen);
+        one["top_logprobs"] = Json::array();
+        for (const auto& t : e.second.top) one["top_logprobs"].push_back(entry(t.second));
+        content.push_back(one);
+      }
+      Json lpj = Json::object();
+      lpj["content"] = content;
+      choice["logprobs"] = lpj;
+    }
     out["choices"] = Json::array();
     out["choices"].push_back(choice);
     out["usage"] = usage;

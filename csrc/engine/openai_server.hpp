@@ -34,6 +34,12 @@ class TokenEngine {
   virtual int prefill(const std::vector<int>& prompt, const SamplerConfig& sampler, uint64_t seed) = 0;
   // The token after the last one returned.
   virtual int next() = 0;
+  // Log-probabilities of the step that produced the token returned last, when the request's sampler asked for them
+  // (`SamplerConfig::logprobs >= 0`); false when this engine cannot report them.
+  virtual bool last_logprobs(TokenLogprobs* out) {
+    (void)out;
+    return false;
+  }
 };
 
 // Child process speaking one JSON object per line on stdin/stdout.

@@ -31,6 +31,25 @@ void apply_penalties(float* logits, int n, const std::vector<int>& generated, co
   }
 }
 
+void token_logprobs(const float* logits, int n, int token, int k, TokenLogprobs* out) {
+  out->top.clear();
+  out->chosen = 0.f;
+  if (n <= 0 || token < 0 || token >= n) return;
+  float mx = logits[0];
+  for (int i = 1; i < n; ++i) mx = std::max(mx, logits[i]);
+  double sum = 0.0;
+  for (int i = 0; i < n; ++i) sum += std::exp((double)(logits[i] - mx));
+  const double lse = (double)mx + std::log(sum);
+  out->chosen = (float)((double)logits[token] - lse);
+  k = std::min(k, n);
+  if (k <= 0) return;
+  std::vector<int> order(n);
+  std::iota(order.begin(), order.end(), 0);
+  std::partial_sort(order.begin(), order.begin() + k, order.end(),
+                    [&](int a, int b) { return logits[a] > logits[b] || (logits[a] == logits[b] && a < b); });
+  for (int i = 0; i < k; ++i) out->top.emplace_back(order[i], (float)((double)logits[order[i]] - lse));
+}
+
 int sample_token(const float* logits, int n, const SamplerConfig& cfg, uint64_t& rng) {
   if (n <= 0) return -1;
   int best = 0;

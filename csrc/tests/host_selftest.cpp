@@ -95,6 +95,14 @@ static int test_sampler() {
   pk::apply_penalties(l2, 5, {1, 2, 1, 77, -3}, pen);
   CHECK(std::fabs(l2[1] - (1.5f - 1.0f - 0.25f)) < 1e-6f && std::fabs(l2[2] - (1.5f - 0.5f - 0.25f)) < 1e-6f && l2[0] == 0.f && l2[4] == 1.f);
   CHECK(pk::sample_token(l2, 5, pen, rng) == 4);
+  // log-probabilities: log-softmax entry of the chosen token and the k largest, ties to the lower id
+  pk::TokenLogprobs lp;
+  pk::token_logprobs(logits, 5, 4, 3, &lp);
+  const double lse = std::log(std::exp(0.0) + 2 * std::exp(3.0) + std::exp(-2.0) + std::exp(1.0));
+  CHECK(std::fabs(lp.chosen - (float)(1.0 - lse)) < 1e-5f && lp.top.size() == 3);
+  CHECK(lp.top[0].first == 1 && lp.top[1].first == 2 && lp.top[2].first == 4 && std::fabs(lp.top[0].second - (float)(3.0 - lse)) < 1e-5f);
+  pk::token_logprobs(logits, 5, 9, 3, &lp);
+  CHECK(lp.top.empty() && lp.chosen == 0.f);          // a token outside the vocabulary reports nothing
   float l3[2] = {-1.f, -4.f};
   pk::apply_penalties(l3, 2, {0}, pen);
   CHECK(std::fabs(l3[0] - (-2.f - 0.5f - 0.25f)) < 1e-6f && l3[1] == -4.f);    // a negative logit is multiplied

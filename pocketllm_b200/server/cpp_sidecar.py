@@ -10,6 +10,7 @@ cpp_engine/tools/cpp_sidecar.py).
                                              "include_usage": b}   |  {"ok": false, "status": 400, "error": "..."}
     {"op": "token", "token": id}         -> {"delta": "text", "channel": "content" | "reasoning_content", "stop": b}
     {"op": "end", "finish_reason": r}    -> {"tail": "text", "channel": ..., "message": {...}, "finish_reason": r'}
+    {"op": "token_texts", "ids": [...]}  -> {"texts": [...]}    (the text of single tokens, for log-probability reports)
     {"op": "quit"}
 """
 from __future__ import annotations
@@ -78,7 +79,7 @@ class Session:
         return {"ok": True, "tokens": [int(t) for t in ids], "max_tokens": p.max_tokens, "stop_token_ids": list(p.stop_token_ids),
                 "stream": opts["stream"], "temperature": p.temperature, "top_p": p.top_p, "top_k": p.top_k, "min_p": p.min_p,
                 "frequency_penalty": p.frequency_penalty, "presence_penalty": p.presence_penalty, "repetition_penalty": p.repetition_penalty,
-                "seed": int(p.seed or 0), "include_usage": opts["include_usage"]}
+                "seed": int(p.seed or 0), "include_usage": opts["include_usage"], "logprobs": p.logprobs}
 
     def _split(self, text: str, final: bool = False) -> tuple[str, str]:
         """Route a delta to the reasoning or the content channel. While reasoning, text that could still
@@ -140,6 +141,8 @@ def main(argv=None) -> int:
             out = s.token(req["token"])
         elif op == "end":
             out = s.end(req.get("finish_reason", "stop"))
+        elif op == "token_texts":
+            out = {"texts": [s.tok.decode([int(i)]) for i in req.get("ids", [])]}
         else:
             out = {"ok": False, "status": 400, "error": f"unknown op {op!r}"}
         sys.stdout.write(json.dumps(out, ensure_ascii=False) + "\n")

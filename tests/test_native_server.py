@@ -246,3 +246,21 @@ def test_sidecar_plan_carries_every_sampling_field_the_native_sampler_reads():
         assert plan[key] == pytest.approx(want), key
     bad = s.begin({"messages": [{"role": "user", "content": "hi"}], "n": 2})
     assert not bad["ok"] and bad["status"] == 400
+
+
+def test_logprobs_of_every_generated_token(server):
+    st, _, data = server.request("POST", "/v1/chat/completions", _chat(max_tokens=3, logprobs=True, top_logprobs=2))
+    out = json.loads(data)
+    assert st == 200, data
+    content = out["choices"][0]["logprobs"]["content"]
+    assert [e["token"] for e in content] == ["H", "e", "l"] and out["choices"][0]["message"]["content"] == "Hel"
+    for e in content:
+        assert e["logprob"] == pytest.approx(-0.6931472, rel=1e-5) and e["bytes"] == [ord(e["token"])]
+        assert [t["token"] for t in e["top_logprobs"]] == [e["token"], chr(ord(e["token"]) + 1)]
+        assert e["top_logprobs"][1]["logprob"] == pytest.approx(-1.3862944, rel=1e-5)
+    # logprobs without alternatives, none when not asked for, and the refusals of the request validation
+    out = json.loads(server.request("POST", "/v1/chat/completions", _chat(max_tokens=2, logprobs=True))[2])
+    assert [e["top_logprobs"] for e in out["choices"][0]["logprobs"]["content"]] == [[], []]
+    assert "logprobs" not in json.loads(server.request("POST", "/v1/chat/completions", _chat(max_tokens=2))[2])["choices"][0]
+    assert server.request("POST", "/v1/chat/completions", _chat(logprobs=True, stream=True))[0] == 400
+    assert server.request("POST", "/v1/chat/completions", _chat(top_logprobs=3))[0] == 400
