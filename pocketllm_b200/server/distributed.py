@@ -13,7 +13,7 @@ from typing import Iterator, Sequence
 
 import torch.distributed as dist
 
-from .engine import SamplingParams
+from .engine import SamplingParams, TokenInfo
 
 _SHUTDOWN = {"op": "shutdown"}
 
@@ -43,7 +43,7 @@ class DistributedBackend:
         try:
             for tok in it:
                 produced.append(int(tok))
-                yield int(tok)
+                yield tok if isinstance(tok, TokenInfo) else int(tok)      # log-probability reports pass through
         finally:
             # the consumer may have left early (client gone, stop string): the workers still run to the natural end
             if not _stops(produced, params):
