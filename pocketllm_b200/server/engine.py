@@ -178,6 +178,10 @@ class ServingEngine:
         finally:
             job.cancelled.set()
 
+    def queue_depth(self) -> int:
+        """Requests waiting for the worker (not counting the one that runs)."""
+        return self._q.qsize() + len(self._held)
+
     def close(self) -> None:
         self._q.put(None)
         self._thread.join(timeout=5)

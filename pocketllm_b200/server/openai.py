@@ -288,6 +288,19 @@ def make_handler(app: OpenAIApp):
                 self._json(200, {"status": "ok", "stats": app.engine.stats})
             elif self.path == "/v1/models":
                 self._json(200, app.models())
+            elif self.path == "/metrics":
+                # Prometheus text format: the serving engine's counters
+                lines = []
+                for key, val in sorted(app.engine.stats.items()):
+                    name = f"pocketllm_{key}_total"
+                    lines += [f"# TYPE {name} counter", f"{name} {int(val)}"]
+                lines += ["# TYPE pocketllm_queue_depth gauge", f"pocketllm_queue_depth {app.engine.queue_depth()}"]
+                data = ("\n".join(lines) + "\n").encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4")
+                self.send_header("Content-Length", str(len(data)))
+                self.end_headers()
+                self.wfile.write(data)
             else:
                 self._error(404, f"no route {self.path}")
 

@@ -246,3 +246,14 @@ def test_server_command_line_takes_profiles_config_files_and_the_reference_flag_
         oa.parse_server_args([], env={})
     with pytest.raises(ValueError):
         oa.parse_server_args(["--ckpt", str(ck), "--serving-profile", "nope"], env={})
+
+
+def test_metrics_endpoint_reports_the_engine_counters(server):
+    url, backend, app = server("ok")
+    assert _post(url, {"messages": [{"role": "user", "content": "x"}]})[0] == 200
+    with urllib.request.urlopen(url + "/metrics", timeout=20) as r:
+        text = r.read().decode()
+        assert r.headers["Content-Type"].startswith("text/plain")
+    vals = dict(line.split() for line in text.splitlines() if not line.startswith("#"))
+    assert vals["pocketllm_requests_total"] == "1" and int(vals["pocketllm_tokens_total"]) >= 2
+    assert vals["pocketllm_errors_total"] == "0" and vals["pocketllm_queue_depth"] == "0"
