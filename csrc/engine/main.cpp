@@ -60,7 +60,7 @@ struct Args {
   bool fake_engine = false;
   int port = 8000;
   // checkpoint tools and smoke / bench modes
-  std::string inspect_tensor;
+  std::string inspect_tensor, model_worker, worker_script = "Hello", worker_tokenizer_path;
   bool qwen_audit = false, smoke_forward = false;
   int smoke_layers = 4, resident_bench = 0;
 };
@@ -92,7 +92,10 @@ void usage() {
                "  --dsv4-config DIR|FILE.gguf [--tp-world N]   parse, validate and print a DeepSeek-V4 config\n"
                "  --weight-source DIR|FILE.gguf [--lookup NAME | --lookup-expert LAYER,EXPERT,w1|w2|w3]   tensor lookup by model name\n"
                "  --serve [--host H --port P --model-name N --tokenizer chars|hf:DIR|gguf:FILE --chat-format qwen|glm|minimax|dsv4\n"
-               "           --sidecar-python EXE --fake-engine-script TEXT --allow-shutdown]\n");
+               "           --sidecar-python EXE --fake-engine-script TEXT --allow-shutdown]\n"
+               "  --serve --model-worker dsv4|gguf|qwen --ckpt PATH [--worker-tokenizer-path DIR]   serve a model family whose runtime is the\n"
+               "                 Python one: this process is the HTTP / SSE front end, generation runs in a worker process\n"
+               "                 (python -m pocketllm_b200.server.model_worker) on the GPU\n");
 }
 
 Args parse(int argc, char** argv) {
@@ -168,6 +171,9 @@ Args parse(int argc, char** argv) {
     }
     else if (f == "--tokenize") { a.tokenize_text = need(i); a.have_tokenize = true; }
     else if (f == "--detokenize") a.detokenize_ids = need(i);
+    else if (f == "--model-worker") a.model_worker = need(i);
+    else if (f == "--worker-script") a.worker_script = need(i);
+    else if (f == "--worker-tokenizer-path") a.worker_tokenizer_path = need(i);
     else if (f == "--inspect-tensor") a.inspect_tensor = need(i);
     else if (f == "--qwen-audit") a.qwen_audit = true;
     else if (f == "--smoke-forward") a.smoke_forward = true;
@@ -359,6 +365,25 @@ int serve_scripted(const Args& a) {
   pk::Sidecar sidecar(sidecar_command(a));
   pk::HttpServer http(a.host, a.port);
   std::printf("openai_server_listening host=%s port=%d engine=scripted\n", a.host.c_str(), http.port());
+  std::fflush(stdout);
+  pk::OpenAIServerOptions so;
+  so.model_name = a.model_name;
+  so.allow_shutdown = a.allow_shutdown;
+  pk::run_openai_server(http, *eng, sidecar, so);
+  return 0;
+}
+
+// The native front end in front of a Python model worker (DeepSeek-V4 runtime, GGUF runtimes).
+int serve_worker(const Args& a) {
+  std::vector<std::string> cmd = {a.sidecar_python, "-m", "pocketllm_b200.server.model_worker", "--model", a.model_worker,
+                                  "--max-context", std::to_string(a.max_context)};
+  if (!a.ckpt.empty()) { cmd.push_back("--ckpt"); cmd.push_back(a.ckpt); }
+  if (!a.worker_tokenizer_path.empty()) { cmd.push_back("--tokenizer-path"); cmd.push_back(a.worker_tokenizer_path); }
+  if (a.model_worker == "scripted") { cmd.push_back("--script"); cmd.push_back(a.worker_script); }
+  auto eng = pk::make_worker_engine(cmd);
+  pk::Sidecar sidecar(sidecar_command(a));
+  pk::HttpServer http(a.host, a.port);
+  std::printf("openai_server_listening host=%s port=%d engine=worker model=%s\n", a.host.c_str(), http.port(), a.model_worker.c_str());
   std::fflush(stdout);
   pk::OpenAIServerOptions so;
   so.model_name = a.model_name;
@@ -591,6 +616,7 @@ int run(const Args& a) {
   if (!a.dsv4_config.empty()) return dsv4_config_tool(a);
   if (!a.weight_source.empty()) return weight_source_tool(a);
   if (a.serve && a.fake_engine) return serve_scripted(a);
+  if (a.serve && !a.model_worker.empty()) return serve_worker(a);
   if (!a.inspect_tensor.empty()) return inspect_tensor(a);
   if (a.qwen_audit) return qwen_audit(a);
   if (a.inspect) {

@@ -145,6 +145,65 @@ int64_t now_s() { return (int64_t)std::chrono::duration_cast<std::chrono::second
 
 }  // namespace
 
+namespace {
+class WorkerEngine : public TokenEngine {
+ public:
+  explicit WorkerEngine(const std::vector<std::string>& argv) : worker_(argv) {
+    const Json hello = worker_.call(Json::parse("{\"op\":\"hello\"}"));
+    max_context_ = (int)hello.get_int("max_context", 4096);
+  }
+  int max_context() const override { return max_context_; }
+  int prefill(const std::vector<int>& prompt, const SamplerConfig& sc, uint64_t seed) override {
+    Json req = Json::object();
+    req["op"] = Json("prefill");
+    req["tokens"] = Json::array();
+    for (int t : prompt) req["tokens"].push_back(Json(t));
+    Json s = Json::object();
+    s["temperature"] = Json((double)sc.temperature);
+    s["top_p"] = Json((double)sc.top_p);
+    s["top_k"] = Json(sc.top_k);
+    s["min_p"] = Json((double)sc.min_p);
+    s["frequency_penalty"] = Json((double)sc.frequency_penalty);
+    s["presence_penalty"] = Json((double)sc.presence_penalty);
+    s["repetition_penalty"] = Json((double)sc.repetition_penalty);
+    s["logprobs"] = Json(sc.logprobs);
+    req["sampler"] = s;
+    req["seed"] = Json((int64_t)(seed & 0x7fffffffULL));
+    return take(worker_.call(req));
+  }
+  int next() override { return take(worker_.call(Json::parse("{\"op\":\"next\"}"))); }
+  bool last_logprobs(TokenLogprobs* out) override {
+    if (!have_lp_) return false;
+    *out = lp_;
+    return true;
+  }
+
+ private:
+  int take(const Json& reply) {
+    if (const Json* err = reply.find("error")) {
+      if (reply.get_bool("lost", false)) throw EngineStepFailed(err->as_string());
+      throw std::runtime_error(err->as_string());
+    }
+    have_lp_ = false;
+    if (const Json* lp = reply.find("logprob")) {
+      lp_.chosen = (float)lp->as_double();
+      lp_.top.clear();
+      if (const Json* top = reply.find("top"))
+        for (const Json& e : top->items())
+          if (e.items().size() == 2) lp_.top.emplace_back((int)e.items()[0].as_int(), (float)e.items()[1].as_double());
+      have_lp_ = true;
+    }
+    return (int)reply.get_int("token", 0);
+  }
+  Sidecar worker_;
+  int max_context_ = 4096;
+  TokenLogprobs lp_;
+  bool have_lp_ = false;
+};
+}  // namespace
+
+std::unique_ptr<TokenEngine> make_worker_engine(const std::vector<std::string>& argv) { return std::make_unique<WorkerEngine>(argv); }
+
 std::unique_ptr<TokenEngine> make_scripted_engine(const std::string& script, int max_context) {
   return std::make_unique<ScriptedEngine>(script, max_context);
 }

@@ -63,6 +63,11 @@ struct OpenAIServerOptions {
 // Blocks until stopped.
 void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, const OpenAIServerOptions& opt);
 
+// A model that lives in a child process (`python -m pocketllm_b200.server.model_worker ...`) and speaks JSON lines:
+// prefill / next / log-probabilities are forwarded, a reply marked "lost" becomes EngineStepFailed. This is how the
+// native front end serves the model families whose runtime is the Python one (DeepSeek-V4, the GGUF runtimes).
+std::unique_ptr<TokenEngine> make_worker_engine(const std::vector<std::string>& argv);
+
 // Deterministic stand-in for a model: replays `script` code points, then token 0 (EOS), for every request.
 // The code point U+2620 in the script makes that step throw EngineStepFailed (to test the error path).
 std::unique_ptr<TokenEngine> make_scripted_engine(const std::string& script, int max_context);

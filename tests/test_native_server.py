@@ -264,3 +264,52 @@ def test_logprobs_of_every_generated_token(server):
     assert "logprobs" not in json.loads(server.request("POST", "/v1/chat/completions", _chat(max_tokens=2))[2])["choices"][0]
     assert server.request("POST", "/v1/chat/completions", _chat(logprobs=True, stream=True))[0] == 400
     assert server.request("POST", "/v1/chat/completions", _chat(top_logprobs=3))[0] == 400
+
+
+class WorkerServer(Server):
+    """The native front end in front of a Python model worker (here the worker's scripted stand-in model)."""
+
+    def __init__(self, script: str):
+        env = dict(os.environ, PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        self.proc = subprocess.Popen(
+            [str(BINARY), "--serve", "--port", "0", "--model-worker", "scripted", "--worker-script", script, "--tokenizer", "chars", "--chat-format", "dsv4",
+             "--sidecar-python", sys.executable, "--allow-shutdown", "--max-context", "512", "--model-name", "worker"],
+            stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+        line = self.proc.stdout.readline()
+        assert line.startswith("openai_server_listening") and "engine=worker" in line, (line, self.proc.stderr.read() if self.proc.poll() is not None else "")
+        self.port = int(dict(kv.split("=") for kv in line.split()[1:])["port"])
+
+
+def test_native_front_end_serves_a_python_model_worker():
+    s = WorkerServer("Bonjour ☠ monde")
+    try:
+        out = json.loads(s.request("POST", "/v1/chat/completions", _chat(max_tokens=7))[2])
+        assert out["choices"][0]["message"]["content"] == "Bonjour" and out["choices"][0]["finish_reason"] == "length"
+        out = json.loads(s.request("POST", "/v1/chat/completions", _chat(max_tokens=3, logprobs=True, top_logprobs=1))[2])
+        content = out["choices"][0]["logprobs"]["content"]
+        assert [e["token"] for e in content] == ["B", "o", "n"] and content[0]["logprob"] == pytest.approx(-0.6931472, rel=1e-5)
+        assert [t["token"] for t in content[1]["top_logprobs"]] == ["o"]
+        # the worker's step failure (a lost step) ends the request with 500; the next request is served
+        st, _, data = s.request("POST", "/v1/chat/completions", _chat(max_tokens=20))
+        assert st == 500 and json.loads(data)["error"]["type"] == "engine_error"
+        assert s.request("POST", "/v1/chat/completions", _chat(max_tokens=2))[0] == 200
+        # the context limit comes from the worker
+        assert s.request("POST", "/v1/chat/completions", _chat(max_tokens=100000))[0] == 400
+    finally:
+        s.close()
+
+
+def test_model_worker_protocol_in_process():
+    import io
+    from pocketllm_b200.server import model_worker as mw
+    reqs = [{"op": "hello"}, {"op": "next"}, {"op": "prefill", "tokens": [1, 2], "sampler": {"logprobs": 1}}, {"op": "next"}, {"op": "next"},
+            {"op": "next"}, {"op": "bogus"}, {"op": "quit"}, {"op": "hello"}]
+    out = io.StringIO()
+    mw.serve(mw.ScriptedBackend("ab"), "scripted", 64, stdin=io.StringIO("".join(json.dumps(r) + "\n" for r in reqs)), stdout=out)
+    replies = [json.loads(l) for l in out.getvalue().splitlines()]
+    assert len(replies) == 7                                              # nothing after quit
+    assert replies[0] == {"ok": True, "max_context": 64, "model": "scripted"}
+    assert "next before prefill" in replies[1]["error"] and replies[1]["lost"] is False
+    assert replies[2]["token"] == ord("a") and replies[2]["top"] == [[ord("a"), pytest.approx(-0.6931472)]]
+    assert replies[3]["token"] == ord("b") and replies[4]["token"] == 0 and replies[5] == {"token": 0, "done": True}
+    assert "unknown op" in replies[6]["error"]
