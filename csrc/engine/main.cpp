@@ -61,6 +61,7 @@ struct Args {
   int port = 8000;
   // checkpoint tools and smoke / bench modes
   std::string inspect_tensor, model_worker, worker_script = "Hello", worker_tokenizer_path;
+  int worker_ranks = 1, worker_port = 29641;
   bool qwen_audit = false, smoke_forward = false;
   int smoke_layers = 4, resident_bench = 0;
 };
@@ -93,7 +94,7 @@ void usage() {
                "  --weight-source DIR|FILE.gguf [--lookup NAME | --lookup-expert LAYER,EXPERT,w1|w2|w3]   tensor lookup by model name\n"
                "  --serve [--host H --port P --model-name N --tokenizer chars|hf:DIR|gguf:FILE --chat-format qwen|glm|minimax|dsv4\n"
                "           --sidecar-python EXE --fake-engine-script TEXT --allow-shutdown]\n"
-               "  --serve --model-worker dsv4|gguf|qwen --ckpt PATH [--worker-tokenizer-path DIR]   serve a model family whose runtime is the\n"
+               "  --serve --model-worker dsv4|gguf|qwen --ckpt PATH [--worker-tokenizer-path DIR] [--worker-ranks N]   serve a model family whose runtime is the\n"
                "                 Python one: this process is the HTTP / SSE front end, generation runs in a worker process\n"
                "                 (python -m pocketllm_b200.server.model_worker) on the GPU\n");
 }
@@ -173,6 +174,8 @@ Args parse(int argc, char** argv) {
     else if (f == "--detokenize") a.detokenize_ids = need(i);
     else if (f == "--model-worker") a.model_worker = need(i);
     else if (f == "--worker-script") a.worker_script = need(i);
+    else if (f == "--worker-ranks") a.worker_ranks = std::stoi(need(i));
+    else if (f == "--worker-master-port") a.worker_port = std::stoi(need(i));
     else if (f == "--worker-tokenizer-path") a.worker_tokenizer_path = need(i);
     else if (f == "--inspect-tensor") a.inspect_tensor = need(i);
     else if (f == "--qwen-audit") a.qwen_audit = true;
@@ -375,8 +378,17 @@ int serve_scripted(const Args& a) {
 
 // The native front end in front of a Python model worker (DeepSeek-V4 runtime, GGUF runtimes).
 int serve_worker(const Args& a) {
-  std::vector<std::string> cmd = {a.sidecar_python, "-m", "pocketllm_b200.server.model_worker", "--model", a.model_worker,
-                                  "--max-context", std::to_string(a.max_context)};
+  std::vector<std::string> cmd = {a.sidecar_python};
+  if (a.worker_ranks > 1) {
+    // one worker rank per GPU: rank 0 inherits this pipe, the other ranks follow its requests
+    for (const char* s : {"-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node"}) cmd.push_back(s);
+    cmd.push_back(std::to_string(a.worker_ranks));
+    for (const char* s : {"--master-addr", "127.0.0.1", "--master-port"}) cmd.push_back(s);
+    cmd.push_back(std::to_string(a.worker_port));
+  }
+  for (const std::string& s : {std::string("-m"), std::string("pocketllm_b200.server.model_worker"), std::string("--model"), a.model_worker,
+                               std::string("--max-context"), std::to_string(a.max_context)})
+    cmd.push_back(s);
   if (!a.ckpt.empty()) { cmd.push_back("--ckpt"); cmd.push_back(a.ckpt); }
   if (!a.worker_tokenizer_path.empty()) { cmd.push_back("--tokenizer-path"); cmd.push_back(a.worker_tokenizer_path); }
   if (a.model_worker == "scripted") { cmd.push_back("--script"); cmd.push_back(a.worker_script); }

@@ -168,10 +168,14 @@ class WorkerEngine : public TokenEngine {
     s["repetition_penalty"] = Json((double)sc.repetition_penalty);
     s["logprobs"] = Json(sc.logprobs);
     req["sampler"] = s;
+    req["max_tokens"] = Json(sc.max_tokens);
+    req["stop_token_ids"] = Json::array();
+    for (int t : sc.stop_token_ids) req["stop_token_ids"].push_back(Json(t));
     req["seed"] = Json((int64_t)(seed & 0x7fffffffULL));
     return take(worker_.call(req));
   }
   int next() override { return take(worker_.call(Json::parse("{\"op\":\"next\"}"))); }
+  void finish() override { worker_.call(Json::parse("{\"op\":\"end\"}")); }
   bool last_logprobs(TokenLogprobs* out) override {
     if (!have_lp_) return false;
     *out = lp_;
@@ -284,6 +288,8 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
     sc.presence_penalty = (float)plan.get_double("presence_penalty", 0.0);
     sc.repetition_penalty = (float)plan.get_double("repetition_penalty", 1.0);
     sc.logprobs = (int)plan.get_int("logprobs", -1);
+    sc.max_tokens = max_tokens;
+    sc.stop_token_ids = eos;
     std::vector<std::pair<int, TokenLogprobs>> lps;      // generated tokens (no end-of-sequence token) with their log-probabilities
     const uint64_t seed = (uint64_t)plan.get_int("seed", 0) * 0x9E3779B97F4A7C15ULL + 0x1234567ULL;
     const std::string id = "chatcmpl-" + std::to_string(now_s()) + "-" + std::to_string(++counter);
@@ -312,6 +318,15 @@ void run_openai_server(HttpServer& http, TokenEngine& engine, Sidecar& sidecar, 
     int generated = 0;
     std::string finish = "length";
     int tok = 0;
+    struct RequestEnd {
+      TokenEngine& e;
+      ~RequestEnd() {
+        try {
+          e.finish();
+        } catch (...) {
+        }
+      }
+    } request_end{engine};
     try {
       tok = engine.prefill(prompt, sc, seed);
     } catch (const std::exception& e) {

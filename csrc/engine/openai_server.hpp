@@ -34,6 +34,9 @@ class TokenEngine {
   virtual int prefill(const std::vector<int>& prompt, const SamplerConfig& sampler, uint64_t seed) = 0;
   // The token after the last one returned.
   virtual int next() = 0;
+  // The request that prefill() started is over (all of its tokens were taken, or it was cut short): engines that run
+  // ahead or in other processes settle here. Called once per started request.
+  virtual void finish() {}
   // Log-probabilities of the step that produced the token returned last, when the request's sampler asked for them
   // (`SamplerConfig::logprobs >= 0`); false when this engine cannot report them.
   virtual bool last_logprobs(TokenLogprobs* out) {

@@ -18,6 +18,10 @@ struct SamplerConfig {
   float frequency_penalty = 0.f, presence_penalty = 0.f;
   float repetition_penalty = 1.f;
   int logprobs = -1;         // -1: off; k >= 0: the engine reports the log-probability of every token and of the k most likely ones
+  // The request's limits, for engines that generate ahead of the server or run on several ranks (every rank must leave a
+  // request at the same step): 0 / empty when unknown. The server itself enforces both.
+  int max_tokens = 0;
+  std::vector<int> stop_token_ids;
   bool has_penalties() const { return frequency_penalty != 0.f || presence_penalty != 0.f || repetition_penalty != 1.f; }
 };
 

@@ -313,3 +313,23 @@ def test_model_worker_protocol_in_process():
     assert replies[2]["token"] == ord("a") and replies[2]["top"] == [[ord("a"), pytest.approx(-0.6931472)]]
     assert replies[3]["token"] == ord("b") and replies[4]["token"] == 0 and replies[5] == {"token": 0, "done": True}
     assert "unknown op" in replies[6]["error"]
+
+
+def test_model_worker_on_two_ranks_follows_rank_zero(tmp_path):
+    """The worker under torchrun (gloo, CPU): rank 0 answers on the pipe, rank 1 follows every request to the step where
+    the limits end it."""
+    import socket
+    with socket.socket() as so:
+        so.bind(("127.0.0.1", 0))
+        port = so.getsockname()[1]
+    env = dict(os.environ, PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    reqs = [{"op": "hello"}, {"op": "prefill", "tokens": [1, 2, 3], "sampler": {}, "max_tokens": 3, "stop_token_ids": [0]}, {"op": "next"},
+            {"op": "prefill", "tokens": [4], "sampler": {}, "max_tokens": 50, "stop_token_ids": [ord("l")]}, {"op": "next"}, {"op": "next"}, {"op": "quit"}]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", str(port), "-m", "pocketllm_b200.server.model_worker", "--model", "scripted", "--script", "Hello", "--max-context", "64"],
+                       input="".join(json.dumps(q) + "\n" for q in reqs), capture_output=True, text=True, timeout=240, env=env)
+    assert r.returncode == 0, r.stderr[-3000:]
+    replies = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert replies[0]["ok"] and [x["token"] for x in replies[1:3]] == [ord("H"), ord("e")]
+    assert [x["token"] for x in replies[3:6]] == [ord("H"), ord("e"), ord("l")]
+    assert "rank 1: followed 2 requests" in r.stderr
