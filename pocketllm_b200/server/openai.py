@@ -192,22 +192,21 @@ class OpenAIApp:
         params, opts, ids = self._prepare(body)
         choices, completion_tokens, timings = [], 0, None
         # no lock here: whole completions may share a batch in the serving engine, which serialises everything else
-        if True:
-            for i in range(opts["n"]):
-                info = None
-                for kind, val in self._run(ids, params, opts, batchable=not opts["logprobs"]):
-                    if kind == "done":
-                        info = val
-                msg = self.tok.parse(info["text"], opts["thinking"])
-                finish = "tool_calls" if msg.get("tool_calls") else info["finish_reason"]
-                choice = {"index": i, "message": msg, "finish_reason": finish}
-                if opts["logprobs"]:
-                    if not info["logprobs"] and info["completion_tokens"] > 1:
-                        raise BadRequest("this model backend does not report log-probabilities")
-                    choice["logprobs"] = {"content": [self._logprob_entry(t) for t in info["logprobs"]]}
-                choices.append(choice)
-                completion_tokens += info["completion_tokens"]
-                timings = info["timings"]
+        for i in range(opts["n"]):
+            info = None
+            for kind, val in self._run(ids, params, opts, batchable=not opts["logprobs"]):
+                if kind == "done":
+                    info = val
+            msg = self.tok.parse(info["text"], opts["thinking"])
+            finish = "tool_calls" if msg.get("tool_calls") else info["finish_reason"]
+            choice = {"index": i, "message": msg, "finish_reason": finish}
+            if opts["logprobs"]:
+                if not info["logprobs"] and info["completion_tokens"] > 1:
+                    raise BadRequest("this model backend does not report log-probabilities")
+                choice["logprobs"] = {"content": [self._logprob_entry(t) for t in info["logprobs"]]}
+            choices.append(choice)
+            completion_tokens += info["completion_tokens"]
+            timings = info["timings"]
         return {"id": "chatcmpl-" + uuid.uuid4().hex[:24], "object": "chat.completion", "created": int(time.time()),
                 "model": self.model_name, "choices": choices,
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": completion_tokens, "total_tokens": len(ids) + completion_tokens},
