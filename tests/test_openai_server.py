@@ -257,3 +257,17 @@ def test_metrics_endpoint_reports_the_engine_counters(server):
     vals = dict(line.split() for line in text.splitlines() if not line.startswith("#"))
     assert vals["pocketllm_requests_total"] == "1" and int(vals["pocketllm_tokens_total"]) >= 2
     assert vals["pocketllm_errors_total"] == "0" and vals["pocketllm_queue_depth"] == "0"
+
+
+def test_backend_is_detected_from_a_gguf_files_architecture(tmp_path):
+    import numpy as np
+    from pocketllm_b200.formats import gguf
+    for arch, want in (("deepseek4", "dsv4"), ("minimax-m2", "gguf"), ("glm-dsa", "gguf")):
+        w = gguf.GGUFWriter()
+        w.add_meta("general.architecture", arch)
+        w.add_tensor("token_embd.weight", np.zeros((2, 4), dtype=np.float32), "f32", (2, 4))
+        path = tmp_path / f"{arch}.gguf"
+        w.write(path)
+        assert oa.detect_model_kind(str(path)) == want
+        args, st = oa.parse_server_args(["--ckpt", str(path)], env={})
+        assert st["kind"] == want
