@@ -120,3 +120,53 @@ def speculative_generate(engine, prompt: Sequence[int], max_new_tokens: int, dra
     finally:
         snap.free()
     return out[:max_new_tokens], stats
+
+
+class DrafterSpeculator:
+    """Round-at-a-time form of `speculative_generate` for serving loops: `prefill(prompt)` returns the first token,
+    `decode(last, n)` runs ONE round (draft, verify rows, rewind and replay on a reject) and returns between 1 and n new
+    tokens. Tokens equal plain greedy decoding. Same interface as the block-drafter speculator of the Qwen backend, so any
+    model-free drafter (`NGramDrafter`) can speed up greedy requests."""
+
+    def __init__(self, engine, drafter: Drafter, k: int = 4):
+        if not 1 <= k <= 7:
+            raise ValueError("k must be in 1..7 (verify passes hold at most 8 rows)")
+        self.engine, self.drafter, self.k = engine, drafter, k
+        self.ctx: list[int] = []
+        self.snap = None
+        self.stats = SpecStats()
+
+    def prefill(self, prompt: Sequence[int]) -> int:
+        first = self.engine.prefill(list(prompt))
+        self.ctx = list(prompt) + [first]
+        if self.snap is not None:
+            self.snap.free()
+        self.snap = self.engine.snapshot()
+        return first
+
+    def decode(self, last: int, n: int) -> list[int]:
+        if n < 1:
+            return []
+        draft = self.drafter.propose(self.ctx, min(self.k, n - 1)) if n > 1 else []
+        if not draft:
+            new = [self.engine.forward_rows([last])[0]]
+            self.stats.plain_steps += 1
+        else:
+            self.snap.update()
+            rows = [last] + draft
+            pred = self.engine.forward_rows(rows)
+            a = 0
+            while a < len(draft) and pred[a] == draft[a]:
+                a += 1
+            self.stats.rounds += 1
+            self.stats.drafted += len(draft)
+            self.stats.accepted += a
+            self.stats.accept_hist.append(a)
+            if a < len(draft):
+                self.snap.restore()
+                pred = self.engine.forward_rows(rows[:a + 1])
+                self.stats.replays += 1
+            new = draft[:a] + [pred[a]]
+        self.ctx += new
+        self.stats.emitted += len(new)
+        return new

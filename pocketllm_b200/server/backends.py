@@ -154,10 +154,12 @@ class HFChatTokenizer:
 
 
 def build(kind: str, ckpt: str, max_context: int, qwen_dspark: str | None = None, tokenizer_path: str | None = None,
-          layer_pipeline: bool = False):
+          layer_pipeline: bool = False, speculative: tuple[str, int] = ("off", 4)):
     """(backend, tokenizer) for `--model qwen|gguf|dsv4`. Under torchrun every rank builds its shard (rank and world come
     from the environment). `tokenizer_path`: directory with tokenizer.json when it is not the checkpoint directory.
-    `layer_pipeline` (dsv4, several ranks): contiguous layer ranges per rank instead of expert parallelism."""
+    `layer_pipeline` (dsv4, several ranks): contiguous layer ranges per rank instead of expert parallelism.
+    `speculative` = (mode, draft length) of the typed configuration: `ngram` gives the Qwen backend a prompt-lookup drafter
+    (greedy requests run as draft + verify rounds with the same tokens as plain decoding)."""
     import os
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     if kind == "dsv4":
@@ -218,6 +220,9 @@ def build(kind: str, ckpt: str, max_context: int, qwen_dspark: str | None = None
             embed = model.get(embed_name)
             lm_head = model.get("lm_head.weight") if "lm_head.weight" in names else embed
             spec = QwenDSparkSpeculator(eng, QwenDSparkRuntime(dcfg, dw, embed, lm_head, max_context=max_context, device=f"cuda:{local}"))
+        if spec is None and speculative[0] == "ngram":
+            from ..runtime.speculative import DrafterSpeculator, NGramDrafter
+            spec = DrafterSpeculator(eng, NGramDrafter(), k=max(1, min(int(speculative[1]), 7)))
         return QwenBackend(eng, speculator=spec), HFChatTokenizer(tok, render, eos)
     from ..models import registry
     md = gguf_tokenizer.read_metadata(ckpt)

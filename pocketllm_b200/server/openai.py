@@ -404,6 +404,7 @@ def parse_server_args(argv=None, env=None):
     settings = {"kind": kind, "model_name": name, "host": args.host or cfg.serving.host, "port": args.port if args.port is not None else cfg.serving.port,
                 "max_context": args.max_context if args.max_context is not None else cfg.model.max_context, "max_queue": cfg.serving.max_queue,
                 "layer_pipeline": args.partition_policy.startswith("layer_pp") or cfg.parallel.policy == "layer_pp",
+                "speculative": (cfg.speculative.mode, cfg.speculative.draft_len),
                 "profile": args.serving_profile or None}
     return args, settings
 
@@ -422,7 +423,7 @@ def main(argv=None) -> int:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         group = distributed.control_group()
     backend, tokenizer = backends.build(st["kind"], args.ckpt, st["max_context"], qwen_dspark=args.qwen_dspark or None,
-                                        tokenizer_path=args.tokenizer_path, layer_pipeline=st["layer_pipeline"])
+                                        tokenizer_path=args.tokenizer_path, layer_pipeline=st["layer_pipeline"], speculative=st["speculative"])
     if world > 1 and rank != 0:
         served = distributed.worker_loop(backend, group)
         print(f"worker {rank}: served {served} requests", flush=True)

@@ -234,6 +234,8 @@ def test_server_command_line_takes_profiles_config_files_and_the_reference_flag_
     args, st = oa.parse_server_args(["--ckpt", str(ck), "--model", "qwen", "--config", str(cfgf), "--port", "9002"],
                                     env={"SERVING_PROFILE": "safe1"})
     assert st["max_queue"] == 1 and st["port"] == 9002 and st["model_name"] == "from-file" and st["max_context"] == 1024 and st["profile"] == "safe1"
+    assert st["speculative"] == ("off", 4)
+    assert oa.parse_server_args(["--ckpt", str(ck), "--serving-profile", "latency2"], env={})[1]["speculative"] == ("ngram", 4)
     # a directory without DeltaNet fields is a DeepSeek-V4 checkpoint; its layer pipeline is a partition policy
     d4dir = tmp_path / "d4"
     d4dir.mkdir()

@@ -136,6 +136,23 @@ def test_speculative_matches_plain_greedy_for_any_drafter():
     assert out == ref
 
 
+def test_round_at_a_time_speculator_matches_plain_greedy():
+    from pocketllm_b200.runtime.speculative import DrafterSpeculator, NGramDrafter, ReplayDrafter
+    prompt = [1, 2, 3, 4, 5, 1, 2, 3]
+    ref = _plain(prompt, 40)
+    for drafter in (NGramDrafter(), ReplayDrafter(ref[1:], len(prompt) + 1), ReplayDrafter([(t + 1) % 11 for t in ref[1:]], len(prompt) + 1)):
+        sp = DrafterSpeculator(_FakeEngine(), drafter, k=4)
+        out = [sp.prefill(prompt)]
+        while len(out) < 40:
+            new = sp.decode(out[-1], min(8, 40 - len(out)))
+            assert 1 <= len(new) <= min(8, 40 - len(out))
+            out += new
+        assert out == ref
+    assert sp.stats.replays == sp.stats.rounds > 0                     # the adversarial drafter: every round rewinds
+    # a second request on the same speculator starts from a fresh context
+    assert sp.prefill(prompt) == ref[0] and sp.ctx == prompt + [ref[0]]
+
+
 def test_speculative_respects_eos_and_gate():
     from pocketllm_b200.runtime.dspark_gate import DSparkGate
     from pocketllm_b200.runtime.speculative import ReplayDrafter, speculative_generate
