@@ -77,6 +77,34 @@ def build_params(body: dict, eos_ids: tuple[int, ...]) -> tuple[SamplingParams, 
     return p, opts
 
 
+def with_tool_directive(messages: list, tools, tool_choice, parallel_tool_calls) -> list:
+    """`tool_choice` = "required" or a named function, and `parallel_tool_calls` = false, are instructions to the model:
+    they are folded into the system message (a new one in front when the conversation has none). "auto" and "none" add
+    nothing ("none" already removed the tools)."""
+    if not tools:
+        return messages
+    notes = []
+    if tool_choice == "required":
+        notes.append("You must answer by calling one of the available tools.")
+    elif isinstance(tool_choice, dict):
+        name = (tool_choice.get("function") or {}).get("name") or tool_choice.get("name")
+        if name:
+            if name not in {(t.get("function") or t).get("name") for t in tools if isinstance(t, dict)}:
+                raise BadRequest(f"`tool_choice` names an unknown tool {name!r}")
+            notes.append(f"You must answer by calling the tool `{name}`.")
+    if parallel_tool_calls is False:
+        notes.append("Call at most one tool in this turn.")
+    if not notes:
+        return messages
+    note = " ".join(notes)
+    out = [dict(m) for m in messages]
+    for m in out:
+        if m.get("role") == "system" and isinstance(m.get("content"), str):
+            m["content"] = m["content"] + "\n\n" + note
+            return out
+    return [{"role": "system", "content": note}] + out
+
+
 class StreamingDecoder:
     """Incremental detokeniser with stop-string handling: text that could still turn into a
     stop string is held back, and nothing after a stop string is ever emitted."""
@@ -136,7 +164,8 @@ class OpenAIApp:
 
     def _prepare(self, body: dict):
         params, opts = build_params(body, tuple(self.tok.eos_ids))
-        ids = self.tok.encode_chat(body["messages"], tools=opts["tools"], thinking=opts["thinking"],
+        messages = with_tool_directive(body["messages"], opts["tools"], body.get("tool_choice"), body.get("parallel_tool_calls"))
+        ids = self.tok.encode_chat(messages, tools=opts["tools"], thinking=opts["thinking"],
                                    reasoning_effort=opts["reasoning_effort"], response_format=opts["response_format"])
         if len(ids) + 1 > self.max_context:
             raise BadRequest(f"prompt has {len(ids)} tokens, the context limit is {self.max_context}")

@@ -273,3 +273,15 @@ def test_backend_is_detected_from_a_gguf_files_architecture(tmp_path):
         assert oa.detect_model_kind(str(path)) == want
         args, st = oa.parse_server_args(["--ckpt", str(path)], env={})
         assert st["kind"] == want
+
+
+def test_tool_choice_and_parallel_tool_calls_become_instructions():
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {}}}]
+    msgs = [{"role": "user", "content": "hi"}]
+    assert oa.with_tool_directive(msgs, tools, "auto", None) is msgs and oa.with_tool_directive(msgs, None, "required", False) is msgs
+    out = oa.with_tool_directive(msgs, tools, "required", False)
+    assert out[0]["role"] == "system" and "must answer by calling one of" in out[0]["content"] and "at most one tool" in out[0]["content"] and out[1:] == msgs
+    named = oa.with_tool_directive([{"role": "system", "content": "Be brief."}] + msgs, tools, {"type": "function", "function": {"name": "get_weather"}}, None)
+    assert named[0]["content"].startswith("Be brief.") and "`get_weather`" in named[0]["content"] and len(named) == 2
+    with pytest.raises(oa.BadRequest):
+        oa.with_tool_directive(msgs, tools, {"type": "function", "function": {"name": "nope"}}, None)
