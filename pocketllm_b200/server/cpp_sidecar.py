@@ -20,7 +20,7 @@ import json
 import sys
 
 from ..encoding import dsv4
-from .openai import BadRequest, StreamingDecoder, build_params
+from .openai import BadRequest, StreamingDecoder, build_params, with_tool_directive
 
 
 class CharTokenizer:
@@ -67,7 +67,8 @@ class Session:
             p, opts = build_params(body, tuple(self.tok.eos_ids))
             if opts["n"] != 1:
                 raise BadRequest("the native server generates one choice per request")
-            ids = self.tok.encode_chat(body["messages"], tools=opts["tools"], thinking=opts["thinking"],
+            messages = with_tool_directive(body["messages"], opts["tools"], body.get("tool_choice"), body.get("parallel_tool_calls"))
+            ids = self.tok.encode_chat(messages, tools=opts["tools"], thinking=opts["thinking"],
                                        reasoning_effort=opts["reasoning_effort"], response_format=opts["response_format"])
         except BadRequest as e:
             return {"ok": False, "status": 400, "error": str(e)}
