@@ -80,16 +80,18 @@ class GGUFBackend:
 
     def generate(self, prompt_ids: Sequence[int], p: SamplingParams) -> Iterator[int]:
         self.rt.reset()
-        if p.logprobs >= 0:
+        greedy = p.temperature <= 0 and p.repetition_penalty == 1.0 and p.frequency_penalty == 0 and p.presence_penalty == 0
+        if p.logprobs >= 0 or not greedy:
+            # sampled or penalised requests, and log-probability reports, take every step's logits through the host sampler
             if not hasattr(self.rt, "forward_logits"):
-                raise RuntimeError("this runtime does not expose logits: log-probabilities are not available")
+                raise RuntimeError("this runtime does not expose logits: sampling and log-probabilities are not available")
             gen = torch.Generator().manual_seed(p.seed) if p.seed is not None else None
             raw = self.rt.forward_logits(list(prompt_ids))
             produced: list[int] = []
             while True:
                 t = sample_token(apply_penalties(raw.clone(), produced, p), p, gen)
                 produced.append(t)
-                yield token_logprobs(raw, t, p.logprobs)
+                yield token_logprobs(raw, t, p.logprobs) if p.logprobs >= 0 else t
                 if len(produced) >= p.max_tokens or t in p.stop_token_ids:
                     return
                 raw = self.rt.forward_logits([t])

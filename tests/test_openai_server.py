@@ -208,6 +208,10 @@ def test_backends_report_logprobs_from_their_logits():
     assert [t.token for t in got] == [4, 0, 2] and all(abs(t.logprob - float(torch.log_softmax(torch.tensor([3.0, 0, 0, 0, 0, 0]), -1)[0])) < 1e-6 for t in got)
     assert all(t.top[0][0] == t.token for t in got)
 
+    # a penalised request without log-probabilities also goes through the logits (plain ints come out)
+    pen = list(GGUFBackend(Runtime()).generate([1, 2], SamplingParams(max_tokens=3, repetition_penalty=100.0, stop_token_ids=(5,))))
+    assert pen[0] == 4 and all(isinstance(t, int) for t in pen) and len(pen) == 3
+
     class Runtime2(Runtime):
         def forward_logits(self, tokens):
             return super().forward_logits(tokens).unsqueeze(0)          # [rows, vocab]
