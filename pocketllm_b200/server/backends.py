@@ -24,7 +24,7 @@ class QwenBackend:
         eng = self.eng
         eng.reset()
         plain = p.temperature <= 0 and p.repetition_penalty == 1.0 and p.frequency_penalty == 0 and p.presence_penalty == 0
-        if self.spec is not None and plain:
+        if self.spec is not None and plain and p.logprobs < 0:
             first = self.spec.prefill(list(prompt_ids))
             yield first
             n, last = 1, first
