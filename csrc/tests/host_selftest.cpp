@@ -12,6 +12,8 @@
 #include <vector>
 
 #include "../common/pk_comm_host.hpp"
+#include "../engine/qwen_audit.hpp"
+#include "../engine/tokenizer.hpp"
 #include "../engine/control_plane.hpp"
 #include "../engine/gguf_reader.hpp"
 #include "../engine/json.hpp"
@@ -64,6 +66,45 @@ static int test_readers(const std::string& gguf_path, const std::string& st_dir)
     if (t.nbytes) sum += ((const uint8_t*)t.data)[0] + ((const uint8_t*)t.data)[t.nbytes - 1];
   }
   std::printf("readers_checksum=%llu\n", (unsigned long long)sum);
+  return 0;
+}
+
+// Checkpoint audit on a complete tiny checkpoint: everything the engine reads is found; four ranks do not cut its
+// 128-row blocks evenly and are refused.
+static int test_qwen_audit(const std::string& st_dir) {
+  pk::SafetensorsModel st(st_dir);
+  const pk::QwenConfig cfg = pk::QwenConfig::from_file(st_dir + "/config.json");
+  const pk::QwenAuditReport one = pk::audit_qwen_checkpoint(st, cfg, 1, false);
+  CHECK(one.ok() && one.expected > 20 && one.fp8_linears > 0 && one.unused.empty() && one.expected_bytes > 0);
+  const pk::QwenAuditReport four = pk::audit_qwen_checkpoint(st, cfg, 4, false);
+  CHECK(!four.ok());
+  const pk::QwenAuditReport mtp = pk::audit_qwen_checkpoint(st, cfg, 1, true);
+  CHECK(!mtp.ok() && mtp.problems.front().rfind("missing mtp.", 0) == 0);      // this checkpoint has no predictor
+  return 0;
+}
+
+// Byte-level BPE from a GGUF vocabulary: every text comes back from decode(encode(text)), the pre-tokeniser loses no
+// byte, special tokens are matched verbatim only when asked to.
+static int test_tokenizer(const std::string& gguf_path) {
+  pk::GgufFile f(gguf_path);
+  const pk::BpeTokenizer tok = pk::BpeTokenizer::from_gguf(f);
+  CHECK(tok.vocab_size() > 256);
+  const char* texts[] = {"Hello, world! It's me.", "  leading spaces and\ttabs\n\nnewlines  ", "x=1+2;y=[3,4]", "na\xc3\xafve caf\xc3\xa9", "", "   ",
+                         "12345 67 8", "<|eos|>after special<|eos|>", "line1\nline2\r\n  indented", "\xf0\x9f\x98\x80 emoji"};
+  for (const char* t : texts) {
+    const std::string text(t);
+    const std::vector<int> ids = tok.encode(text);
+    CHECK(tok.decode(ids) == text);
+    for (int id : ids) CHECK(id >= 0 && id < tok.vocab_size());
+    std::string glued;
+    for (const std::string& piece : pk::BpeTokenizer::pre_tokenize(text)) glued += piece;
+    CHECK(glued == text);
+  }
+  const int eos = tok.token_id("<|eos|>");
+  CHECK(eos >= 0);
+  const std::vector<int> sp = tok.encode("<|eos|>x", true), plain = tok.encode("<|eos|>x", false);
+  CHECK(sp.size() == 2 && sp[0] == eos && plain.size() > 2);
+  CHECK(tok.decode(sp, true) == "x");
   return 0;
 }
 
@@ -352,12 +393,14 @@ static int test_spec_policy() {
 
 int main(int argc, char** argv) {
   if (argc < 4) {
-    std::fprintf(stderr, "usage: host_selftest file.gguf safetensors_dir scratch_dir\n");
+    std::fprintf(stderr, "usage: host_selftest file.gguf safetensors_dir scratch_dir [tokenizer.gguf]\n");
     return 2;
   }
   try {
     if (test_json()) return 1;
     if (test_readers(argv[1], argv[2])) return 1;
+    if (test_qwen_audit(argv[2])) return 1;
+    if (argc > 4 && test_tokenizer(argv[4])) return 1;
     if (test_sampler()) return 1;
     if (test_control_plane(argv[3])) return 1;
     if (test_protocol()) return 1;

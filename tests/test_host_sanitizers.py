@@ -1,4 +1,4 @@
-"""The engine's host C++ (JSON, readers, sampler, rendezvous, command channel, protocol model) built with
+"""The engine's host C++ (JSON, readers, sampler, checkpoint audit, rendezvous, command channel, protocol models) built with
 AddressSanitizer + UndefinedBehaviorSanitizer, and the protocol model again under ThreadSanitizer."""
 import shutil
 import subprocess
@@ -8,7 +8,8 @@ import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 SRC = [ROOT / "csrc" / "tests" / "host_selftest.cpp"] + [ROOT / "csrc" / "engine" / f for f in
-                                                        ("json.cpp", "gguf_reader.cpp", "safetensors.cpp", "sampler.cpp", "control_plane.cpp")]
+                                                        ("json.cpp", "gguf_reader.cpp", "safetensors.cpp", "sampler.cpp", "control_plane.cpp", "qwen_audit.cpp",
+                                                         "qwen_config.cpp", "tokenizer.cpp")]
 GXX = shutil.which("g++", path="/usr/bin") or shutil.which("g++")
 
 
@@ -18,7 +19,33 @@ def _inputs(tmp_path):
     cfg = qh.QwenHybridConfig.tiny(layers=2, hidden=128, inter=256, vocab=256)
     qh.save_checkpoint(tmp_path / "st", cfg, qh.random_checkpoint(cfg, seed=0))
     (tmp_path / "scratch").mkdir()
-    return [str(tmp_path / "m.gguf"), str(tmp_path / "st"), str(tmp_path / "scratch")]
+    return [str(tmp_path / "m.gguf"), str(tmp_path / "st"), str(tmp_path / "scratch"), str(_tokenizer_gguf(tmp_path))]
+
+
+def _tokenizer_gguf(tmp_path):
+    """A small byte-level BPE vocabulary trained here and stored as GGUF tokenizer metadata."""
+    import json
+    import numpy as np
+    from tokenizers import Tokenizer, models, pre_tokenizers, trainers
+    from pocketllm_b200.formats import gguf
+    corpus = ["The quick brown fox jumps over the lazy dog.", "It's 2024, isn't it? We've seen 1,234 things; they'll see more!",
+              "def f(x):\n    return x * 2  # twice\n\n", "naïve café über straße", "hello world hello there general kenobi"] * 3
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=400, initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), special_tokens=["<|eos|>"]))
+    model = json.loads(tok.to_str())["model"]
+    tokens = [k for k, _ in sorted(model["vocab"].items(), key=lambda kv: kv[1])]
+    merges = [m if isinstance(m, str) else " ".join(m) for m in model["merges"]]
+    w = gguf.GGUFWriter()
+    w.add_meta("general.architecture", "minimax-m2")
+    w.add_meta("tokenizer.ggml.model", "gpt2")
+    w.add_meta("tokenizer.ggml.tokens", tokens)
+    w.add_meta("tokenizer.ggml.merges", merges)
+    w.add_meta("tokenizer.ggml.token_type", [3 if t == "<|eos|>" else 1 for t in tokens])
+    w.add_tensor("dummy", np.zeros(32, np.float32), "f32")
+    path = tmp_path / "tok.gguf"
+    w.write(path)
+    return path
 
 
 @pytest.mark.skipif(GXX is None, reason="no g++")
