@@ -14,6 +14,8 @@
 #include "../common/pk_comm_host.hpp"
 #include "../engine/qwen_audit.hpp"
 #include "../engine/tokenizer.hpp"
+#include "../engine/dsv4_config.hpp"
+#include "../engine/weight_source.hpp"
 #include "../engine/control_plane.hpp"
 #include "../engine/gguf_reader.hpp"
 #include "../engine/json.hpp"
@@ -105,6 +107,50 @@ static int test_tokenizer(const std::string& gguf_path) {
   const std::vector<int> sp = tok.encode("<|eos|>x", true), plain = tok.encode("<|eos|>x", false);
   CHECK(sp.size() == 2 && sp[0] == eos && plain.size() > 2);
   CHECK(tok.decode(sp, true) == "x");
+  return 0;
+}
+
+// Container-agnostic tensor lookup over both formats, and the DeepSeek-V4 config parser (defaults, validation).
+static int test_weight_source_and_dsv4_config(const std::string& gguf_path, const std::string& st_dir) {
+  bool other_family = false;
+  try {
+    pk::open_weight_source(gguf_path);                  // a MiniMax file is not a DeepSeek-V4 checkpoint
+  } catch (const std::exception&) {
+    other_family = true;
+  }
+  CHECK(other_family);
+  for (const std::string& path : {st_dir}) {
+    auto src = pk::open_weight_source(path);
+    const std::vector<std::string> names = src->names();
+    CHECK(!names.empty());
+    uint64_t total = 0;
+    for (const std::string& n : names) {
+      const pk::TensorView v = src->get(n);
+      CHECK(v.found && v.data != nullptr && v.nbytes > 0 && !v.shape.empty());
+      total += v.data[0] + v.data[v.nbytes - 1];       // first and last byte are inside the mapping
+    }
+    (void)total;
+    CHECK(!src->get("no.such.tensor").found);
+    bool threw = false;
+    try {
+      src->require("no.such.tensor");
+    } catch (const std::exception&) {
+      threw = true;
+    }
+    CHECK(threw);
+  }
+  pk::Dsv4Config cfg = pk::Dsv4Config::from_json(pk::Json::parse("{\"n_layers\": 4, \"dim\": 256, \"n_heads\": 4, \"o_groups\": 2, \"n_routed_experts\": 8}"));
+  CHECK(cfg.n_layers == 4 && cfg.dim == 256 && cfg.head_dim == 512 && cfg.index_topk == 512);      // the rest keeps the defaults
+  cfg.validate(2);
+  bool refused = false;
+  try {
+    cfg.validate(3);                                    // three ranks divide neither heads nor experts
+  } catch (const std::exception&) {
+    refused = true;
+  }
+  CHECK(refused);
+  const pk::Dsv4Config again = pk::Dsv4Config::from_json(cfg.to_json());
+  CHECK(again.n_layers == cfg.n_layers && again.dim == cfg.dim && again.score_func == cfg.score_func);
   return 0;
 }
 
@@ -400,6 +446,7 @@ int main(int argc, char** argv) {
     if (test_json()) return 1;
     if (test_readers(argv[1], argv[2])) return 1;
     if (test_qwen_audit(argv[2])) return 1;
+    if (test_weight_source_and_dsv4_config(argv[1], argv[2])) return 1;
     if (argc > 4 && test_tokenizer(argv[4])) return 1;
     if (test_sampler()) return 1;
     if (test_control_plane(argv[3])) return 1;

@@ -9,7 +9,7 @@ import pytest
 ROOT = Path(__file__).resolve().parent.parent
 SRC = [ROOT / "csrc" / "tests" / "host_selftest.cpp"] + [ROOT / "csrc" / "engine" / f for f in
                                                         ("json.cpp", "gguf_reader.cpp", "safetensors.cpp", "sampler.cpp", "control_plane.cpp", "qwen_audit.cpp",
-                                                         "qwen_config.cpp", "tokenizer.cpp")]
+                                                         "qwen_config.cpp", "tokenizer.cpp", "weight_source.cpp", "dsv4_config.cpp")]
 GXX = shutil.which("g++", path="/usr/bin") or shutil.which("g++")
 
 
