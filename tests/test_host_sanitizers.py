@@ -59,3 +59,23 @@ def test_host_selftest_under_sanitizers(tmp_path, flags):
     assert b.returncode == 0, b.stderr[-3000:]
     r = subprocess.run([str(exe), *_inputs(tmp_path)], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "host_selftest=ok" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+@pytest.mark.skipif(GXX is None, reason="no g++")
+def test_kv_swap_tier_and_lru_map_host_only_under_asan(tmp_path):
+    """The KV swap tier in its host-only mode and the LRU slot map under AddressSanitizer + UBSan. The CUDA runtime is
+    linked (the sources also hold the device paths) but never called."""
+    cuda = Path("/usr/local/cuda")
+    if not (cuda / "include" / "cuda_runtime.h").exists() or not list((cuda / "lib64").glob("libcudart.so*")):
+        pytest.skip("CUDA toolkit headers / runtime not found")
+    eng = ROOT / "csrc" / "engine"
+    exe = tmp_path / "host_swap_selftest"
+    cmd = [GXX, "-std=c++17", "-O1", "-g", "-pthread", "-fsanitize=address,undefined", "-fno-sanitize-recover=all", f"-I{cuda / 'include'}",
+           str(ROOT / "csrc" / "tests" / "host_swap_selftest.cpp"), str(eng / "kv_swap.cpp"), str(eng / "staging.cpp"), f"-L{cuda / 'lib64'}",
+           "-lcudart", f"-Wl,-rpath,{cuda / 'lib64'}", "-o", str(exe)]
+    b = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    if b.returncode != 0 and ("cannot find -l" in b.stderr or "libasan" in b.stderr or "libubsan" in b.stderr):
+        pytest.skip("sanitizer or CUDA runtime library is not installed")
+    assert b.returncode == 0, b.stderr[-3000:]
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env={"ASAN_OPTIONS": "protect_shadow_gap=0:detect_leaks=0"})
+    assert r.returncode == 0 and "host_swap_selftest=ok" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
