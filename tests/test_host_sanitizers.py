@@ -79,3 +79,57 @@ def test_kv_swap_tier_and_lru_map_host_only_under_asan(tmp_path):
     assert b.returncode == 0, b.stderr[-3000:]
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env={"ASAN_OPTIONS": "protect_shadow_gap=0:detect_leaks=0"})
     assert r.returncode == 0 and "host_swap_selftest=ok" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+@pytest.mark.skipif(GXX is None, reason="no g++")
+@pytest.mark.parametrize("mode", ["scripted", "worker"])
+def test_openai_front_end_under_asan(tmp_path, mode):
+    """The C++ OpenAI front end built with AddressSanitizer + UBSan and driven over HTTP: plain and streamed completions,
+    log-probability reports, a lost step, a bad request; with its scripted engine and with a Python model worker."""
+    import http.client
+    import json
+    import os
+    import sys
+    eng = ROOT / "csrc" / "engine"
+    exe = tmp_path / "host_server_selftest"
+    cmd = [GXX, "-std=c++17", "-O1", "-g", "-pthread", "-fsanitize=address,undefined", "-fno-sanitize-recover=all",
+           str(ROOT / "csrc" / "tests" / "host_server_selftest.cpp"), *(str(eng / f) for f in ("openai_server.cpp", "http_server.cpp", "json.cpp", "sampler.cpp")),
+           "-o", str(exe)]
+    b = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    if b.returncode != 0 and ("cannot find -l" in b.stderr or "libasan" in b.stderr or "libubsan" in b.stderr):
+        pytest.skip("sanitizer runtime is not installed")
+    assert b.returncode == 0, b.stderr[-3000:]
+    env = dict(os.environ, PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""), ASAN_OPTIONS="detect_leaks=0")
+    proc = subprocess.Popen([str(exe), sys.executable, mode, "Hello ☠ world"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+    try:
+        line = proc.stdout.readline()
+        assert line.startswith("openai_server_listening"), (line, proc.stderr.read() if proc.poll() is not None else "")
+        port = int(dict(kv.split("=") for kv in line.split()[1:])["port"])
+
+        def post(body, path="/v1/chat/completions"):
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=60)
+            c.request("POST", path, json.dumps(body), {"Content-Type": "application/json"})
+            r = c.getresponse()
+            data = r.read().decode()
+            c.close()
+            return r.status, data
+
+        chat = {"messages": [{"role": "user", "content": "hi"}]}
+        st, data = post(dict(chat, max_tokens=5))
+        assert st == 200 and json.loads(data)["choices"][0]["message"]["content"] == "Hello"
+        st, data = post(dict(chat, max_tokens=3, logprobs=True, top_logprobs=2))
+        assert st == 200 and [e["token"] for e in json.loads(data)["choices"][0]["logprobs"]["content"]] == ["H", "e", "l"]
+        st, data = post(dict(chat, max_tokens=4, stream=True, stream_options={"include_usage": True}))
+        assert st == 200 and "data: [DONE]" in data and '"content":"H"' in data.replace(" ", "")
+        st, data = post(dict(chat, max_tokens=30))                          # runs into the scripted step failure
+        assert st == 500 and json.loads(data)["error"]["type"] == "engine_error"
+        assert post({"messages": []})[0] == 400 and post(dict(chat, max_tokens=100000))[0] == 400
+        assert post(dict(chat, max_tokens=2))[0] == 200                     # and serves on
+        post({}, "/shutdown")
+        proc.wait(timeout=60)
+        out, err = proc.stdout.read(), proc.stderr.read()
+        assert proc.returncode == 0 and "host_server_selftest=ok" in out, (out[-2000:], err[-4000:])
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+            proc.wait(timeout=20)
