@@ -125,6 +125,22 @@ def test_openai_front_end_under_asan(tmp_path, mode):
         assert st == 500 and json.loads(data)["error"]["type"] == "engine_error"
         assert post({"messages": []})[0] == 400 and post(dict(chat, max_tokens=100000))[0] == 400
         assert post(dict(chat, max_tokens=2))[0] == 200                     # and serves on
+        # malformed traffic must not bring the process down (or trip the sanitizers)
+        import socket
+        for raw in (b"GARBAGE\r\n\r\n", b"POST /v1/chat/completions HTTP/1.1\r\nContent-Length: 999999\r\n\r\n{\"messages\"",
+                    b"GET /" + b"a" * 70000 + b" HTTP/1.1\r\n\r\n", b"POST /v1/chat/completions HTTP/1.1\r\nContent-Length: -5\r\n\r\n",
+                    b"POST /v1/chat/completions HTTP/1.1\r\nContent-Length: 7\r\n\r\nnotjson", b"\x00\xff\xfe" * 100, b""):
+            with socket.create_connection(("127.0.0.1", port), timeout=10) as so:
+                so.settimeout(3)
+                if raw:
+                    so.sendall(raw)
+                try:
+                    so.shutdown(socket.SHUT_WR)
+                    while so.recv(65536):
+                        pass
+                except OSError:
+                    pass
+        assert post(dict(chat, max_tokens=2))[0] == 200
         post({}, "/shutdown")
         proc.wait(timeout=60)
         out, err = proc.stdout.read(), proc.stderr.read()
