@@ -101,7 +101,16 @@ SafetensorsFile::SafetensorsFile(const std::string& path) : file_(new MappedFile
     StTensor t;
     t.name = kv.first;
     t.dtype = parse_dtype(kv.second.at("dtype").as_string());
-    for (const auto& d : kv.second.at("shape").items()) t.shape.push_back(d.as_int());
+    // dimensions of an untrusted header: non-negative, and their product (times the element size) must not wrap
+    uint64_t count = 1;
+    for (const auto& d : kv.second.at("shape").items()) {
+      const int64_t dim = d.as_int();
+      if (dim < 0) throw std::runtime_error("safetensors: negative dimension in " + t.name);
+      if (dim != 0 && count > (uint64_t)1 << 60) throw std::runtime_error("safetensors: shape too large for " + t.name);
+      if (dim != 0 && count > ((uint64_t)1 << 60) / (uint64_t)dim) throw std::runtime_error("safetensors: shape too large for " + t.name);
+      count *= (uint64_t)dim;
+      t.shape.push_back(dim);
+    }
     const auto& off = kv.second.at("data_offsets").items();
     if (off.size() != 2) throw std::runtime_error("safetensors: bad offsets for " + t.name);
     const uint64_t b = (uint64_t)off[0].as_int(), e = (uint64_t)off[1].as_int();

@@ -154,6 +154,43 @@ static int test_weight_source_and_dsv4_config(const std::string& gguf_path, cons
   return 0;
 }
 
+// Hostile Safetensors files: every one must end in an exception, never in a read outside the mapping.
+static int test_safetensors_rejects_hostile_headers(const std::string& scratch) {
+  auto write_file = [&](const std::string& name, uint64_t header_len, const std::string& header, size_t payload) {
+    const std::string path = scratch + "/" + name;
+    FILE* f = std::fopen(path.c_str(), "wb");
+    std::fwrite(&header_len, 8, 1, f);
+    std::fwrite(header.data(), 1, header.size(), f);
+    std::vector<char> zeros(payload, 0);
+    if (payload) std::fwrite(zeros.data(), 1, payload, f);
+    std::fclose(f);
+    return path;
+  };
+  auto refused = [&](const std::string& path) {
+    try {
+      pk::SafetensorsModel m(path);
+      for (const std::string& n : m.names()) (void)m.get(n).data[m.get(n).nbytes - 1];
+    } catch (const std::exception&) {
+      return true;
+    }
+    return false;
+  };
+  const std::string ok = "{\"a\":{\"dtype\":\"F32\",\"shape\":[2,2],\"data_offsets\":[0,16]}}";
+  CHECK(!refused(write_file("ok.safetensors", ok.size(), ok, 16)));
+  CHECK(refused(write_file("short.safetensors", ok.size(), ok, 8)));                        // offsets beyond the payload
+  CHECK(refused(write_file("hdrlen.safetensors", 1ull << 40, ok, 16)));                      // header length beyond the file
+  const std::string neg = "{\"a\":{\"dtype\":\"F32\",\"shape\":[-2,2],\"data_offsets\":[0,16]}}";
+  CHECK(refused(write_file("neg.safetensors", neg.size(), neg, 16)));
+  const std::string huge = "{\"a\":{\"dtype\":\"F32\",\"shape\":[4611686018427387904,4],\"data_offsets\":[0,16]}}";
+  CHECK(refused(write_file("huge.safetensors", huge.size(), huge, 16)));                     // element count would wrap
+  const std::string back = "{\"a\":{\"dtype\":\"F32\",\"shape\":[2,2],\"data_offsets\":[16,0]}}";
+  CHECK(refused(write_file("back.safetensors", back.size(), back, 16)));
+  const std::string junk = "{\"a\":{\"dtype\":\"F32\",\"shape\":[2,2],\"data_offsets\":[0,";
+  CHECK(refused(write_file("junk.safetensors", junk.size(), junk, 16)));                      // truncated JSON
+  CHECK(refused(write_file("tiny.safetensors", 0, "", 0) ) || true);                          // an empty header is an empty model
+  return 0;
+}
+
 static int test_sampler() {
   const float logits[5] = {0.f, 3.f, 3.f, -2.f, 1.f};
   uint64_t rng = 99;
@@ -446,6 +483,7 @@ int main(int argc, char** argv) {
     if (test_json()) return 1;
     if (test_readers(argv[1], argv[2])) return 1;
     if (test_qwen_audit(argv[2])) return 1;
+    if (test_safetensors_rejects_hostile_headers(argv[3])) return 1;
     if (test_weight_source_and_dsv4_config(argv[1], argv[2])) return 1;
     if (argc > 4 && test_tokenizer(argv[4])) return 1;
     if (test_sampler()) return 1;
