@@ -21,7 +21,7 @@ def test_rmsnorm_quant_equals_norm_then_quantise(M, K, terms):
     y, q, sc = ops.rmsnorm_quant(x, gamma, mode=1, eps=1e-6, terms=terms)
     xf = x.float()
     want = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * (1 + gamma)
-    assert _rel_err(y, want) < 4e-3
+    assert _rel_err(y, want) < 5e-3
     # the two norm kernels add the squares in different orders: rows may differ by a bf16 rounding step here and there
     assert _rel_err(y, ops.rmsnorm(x, gamma, mode=1, eps=1e-6)) < 1e-3
     q_ref, sc_ref = ops.quant_act_fp8(y, terms)
