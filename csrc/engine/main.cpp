@@ -62,6 +62,7 @@ struct Args {
   // checkpoint tools and smoke / bench modes
   std::string inspect_tensor, model_worker, worker_script = "Hello", worker_tokenizer_path;
   int worker_ranks = 1, worker_port = 29641;
+  std::string qwen_dspark;   // directory of an external block drafter
   bool qwen_audit = false, smoke_forward = false;
   int smoke_layers = 4, resident_bench = 0;
 };
@@ -189,11 +190,17 @@ Args parse(int argc, char** argv) {
     else if (f == "--sidecar") {}                                // --serve always runs the templating sidecar
     else if (f == "--forward-token" || f == "--position")
       throw std::runtime_error(f + ": the hybrid engine consumes positions in order (recurrent state); feed the tokens with --token-ids");
-    else if (f == "--qwen-dspark")
-      throw std::runtime_error("--qwen-dspark: the external block drafter runs beside the engine in the Python server "
-                               "(python -m pocketllm_b200.server.openai --model qwen --ckpt DIR --qwen-dspark DRAFTER_DIR)");
+    else if (f == "--qwen-dspark") a.qwen_dspark = need(i);
     else if (f == "--help" || f == "-h") { usage(); std::exit(0); }
     else throw std::runtime_error("unknown flag " + f);
+  }
+  if (!a.qwen_dspark.empty()) {
+    // the drafter's layers run in the Python runtime beside the engine: a served model gets both through a model worker
+    if (!a.serve)
+      throw std::runtime_error("--qwen-dspark: the external block drafter runs beside the engine in the Python runtime; serve it with "
+                               "--serve --qwen-dspark DIR (model worker) or python -m pocketllm_b200.server.openai --model qwen --ckpt DIR --qwen-dspark DIR");
+    if (a.model_worker.empty()) a.model_worker = "qwen";
+    if (a.model_worker != "qwen") throw std::runtime_error("--qwen-dspark goes with the qwen model worker");
   }
   if (a.device < 0) a.device = a.tp_rank;
   return a;
@@ -392,6 +399,7 @@ int serve_worker(const Args& a) {
   if (!a.ckpt.empty()) { cmd.push_back("--ckpt"); cmd.push_back(a.ckpt); }
   if (!a.worker_tokenizer_path.empty()) { cmd.push_back("--tokenizer-path"); cmd.push_back(a.worker_tokenizer_path); }
   if (a.model_worker == "scripted") { cmd.push_back("--script"); cmd.push_back(a.worker_script); }
+  if (!a.qwen_dspark.empty()) { cmd.push_back("--qwen-dspark"); cmd.push_back(a.qwen_dspark); }
   auto eng = pk::make_worker_engine(cmd);
   pk::Sidecar sidecar(sidecar_command(a));
   pk::HttpServer http(a.host, a.port);

@@ -101,6 +101,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-context", type=int, default=4096)
     ap.add_argument("--tokenizer-path", default=None)
     ap.add_argument("--script", default="Hello", help="scripted: the text the stand-in model generates")
+    ap.add_argument("--qwen-dspark", default="", help="qwen: directory of an external DSpark block drafter (greedy requests run as speculative rounds)")
     args = ap.parse_args(argv)
     import os
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
@@ -121,7 +122,8 @@ def main(argv=None) -> int:
         backend = ScriptedBackend(args.script)
     else:
         from . import backends
-        backend, _ = backends.build(args.model, args.ckpt, args.max_context, tokenizer_path=args.tokenizer_path)
+        backend, _ = backends.build(args.model, args.ckpt, args.max_context, tokenizer_path=args.tokenizer_path,
+                                    qwen_dspark=args.qwen_dspark or None)
     if world > 1:
         from . import distributed
         if rank != 0:
