@@ -289,3 +289,68 @@ def test_tool_choice_and_parallel_tool_calls_become_instructions():
     assert named[0]["content"].startswith("Be brief.") and "`get_weather`" in named[0]["content"] and len(named) == 2
     with pytest.raises(oa.BadRequest):
         oa.with_tool_directive(msgs, tools, {"type": "function", "function": {"name": "nope"}}, None)
+
+
+def test_qwen_backend_logprob_and_speculator_paths_with_a_stand_in_engine():
+    """The Qwen backend's control flow over a stand-in engine: log-probability requests read every step's logits and bypass
+    the speculator; plain greedy requests go through the speculator when there is one."""
+    import torch
+    from pocketllm_b200.server.backends import QwenBackend
+
+    class Engine:
+        tp_world = 1
+
+        def __init__(self):
+            self.fed, self.calls = [], []
+
+        def reset(self):
+            self.fed = []
+
+        def _z(self):
+            z = torch.zeros(8)
+            z[(sum(self.fed) + len(self.fed)) % 8] = 4.0
+            return z
+
+        def prefill(self, tokens):
+            self.calls.append("prefill")
+            self.fed = list(tokens)
+            return int(self._z().argmax())
+
+        def logits(self, row=0):
+            return self._z()
+
+        def forward_rows(self, tokens):
+            self.calls.append("rows")
+            out = []
+            for t in tokens:
+                self.fed.append(t)
+                out.append(int(self._z().argmax()))
+            return out
+
+        def decode(self, n, sync_each_step=False):
+            self.calls.append("decode")
+            out = []
+            for _ in range(n):
+                out += self.forward_rows([int(self._z().argmax())])
+            return out
+
+    class Spec:
+        def __init__(self):
+            self.used = 0
+
+        def prefill(self, prompt):
+            self.used += 1
+            return 1
+
+        def decode(self, last, n):
+            return [2] * n
+
+    plain = list(QwenBackend(Engine()).generate([1, 2, 3], SamplingParams(max_tokens=4)))
+    eng = Engine()
+    with_lp = list(QwenBackend(eng).generate([1, 2, 3], SamplingParams(max_tokens=4, logprobs=2)))
+    assert [t.token for t in with_lp] == plain and "decode" not in eng.calls
+    assert all(t.top[0][0] == t.token and len(t.top) == 2 and t.logprob < 0 for t in with_lp)
+    spec = Spec()
+    assert list(QwenBackend(Engine(), speculator=spec).generate([1], SamplingParams(max_tokens=3))) == [1, 2, 2] and spec.used == 1
+    lp_spec = list(QwenBackend(Engine(), speculator=spec).generate([1, 2, 3], SamplingParams(max_tokens=4, logprobs=0)))
+    assert [t.token for t in lp_spec] == plain and spec.used == 1          # log-probabilities: the speculator is bypassed
